@@ -1,0 +1,119 @@
+// Python bindings (torch tensors -> raw-pointer host API). Only this file sees torch headers.
+#include <torch/extension.h>
+#include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "host_api.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+const void* opt_ptr(const c10::optional<torch::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+void check_bf16_2d(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16, name, " must be bf16");
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, name, " must be 2-D with unit inner stride");
+}
+
+// C = epilogue(A_op * B_op^T). a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn).
+void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, torch::Tensor& c, int64_t flags,
+          const c10::optional<torch::Tensor>& bias, const c10::optional<torch::Tensor>& residual,
+          const c10::optional<torch::Tensor>& aux, const c10::optional<torch::Tensor>& c2, double alpha,
+          int64_t split_k, int64_t bn, const c10::optional<torch::Tensor>& status, int64_t shuffle_cout,
+          int64_t out_w, int64_t out_h, int64_t sms) {
+  check_bf16_2d(a, "a");
+  check_bf16_2d(b, "b");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm: contraction mismatch ", K, " vs ", Kb);
+  tb::GemmOperand A{a.data_ptr(), a.stride(0), a_mn ? 1 : 0};
+  tb::GemmOperand B{b.data_ptr(), b.stride(0), b_mn ? 1 : 0};
+  tb::GemmEpilogue e{};
+  e.flags = static_cast<int>(flags);
+  e.C = c.data_ptr();
+  e.ldc = c.dim() >= 2 ? c.stride(c.dim() - 2) : c.size(-1);
+  if (shuffle_cout > 0) e.ldc = shuffle_cout;
+  e.C2 = c2.has_value() ? c2->data_ptr() : nullptr;
+  e.ldc2 = c2.has_value() ? c2->stride(0) : 0;
+  e.bias = opt_ptr(bias);
+  e.residual = opt_ptr(residual);
+  e.ldr = residual.has_value() ? residual->stride(residual->dim() - 2) : 0;
+  e.aux = opt_ptr(aux);
+  e.ldaux = aux.has_value() ? aux->stride(0) : 0;
+  e.alpha = static_cast<float>(alpha);
+  e.status = status.has_value() ? status->data_ptr() : nullptr;
+  e.shuffle_cout = static_cast<int>(shuffle_cout);
+  e.out_w = static_cast<int>(out_w);
+  e.out_h = static_cast<int>(out_h);
+  const int rc = tb::gemm_bf16(A, B, M, N, K, e, static_cast<int>(split_k), static_cast<int>(bn),
+                               sms > 0 ? static_cast<int>(sms) : sm_count(), cur_stream());
+  TORCH_CHECK(rc == 0, "terra_b200 gemm launch failed, code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+}
+
+// x: [B,H,W,Cin] bf16 NHWC, w: [Cout, 9*Cin_pad] bf16, y: [B,Ho,Wo,Cout]
+void conv3x3_fwd(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& y, int64_t stride, int64_t flags,
+                 const c10::optional<torch::Tensor>& bias, const c10::optional<torch::Tensor>& residual,
+                 const c10::optional<torch::Tensor>& status) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 4, "x: NHWC bf16");
+  TORCH_CHECK(w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.dim() == 2, "w: [Cout, 9*Cin_pad] bf16");
+  TORCH_CHECK(y.is_contiguous(), "y must be contiguous");
+  const c10::cuda::CUDAGuard guard(x.device());
+  tb::GemmEpilogue e{};
+  e.flags = static_cast<int>(flags);
+  e.C = y.data_ptr();
+  e.ldc = y.size(3);
+  e.bias = opt_ptr(bias);
+  e.residual = opt_ptr(residual);
+  e.ldr = y.size(3);
+  e.alpha = 1.0f;
+  e.status = status.has_value() ? status->data_ptr() : nullptr;
+  const int rc = tb::conv3x3_fwd_bf16(x.data_ptr(), w.data_ptr(), x.size(0), x.size(1), x.size(2), x.size(3), w.size(0),
+                                      static_cast<int>(stride), e, sm_count(), cur_stream());
+  TORCH_CHECK(rc == 0, "terra_b200 conv3x3_fwd launch failed, code ", rc);
+}
+
+// dw: [9, Cout, Cin] fp32 (zeroed by the caller)
+void conv3x3_wgrad(const torch::Tensor& x, const torch::Tensor& dy, torch::Tensor& dw, int64_t stride, int64_t split_k,
+                   const c10::optional<torch::Tensor>& status) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 4, "x: NHWC bf16");
+  TORCH_CHECK(dy.scalar_type() == torch::kBFloat16 && dy.is_contiguous() && dy.dim() == 4, "dy: NHWC bf16");
+  TORCH_CHECK(dw.scalar_type() == torch::kFloat32 && dw.is_contiguous(), "dw: fp32 [9,Cout,Cin]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int rc = tb::conv3x3_wgrad_bf16(x.data_ptr(), dy.data_ptr(), dw.data_ptr<float>(), x.size(0), x.size(1),
+                                        x.size(2), x.size(3), dy.size(3), static_cast<int>(stride),
+                                        static_cast<int>(split_k), status.has_value() ? status->data_ptr() : nullptr,
+                                        sm_count(), cur_stream());
+  TORCH_CHECK(rc == 0, "terra_b200 conv3x3_wgrad launch failed, code ", rc);
+}
+
+}  // namespace
+
+void bind_elementwise(pybind11::module_& m);
+void bind_attention(pybind11::module_& m);
+void bind_copy_engine(pybind11::module_& m);
+void bind_comm(pybind11::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogues");
+  m.def("conv3x3_fwd", &conv3x3_fwd, "implicit-GEMM 3x3 convolution (NHWC bf16)");
+  m.def("conv3x3_wgrad", &conv3x3_wgrad, "3x3 convolution weight gradient (fp32 atomics)");
+  bind_elementwise(m);
+  bind_attention(m);
+  bind_copy_engine(m);
+  bind_comm(m);
+}

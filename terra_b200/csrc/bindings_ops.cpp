@@ -1,0 +1,171 @@
+// Bindings for the memory-bound kernels and window attention.
+#include <torch/extension.h>
+#include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "host_api.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+const void* opt_ptr(const c10::optional<torch::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+void* opt_mut(const c10::optional<torch::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+void need(bool ok, const char* what) { TORCH_CHECK(ok, "terra_b200: ", what); }
+void rc_check(int rc, const char* what) { TORCH_CHECK(rc == 0, "terra_b200: ", what, " failed with code ", rc); }
+
+void layernorm_fwd(const torch::Tensor& x, const torch::Tensor& g, const torch::Tensor& b, torch::Tensor& y,
+                   torch::Tensor& mean, torch::Tensor& rstd, double eps) {
+  need(x.is_cuda() && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "layernorm_fwd: x bf16 contiguous");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = x.size(-1);
+  rc_check(tb::layernorm_fwd(x.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
+                             rstd.data_ptr<float>(), x.numel() / C, C, static_cast<float>(eps), cur_stream()),
+           "layernorm_fwd");
+}
+
+void layernorm_bwd(const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& g, const torch::Tensor& mean,
+                   const torch::Tensor& rstd, torch::Tensor& dx, torch::Tensor& dg, torch::Tensor& db) {
+  need(dy.is_contiguous() && x.is_contiguous(), "layernorm_bwd: contiguous inputs");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = x.size(-1);
+  rc_check(tb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), g.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                             dx.data_ptr(), dg.data_ptr<float>(), db.data_ptr<float>(), x.numel() / C, C, cur_stream()),
+           "layernorm_bwd");
+}
+
+void colsum(const torch::Tensor& x, torch::Tensor& out) {
+  need(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == torch::kBFloat16, "colsum: 2-D bf16");
+  const c10::cuda::CUDAGuard guard(x.device());
+  rc_check(tb::colsum_bf16(x.data_ptr(), out.data_ptr<float>(), x.size(0), x.size(1), x.stride(0), cur_stream()),
+           "colsum");
+}
+
+void groupnorm_stats(const torch::Tensor& x, torch::Tensor& sums, int64_t groups) {
+  need(x.is_contiguous() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16, "groupnorm_stats: [B,HW,C] bf16");
+  const c10::cuda::CUDAGuard guard(x.device());
+  rc_check(tb::groupnorm_stats(x.data_ptr(), sums.data_ptr<float>(), x.size(0), x.size(1), x.size(2), groups, cur_stream()),
+           "groupnorm_stats");
+}
+
+void groupnorm_silu_apply(const torch::Tensor& x, const torch::Tensor& stats, const torch::Tensor& g,
+                          const torch::Tensor& b, torch::Tensor& y, int64_t groups) {
+  need(x.is_contiguous() && x.dim() == 3, "groupnorm_silu_apply: [B,HW,C]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  rc_check(tb::groupnorm_silu_apply(x.data_ptr(), stats.data_ptr<float>(), g.data_ptr(), b.data_ptr(), y.data_ptr(),
+                                    x.size(0), x.size(1), x.size(2), groups, cur_stream()),
+           "groupnorm_silu_apply");
+}
+
+void groupnorm_silu_bwd_reduce(const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& stats,
+                               const torch::Tensor& g, const torch::Tensor& b, torch::Tensor& red, int64_t groups) {
+  need(x.is_contiguous() && dy.is_contiguous() && x.dim() == 3, "groupnorm_silu_bwd_reduce: [B,HW,C]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  rc_check(tb::groupnorm_silu_bwd_reduce(dy.data_ptr(), x.data_ptr(), stats.data_ptr<float>(), g.data_ptr(), b.data_ptr(),
+                                         red.data_ptr<float>(), nullptr, nullptr, x.size(0), x.size(1), x.size(2), groups,
+                                         cur_stream()),
+           "groupnorm_silu_bwd_reduce");
+}
+
+void groupnorm_silu_bwd_apply(const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& stats,
+                              const torch::Tensor& red, const torch::Tensor& g, const torch::Tensor& b,
+                              torch::Tensor& dx, int64_t groups, double inv_count) {
+  need(x.is_contiguous() && dy.is_contiguous() && x.dim() == 3, "groupnorm_silu_bwd_apply: [B,HW,C]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  rc_check(tb::groupnorm_silu_bwd_apply(dy.data_ptr(), x.data_ptr(), stats.data_ptr<float>(), red.data_ptr<float>(),
+                                        g.data_ptr(), b.data_ptr(), dx.data_ptr(), x.size(0), x.size(1), x.size(2),
+                                        groups, static_cast<float>(inv_count), cur_stream()),
+           "groupnorm_silu_bwd_apply");
+}
+
+void masked_loss(const torch::Tensor& pred, const torch::Tensor& label, const c10::optional<torch::Tensor>& mask,
+                 int64_t kind, double grad_scale, torch::Tensor& loss_sum, const c10::optional<torch::Tensor>& grad) {
+  need(pred.is_contiguous() && label.is_contiguous() && pred.scalar_type() == torch::kBFloat16 &&
+           label.scalar_type() == torch::kBFloat16,
+       "masked_loss: bf16 contiguous pred/label");
+  const c10::cuda::CUDAGuard guard(pred.device());
+  rc_check(tb::masked_loss_fwd_bwd(pred.data_ptr(), label.data_ptr(), opt_ptr(mask), pred.numel(),
+                                   mask.has_value() ? mask->numel() : 0, static_cast<int>(kind),
+                                   static_cast<float>(grad_scale), loss_sum.data_ptr<float>(), opt_mut(grad), cur_stream()),
+           "masked_loss");
+}
+
+void adamw_step(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const torch::Tensor& grad,
+                const c10::optional<torch::Tensor>& param_bf16, double lr, double b1, double b2, double eps, double wd,
+                int64_t step, double grad_scale) {
+  need(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && grad.is_contiguous(), "adamw: contiguous");
+  need(master.scalar_type() == torch::kFloat32, "adamw: fp32 master");
+  const c10::cuda::CUDAGuard guard(master.device());
+  const double bc1 = 1.0 - std::pow(b1, static_cast<double>(step));
+  const double bc2 = 1.0 - std::pow(b2, static_cast<double>(step));
+  rc_check(tb::adamw_step(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(),
+                          grad.scalar_type() == torch::kBFloat16 ? 1 : 0, opt_mut(param_bf16), master.numel(),
+                          static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2), static_cast<float>(eps),
+                          static_cast<float>(wd), static_cast<float>(bc1), static_cast<float>(std::sqrt(bc2)),
+                          static_cast<float>(grad_scale), cur_stream()),
+           "adamw_step");
+}
+
+void window_attn(const torch::Tensor& qkv, torch::Tensor& out, const c10::optional<torch::Tensor>& bias_table,
+                 torch::Tensor& lse, int64_t B, int64_t Hh, int64_t Ww, int64_t heads, int64_t wh, int64_t ww,
+                 int64_t sh, int64_t sw, bool use_mask, int64_t grid_h, int64_t grid_w, int64_t row_offset,
+                 double scale) {
+  need(qkv.is_cuda() && qkv.is_contiguous() && qkv.scalar_type() == torch::kBFloat16, "window_attn: qkv bf16");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  tb::WindowAttnArgs a{};
+  a.qkv = qkv.data_ptr();
+  a.out = out.data_ptr();
+  a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
+  a.lse = lse.data_ptr<float>();
+  a.B = B; a.Hh = Hh; a.Ww = Ww;
+  a.C = qkv.size(-1) / 3;
+  a.num_heads = heads;
+  a.wh = wh; a.ww = ww; a.sh = sh; a.sw = sw;
+  a.use_mask = use_mask ? 1 : 0;
+  a.grid_h = grid_h; a.grid_w = grid_w; a.row_offset = row_offset;
+  a.scale = static_cast<float>(scale);
+  rc_check(tb::window_attn_fwd(a, cur_stream()), "window_attn_fwd");
+}
+
+void window_attn_bwd(const torch::Tensor& qkv, const torch::Tensor& dout, torch::Tensor& dqkv,
+                     const c10::optional<torch::Tensor>& bias_table, const c10::optional<torch::Tensor>& dbias_table,
+                     const torch::Tensor& lse, int64_t B, int64_t Hh, int64_t Ww, int64_t heads, int64_t wh, int64_t ww,
+                     int64_t sh, int64_t sw, bool use_mask, int64_t grid_h, int64_t grid_w, int64_t row_offset,
+                     double scale) {
+  need(qkv.is_contiguous() && dout.is_contiguous() && dqkv.is_contiguous(), "window_attn_bwd: contiguous");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  tb::WindowAttnArgs a{};
+  a.qkv = qkv.data_ptr();
+  a.dout = dout.data_ptr();
+  a.dqkv = dqkv.data_ptr();
+  a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
+  a.dbias_table = dbias_table.has_value() ? dbias_table->data_ptr<float>() : nullptr;
+  a.lse = const_cast<float*>(lse.data_ptr<float>());
+  a.B = B; a.Hh = Hh; a.Ww = Ww;
+  a.C = qkv.size(-1) / 3;
+  a.num_heads = heads;
+  a.wh = wh; a.ww = ww; a.sh = sh; a.sw = sw;
+  a.use_mask = use_mask ? 1 : 0;
+  a.grid_h = grid_h; a.grid_w = grid_w; a.row_offset = row_offset;
+  a.scale = static_cast<float>(scale);
+  rc_check(tb::window_attn_bwd(a, cur_stream()), "window_attn_bwd");
+}
+
+}  // namespace
+
+void bind_elementwise(pybind11::module_& m) {
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("colsum", &colsum);
+  m.def("groupnorm_stats", &groupnorm_stats);
+  m.def("groupnorm_silu_apply", &groupnorm_silu_apply);
+  m.def("groupnorm_silu_bwd_reduce", &groupnorm_silu_bwd_reduce);
+  m.def("groupnorm_silu_bwd_apply", &groupnorm_silu_bwd_apply);
+  m.def("masked_loss", &masked_loss);
+  m.def("adamw_step", &adamw_step);
+}
+
+void bind_attention(pybind11::module_& m) {
+  m.def("window_attn_fwd", &window_attn);
+  m.def("window_attn_bwd", &window_attn_bwd);
+}

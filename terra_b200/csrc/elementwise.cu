@@ -1,0 +1,605 @@
+// Memory-bound kernels: LayerNorm, GroupNorm(+SiLU), column sums, masked loss, fused AdamW.
+// All are single-pass over HBM where the math allows it, with 16-byte vector accesses.
+#include "common.cuh"
+#include "host_api.h"
+
+namespace tb {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 x = unpack_bf16x2(w[k]);
+    f[2 * k] = x.x;
+    f[2 * k + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+// ------------------------------------------------------------------------------------------ LayerNorm
+// One warp per row; the row lives in registers (VPL 16-byte vectors per lane).
+template <int VPL>
+__global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ gamma,
+                                                            const __nv_bfloat16* __restrict__ beta,
+                                                            __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                                                            float* __restrict__ rstd_out, long long rows, int C,
+                                                            float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int nvec = C >> 3;
+  for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+    float v[VPL][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        unpack8(xr[vi], v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[i][j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+      }
+    }
+    const float mean = warp_sum(s) / C;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[i][j] - mean;
+          q += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) / C + eps);
+    uint4* yr = reinterpret_cast<uint4*>(y + row * C);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float g[8], b[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(gamma)[vi], g);
+        unpack8(reinterpret_cast<const uint4*>(beta)[vi], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
+        yr[vi] = pack8(o);
+      }
+    }
+    if (lane == 0) {
+      mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ gamma,
+                                                            const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                            __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
+                                                            float* __restrict__ dbeta, long long rows, int C) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int nvec = C >> 3;
+  float ag[VPL][8], ab[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ag[i][j] = ab[i][j] = 0.f;
+  float g[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) unpack8(reinterpret_cast<const uint4*>(gamma)[vi], g[i]);
+  }
+  for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+    const uint4* dr = reinterpret_cast<const uint4*>(dy + row * C);
+    const float mu = mean[row], rs = rstd[row];
+    float xh[VPL][8], dv[VPL][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float xv[8], dyv[8];
+        unpack8(xr[vi], xv);
+        unpack8(dr[vi], dyv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xv[j] - mu) * rs;
+          ag[i][j] += dyv[j] * xh[i][j];
+          ab[i][j] += dyv[j];
+          dv[i][j] = dyv[j] * g[i][j];
+          s1 += dv[i][j];
+          s2 += dv[i][j] * xh[i][j];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+    uint4* or_ = reinterpret_cast<uint4*>(dx + row * C);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (dv[i][j] - s1 - xh[i][j] * s2);
+        or_[vi] = pack8(o);
+      }
+    }
+  }
+  // reduce the per-lane column partials across the block's warps through shared memory, then one atomic per column
+  extern __shared__ float sh[];   // [2][C]
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) sh[c] = 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&sh[vi * 8 + j], ag[i][j]);
+        atomicAdd(&sh[C + vi * 8 + j], ab[i][j]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    atomicAdd(&dgamma[c], sh[c]);
+    atomicAdd(&dbeta[c], sh[C + c]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ column sums
+__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
+                                                     long long rows, int C, long long ld, int rows_per_block) {
+  // thread -> one 8-wide column vector; blockDim.y rows in flight
+  const int nvec = C >> 3;
+  const int vi = blockIdx.y * blockDim.x + threadIdx.x;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long r0 = static_cast<long long>(blockIdx.x) * rows_per_block;
+  const long long r1 = min(rows, r0 + rows_per_block);
+  if (vi < nvec) {
+    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + r * ld + vi * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+  }
+  __shared__ float sh[8][32 * 8 + 1];
+  if (threadIdx.x < 32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sh[threadIdx.y][threadIdx.x * 8 + j] = acc[j];
+  }
+  __syncthreads();
+  if (threadIdx.y == 0 && vi < nvec) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+      for (int y = 0; y < blockDim.y; ++y) s += sh[y][threadIdx.x * 8 + j];
+      atomicAdd(&out[vi * 8 + j], s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ GroupNorm
+// x: [B, HW, C] bf16. Block = (C/8 column vectors) x (rows in flight); per-channel partials in shared memory,
+// folded to groups, two atomics per (block, group).
+__global__ void __launch_bounds__(512) groupnorm_stats_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              float* __restrict__ sums, long long HW, int C, int groups,
+                                                              int pix_per_block) {
+  extern __shared__ float sh[];  // [2][C]
+  const int nvec = C >> 3;
+  const int b = blockIdx.y;
+  for (int c = threadIdx.y * blockDim.x + threadIdx.x; c < 2 * C; c += blockDim.x * blockDim.y) sh[c] = 0.f;
+  __syncthreads();
+  const long long p0 = static_cast<long long>(blockIdx.x) * pix_per_block;
+  const long long p1 = min(HW, p0 + pix_per_block);
+  for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+    float s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long long p = p0 + threadIdx.y; p < p1; p += blockDim.y) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + (static_cast<long long>(b) * HW + p) * C + vi * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s[j] += f[j];
+        q[j] += f[j] * f[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      atomicAdd(&sh[vi * 8 + j], s[j]);
+      atomicAdd(&sh[C + vi * 8 + j], q[j]);
+    }
+  }
+  __syncthreads();
+  const int cpg = C / groups;
+  for (int g = threadIdx.y * blockDim.x + threadIdx.x; g < groups; g += blockDim.x * blockDim.y) {
+    float s = 0.f, q = 0.f;
+    for (int c = g * cpg; c < (g + 1) * cpg; ++c) {
+      s += sh[c];
+      q += sh[C + c];
+    }
+    atomicAdd(&sums[(b * groups + g) * 2 + 0], s);
+    atomicAdd(&sums[(b * groups + g) * 2 + 1], q);
+  }
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + __expf(-z)); }
+
+__global__ void __launch_bounds__(256) groupnorm_silu_apply_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                   const float* __restrict__ stats,
+                                                                   const __nv_bfloat16* __restrict__ gamma,
+                                                                   const __nv_bfloat16* __restrict__ beta,
+                                                                   __nv_bfloat16* __restrict__ y, long long HW, int C,
+                                                                   int groups, long long total_vec) {
+  const int nvec = C >> 3;
+  const int cpg = C / groups;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int vi = static_cast<int>(i % nvec);
+    const long long pix = i / nvec;
+    const int b = static_cast<int>(pix / HW);
+    float f[8], g[8], bt[8], o[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+    unpack8(reinterpret_cast<const uint4*>(gamma)[vi], g);
+    unpack8(reinterpret_cast<const uint4*>(beta)[vi], bt);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int grp = (vi * 8 + j) / cpg;
+      const float mu = stats[(b * groups + grp) * 2], rs = stats[(b * groups + grp) * 2 + 1];
+      const float z = (f[j] - mu) * rs * g[j] + bt[j];
+      o[j] = z * sigmoidf_(z);
+    }
+    reinterpret_cast<uint4*>(y)[i] = pack8(o);
+  }
+}
+
+// pass 1 of the backward: red[b][c] = {sum dz, sum dz * xhat}
+__global__ void __launch_bounds__(512) groupnorm_silu_bwd_reduce_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ stats,
+    const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta, float* __restrict__ red,
+    long long HW, int C, int groups, int pix_per_block) {
+  extern __shared__ float sh[];  // [2][C]
+  const int nvec = C >> 3;
+  const int cpg = C / groups;
+  const int b = blockIdx.y;
+  for (int c = threadIdx.y * blockDim.x + threadIdx.x; c < 2 * C; c += blockDim.x * blockDim.y) sh[c] = 0.f;
+  __syncthreads();
+  const long long p0 = static_cast<long long>(blockIdx.x) * pix_per_block;
+  const long long p1 = min(HW, p0 + pix_per_block);
+  for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+    float g[8], bt[8], mu[8], rs[8];
+    unpack8(reinterpret_cast<const uint4*>(gamma)[vi], g);
+    unpack8(reinterpret_cast<const uint4*>(beta)[vi], bt);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int grp = (vi * 8 + j) / cpg;
+      mu[j] = stats[(b * groups + grp) * 2];
+      rs[j] = stats[(b * groups + grp) * 2 + 1];
+    }
+    float s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long long p = p0 + threadIdx.y; p < p1; p += blockDim.y) {
+      const long long off = (static_cast<long long>(b) * HW + p) * C + vi * 8;
+      float f[8], d[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + off), f);
+      unpack8(*reinterpret_cast<const uint4*>(dy + off), d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (f[j] - mu[j]) * rs[j];
+        const float z = xh * g[j] + bt[j];
+        const float sg = sigmoidf_(z);
+        const float dz = d[j] * sg * (1.f + z * (1.f - sg));
+        s[j] += dz;
+        q[j] += dz * xh;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      atomicAdd(&sh[vi * 8 + j], s[j]);
+      atomicAdd(&sh[C + vi * 8 + j], q[j]);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.y * blockDim.x + threadIdx.x; c < C; c += blockDim.x * blockDim.y) {
+    atomicAdd(&red[(static_cast<long long>(b) * C + c) * 2 + 0], sh[c]);
+    atomicAdd(&red[(static_cast<long long>(b) * C + c) * 2 + 1], sh[C + c]);
+  }
+}
+
+// pass 2: dx = rstd * (dz*gamma - s1/n - xhat * s2/n), s1 = sum_c gamma_c red[b][c][0], s2 likewise with [1]
+__global__ void __launch_bounds__(256) groupnorm_silu_bwd_apply_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ stats,
+    const float* __restrict__ red, const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
+    __nv_bfloat16* __restrict__ dx, int B, long long HW, int C, int groups, float inv_count, long long total_vec) {
+  extern __shared__ float gs[];  // [B][groups][2]
+  const int cpg = C / groups;
+  for (int i = threadIdx.x; i < B * groups; i += blockDim.x) {
+    const int b = i / groups, g = i % groups;
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = g * cpg; c < (g + 1) * cpg; ++c) {
+      const float gm = __bfloat162float(gamma[c]);
+      s1 += gm * red[(static_cast<long long>(b) * C + c) * 2];
+      s2 += gm * red[(static_cast<long long>(b) * C + c) * 2 + 1];
+    }
+    gs[i * 2] = s1 * inv_count;
+    gs[i * 2 + 1] = s2 * inv_count;
+  }
+  __syncthreads();
+  const int nvec = C >> 3;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int vi = static_cast<int>(i % nvec);
+    const long long pix = i / nvec;
+    const int b = static_cast<int>(pix / HW);
+    float f[8], d[8], g[8], bt[8], o[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+    unpack8(reinterpret_cast<const uint4*>(dy)[i], d);
+    unpack8(reinterpret_cast<const uint4*>(gamma)[vi], g);
+    unpack8(reinterpret_cast<const uint4*>(beta)[vi], bt);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int grp = (vi * 8 + j) / cpg;
+      const float mu = stats[(b * groups + grp) * 2], rs = stats[(b * groups + grp) * 2 + 1];
+      const float xh = (f[j] - mu) * rs;
+      const float z = xh * g[j] + bt[j];
+      const float sg = sigmoidf_(z);
+      const float dz = d[j] * sg * (1.f + z * (1.f - sg));
+      o[j] = rs * (dz * g[j] - gs[(b * groups + grp) * 2] - xh * gs[(b * groups + grp) * 2 + 1]);
+    }
+    reinterpret_cast<uint4*>(dx)[i] = pack8(o);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ masked loss
+__global__ void __launch_bounds__(256) masked_loss_kernel(const __nv_bfloat16* __restrict__ pred,
+                                                          const __nv_bfloat16* __restrict__ label,
+                                                          const __nv_bfloat16* __restrict__ mask, long long nvec,
+                                                          long long mask_period_vec, int kind, float grad_scale,
+                                                          float* __restrict__ loss_sum, __nv_bfloat16* __restrict__ grad) {
+  float acc = 0.f;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float p[8], l[8], m[8], g[8];
+    unpack8(reinterpret_cast<const uint4*>(pred)[i], p);
+    unpack8(reinterpret_cast<const uint4*>(label)[i], l);
+    if (mask != nullptr) {
+      unpack8(reinterpret_cast<const uint4*>(mask)[i % mask_period_vec], m);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m[j] = 1.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float d = p[j] * m[j] - l[j];
+      if (kind == 0) {
+        acc += fabsf(d);
+        g[j] = (d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f)) * m[j] * grad_scale;
+      } else {
+        acc += d * d;
+        g[j] = 2.f * d * m[j] * grad_scale;
+      }
+    }
+    if (grad != nullptr) reinterpret_cast<uint4*>(grad)[i] = pack8(g);
+  }
+  acc = warp_sum(acc);
+  __shared__ float sh[8];
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) s += sh[w];
+    atomicAdd(loss_sum, s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ AdamW
+template <bool GRAD_BF16>
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, float* __restrict__ m,
+                                                    float* __restrict__ v, const void* __restrict__ grad,
+                                                    __nv_bfloat16* __restrict__ param, long long n, float lr, float b1,
+                                                    float b2, float eps, float wd, float bc1, float bc2s,
+                                                    float gscale) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g = GRAD_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(grad)[i])
+                        : static_cast<const float*>(grad)[i];
+    g *= gscale;
+    float p = master[i];
+    p *= 1.f - lr * wd;
+    const float mi = b1 * m[i] + (1.f - b1) * g;
+    const float vi = b2 * v[i] + (1.f - b2) * g * g;
+    const float denom = sqrtf(vi) / bc2s + eps;
+    p -= (lr / bc1) * (mi / denom);
+    m[i] = mi;
+    v[i] = vi;
+    master[i] = p;
+    if (param != nullptr) param[i] = __float2bfloat16(p);
+  }
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d, long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    d[i] = __float2bfloat16(s[i]);
+}
+
+__global__ void add_bf16_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ o,
+                                long long nvec) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float x[8], y[8];
+    unpack8(a[i], x);
+    unpack8(b[i], y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += y[j];
+    o[i] = pack8(x);
+  }
+}
+
+int grid_for(long long work_items, int block, int max_blocks = 148 * 16) {
+  long long g = (work_items + block - 1) / block;
+  if (g > max_blocks) g = max_blocks;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+#define TB_LN_DISPATCH(VPL_EXPR, CALL)                      \
+  switch (VPL_EXPR) {                                       \
+    case 1: { constexpr int VPL = 1; CALL; break; }         \
+    case 2: { constexpr int VPL = 2; CALL; break; }         \
+    case 3: { constexpr int VPL = 3; CALL; break; }         \
+    case 4: { constexpr int VPL = 4; CALL; break; }         \
+    case 5: case 6: { constexpr int VPL = 6; CALL; break; } \
+    case 7: case 8: { constexpr int VPL = 8; CALL; break; } \
+    default: return -1;                                     \
+  }
+
+int layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                  long long rows, int C, float eps, cudaStream_t stream) {
+  if (C % 8 != 0 || C > 2048) return -1;
+  const int vpl = (C / 8 + 31) / 32;
+  const int grid = grid_for(rows, 8);
+  TB_LN_DISPATCH(vpl, (layernorm_fwd_kernel<VPL><<<grid, 256, 0, stream>>>(
+                          static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),
+                          static_cast<const __nv_bfloat16*>(beta), static_cast<__nv_bfloat16*>(y), mean, rstd, rows, C,
+                          eps)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                  float* dgamma, float* dbeta, long long rows, int C, cudaStream_t stream) {
+  if (C % 8 != 0 || C > 2048) return -1;
+  const int vpl = (C / 8 + 31) / 32;
+  const int grid = grid_for(rows, 8, 148 * 4);
+  const size_t sh = 2 * C * sizeof(float);
+  TB_LN_DISPATCH(vpl, (layernorm_bwd_kernel<VPL><<<grid, 256, sh, stream>>>(
+                          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                          static_cast<const __nv_bfloat16*>(gamma), mean, rstd, static_cast<__nv_bfloat16*>(dx), dgamma,
+                          dbeta, rows, C)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int colsum_bf16(const void* x, float* out, long long rows, int C, long long ld, cudaStream_t stream) {
+  if (C % 8 != 0) return -1;
+  const int nvec = C / 8;
+  dim3 block(32, 8);
+  const int rows_per_block = 512;
+  dim3 grid(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block), (nvec + 31) / 32);
+  colsum_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), out, rows, C, ld, rows_per_block);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int groupnorm_stats(const void* x, float* sums, int B, long long HW, int C, int groups, cudaStream_t stream) {
+  if (C % 8 != 0 || C % groups != 0) return -1;
+  const int nvec = C / 8;
+  const int bx = nvec < 64 ? nvec : 64;
+  dim3 block(bx, 512 / bx > 0 ? 512 / bx : 1);
+  const int pix_per_block = 1024;
+  dim3 grid(static_cast<unsigned>((HW + pix_per_block - 1) / pix_per_block), B);
+  groupnorm_stats_kernel<<<grid, block, 2 * C * sizeof(float), stream>>>(static_cast<const __nv_bfloat16*>(x), sums, HW,
+                                                                         C, groups, pix_per_block);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int groupnorm_silu_apply(const void* x, const float* stats, const void* gamma, const void* beta, void* y, int B,
+                         long long HW, int C, int groups, cudaStream_t stream) {
+  if (C % 8 != 0 || C % groups != 0) return -1;
+  const long long total_vec = static_cast<long long>(B) * HW * (C / 8);
+  groupnorm_silu_apply_kernel<<<grid_for(total_vec, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), stats, static_cast<const __nv_bfloat16*>(gamma),
+      static_cast<const __nv_bfloat16*>(beta), static_cast<__nv_bfloat16*>(y), HW, C, groups, total_vec);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int groupnorm_silu_bwd_reduce(const void* dy, const void* x, const float* stats, const void* gamma, const void* beta,
+                              float* red, float* /*dgamma*/, float* /*dbeta*/, int B, long long HW, int C, int groups,
+                              cudaStream_t stream) {
+  if (C % 8 != 0 || C % groups != 0) return -1;
+  const int nvec = C / 8;
+  const int bx = nvec < 64 ? nvec : 64;
+  dim3 block(bx, 512 / bx > 0 ? 512 / bx : 1);
+  const int pix_per_block = 1024;
+  dim3 grid(static_cast<unsigned>((HW + pix_per_block - 1) / pix_per_block), B);
+  groupnorm_silu_bwd_reduce_kernel<<<grid, block, 2 * C * sizeof(float), stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats,
+      static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta), red, HW, C, groups,
+      pix_per_block);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int groupnorm_silu_bwd_apply(const void* dy, const void* x, const float* stats, const float* red, const void* gamma,
+                             const void* beta, void* dx, int B, long long HW, int C, int groups, float inv_count,
+                             cudaStream_t stream) {
+  if (C % 8 != 0 || C % groups != 0) return -1;
+  const long long total_vec = static_cast<long long>(B) * HW * (C / 8);
+  groupnorm_silu_bwd_apply_kernel<<<grid_for(total_vec, 256), 256, B * groups * 2 * sizeof(float), stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats, red,
+      static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta),
+      static_cast<__nv_bfloat16*>(dx), B, HW, C, groups, inv_count, total_vec);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int masked_loss_fwd_bwd(const void* pred, const void* label, const void* mask, long long n, long long mask_period,
+                        int kind, float grad_scale, float* loss_sum, void* grad, cudaStream_t stream) {
+  if (n % 8 != 0 || (mask != nullptr && mask_period % 8 != 0)) return -1;
+  const long long nvec = n / 8;
+  masked_loss_kernel<<<grid_for(nvec, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(pred), static_cast<const __nv_bfloat16*>(label),
+      static_cast<const __nv_bfloat16*>(mask), nvec, mask != nullptr ? mask_period / 8 : 1, kind, grad_scale, loss_sum,
+      static_cast<__nv_bfloat16*>(grad));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int adamw_step(float* master, float* exp_avg, float* exp_avg_sq, const void* grad, int grad_is_bf16, void* param_bf16,
+               long long n, float lr, float beta1, float beta2, float eps, float weight_decay, float bias_corr1,
+               float bias_corr2_sqrt, float grad_scale, cudaStream_t stream) {
+  const int grid = grid_for(n, 256);
+  if (grad_is_bf16)
+    adamw_kernel<true><<<grid, 256, 0, stream>>>(master, exp_avg, exp_avg_sq, grad,
+                                                 static_cast<__nv_bfloat16*>(param_bf16), n, lr, beta1, beta2, eps,
+                                                 weight_decay, bias_corr1, bias_corr2_sqrt, grad_scale);
+  else
+    adamw_kernel<false><<<grid, 256, 0, stream>>>(master, exp_avg, exp_avg_sq, grad,
+                                                  static_cast<__nv_bfloat16*>(param_bf16), n, lr, beta1, beta2, eps,
+                                                  weight_decay, bias_corr1, bias_corr2_sqrt, grad_scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream) {
+  cast_f32_bf16_kernel<<<grid_for(n, 256), 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream) {
+  if (n % 8 != 0) return -1;
+  add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
+                                                            static_cast<uint4*>(out), n / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace tb

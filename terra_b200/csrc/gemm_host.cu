@@ -1,0 +1,276 @@
+// Host-side construction of TMA tensor maps and GemmParams for the tcgen05 GEMM family.
+// No allocation happens here: callers pass every buffer.
+#include "gemm_sm100.cuh"
+#include "host_api.h"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace tb {
+
+cudaError_t launch_gemm(const GemmParams& p, int bn, int num_sms, cudaStream_t stream);
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// rank <= 5, bf16 elements, 128-byte swizzle, zero fill outside the tensor.
+// dims/box are innermost first; strides (bytes) are for dims 1..rank-1.
+int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const unsigned long long* dims,
+                         const unsigned long long* strides_bytes, const unsigned int* box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[4];
+  cuuint32_t bdim[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return -2;
+  for (int i = 0; i + 1 < rank; ++i)
+    if (gstr[i] % 16 != 0) return -3;
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
+                  gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -100 - static_cast<int>(r);
+}
+
+static int map_2d(CUtensorMap* out, const void* base, long long inner, long long outer, long long ld_elems,
+                  int box_inner, int box_outer) {
+  unsigned long long dims[2] = {static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer)};
+  unsigned long long str[1] = {static_cast<unsigned long long>(ld_elems) * 2ull};
+  unsigned int box[2] = {static_cast<unsigned int>(box_inner), static_cast<unsigned int>(box_outer)};
+  return make_tensor_map_bf16(out, base, 2, dims, str, box);
+}
+
+static int pick_bn(long long N, int requested) {
+  if (requested == 64 || requested == 128 || requested == 256) return requested;
+  if (N <= 64) return 64;
+  if (N % 256 == 0 && N >= 1024) return 256;
+  return 128;
+}
+
+static void fill_epilogue(GemmParams& p, const GemmEpilogue& e) {
+  p.epi = e.flags;
+  p.C = e.C;
+  p.C2 = e.C2;
+  p.bias = e.bias;
+  p.residual = static_cast<const __nv_bfloat16*>(e.residual);
+  p.aux = static_cast<const __nv_bfloat16*>(e.aux);
+  p.ldc = e.ldc;
+  p.ldc2 = e.ldc2;
+  p.ldr = e.ldr;
+  p.ldaux = e.ldaux;
+  p.alpha = e.alpha;
+  p.status = static_cast<KernelStatus*>(e.status);
+}
+
+int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
+              const GemmEpilogue& epi, int split_k, int bn_request, int num_sms, cudaStream_t stream) {
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  const int bn = pick_bn(N, bn_request);
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.num_m_tiles = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
+  p.num_n_tiles = static_cast<int>((N + bn - 1) / bn);
+  p.k_blocks = static_cast<int>((K + GEMM_BK - 1) / GEMM_BK);
+  p.groups = 1;
+  if (split_k < 1) split_k = 1;
+  if (split_k > p.k_blocks) split_k = p.k_blocks;
+  {
+    const int per = (p.k_blocks + split_k - 1) / split_k;
+    split_k = (p.k_blocks + per - 1) / per;   // no empty split
+  }
+  p.split_k = split_k;
+  if (split_k > 1 && !((epi.flags & EPI_ATOMIC) && (epi.flags & EPI_OUT_F32))) return -10;
+  p.a_mode = A.mn_major ? OP_MNMAJOR_2D : OP_KMAJOR_2D;
+  p.b_mode = B.mn_major ? OP_MNMAJOR_2D : OP_KMAJOR_2D;
+  int rc;
+  if (A.mn_major) rc = map_2d(&p.map_a, A.ptr, M, K, A.ld, 64, GEMM_BK);
+  else rc = map_2d(&p.map_a, A.ptr, K, M, A.ld, GEMM_BK, GEMM_BM);
+  if (rc != 0) return rc;
+  if (B.mn_major) rc = map_2d(&p.map_b, B.ptr, N, K, B.ld, 64, GEMM_BK);
+  else rc = map_2d(&p.map_b, B.ptr, K, N, B.ld, GEMM_BK, bn);
+  if (rc != 0) return rc - 1000;
+  fill_epilogue(p, epi);
+  p.tile_n0 = 1;
+  p.tile_n1 = 1;
+  p.out_w = epi.out_w;
+  p.out_h = epi.out_h;
+  p.shuffle_cout = epi.shuffle_cout > 0 ? epi.shuffle_cout : 1;
+  cudaError_t e = launch_gemm(p, bn, num_sms, stream);
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
+
+// 3x3 convolution, padding 1, stride 1 or 2, NHWC bf16, as implicit GEMM.
+//   x: [B, H, W, Cin]   w: [Cout, 9 * Cin_pad] (tap-major, Cin padded to a multiple of 64 with zeros)
+//   y: [B, Ho, Wo, Cout]
+int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin, int Cout, int stride,
+                     const GemmEpilogue& epi, int num_sms, cudaStream_t stream) {
+  if (stride != 1 && stride != 2) return -11;
+  if (stride == 2 && (W % 2 != 0)) return -12;
+  if (Cin % 8 != 0 || Cout % 8 != 0) return -13;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  const int Ho = (stride == 1) ? H : (H + 1) / 2;
+  const int Wo = (stride == 1) ? W : W / 2;
+  const int cchunks = (Cin + 63) / 64;
+  const int cin_pad = cchunks * 64;
+  if (9 * cchunks > GEMM_MAX_KTABLE) return -14;
+  const int bn = pick_bn(Cout, 0);
+  p.M = B * Ho * Wo;
+  p.N = Cout;
+  p.K = 9 * cin_pad;
+  p.tile_n0 = (Wo + GEMM_BM - 1) / GEMM_BM;
+  p.tile_n1 = Ho;
+  p.num_m_tiles = p.tile_n0 * Ho * B;
+  p.num_n_tiles = (Cout + bn - 1) / bn;
+  p.k_blocks = 9 * cchunks;
+  p.split_k = 1;
+  p.groups = 1;
+  p.a_mode = OP_TABLE_5D;
+  p.b_mode = OP_KMAJOR_2D;
+  // 5-D view of x: {Cin, parity, W / par, H, B}; par = stride.
+  const int par = stride;
+  unsigned long long dims[5] = {static_cast<unsigned long long>(Cin), static_cast<unsigned long long>(par),
+                                static_cast<unsigned long long>(W / par), static_cast<unsigned long long>(H),
+                                static_cast<unsigned long long>(B)};
+  unsigned long long str[4] = {static_cast<unsigned long long>(Cin) * 2ull,
+                               static_cast<unsigned long long>(Cin) * 2ull * par,
+                               static_cast<unsigned long long>(Cin) * 2ull * W,
+                               static_cast<unsigned long long>(Cin) * 2ull * W * H};
+  unsigned int box[5] = {64, 1, GEMM_BM, 1, 1};
+  int rc = make_tensor_map_bf16(&p.map_a, x, 5, dims, str, box);
+  if (rc != 0) return rc;
+  rc = map_2d(&p.map_b, w, p.K, Cout, p.K, GEMM_BK, bn);
+  if (rc != 0) return rc - 1000;
+  // tile (t0, t1, t2) = (w chunk, ho, b): base coordinates
+  p.a_mul0[2] = GEMM_BM;          // w (in units of the strided grid)
+  p.a_mul1[3] = stride;           // h_in = ho * stride + dh
+  p.a_mul2[4] = 1;                // b
+  for (int tap = 0; tap < 9; ++tap) {
+    const int dy = tap / 3, dx = tap % 3;
+    for (int c = 0; c < cchunks; ++c) {
+      short* e = p.ktable[tap * cchunks + c];
+      e[0] = static_cast<short>(c * 64);
+      if (stride == 1) {
+        e[1] = 0;
+        e[2] = static_cast<short>(dx - 1);
+      } else {
+        // w_in = 2*wo + dx - 1: dx=0 -> parity 1 of column wo-1; dx=1 -> parity 0 of wo; dx=2 -> parity 1 of wo
+        e[1] = static_cast<short>(dx == 1 ? 0 : 1);
+        e[2] = static_cast<short>(dx == 0 ? -1 : 0);
+      }
+      e[3] = static_cast<short>(dy - 1);
+    }
+  }
+  fill_epilogue(p, epi);
+  p.epi |= EPI_ROW_CONV;
+  p.out_w = Wo;
+  p.out_h = Ho;
+  p.shuffle_cout = 1;
+  cudaError_t e = launch_gemm(p, bn, num_sms, stream);
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
+
+// Weight gradient of the 3x3 convolution: dw[tap][Cout][Cin] (fp32, pre-zeroed, atomically accumulated)
+//   = sum over output pixels of dy[pix][Cout]^T * x[pix shifted by tap][Cin].
+int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, int W, int Cin, int Cout, int stride,
+                       int split_k, void* status, int num_sms, cudaStream_t stream) {
+  if (stride != 1 && stride != 2) return -11;
+  if (stride == 2 && (W % 2 != 0)) return -12;
+  if (Cin % 8 != 0 || Cout % 8 != 0) return -13;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  const int Ho = (stride == 1) ? H : (H + 1) / 2;
+  const int Wo = (stride == 1) ? W : W / 2;
+  const int bn = pick_bn(Cin, 128);
+  p.M = Cout;
+  p.N = Cin;
+  p.pix_n0 = (Wo + GEMM_BK - 1) / GEMM_BK;
+  p.pix_n1 = Ho;
+  p.pix_hmul = stride;
+  p.k_blocks = p.pix_n0 * Ho * B;
+  p.K = p.k_blocks * GEMM_BK;
+  p.num_m_tiles = (Cout + GEMM_BM - 1) / GEMM_BM;
+  p.num_n_tiles = (Cin + bn - 1) / bn;
+  p.groups = 9;
+  if (split_k < 1) split_k = 1;
+  if (split_k > p.k_blocks) split_k = p.k_blocks;
+  {
+    const int per = (p.k_blocks + split_k - 1) / split_k;
+    split_k = (p.k_blocks + per - 1) / per;
+  }
+  p.split_k = split_k;
+  p.a_mode = OP_PIXELS_5D;
+  p.b_mode = OP_PIXELS_5D;
+  {
+    unsigned long long dims[5] = {static_cast<unsigned long long>(Cout), 1ull, static_cast<unsigned long long>(Wo),
+                                  static_cast<unsigned long long>(Ho), static_cast<unsigned long long>(B)};
+    unsigned long long str[4] = {static_cast<unsigned long long>(Cout) * 2ull, static_cast<unsigned long long>(Cout) * 2ull,
+                                 static_cast<unsigned long long>(Cout) * 2ull * Wo,
+                                 static_cast<unsigned long long>(Cout) * 2ull * Wo * Ho};
+    unsigned int box[5] = {64, 1, GEMM_BK, 1, 1};
+    int rc = make_tensor_map_bf16(&p.map_a, dy, 5, dims, str, box);
+    if (rc != 0) return rc;
+  }
+  {
+    const int par = stride;
+    unsigned long long dims[5] = {static_cast<unsigned long long>(Cin), static_cast<unsigned long long>(par),
+                                  static_cast<unsigned long long>(W / par), static_cast<unsigned long long>(H),
+                                  static_cast<unsigned long long>(B)};
+    unsigned long long str[4] = {static_cast<unsigned long long>(Cin) * 2ull,
+                                 static_cast<unsigned long long>(Cin) * 2ull * par,
+                                 static_cast<unsigned long long>(Cin) * 2ull * W,
+                                 static_cast<unsigned long long>(Cin) * 2ull * W * H};
+    unsigned int box[5] = {64, 1, GEMM_BK, 1, 1};
+    int rc = make_tensor_map_bf16(&p.map_b, x, 5, dims, str, box);
+    if (rc != 0) return rc - 1000;
+  }
+  for (int tap = 0; tap < 9; ++tap) {
+    const int dyy = tap / 3, dxx = tap % 3;
+    short* g = p.grp_off[tap];
+    if (stride == 1) {
+      g[0] = 0;
+      g[1] = static_cast<short>(dxx - 1);
+    } else {
+      g[0] = static_cast<short>(dxx == 1 ? 0 : 1);
+      g[1] = static_cast<short>(dxx == 0 ? -1 : 0);
+    }
+    g[2] = static_cast<short>(dyy - 1);
+  }
+  p.grp_c_stride = static_cast<long long>(Cout) * Cin;
+  p.epi = EPI_OUT_F32 | EPI_ATOMIC;
+  p.C = dw;
+  p.ldc = Cin;
+  p.alpha = 1.0f;
+  p.status = static_cast<KernelStatus*>(status);
+  p.tile_n0 = 1;
+  p.tile_n1 = 1;
+  p.shuffle_cout = 1;
+  cudaError_t e = launch_gemm(p, bn, num_sms, stream);
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
+
+}  // namespace tb

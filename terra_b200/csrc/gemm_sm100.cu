@@ -1,0 +1,377 @@
+// Persistent, warp-specialised bf16 GEMM / implicit-GEMM for sm_100a.
+//
+//   D[M,N] (+)= A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory.
+//
+// Roles inside a 192-thread CTA (one CTA per SM, tiles assigned round-robin):
+//   warp 0   one elected lane issues TMA loads (per-CTA, no cluster fan-out) into a ring of
+//            128-byte-swizzled shared-memory stages, signalling `full[s]` by transaction bytes;
+//   warp 1   owns the TMEM allocation; one elected lane issues tcgen05.mma (M=128, N=BN, K=16)
+//            and commits to `empty[s]` (stage reusable) and `tfull[a]` (accumulator a complete);
+//   warps 2-5 epilogue: tcgen05.ld of their 32-lane TMEM quadrant, fused bias / GELU / residual /
+//            GELU-gradient / pixel-shuffle / split-K atomics, 16-byte global stores.
+// Two accumulators (2*BN TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Operand addressing is data driven (see gemm_sm100.cuh) so that the same kernel serves
+//   * linear layers forward (K-major x K-major),
+//   * their input gradients (B read MN-major: the weight is used untransposed),
+//   * their weight gradients (both operands MN-major, contraction over tokens, split-K atomics),
+//   * 3x3 convolutions (stride 1 and 2) as implicit GEMM: A rows gathered by 5-D TMA boxes with
+//     zero fill outside the image, k-blocks enumerate (tap, channel chunk),
+//   * convolution weight gradients (contraction over pixels, one tile group per tap).
+//
+// Every wait is bounded; on expiry the CTA sets its abort flag, records the site in the
+// KernelStatus word, drains, releases TMEM and returns.
+#include "gemm_sm100.cuh"
+
+namespace tb {
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 6 : 8);
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct TileCoord {
+  int grp, m_blk, n_blk, split;
+  int kb_begin, kb_end;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile) {
+  TileCoord t;
+  t.split = tile % p.split_k;
+  int r = tile / p.split_k;
+  t.n_blk = r % p.num_n_tiles;
+  r /= p.num_n_tiles;
+  t.m_blk = r % p.num_m_tiles;
+  t.grp = r / p.num_m_tiles;
+  const int per = (p.k_blocks + p.split_k - 1) / p.split_k;
+  t.kb_begin = t.split * per;
+  t.kb_end = min(p.k_blocks, t.kb_begin + per);
+  return t;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + Cfg::STAGES;
+  uint64_t* tfull = empty + Cfg::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&p.map_a);
+    tma_prefetch_desc(&p.map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<Cfg::TMEM_COLS>(tmem_slot);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const TileCoord tc = decode_tile(p, tile);
+        const int m0 = tc.m_blk * GEMM_BM;
+        const int n0 = tc.n_blk * BN;
+        int abase[5] = {0, 0, 0, 0, 0};
+        if (p.a_mode == OP_TABLE_5D) {
+          const int t0 = tc.m_blk % p.tile_n0;
+          const int t1 = (tc.m_blk / p.tile_n0) % p.tile_n1;
+          const int t2 = tc.m_blk / (p.tile_n0 * p.tile_n1);
+#pragma unroll
+          for (int d = 0; d < 5; ++d) abase[d] = t0 * p.a_mul0[d] + t1 * p.a_mul1[d] + t2 * p.a_mul2[d];
+        }
+        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (it / Cfg::STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 0x100u + s)) break;
+          uint8_t* sA = smem + s * Cfg::STAGE_BYTES;
+          uint8_t* sB = sA + Cfg::A_BYTES;
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          int pw = 0, ph_ = 0, pb = 0;
+          if (p.a_mode == OP_PIXELS_5D || p.b_mode == OP_PIXELS_5D) {
+            pw = kb % p.pix_n0;
+            ph_ = (kb / p.pix_n0) % p.pix_n1;
+            pb = kb / (p.pix_n0 * p.pix_n1);
+          }
+          // ---- operand A
+          if (p.a_mode == OP_KMAJOR_2D) {
+            tma_load_2d(sA, &p.map_a, &full[s], kb * GEMM_BK, m0);
+          } else if (p.a_mode == OP_MNMAJOR_2D) {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j)
+              tma_load_2d(sA + j * (GEMM_BK * 128), &p.map_a, &full[s], m0 + j * 64, kb * GEMM_BK);
+          } else if (p.a_mode == OP_TABLE_5D) {
+            const short* e = p.ktable[kb];
+            tma_load_5d(sA, &p.map_a, &full[s], abase[0] + e[0], abase[1] + e[1], abase[2] + e[2], abase[3] + e[3],
+                        abase[4]);
+          } else {  // OP_PIXELS_5D: {channels, 1, w, h, b}
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j)
+              tma_load_5d(sA + j * (GEMM_BK * 128), &p.map_a, &full[s], m0 + j * 64, 0, pw * GEMM_BK, ph_, pb);
+          }
+          // ---- operand B
+          if (p.b_mode == OP_KMAJOR_2D) {
+            tma_load_2d(sB, &p.map_b, &full[s], kb * GEMM_BK, n0);
+          } else if (p.b_mode == OP_MNMAJOR_2D) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sB + j * (GEMM_BK * 128), &p.map_b, &full[s], n0 + j * 64, kb * GEMM_BK);
+          } else {  // OP_PIXELS_5D with per-group (tap) displacement
+            const short* g = p.grp_off[tc.grp];
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_5d(sB + j * (GEMM_BK * 128), &p.map_b, &full[s], n0 + j * 64, g[0], pw * GEMM_BK + g[1],
+                          ph_ * p.pix_hmul + g[2], pb);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mode == OP_MNMAJOR_2D || p.a_mode == OP_PIXELS_5D,
+                                             p.b_mode == OP_MNMAJOR_2D || p.b_mode == OP_PIXELS_5D);
+      const bool a_mn = (p.a_mode == OP_MNMAJOR_2D || p.a_mode == OP_PIXELS_5D);
+      const bool b_mn = (p.b_mode == OP_MNMAJOR_2D || p.b_mode == OP_PIXELS_5D);
+      const uint32_t a_lbo = a_mn ? GEMM_BK * 128 : 16, b_lbo = b_mn ? GEMM_BK * 128 : 16;
+      const uint32_t a_kstep = a_mn ? (16 * 128) >> 4 : 32 >> 4;   // descriptor units of 16 bytes
+      const uint32_t b_kstep = b_mn ? (16 * 128) >> 4 : 32 >> 4;
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+        const TileCoord tc = decode_tile(p, tile);
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1u;
+        if (!mbar_wait(&tempty[acc], aph ^ 1u, abort_flag, p.status, 0x200u + acc)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (it / Cfg::STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 0x300u + s)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint64_t da = make_smem_desc(sA, a_lbo, 1024);
+          const uint64_t db = make_smem_desc(sB, b_lbo, 1024);
+#pragma unroll
+          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+            umma_bf16(d_tmem, da + kk * a_kstep, db + kk * b_kstep, idesc, (kb > tc.kb_begin || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;               // TMEM lane quadrant this warp may read
+    const int r = q * 32 + lane;          // row inside the 128-row tile
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+      const TileCoord tc = decode_tile(p, tile);
+      const int acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1u;
+      if (!mbar_wait(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
+      tc_fence_after();
+      const int n0 = tc.n_blk * BN;
+      // ---- row -> output pixel/row index
+      long long row = -1;
+      int col0 = n0;
+      if (p.epi & EPI_ROW_CONV) {
+        const int t0 = tc.m_blk % p.tile_n0;
+        const int t1 = (tc.m_blk / p.tile_n0) % p.tile_n1;
+        const int t2 = tc.m_blk / (p.tile_n0 * p.tile_n1);
+        const int w = t0 * GEMM_BM + r;
+        if (w < p.out_w) row = (static_cast<long long>(t2) * p.tile_n1 + t1) * p.out_w + w;
+      } else if (p.epi & EPI_ROW_SHUFFLE) {
+        const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;
+        if (g < p.M) {
+          const int w = static_cast<int>(g % p.out_w);
+          const long long t = g / p.out_w;
+          const int h = static_cast<int>(t % p.out_h);
+          const long long b = t / p.out_h;
+          const int qd = n0 / p.shuffle_cout;
+          row = ((b * 2 * p.out_h + 2 * h + (qd >> 1)) * 2 * p.out_w) + 2 * w + (qd & 1);
+        }
+        col0 = n0 % p.shuffle_cout;
+      } else {
+        const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;
+        if (g < p.M) row = g;
+      }
+      const long long gofs = static_cast<long long>(tc.grp) * p.grp_c_stride;
+      const int ncols_out = (p.epi & EPI_ROW_SHUFFLE) ? p.shuffle_cout : p.N;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (n0 + c * 32 >= p.N) break;   // warp-uniform
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+        tmem_ld_wait();
+        if (row >= 0) {
+          const int cb = col0 + c * 32;          // first output column of this chunk
+          const int nb = n0 + c * 32;            // first logical column (bias index)
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+          if (p.epi & EPI_BIAS) {
+            if (p.epi & EPI_BIAS_F32) {
+              const float* b = static_cast<const float*>(p.bias);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) f[j] += __ldg(b + nb + j);
+            } else {
+              const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) f[j] += __bfloat162float(b[nb + j]);
+            }
+          }
+          if (p.epi & EPI_SAVE_PRE) {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.C2) + row * p.ldc2 + cb;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (cb + j < ncols_out) {
+                uint4 u = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
+                                     pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
+                *reinterpret_cast<uint4*>(o + j) = u;
+              }
+            }
+          }
+          if (p.epi & EPI_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+          }
+          if (p.epi & EPI_MUL_DGELU) {
+            const __nv_bfloat16* a = p.aux + row * p.ldaux + cb;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (cb + j < ncols_out) {
+                const uint4 u = *reinterpret_cast<const uint4*>(a + j);
+                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const float2 x = unpack_bf16x2(w4[k]);
+                  f[j + 2 * k] *= gelu_erf_grad(x.x);
+                  f[j + 2 * k + 1] *= gelu_erf_grad(x.y);
+                }
+              }
+            }
+          }
+          if (p.epi & EPI_RESIDUAL) {
+            const __nv_bfloat16* a = p.residual + row * p.ldr + cb;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (cb + j < ncols_out) {
+                const uint4 u = *reinterpret_cast<const uint4*>(a + j);
+                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const float2 x = unpack_bf16x2(w4[k]);
+                  f[j + 2 * k] += x.x;
+                  f[j + 2 * k + 1] += x.y;
+                }
+              }
+            }
+          }
+          if (p.epi & EPI_OUT_F32) {
+            float* o = static_cast<float*>(p.C) + gofs + row * p.ldc + cb;
+            if (p.epi & EPI_ATOMIC) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (cb + j < ncols_out) atomicAdd(o + j, f[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                if (cb + j < ncols_out) *reinterpret_cast<float4*>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            }
+          } else {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.C) + gofs + row * p.ldc + cb;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (cb + j < ncols_out) {
+                uint4 u = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
+                                     pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
+                *reinterpret_cast<uint4*>(o + j) = u;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    // Give copies that are still in flight time to land before shared memory is released.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc<Cfg::TMEM_COLS>(tmem_base);
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+template <int BN>
+static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int total = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
+  const int grid = total < num_sms ? total : num_sms;
+  if (grid <= 0) return cudaSuccess;
+  gemm_tcgen05_kernel<BN><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gemm(const GemmParams& p, int bn, int num_sms, cudaStream_t stream) {
+  switch (bn) {
+    case 64: return launch_bn<64>(p, num_sms, stream);
+    case 128: return launch_bn<128>(p, num_sms, stream);
+    case 256: return launch_bn<256>(p, num_sms, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace tb

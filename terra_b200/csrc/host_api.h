@@ -1,0 +1,92 @@
+// Plain C++ host API of the terra_b200 CUDA kernels (no torch types). The Python binding layer
+// (bindings.cpp) and C callers use these entry points; none of them allocates device memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb {
+
+struct GemmOperand {
+  const void* ptr;   // bf16
+  long long ld;      // leading dimension in elements (stride of the outer stored dimension)
+  int mn_major;      // 0: stored [rows][K] (K contiguous); 1: stored [K][rows] (rows contiguous)
+};
+
+struct GemmEpilogue {
+  int flags;          // EPI_* bit mask (gemm_sm100.cuh)
+  void* C;
+  void* C2;
+  const void* bias;
+  const void* residual;
+  const void* aux;
+  long long ldc, ldc2, ldr, ldaux;
+  float alpha;
+  int out_w, out_h, shuffle_cout;
+  void* status;       // KernelStatus* (device), may be null
+};
+
+// gemm_host.cu
+int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
+              const GemmEpilogue& epi, int split_k, int bn_request, int num_sms, cudaStream_t stream);
+int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin, int Cout, int stride,
+                     const GemmEpilogue& epi, int num_sms, cudaStream_t stream);
+int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, int W, int Cin, int Cout, int stride,
+                       int split_k, void* status, int num_sms, cudaStream_t stream);
+
+// elementwise.cu -------------------------------------------------------------------------------
+// LayerNorm over the last dimension (C <= 8192, C % 8 == 0), bf16 in/out, fp32 statistics.
+int layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                  long long rows, int C, float eps, cudaStream_t stream);
+// dx (bf16); dgamma/dbeta accumulated atomically into fp32 buffers that the caller zeroed.
+int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                  float* dgamma, float* dbeta, long long rows, int C, cudaStream_t stream);
+// Column sums of a bf16 [rows, C] matrix into fp32 out[C] (atomic accumulate; caller zeroes out).
+int colsum_bf16(const void* x, float* out, long long rows, int C, long long ld, cudaStream_t stream);
+// GroupNorm statistics over NHWC bf16 [B, HW, C]: accumulates per (b, group) sum and sum of squares (fp32, zeroed).
+int groupnorm_stats(const void* x, float* sums, int B, long long HW, int C, int groups, cudaStream_t stream);
+// y = silu((x - mean) * rstd * gamma + beta); `stats` holds {mean, rstd} per (b, group).
+int groupnorm_silu_apply(const void* x, const float* stats, const void* gamma, const void* beta, void* y, int B,
+                         long long HW, int C, int groups, cudaStream_t stream);
+// Backward of GroupNorm+SiLU. Pass 1 accumulates per (b,group) {sum(dz), sum(dz*xhat)} and per-channel dgamma/dbeta;
+// pass 2 produces dx. dz = dy * silu'(z).
+int groupnorm_silu_bwd_reduce(const void* dy, const void* x, const float* stats, const void* gamma, const void* beta,
+                              float* red, float* dgamma, float* dbeta, int B, long long HW, int C, int groups,
+                              cudaStream_t stream);
+int groupnorm_silu_bwd_apply(const void* dy, const void* x, const float* stats, const float* red, const void* gamma,
+                             const void* beta, void* dx, int B, long long HW, int C, int groups, float inv_count,
+                             cudaStream_t stream);
+// Masked loss: loss_sum += sum(f(pred * mask - label)), f = |.| (kind 0) or square (kind 1);
+// grad = mask * f'(.) * scale (bf16). `mask` may be null. Partial sums are fp32 atomics on loss_sum[0].
+int masked_loss_fwd_bwd(const void* pred, const void* label, const void* mask, long long n, long long mask_period,
+                        int kind, float grad_scale, float* loss_sum, void* grad, cudaStream_t stream);
+// Fused AdamW on an fp32 master with a bf16 (or fp32) gradient, writing the bf16 working copy.
+int adamw_step(float* master, float* exp_avg, float* exp_avg_sq, const void* grad, int grad_is_bf16, void* param_bf16,
+               long long n, float lr, float beta1, float beta2, float eps, float weight_decay, float bias_corr1,
+               float bias_corr2_sqrt, float grad_scale, cudaStream_t stream);
+// bf16 <-> fp32 helpers
+int cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
+// out[b, i, j, c] = a + b elementwise (bf16)
+int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
+
+// window_attn.cu -------------------------------------------------------------------------------
+struct WindowAttnArgs {
+  const void* qkv;      // bf16 token-major [tokens, 3*C]  (q | k | v, head-major inside each)
+  void* out;            // bf16 [tokens, C]
+  const void* dout;     // backward: bf16 [tokens, C]
+  void* dqkv;           // backward: bf16 [tokens, 3*C]
+  const float* bias_table;  // fp32 [(2wh-1)*(2ww-1), nH] or null
+  float* dbias_table;       // backward, fp32 atomics, or null
+  float* lse;           // fp32 [tokens, nH]: log-sum-exp per query row (saved by forward, read by backward)
+  int B, Hh, Ww;        // token grid of this rank's activation, image-major [B, Hh, Ww, *]
+  int C, num_heads;
+  int wh, ww;           // window
+  int sh, sw;           // cyclic shift (0 for regular blocks)
+  int use_mask;         // apply the shifted-window region mask (-100)
+  int grid_h, grid_w;   // global token grid (for the mask regions); rows of this rank start at row_offset
+  int row_offset;
+  float scale;
+};
+int window_attn_fwd(const WindowAttnArgs& a, cudaStream_t stream);
+int window_attn_bwd(const WindowAttnArgs& a, cudaStream_t stream);
+
+}  // namespace tb

@@ -1,0 +1,93 @@
+"""Python front end of the tcgen05 GEMM family.
+
+``gemm`` computes ``epilogue(A_op @ B_op^T)`` where the stored orientation of each operand is a flag, so
+that forward, input-gradient and weight-gradient products of a linear layer all run on the same kernel
+without materialising a transpose:
+
+    forward      y  = x  @ W^T          a=x  [M,K]         b=W  [N,K]
+    input grad   dx = dy @ W            a=dy [M,N]         b=W  [N,K] read MN-major (b_mn=True)
+    weight grad  dW = dy^T @ x          a=dy [M,N] (a_mn)  b=x  [M,K] (b_mn), split-K fp32 atomics
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _ext
+from . import _flags as F
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device 4 x uint32 record that kernels write when a bounded wait runs out."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Raise if any kernel since the last check reported a timed-out wait (synchronises)."""
+    st = status_word(device).cpu().tolist()
+    if st[0] != 0:
+        status_word(device).zero_()
+        raise RuntimeError(
+            f"terra_b200 kernel reported error {st[0]} at site 0x{st[1] & 0xffffffff:x} (info {st[2]}, {st[3]})"
+        )
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    bias: Optional[torch.Tensor] = None,
+    gelu: bool = False,
+    save_pre: bool = False,
+    residual: Optional[torch.Tensor] = None,
+    dgelu_aux: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    out_f32: bool = False,
+    accumulate: bool = False,
+    split_k: int = 1,
+    alpha: float = 1.0,
+    bn: int = 0,
+    sms: int = 0,
+):
+    """Returns ``out`` (and the saved pre-activation when ``save_pre``)."""
+    ext = _ext.load()
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    flags = 0
+    if bias is not None:
+        flags |= F.EPI_BIAS
+        if bias.dtype == torch.float32:
+            flags |= F.EPI_BIAS_F32
+    if gelu:
+        flags |= F.EPI_GELU
+    if residual is not None:
+        flags |= F.EPI_RESIDUAL
+    if dgelu_aux is not None:
+        flags |= F.EPI_MUL_DGELU
+    if out_f32 or accumulate or split_k > 1:
+        flags |= F.EPI_OUT_F32
+    if accumulate or split_k > 1:
+        flags |= F.EPI_ATOMIC
+    if out is None:
+        dt = torch.float32 if (flags & F.EPI_OUT_F32) else torch.bfloat16
+        if flags & F.EPI_ATOMIC:
+            out = torch.zeros(M, N, dtype=dt, device=a.device)
+        else:
+            out = torch.empty(M, N, dtype=dt, device=a.device)
+    pre = None
+    if save_pre:
+        flags |= F.EPI_SAVE_PRE
+        pre = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    ext.gemm(a, a_mn, b, b_mn, out, flags, bias, residual, dgelu_aux, pre, float(alpha), int(split_k), int(bn),
+             status_word(a.device), 0, 0, 0, int(sms))
+    if save_pre:
+        return out, pre
+    return out
