@@ -106,48 +106,56 @@ void adamw_step(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const
            "adamw_step");
 }
 
-void window_attn(const torch::Tensor& qkv, torch::Tensor& out, const c10::optional<torch::Tensor>& bias_table,
-                 torch::Tensor& lse, int64_t B, int64_t Hh, int64_t Ww, int64_t heads, int64_t wh, int64_t ww,
-                 int64_t sh, int64_t sw, bool use_mask, int64_t grid_h, int64_t grid_w, int64_t row_offset,
-                 double scale) {
-  need(qkv.is_cuda() && qkv.is_contiguous() && qkv.scalar_type() == torch::kBFloat16, "window_attn: qkv bf16");
-  const c10::cuda::CUDAGuard guard(qkv.device());
+// Peer buffers are passed as raw device addresses (int64) so that symmetric-memory peers can be addressed;
+// for a single rank the lists hold one entry each.
+tb::WindowAttnArgs make_wa(const std::vector<int64_t>& win_start, int64_t my_wg, int64_t sp, int64_t my_sp,
+                           int64_t shardN, int64_t B, int64_t nWh, int64_t nWw, int64_t C, int64_t heads, int64_t wh,
+                           int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale) {
   tb::WindowAttnArgs a{};
-  a.qkv = qkv.data_ptr();
-  a.out = out.data_ptr();
-  a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
-  a.lse = lse.data_ptr<float>();
-  a.B = B; a.Hh = Hh; a.Ww = Ww;
-  a.C = qkv.size(-1) / 3;
-  a.num_heads = heads;
+  need(win_start.size() >= 2 && win_start.size() <= 9, "window_attn: win_start must have n_wg+1 <= 9 entries");
+  a.n_wg = static_cast<int>(win_start.size()) - 1;
+  for (size_t i = 0; i < win_start.size(); ++i) a.win_start[i] = static_cast<int>(win_start[i]);
+  a.my_wg = my_wg; a.sp = sp; a.my_sp = my_sp; a.shardN = shardN;
+  a.B = B; a.nWh = nWh; a.nWw = nWw; a.C = C; a.num_heads = heads;
   a.wh = wh; a.ww = ww; a.sh = sh; a.sw = sw;
   a.use_mask = use_mask ? 1 : 0;
-  a.grid_h = grid_h; a.grid_w = grid_w; a.row_offset = row_offset;
   a.scale = static_cast<float>(scale);
+  need(a.n_wg * a.sp <= tb::WA_MAX_PEERS, "window_attn: too many peer slots");
+  return a;
+}
+
+void window_attn(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t>& out_ptrs,
+                 const c10::optional<torch::Tensor>& bias_table, const std::vector<int64_t>& win_start, int64_t my_wg,
+                 int64_t sp, int64_t my_sp, int64_t shardN, int64_t B, int64_t nWh, int64_t nWw, int64_t C,
+                 int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale) {
+  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale);
+  need(qkv_ptrs.size() == static_cast<size_t>(a.n_wg * a.sp) && out_ptrs.size() == qkv_ptrs.size(),
+       "window_attn: one buffer per peer slot");
+  for (size_t i = 0; i < qkv_ptrs.size(); ++i) {
+    a.qkv[i] = reinterpret_cast<const void*>(qkv_ptrs[i]);
+    a.out[i] = reinterpret_cast<void*>(out_ptrs[i]);
+  }
+  a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
   rc_check(tb::window_attn_fwd(a, cur_stream()), "window_attn_fwd");
 }
 
-void window_attn_bwd(const torch::Tensor& qkv, const torch::Tensor& dout, torch::Tensor& dqkv,
-                     const c10::optional<torch::Tensor>& bias_table, const c10::optional<torch::Tensor>& dbias_table,
-                     const torch::Tensor& lse, int64_t B, int64_t Hh, int64_t Ww, int64_t heads, int64_t wh, int64_t ww,
-                     int64_t sh, int64_t sw, bool use_mask, int64_t grid_h, int64_t grid_w, int64_t row_offset,
+void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t>& dout_ptrs,
+                     const std::vector<int64_t>& dqkv_ptrs, const c10::optional<torch::Tensor>& bias_table,
+                     const c10::optional<torch::Tensor>& dbias_table, const std::vector<int64_t>& win_start,
+                     int64_t my_wg, int64_t sp, int64_t my_sp, int64_t shardN, int64_t B, int64_t nWh, int64_t nWw,
+                     int64_t C, int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask,
                      double scale) {
-  need(qkv.is_contiguous() && dout.is_contiguous() && dqkv.is_contiguous(), "window_attn_bwd: contiguous");
-  const c10::cuda::CUDAGuard guard(qkv.device());
-  tb::WindowAttnArgs a{};
-  a.qkv = qkv.data_ptr();
-  a.dout = dout.data_ptr();
-  a.dqkv = dqkv.data_ptr();
+  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale);
+  need(qkv_ptrs.size() == static_cast<size_t>(a.n_wg * a.sp) && dout_ptrs.size() == qkv_ptrs.size() &&
+           dqkv_ptrs.size() == qkv_ptrs.size(),
+       "window_attn_bwd: one buffer per peer slot");
+  for (size_t i = 0; i < qkv_ptrs.size(); ++i) {
+    a.qkv[i] = reinterpret_cast<const void*>(qkv_ptrs[i]);
+    a.dout[i] = reinterpret_cast<const void*>(dout_ptrs[i]);
+    a.dqkv[i] = reinterpret_cast<void*>(dqkv_ptrs[i]);
+  }
   a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
   a.dbias_table = dbias_table.has_value() ? dbias_table->data_ptr<float>() : nullptr;
-  a.lse = const_cast<float*>(lse.data_ptr<float>());
-  a.B = B; a.Hh = Hh; a.Ww = Ww;
-  a.C = qkv.size(-1) / 3;
-  a.num_heads = heads;
-  a.wh = wh; a.ww = ww; a.sh = sh; a.sw = sw;
-  a.use_mask = use_mask ? 1 : 0;
-  a.grid_h = grid_h; a.grid_w = grid_w; a.row_offset = row_offset;
-  a.scale = static_cast<float>(scale);
   rc_check(tb::window_attn_bwd(a, cur_stream()), "window_attn_bwd");
 }
 

@@ -69,21 +69,23 @@ int cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stre
 int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
 
 // window_attn.cu -------------------------------------------------------------------------------
+constexpr int WA_MAX_PEERS = 16;
+// Window attention over window-major activations (see window_attn.cu). Peer slot = wg_rank * sp + sp_rank.
 struct WindowAttnArgs {
-  const void* qkv;      // bf16 token-major [tokens, 3*C]  (q | k | v, head-major inside each)
-  void* out;            // bf16 [tokens, C]
-  const void* dout;     // backward: bf16 [tokens, C]
-  void* dqkv;           // backward: bf16 [tokens, 3*C]
-  const float* bias_table;  // fp32 [(2wh-1)*(2ww-1), nH] or null
-  float* dbias_table;       // backward, fp32 atomics, or null
-  float* lse;           // fp32 [tokens, nH]: log-sum-exp per query row (saved by forward, read by backward)
-  int B, Hh, Ww;        // token grid of this rank's activation, image-major [B, Hh, Ww, *]
-  int C, num_heads;
-  int wh, ww;           // window
-  int sh, sw;           // cyclic shift (0 for regular blocks)
-  int use_mask;         // apply the shifted-window region mask (-100)
-  int grid_h, grid_w;   // global token grid (for the mask regions); rows of this rank start at row_offset
-  int row_offset;
+  const void* qkv[WA_MAX_PEERS];   // bf16 [B * nW_p * shardN, 3*C] per peer slot (q | k | v, head-major inside each)
+  void* out[WA_MAX_PEERS];         // forward: bf16 [B * nW_p * shardN, C] per peer slot
+  const void* dout[WA_MAX_PEERS];  // backward: gradient of out
+  void* dqkv[WA_MAX_PEERS];        // backward: gradient of qkv
+  const float* bias_table;         // fp32 [(2wh-1)*(2ww-1), num_heads] or null
+  float* dbias_table;              // backward, fp32 atomics (caller zeroes), or null
+  int win_start[9];                // flat window range of window-group rank p: [win_start[p], win_start[p+1])
+  int n_wg, my_wg;                 // ranks along the window dimension, and mine
+  int sp, my_sp, shardN;           // tokens of a window are split into sp shards of shardN tokens
+  int B, nWh, nWw;                 // batch and global window grid
+  int wh, ww, sh, sw;              // window and cyclic shift (0 for regular blocks)
+  int use_mask;                    // shifted-window region mask (-100)
+  int C, num_heads;                // channels / heads held by this rank (C/tp, nH/tp)
+  int heads_per_cta;               // filled by the launcher
   float scale;
 };
 int window_attn_fwd(const WindowAttnArgs& a, cudaStream_t stream);

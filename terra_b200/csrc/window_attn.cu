@@ -1,6 +1,515 @@
+// Swin window attention (forward and backward) over a window-major activation layout, with the
+// shifted-window roll / partition / reverse, the window-parallel halo and the sequence-parallel K/V
+// gather all expressed as index math on the loads and stores:
+//
+//   * activations are stored unshifted, window-major: rank p of the window dimension holds
+//     [B, nW_p, shardN, *] rows for its flat window range [win_start[p], win_start[p+1]);
+//   * a CTA owns one window of the *shifted* frame and a group of heads; every token of that window is
+//     located (owner rank, row) in closed form and its Q/K/V row is read from the owner's buffer
+//     (a peer pointer over NVLink when the owner is another GPU); outputs are stored to the token's
+//     home row, again possibly on a peer;
+//   * relative-position bias comes from a shared-memory copy of the table, the shifted-window mask
+//     from the token's region id in the rolled frame; nothing of size [nW, N, N] is materialised.
+//
+// Windows here are small (N = wh*ww <= 128 keys), far below the tile sizes at which tcgen05 pays off,
+// and the op is bound by the Q/K/V/O traffic, so the products run on warp-level mma.sync with operands
+// staged in shared memory by 16-byte gathers.
 #include "common.cuh"
 #include "host_api.h"
+
 namespace tb {
-int window_attn_fwd(const WindowAttnArgs&, cudaStream_t) { return -999; }
-int window_attn_bwd(const WindowAttnArgs&, cudaStream_t) { return -999; }
+namespace {
+
+constexpr int WA_THREADS = 128;
+constexpr int WA_WARPS = 4;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+
+struct Geo {
+  int N, nrel;
+  int Hg, Wg;  // global token grid
+};
+
+// Home of token `tok` of shifted-frame window (ii, jj): which peer slot and which row of its buffer.
+struct Home {
+  int slot;
+  long long row;
+  int region;
+};
+
+__device__ __forceinline__ Home locate(const WindowAttnArgs& a, const Geo& g, int b, int ii, int jj, int tok) {
+  const int ti = tok / a.ww, tj = tok % a.ww;
+  const int hs = ii * a.wh + ti, ws = jj * a.ww + tj;  // position in the rolled frame
+  int gh = hs + a.sh, gw = ws + a.sw;
+  if (gh >= g.Hg) gh -= g.Hg;
+  if (gw >= g.Wg) gw -= g.Wg;
+  const int flat = (gh / a.wh) * a.nWw + (gw / a.ww);
+  const int st = (gh % a.wh) * a.ww + (gw % a.ww);
+  int wgr = 0;
+  while (wgr + 1 < a.n_wg && flat >= a.win_start[wgr + 1]) ++wgr;
+  const int nwp = a.win_start[wgr + 1] - a.win_start[wgr];
+  const int s = st / a.shardN;
+  Home h;
+  h.slot = wgr * a.sp + s;
+  h.row = (static_cast<long long>(b) * nwp + (flat - a.win_start[wgr])) * a.shardN + (st - s * a.shardN);
+  int rh = 0, rw = 0;
+  if (a.sh > 0) rh = hs < g.Hg - a.wh ? 0 : (hs < g.Hg - a.sh ? 1 : 2);
+  if (a.sw > 0) rw = ws < g.Wg - a.ww ? 0 : (ws < g.Wg - a.sw ? 1 : 2);
+  h.region = rh * 3 + rw;
+  return h;
+}
+
+// Shared-memory carve-up (bytes are computed identically on the host).
+template <int HD, int NPAD>
+struct Smem {
+  int G;        // channels per CTA (heads_per_cta * HD)
+  int stride;   // row stride in elements
+  __host__ __device__ Smem(int g) : G(g), stride(g + 8) {}
+  __host__ __device__ size_t tile_bytes() const { return static_cast<size_t>(NPAD) * stride * 2; }
+};
+
+template <int HD, int NPAD, bool BWD>
+__global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_constant__ WindowAttnArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int hpc = a.heads_per_cta;
+  const int G = hpc * HD;
+  const int stride = G + 8;
+  const int pstride = NPAD + 8;
+  Geo geo;
+  geo.N = a.wh * a.ww;
+  geo.nrel = (2 * a.wh - 1) * (2 * a.ww - 1);
+  geo.Hg = a.nWh * a.wh;
+  geo.Wg = a.nWw * a.ww;
+  const int N = geo.N;
+
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);
+  __nv_bfloat16* Ks = Qs + NPAD * stride;
+  __nv_bfloat16* Vs = Ks + NPAD * stride;
+  __nv_bfloat16* dOs = Vs + NPAD * stride;                              // BWD only
+  __nv_bfloat16* Ps = dOs + (BWD ? NPAD * stride : 0);                  // BWD only [NPAD][pstride]
+  __nv_bfloat16* dSs = Ps + (BWD ? NPAD * pstride : 0);                 // BWD only
+  __nv_bfloat16* dQs = dSs + (BWD ? NPAD * pstride : 0);                // BWD only [NPAD][HD+8]
+  float* bias_s = reinterpret_cast<float*>(dQs + (BWD ? NPAD * (HD + 8) : 0));   // [hpc][nrel]
+  float* dbias_s = bias_s + hpc * geo.nrel;                                         // BWD only [hpc][nrel]
+  long long* rowofs = reinterpret_cast<long long*>(dbias_s + (BWD ? hpc * geo.nrel : 0));  // [NPAD]
+  int* rowslot = reinterpret_cast<int*>(rowofs + NPAD);                                      // [NPAD]
+  int* rowreg = rowslot + NPAD;                                                              // [NPAD]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int cg = blockIdx.y;            // head group
+  const int head0 = cg * hpc;
+  const bool use_bias = a.bias_table != nullptr;
+  const int my_nw = a.win_start[a.my_wg + 1] - a.win_start[a.my_wg];
+  const int q0 = a.my_sp * a.shardN;
+  const int q1 = min(N, q0 + a.shardN);
+
+  for (int i = tid; i < hpc * geo.nrel; i += WA_THREADS) {
+    const int h = i / geo.nrel, r = i % geo.nrel;
+    bias_s[i] = use_bias ? a.bias_table[r * a.num_heads + head0 + h] : 0.f;
+    if (BWD) dbias_s[i] = 0.f;
+  }
+
+  const int items = a.B * my_nw;
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    const int b = item / my_nw, lw = item % my_nw;
+    const int flat = a.win_start[a.my_wg] + lw;
+    const int ii = flat / a.nWw, jj = flat % a.nWw;
+    __syncthreads();   // previous item fully consumed
+    if (tid < NPAD) {
+      if (tid < N) {
+        const Home h = locate(a, geo, b, ii, jj, tid);
+        rowofs[tid] = h.row;
+        rowslot[tid] = h.slot;
+        rowreg[tid] = h.region;
+      } else {
+        rowofs[tid] = -1;
+        rowslot[tid] = 0;
+        rowreg[tid] = 0;
+      }
+    }
+    __syncthreads();
+    // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group, 16 bytes at a time
+    {
+      const int vpr = G / 8;
+      const int mats = BWD ? 4 : 3;
+      for (int i = tid; i < NPAD * mats * vpr; i += WA_THREADS) {
+        const int v = i % vpr;
+        const int m = (i / vpr) % mats;
+        const int r = i / (vpr * mats);
+        uint4 val = make_uint4(0, 0, 0, 0);
+        const bool is_q_like = (m == 0 || m == 3);
+        if (r < N && (!is_q_like || BWD || (r >= q0 && r < q1))) {
+          const long long ro = rowofs[r];
+          const int sl = rowslot[r];
+          if (m < 3) {
+            const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(a.qkv[sl]);
+            val = *reinterpret_cast<const uint4*>(base + ro * (3LL * a.C) + m * a.C + cg * G + v * 8);
+          } else {
+            const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(a.dout[sl]);
+            val = *reinterpret_cast<const uint4*>(base + ro * a.C + cg * G + v * 8);
+          }
+        }
+        __nv_bfloat16* dst = (m == 0 ? Qs : (m == 1 ? Ks : (m == 2 ? Vs : dOs)));
+        *reinterpret_cast<uint4*>(dst + r * stride + v * 8) = val;
+      }
+    }
+    __syncthreads();
+
+    const int rblocks = NPAD / 16;
+    for (int hh = 0; hh < hpc; ++hh) {
+      const float* bt = bias_s + hh * geo.nrel;
+      // =============================== phase 1: per 16-query-row block
+      for (int rb = warp; rb < rblocks; rb += WA_WARPS) {
+        if (rb * 16 >= N) continue;
+        if (!BWD && (rb * 16 >= q1 || rb * 16 + 16 <= q0)) continue;
+        float s[NPAD / 8][4];
+#pragma unroll
+        for (int nb = 0; nb < NPAD / 8; ++nb)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) s[nb][k] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          uint32_t af[4];
+          ldsm_x4(af, Qs + (rb * 16 + (lane & 15)) * stride + hh * HD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+          for (int nb = 0; nb < NPAD / 8; nb += 2) {
+            uint32_t bf[4];
+            ldsm_x4(bf, Ks + (nb * 8 + (lane & 7) + (lane >> 4) * 8) * stride + hh * HD + kk * 16 + ((lane >> 3) & 1) * 8);
+            const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
+            mma_bf16_16816(s[nb], af, b0);
+            mma_bf16_16816(s[nb + 1], af, b1);
+          }
+        }
+        // scale, bias, mask, softmax (rows gq and gq+8 of the block)
+        const int r0 = rb * 16 + gq, r1 = r0 + 8;
+        const int reg0 = rowreg[min(r0, NPAD - 1)], reg1 = rowreg[min(r1, NPAD - 1)];
+        const int ti0 = r0 / a.ww, tj0 = r0 % a.ww, ti1 = r1 / a.ww, tj1 = r1 % a.ww;
+        float mx0 = -1e30f, mx1 = -1e30f;
+#pragma unroll
+        for (int nb = 0; nb < NPAD / 8; ++nb) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int col = nb * 8 + tq * 2 + (k & 1);
+            const bool lo = k < 2;
+            float v = s[nb][k] * a.scale;
+            if (col < N) {
+              const int ki = col / a.ww, kj = col % a.ww;
+              if (use_bias && (lo ? r0 : r1) < N) {
+                const int ti = lo ? ti0 : ti1, tj = lo ? tj0 : tj1;
+                v += bt[(ti - ki + a.wh - 1) * (2 * a.ww - 1) + (tj - kj + a.ww - 1)];
+              }
+              if (a.use_mask && rowreg[col] != (lo ? reg0 : reg1)) v += -100.f;
+            } else {
+              v = -1e30f;
+            }
+            s[nb][k] = v;
+            if (lo) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int nb = 0; nb < NPAD / 8; ++nb) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float e = __expf(s[nb][k] - (k < 2 ? mx0 : mx1));
+            s[nb][k] = e;
+            if (k < 2) sum0 += e; else sum1 += e;
+          }
+        }
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+        const float inv0 = 1.f / sum0, inv1 = 1.f / sum1;
+#pragma unroll
+        for (int nb = 0; nb < NPAD / 8; ++nb) {
+          s[nb][0] *= inv0;
+          s[nb][1] *= inv0;
+          s[nb][2] *= inv1;
+          s[nb][3] *= inv1;
+        }
+        if (!BWD) {
+          // O = P V, staged over this warp's own Q rows (no other warp reads them)
+          float o[HD / 8][4];
+#pragma unroll
+          for (int nb = 0; nb < HD / 8; ++nb)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) o[nb][k] = 0.f;
+#pragma unroll
+          for (int j = 0; j < NPAD / 16; ++j) {
+            const uint32_t pf[4] = {pack_bf16x2(s[2 * j][0], s[2 * j][1]), pack_bf16x2(s[2 * j][2], s[2 * j][3]),
+                                    pack_bf16x2(s[2 * j + 1][0], s[2 * j + 1][1]),
+                                    pack_bf16x2(s[2 * j + 1][2], s[2 * j + 1][3])};
+#pragma unroll
+            for (int nb = 0; nb < HD / 8; nb += 2) {
+              uint32_t bf[4];
+              ldsm_x4_t(bf, Vs + (j * 16 + (lane & 15)) * stride + hh * HD + nb * 8 + (lane >> 4) * 8);
+              const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
+              mma_bf16_16816(o[nb], pf, b0);
+              mma_bf16_16816(o[nb + 1], pf, b1);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int nb = 0; nb < HD / 8; ++nb) {
+            *reinterpret_cast<uint32_t*>(Qs + r0 * stride + hh * HD + nb * 8 + tq * 2) = pack_bf16x2(o[nb][0], o[nb][1]);
+            *reinterpret_cast<uint32_t*>(Qs + r1 * stride + hh * HD + nb * 8 + tq * 2) = pack_bf16x2(o[nb][2], o[nb][3]);
+          }
+        } else {
+          // dP = dO V^T
+          float dp[NPAD / 8][4];
+#pragma unroll
+          for (int nb = 0; nb < NPAD / 8; ++nb)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) dp[nb][k] = 0.f;
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            uint32_t af[4];
+            ldsm_x4(af, dOs + (rb * 16 + (lane & 15)) * stride + hh * HD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < NPAD / 8; nb += 2) {
+              uint32_t bf[4];
+              ldsm_x4(bf, Vs + (nb * 8 + (lane & 7) + (lane >> 4) * 8) * stride + hh * HD + kk * 16 + ((lane >> 3) & 1) * 8);
+              const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
+              mma_bf16_16816(dp[nb], af, b0);
+              mma_bf16_16816(dp[nb + 1], af, b1);
+            }
+          }
+          float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+          for (int nb = 0; nb < NPAD / 8; ++nb) {
+            d0 += s[nb][0] * dp[nb][0] + s[nb][1] * dp[nb][1];
+            d1 += s[nb][2] * dp[nb][2] + s[nb][3] * dp[nb][3];
+          }
+          d0 += __shfl_xor_sync(0xffffffffu, d0, 1);
+          d0 += __shfl_xor_sync(0xffffffffu, d0, 2);
+          d1 += __shfl_xor_sync(0xffffffffu, d1, 1);
+          d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
+          // dS = P * (dP - D); stash P and dS (bf16) for phase 2, accumulate the bias gradient
+#pragma unroll
+          for (int nb = 0; nb < NPAD / 8; ++nb) {
+            float ds[4];
+            ds[0] = s[nb][0] * (dp[nb][0] - d0);
+            ds[1] = s[nb][1] * (dp[nb][1] - d0);
+            ds[2] = s[nb][2] * (dp[nb][2] - d1);
+            ds[3] = s[nb][3] * (dp[nb][3] - d1);
+            const int col = nb * 8 + tq * 2;
+            *reinterpret_cast<uint32_t*>(Ps + r0 * pstride + col) = pack_bf16x2(s[nb][0], s[nb][1]);
+            *reinterpret_cast<uint32_t*>(Ps + r1 * pstride + col) = pack_bf16x2(s[nb][2], s[nb][3]);
+            *reinterpret_cast<uint32_t*>(dSs + r0 * pstride + col) = pack_bf16x2(ds[0], ds[1]);
+            *reinterpret_cast<uint32_t*>(dSs + r1 * pstride + col) = pack_bf16x2(ds[2], ds[3]);
+            if (use_bias && a.dbias_table != nullptr) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int c = col + (k & 1);
+                const int r = (k < 2) ? r0 : r1;
+                if (c < N && r < N && r >= q0 && r < q1) {
+                  const int ti = (k < 2) ? ti0 : ti1, tj = (k < 2) ? tj0 : tj1;
+                  atomicAdd(&dbias_s[hh * geo.nrel + (ti - c / a.ww + a.wh - 1) * (2 * a.ww - 1) + (tj - c % a.ww + a.ww - 1)],
+                            ds[k]);
+                }
+              }
+            }
+            dp[nb][0] = ds[0]; dp[nb][1] = ds[1]; dp[nb][2] = ds[2]; dp[nb][3] = ds[3];
+          }
+          // dQ = scale * dS K
+          float dq[HD / 8][4];
+#pragma unroll
+          for (int nb = 0; nb < HD / 8; ++nb)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) dq[nb][k] = 0.f;
+#pragma unroll
+          for (int j = 0; j < NPAD / 16; ++j) {
+            const uint32_t pf[4] = {pack_bf16x2(dp[2 * j][0], dp[2 * j][1]), pack_bf16x2(dp[2 * j][2], dp[2 * j][3]),
+                                    pack_bf16x2(dp[2 * j + 1][0], dp[2 * j + 1][1]),
+                                    pack_bf16x2(dp[2 * j + 1][2], dp[2 * j + 1][3])};
+#pragma unroll
+            for (int nb = 0; nb < HD / 8; nb += 2) {
+              uint32_t bf[4];
+              ldsm_x4_t(bf, Ks + (j * 16 + (lane & 15)) * stride + hh * HD + nb * 8 + (lane >> 4) * 8);
+              const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
+              mma_bf16_16816(dq[nb], pf, b0);
+              mma_bf16_16816(dq[nb + 1], pf, b1);
+            }
+          }
+#pragma unroll
+          for (int nb = 0; nb < HD / 8; ++nb) {
+            *reinterpret_cast<uint32_t*>(dQs + r0 * (HD + 8) + nb * 8 + tq * 2) =
+                pack_bf16x2(dq[nb][0] * a.scale, dq[nb][1] * a.scale);
+            *reinterpret_cast<uint32_t*>(dQs + r1 * (HD + 8) + nb * 8 + tq * 2) =
+                pack_bf16x2(dq[nb][2] * a.scale, dq[nb][3] * a.scale);
+          }
+        }
+      }
+      if (BWD) {
+        __syncthreads();
+        // =============================== phase 2: per 16-key block: dV = P^T dO, dK = scale * dS^T Q
+        for (int kb = warp; kb < rblocks; kb += WA_WARPS) {
+          if (kb * 16 >= N) continue;
+          float dv[HD / 8][4], dk[HD / 8][4];
+#pragma unroll
+          for (int nb = 0; nb < HD / 8; ++nb)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) dv[nb][k] = dk[nb][k] = 0.f;
+#pragma unroll
+          for (int j = 0; j < NPAD / 16; ++j) {   // query blocks (contraction)
+            uint32_t pa[4], sa[4];
+            const int prow = j * 16 + (lane & 7) + (lane >> 4) * 8;
+            const int pcol = kb * 16 + ((lane >> 3) & 1) * 8;
+            ldsm_x4_t(pa, Ps + prow * pstride + pcol);
+            ldsm_x4_t(sa, dSs + prow * pstride + pcol);
+#pragma unroll
+            for (int nb = 0; nb < HD / 8; nb += 2) {
+              uint32_t bf[4];
+              ldsm_x4_t(bf, dOs + (j * 16 + (lane & 15)) * stride + hh * HD + nb * 8 + (lane >> 4) * 8);
+              const uint32_t b0[2] = {bf[0], bf[1]}, b1[2] = {bf[2], bf[3]};
+              mma_bf16_16816(dv[nb], pa, b0);
+              mma_bf16_16816(dv[nb + 1], pa, b1);
+              ldsm_x4_t(bf, Qs + (j * 16 + (lane & 15)) * stride + hh * HD + nb * 8 + (lane >> 4) * 8);
+              const uint32_t c0[2] = {bf[0], bf[1]}, c1[2] = {bf[2], bf[3]};
+              mma_bf16_16816(dk[nb], sa, c0);
+              mma_bf16_16816(dk[nb + 1], sa, c1);
+            }
+          }
+          // K and V columns of this head are dead after phase 1: reuse them as the staging of dK, dV
+          const int r0 = kb * 16 + gq, r1 = r0 + 8;
+          __syncwarp();
+#pragma unroll
+          for (int nb = 0; nb < HD / 8; ++nb) {
+            const int c = hh * HD + nb * 8 + tq * 2;
+            *reinterpret_cast<uint32_t*>(Ks + r0 * stride + c) = pack_bf16x2(dk[nb][0] * a.scale, dk[nb][1] * a.scale);
+            *reinterpret_cast<uint32_t*>(Ks + r1 * stride + c) = pack_bf16x2(dk[nb][2] * a.scale, dk[nb][3] * a.scale);
+            *reinterpret_cast<uint32_t*>(Vs + r0 * stride + c) = pack_bf16x2(dv[nb][0], dv[nb][1]);
+            *reinterpret_cast<uint32_t*>(Vs + r1 * stride + c) = pack_bf16x2(dv[nb][2], dv[nb][3]);
+          }
+        }
+        __syncthreads();
+        // flush dQ of this head to the tokens' home rows
+        {
+          const int vpr = HD / 8;
+          for (int i = tid; i < (q1 - q0) * vpr; i += WA_THREADS) {
+            const int r = q0 + i / vpr, v = i % vpr;
+            __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.dqkv[rowslot[r]]);
+            *reinterpret_cast<uint4*>(base + rowofs[r] * (3LL * a.C) + cg * G + hh * HD + v * 8) =
+                *reinterpret_cast<const uint4*>(dQs + r * (HD + 8) + v * 8);
+          }
+        }
+        // the next head's phase 1 writes Ps/dSs/dQs again: wait for every reader
+        __syncthreads();
+      }
+    }
+    __syncthreads();
+    // ---- scatter results to the home rows
+    {
+      const int vpr = G / 8;
+      if (!BWD) {
+        for (int i = tid; i < (q1 - q0) * vpr; i += WA_THREADS) {
+          const int r = q0 + i / vpr, v = i % vpr;
+          __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.out[rowslot[r]]);
+          *reinterpret_cast<uint4*>(base + rowofs[r] * a.C + cg * G + v * 8) =
+              *reinterpret_cast<const uint4*>(Qs + r * stride + v * 8);
+        }
+      } else {
+        // With sequence parallelism every rank of the window recomputes the whole window (cheap) and keeps
+        // only the gradients of its own token shard, so no cross-rank reduction of dK/dV is needed.
+        for (int i = tid; i < (q1 - q0) * 2 * vpr; i += WA_THREADS) {
+          const int v = i % vpr;
+          const int m = (i / vpr) % 2;
+          const int r = q0 + i / (2 * vpr);
+          __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.dqkv[rowslot[r]]);
+          *reinterpret_cast<uint4*>(base + rowofs[r] * (3LL * a.C) + (1 + m) * a.C + cg * G + v * 8) =
+              *reinterpret_cast<const uint4*>((m == 0 ? Ks : Vs) + r * stride + v * 8);
+        }
+      }
+    }
+  }
+  if (BWD && use_bias && a.dbias_table != nullptr) {
+    __syncthreads();
+    for (int i = tid; i < hpc * geo.nrel; i += WA_THREADS) {
+      const int h = i / geo.nrel, r = i % geo.nrel;
+      atomicAdd(&a.dbias_table[r * a.num_heads + head0 + h], dbias_s[i]);
+    }
+  }
+}
+
+template <int HD, int NPAD, bool BWD>
+size_t smem_bytes(int hpc, int nrel) {
+  const int G = hpc * HD, stride = G + 8, pstride = NPAD + 8;
+  size_t b = static_cast<size_t>(NPAD) * stride * 2 * (BWD ? 4 : 3);
+  if (BWD) b += static_cast<size_t>(NPAD) * pstride * 2 * 2 + static_cast<size_t>(NPAD) * (HD + 8) * 2;
+  b += static_cast<size_t>(hpc) * nrel * 4 * (BWD ? 2 : 1);
+  b += NPAD * (8 + 4 + 4);
+  return b;
+}
+
+template <int HD, int NPAD, bool BWD>
+int launch(WindowAttnArgs a, cudaStream_t stream) {
+  const int nrel = (2 * a.wh - 1) * (2 * a.ww - 1);
+  // heads per CTA: as many as fit 128 channels and the shared-memory budget, dividing the head count
+  int hpc = 128 / HD;
+  if (hpc < 1) hpc = 1;
+  while (hpc > 1 && (a.num_heads % hpc != 0 || smem_bytes<HD, NPAD, BWD>(hpc, nrel) > 200 * 1024)) --hpc;
+  const size_t sb = smem_bytes<HD, NPAD, BWD>(hpc, nrel);
+  if (sb > 227 * 1024) return -20;
+  a.heads_per_cta = hpc;
+  static size_t configured = 0;
+  if (sb > configured) {
+    if (cudaFuncSetAttribute(window_attn_kernel<HD, NPAD, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(sb)) != cudaSuccess)
+      return -21;
+    configured = sb;
+  }
+  const int my_nw = a.win_start[a.my_wg + 1] - a.win_start[a.my_wg];
+  const int items = a.B * my_nw;
+  if (items <= 0) return 0;
+  const int groups = a.num_heads / hpc;
+  int gx = (148 * 4 + groups - 1) / groups;
+  if (gx > items) gx = items;
+  dim3 grid(gx, groups);
+  window_attn_kernel<HD, NPAD, BWD><<<grid, WA_THREADS, sb, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -22;
+}
+
+template <bool BWD>
+int dispatch(const WindowAttnArgs& a, cudaStream_t stream) {
+  const int N = a.wh * a.ww;
+  if (a.num_heads <= 0 || a.C % a.num_heads != 0) return -10;
+  const int hd = a.C / a.num_heads;
+  if (N > 128) return -11;
+  if (a.sp < 1 || a.shardN < 1 || a.n_wg < 1 || a.n_wg > 8 || a.n_wg * a.sp > WA_MAX_PEERS) return -12;
+  const int npad = N <= 64 ? 64 : (N <= 96 ? 96 : 128);
+#define TB_WA_CASE(HD_, NP_) \
+  if (hd == HD_ && npad == NP_) return launch<HD_, NP_, BWD>(a, stream);
+  TB_WA_CASE(16, 64) TB_WA_CASE(32, 64) TB_WA_CASE(64, 64) TB_WA_CASE(128, 64)
+  TB_WA_CASE(16, 96) TB_WA_CASE(32, 96) TB_WA_CASE(64, 96) TB_WA_CASE(128, 96)
+  TB_WA_CASE(16, 128) TB_WA_CASE(32, 128) TB_WA_CASE(64, 128) TB_WA_CASE(128, 128)
+#undef TB_WA_CASE
+  return -13;
+}
+
+}  // namespace
+
+int window_attn_fwd(const WindowAttnArgs& a, cudaStream_t stream) { return dispatch<false>(a, stream); }
+int window_attn_bwd(const WindowAttnArgs& a, cudaStream_t stream) { return dispatch<true>(a, stream); }
+
 }  // namespace tb
