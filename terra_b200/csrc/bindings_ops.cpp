@@ -25,12 +25,14 @@ void layernorm_fwd(const torch::Tensor& x, const torch::Tensor& g, const torch::
 }
 
 void layernorm_bwd(const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& g, const torch::Tensor& mean,
-                   const torch::Tensor& rstd, torch::Tensor& dx, torch::Tensor& dg, torch::Tensor& db) {
+                   const torch::Tensor& rstd, torch::Tensor& dx, torch::Tensor& dg, torch::Tensor& db,
+                   const c10::optional<torch::Tensor>& dres) {
   need(dy.is_contiguous() && x.is_contiguous(), "layernorm_bwd: contiguous inputs");
   const c10::cuda::CUDAGuard guard(x.device());
   const int C = x.size(-1);
   rc_check(tb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), g.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                             dx.data_ptr(), dg.data_ptr<float>(), db.data_ptr<float>(), x.numel() / C, C, cur_stream()),
+                             dx.data_ptr(), dg.data_ptr<float>(), db.data_ptr<float>(), opt_ptr(dres), x.numel() / C, C,
+                             cur_stream()),
            "layernorm_bwd");
 }
 
@@ -49,10 +51,10 @@ void groupnorm_stats(const torch::Tensor& x, torch::Tensor& sums, int64_t groups
 }
 
 void groupnorm_silu_apply(const torch::Tensor& x, const torch::Tensor& stats, const torch::Tensor& g,
-                          const torch::Tensor& b, torch::Tensor& y, int64_t groups) {
+                          const torch::Tensor& b, const c10::optional<torch::Tensor>& res, torch::Tensor& y, int64_t groups) {
   need(x.is_contiguous() && x.dim() == 3, "groupnorm_silu_apply: [B,HW,C]");
   const c10::cuda::CUDAGuard guard(x.device());
-  rc_check(tb::groupnorm_silu_apply(x.data_ptr(), stats.data_ptr<float>(), g.data_ptr(), b.data_ptr(), y.data_ptr(),
+  rc_check(tb::groupnorm_silu_apply(x.data_ptr(), stats.data_ptr<float>(), g.data_ptr(), b.data_ptr(), opt_ptr(res), y.data_ptr(),
                                     x.size(0), x.size(1), x.size(2), groups, cur_stream()),
            "groupnorm_silu_apply");
 }

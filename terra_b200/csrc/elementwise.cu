@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const __nv_bfloat16*
                                                             const __nv_bfloat16* __restrict__ gamma,
                                                             const float* __restrict__ mean, const float* __restrict__ rstd,
                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
-                                                            float* __restrict__ dbeta, long long rows, int C) {
+                                                            float* __restrict__ dbeta, const __nv_bfloat16* __restrict__ dres,
+                                                            long long rows, int C) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int nvec = C >> 3;
@@ -145,6 +146,12 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const __nv_bfloat16*
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rs * (dv[i][j] - s1 - xh[i][j] * s2);
+        if (dres != nullptr) {
+          float rr[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + row * C)[vi], rr);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rr[j];
+        }
         or_[vi] = pack8(o);
       }
     }
@@ -253,6 +260,7 @@ __global__ void __launch_bounds__(256) groupnorm_silu_apply_kernel(const __nv_bf
                                                                    const float* __restrict__ stats,
                                                                    const __nv_bfloat16* __restrict__ gamma,
                                                                    const __nv_bfloat16* __restrict__ beta,
+                                                                   const __nv_bfloat16* __restrict__ res,
                                                                    __nv_bfloat16* __restrict__ y, long long HW, int C,
                                                                    int groups, long long total_vec) {
   const int nvec = C >> 3;
@@ -272,6 +280,12 @@ __global__ void __launch_bounds__(256) groupnorm_silu_apply_kernel(const __nv_bf
       const float mu = stats[(b * groups + grp) * 2], rs = stats[(b * groups + grp) * 2 + 1];
       const float z = (f[j] - mu) * rs * g[j] + bt[j];
       o[j] = z * sigmoidf_(z);
+    }
+    if (res != nullptr) {
+      float rr[8];
+      unpack8(reinterpret_cast<const uint4*>(res)[i], rr);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] += rr[j];
     }
     reinterpret_cast<uint4*>(y)[i] = pack8(o);
   }
@@ -492,7 +506,7 @@ int layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, f
 }
 
 int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
-                  float* dgamma, float* dbeta, long long rows, int C, cudaStream_t stream) {
+                  float* dgamma, float* dbeta, const void* dres, long long rows, int C, cudaStream_t stream) {
   if (C % 8 != 0 || C > 2048) return -1;
   const int vpl = (C / 8 + 31) / 32;
   const int grid = grid_for(rows, 8, 148 * 4);
@@ -500,7 +514,7 @@ int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float*
   TB_LN_DISPATCH(vpl, (layernorm_bwd_kernel<VPL><<<grid, 256, sh, stream>>>(
                           static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
                           static_cast<const __nv_bfloat16*>(gamma), mean, rstd, static_cast<__nv_bfloat16*>(dx), dgamma,
-                          dbeta, rows, C)));
+                          dbeta, static_cast<const __nv_bfloat16*>(dres), rows, C)));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -526,13 +540,14 @@ int groupnorm_stats(const void* x, float* sums, int B, long long HW, int C, int 
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int groupnorm_silu_apply(const void* x, const float* stats, const void* gamma, const void* beta, void* y, int B,
-                         long long HW, int C, int groups, cudaStream_t stream) {
+int groupnorm_silu_apply(const void* x, const float* stats, const void* gamma, const void* beta, const void* res, void* y,
+                         int B, long long HW, int C, int groups, cudaStream_t stream) {
   if (C % 8 != 0 || C % groups != 0) return -1;
   const long long total_vec = static_cast<long long>(B) * HW * (C / 8);
   groupnorm_silu_apply_kernel<<<grid_for(total_vec, 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), stats, static_cast<const __nv_bfloat16*>(gamma),
-      static_cast<const __nv_bfloat16*>(beta), static_cast<__nv_bfloat16*>(y), HW, C, groups, total_vec);
+      static_cast<const __nv_bfloat16*>(beta), static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(y), HW,
+      C, groups, total_vec);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -37,16 +37,16 @@ int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, i
 // LayerNorm over the last dimension (C <= 8192, C % 8 == 0), bf16 in/out, fp32 statistics.
 int layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
                   long long rows, int C, float eps, cudaStream_t stream);
-// dx (bf16); dgamma/dbeta accumulated atomically into fp32 buffers that the caller zeroed.
+// dx (bf16, plus `dres` when given); dgamma/dbeta accumulated atomically into fp32 buffers that the caller zeroed.
 int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
-                  float* dgamma, float* dbeta, long long rows, int C, cudaStream_t stream);
+                  float* dgamma, float* dbeta, const void* dres, long long rows, int C, cudaStream_t stream);
 // Column sums of a bf16 [rows, C] matrix into fp32 out[C] (atomic accumulate; caller zeroes out).
 int colsum_bf16(const void* x, float* out, long long rows, int C, long long ld, cudaStream_t stream);
 // GroupNorm statistics over NHWC bf16 [B, HW, C]: accumulates per (b, group) sum and sum of squares (fp32, zeroed).
 int groupnorm_stats(const void* x, float* sums, int B, long long HW, int C, int groups, cudaStream_t stream);
-// y = silu((x - mean) * rstd * gamma + beta); `stats` holds {mean, rstd} per (b, group).
-int groupnorm_silu_apply(const void* x, const float* stats, const void* gamma, const void* beta, void* y, int B,
-                         long long HW, int C, int groups, cudaStream_t stream);
+// y = silu((x - mean) * rstd * gamma + beta) [+ res]; `stats` holds {mean, rstd} per (b, group).
+int groupnorm_silu_apply(const void* x, const float* stats, const void* gamma, const void* beta, const void* res, void* y,
+                         int B, long long HW, int C, int groups, cudaStream_t stream);
 // Backward of GroupNorm+SiLU. Pass 1 accumulates per (b,group) {sum(dz), sum(dz*xhat)} and per-channel dgamma/dbeta;
 // pass 2 produces dx. dz = dy * silu'(z).
 int groupnorm_silu_bwd_reduce(const void* dy, const void* x, const float* stats, const void* gamma, const void* beta,

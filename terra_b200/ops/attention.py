@@ -1,0 +1,201 @@
+"""Swin window attention over the window-major activation layout.
+
+``WindowGeometry`` describes one rank's slice of the global window grid. ``window_attention`` dispatches to
+the sm_100a kernel (csrc/window_attn.cu) on CUDA tensors and to ``window_attention_reference`` (plain PyTorch,
+also the numerical oracle of the tests) elsewhere.
+
+Layout contract: activations are ``[B * nW_local * shardN, C]`` rows, windows in row-major order of the
+rank's flat window range, tokens row-major inside the window, never shifted. For odd ("shifted") blocks the
+roll by ``(-sh, -sw)``, the partition, the reverse and the roll back are index arithmetic
+(reference semantics: models/transformer.py:976-1023, core/window_parallel.py:26-46).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _ext
+
+
+@dataclass
+class WindowGeometry:
+    B: int
+    nWh: int
+    nWw: int
+    wh: int
+    ww: int
+    win_start: List[int] = field(default_factory=list)   # flat window range per window-group rank
+    my_wg: int = 0
+    sp: int = 1
+    my_sp: int = 0
+
+    def __post_init__(self):
+        if not self.win_start:
+            self.win_start = [0, self.nWh * self.nWw]
+
+    @property
+    def N(self) -> int:
+        return self.wh * self.ww
+
+    @property
+    def shardN(self) -> int:
+        return (self.N + self.sp - 1) // self.sp
+
+    @property
+    def n_wg(self) -> int:
+        return len(self.win_start) - 1
+
+    @property
+    def nW_local(self) -> int:
+        return self.win_start[self.my_wg + 1] - self.win_start[self.my_wg]
+
+    @property
+    def rows_local(self) -> int:
+        return self.B * self.nW_local * self.shardN
+
+    def shift(self, shifted: bool):
+        return (self.wh // 2, self.ww // 2) if shifted else (0, 0)
+
+
+def relative_position_index(wh: int, ww: int) -> torch.Tensor:
+    """[N, N] index into the ``(2wh-1)*(2ww-1)`` bias table (standard Swin)."""
+    coords = torch.stack(torch.meshgrid(torch.arange(wh), torch.arange(ww), indexing="ij")).flatten(1)
+    rel = coords[:, :, None] - coords[:, None, :]
+    return (rel[0] + wh - 1) * (2 * ww - 1) + (rel[1] + ww - 1)
+
+
+def region_ids(H: int, W: int, wh: int, ww: int, sh: int, sw: int) -> torch.Tensor:
+    """[H, W] region id (0..8) of every position of the rolled frame (Swin SW-MSA mask regions)."""
+    rh = torch.zeros(H, dtype=torch.long)
+    rw = torch.zeros(W, dtype=torch.long)
+    if sh > 0:
+        rh[H - wh:H - sh] = 1
+        rh[H - sh:] = 2
+    if sw > 0:
+        rw[W - ww:W - sw] = 1
+        rw[W - sw:] = 2
+    return rh[:, None] * 3 + rw[None, :]
+
+
+def shifted_window_sources(geo: WindowGeometry, shifted: bool):
+    """For every window of the shifted frame (all ``nWh*nWw`` of them) and token, the flat source window and
+    source token in the unshifted frame, plus the token's mask region. Shapes ``[nW, N]``."""
+    sh, sw = geo.shift(shifted)
+    H, W = geo.nWh * geo.wh, geo.nWw * geo.ww
+    hs = torch.arange(H)[:, None].expand(H, W)
+    ws = torch.arange(W)[None, :].expand(H, W)
+    gh = (hs + sh) % H
+    gw = (ws + sw) % W
+    src_win = (gh // geo.wh) * geo.nWw + (gw // geo.ww)
+    src_tok = (gh % geo.wh) * geo.ww + (gw % geo.ww)
+    reg = region_ids(H, W, geo.wh, geo.ww, sh, sw)
+
+    def part(t):
+        return t.view(geo.nWh, geo.wh, geo.nWw, geo.ww).permute(0, 2, 1, 3).reshape(geo.nWh * geo.nWw, geo.N)
+
+    return part(src_win), part(src_tok), part(reg)
+
+
+def attention_core_reference(q, k, v, scale, bias, mask):
+    """q,k,v: [nWin, nH, Nq|N, hd] fp32; bias [nH, Nq, N] or None; mask [nWin, Nq, N] additive or None."""
+    attn = (q * scale) @ k.transpose(-2, -1)
+    if bias is not None:
+        attn = attn + bias.unsqueeze(0)
+    if mask is not None:
+        attn = attn + mask.unsqueeze(1)
+    return torch.softmax(attn, dim=-1) @ v
+
+
+def window_attention_reference(qkv_all: torch.Tensor, geo: WindowGeometry, num_heads: int, shifted: bool,
+                               bias_table: Optional[torch.Tensor], use_mask: bool, scale: float) -> torch.Tensor:
+    """Reference on the *global* window-major tensor ``[B, nW_total, N, 3C]`` -> ``[B, nW_total, N, C]``
+    (single rank view; rows are gathered with explicit index tensors)."""
+    B, nW, N = geo.B, geo.nWh * geo.nWw, geo.N
+    C = qkv_all.shape[-1] // 3
+    hd = C // num_heads
+    src_win, src_tok, reg = shifted_window_sources(geo, shifted)
+    flat_src = (src_win * N + src_tok).to(qkv_all.device)                       # [nW, N]
+    x = qkv_all.reshape(B, nW * N, 3 * C)[:, flat_src.reshape(-1)].reshape(B, nW, N, 3, num_heads, hd)
+    q, k, v = (x[:, :, :, i].permute(0, 1, 3, 2, 4).reshape(B * nW, num_heads, N, hd) for i in range(3))
+    bias = None
+    if bias_table is not None:
+        idx = relative_position_index(geo.wh, geo.ww).to(bias_table.device)
+        bias = bias_table[idx.reshape(-1)].reshape(N, N, num_heads).permute(2, 0, 1)
+    mask = None
+    if use_mask and shifted:
+        reg = reg.to(qkv_all.device)
+        mask = (reg[:, :, None] != reg[:, None, :]).to(q.dtype) * -100.0
+        mask = mask.repeat(B, 1, 1)
+    o = attention_core_reference(q, k, v, scale, bias, mask)                     # [B*nW, nH, N, hd]
+    o = o.permute(0, 2, 1, 3).reshape(B, nW * N, C)
+    out = torch.empty_like(o)
+    out[:, flat_src.reshape(-1)] = o
+    return out.reshape(B, nW, N, C)
+
+
+class _WindowAttnFn(torch.autograd.Function):
+    """CUDA path. ``qkv`` is this rank's buffer; ``peers`` optionally lists raw device addresses of every peer
+    slot's qkv / out / dout / dqkv buffers (symmetric memory) - absent for a single rank."""
+
+    @staticmethod
+    def forward(ctx, qkv, bias_table, geo, num_heads, shifted, use_mask, scale, comm):
+        ext = _ext.load()
+        C = qkv.shape[-1] // 3
+        sh, sw = geo.shift(shifted)
+        bias_f32 = None
+        if bias_table is not None:
+            bias_f32 = bias_table.detach().float().contiguous()
+        if comm is None:
+            out = torch.empty(qkv.shape[0], C, dtype=torch.bfloat16, device=qkv.device)
+            qkv_ptrs, out_ptrs = [qkv.data_ptr()], [out.data_ptr()]
+        else:
+            out, qkv_ptrs, out_ptrs = comm.attn_forward_buffers(qkv, C)
+        ext.window_attn_fwd(qkv_ptrs, out_ptrs, bias_f32, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
+                            geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh, geo.ww, sh, sw,
+                            bool(use_mask and shifted), float(scale))
+        if comm is not None:
+            out = comm.attn_forward_done(out)
+        ctx.save_for_backward(qkv, bias_f32 if bias_f32 is not None else torch.empty(0, device=qkv.device))
+        ctx.geo, ctx.num_heads, ctx.shifted, ctx.use_mask, ctx.scale, ctx.comm = geo, num_heads, shifted, use_mask, scale, comm
+        ctx.has_bias = bias_table is not None
+        ctx.bias_param = bias_table
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ext = _ext.load()
+        qkv, bias_f32 = ctx.saved_tensors
+        geo = ctx.geo
+        C = qkv.shape[-1] // 3
+        sh, sw = geo.shift(ctx.shifted)
+        dout = dout.contiguous()
+        dbias = torch.zeros_like(bias_f32) if ctx.has_bias else None
+        if ctx.comm is None:
+            dqkv = torch.empty_like(qkv)
+            qkv_ptrs, dout_ptrs, dqkv_ptrs = [qkv.data_ptr()], [dout.data_ptr()], [dqkv.data_ptr()]
+        else:
+            dqkv, qkv_ptrs, dout_ptrs, dqkv_ptrs = ctx.comm.attn_backward_buffers(qkv, dout)
+        ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32 if ctx.has_bias else None, dbias,
+                            list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw,
+                            C, ctx.num_heads, geo.wh, geo.ww, sh, sw, bool(ctx.use_mask and ctx.shifted),
+                            float(ctx.scale))
+        if ctx.comm is not None:
+            dqkv = ctx.comm.attn_backward_done(dqkv)
+        return dqkv, dbias, None, None, None, None, None, None
+
+
+def window_attention(qkv: torch.Tensor, geo: WindowGeometry, num_heads: int, shifted: bool,
+                     bias_table: Optional[torch.Tensor], use_mask: bool, scale: float, comm=None) -> torch.Tensor:
+    """``qkv``: ``[rows_local, 3C]`` -> ``[rows_local, C]``. ``comm`` supplies peer access for multi-rank layouts
+    (``None``: this rank owns every window and token)."""
+    fused = comm is None or getattr(comm, "fused", False)
+    if qkv.is_cuda and fused:
+        return _WindowAttnFn.apply(qkv, bias_table, geo, num_heads, shifted, use_mask, scale, comm)
+    if comm is not None and comm.world > 1:
+        return comm.window_attention_portable(qkv, geo, num_heads, shifted, bias_table, use_mask, scale)
+    C = qkv.shape[-1] // 3
+    out = window_attention_reference(qkv.reshape(geo.B, geo.nWh * geo.nWw, geo.N, 3 * C), geo, num_heads, shifted,
+                                     bias_table, use_mask, scale)
+    return out.reshape(-1, C)

@@ -1,0 +1,365 @@
+"""Per-rank view of the parallel layout: who owns which rows, windows, token shards and channel shards, and the
+operators whose implementation depends on that (attention / MLP halves, stripe <-> window relayout, sampling-block
+halos and distributed GroupNorm).
+
+Layouts (reference semantics: core/parallel/layout_transform.py, core/rank_manager.py:216-246):
+
+* conv stage: NHWC row stripes of the token grid, ``H / wp`` rows per window-parallel rank, non-periodic halos;
+* transformer stage: window-major rows ``[B, windows of my window group (TP chunk), my token shard, C]``:
+  window group ``g`` owns the windows that the assignment mode gives it, SP rank ``s`` the tokens
+  ``[s*shardN, (s+1)*shardN)`` of each window, TP rank ``t`` the chunk ``[t*wpt, (t+1)*wpt)`` of the group's
+  windows between blocks (activations) and the heads / hidden channels ``t`` inside blocks (parameters).
+
+With one rank every method degenerates to local index permutations.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import numpy as np
+import torch
+import torch.nn.functional as TF
+
+from ..ops import blocks as B
+from ..ops.attention import WindowGeometry, window_attention, window_attention_reference
+from . import collectives as C
+from .window_assignment import window_owner_map
+
+
+class DomainComm:
+    """Row-stripe helpers for the sampling blocks (halo rows, GroupNorm statistics)."""
+
+    def __init__(self, group, ranks: Optional[List[int]], rank_in_group: int):
+        self.group = group
+        self.ranks = ranks or [0]
+        self.world = len(self.ranks)
+        self.idx = rank_in_group
+        self.prev = self.ranks[self.idx - 1] if self.idx > 0 else None
+        self.next = self.ranks[self.idx + 1] if self.idx < self.world - 1 else None
+
+    # ---- CPU / portable
+    def halo_exchange_cpu(self, x_nchw, halo: int):
+        return C.halo_rows(x_nchw, halo, self.prev, self.next, self.group)
+
+    def group_norm_cpu(self, x, groups, weight, bias, eps):
+        """GroupNorm whose statistics span the stripes of all ranks (two-moment form, one all-reduce)."""
+        Bn, Cn, H, W = x.shape
+        xg = x.reshape(Bn, groups, -1)
+        s = torch.stack([xg.sum(-1), (xg * xg).sum(-1)], dim=-1)
+        s = C.all_reduce_sum(s, self.group)
+        n = xg.shape[-1] * self.world
+        mean = s[..., 0] / n
+        var = (s[..., 1] / n - mean * mean).clamp_min(0)
+        xn = (xg - mean[..., None]) * torch.rsqrt(var + eps)[..., None]
+        return xn.reshape(Bn, Cn, H, W) * weight[None, :, None, None] + bias[None, :, None, None]
+
+    # ---- CUDA (portable-collective version; the peer-memory halo path replaces these where enabled)
+    def all_reduce_small(self, t):
+        return C.all_reduce_(t.clone(), self.group)
+
+    def _pad_rows(self, x):
+        """NHWC [B,h,W,C] -> [B,h+2,W,C] with neighbour rows (zeros at the global edges)."""
+        xp = C._HaloRows.forward(_Ctx(), x.permute(0, 3, 1, 2), 1, self.prev, self.next, self.group)
+        return xp.permute(0, 2, 3, 1).contiguous()
+
+    def conv_fwd(self, x, wp, y, stride, bias16):
+        """3x3 convolution of a row stripe: neighbour rows are attached, the single-image kernel runs on the
+        taller tensor and the rows that belong to this rank are kept."""
+        from .. import _ext
+        from ..ops import _flags as F
+        from ..ops.gemm import status_word
+
+        ext = _ext.load()
+        xp = self._pad_rows(x)
+        Bn, h, W, _ = x.shape
+        flags = F.EPI_BIAS if bias16 is not None else 0
+        if stride == 1:
+            yp = torch.empty(Bn, h + 2, W, y.shape[3], device=x.device, dtype=torch.bfloat16)
+            ext.conv3x3_fwd(xp, wp, yp, 1, flags, bias16, None, status_word(x.device))
+            y.copy_(yp[:, 1:h + 1])
+        else:
+            # local output row j reads local rows 2j-1..2j+1 = rows 2j+1..2j+3 of T = [zero row, xp]:
+            # that is output row j+1 of the single-image kernel on T
+            T = torch.cat([xp.new_zeros(Bn, 1, W, xp.shape[3]), xp], dim=1)
+            yp = torch.empty(Bn, (T.shape[1] + 1) // 2, W // 2, y.shape[3], device=x.device, dtype=torch.bfloat16)
+            ext.conv3x3_fwd(T, wp, yp, 2, flags, bias16, None, status_word(x.device))
+            y.copy_(yp[:, 1:1 + y.shape[1]])
+
+    def conv_wgrad(self, x, dy, dw9, stride):
+        from .. import _ext
+        from ..ops.gemm import status_word
+
+        ext = _ext.load()
+        xp = self._pad_rows(x)
+        Bn, h, W, _ = x.shape
+        if stride == 1:
+            dyp = torch.zeros(Bn, h + 2, W, dy.shape[3], device=x.device, dtype=torch.bfloat16)
+            dyp[:, 1:h + 1] = dy
+            ext.conv3x3_wgrad(xp, dyp, dw9, 1, 8, status_word(x.device))
+        else:
+            T = torch.cat([xp.new_zeros(Bn, 1, W, xp.shape[3]), xp], dim=1)
+            dyp = torch.zeros(Bn, (T.shape[1] + 1) // 2, W // 2, dy.shape[3], device=x.device, dtype=torch.bfloat16)
+            dyp[:, 1:1 + dy.shape[1]] = dy
+            ext.conv3x3_wgrad(T, dyp, dw9, 2, 8, status_word(x.device))
+
+    def fold_halo_grad(self, dxp, H, W):
+        """dxp: [B, H+2, W+2, C] gradient of the zero/halo padded input -> gradient of the local rows, with the
+        halo rows' gradients sent back to their owners."""
+        g = dxp[:, :, 1:W + 1].permute(0, 3, 1, 2).contiguous()
+        gx = C._HaloRows.backward(_Ctx((1, self.prev, self.next, self.group)), g)[0]
+        return gx.permute(0, 2, 3, 1)
+
+
+class _Ctx:
+    """Minimal stand-in for an autograd context when a Function's forward/backward is used as a plain routine."""
+
+    def __init__(self, p=None):
+        self.p = p
+
+
+class ParallelContext:
+    def __init__(self, manager=None, window_size=(8, 8), token_hw=(0, 0), batch=1, window_assignment_mode="regular"):
+        self.manager = manager
+        self.wh, self.ww = int(window_size[0]), int(window_size[1])
+        self.Ht, self.Wt = int(token_hw[0]), int(token_hw[1])
+        if self.Ht % self.wh or self.Wt % self.ww:
+            raise ValueError(f"token grid {(self.Ht, self.Wt)} must be divisible by window {(self.wh, self.ww)}")
+        self.nWh, self.nWw = self.Ht // self.wh, self.Wt // self.ww
+        self.B = batch
+        m = manager
+        self.world = m.wp_size if m is not None else 1
+        self.wp_rank = m.wp_rank if m is not None else 0
+        self.n_wg = m.xfmr_window_group_size if m is not None else 1
+        self.sp = m.xfmr_sp_size if m is not None else 1
+        self.tp = m.xfmr_tp_size if m is not None else 1
+        self.wg_rank = m.xfmr_window_group_rank if m is not None else 0
+        self.sp_rank = m.xfmr_sp_rank if m is not None else 0
+        self.tp_rank = m.xfmr_tp_rank if m is not None else 0
+        self.mode = window_assignment_mode
+        topo = m.xfmr_wp_topo if m is not None else (1, 1)
+        owner = window_owner_map(self.nWh, self.nWw, topo[0], topo[1], self.mode).reshape(-1)
+        self.owner = owner
+        self.windows_of = [np.nonzero(owner == g)[0] for g in range(self.n_wg)]      # flat ids, row-major
+        counts = [len(w) for w in self.windows_of]
+        self.contiguous = all(len(w) == 0 or (w[-1] - w[0] + 1 == len(w)) for w in self.windows_of) and \
+            all(self.windows_of[g][0] == sum(counts[:g]) for g in range(self.n_wg) if counts[g])
+        self.win_start = [0] + np.cumsum(counts).tolist()
+        self.N = self.wh * self.ww
+        self.shardN = (self.N + self.sp - 1) // self.sp
+        if self.N % self.sp != 0:
+            raise ValueError(f"window tokens {self.N} must be divisible by xfmr_sp_size {self.sp}")
+        self.nW_group = counts[self.wg_rank]
+        self.wpt = (self.nW_group + self.tp - 1) // self.tp                            # windows per TP rank
+        self.tp_sizes_windows = [max(0, min(self.wpt, self.nW_group - t * self.wpt)) for t in range(self.tp)]
+        self.dom = DomainComm(m.window_parallel_group if m is not None else None,
+                              m.window_parallel_ranks if m is not None else None, self.wp_rank)
+        self.fused_comm = None     # peer-memory (NVLink) implementation, attached by terra_b200.parallel.nvlink
+
+    # ------------------------------------------------------------------ geometry
+    def geometry(self, batch: int) -> WindowGeometry:
+        return WindowGeometry(batch, self.nWh, self.nWw, self.wh, self.ww, list(self.win_start), self.wg_rank, self.sp,
+                              self.sp_rank)
+
+    def rows_between_blocks(self, batch: int) -> int:
+        return batch * self.tp_sizes_windows[self.tp_rank] * self.shardN
+
+    # ------------------------------------------------------------------ transformer halves
+    def attention_half(self, x, mod):
+        batch = self._batch_of(x)
+        geo = self.geometry(batch)
+        comm = self._attn_comm(batch)
+        if self.sp == 1 and self.tp == 1 and (comm is None or getattr(comm, "fused", False)):
+            return B.attention_half(x, mod, geo, mod.shifted, comm)
+        return self._attention_half_factorized(x, mod, geo, batch)
+
+    def mlp_half(self, x, mod):
+        if self.tp == 1:
+            return B.mlp_half(x, mod)
+        return self._mlp_half_tp(x, mod)
+
+    def _batch_of(self, x) -> int:
+        per = self.tp_sizes_windows[self.tp_rank] * self.shardN
+        return x.shape[0] // max(per, 1)
+
+    def _attn_comm(self, batch):
+        if self.n_wg * self.sp == 1:
+            return None
+        if self.fused_comm is not None and self.contiguous:
+            return self.fused_comm
+        return _PortableAttnComm(self, batch)
+
+    # ---- factorised SP / TP halves on portable collectives (CPU oracle path and the NCCL baseline)
+    def _tp_sizes_rows(self, batch):
+        return [batch * n * self.shardN for n in self.tp_sizes_windows]
+
+    def _ag_tp(self, x, batch):
+        if self.tp == 1:
+            return x
+        # rows are [B, windows, tokens]: gather along windows, batch stays outermost
+        per = [n * self.shardN for n in self.tp_sizes_windows]
+        xs = x.reshape(batch, per[self.tp_rank], -1).transpose(0, 1)
+        full = C.all_gather_rows(xs, self.manager.xfmr_tp_group, per)
+        return full.transpose(0, 1).reshape(batch * sum(per), -1)
+
+    def _rs_tp(self, x, batch):
+        if self.tp == 1:
+            return x
+        per = [n * self.shardN for n in self.tp_sizes_windows]
+        xs = x.reshape(batch, sum(per), -1).transpose(0, 1)
+        mine = C.reduce_scatter_rows(xs, self.manager.xfmr_tp_group, per)
+        return mine.transpose(0, 1).reshape(batch * per[self.tp_rank], -1)
+
+    def _lin(self, x, lin, residual=None):
+        if x.is_cuda:
+            return B.linear(x.contiguous(), lin, residual)
+        y = TF.linear(x, lin.weight, lin.bias)
+        return y if residual is None else y + residual
+
+    def _ln(self, x, norm):
+        if x.is_cuda:
+            return _LayerNormFn.apply(x.contiguous(), norm.weight, norm.bias)
+        return TF.layer_norm(x, (x.shape[-1],), norm.weight, norm.bias, B.LN_EPS)
+
+    def _attention_half_factorized(self, x, mod, geo, batch):
+        a = mod.attn
+        xn = self._ln(x, mod.norm1)
+        xa = self._ag_tp(xn, batch)
+        qkv = torch.cat([self._lin(xa, a.q_linear), self._lin(xa, a.k_linear), self._lin(xa, a.v_linear)], dim=-1)
+        comm = self._attn_comm(batch)
+        o = window_attention(qkv.contiguous(), geo, a.num_heads, mod.shifted, a.bias_table(), mod.use_attn_mask, a.scale,
+                             comm)
+        part = self._lin(o, a.proj)
+        y = self._rs_tp(part, batch)
+        if hasattr(a, "proj_bias"):
+            y = y + a.proj_bias.to(y.dtype)
+        return x + y
+
+    def _mlp_half_tp(self, x, mod):
+        batch = self._batch_of(x)
+        xn = self._ln(x, mod.norm2)
+        xa = self._ag_tp(xn, batch)
+        h = self._lin(xa, mod.linear1)
+        h = TF.gelu(h.float()).to(h.dtype) if h.is_cuda else TF.gelu(h)
+        part = self._lin(h, mod.linear2)
+        y = self._rs_tp(part, batch)
+        return x + y + mod.bias2.to(y.dtype)
+
+    # ------------------------------------------------------------------ stripe <-> window relayout
+    def stripe_to_windows(self, x):
+        """NHWC row stripe ``[B, Ht/wp, Wt, C]`` -> this rank's window-major rows."""
+        Bn, h, W, Cn = x.shape
+        if self.world == 1:
+            full = x
+        else:
+            rows = C.all_gather_rows(x.permute(1, 0, 2, 3).contiguous(), self.manager.window_parallel_group, None)
+            full = rows.permute(1, 0, 2, 3)
+        win = full.reshape(Bn, self.nWh, self.wh, self.nWw, self.ww, Cn).permute(0, 1, 3, 2, 4, 5)
+        win = win.reshape(Bn, self.nWh * self.nWw, self.N, Cn)
+        if self.world == 1:
+            return win.reshape(-1, Cn).contiguous()
+        ids = torch.as_tensor(self._my_window_ids(), device=x.device)
+        mine = win[:, ids][:, :, self.sp_rank * self.shardN:(self.sp_rank + 1) * self.shardN]
+        return mine.reshape(-1, Cn).contiguous()
+
+    def _my_window_ids(self):
+        w = self.windows_of[self.wg_rank]
+        t0 = self.tp_rank * self.wpt
+        return w[t0:t0 + self.tp_sizes_windows[self.tp_rank]]
+
+    def windows_to_stripe(self, rows, batch):
+        """Inverse of ``stripe_to_windows``."""
+        Cn = rows.shape[-1]
+        if self.world == 1:
+            win = rows.reshape(batch, self.nWh, self.nWw, self.wh, self.ww, Cn).permute(0, 1, 3, 2, 4, 5)
+            return win.reshape(batch, self.Ht, self.Wt, Cn).contiguous()
+        m = self.manager
+        sizes, index = self._relayout_table(batch)
+        allrows = C.all_gather_rows(rows.contiguous(), m.window_parallel_group, sizes)
+        full = allrows[index.to(rows.device)]                                            # [B*Ht*Wt, C] image-major
+        full = full.reshape(batch, self.Ht, self.Wt, Cn)
+        h = self.Ht // self.world
+        return full[:, self.wp_rank * h:(self.wp_rank + 1) * h].contiguous()
+
+    def _relayout_table(self, batch):
+        """Row counts of every WP rank's window-major buffer and, for every image-major token, its position in
+        the concatenation of those buffers."""
+        key = ("relayout", batch)
+        cache = self.__dict__.setdefault("_cache", {})
+        if key in cache:
+            return cache[key]
+        m = self.manager
+        nW, N = self.nWh * self.nWw, self.N
+        pos = np.full((batch, nW, N), -1, dtype=np.int64)
+        sizes, cursor = [], 0
+        for wp in range(self.world):
+            g, s, t = m.wp_rank_to_xfmr_coord(wp)
+            wins = self.windows_of[g]
+            wpt = (len(wins) + self.tp - 1) // self.tp
+            mine = wins[t * wpt:min(len(wins), (t + 1) * wpt)]
+            n = batch * len(mine) * self.shardN
+            local = cursor + np.arange(n).reshape(batch, len(mine), self.shardN)
+            pos[:, mine, s * self.shardN:(s + 1) * self.shardN] = local
+            sizes.append(n)
+            cursor += n
+        img = pos.reshape(batch, self.nWh, self.nWw, self.wh, self.ww).transpose(0, 1, 3, 2, 4).reshape(-1)
+        cache[key] = (sizes, torch.from_numpy(img))
+        return cache[key]
+
+
+class _LayerNormFn(torch.autograd.Function):
+    """Standalone LayerNorm on the CUDA kernels (used where the norm is followed by a collective)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        y, mean, rstd = B.layernorm_cuda(x, weight.bf16, bias.bf16)
+        ctx.save_for_backward(x, mean, rstd)
+        ctx.p = (weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, mean, rstd = ctx.saved_tensors
+        weight, bias = ctx.p
+        dx = B.layernorm_bwd_cuda(dy.contiguous(), x, weight.bf16, mean, rstd, weight.grad, bias.grad)
+        return dx, None, None
+
+
+class _PortableAttnComm:
+    """Window attention across window groups / token shards using only portable collectives: every rank of the
+    (window group x SP) set gathers all q/k/v rows, evaluates the windows and keeps the outputs whose home
+    rows it owns. Quadratically wasteful - it exists as the semantic oracle for gloo ranks and as the NCCL
+    baseline; the peer-memory kernel path replaces it on NVLink."""
+
+    fused = False
+
+    def __init__(self, pctx: ParallelContext, batch: int):
+        self.p = pctx
+        self.batch = batch
+        self.world = pctx.n_wg * pctx.sp
+
+    def window_attention_portable(self, qkv, geo, num_heads, shifted, bias_table, use_mask, scale):
+        p, m = self.p, self.p.manager
+        Bn, N, sN = self.batch, p.N, p.shardN
+        C3 = qkv.shape[-1]
+        group, ranks = m.xfmr_tp_param_group, m.xfmr_tp_param_ranks            # (wg, sp) at my TP rank, wg-major
+        sizes = []
+        for g in range(p.n_wg):
+            for s in range(p.sp):
+                sizes.append(Bn * len(p.windows_of[g]) * sN)
+        allrows = C.all_gather_rows(qkv.contiguous(), group, sizes)
+        nW = p.nWh * p.nWw
+        pos = np.full((Bn, nW, N), -1, dtype=np.int64)
+        cursor = 0
+        for g in range(p.n_wg):
+            wins = p.windows_of[g]
+            for s in range(p.sp):
+                n = Bn * len(wins) * sN
+                pos[:, wins, s * sN:(s + 1) * sN] = cursor + np.arange(n).reshape(Bn, len(wins), sN)
+                cursor += n
+        index = torch.from_numpy(pos.reshape(-1)).to(qkv.device)
+        full = allrows[index].reshape(Bn, nW, N, C3)
+        gfull = WindowGeometry(Bn, p.nWh, p.nWw, p.wh, p.ww)
+        out = window_attention_reference(full, gfull, num_heads, shifted, bias_table, use_mask, scale)
+        ids = torch.as_tensor(p.windows_of[p.wg_rank], device=qkv.device)
+        mine = out[:, ids][:, :, p.sp_rank * sN:(p.sp_rank + 1) * sN]
+        return mine.reshape(-1, C3 // 3)

@@ -88,7 +88,7 @@ def test_layernorm(rows, C):
     dx = torch.empty_like(x)
     dg = torch.zeros(C, device="cuda")
     db = torch.zeros(C, device="cuda")
-    ext.layernorm_bwd(dy, x, g, mean, rstd, dx, dg, db)
+    ext.layernorm_bwd(dy, x, g, mean, rstd, dx, dg, db, None)
     _close(dx, xr.grad)
     _close(dg, gr.grad, rtol=3e-2, atol=5e-2)
     _close(db, br.grad, rtol=3e-2, atol=5e-2)
@@ -110,7 +110,7 @@ def test_groupnorm_silu(B, HW, C):
     var = sums[..., 1] / n - mean * mean
     stats = torch.stack([mean, torch.rsqrt(var + 1e-5)], dim=-1).contiguous()
     y = torch.empty_like(x)
-    ext.groupnorm_silu_apply(x, stats, g, b, y, G)
+    ext.groupnorm_silu_apply(x, stats, g, b, None, y, G)
     xr = x.float().requires_grad_(True)
     gr, br = g.float().requires_grad_(True), b.float().requires_grad_(True)
     ref = TF.silu(TF.group_norm(xr.permute(0, 2, 1), G, gr, br, 1e-5)).permute(0, 2, 1)
