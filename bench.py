@@ -1,0 +1,212 @@
+"""Headline benchmark: training samples/s of the high-resolution hierarchical Swin step on N B200 GPUs of one node.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref, same metric and config
+
+One sample (B = 1, 2 x 93 channels, 2048 x 4320 grid; patch 4, embed 384, depths [2,6,6,2], heads [6,12,24,12], window
+8 x 8 with shift, conv down/up block) is split over the N GPUs (row stripes for the conv stage, row-major ragged window
+ownership for the Swin stage), so scaling is strong. Synthetic N(0,1) fields with a seeded ~30 % blob land mask, random
+initial weights, bf16 compute with fp32 master weights, masked L1 loss, AdamW step inside the timed region.
+
+Rank 0 prints ONE JSON line. ``value`` is device-timed (CUDA events, max over ranks) on device-resident inputs
+(each 3.3 GB, far larger than L2); ``e2e`` times the same step through ``terra_b200.api.Trainer.step`` including the
+per-step host->device copy of input and label from pinned memory and the device->host read of the loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "train_samples_per_s"
+
+
+def flagship_config(n_gpus: int, small: bool = False) -> dict:
+    cfg = dict(
+        task_type="glorys", model_architecture="credit_hierarchical_swin", model_type="parallel",
+        height=2048, width=4320, num_channels=186, patch_size=4, embedding_dim=384, depths=[2, 6, 6, 2],
+        num_heads=[6, 12, 24, 12], num_layers=16, window_size=8, padding_policy="auto",
+        window_assignment_mode="terra_m1_ragged_auto", wp_topo=f"({n_gpus}, 1)", xfmr_wp_topo=f"({n_gpus}, 1)",
+        xfmr_sp_size=1, tensor_parallel_size=1, optimizer_config=6 if n_gpus > 1 else 4, precision="bf16",
+        half_model=False, loss_func="L1", learning_rate=1e-4, micro_batch_size=1, use_attn_mask=True,
+        use_relative_position_bias=True, comm_backend=os.environ.get("TERRA_COMM_BACKEND", "nvlink"))
+    if small:
+        cfg.update(height=256, width=512, num_channels=64, embedding_dim=96, depths=[2, 2], num_heads=[3, 6], num_layers=4)
+    return cfg
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of this process's GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()     # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        try:
+            rows = [ln.strip().split(", ") for ln in open(self.path) if ln.strip()]
+            os.unlink(self.path)
+        except Exception:
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from terra_b200 import _ext
+    from terra_b200.api import Trainer
+
+    cfg = flagship_config(args.gpus, args.small)
+    trainer = Trainer(cfg, data_parallel_group_size=1)
+    rank, world, dev = trainer.rank, trainer.world, trainer.device
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    ext = _ext.load()
+    live = dist.is_initialized()
+
+    def barrier():
+        if live:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    host = [trainer.synthetic_batch(sample=i) for i in range(2)]
+    devb = [{k: v.to(dev, non_blocking=True) for k, v in b.items()} for b in host]
+    h2d_bytes = sum(v.numel() * v.element_size() for v in host[0].values())
+
+    # ---- device-timed kernel-only number
+    for i in range(args.warmup):
+        trainer.step_on_device(devb[i % 2])
+    barrier()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    launches0 = ext.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        loss = trainer.step_on_device(devb[i % 2])
+    ev1.record()
+    barrier()
+    launches = ext.launch_count() - launches0
+    ms = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev)
+    if live:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = ms.item()
+    last_loss = float(loss.item())
+
+    # ---- end to end through the public API: staged H2D of every step's batch + D2H of the loss
+    staged = trainer.stage(host[0])
+    for i in range(max(1, args.warmup // 2)):
+        nxt = trainer.stage(host[(i + 1) % 2])
+        trainer.step(host[i % 2], staged)
+        staged = nxt
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        nxt = trainer.stage(host[(i + 1) % 2])       # next step's upload overlaps this step's compute
+        e2e_loss = trainer.step(host[i % 2], staged)
+        staged = nxt
+    barrier()
+    e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device=dev)
+    if live:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop()
+
+    gb = 1
+    par = f"wp{args.gpus}" if args.gpus > 1 else "single"
+    line = {
+        "metric": METRIC, "value": gb / (ms_per_step * 1e-3), "unit": "samples/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "terra_b200",
+        "config": {"model": "credit_hierarchical_swin 2048x4320x186 p4 D384 depths[2,6,6,2] heads[6,12,24,12] ws8"
+                   if not args.small else "credit_hierarchical_swin small (smoke)",
+                   "global_batch": gb, "seq_len": trainer.archi["padded_shape"][0] // 8 * (trainer.archi["padded_shape"][1] // 8),
+                   "parallelism": par, "l2_policy": "inputs (3.3 GB each) larger than L2, two batches alternated",
+                   "optimizer": "AdamW fp32 master, sharded over ranks when N>1"},
+        "clocks": clocks,
+        "e2e": {"value": gb / (e2e_ms.item() * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms.item(),
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches), "loss": last_loss, "e2e_loss": e2e_loss,
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    trainer.close()
+
+
+def run_reference(args):
+    try:
+        from baseline import ref_harness
+    except Exception as exc:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"harness import failed: {exc!r}"[:300]}), flush=True)
+        return
+    ref_harness.main(args, flagship_config(args.gpus, args.small), ClockSampler, METRIC)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--small", action="store_true", help="tiny model (smoke test of the harness, not a benchmark)")
+    args = ap.parse_args()
+    if args.warmup < 3 and not args.small:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,159 @@
+"""Public training API: ``Trainer(config)`` builds topology, model, optimizer and the input pipeline;
+``trainer.step(batch)`` runs one optimisation step on a batch that lives in pinned host memory and returns the
+loss as a Python float.
+
+    trainer = Trainer("configs/model/pretrain/x.yaml", data_parallel_group_size=1)
+    batch = trainer.synthetic_batch(sample=0)           # pinned host tensors of this rank's stripe
+    loss = trainer.step(batch)
+
+The same object backs ``train_scripts/train.py`` and ``bench.py``.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Optional, Union
+
+import torch
+import torch.distributed as dist
+
+from . import _ext
+from .config import get_model_archi_params_and_other_params, load_yaml
+from .data.synthetic import blob_land_mask, block_normal
+from .distributed import init_distributed, set_random_seed
+from .models.get_model import get_model_for_train
+from .models.hierarchical_swin import patchify
+from .parallel.rank_manager import ParallelManager, SingleProcessManager
+from .runtime.run_model import one_step_train_production
+
+
+class Trainer:
+    def __init__(self, model_config: Union[str, dict], data_parallel_group_size: int = 1, backend: Optional[str] = None,
+                 seed: int = 1234):
+        cfg = load_yaml(model_config) if isinstance(model_config, str) else dict(model_config)
+        self.cfg = cfg
+        self.rank, self.world, self.device = init_distributed(backend)
+        set_random_seed(seed)
+        self.task_type = cfg.get("task_type", "glorys")
+        self.model_type = cfg["model_type"]
+        self.archi, self.other = get_model_archi_params_and_other_params(self.task_type, cfg, data_parallel_group_size, self.world)
+        if self.world > 1:
+            self.manager = ParallelManager(
+                dp_size=data_parallel_group_size, mp_size=self.other["mp_size"], wp_topo=self.other["wp_topo"],
+                xfmr_wp_topo=self.other["xfmr_wp_topo"], rank=self.rank, world_size=self.world, device=self.device,
+                window_assignment_mode=self.other["window_assignment_mode"], xfmr_sp_size=self.other["xfmr_sp_size"],
+                tensor_parallel_size=self.other["tensor_parallel_size"], sp_tp_placement=self.other["sp_tp_placement"])
+        else:
+            self.manager = SingleProcessManager(self.device, self.other["window_assignment_mode"])
+        self.model, self.engine, self.optimizer, self.gscaler, self.opt_state = get_model_for_train(
+            self.archi, cfg, self.task_type, self.model_type, self.other["embedding_parallel_type"],
+            self.other["attn_parallel_type"], self.other["mlp_parallel_type"], self.manager, self.device)
+        self.loss_func = cfg.get("loss_func", "L1")
+        self.precision = cfg.get("precision", "bf16")
+        self.batch = int(cfg.get("micro_batch_size", 1))
+        self._build_task_constants()
+        self._copy = _ext.load().CopyEngine(self.device.index or 0) if self.device.type == "cuda" else None
+        self._slots = [None, None]
+        self._slot = 0
+
+    # ------------------------------------------------------------------ shapes
+    @property
+    def local_input_shape(self):
+        """Shape of this rank's model input."""
+        p, C = self.archi["patch_size"], self.archi["num_channels"]
+        ph, pw = self.archi["padded_shape"]
+        if self.model_type == "sequential":
+            return (self.batch, self.archi["height"], self.archi["width"], C)
+        wp = self.manager.wp_size
+        return (self.batch, ph // p // wp, pw // p, p * p * C)
+
+    def _build_task_constants(self):
+        """Land-sea mask (seeded blobs unless ``land_mask: ones``), padded, patchified and row-sliced like the input,
+        and ``padding_loss_scale`` = padded area / real area (dataloader/task_specific_data.py:11-82)."""
+        a = self.archi
+        H, W, C, p = a["height"], a["width"], a["num_channels"], a["patch_size"]
+        ph, pw = a["padded_shape"]
+        left, right, top, bottom = a["initial_padding"]
+        if self.cfg.get("land_mask", "blobs") == "ones":
+            m2 = torch.ones(H, W)
+        else:
+            m2 = blob_land_mask(H, W, float(self.cfg.get("land_fraction", 0.3)), int(self.cfg.get("land_mask_seed", 7)))
+        dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        if self.model_type == "sequential":
+            mask = m2[:, :, None].expand(H, W, C).contiguous()
+            self.task_data = {"land_sea_mask": mask.to(self.device, dt), "padding_loss_scale": 1.0,
+                              "test_iter_num": -1, "show_gradient_flag": False}
+            return
+        mp = torch.nn.functional.pad(m2, (left, right, top, bottom))
+        wp, r = self.manager.wp_size, self.manager.wp_rank
+        rows = ph // wp
+        stripe = mp[r * rows:(r + 1) * rows]                                   # [rows, pw]
+        mask = patchify(stripe[None, :, :, None].expand(1, rows, pw, C), p)[0]   # [rows/p, pw/p, p*p*C]
+        self.task_data = {"land_sea_mask": mask.contiguous().to(self.device, dt),
+                          "padding_loss_scale": float(ph * pw) / float(H * W), "test_iter_num": -1,
+                          "show_gradient_flag": False}
+
+    # ------------------------------------------------------------------ data
+    def synthetic_batch(self, sample: int = 0, seed: int = 2025, pin: bool = True) -> Dict[str, torch.Tensor]:
+        """This rank's slice of a seeded N(0,1) input / next-step label pair, in pinned host memory, already in
+        the layout the model takes (the work the reference's data loader does on the CPU)."""
+        a = self.archi
+        H, W, C, p = a["height"], a["width"], a["num_channels"], a["patch_size"]
+        dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        out = {}
+        for state, key in ((0, "input_tensor"), (1, "label_tensor")):
+            if self.model_type == "sequential":
+                t = torch.stack([block_normal(seed, sample * self.batch + b, state, 0, H, W, C) for b in range(self.batch)])
+            else:
+                ph, pw = a["padded_shape"]
+                left, right, top, bottom = a["initial_padding"]
+                wp, r = self.manager.wp_size, self.manager.wp_rank
+                rows = ph // wp
+                g0, g1 = r * rows - top, (r + 1) * rows - top                  # rows of the unpadded field
+                parts = []
+                for b in range(self.batch):
+                    loc = torch.zeros(rows, pw, C)
+                    lo, hi = max(g0, 0), min(g1, H)
+                    if hi > lo:
+                        loc[lo - g0:hi - g0, left:left + W] = block_normal(seed, sample * self.batch + b, state, lo, hi, W, C)
+                    parts.append(patchify(loc[None], p)[0])
+                t = torch.stack(parts)
+            t = t.to(dt).contiguous()
+            out[key] = t.pin_memory() if (pin and torch.cuda.is_available()) else t
+        return out
+
+    def stage(self, batch: Dict[str, torch.Tensor]):
+        """Start the host->device copy of a batch on the copy engine's upload stream; returns a handle for ``step``."""
+        if self._copy is None:
+            return {k: v for k, v in batch.items()}
+        slot = self._slot
+        self._slot ^= 1
+        if self._slots[slot] is None or any(self._slots[slot][k].shape != v.shape for k, v in batch.items()):
+            self._slots[slot] = {k: torch.empty(v.shape, dtype=v.dtype, device=self.device) for k, v in batch.items()}
+        dev = self._slots[slot]
+        for k, v in batch.items():
+            self._copy.upload(v, dev[k], False)
+        return dev
+
+    def step(self, batch: Dict[str, torch.Tensor], staged=None) -> float:
+        """One optimisation step. ``batch`` holds pinned host tensors (``staged`` = handle of an earlier ``stage``
+        of the same batch, so that its upload overlapped the previous step). Returns the loss (device->host read)."""
+        dev = staged if staged is not None else self.stage(batch)
+        if self._copy is not None:
+            self._copy.wait_uploads()
+        _, loss, _, _ = one_step_train_production(
+            self.task_type, self.model_type, self.model, self.engine, self.optimizer, dev, self.task_data, self.other,
+            self.precision, self.cfg.get("half_model", False), None, self.loss_func, self.gscaler, self.manager,
+            self.opt_state)
+        return float(loss.item())
+
+    def step_on_device(self, dev_batch: Dict[str, torch.Tensor]):
+        """Step on tensors that already live on the device; returns the loss tensor (no host synchronisation)."""
+        _, loss, _, _ = one_step_train_production(
+            self.task_type, self.model_type, self.model, self.engine, self.optimizer, dev_batch, self.task_data,
+            self.other, self.precision, self.cfg.get("half_model", False), None, self.loss_func, self.gscaler,
+            self.manager, self.opt_state)
+        return loss
+
+    def close(self):
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()

@@ -4,6 +4,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include "host_api.h"
+#include "launch_count.h"
 
 namespace {
 
@@ -60,6 +61,7 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
   e.shuffle_cout = static_cast<int>(shuffle_cout);
   e.out_w = static_cast<int>(out_w);
   e.out_h = static_cast<int>(out_h);
+  tb::note_launch();
   const int rc = tb::gemm_bf16(A, B, M, N, K, e, static_cast<int>(split_k), static_cast<int>(bn),
                                sms > 0 ? static_cast<int>(sms) : sm_count(), cur_stream());
   TORCH_CHECK(rc == 0, "terra_b200 gemm launch failed, code ", rc, " (M=", M, " N=", N, " K=", K, ")");
@@ -82,6 +84,7 @@ void conv3x3_fwd(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& 
   e.ldr = y.size(3);
   e.alpha = 1.0f;
   e.status = status.has_value() ? status->data_ptr() : nullptr;
+  tb::note_launch();
   const int rc = tb::conv3x3_fwd_bf16(x.data_ptr(), w.data_ptr(), x.size(0), x.size(1), x.size(2), x.size(3), w.size(0),
                                       static_cast<int>(stride), e, sm_count(), cur_stream());
   TORCH_CHECK(rc == 0, "terra_b200 conv3x3_fwd launch failed, code ", rc);
@@ -94,6 +97,7 @@ void conv3x3_wgrad(const torch::Tensor& x, const torch::Tensor& dy, torch::Tenso
   TORCH_CHECK(dy.scalar_type() == torch::kBFloat16 && dy.is_contiguous() && dy.dim() == 4, "dy: NHWC bf16");
   TORCH_CHECK(dw.scalar_type() == torch::kFloat32 && dw.is_contiguous(), "dw: fp32 [9,Cout,Cin]");
   const c10::cuda::CUDAGuard guard(x.device());
+  tb::note_launch();
   const int rc = tb::conv3x3_wgrad_bf16(x.data_ptr(), dy.data_ptr(), dw.data_ptr<float>(), x.size(0), x.size(1),
                                         x.size(2), x.size(3), dy.size(3), static_cast<int>(stride),
                                         static_cast<int>(split_k), status.has_value() ? status->data_ptr() : nullptr,
@@ -109,6 +113,7 @@ void bind_copy_engine(pybind11::module_& m);
 void bind_comm(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("launch_count", []() { return static_cast<int64_t>(tb::g_kernel_launches.load()); });
   m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogues");
   m.def("conv3x3_fwd", &conv3x3_fwd, "implicit-GEMM 3x3 convolution (NHWC bf16)");
   m.def("conv3x3_wgrad", &conv3x3_wgrad, "3x3 convolution weight gradient (fp32 atomics)");

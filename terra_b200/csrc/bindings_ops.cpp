@@ -4,6 +4,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include "host_api.h"
+#include "launch_count.h"
 
 namespace {
 
@@ -19,6 +20,7 @@ void layernorm_fwd(const torch::Tensor& x, const torch::Tensor& g, const torch::
   need(x.is_cuda() && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "layernorm_fwd: x bf16 contiguous");
   const c10::cuda::CUDAGuard guard(x.device());
   const int C = x.size(-1);
+  tb::note_launch();
   rc_check(tb::layernorm_fwd(x.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
                              rstd.data_ptr<float>(), x.numel() / C, C, static_cast<float>(eps), cur_stream()),
            "layernorm_fwd");
@@ -30,6 +32,7 @@ void layernorm_bwd(const torch::Tensor& dy, const torch::Tensor& x, const torch:
   need(dy.is_contiguous() && x.is_contiguous(), "layernorm_bwd: contiguous inputs");
   const c10::cuda::CUDAGuard guard(x.device());
   const int C = x.size(-1);
+  tb::note_launch();
   rc_check(tb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), g.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
                              dx.data_ptr(), dg.data_ptr<float>(), db.data_ptr<float>(), opt_ptr(dres), x.numel() / C, C,
                              cur_stream()),
@@ -39,6 +42,7 @@ void layernorm_bwd(const torch::Tensor& dy, const torch::Tensor& x, const torch:
 void colsum(const torch::Tensor& x, torch::Tensor& out) {
   need(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == torch::kBFloat16, "colsum: 2-D bf16");
   const c10::cuda::CUDAGuard guard(x.device());
+  tb::note_launch();
   rc_check(tb::colsum_bf16(x.data_ptr(), out.data_ptr<float>(), x.size(0), x.size(1), x.stride(0), cur_stream()),
            "colsum");
 }
@@ -46,6 +50,7 @@ void colsum(const torch::Tensor& x, torch::Tensor& out) {
 void groupnorm_stats(const torch::Tensor& x, torch::Tensor& sums, int64_t groups) {
   need(x.is_contiguous() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16, "groupnorm_stats: [B,HW,C] bf16");
   const c10::cuda::CUDAGuard guard(x.device());
+  tb::note_launch();
   rc_check(tb::groupnorm_stats(x.data_ptr(), sums.data_ptr<float>(), x.size(0), x.size(1), x.size(2), groups, cur_stream()),
            "groupnorm_stats");
 }
@@ -54,6 +59,7 @@ void groupnorm_silu_apply(const torch::Tensor& x, const torch::Tensor& stats, co
                           const torch::Tensor& b, const c10::optional<torch::Tensor>& res, torch::Tensor& y, int64_t groups) {
   need(x.is_contiguous() && x.dim() == 3, "groupnorm_silu_apply: [B,HW,C]");
   const c10::cuda::CUDAGuard guard(x.device());
+  tb::note_launch();
   rc_check(tb::groupnorm_silu_apply(x.data_ptr(), stats.data_ptr<float>(), g.data_ptr(), b.data_ptr(), opt_ptr(res), y.data_ptr(),
                                     x.size(0), x.size(1), x.size(2), groups, cur_stream()),
            "groupnorm_silu_apply");
@@ -63,6 +69,7 @@ void groupnorm_silu_bwd_reduce(const torch::Tensor& dy, const torch::Tensor& x, 
                                const torch::Tensor& g, const torch::Tensor& b, torch::Tensor& red, int64_t groups) {
   need(x.is_contiguous() && dy.is_contiguous() && x.dim() == 3, "groupnorm_silu_bwd_reduce: [B,HW,C]");
   const c10::cuda::CUDAGuard guard(x.device());
+  tb::note_launch();
   rc_check(tb::groupnorm_silu_bwd_reduce(dy.data_ptr(), x.data_ptr(), stats.data_ptr<float>(), g.data_ptr(), b.data_ptr(),
                                          red.data_ptr<float>(), nullptr, nullptr, x.size(0), x.size(1), x.size(2), groups,
                                          cur_stream()),
@@ -74,6 +81,7 @@ void groupnorm_silu_bwd_apply(const torch::Tensor& dy, const torch::Tensor& x, c
                               torch::Tensor& dx, int64_t groups, double inv_count) {
   need(x.is_contiguous() && dy.is_contiguous() && x.dim() == 3, "groupnorm_silu_bwd_apply: [B,HW,C]");
   const c10::cuda::CUDAGuard guard(x.device());
+  tb::note_launch();
   rc_check(tb::groupnorm_silu_bwd_apply(dy.data_ptr(), x.data_ptr(), stats.data_ptr<float>(), red.data_ptr<float>(),
                                         g.data_ptr(), b.data_ptr(), dx.data_ptr(), x.size(0), x.size(1), x.size(2),
                                         groups, static_cast<float>(inv_count), cur_stream()),
@@ -86,6 +94,7 @@ void masked_loss(const torch::Tensor& pred, const torch::Tensor& label, const c1
            label.scalar_type() == torch::kBFloat16,
        "masked_loss: bf16 contiguous pred/label");
   const c10::cuda::CUDAGuard guard(pred.device());
+  tb::note_launch();
   rc_check(tb::masked_loss_fwd_bwd(pred.data_ptr(), label.data_ptr(), opt_ptr(mask), pred.numel(),
                                    mask.has_value() ? mask->numel() : 0, static_cast<int>(kind),
                                    static_cast<float>(grad_scale), loss_sum.data_ptr<float>(), opt_mut(grad), cur_stream()),
@@ -100,6 +109,7 @@ void adamw_step(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const
   const c10::cuda::CUDAGuard guard(master.device());
   const double bc1 = 1.0 - std::pow(b1, static_cast<double>(step));
   const double bc2 = 1.0 - std::pow(b2, static_cast<double>(step));
+  tb::note_launch();
   rc_check(tb::adamw_step(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(),
                           grad.scalar_type() == torch::kBFloat16 ? 1 : 0, opt_mut(param_bf16), master.numel(),
                           static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2), static_cast<float>(eps),
@@ -138,6 +148,7 @@ void window_attn(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t
     a.out[i] = reinterpret_cast<void*>(out_ptrs[i]);
   }
   a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
+  tb::note_launch();
   rc_check(tb::window_attn_fwd(a, cur_stream()), "window_attn_fwd");
 }
 
@@ -158,6 +169,7 @@ void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int
   }
   a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
   a.dbias_table = dbias_table.has_value() ? dbias_table->data_ptr<float>() : nullptr;
+  tb::note_launch();
   rc_check(tb::window_attn_bwd(a, cur_stream()), "window_attn_bwd");
 }
 

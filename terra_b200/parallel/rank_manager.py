@@ -260,3 +260,58 @@ class ParallelManager:
         prev_rank = base + self._domain_rank - 1 if self._domain_rank > 0 else None
         next_rank = base + self._domain_rank + 1 if self._domain_rank < self.domain_parallel_size - 1 else None
         return prev_rank, next_rank
+
+
+class SingleProcessManager:
+    """Stand-in with the ``ParallelManager`` surface for a run without ``torch.distributed`` (one GPU or CPU)."""
+
+    def __init__(self, device=None, window_assignment_mode="regular"):
+        self.topology = Topology()
+        self.rank = self.global_rank = 0
+        self.world_size = 1
+        self.dp_size = self.mp_size = self.wp_size = 1
+        self.xfmr_sp_size = self.xfmr_tp_size = self.xfmr_window_group_size = 1
+        self.sp_tp_placement = "tp_first"
+        self.data_wp_topo = self.xfmr_wp_topo = (1, 1)
+        self.data_wp_group_h = self.data_wp_group_w = self.wp_group_h = self.wp_group_w = 1
+        self.xfmr_wp_group_h = self.xfmr_wp_group_w = 1
+        self.window_assignment_mode = window_assignment_mode
+        self.num_windows_h = self.num_windows_w = -1
+        self.device = device
+        self.dp_rank = self.mp_rank = self.wp_rank = 0
+        self.xfmr_window_group_rank = self.xfmr_sp_rank = self.xfmr_tp_rank = 0
+        for name in ("data_parallel", "model_parallel", "window_parallel", "xfmr_sp", "xfmr_tp", "xfmr_tp_param",
+                     "full_param_replica", "xfmr_tp_param_replica", "xfmr_window"):
+            setattr(self, name + "_group", None)
+            setattr(self, name + "_ranks", [0])
+        self.mp_group_size = self.dp_group_size = self.wp_group_size = self.domain_parallel_size = 1
+
+    def update_window_info(self, h, w):
+        self.num_windows_h, self.num_windows_w = h, w
+
+    def xfmr_coord_to_wp_rank(self, wg, sp, tp):
+        return 0
+
+    def wp_rank_to_xfmr_coord(self, wp_rank):
+        return 0, 0, 0
+
+    def get_rank(self):
+        return 0
+
+    get_dp_rank = get_mp_rank = get_wp_rank = get_rank
+
+    def get_dp_group_size(self):
+        return 1
+
+    get_mp_group_size = get_wp_group_size = get_dp_group_size
+
+    def get_global_rank(self, dp_rank, mp_rank, wp_rank):
+        return 0
+
+    def is_first_domain_rank(self):
+        return True
+
+    is_last_domain_rank = is_first_domain_rank
+
+    def get_neighbor_global_rank(self, *a, **k):
+        return None, None

@@ -20,6 +20,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 ALIGN = 64  # elements: 128 B in bf16, 256 B in fp32 -> every parameter is a legal TMA base
+SEGMENT_ALIGN = ALIGN * 16  # a segment splits evenly over 1, 2, 4, 8 or 16 replica ranks in ALIGN-sized units
 
 
 @dataclass
@@ -84,7 +85,7 @@ class ParamArena:
                 for m in members:
                     offsets[id(m)] = cursor
                     cursor += m.numel()
-            cursor = (cursor + ALIGN - 1) // ALIGN * ALIGN
+            cursor = (cursor + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
             self.segments.append(Segment(label, seg_start, cursor))
         self.numel = cursor
 

@@ -1,0 +1,44 @@
+"""Window attention kernel (forward and backward) against the PyTorch reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(got, ref, rtol=3e-2, atol=3e-2):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err <= atol + rtol * denom, f"max abs err {err} vs ref max {denom}"
+
+
+@pytest.mark.parametrize("B,nWh,nWw,wh,ww,C,heads,shifted,use_bias", [
+    (1, 2, 4, 8, 8, 96, 3, False, True),
+    (1, 2, 4, 8, 8, 96, 3, True, True),
+    (2, 3, 5, 8, 8, 192, 12, True, True),
+    (1, 3, 4, 8, 12, 192, 6, True, True),
+    (1, 4, 4, 8, 8, 384, 6, True, False),
+    (1, 2, 3, 8, 8, 256, 2, True, True),
+    (1, 3, 3, 7, 7, 64, 2, True, True),
+])
+def test_window_attention_fwd_bwd(B, nWh, nWw, wh, ww, C, heads, shifted, use_bias):
+    from terra_b200.ops.attention import WindowGeometry, window_attention, window_attention_reference
+
+    torch.manual_seed(0)
+    geo = WindowGeometry(B, nWh, nWw, wh, ww)
+    N, nW = wh * ww, nWh * nWw
+    qkv = (torch.randn(B * nW * N, 3 * C, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    table = (torch.randn((2 * wh - 1) * (2 * ww - 1), heads, device="cuda") * 0.2).requires_grad_(True) if use_bias else None
+    scale = (C // heads) ** -0.5
+    out = window_attention(qkv, geo, heads, shifted, table, True, scale)
+    dout = (torch.randn_like(out.float()) * 0.5).to(torch.bfloat16)
+    out.backward(dout)
+
+    q32 = qkv.detach().float().requires_grad_(True)
+    t32 = table.detach().clone().requires_grad_(True) if use_bias else None
+    ref = window_attention_reference(q32.reshape(B, nW, N, 3 * C), geo, heads, shifted, t32, True, scale).reshape(-1, C)
+    ref.backward(dout.float())
+    _close(out, ref)
+    _close(qkv.grad, q32.grad)
+    if use_bias:
+        _close(table.grad, t32.grad, rtol=3e-2, atol=5e-2)
