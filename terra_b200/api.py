@@ -18,10 +18,9 @@ import torch.distributed as dist
 
 from . import _ext
 from .config import get_model_archi_params_and_other_params, load_yaml
-from .data.synthetic import blob_land_mask, block_normal
+from .data.synthetic import land_mask_for_rank, synthetic_batch
 from .distributed import init_distributed, set_random_seed
 from .models.get_model import get_model_for_train
-from .models.hierarchical_swin import patchify
 from .parallel.rank_manager import ParallelManager, SingleProcessManager
 from .runtime.run_model import one_step_train_production
 
@@ -70,26 +69,12 @@ class Trainer:
         """Land-sea mask (seeded blobs unless ``land_mask: ones``), padded, patchified and row-sliced like the input,
         and ``padding_loss_scale`` = padded area / real area (dataloader/task_specific_data.py:11-82)."""
         a = self.archi
-        H, W, C, p = a["height"], a["width"], a["num_channels"], a["patch_size"]
-        ph, pw = a["padded_shape"]
-        left, right, top, bottom = a["initial_padding"]
-        if self.cfg.get("land_mask", "blobs") == "ones":
-            m2 = torch.ones(H, W)
-        else:
-            m2 = blob_land_mask(H, W, float(self.cfg.get("land_fraction", 0.3)), int(self.cfg.get("land_mask_seed", 7)))
+        mask, scale = land_mask_for_rank(
+            a["height"], a["width"], a["num_channels"], a["patch_size"], a["padded_shape"], a["initial_padding"],
+            self.model_type, self.manager.wp_size, self.manager.wp_rank, float(self.cfg.get("land_fraction", 0.3)),
+            int(self.cfg.get("land_mask_seed", 7)), self.cfg.get("land_mask", "blobs") == "ones")
         dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
-        if self.model_type == "sequential":
-            mask = m2[:, :, None].expand(H, W, C).contiguous()
-            self.task_data = {"land_sea_mask": mask.to(self.device, dt), "padding_loss_scale": 1.0,
-                              "test_iter_num": -1, "show_gradient_flag": False}
-            return
-        mp = torch.nn.functional.pad(m2, (left, right, top, bottom))
-        wp, r = self.manager.wp_size, self.manager.wp_rank
-        rows = ph // wp
-        stripe = mp[r * rows:(r + 1) * rows]                                   # [rows, pw]
-        mask = patchify(stripe[None, :, :, None].expand(1, rows, pw, C), p)[0]   # [rows/p, pw/p, p*p*C]
-        self.task_data = {"land_sea_mask": mask.contiguous().to(self.device, dt),
-                          "padding_loss_scale": float(ph * pw) / float(H * W), "test_iter_num": -1,
+        self.task_data = {"land_sea_mask": mask.to(self.device, dt), "padding_loss_scale": scale, "test_iter_num": -1,
                           "show_gradient_flag": False}
 
     # ------------------------------------------------------------------ data
@@ -97,29 +82,10 @@ class Trainer:
         """This rank's slice of a seeded N(0,1) input / next-step label pair, in pinned host memory, already in
         the layout the model takes (the work the reference's data loader does on the CPU)."""
         a = self.archi
-        H, W, C, p = a["height"], a["width"], a["num_channels"], a["patch_size"]
         dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
-        out = {}
-        for state, key in ((0, "input_tensor"), (1, "label_tensor")):
-            if self.model_type == "sequential":
-                t = torch.stack([block_normal(seed, sample * self.batch + b, state, 0, H, W, C) for b in range(self.batch)])
-            else:
-                ph, pw = a["padded_shape"]
-                left, right, top, bottom = a["initial_padding"]
-                wp, r = self.manager.wp_size, self.manager.wp_rank
-                rows = ph // wp
-                g0, g1 = r * rows - top, (r + 1) * rows - top                  # rows of the unpadded field
-                parts = []
-                for b in range(self.batch):
-                    loc = torch.zeros(rows, pw, C)
-                    lo, hi = max(g0, 0), min(g1, H)
-                    if hi > lo:
-                        loc[lo - g0:hi - g0, left:left + W] = block_normal(seed, sample * self.batch + b, state, lo, hi, W, C)
-                    parts.append(patchify(loc[None], p)[0])
-                t = torch.stack(parts)
-            t = t.to(dt).contiguous()
-            out[key] = t.pin_memory() if (pin and torch.cuda.is_available()) else t
-        return out
+        return synthetic_batch(a["height"], a["width"], a["num_channels"], a["patch_size"], a["padded_shape"],
+                               a["initial_padding"], self.model_type, self.manager.wp_size, self.manager.wp_rank,
+                               self.batch, sample, seed, dt, pin)
 
     def stage(self, batch: Dict[str, torch.Tensor]):
         """Start the host->device copy of a batch on the copy engine's upload stream; returns a handle for ``step``."""

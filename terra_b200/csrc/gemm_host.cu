@@ -35,6 +35,14 @@ int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uns
                          const unsigned long long* strides_bytes, const unsigned int* box) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
+  // cuTensorMapEncodeTiled is a driver call: it needs the primary context bound to THIS thread. A thread that
+  // has only queried the device so far (e.g. an autograd worker before its first runtime call) has none, so
+  // bind it once per thread through the runtime.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   cuuint64_t gdim[5];
   cuuint64_t gstr[4];
   cuuint32_t bdim[5];

@@ -106,7 +106,9 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
   __nv_bfloat16* dQs = dSs + (BWD ? NPAD * pstride : 0);                // BWD only [NPAD][HD+8]
   float* bias_s = reinterpret_cast<float*>(dQs + (BWD ? NPAD * (HD + 8) : 0));   // [hpc][nrel]
   float* dbias_s = bias_s + hpc * geo.nrel;                                         // BWD only [hpc][nrel]
-  long long* rowofs = reinterpret_cast<long long*>(dbias_s + (BWD ? hpc * geo.nrel : 0));  // [NPAD]
+  // the float tables have an arbitrary length: round up so that the 8-byte row offsets are aligned
+  long long* rowofs = reinterpret_cast<long long*>(
+      (reinterpret_cast<uintptr_t>(dbias_s + (BWD ? hpc * geo.nrel : 0)) + 15) & ~uintptr_t(15));  // [NPAD]
   int* rowslot = reinterpret_cast<int*>(rowofs + NPAD);                                      // [NPAD]
   int* rowreg = rowslot + NPAD;                                                              // [NPAD]
 
@@ -458,6 +460,7 @@ size_t smem_bytes(int hpc, int nrel) {
   size_t b = static_cast<size_t>(NPAD) * stride * 2 * (BWD ? 4 : 3);
   if (BWD) b += static_cast<size_t>(NPAD) * pstride * 2 * 2 + static_cast<size_t>(NPAD) * (HD + 8) * 2;
   b += static_cast<size_t>(hpc) * nrel * 4 * (BWD ? 2 : 1);
+  b += 16;   // alignment slack before the row tables
   b += NPAD * (8 + 4 + 4);
   return b;
 }

@@ -52,3 +52,50 @@ def blob_land_mask(height, width, frac=0.3, seed=7, num_blobs=48):
         land |= (dy / ry) ** 2 + (dx / rx) ** 2 <= 1.0
         tries += 1
     return torch.from_numpy((~land).astype(np.float32))
+
+
+def patchify_hwc(x, p):
+    """[B, H, W, C] -> [B, H/p, W/p, p*p*C] with (p1, p2, c) feature order."""
+    Bn, H, W, C = x.shape
+    return x.reshape(Bn, H // p, p, W // p, p, C).permute(0, 1, 3, 2, 4, 5).reshape(Bn, H // p, W // p, p * p * C)
+
+
+def synthetic_batch(height, width, channels, patch_size, padded_shape, initial_padding, model_type, wp_size=1, wp_rank=0,
+                    batch=1, sample=0, seed=2025, dtype=torch.float32, pin=False):
+    """Seeded N(0,1) input / next-step label pair in the layout the model takes: the raw NHWC field for the
+    sequential build, this rank's row stripe of the padded, patchified field for the parallel build."""
+    out = {}
+    for state, key in ((0, "input_tensor"), (1, "label_tensor")):
+        if model_type == "sequential":
+            t = torch.stack([block_normal(seed, sample * batch + b, state, 0, height, width, channels) for b in range(batch)])
+        else:
+            ph, pw = padded_shape
+            left, right, top, bottom = initial_padding
+            rows = ph // wp_size
+            g0, g1 = wp_rank * rows - top, (wp_rank + 1) * rows - top          # rows of the unpadded field
+            parts = []
+            for b in range(batch):
+                loc = torch.zeros(rows, pw, channels)
+                lo, hi = max(g0, 0), min(g1, height)
+                if hi > lo:
+                    loc[lo - g0:hi - g0, left:left + width] = block_normal(seed, sample * batch + b, state, lo, hi, width, channels)
+                parts.append(patchify_hwc(loc[None], patch_size)[0])
+            t = torch.stack(parts)
+        t = t.to(dtype).contiguous()
+        out[key] = t.pin_memory() if (pin and torch.cuda.is_available()) else t
+    return out
+
+
+def land_mask_for_rank(height, width, channels, patch_size, padded_shape, initial_padding, model_type, wp_size=1,
+                       wp_rank=0, frac=0.3, seed=7, ones=False):
+    """Mask in the model's output layout (no batch dimension) and ``padding_loss_scale`` = padded / real area."""
+    m2 = torch.ones(height, width) if ones else blob_land_mask(height, width, frac, seed)
+    if model_type == "sequential":
+        return m2[:, :, None].expand(height, width, channels).contiguous(), 1.0
+    ph, pw = padded_shape
+    left, right, top, bottom = initial_padding
+    mp = torch.nn.functional.pad(m2, (left, right, top, bottom))
+    rows = ph // wp_size
+    stripe = mp[wp_rank * rows:(wp_rank + 1) * rows]
+    mask = patchify_hwc(stripe[None, :, :, None].expand(1, rows, pw, channels), patch_size)[0].contiguous()
+    return mask, float(ph * pw) / float(height * width)

@@ -10,6 +10,8 @@ without materialising a transpose:
 """
 from __future__ import annotations
 
+import os
+import sys
 from typing import Optional
 
 import torch
@@ -18,6 +20,7 @@ from .. import _ext
 from . import _flags as F
 
 _status = {}
+_TRACE = os.environ.get("TERRA_TRACE", "0") == "1"
 
 
 def status_word(device) -> torch.Tensor:
@@ -86,6 +89,12 @@ def gemm(
     if save_pre:
         flags |= F.EPI_SAVE_PRE
         pre = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    if _TRACE:
+        print(f"[terra trace] gemm a={tuple(a.shape)}/{a.dtype}/{a.stride()} a_mn={a_mn} b={tuple(b.shape)}/{b.dtype}/{b.stride()} "
+              f"b_mn={b_mn} out={tuple(out.shape)}/{out.dtype}/{out.stride()}/{out.device} flags={flags} split_k={split_k} bn={bn} "
+              f"bias={None if bias is None else (tuple(bias.shape), bias.dtype)} "
+              f"res={None if residual is None else (tuple(residual.shape), residual.dtype, residual.stride())}",
+              file=sys.stderr, flush=True)
     ext.gemm(a, a_mn, b, b_mn, out, flags, bias, residual, dgelu_aux, pre, float(alpha), int(split_k), int(bn),
              status_word(a.device), 0, 0, 0, int(sms))
     if save_pre:
