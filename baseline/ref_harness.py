@@ -103,7 +103,7 @@ def _run(args, cfg, ClockSampler, metric):
             "show_gradient_flag": False}
     other = {"embedding_parallel_type": "window_linear" if n > 1 else None}
     host = [synthetic_batch(H, W, C, p, spec["padded_shape"], spec["initial_padding"], model_type, n, rank, 1, i, 2025,
-                            torch.bfloat16, pin=True) for i in range(2)]
+                            torch.bfloat16, pin=True, gen_device="cuda") for i in range(2)]
     devb = [{k: v.to(dev, non_blocking=True) for k, v in b.items()} for b in host]
     h2d_bytes = sum(v.numel() * v.element_size() for v in host[0].values())
     state = (True, False, None, False)   # USE_DDP, USE_FSDP, ZERO_STAGE_NUMBER, USE_DIST_OPT

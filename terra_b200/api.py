@@ -85,7 +85,7 @@ class Trainer:
         dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         return synthetic_batch(a["height"], a["width"], a["num_channels"], a["patch_size"], a["padded_shape"],
                                a["initial_padding"], self.model_type, self.manager.wp_size, self.manager.wp_rank,
-                               self.batch, sample, seed, dt, pin)
+                               self.batch, sample, seed, dt, pin, "cuda" if self.device.type == "cuda" else "cpu")
 
     def stage(self, batch: Dict[str, torch.Tensor]):
         """Start the host->device copy of a batch on the copy engine's upload stream; returns a handle for ``step``."""

@@ -25,15 +25,19 @@ def _hash_seed(seed: int, sample: int, state: int, block: int) -> int:
     return h & ((1 << 63) - 1)
 
 
-def block_normal(seed, sample, state, row0, row1, width, channels, dtype=torch.float32):
-    """Rows ``[row0, row1)`` of the N(0,1) field ``[H, W, C]`` of (seed, sample, state)."""
+def block_normal(seed, sample, state, row0, row1, width, channels, dtype=torch.float32, device="cpu"):
+    """Rows ``[row0, row1)`` of the N(0,1) field ``[H, W, C]`` of (seed, sample, state).
+
+    ``device="cuda"`` draws the blocks with the GPU generator (much faster for benchmark-sized fields; the values
+    differ from the CPU generator's but have the same block-addressable property) and returns a host tensor."""
     out = torch.empty(row1 - row0, width, channels, dtype=dtype)
     b0, b1 = row0 // BLOCK_ROWS, (row1 - 1) // BLOCK_ROWS
+    dev = torch.device(device)
     for b in range(b0, b1 + 1):
-        g = torch.Generator().manual_seed(_hash_seed(seed, sample, state, b))
-        blk = torch.randn(BLOCK_ROWS, width, channels, generator=g, dtype=torch.float32)
+        g = torch.Generator(device=dev).manual_seed(_hash_seed(seed, sample, state, b))
+        blk = torch.randn(BLOCK_ROWS, width, channels, generator=g, dtype=torch.float32, device=dev)
         lo, hi = max(row0, b * BLOCK_ROWS), min(row1, (b + 1) * BLOCK_ROWS)
-        out[lo - row0:hi - row0] = blk[lo - b * BLOCK_ROWS:hi - b * BLOCK_ROWS].to(dtype)
+        out[lo - row0:hi - row0] = blk[lo - b * BLOCK_ROWS:hi - b * BLOCK_ROWS].to(dtype).cpu()
     return out
 
 
@@ -61,13 +65,14 @@ def patchify_hwc(x, p):
 
 
 def synthetic_batch(height, width, channels, patch_size, padded_shape, initial_padding, model_type, wp_size=1, wp_rank=0,
-                    batch=1, sample=0, seed=2025, dtype=torch.float32, pin=False):
+                    batch=1, sample=0, seed=2025, dtype=torch.float32, pin=False, gen_device="cpu"):
     """Seeded N(0,1) input / next-step label pair in the layout the model takes: the raw NHWC field for the
     sequential build, this rank's row stripe of the padded, patchified field for the parallel build."""
     out = {}
     for state, key in ((0, "input_tensor"), (1, "label_tensor")):
         if model_type == "sequential":
-            t = torch.stack([block_normal(seed, sample * batch + b, state, 0, height, width, channels) for b in range(batch)])
+            t = torch.stack([block_normal(seed, sample * batch + b, state, 0, height, width, channels, dtype, gen_device)
+                             for b in range(batch)])
         else:
             ph, pw = padded_shape
             left, right, top, bottom = initial_padding
@@ -75,10 +80,11 @@ def synthetic_batch(height, width, channels, patch_size, padded_shape, initial_p
             g0, g1 = wp_rank * rows - top, (wp_rank + 1) * rows - top          # rows of the unpadded field
             parts = []
             for b in range(batch):
-                loc = torch.zeros(rows, pw, channels)
+                loc = torch.zeros(rows, pw, channels, dtype=dtype)
                 lo, hi = max(g0, 0), min(g1, height)
                 if hi > lo:
-                    loc[lo - g0:hi - g0, left:left + width] = block_normal(seed, sample * batch + b, state, lo, hi, width, channels)
+                    loc[lo - g0:hi - g0, left:left + width] = block_normal(seed, sample * batch + b, state, lo, hi, width, channels,
+                                                                         dtype, gen_device)
                 parts.append(patchify_hwc(loc[None], patch_size)[0])
             t = torch.stack(parts)
         t = t.to(dtype).contiguous()
