@@ -1,0 +1,122 @@
+"""Checkpoint files (reference layout: train_scripts/train.py:56-280, finetune.py:60-318).
+
+``{train_path}/{description}/ckpt/<kind dir>/epoch{E}.pth`` (pretrain) and
+``{train_path}/{description}/lead_{L}/ckpt/<kind dir>/{epoch{E}|step{N}}.pth`` (finetune), each holding
+``model_state_dict, optimizer_state_dict, loss, epoch, global_step, ckpt_layout`` (+ ``scaler``).
+
+Who writes what (``ckpt_layout``):
+  ``single``      sequential build: rank 0 writes ``ckpt/``
+  ``wp_rank``     parallel build with a replicated optimizer: the ranks of DP replica 0 write ``ckpt/wp_rank_{w}/``
+  ``rank_local``  sharded optimizer: every rank writes ``ckpt/rank_{r}/`` (optimizer state exists only on its owner)
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+def checkpoint_kind(model_type: str, optimizer_state_tuple) -> str:
+    use_ddp, use_fsdp, zero_stage, use_dist_opt = optimizer_state_tuple
+    if use_dist_opt:
+        return "rank_local"
+    if model_type in ("parallel", "hybrid"):
+        return "wp_rank"
+    return "single"
+
+
+def checkpoint_dir(train_path, description, kind, manager, lead: Optional[int] = None) -> str:
+    base = os.path.join(train_path, description)
+    if lead is not None:
+        base = os.path.join(base, f"lead_{lead}")
+    base = os.path.join(base, "ckpt")
+    if kind == "rank_local":
+        return os.path.join(base, f"rank_{manager.get_rank()}")
+    if kind == "wp_rank":
+        return os.path.join(base, f"wp_rank_{manager.get_wp_rank()}")
+    return base
+
+
+def should_write(kind, manager) -> bool:
+    if kind == "rank_local":
+        return True
+    if kind == "wp_rank":
+        return manager.get_dp_rank() == 0
+    return manager.get_rank() == 0
+
+
+def strip_module_prefix(state_dict):
+    return {(k[len("module."):] if k.startswith("module.") else k): v for k, v in state_dict.items()}
+
+
+def save_checkpoint(model, optimizer, loss, epoch, train_path, description, model_type, optimizer_state_tuple, manager,
+                    scaler=None, lead=None, step=None) -> Optional[str]:
+    kind = checkpoint_kind(model_type, optimizer_state_tuple)
+    path = None
+    if hasattr(optimizer, "sync_masters"):
+        optimizer.sync_masters()
+    if should_write(kind, manager):
+        d = checkpoint_dir(train_path, description, kind, manager, lead)
+        os.makedirs(d, exist_ok=True)
+        name = f"step{step}.pth" if step is not None else f"epoch{epoch}.pth"
+        path = os.path.join(d, name)
+        real = model.module if hasattr(model, "module") else model
+        blob = {"model_state_dict": {k: v.detach().cpu() for k, v in real.state_dict().items()},
+                "optimizer_state_dict": optimizer.state_dict(), "loss": float(loss) if loss is not None else None,
+                "epoch": epoch, "global_step": int(getattr(optimizer, "global_step", 0)), "ckpt_layout": kind}
+        if scaler is not None:
+            blob["scaler"] = scaler.state_dict()
+        torch.save(blob, path + ".tmp")
+        os.replace(path + ".tmp", path)
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+    return path
+
+
+def load_checkpoint(model, optimizer, train_path, description, model_type, optimizer_state_tuple, manager, epoch=None,
+                    step=None, scaler=None, lead=None, strict=True):
+    """Returns ``(epoch, global_step, loss)`` of the loaded file."""
+    kind = checkpoint_kind(model_type, optimizer_state_tuple)
+    d = checkpoint_dir(train_path, description, kind, manager, lead)
+    if kind == "wp_rank" and not os.path.isdir(d):
+        d = checkpoint_dir(train_path, description, "single", manager, lead)
+    name = f"step{step}.pth" if step is not None else f"epoch{epoch}.pth"
+    blob = torch.load(os.path.join(d, name), map_location="cpu", weights_only=False)
+    real = model.module if hasattr(model, "module") else model
+    real.load_state_dict(strip_module_prefix(blob["model_state_dict"]), strict=strict)
+    arena = getattr(real, "_param_arena", None)
+    if arena is not None:
+        arena.sync_bf16()
+    if optimizer is not None and blob.get("optimizer_state_dict") is not None:
+        optimizer.load_state_dict(blob["optimizer_state_dict"])
+        optimizer.global_step = int(blob.get("global_step", 0))
+    if scaler is not None and "scaler" in blob:
+        scaler.load_state_dict(blob["scaler"])
+    return int(blob.get("epoch", 0)), int(blob.get("global_step", 0)), blob.get("loss")
+
+
+def load_pretrained_weights(model, path, skip_suffixes=("attn_mask",), log=print):
+    """Finetune import: keep the entries whose key exists with the same shape, drop the listed suffixes, load
+    non-strictly (train_scripts/finetune.py:86-216)."""
+    blob = torch.load(path, map_location="cpu", weights_only=False)
+    sd = strip_module_prefix(blob.get("model_state_dict", blob) if isinstance(blob, dict) else blob)
+    real = model.module if hasattr(model, "module") else model
+    own = real.state_dict()
+    keep, dropped = {}, []
+    for k, v in sd.items():
+        if any(k.endswith(s) for s in skip_suffixes):
+            continue
+        if k in own and tuple(own[k].shape) == tuple(v.shape):
+            keep[k] = v
+        else:
+            dropped.append(k)
+    missing = [k for k in own if k not in keep]
+    real.load_state_dict(keep, strict=False)
+    arena = getattr(real, "_param_arena", None)
+    if arena is not None:
+        arena.sync_bf16()
+    if log is not None:
+        log(f"[pretrained] loaded {len(keep)} tensors, skipped {len(dropped)} (key/shape mismatch), {len(missing)} left at init")
+    return keep.keys(), dropped, missing

@@ -1,0 +1,123 @@
+"""Multi-rank layouts on gloo CPU ranks against the single-rank model (same seeded weights, same data):
+loss, output and the reduced gradients must agree."""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent('''
+    import os, sys, json
+    sys.path.insert(0, %(root)r)
+    import torch, torch.distributed as dist
+    from terra_b200.api import Trainer
+    from terra_b200.data.synthetic import synthetic_batch, land_mask_for_rank, patchify_hwc
+    from terra_b200.models import SequentialHierarchicalSwin
+    from terra_b200.ops.loss import masked_loss
+
+    cfg = dict(%(cfg)s)
+    t = Trainer(cfg, data_parallel_group_size=1, backend="gloo")
+    a = t.archi
+    batch = t.synthetic_batch(0)
+    # one forward/backward through the runtime pieces (no optimizer step, to compare raw gradients)
+    from terra_b200.runtime.run_one_step import loss_scale_factor, grad_post_process, backbone_run, cal_loss
+    t.optimizer.zero_grad()
+    outs = backbone_run("glorys", t.model, batch, t.task_data)
+    post = loss_scale_factor("parallel", "window_linear", t.manager, t.task_data, False)
+    loss = cal_loss("glorys", outs, batch, t.task_data, torch.nn.MSELoss()) * post
+    loss.backward()
+    grad_post_process("parallel", (True, False, -1, False), t.model, t.manager, dp_average=True)
+    rep = loss.detach().clone(); dist.all_reduce(rep)
+
+    # single-rank oracle on the whole padded field, same seeded init
+    H, W, C, p = a["height"], a["width"], a["num_channels"], a["patch_size"]
+    ser = SequentialHierarchicalSwin(padding_scale=1, num_channels=C, patch_size=p, window_size=a["window_size"], height=H,
+                                     width=W, embedding_dim=a["embedding_dim"], num_heads=a["num_heads"],
+                                     num_layers=a["num_layers"], depths=a.get("depths"),
+                                     padding_spec={"padded_shape": a["padded_shape"]})
+    full = synthetic_batch(H, W, C, p, a["padded_shape"], a["initial_padding"], "sequential", 1, 0, 1, 0)
+    mask, _ = land_mask_for_rank(H, W, C, p, a["padded_shape"], a["initial_padding"], "sequential")
+    y = ser(full["input_tensor"]) * mask
+    ref_loss = torch.nn.functional.mse_loss(y, full["label_tensor"])
+    ref_loss.backward()
+
+    # compare: loss, my stripe of the output, gradients of replicated parameters
+    wp, r = t.manager.wp_size, t.manager.wp_rank
+    rows = a["padded_shape"][0] // wp
+    left, right, top, bottom = a["initial_padding"]
+    ypad = torch.nn.functional.pad(y.detach(), (0, 0, left, right, top, bottom))
+    mine_ref = patchify_hwc(ypad[:, r * rows:(r + 1) * rows], p)
+    out_err = (outs[0].detach() - mine_ref).abs().max().item()
+    sp = dict(ser.named_parameters())
+    worst = 0.0
+    names = {"patch_embed.weight": "patch_embed.linear.weight", "patch_recovery.weight": "patch_recovery.linear.weight",
+             "patch_embed.bias": "patch_embed.linear.bias", "patch_recovery.bias": "patch_recovery.linear.bias"}
+    checked = 0
+    for n, q in t.model.named_parameters():
+        if getattr(q, "terra_grad_reduce_group", None):
+            continue      # TP shards are compared separately
+        sn = names.get(n, n.replace(".conv.conv.", ".conv.").replace(".conv.weight", ".weight").replace(".conv.bias", ".bias") if ".b." in n else names.get(n, n.replace("down_blk.conv.conv", "down_blk.conv").replace("up_blk.conv.conv", "up_blk.conv")))
+        if sn not in sp:
+            continue
+        g_ref = sp[sn].grad
+        if g_ref is None or g_ref.abs().max() < 1e-9:
+            continue
+        worst = max(worst, ((q.grad - g_ref).abs().max() / (g_ref.abs().max() + 1e-12)).item())
+        checked += 1
+    print("RESULT " + json.dumps(dict(rank=dist.get_rank(), loss=rep.item(), ref_loss=ref_loss.item(), out_err=out_err,
+                                      worst_grad_rel=worst, checked=checked)), flush=True)
+    dist.destroy_process_group()
+''')
+
+BASE = ("task_type='glorys', model_architecture='credit_hierarchical_swin', model_type='parallel', height=128, width=256, "
+        "num_channels=16, patch_size=4, embedding_dim=64, num_layers=2, num_heads=4, window_size=8, padding_policy='auto', "
+        "optimizer_config=4, precision='fp32', loss_func='MSE', learning_rate=1e-4, land_mask='blobs', ")
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _run(world, extra):
+    code = WORKER % dict(root=ROOT, cfg=BASE + extra)
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+        procs.append(subprocess.Popen([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                                      text=True))
+    results = []
+    for p in procs:
+        try:
+            out, err = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        assert p.returncode == 0, err[-3000:]
+        line = [ln for ln in out.splitlines() if ln.startswith("RESULT ")][-1]
+        results.append(__import__("json").loads(line[len("RESULT "):]))
+    return results
+
+
+@pytest.mark.parametrize("world,extra", [
+    (2, "wp_topo='(2, 1)', xfmr_wp_topo='(2, 1)', window_assignment_mode='terra_m1_ragged_auto'"),
+    (2, "wp_topo='(2, 1)', xfmr_wp_topo='(2, 1)', window_assignment_mode='regular'"),
+    (2, "wp_topo='(2, 1)', xfmr_wp_topo='(1, 1)', xfmr_sp_size=2, window_assignment_mode='terra_m1_ragged_auto'"),
+    (2, "wp_topo='(2, 1)', xfmr_wp_topo='(1, 1)', tensor_parallel_size=2, window_assignment_mode='terra_m1_ragged_auto'"),
+    (4, "wp_topo='(4, 1)', xfmr_wp_topo='(1, 1)', xfmr_sp_size=2, tensor_parallel_size=2, window_assignment_mode='terra_m1_ragged_auto'"),
+])
+def test_parallel_layout_matches_serial(world, extra):
+    for res in _run(world, extra):
+        assert abs(res["loss"] - res["ref_loss"]) < 1e-4 * max(1.0, abs(res["ref_loss"])), res
+        assert res["out_err"] < 2e-3, res
+        assert res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res

@@ -1,0 +1,115 @@
+"""Benchmark / correctness harness for pretraining (reference: train_scripts/test_pretrain.py:61-699).
+
+Runs ``--steps`` optimisation steps and records, per step, the loss, the output sum, the peak memory and the step time
+(``--metrics_csv``), plus run metadata, parameter counts and FLOPs (``--metrics_json``). ``MEM_PROF`` = 1 / 2 turns
+the memory timeline on (2 adds the per-primitive summary).
+"""
+from __future__ import annotations
+
+import csv
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from train_scripts.common import PRETRAIN_DEFAULTS, Session, base_parser  # noqa: E402
+from terra_b200 import global_env_config as G  # noqa: E402
+from terra_b200.logging_utils import set_dp_rank_print_redirect  # noqa: E402
+from terra_b200.memory.boundary_offload import get_boundary_offload_stats, reset_boundary_offload_stats  # noqa: E402
+from terra_b200.profiler.flops_profiler import TorchFlopsProfiler, analytic_step_flops  # noqa: E402
+from terra_b200.profiler.memory_timeline import CudaMemoryTimeline  # noqa: E402
+from terra_b200.runtime.run_model import one_step_train  # noqa: E402
+from terra_b200.utils.misc import count_parameters  # noqa: E402
+
+
+def main(argv=None):
+    ap = base_parser("terra_b200 pretraining test harness")
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--metrics_csv", default=None)
+    ap.add_argument("--metrics_json", default=None)
+    ap.add_argument("--metrics_no_json", action="store_true")
+    ap.add_argument("--disable_torch_prof", action="store_true")
+    ap.add_argument("--quiet_metrics", action="store_true")
+    ap.add_argument("--disable_rank_log_redirect", action="store_true")
+    ap.add_argument("--mem_prof", type=int, default=None)
+    args = ap.parse_args(argv)
+    if args.steps is not None and args.steps <= 0:
+        raise ValueError(f"--steps must be positive, got {args.steps}")
+    steps = args.steps or 4
+
+    s = Session(args.model_cfg, args.data_parallel_group_size, dict(PRETRAIN_DEFAULTS, use_fake_input=True))
+    c = s.cfg
+    set_dp_rank_print_redirect(s.manager, s.model_type, s.opt_state, s.other.get("embedding_parallel_type"),
+                               quiet=args.quiet_metrics, disable=args.disable_rank_log_redirect or s.world == 1)
+    reset_boundary_offload_stats()
+    mem_prof = args.mem_prof if args.mem_prof is not None else int(os.environ.get("MEM_PROF", G.MEM_PROF))
+    timeline = CudaMemoryTimeline(s.device if s.device.type == "cuda" else None, enabled=mem_prof > 0)
+    use_prof = G.ENABLE_TORCH_PROF and not args.disable_torch_prof and not G.DISABLE_TORCH_PROF
+    prof = TorchFlopsProfiler(G.TORCH_PROF_STEP_LIST, enabled=use_prof, rank=s.rank,
+                              trace_dir="./log/torch_prof" if G.TORCH_PROF_WRITE_TRACE else None)
+    loader = s.pretrain_loader(status=0)
+    rows = []
+    it = iter(loader)
+    with prof:
+        for i in range(steps):
+            try:
+                batch = next(it)
+            except StopIteration:
+                it = iter(loader)
+                batch = next(it)
+            tensors = s.to_required_tensors(batch)
+            if s.device.type == "cuda":
+                torch.cuda.reset_peak_memory_stats(s.device)
+            with timeline.iteration(i):
+                out, loss, step_time, fwd_time = one_step_train(
+                    s.task_type, s.model_type, s.model, s.engine, s.optimizer, tensors, s.task_data, s.other, s.precision,
+                    c["half_model"], s.my_dtype, s.loss_fn, s.gscaler, s.manager, s.opt_state, memory_timeline=timeline,
+                    clip_grad=c["clip_grad"])
+            prof.step()
+            out_sum = out.detach().float().sum()
+            if dist.is_available() and dist.is_initialized() and s.model_type != "sequential":
+                dist.all_reduce(out_sum, group=s.manager.window_parallel_group)
+            peak = torch.cuda.max_memory_allocated(s.device) / 2 ** 20 if s.device.type == "cuda" else 0.0
+            rows.append(dict(iter=i, loss=float(loss.item()), output_sum=float(out_sum.item()), dtype=str(out.dtype),
+                             peak_memory_mb=peak, step_time_s=step_time, forward_time_s=fwd_time,
+                             padded_h=s.archi["padded_shape"][0], padded_w=s.archi["padded_shape"][1],
+                             padding_policy=s.archi.get("padding_policy", "")))
+            if s.is_log_rank() and not args.quiet_metrics:
+                print(f"iter {i} loss {rows[-1]['loss']:.8f} output_sum {rows[-1]['output_sum']:.6f} "
+                      f"peak_memory_mb {peak:.1f} step_time_s {step_time:.4f}", flush=True)
+    if s.is_log_rank():
+        if args.metrics_csv:
+            os.makedirs(os.path.dirname(os.path.abspath(args.metrics_csv)), exist_ok=True)
+            with open(args.metrics_csv, "w", newline="") as f:
+                w = csv.DictWriter(f, fieldnames=list(rows[0].keys()))
+                w.writeheader()
+                w.writerows(rows)
+        if args.metrics_json and not args.metrics_no_json:
+            total, trainable = count_parameters(s.model)
+            flops = analytic_step_flops(s.archi, c["micro_batch_size"])
+            times = [r["step_time_s"] for r in rows[1:]] or [rows[0]["step_time_s"]]
+            meta = dict(description=c.get("description"), model_type=s.model_type, world_size=s.world, dp=s.dp,
+                        wp_topo=list(s.other["wp_topo"]), xfmr_wp_topo=list(s.other["xfmr_wp_topo"]),
+                        xfmr_sp_size=s.other["xfmr_sp_size"], tensor_parallel_size=s.other["tensor_parallel_size"],
+                        optimizer_config=c["optimizer_config"], precision=s.precision, parameters=total,
+                        trainable_parameters=trainable, analytic_flops_per_step=flops,
+                        avg_step_time_s=sum(times) / len(times), tflops=flops / (sum(times) / len(times)) / 1e12,
+                        profiler=prof.summarize(), offload=get_boundary_offload_stats(), final_loss=rows[-1]["loss"])
+            os.makedirs(os.path.dirname(os.path.abspath(args.metrics_json)), exist_ok=True)
+            with open(args.metrics_json, "w") as f:
+                json.dump(meta, f, indent=1)
+        if mem_prof > 0 and timeline.events:
+            d = os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline")
+            timeline.write_csv(os.path.join(d, "timeline_rank0.csv"))
+            if mem_prof > 1:
+                timeline.write_summary_csv(os.path.join(d, "primitive_summary_rank0.csv"))
+    s.close()
+    return rows
+
+
+if __name__ == "__main__":
+    main()

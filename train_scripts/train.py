@@ -1,0 +1,67 @@
+"""Production pretraining loop (CLI and files as in the reference's train_scripts/train.py:40-592).
+
+    torchrun --nproc-per-node N train_scripts/train.py --data_parallel_group_size D --model_cfg X.yaml
+
+Per step: LR schedule (linear warm-up, cosine decay) -> batch to this rank's layout -> one optimisation step -> rank-0
+log line in ``{train_path}/{description}/loss/rank0.txt``. Checkpoints every ``save_interval_epochs`` under
+``{train_path}/{description}/ckpt/...``; ``ckpt_start: True`` + ``ckpt_epoch`` resumes.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from train_scripts.common import PRETRAIN_DEFAULTS, Session, base_parser  # noqa: E402
+from terra_b200.checkpoint_io import load_checkpoint, save_checkpoint  # noqa: E402
+from terra_b200.optim.utils import get_lr_by_global_step, set_lr  # noqa: E402
+from terra_b200.runtime.run_model import one_step_train_production  # noqa: E402
+
+
+def main(argv=None):
+    args = base_parser("terra_b200 pretraining").parse_args(argv)
+    s = Session(args.model_cfg, args.data_parallel_group_size, PRETRAIN_DEFAULTS)
+    c = s.cfg
+    loader = s.pretrain_loader(status=0)
+    start_epoch = int(c.get("start_epoch", 0))
+    if c.get("ckpt_start", False):
+        epoch, gstep, _ = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type, s.opt_state,
+                                          s.manager, epoch=c["ckpt_epoch"], scaler=s.gscaler)
+        start_epoch = epoch + 1
+    log_file = None
+    if s.is_log_rank():
+        d = os.path.join(c["train_path"], c["description"], "loss")
+        os.makedirs(d, exist_ok=True)
+        log_file = open(os.path.join(d, "rank0.txt"), "a", buffering=1)
+    last_loss = None
+    for epoch in range(start_epoch, int(c["num_pre_train_epochs"])):
+        if hasattr(loader.sampler, "set_epoch"):
+            loader.sampler.set_epoch(epoch)
+        for step, batch in enumerate(loader):
+            limit = c.get("max_train_steps_per_epoch")
+            if limit is not None and step >= int(limit):
+                break
+            lr = get_lr_by_global_step(s.task_type, s.optimizer.global_step, c["learning_rate"], c["warmup_steps"],
+                                       c["num_pre_train_epochs"])
+            set_lr(s.optimizer, lr)
+            tensors = s.to_required_tensors(batch)
+            _, loss, step_time, fwd_time = one_step_train_production(
+                s.task_type, s.model_type, s.model, s.engine, s.optimizer, tensors, s.task_data, s.other, s.precision,
+                c["half_model"], s.my_dtype, s.loss_fn, s.gscaler, s.manager, s.opt_state, clip_grad=c["clip_grad"])
+            last_loss = float(loss.item())
+            if log_file is not None:
+                log_file.write(f"{c['description']} epoch {epoch} step {step} loss {last_loss:.8f} lr {lr:.3e} "
+                               f"global_step {s.optimizer.global_step} step_time_s {step_time:.4f} "
+                               f"forward_time_s {fwd_time:.4f}\n")
+        if (epoch + 1) % int(c["save_interval_epochs"]) == 0:
+            save_checkpoint(s.model, s.optimizer, last_loss, epoch, c["train_path"], c["description"], s.model_type,
+                            s.opt_state, s.manager, s.gscaler)
+    if log_file is not None:
+        log_file.close()
+    s.close()
+    return last_loss
+
+
+if __name__ == "__main__":
+    main()
