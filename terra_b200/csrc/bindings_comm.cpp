@@ -1,4 +1,78 @@
-// Bindings of the peer-memory (NVLink) communication kernels.
+// Bindings of the peer-memory (NVLink) communication kernels. Peer buffers are passed as raw device addresses.
 #include <torch/extension.h>
+#include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAGuard.h>
 
-void bind_comm(pybind11::module_& m) { (void)m; }
+#include <cmath>
+
+#include "comm_api.h"
+#include "launch_count.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void dist_adamw_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& bf16_ptrs, torch::Tensor& master,
+                     torch::Tensor& exp_avg, torch::Tensor& exp_avg_sq, int64_t lo, int64_t n, double lr, double b1,
+                     double b2, double eps, double wd, int64_t step, double grad_scale) {
+  TORCH_CHECK(grad_ptrs.size() == bf16_ptrs.size() && !grad_ptrs.empty() && grad_ptrs.size() <= tb::COMM_MAX_PEERS,
+              "dist_adamw_step: one gradient and one working-copy base per replica");
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == torch::kFloat32 && exp_avg.numel() >= n, "dist_adamw_step: bad state");
+  const c10::cuda::CUDAGuard guard(master.device());
+  tb::DistAdamWArgs a{};
+  a.num_peers = static_cast<int>(grad_ptrs.size());
+  for (int i = 0; i < a.num_peers; ++i) {
+    a.grad[i] = reinterpret_cast<const float*>(grad_ptrs[i]);
+    a.param_bf16[i] = reinterpret_cast<void*>(bf16_ptrs[i]);
+  }
+  a.master = master.data_ptr<float>();
+  a.exp_avg = exp_avg.data_ptr<float>();
+  a.exp_avg_sq = exp_avg_sq.data_ptr<float>();
+  a.lo = lo;
+  a.n = n;
+  a.lr = static_cast<float>(lr);
+  a.beta1 = static_cast<float>(b1);
+  a.beta2 = static_cast<float>(b2);
+  a.eps = static_cast<float>(eps);
+  a.weight_decay = static_cast<float>(wd);
+  a.bias_corr1 = static_cast<float>(1.0 - std::pow(b1, static_cast<double>(step)));
+  a.bias_corr2_sqrt = static_cast<float>(std::sqrt(1.0 - std::pow(b2, static_cast<double>(step))));
+  a.grad_scale = static_cast<float>(grad_scale);
+  tb::note_launch();
+  TORCH_CHECK(tb::dist_adamw_step(a, cur_stream()) == 0, "dist_adamw_step launch failed");
+}
+
+void peer_copy_rows(int64_t dst, int64_t src, int64_t rows, int64_t row_bytes, int64_t dst_stride, int64_t src_stride) {
+  tb::note_launch();
+  TORCH_CHECK(tb::peer_copy_rows(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), rows, row_bytes,
+                                 dst_stride, src_stride, cur_stream()) == 0,
+              "peer_copy_rows launch failed");
+}
+
+void peer_sum_small(torch::Tensor& dst, const std::vector<int64_t>& src_ptrs) {
+  std::vector<const float*> p;
+  for (auto v : src_ptrs) p.push_back(reinterpret_cast<const float*>(v));
+  tb::note_launch();
+  TORCH_CHECK(tb::peer_sum_small(dst.data_ptr<float>(), p.data(), static_cast<int>(p.size()), dst.numel(), cur_stream()) == 0,
+              "peer_sum_small launch failed");
+}
+
+void peer_barrier(const std::vector<int64_t>& pads, int64_t my_rank, int64_t epoch, const c10::optional<torch::Tensor>& status,
+                  int64_t spin_limit) {
+  std::vector<uint32_t*> p;
+  for (auto v : pads) p.push_back(reinterpret_cast<uint32_t*>(v));
+  tb::note_launch();
+  TORCH_CHECK(tb::peer_barrier(p.data(), static_cast<int>(my_rank), static_cast<int>(p.size()), static_cast<uint32_t>(epoch),
+                               status.has_value() ? status->data_ptr() : nullptr,
+                               static_cast<unsigned long long>(spin_limit), cur_stream()) == 0,
+              "peer_barrier launch failed");
+}
+
+}  // namespace
+
+void bind_comm(pybind11::module_& m) {
+  m.def("dist_adamw_step", &dist_adamw_step);
+  m.def("peer_copy_rows", &peer_copy_rows);
+  m.def("peer_sum_small", &peer_sum_small);
+  m.def("peer_barrier", &peer_barrier);
+}

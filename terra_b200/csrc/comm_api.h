@@ -1,0 +1,39 @@
+// Peer-memory (NVLink / NVSwitch) communication kernels. Buffers live in symmetric memory: every rank of a group
+// allocated the same layout, so a kernel addresses a peer's copy as peer_base + the same offset.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb {
+
+constexpr int COMM_MAX_PEERS = 16;
+
+// Sharded AdamW over replicas: this rank owns `n` elements starting at element `lo` of every replica's flat
+// gradient / working-copy arena. For the owned range the kernel sums the fp32 gradients of all replicas (P2P
+// loads), applies AdamW to the local fp32 master and moments, and stores the new bf16 values into every
+// replica's working copy (P2P stores). Group barriers before and after are the caller's.
+struct DistAdamWArgs {
+  const float* grad[COMM_MAX_PEERS];   // base of each replica's fp32 gradient arena
+  void* param_bf16[COMM_MAX_PEERS];    // base of each replica's bf16 working copy
+  int num_peers;
+  float* master;        // local fp32 master arena (base)
+  float* exp_avg;       // local moments of the owned range (n elements)
+  float* exp_avg_sq;
+  long long lo, n;
+  float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2_sqrt, grad_scale;
+};
+int dist_adamw_step(const DistAdamWArgs& a, cudaStream_t stream);
+
+// Rows [row0, row0 + rows) x row_bytes copied from a peer buffer into a local one (halo rows, relayout pulls).
+int peer_copy_rows(void* dst, const void* src_peer, long long rows, long long row_bytes, long long dst_stride_bytes,
+                   long long src_stride_bytes, cudaStream_t stream);
+
+// Sum of `num_peers` small fp32 vectors that live at the same offset on every peer (GroupNorm statistics).
+int peer_sum_small(float* dst, const float* const* src_peers, int num_peers, int n, cudaStream_t stream);
+
+// Group barrier on a symmetric signal pad: every rank adds 1 to its slot on all peers, then waits (bounded) until
+// its own pad shows `epoch` from everyone. `status` receives TB_ERR_PEER_TIMEOUT when the wait runs out.
+int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,
+                 unsigned long long spin_limit, cudaStream_t stream);
+
+}  // namespace tb

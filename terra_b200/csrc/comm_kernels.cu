@@ -1,0 +1,135 @@
+// Kernels that read and write other GPUs' memory directly (plain loads / stores over NVLink through NVSwitch).
+#include "comm_api.h"
+#include "common.cuh"
+
+namespace tb {
+namespace {
+
+__global__ void __launch_bounds__(256) dist_adamw_kernel(const __grid_constant__ DistAdamWArgs a) {
+  const long long nvec = a.n / 4;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = a.lo + i * 4;
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int p = 0; p < a.num_peers; ++p) {
+      const float4 v = *reinterpret_cast<const float4*>(a.grad[p] + e);
+      g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
+    }
+    float gv[4] = {g.x * a.grad_scale, g.y * a.grad_scale, g.z * a.grad_scale, g.w * a.grad_scale};
+    float4 pm = *reinterpret_cast<const float4*>(a.master + e);
+    float4 m4 = *reinterpret_cast<const float4*>(a.exp_avg + i * 4);
+    float4 v4 = *reinterpret_cast<const float4*>(a.exp_avg_sq + i * 4);
+    float pv[4] = {pm.x, pm.y, pm.z, pm.w}, mv[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      pv[k] *= 1.f - a.lr * a.weight_decay;
+      mv[k] = a.beta1 * mv[k] + (1.f - a.beta1) * gv[k];
+      vv[k] = a.beta2 * vv[k] + (1.f - a.beta2) * gv[k] * gv[k];
+      const float denom = sqrtf(vv[k]) / a.bias_corr2_sqrt + a.eps;
+      pv[k] -= (a.lr / a.bias_corr1) * (mv[k] / denom);
+    }
+    *reinterpret_cast<float4*>(a.master + e) = make_float4(pv[0], pv[1], pv[2], pv[3]);
+    *reinterpret_cast<float4*>(a.exp_avg + i * 4) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+    *reinterpret_cast<float4*>(a.exp_avg_sq + i * 4) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    const uint2 packed = make_uint2(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]));
+#pragma unroll 4
+    for (int p = 0; p < a.num_peers; ++p)
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.param_bf16[p]) + e) = packed;
+  }
+}
+
+__global__ void __launch_bounds__(256) peer_copy_rows_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src,
+                                                             long long rows, long long vec_per_row,
+                                                             long long dst_stride, long long src_stride) {
+  const long long total = rows * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row, v = i % vec_per_row;
+    *reinterpret_cast<uint4*>(dst + r * dst_stride + v * 16) = *reinterpret_cast<const uint4*>(src + r * src_stride + v * 16);
+  }
+}
+
+struct PeerPtrs {
+  const float* p[COMM_MAX_PEERS];
+};
+__global__ void peer_sum_small_kernel(float* dst, const __grid_constant__ PeerPtrs srcs, int num_peers, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    float s = 0.f;
+    for (int p = 0; p < num_peers; ++p) s += srcs.p[p][i];
+    dst[i] = s;
+  }
+}
+
+struct PadPtrs {
+  uint32_t* p[COMM_MAX_PEERS];
+};
+// One block. Thread t < num_peers signals peer t, then everyone waits on the local pad.
+__global__ void peer_barrier_kernel(const __grid_constant__ PadPtrs pads, int my_rank, int num_peers, uint32_t epoch,
+                                    KernelStatus* status, unsigned long long spin_limit) {
+  const int t = threadIdx.x;
+  if (t < num_peers) {
+    __threadfence_system();
+    // slot [my_rank] on peer t
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(pads.p[t] + my_rank) : "memory");
+  }
+  if (t < num_peers) {
+    const volatile uint32_t* mine = pads.p[my_rank] + t;
+    unsigned long long spins = 0;
+    uint32_t seen;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(seen - epoch) >= 0) break;
+      if (++spins > spin_limit) {
+        report_error(status, TB_ERR_PEER_TIMEOUT, 0x900u, static_cast<unsigned int>(t), epoch);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+}
+
+}  // namespace
+
+int dist_adamw_step(const DistAdamWArgs& a, cudaStream_t stream) {
+  if (a.num_peers < 1 || a.num_peers > COMM_MAX_PEERS || a.n % 4 != 0 || a.lo % 4 != 0) return -1;
+  if (a.n == 0) return 0;
+  long long blocks = (a.n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  dist_adamw_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int peer_copy_rows(void* dst, const void* src_peer, long long rows, long long row_bytes, long long dst_stride_bytes,
+                   long long src_stride_bytes, cudaStream_t stream) {
+  if (row_bytes % 16 != 0 || dst_stride_bytes % 16 != 0 || src_stride_bytes % 16 != 0) return -1;
+  if (rows <= 0 || row_bytes <= 0) return 0;
+  const long long total = rows * (row_bytes / 16);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  peer_copy_rows_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<uint8_t*>(dst),
+                                                                      static_cast<const uint8_t*>(src_peer), rows,
+                                                                      row_bytes / 16, dst_stride_bytes, src_stride_bytes);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int peer_sum_small(float* dst, const float* const* src_peers, int num_peers, int n, cudaStream_t stream) {
+  if (num_peers < 1 || num_peers > COMM_MAX_PEERS || n <= 0) return -1;
+  PeerPtrs pp;
+  for (int i = 0; i < num_peers; ++i) pp.p[i] = src_peers[i];
+  peer_sum_small_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, pp, num_peers, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,
+                 unsigned long long spin_limit, cudaStream_t stream) {
+  if (num_peers < 1 || num_peers > COMM_MAX_PEERS) return -1;
+  PadPtrs pp;
+  for (int i = 0; i < num_peers; ++i) pp.p[i] = signal_pads[i];
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(pp, my_rank, num_peers, epoch, static_cast<KernelStatus*>(status), spin_limit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace tb

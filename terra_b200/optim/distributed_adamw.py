@@ -96,19 +96,23 @@ class DistributedAdamW(torch.optim.Optimizer):
         if self.fused is not None:
             self.fused.step(self, g0, scale)
             return loss
-        a = self.arena
         for sh in self.shards:
-            n_own = sh.hi - sh.lo
-            if sh.size > 1:
-                self._reduce_scatter(a.grad, sh)
-            if sh.exp_avg is None:
-                sh.exp_avg = torch.zeros(n_own, dtype=torch.float32, device=a.master.device)
-                sh.exp_avg_sq = torch.zeros_like(sh.exp_avg)
-            if n_own > 0:
-                self._update(a, sh, g0, scale)
-            if sh.size > 1:
-                self._all_gather(a, sh)
+            self.portable_shard_step(sh, g0, scale)
         return loss
+
+    def portable_shard_step(self, sh: "_Shard", g0, scale):
+        """Collective version of one shard's step: reduce-scatter, update of the owned range, all-gather."""
+        a = self.arena
+        n_own = sh.hi - sh.lo
+        if sh.size > 1:
+            self._reduce_scatter(a.grad, sh)
+        if sh.exp_avg is None:
+            sh.exp_avg = torch.zeros(max(n_own, 1), dtype=torch.float32, device=a.master.device)
+            sh.exp_avg_sq = torch.zeros_like(sh.exp_avg)
+        if n_own > 0:
+            self._update(a, sh, g0, scale)
+        if sh.size > 1:
+            self._all_gather(a, sh)
 
     def _reduce_scatter(self, grad, sh: _Shard):
         seg = grad[sh.start:sh.end]
@@ -122,18 +126,19 @@ class DistributedAdamW(torch.optim.Optimizer):
         lo, hi = sh.lo, sh.hi
         b1, b2 = g0["betas"]
         if a.master.is_cuda:
-            _ext.load().adamw_step(a.master[lo:hi], sh.exp_avg, sh.exp_avg_sq, a.grad[lo:hi],
+            _ext.load().adamw_step(a.master[lo:hi], sh.exp_avg[:hi - lo], sh.exp_avg_sq[:hi - lo], a.grad[lo:hi],
                                    a.bf16[lo:hi] if a.bf16 is not None else None, g0["lr"], b1, b2, g0["eps"],
                                    g0["weight_decay"], self.step_count, scale)
             return
         g = a.grad[lo:hi] * scale
         p = a.master[lo:hi]
         p.mul_(1 - g0["lr"] * g0["weight_decay"])
-        sh.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
-        sh.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+        m, v = sh.exp_avg[:hi - lo], sh.exp_avg_sq[:hi - lo]
+        m.mul_(b1).add_(g, alpha=1 - b1)
+        v.mul_(b2).addcmul_(g, g, value=1 - b2)
         bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
-        denom = sh.exp_avg_sq.sqrt().div_(math.sqrt(bc2)).add_(g0["eps"])
-        p.addcdiv_(sh.exp_avg, denom, value=-g0["lr"] / bc1)
+        denom = v.sqrt().div_(math.sqrt(bc2)).add_(g0["eps"])
+        p.addcdiv_(m, denom, value=-g0["lr"] / bc1)
 
     def _all_gather(self, a: ParamArena, sh: _Shard):
         """Every replica receives the updated values: the bf16 working copy on GPU (masters of foreign ranges are

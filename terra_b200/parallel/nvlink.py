@@ -1,0 +1,227 @@
+"""NVLink / NVSwitch backend: symmetric (peer-mapped) arenas and the operators that use them.
+
+Every rank of a group allocates the same arena layout through ``torch.distributed._symmetric_memory`` (PyTorch does
+the handle exchange and the peer mapping); kernels then address a peer's copy of a buffer as
+``peer_base + same offset``. On top of that:
+
+* ``FusedAttnComm``  - window attention whose CTAs read q/k/v rows of halo windows (window parallel) and of the other
+  token shards (sequence parallel) straight from the owners' buffers and store outputs to the tokens' home rows;
+  the only collectives left are two flag barriers around the shifted / sharded blocks;
+* ``FusedDistAdamW`` - the sharded optimizer step as one kernel: P2P reduce of the owned gradient range, fp32
+  AdamW, P2P store of the bf16 working copy to every replica;
+* small helpers: barrier on a symmetric signal pad (monotonic epochs, bounded spin, status word on expiry), sum of
+  small per-rank vectors (GroupNorm statistics).
+
+No TMA load here fans out over a cluster; remote data is read with plain loads or per-CTA TMA.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _ext
+from ..ops.gemm import status_word
+
+PAD_BYTES = 4096            # signal pads at the start of every arena
+BARRIER_SPIN_LIMIT = 200_000_000
+
+
+def _symm():
+    import torch.distributed._symmetric_memory as symm_mem
+
+    return symm_mem
+
+
+class SymmetricArena:
+    """Bump allocator over one symmetric allocation shared (by layout) with the ranks of ``group``."""
+
+    def __init__(self, group, nbytes: int, device: torch.device):
+        symm_mem = _symm()
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.nbytes = int(nbytes + PAD_BYTES + 255) // 256 * 256
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:
+            pass
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.hdl = symm_mem.rendezvous(self.buf, group=group)
+        self.base_ptrs: List[int] = [int(p) for p in self.hdl.buffer_ptrs]
+        if self.base_ptrs[self.rank] != self.buf.data_ptr():
+            # some versions report the local mapping under a different address; use the tensor's
+            self.base_ptrs[self.rank] = self.buf.data_ptr()
+        self.cursor = PAD_BYTES
+        self.persistent_end = PAD_BYTES
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    # ---- allocation
+    def alloc(self, shape, dtype, persistent: bool = False) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = (self.cursor + 255) // 256 * 256
+        if start + nbytes > self.nbytes:
+            raise RuntimeError(f"symmetric arena exhausted: need {start + nbytes} of {self.nbytes} bytes "
+                               "(raise TERRA_SYMM_ARENA_GB)")
+        self.cursor = start + nbytes
+        if persistent:
+            if start != (self.persistent_end + 255) // 256 * 256:
+                raise RuntimeError("persistent symmetric allocations must come before any per-step allocation")
+            self.persistent_end = self.cursor
+        return self.buf[start:start + nbytes].view(dtype).view(*shape)
+
+    def reset(self) -> None:
+        """Forget the per-step allocations (call between steps, when no kernel of the previous step is pending
+        on a peer: the last cross-rank access of a step is followed by a barrier)."""
+        self.cursor = self.persistent_end
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        off = t.data_ptr() - self.buf.data_ptr()
+        if off < 0 or off >= self.nbytes:
+            raise ValueError("tensor is not inside this symmetric arena")
+        return off
+
+    def peer_ptrs(self, t: torch.Tensor) -> List[int]:
+        off = self.offset_of(t)
+        return [b + off for b in self.base_ptrs]
+
+    # ---- synchronisation
+    def barrier(self) -> None:
+        """Stream-ordered barrier over the group (device side; the host does not wait)."""
+        self.epoch += 1
+        _ext.load().peer_barrier(self.base_ptrs, self.rank, self.epoch, status_word(self.buf.device), BARRIER_SPIN_LIMIT)
+
+
+class FusedAttnComm:
+    """Peer access for ``window_attn`` over the (window group x token shard) ranks that share a TP rank."""
+
+    fused = True
+
+    def __init__(self, arena: SymmetricArena, n_wg: int, sp: int):
+        self.arena = arena
+        self.world = arena.world
+        self.n_wg, self.sp = n_wg, sp
+        if arena.world != n_wg * sp:
+            raise ValueError(f"attention peer group has {arena.world} ranks, expected {n_wg} x {sp}")
+        self.max_rows: Optional[int] = None
+
+    def _needs_peers(self, shifted: bool) -> bool:
+        return self.sp > 1 or (shifted and self.n_wg > 1)
+
+    def _rows(self, rows: int) -> int:
+        # every rank must advance the arena identically: size by the largest shard (ragged ownership)
+        if self.max_rows is None:
+            t = torch.tensor([rows], device=self.arena.buf.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.arena.group)
+            self.max_rows = int(t.item())
+        return max(rows, self.max_rows)
+
+    def alloc_qkv(self, rows, cols):
+        full = self.arena.alloc((self._rows(rows), cols), torch.bfloat16)
+        return full[:rows]
+
+    def attn_forward_buffers(self, qkv, C, shifted):
+        rows = qkv.shape[0]
+        o = self.arena.alloc((self._rows(rows), C), torch.bfloat16)[:rows]
+        if self._needs_peers(shifted):
+            self.arena.barrier()                       # every peer's q/k/v is complete
+        return o, self.arena.peer_ptrs(qkv), self.arena.peer_ptrs(o)
+
+    def attn_forward_done(self, o, qkv, shifted):
+        if self._needs_peers(shifted):
+            self.arena.barrier()                       # every peer's stores into my rows have landed
+        return o, qkv
+
+    def alloc_dout(self, rows, C):
+        return self.arena.alloc((self._rows(rows), C), torch.bfloat16)[:rows]
+
+    def attn_backward_buffers(self, qkv, do, shifted):
+        rows = qkv.shape[0]
+        dqkv = self.arena.alloc((self._rows(rows), qkv.shape[1]), torch.bfloat16)[:rows]
+        if self._needs_peers(shifted):
+            self.arena.barrier()
+        return dqkv, self.arena.peer_ptrs(qkv), self.arena.peer_ptrs(do), self.arena.peer_ptrs(dqkv)
+
+    def attn_backward_done(self, dqkv, shifted):
+        if self._needs_peers(shifted):
+            self.arena.barrier()
+        return dqkv
+
+
+class FusedDistAdamW:
+    """One kernel per parameter class: reduce-scatter + AdamW + all-gather over peer memory."""
+
+    def __init__(self, arenas: Dict[str, SymmetricArena], grad_views: Dict[str, torch.Tensor],
+                 bf16_views: Dict[str, torch.Tensor]):
+        self.arenas, self.grad_views, self.bf16_views = arenas, grad_views, bf16_views
+
+    def step(self, opt, g0, scale):
+        ext = _ext.load()
+        a = opt.arena
+        b1, b2 = g0["betas"]
+        for sh in opt.shards:
+            ar = self.arenas.get(sh.label)
+            if ar is None or sh.size == 1:
+                opt.portable_shard_step(sh, g0, scale)
+                continue
+            n_own = sh.hi - sh.lo
+            if sh.exp_avg is None:
+                sh.exp_avg = torch.zeros(max(n_own, 1), dtype=torch.float32, device=a.master.device)
+                sh.exp_avg_sq = torch.zeros_like(sh.exp_avg)
+            ar.barrier()                                   # every replica's gradients are final
+            ext.dist_adamw_step(ar.peer_ptrs(self.grad_views[sh.label]), ar.peer_ptrs(self.bf16_views[sh.label]),
+                                a.master, sh.exp_avg, sh.exp_avg_sq, sh.lo, n_own, g0["lr"], b1, b2, g0["eps"],
+                                g0["weight_decay"], opt.step_count, scale)
+            ar.barrier()                                   # every replica's working copy is complete
+            opt._masters_stale = True
+
+
+def attach(model, optimizer, manager) -> None:
+    """Switch a freshly built (model, optimizer) pair to the peer-memory paths."""
+    import os
+
+    from ..optim.distributed_adamw import DistributedAdamW
+    from ..utils.flat_params import ParamArena, get_arena
+
+    device = next(model.parameters()).device
+    pctx = model.pctx
+    gb = float(os.environ.get("TERRA_SYMM_ARENA_GB", "0"))
+    # ---- attention peers: (window group x token shard) at this TP rank
+    if pctx.n_wg * pctx.sp > 1 and pctx.contiguous:
+        if gb <= 0:
+            rows = max(len(w) for w in pctx.windows_of) * pctx.shardN * pctx.B
+            C = model.embedding_dim // pctx.tp
+            per_layer = rows * C * 2 * (3 + 1 + 1 + 3)            # qkv, o, do, dqkv
+            nbytes = int(per_layer * model.num_layers * 1.25) + (64 << 20)
+        else:
+            nbytes = int(gb * (1 << 30))
+        arena = SymmetricArena(manager.xfmr_tp_param_group, nbytes, device)
+        pctx.fused_comm = FusedAttnComm(arena, pctx.n_wg, pctx.sp)
+        pctx.attn_arena = arena
+    # ---- sharded optimizer: gradients and working copy must be peer visible. One symmetric allocation is mapped
+    # for one group, so the largest parameter class gets the fused kernel; other classes (TP shards, whose replica
+    # group differs) keep the collective path on the same buffers.
+    if isinstance(optimizer, DistributedAdamW):
+        pa = get_arena(model)
+        cands = [sh for sh in optimizer.shards if sh.size > 1]
+        if cands:
+            sh = max(cands, key=lambda s: s.end - s.start)
+            n = pa.numel
+            ar = SymmetricArena(sh.group, n * 4 + n * 2 + 8192, device)
+            g = ar.alloc((n,), torch.float32, persistent=True)
+            b = ar.alloc((n,), torch.bfloat16, persistent=True)
+            pa.rebind(g, b)
+            optimizer.fused = FusedDistAdamW({sh.label: ar}, {sh.label: g}, {sh.label: b})
+
+
+def reset_step_arenas(model) -> None:
+    arena = getattr(model.pctx, "attn_arena", None)
+    if arena is not None:
+        arena.reset()

@@ -107,6 +107,7 @@ class ParamArena:
             self.params.append(p)
             self.names.append(n)
             self.offsets.append(off)
+        self._fused_records = []
         for label in ordered:
             for members, tag in ordered[label]:
                 if tag is None:
@@ -119,11 +120,31 @@ class ParamArena:
                 if fused is None:
                     fused = {}
                     mod.fused = fused
+                self._fused_records.append((mod, gname, off, total, shape))
                 fused[gname] = FusedView(
                     self.master[off:off + total].view(shape), self.grad[off:off + total].view(shape),
                     self.bf16[off:off + total].view(shape) if self.bf16 is not None else None)
         self.sync_bf16()
         model._param_arena = self
+
+    def rebind(self, grad: torch.Tensor, bf16: Optional[torch.Tensor]) -> None:
+        """Move the gradient arena (and the bf16 working copy) into caller-provided flat buffers of the same
+        length, e.g. peer-visible symmetric memory, and re-point every view."""
+        if grad.numel() != self.numel or grad.dtype != torch.float32:
+            raise ValueError("rebind: gradient buffer must be fp32 with the arena's length")
+        grad.copy_(self.grad)
+        self.grad = grad
+        if bf16 is not None:
+            if bf16.numel() != self.numel or bf16.dtype != torch.bfloat16:
+                raise ValueError("rebind: working copy must be bf16 with the arena's length")
+            bf16.copy_(self.master)
+            self.bf16 = bf16
+        for p, off in zip(self.params, self.offsets):
+            p.grad = self.grad[off:off + p.numel()].view(p.shape)
+            p.bf16 = self.bf16[off:off + p.numel()].view(p.shape) if self.bf16 is not None else None
+        for mod, gname, off, total, shape in self._fused_records:
+            mod.fused[gname] = FusedView(self.master[off:off + total].view(shape), self.grad[off:off + total].view(shape),
+                                         self.bf16[off:off + total].view(shape) if self.bf16 is not None else None)
 
     def sync_bf16(self) -> None:
         """Refresh the bf16 working copy from the fp32 masters (after init or a checkpoint load)."""

@@ -1,0 +1,135 @@
+"""Pure-function units: padding, config validation, rank algebra, activation config, recompute scheduler, LR."""
+import math
+
+import pytest
+
+from terra_b200.config import get_model_archi_params_and_other_params
+from terra_b200.memory.activation import (activation_config_for_layer, activation_config_for_sampling,
+                                          normalize_activation_config, normalize_activation_mode)
+from terra_b200.memory.selective_recompute import SelectiveRecomputeScheduler
+from terra_b200.optim.utils import get_finetune_lr_by_global_step, get_lr_by_global_step
+from terra_b200.parallel.rank_manager import Topology
+from terra_b200.utils.padding import compute_auto_padded_shape, get_padded_shape
+
+
+def test_padding_rules():
+    need, pad, shape = get_padded_shape(2041, 4320, 4, 8, padding_scale=2)
+    assert shape == (2048, 4352) and need and pad == (16, 16, 3, 4)
+    need, pad, shape = get_padded_shape(128, 256, 4, 8, padded_shape=(128, 256))
+    assert not need and shape == (128, 256)
+    with pytest.raises(ValueError):
+        get_padded_shape(128, 256, 4, 8, padded_shape=(64, 256))
+    assert compute_auto_padded_shape(2048, 4320, 4, 8, 2, (8, 1), (8, 1), "terra_m1_ragged_auto") == (2048, 4352)
+    assert compute_auto_padded_shape(720, 1440, 4, (8, 12), 2, (8, 1), (8, 1), "terra_m1_ragged_auto") == (768, 1440)
+    assert compute_auto_padded_shape(2041, 4320, 4, 32, 2, (8, 1), (8, 1), "terra_m1_ragged_auto") == (2048, 4352)
+
+
+def test_padding_matches_reference_when_installed():
+    from baseline import ref_import
+
+    if not ref_import.available():
+        pytest.skip("reference not installed")
+    ref_import.enable()
+    from models.model_utils.get_model import _compute_auto_padded_shape as ref_auto
+    from utils import get_padded_shape as ref_pad
+
+    for (h, w, p, ws, scale) in [(2041, 4320, 4, 8, 2), (721, 1440, 4, 8, 1), (100, 300, 2, 6, 2)]:
+        assert get_padded_shape(h, w, p, ws, scale) == ref_pad(h, w, p, ws, scale)
+    for mode, topo in [("terra_m1_ragged_auto", (8, 1)), ("terra_m1_regular", (4, 1)), ("regular", (2, 2)),
+                       ("terra_m1_ragged_row", (6, 1)), ("ragged_round_robin", (8, 1))]:
+        wp = (topo[0] * topo[1], 1)
+        got = compute_auto_padded_shape(2041, 4320, 4, 8, 2, wp, topo, mode)
+        assert got == ref_auto(2041, 4320, 4, 8, "credit_hierarchical_swin", wp, topo, mode), (mode, got)
+
+
+BASE = dict(task_type="glorys", model_architecture="credit_hierarchical_swin", model_type="parallel", height=2048,
+            width=4320, num_channels=186, patch_size=4, embedding_dim=384, depths=[2, 6, 6, 2], num_heads=[6, 12, 24, 12],
+            num_layers=16, window_size=8, padding_policy="auto", window_assignment_mode="terra_m1_ragged_auto")
+
+
+def test_config_resolution_high_res_2x2x2():
+    cfg = dict(BASE, wp_topo="(8, 1)", xfmr_wp_topo="(2, 1)", xfmr_sp_size=2, tensor_parallel_size=2)
+    archi, other = get_model_archi_params_and_other_params("glorys", cfg, 1, 8)
+    assert archi["padded_shape"] == (2048, 4352) and archi["num_layers"] == 16
+    assert other["wp_topo"] == (8, 1) and other["xfmr_wp_topo"] == (2, 1)
+    assert archi["padding_spec"]["num_windows"] == (32, 68)
+    with pytest.raises(ValueError):                    # product rule
+        get_model_archi_params_and_other_params("glorys", dict(cfg, xfmr_sp_size=4), 1, 8)
+    with pytest.raises(ValueError):                    # the all-to-all SP of the reference would need heads % 4 == 0
+        get_model_archi_params_and_other_params("glorys", dict(cfg, strict_ulysses_heads=True), 1, 8)
+    with pytest.raises(ValueError):
+        get_model_archi_params_and_other_params("glorys", dict(cfg, window_topology="mn"), 1, 8)
+
+
+def test_rank_algebra_roundtrip():
+    for placement in ("tp_first", "sp_first"):
+        t = Topology(dp_size=2, mp_size=1, wp_topo=(8, 1), xfmr_wp_topo=(2, 1), xfmr_sp_size=2, xfmr_tp_size=2,
+                     sp_tp_placement=placement)
+        seen = set()
+        for wg in range(2):
+            for sp in range(2):
+                for tp in range(2):
+                    r = t.xfmr_coord_to_wp_rank(wg, sp, tp)
+                    assert t.wp_rank_to_xfmr_coord(r) == (wg, sp, tp)
+                    seen.add(r)
+        assert seen == set(range(8))
+        assert t.global_rank(1, 0, 3) == 11 and t.split_rank(11) == (1, 0, 3)
+        for groups in (t.dp_groups(), t.wp_groups(), t.sp_groups(), t.tp_groups(), t.tp_param_groups(),
+                       t.full_param_replica_groups(), t.tp_param_replica_groups(), t.window_group_groups()):
+            flat = sorted(r for g in groups for r in g)
+            assert flat == sorted(list(range(16)) * (len(flat) // 16))
+    assert Topology(wp_topo=(4, 1), xfmr_wp_topo=(2, 1), xfmr_tp_size=2).tp_groups() == [[0, 1], [2, 3]]
+    with pytest.raises(ValueError):
+        Topology(wp_topo=(4, 1), xfmr_wp_topo=(2, 1), xfmr_tp_size=4)
+
+
+def test_activation_config_normalisation():
+    assert normalize_activation_mode("torch") == "torch_recompute"
+    assert normalize_activation_mode("cpu_offload_boundary") == "cpu_boundary_offload_recompute"
+    with pytest.raises(ValueError):
+        normalize_activation_mode("bogus")
+    off = normalize_activation_config({"activation": {"mode": "none"}})
+    assert not off["enabled"] and off["checkpoint_layers"] == []
+    cfg = normalize_activation_config({"activation": {
+        "mode": "torch_recompute", "policy": "larger_wrapper", "checkpoint_layers": ["D1", "0-3", 5, "U0"],
+        "layer_modes": {"cpu_boundary_offload": [0], "5": "none"}, "sampling_modes": {"down": "boundary_offload"}}})
+    assert cfg["checkpoint_segments"] == [(0, 4), (5, 6)]
+    assert cfg["checkpoint_down_mode"] == "D1" and cfg["checkpoint_up_mode"] == "U0"
+    assert activation_config_for_layer(cfg, 0)["mode"] == "cpu_boundary_offload_recompute"
+    assert activation_config_for_layer(cfg, 5)["mode"] == "none"
+    assert activation_config_for_sampling(cfg, "down")["mode"] == "cpu_boundary_offload_recompute"
+    assert activation_config_for_sampling(cfg, "up")["mode"] == "torch_recompute"
+    legacy = normalize_activation_config({"selective_recompute": {"enabled": True, "impl": "torch", "block_indices": [1, 2]}})
+    assert legacy["mode"] == "torch_recompute" and legacy["checkpoint_layers"] == [1, 2]
+    with pytest.raises(ValueError):
+        normalize_activation_config({"activation": {"mode": "torch", "checkpoint_sampling_blocks": True}})
+
+
+def test_recompute_scheduler_segments():
+    s = SelectiveRecomputeScheduler({"mode": "torch", "policy": "uniform", "checkpoint_every_n_layers": 3}, depth=7)
+    assert list(s.execution_segments()) == [(0, 1, True), (1, 2, False), (2, 3, False), (3, 4, True), (4, 5, False),
+                                            (5, 6, False), (6, 7, True)]
+    s = SelectiveRecomputeScheduler({"mode": "torch", "checkpoint_layers": ["1-2", 4]}, depth=6)
+    assert list(s.execution_segments()) == [(0, 1, False), (1, 3, True), (3, 4, False), (4, 5, True), (5, 6, False)]
+    s.set_checkpoint_plan(["0-1", "3-5"], activation_mode="cpu_boundary_offload_recompute",
+                          segment_activation_modes=["torch", "boundary_offload"])
+    assert s.checkpoint_segments == [(0, 2), (3, 6)]
+    assert s.config_for_block(0)["mode"] == "torch_recompute"
+    assert s.config_for_block(3)["mode"] == "cpu_boundary_offload_recompute"
+    with pytest.raises(ValueError):
+        SelectiveRecomputeScheduler({"mode": "torch", "checkpoint_layers": ["2-4", "3-5"]}, depth=8)
+    assert list(SelectiveRecomputeScheduler(None, depth=2).execution_segments()) == [(0, 1, False), (1, 2, False)]
+    full = SelectiveRecomputeScheduler({"mode": "torch"}, depth=3)
+    assert full.checkpoint_segments == [(0, 1), (1, 2), (2, 3)]
+
+
+def test_lr_schedules():
+    assert get_lr_by_global_step("glorys", 0, 1e-3, 10, 2) == 0.0
+    assert get_lr_by_global_step("glorys", 5, 1e-3, 10, 2) == pytest.approx(5e-4)
+    assert get_lr_by_global_step("glorys", 10, 1e-3, 10, 2) == pytest.approx(1e-3)
+    end = get_lr_by_global_step("glorys", 2 * 594, 1e-3, 10, 2)
+    assert end == pytest.approx(1e-6)
+    mid = get_lr_by_global_step("glorys", 10 + (2 * 594 - 10) // 2, 1e-3, 10, 2)
+    assert mid == pytest.approx(1e-6 + (1e-3 - 1e-6) * 0.5, rel=1e-6)
+    assert get_finetune_lr_by_global_step(3, 1e-3, 6) == pytest.approx(5e-4)
+    assert get_finetune_lr_by_global_step(60, 1e-3, 6) == 1e-3
