@@ -1,0 +1,122 @@
+"""Rollout finetuning loop (reference: train_scripts/finetune.py:60-623).
+
+Starts from pretrained weights (``trained_model_checkpoint_path`` or ``trained_model_config_path`` + ``trained_model_epoch``;
+entries are kept by key and shape, ``attn_mask`` buffers are skipped, loading is non-strict), rolls the model out for
+``finetune_lead_time`` steps per sample, and checkpoints under ``{train_path}/{description}/lead_{L}/ckpt/...`` by epoch
+and, with ``save_interval_steps``, by step (``ckpt_step`` resumes from one).
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from train_scripts.common import FINETUNE_DEFAULTS, Session, base_parser  # noqa: E402
+from terra_b200.checkpoint_io import (checkpoint_dir, checkpoint_kind, load_checkpoint, load_pretrained_weights,  # noqa: E402
+                                      save_checkpoint)
+from terra_b200.config import load_yaml  # noqa: E402
+from terra_b200.data.dataloader_utils import resolve_glorys_finetune_double_buffer  # noqa: E402
+from terra_b200.optim.utils import get_finetune_lr_by_global_step, set_lr  # noqa: E402
+from terra_b200.runtime.finetune_one_step import one_step_finetune  # noqa: E402
+
+
+def pretrained_path(s: Session):
+    c = s.cfg
+    if c.get("trained_model_checkpoint_path"):
+        return c["trained_model_checkpoint_path"]
+    if c.get("trained_model_config_path") and c.get("trained_model_epoch") is not None:
+        src = load_yaml(c["trained_model_config_path"])
+        kind = checkpoint_kind(src.get("model_type", s.model_type), s.opt_state)
+
+        class _Rank0:
+            """Window-parallel replicas hold identical weights, so rank 0's file serves every rank."""
+
+            def get_rank(self):
+                return 0 if c.get("load_pretrained_from_wp_rank0", True) else s.manager.get_rank()
+
+            def get_wp_rank(self):
+                return 0 if c.get("load_pretrained_from_wp_rank0", True) else s.manager.get_wp_rank()
+
+        d = checkpoint_dir(src.get("train_path", "./outputs"), src.get("description", "terra_run"), kind, _Rank0())
+        return os.path.join(d, f"epoch{c['trained_model_epoch']}.pth")
+    return None
+
+
+def sequence_to_leads(s: Session, seq_batch, lead_time):
+    """``[B, L+1, ...]`` host batch -> list of per-lead ``{'input_tensor', 'label_tensor'}`` (labels double buffered)."""
+    if s.model_type == "sequential":
+        from terra_b200.data.dataloader_utils import to_nhwc
+
+        seq_batch = to_nhwc(seq_batch, s.archi["num_channels"])
+    frames = resolve_glorys_finetune_double_buffer(seq_batch, s.device, s.data_dtype, lead_time,
+                                                   enabled=s.cfg.get("input_double_buffer", True))
+
+    class _Leads:
+        def __getitem__(self, lead):
+            out = {"label_tensor": frames[lead + 1]}
+            if lead == 0:
+                out["input_tensor"] = frames[0]
+            return out
+
+    return _Leads(), frames
+
+
+def main(argv=None):
+    args = base_parser("terra_b200 rollout finetuning").parse_args(argv)
+    s = Session(args.model_cfg, args.data_parallel_group_size, FINETUNE_DEFAULTS)
+    c = s.cfg
+    lead = int(c["finetune_lead_time"])
+    path = pretrained_path(s)
+    if path is not None and os.path.exists(path):
+        load_pretrained_weights(s.model, path, tuple(c.get("skip_pretrained_state_suffixes", ["attn_mask"])),
+                                log=print if s.is_log_rank() else None)
+    start_epoch = int(c.get("start_epoch", 0))
+    if c.get("ckpt_start", False):
+        epoch, gstep, _ = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type, s.opt_state,
+                                          s.manager, epoch=c.get("ckpt_epoch"), step=c.get("ckpt_step"), scaler=s.gscaler,
+                                          lead=lead)
+        start_epoch = epoch + (0 if c.get("ckpt_step") is not None else 1)
+    loader = s.finetune_loader(lead, status=0)
+    log_file = None
+    if s.is_log_rank():
+        d = os.path.join(c["train_path"], c["description"], f"lead_{lead}", "loss")
+        os.makedirs(d, exist_ok=True)
+        log_file = open(os.path.join(d, f"rank{s.rank}.txt"), "a", buffering=1)
+    last = None
+    for epoch in range(start_epoch, int(c["num_finetune_epochs"])):
+        if hasattr(loader.sampler, "set_epoch"):
+            loader.sampler.set_epoch(epoch)
+        for step, seq in enumerate(loader):
+            limit = c.get("max_train_steps_per_epoch")
+            if limit is not None and step >= int(limit):
+                break
+            lr = get_finetune_lr_by_global_step(s.optimizer.global_step, c["learning_rate"], c["warmup_steps"])
+            set_lr(s.optimizer, lr)
+            leads, frames = sequence_to_leads(s, seq, lead)
+            _, loss, step_time, _ = one_step_finetune(
+                s.task_type, s.model_type, s.model, s.engine, s.optimizer, leads, s.task_data, s.other, s.precision,
+                c["half_model"], s.my_dtype, s.loss_fn, s.gscaler, s.manager, s.opt_state, lead_time=lead,
+                loss_reduction=c["finetune_loss_reduction"], clip_grad=c["clip_grad"], sync_for_timing=False,
+                barrier_for_timing=False)
+            last = float(loss.item())
+            if hasattr(frames, "release"):
+                frames.release()
+            if log_file is not None:
+                log_file.write(f"{c['description']} lead {lead} epoch {epoch} step {step} loss {last:.8f} lr {lr:.3e} "
+                               f"global_step {s.optimizer.global_step} step_time_s {step_time:.4f}\n")
+            every = int(c.get("save_interval_steps") or 0)
+            if every > 0 and s.optimizer.global_step % every == 0:
+                save_checkpoint(s.model, s.optimizer, last, epoch, c["train_path"], c["description"], s.model_type,
+                                s.opt_state, s.manager, s.gscaler, lead=lead, step=s.optimizer.global_step)
+        if (epoch + 1) % int(c["save_interval_epochs"]) == 0:
+            save_checkpoint(s.model, s.optimizer, last, epoch, c["train_path"], c["description"], s.model_type, s.opt_state,
+                            s.manager, s.gscaler, lead=lead)
+    if log_file is not None:
+        log_file.close()
+    s.close()
+    return last
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,156 @@
+"""Benchmark / correctness harness for rollout finetuning (reference: train_scripts/test_finetune.py:60-1270).
+
+Per step: loss, output sum, peak memory, step time, input-transfer time, offload statistics; ``--memory_timeline_csv``
+writes one row per (iteration, lead). Activation plans can change per lead:
+
+    activation:
+      lead_checkpoint_schedule:            # lead index -> plan applied just before that lead's forward
+        0: {checkpoint_layers: [], mode: none}
+        1: {checkpoint_layers: ['0-3'], mode: torch_recompute}
+        2: {checkpoint_layers: ['0-7'], mode: cpu_boundary_offload_recompute, offload: {min_numel: 1048576}}
+      lead_sampling_checkpoint_schedule:   # lead index -> {down: D0|D1|none, up: U0|U1|none}
+        2: {down: D1, up: U1}
+"""
+from __future__ import annotations
+
+import csv
+import json
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from train_scripts.common import FINETUNE_DEFAULTS, Session, base_parser  # noqa: E402
+from train_scripts.finetune import sequence_to_leads  # noqa: E402
+from terra_b200 import global_env_config as G  # noqa: E402
+from terra_b200.logging_utils import set_dp_rank_print_redirect  # noqa: E402
+from terra_b200.memory.activation import normalize_sampling_mode  # noqa: E402
+from terra_b200.memory.boundary_offload import get_boundary_offload_stats, reset_boundary_offload_stats  # noqa: E402
+from terra_b200.profiler.memory_timeline import CudaMemoryTimeline, set_memory_timeline_context  # noqa: E402
+from terra_b200.runtime.finetune_one_step import one_step_finetune  # noqa: E402
+
+
+def _int_keys(d):
+    return {int(k): v for k, v in (d or {}).items()}
+
+
+def make_lead_callback(model, cfg, records):
+    """Applies ``lead_checkpoint_schedule`` / ``lead_sampling_checkpoint_schedule`` before each lead's forward."""
+    act = cfg.get("activation") or {}
+    plans = _int_keys(act.get("lead_checkpoint_schedule"))
+    sampling = _int_keys(act.get("lead_sampling_checkpoint_schedule"))
+    real = model.module if hasattr(model, "module") else model
+    sched = real.recompute_scheduler
+    base_down, base_up = real.checkpoint_down_mode, real.checkpoint_up_mode
+
+    def callback(event, lead, loss):
+        if event == "before_forward":
+            plan = plans.get(lead)
+            if plan is not None:
+                sched.set_checkpoint_plan(plan.get("checkpoint_layers", []), plan.get("mode"), plan.get("offload"),
+                                          plan.get("segment_activation_modes"))
+            smp = sampling.get(lead)
+            if smp is not None:
+                real.checkpoint_down_mode = normalize_sampling_mode(smp.get("down"), "down")
+                real.checkpoint_up_mode = normalize_sampling_mode(smp.get("up"), "up")
+            else:
+                real.checkpoint_down_mode, real.checkpoint_up_mode = base_down, base_up
+            records.append(dict(lead=lead, segments=list(sched.checkpoint_segments), mode=sched.mode,
+                                down=real.checkpoint_down_mode, up=real.checkpoint_up_mode,
+                                allocated_mib=torch.cuda.memory_allocated() / 2 ** 20 if torch.cuda.is_available() else 0.0))
+        elif event == "after_loss" and records:
+            records[-1]["loss"] = float(loss.detach().item()) if loss is not None else None
+
+    return callback if (plans or sampling) else (lambda event, lead, loss: records.append(dict(lead=lead)) if event == "before_forward" else None)
+
+
+def main(argv=None):
+    ap = base_parser("terra_b200 finetuning test harness")
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--metrics_csv", default=None)
+    ap.add_argument("--metrics_json", default=None)
+    ap.add_argument("--memory_timeline_csv", default=None)
+    ap.add_argument("--metrics_no_json", action="store_true")
+    ap.add_argument("--disable_torch_prof", action="store_true")
+    ap.add_argument("--quiet_metrics", action="store_true")
+    ap.add_argument("--disable_rank_log_redirect", action="store_true")
+    ap.add_argument("--mem_prof", type=int, default=None)
+    args = ap.parse_args(argv)
+    if args.steps is not None and args.steps <= 0:
+        raise ValueError(f"--steps must be positive, got {args.steps}")
+    steps = args.steps or 2
+    s = Session(args.model_cfg, args.data_parallel_group_size, dict(FINETUNE_DEFAULTS, use_fake_input=True))
+    c = s.cfg
+    lead = int(c["finetune_lead_time"])
+    set_dp_rank_print_redirect(s.manager, s.model_type, s.opt_state, s.other.get("embedding_parallel_type"),
+                               quiet=args.quiet_metrics, disable=args.disable_rank_log_redirect or s.world == 1)
+    reset_boundary_offload_stats()
+    mem_prof = args.mem_prof if args.mem_prof is not None else int(os.environ.get("MEM_PROF", G.MEM_PROF))
+    timeline = CudaMemoryTimeline(s.device if s.device.type == "cuda" else None, enabled=mem_prof > 0)
+    loader = s.finetune_loader(lead, status=0)
+    rows, lead_rows = [], []
+    it = iter(loader)
+    for i in range(steps):
+        t_load = time.time()
+        try:
+            seq = next(it)
+        except StopIteration:
+            it = iter(loader)
+            seq = next(it)
+        load_time = time.time() - t_load
+        leads, frames = sequence_to_leads(s, seq, lead)
+        records = []
+        cb = make_lead_callback(s.model, c, records)
+        if s.device.type == "cuda":
+            torch.cuda.reset_peak_memory_stats(s.device)
+        set_memory_timeline_context(iter=i)
+        with timeline.iteration(i):
+            out, loss, step_time, fwd_time = one_step_finetune(
+                s.task_type, s.model_type, s.model, s.engine, s.optimizer, leads, s.task_data, s.other, s.precision,
+                c["half_model"], s.my_dtype, s.loss_fn, s.gscaler, s.manager, s.opt_state, lead_time=lead,
+                loss_reduction=c["finetune_loss_reduction"], lead_callback=cb, memory_timeline=timeline,
+                clip_grad=c["clip_grad"])
+        transfer = frames.transfer_time_s() if hasattr(frames, "transfer_time_s") else 0.0
+        out_sum = out.detach().float().sum()
+        if dist.is_available() and dist.is_initialized() and s.model_type != "sequential":
+            dist.all_reduce(out_sum, group=s.manager.window_parallel_group)
+        peak = torch.cuda.max_memory_allocated(s.device) / 2 ** 20 if s.device.type == "cuda" else 0.0
+        off = get_boundary_offload_stats()
+        rows.append(dict(iter=i, lead_time=lead, loss=float(loss.item()), output_sum=float(out_sum.item()),
+                         dtype=str(out.dtype), peak_memory_mb=peak, step_time_s=step_time, forward_time_s=fwd_time,
+                         load_data_time_s=load_time, input_transfer_time_s=transfer,
+                         offloaded_tensors=off["offloaded_tensors"], d2h_bytes=off["d2h_bytes"], h2d_bytes=off["h2d_bytes"]))
+        for r in records:
+            lead_rows.append(dict(iter=i, **{k: (str(v) if isinstance(v, list) else v) for k, v in r.items()}))
+        if s.is_log_rank() and not args.quiet_metrics:
+            print(f"iter {i} loss {rows[-1]['loss']:.8f} peak_memory_mb {peak:.1f} step_time_s {step_time:.4f} "
+                  f"offloaded {off['offloaded_tensors']}", flush=True)
+    if s.is_log_rank():
+        for path, data in ((args.metrics_csv, rows), (args.memory_timeline_csv, lead_rows)):
+            if path and data:
+                os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+                keys = sorted({k for r in data for k in r})
+                with open(path, "w", newline="") as f:
+                    w = csv.DictWriter(f, fieldnames=keys)
+                    w.writeheader()
+                    w.writerows(data)
+        if args.metrics_json and not args.metrics_no_json:
+            os.makedirs(os.path.dirname(os.path.abspath(args.metrics_json)), exist_ok=True)
+            with open(args.metrics_json, "w") as f:
+                json.dump(dict(description=c.get("description"), lead_time=lead, world_size=s.world,
+                               offload=get_boundary_offload_stats(), final_loss=rows[-1]["loss"],
+                               recompute=s.model.recompute_scheduler.summary()), f, indent=1, default=str)
+        if mem_prof > 0 and timeline.events:
+            d = os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline")
+            timeline.write_csv(os.path.join(d, "finetune_timeline_rank0.csv"))
+            timeline.write_summary_csv(os.path.join(d, "finetune_primitive_summary_rank0.csv"))
+    s.close()
+    return rows
+
+
+if __name__ == "__main__":
+    main()
