@@ -145,21 +145,23 @@ def run_ours(args):
     last_loss = float(loss.item())
 
     # ---- end to end through the public API: staged H2D of every step's batch + D2H of the loss
-    staged = trainer.stage(host[0])
-    for i in range(max(1, args.warmup // 2)):
-        nxt = trainer.stage(host[(i + 1) % 2])
-        trainer.step(host[i % 2], staged)
-        staged = nxt
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        nxt = trainer.stage(host[(i + 1) % 2])       # next step's upload overlaps this step's compute
-        e2e_loss = trainer.step(host[i % 2], staged)
-        staged = nxt
-    barrier()
-    e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device=dev)
-    if live:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_loss, e2e_ms = None, torch.tensor([float("nan")], device=dev)
+    if not args.skip_e2e:
+        staged = trainer.stage(host[0])
+        for i in range(max(1, args.warmup // 2)):
+            nxt = trainer.stage(host[(i + 1) % 2])
+            trainer.step(host[i % 2], staged)
+            staged = nxt
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            nxt = trainer.stage(host[(i + 1) % 2])       # next step's upload overlaps this step's compute
+            e2e_loss = trainer.step(host[i % 2], staged)
+            staged = nxt
+        barrier()
+        e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device=dev)
+        if live:
+            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     clocks = sampler.stop()
 
     gb = 1
@@ -174,8 +176,9 @@ def run_ours(args):
                    "parallelism": par, "l2_policy": "inputs (3.3 GB each) larger than L2, two batches alternated",
                    "optimizer": "AdamW fp32 master, sharded over ranks when N>1"},
         "clocks": clocks,
-        "e2e": {"value": gb / (e2e_ms.item() * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms.item(),
-                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
+        "e2e": None if args.skip_e2e else {"value": gb / (e2e_ms.item() * 1e-3), "unit": "samples/s",
+                                           "ms_per_step": e2e_ms.item(), "h2d_bytes_per_step": h2d_bytes,
+                                           "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches), "loss": last_loss, "e2e_loss": e2e_loss,
     }
     if rank == 0:
@@ -199,6 +202,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test of the harness, not a benchmark)")
+    ap.add_argument("--skip-e2e", action="store_true", help="only the device-timed loop (used when profiling)")
     args = ap.parse_args()
     if args.warmup < 3 and not args.small:
         args.warmup = 3
