@@ -1,0 +1,56 @@
+"""Multi-GPU layouts on real GPUs (NCCL bootstrap + peer-memory kernels) against the single-GPU run of the same
+model and data. Skipped unless at least two GPUs are visible. NVLS is switched off for these child processes and the
+kernels use plain peer loads / stores."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _launch(n, layout, steps=4):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
+    worker = os.path.join(ROOT, "tests", "multigpu_worker.py")
+    if n == 1:
+        cmd = [sys.executable, worker, json.dumps(layout), str(steps)]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), worker, json.dumps(layout), str(steps)]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-4000:])
+    line = [ln for ln in out.stdout.splitlines() if ln.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+@pytest.mark.parametrize("n,layout", [
+    (2, {"xfmr_wp_topo": "(2, 1)"}),
+    (2, {"xfmr_wp_topo": "(1, 1)", "xfmr_sp_size": 2}),
+    (2, {"xfmr_wp_topo": "(1, 1)", "tensor_parallel_size": 2}),
+    (4, {"xfmr_wp_topo": "(4, 1)"}),
+    (4, {"xfmr_wp_topo": "(2, 1)", "xfmr_sp_size": 2}),
+])
+def test_layout_matches_single_gpu(n, layout):
+    _need(n)
+    ref = _launch(1, {})
+    got = _launch(n, layout)
+    for a, b in zip(got["losses"], ref["losses"]):
+        assert abs(a - b) < 3e-2 * abs(b), (got, ref)
