@@ -70,9 +70,14 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
 // x: [B,H,W,Cin] bf16 NHWC, w: [Cout, 9*Cin_pad] bf16, y: [B,Ho,Wo,Cout]
 void conv3x3_fwd(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& y, int64_t stride, int64_t flags,
                  const c10::optional<torch::Tensor>& bias, const c10::optional<torch::Tensor>& residual,
-                 const c10::optional<torch::Tensor>& status) {
+                 const c10::optional<torch::Tensor>& status, const c10::optional<torch::Tensor>& halo_lo,
+                 const c10::optional<torch::Tensor>& halo_hi) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 4, "x: NHWC bf16");
   TORCH_CHECK(w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.dim() == 2, "w: [Cout, 9*Cin_pad] bf16");
+  for (const auto* h : {&halo_lo, &halo_hi})
+    TORCH_CHECK(!h->has_value() || ((*h)->is_contiguous() && (*h)->scalar_type() == torch::kBFloat16 &&
+                                    (*h)->numel() == x.size(0) * x.size(2) * x.size(3)),
+                "halo rows must be contiguous bf16 [B, 1, W, Cin]");
   TORCH_CHECK(y.is_contiguous(), "y must be contiguous");
   const c10::cuda::CUDAGuard guard(x.device());
   tb::GemmEpilogue e{};
@@ -86,13 +91,15 @@ void conv3x3_fwd(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& 
   e.status = status.has_value() ? status->data_ptr() : nullptr;
   tb::note_launch();
   const int rc = tb::conv3x3_fwd_bf16(x.data_ptr(), w.data_ptr(), x.size(0), x.size(1), x.size(2), x.size(3), w.size(0),
-                                      static_cast<int>(stride), e, sm_count(), cur_stream());
+                                      static_cast<int>(stride), e, sm_count(), cur_stream(), opt_ptr(halo_lo),
+                                      opt_ptr(halo_hi));
   TORCH_CHECK(rc == 0, "terra_b200 conv3x3_fwd launch failed, code ", rc);
 }
 
 // dw: [9, Cout, Cin] fp32 (zeroed by the caller)
 void conv3x3_wgrad(const torch::Tensor& x, const torch::Tensor& dy, torch::Tensor& dw, int64_t stride, int64_t split_k,
-                   const c10::optional<torch::Tensor>& status) {
+                   const c10::optional<torch::Tensor>& status, const c10::optional<torch::Tensor>& halo_lo,
+                   const c10::optional<torch::Tensor>& halo_hi) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 4, "x: NHWC bf16");
   TORCH_CHECK(dy.scalar_type() == torch::kBFloat16 && dy.is_contiguous() && dy.dim() == 4, "dy: NHWC bf16");
   TORCH_CHECK(dw.scalar_type() == torch::kFloat32 && dw.is_contiguous(), "dw: fp32 [9,Cout,Cin]");
@@ -101,7 +108,7 @@ void conv3x3_wgrad(const torch::Tensor& x, const torch::Tensor& dy, torch::Tenso
   const int rc = tb::conv3x3_wgrad_bf16(x.data_ptr(), dy.data_ptr(), dw.data_ptr<float>(), x.size(0), x.size(1),
                                         x.size(2), x.size(3), dy.size(3), static_cast<int>(stride),
                                         static_cast<int>(split_k), status.has_value() ? status->data_ptr() : nullptr,
-                                        sm_count(), cur_stream());
+                                        sm_count(), cur_stream(), opt_ptr(halo_lo), opt_ptr(halo_hi));
   TORCH_CHECK(rc == 0, "terra_b200 conv3x3_wgrad launch failed, code ", rc);
 }
 

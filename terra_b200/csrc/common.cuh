@@ -201,13 +201,28 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_ma
 }
 
 // ----------------------------------------------------------------------------- small math
+// erf by the rational approximation 7.1.26 of Abramowitz & Stegun (|error| <= 1.5e-7, far below bf16 resolution):
+// one exponential, one reciprocal, a degree-5 polynomial. `e` returns exp(-x^2) for callers that need it too.
+__device__ __forceinline__ float erf_as(float x, float& e) {
+  const float ax = fabsf(x);
+  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
+  e = __expf(-ax * ax);
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  const float y = fmaf(-p * t, e, 1.0f);
+  return copysignf(y, x);
+}
+// Exact (erf-based) GELU and its derivative.
 __device__ __forceinline__ float gelu_erf(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+  float e;
+  return 0.5f * x * (1.0f + erf_as(x * 0.70710678118654752440f, e));
 }
 __device__ __forceinline__ float gelu_erf_grad(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
-  const float pdf = 0.39894228040143267794f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  float e;   // exp(-(x / sqrt 2)^2) = exp(-x^2 / 2): the Gaussian of the density term
+  const float cdf = 0.5f * (1.0f + erf_as(x * 0.70710678118654752440f, e));
+  return fmaf(x * 0.39894228040143267794f, e, cdf);
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

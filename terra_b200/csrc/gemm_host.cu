@@ -134,8 +134,38 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
 // 3x3 convolution, padding 1, stride 1 or 2, NHWC bf16, as implicit GEMM.
 //   x: [B, H, W, Cin]   w: [Cout, 9 * Cin_pad] (tap-major, Cin padded to a multiple of 64 with zeros)
 //   y: [B, Ho, Wo, Cout]
+static int image_map(CUtensorMap* out, const void* base, int Cin, int par, int W, int rows, int B, int box_w) {
+  unsigned long long dims[5] = {static_cast<unsigned long long>(Cin), static_cast<unsigned long long>(par),
+                                static_cast<unsigned long long>(W / par), static_cast<unsigned long long>(rows),
+                                static_cast<unsigned long long>(B)};
+  unsigned long long str[4] = {static_cast<unsigned long long>(Cin) * 2ull,
+                               static_cast<unsigned long long>(Cin) * 2ull * par,
+                               static_cast<unsigned long long>(Cin) * 2ull * W,
+                               static_cast<unsigned long long>(Cin) * 2ull * W * rows};
+  unsigned int box[5] = {64, 1, static_cast<unsigned int>(box_w), 1, 1};
+  return make_tensor_map_bf16(out, base, 5, dims, str, box);
+}
+
+static int attach_halos(GemmParams& p, const void* halo_lo, const void* halo_hi, int Cin, int par, int W, int H, int B,
+                        int box_w) {
+  p.img_h = H;
+  p.halo_flags = 0;
+  if (halo_lo != nullptr) {
+    const int rc = image_map(&p.map_halo_lo, halo_lo, Cin, par, W, 1, B, box_w);
+    if (rc != 0) return rc - 3000;
+    p.halo_flags |= 1;
+  }
+  if (halo_hi != nullptr) {
+    const int rc = image_map(&p.map_halo_hi, halo_hi, Cin, par, W, 1, B, box_w);
+    if (rc != 0) return rc - 4000;
+    p.halo_flags |= 2;
+  }
+  return 0;
+}
+
 int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin, int Cout, int stride,
-                     const GemmEpilogue& epi, int num_sms, cudaStream_t stream) {
+                     const GemmEpilogue& epi, int num_sms, cudaStream_t stream, const void* halo_lo,
+                     const void* halo_hi) {
   if (stride != 1 && stride != 2) return -11;
   if (stride == 2 && (W % 2 != 0)) return -12;
   if (Cin % 8 != 0 || Cout % 8 != 0) return -13;
@@ -173,6 +203,8 @@ int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin,
   if (rc != 0) return rc;
   rc = map_2d(&p.map_b, w, p.K, Cout, p.K, GEMM_BK, bn);
   if (rc != 0) return rc - 1000;
+  rc = attach_halos(p, halo_lo, halo_hi, Cin, par, W, H, B, GEMM_BM);
+  if (rc != 0) return rc;
   // tile (t0, t1, t2) = (w chunk, ho, b): base coordinates
   p.a_mul0[2] = GEMM_BM;          // w (in units of the strided grid)
   p.a_mul1[3] = stride;           // h_in = ho * stride + dh
@@ -205,7 +237,8 @@ int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin,
 // Weight gradient of the 3x3 convolution: dw[tap][Cout][Cin] (fp32, pre-zeroed, atomically accumulated)
 //   = sum over output pixels of dy[pix][Cout]^T * x[pix shifted by tap][Cin].
 int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, int W, int Cin, int Cout, int stride,
-                       int split_k, void* status, int num_sms, cudaStream_t stream) {
+                       int split_k, void* status, int num_sms, cudaStream_t stream, const void* halo_lo,
+                       const void* halo_hi) {
   if (stride != 1 && stride != 2) return -11;
   if (stride == 2 && (W % 2 != 0)) return -12;
   if (Cin % 8 != 0 || Cout % 8 != 0) return -13;
@@ -255,6 +288,10 @@ int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, i
     unsigned int box[5] = {64, 1, GEMM_BK, 1, 1};
     int rc = make_tensor_map_bf16(&p.map_b, x, 5, dims, str, box);
     if (rc != 0) return rc - 1000;
+  }
+  {
+    const int rc = attach_halos(p, halo_lo, halo_hi, Cin, stride, W, H, B, GEMM_BK);
+    if (rc != 0) return rc;
   }
   for (int tap = 0; tap < 9; ++tap) {
     const int dyy = tap / 3, dxx = tap % 3;

@@ -2,12 +2,12 @@
 //
 //   D[M,N] (+)= A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory.
 //
-// Roles inside a 192-thread CTA (one CTA per SM, tiles assigned round-robin):
+// Roles inside a 320-thread CTA (one CTA per SM, tiles assigned round-robin):
 //   warp 0   one elected lane issues TMA loads (per-CTA, no cluster fan-out) into a ring of
 //            128-byte-swizzled shared-memory stages, signalling `full[s]` by transaction bytes;
 //   warp 1   owns the TMEM allocation; one elected lane issues tcgen05.mma (M=128, N=BN, K=16)
 //            and commits to `empty[s]` (stage reusable) and `tfull[a]` (accumulator a complete);
-//   warps 2-5 epilogue: tcgen05.ld of their 32-lane TMEM quadrant, fused bias / GELU / residual /
+//   warps 2-9 epilogue (two per 32-lane TMEM quadrant, half of the columns each): tcgen05.ld, fused bias / GELU / residual /
 //            GELU-gradient / pixel-shuffle / split-K atomics, 16-byte global stores.
 // Two accumulators (2*BN TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
 //
@@ -35,6 +35,9 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+// warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per TMEM lane quadrant, each taking half of the columns)
+constexpr int GEMM_THREADS = 320;
+
 struct TileCoord {
   int grp, m_blk, n_blk, split;
   int kb_begin, kb_end;
@@ -55,7 +58,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile) 
 }
 
 template <int BN>
-__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -76,7 +79,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);
+      mbar_init(&tempty[a], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -132,8 +135,16 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               tma_load_2d(sA + j * (GEMM_BK * 128), &p.map_a, &full[s], m0 + j * 64, kb * GEMM_BK);
           } else if (p.a_mode == OP_TABLE_5D) {
             const short* e = p.ktable[kb];
-            tma_load_5d(sA, &p.map_a, &full[s], abase[0] + e[0], abase[1] + e[1], abase[2] + e[2], abase[3] + e[3],
-                        abase[4]);
+            int h = abase[3] + e[3];
+            const CUtensorMap* m = &p.map_a;
+            if (h < 0 && (p.halo_flags & 1)) {
+              m = &p.map_halo_lo;
+              h += 1;
+            } else if (h >= p.img_h && (p.halo_flags & 2)) {
+              m = &p.map_halo_hi;
+              h -= p.img_h;
+            }
+            tma_load_5d(sA, m, &full[s], abase[0] + e[0], abase[1] + e[1], abase[2] + e[2], h, abase[4]);
           } else {  // OP_PIXELS_5D: {channels, 1, w, h, b}
 #pragma unroll
             for (int j = 0; j < GEMM_BM / 64; ++j)
@@ -148,10 +159,18 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               tma_load_2d(sB + j * (GEMM_BK * 128), &p.map_b, &full[s], n0 + j * 64, kb * GEMM_BK);
           } else {  // OP_PIXELS_5D with per-group (tap) displacement
             const short* g = p.grp_off[tc.grp];
+            int h = ph_ * p.pix_hmul + g[2];
+            const CUtensorMap* m = &p.map_b;
+            if (h < 0 && (p.halo_flags & 1)) {
+              m = &p.map_halo_lo;
+              h += 1;
+            } else if (h >= p.img_h && (p.halo_flags & 2)) {
+              m = &p.map_halo_hi;
+              h -= p.img_h;
+            }
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_5d(sB + j * (GEMM_BK * 128), &p.map_b, &full[s], n0 + j * 64, g[0], pw * GEMM_BK + g[1],
-                          ph_ * p.pix_hmul + g[2], pb);
+              tma_load_5d(sB + j * (GEMM_BK * 128), m, &full[s], n0 + j * 64, g[0], pw * GEMM_BK + g[1], h, pb);
           }
         }
       }
@@ -195,8 +214,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;               // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
+    constexpr int CHUNKS = BN / 32;
+    constexpr int CH_LO = (CHUNKS + 1) / 2;
     const int r = q * 32 + lane;          // row inside the 128-row tile
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
@@ -233,7 +255,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const long long gofs = static_cast<long long>(tc.grp) * p.grp_c_stride;
       const int ncols_out = (p.epi & EPI_ROW_SHUFFLE) ? p.shuffle_cout : p.N;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * CH_LO; c < (half == 0 ? CH_LO : CHUNKS); ++c) {
         if (n0 + c * 32 >= p.N) break;   // warp-uniform
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
@@ -361,7 +383,7 @@ static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stre
   const int total = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
   const int grid = total < num_sms ? total : num_sms;
   if (grid <= 0) return cudaSuccess;
-  gemm_tcgen05_kernel<BN><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(p);
+  gemm_tcgen05_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -34,6 +34,13 @@ constexpr int GEMM_MAX_KTABLE = 128;
 struct GemmParams {
   CUtensorMap map_a;
   CUtensorMap map_b;
+  // Row-stripe domain parallelism: image rows above / below the local stripe live in separate one-row tensors
+  // (received from the neighbours). The image operand (A in OP_TABLE_5D, B in OP_PIXELS_5D) reads row -1 from
+  // map_halo_lo and row img_h from map_halo_hi when the corresponding flag is set; otherwise those rows are zero.
+  CUtensorMap map_halo_lo;
+  CUtensorMap map_halo_hi;
+  int halo_flags;              // bit 0: lo valid, bit 1: hi valid
+  int img_h;                   // rows of the local image
   int M, N, K;                 // logical output rows, cols, contraction length (elements)
   int num_m_tiles, num_n_tiles;
   int k_blocks;                // total 64-wide k-blocks

@@ -28,10 +28,14 @@ struct GemmEpilogue {
 // gemm_host.cu
 int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
               const GemmEpilogue& epi, int split_k, int bn_request, int num_sms, cudaStream_t stream);
+// halo_lo / halo_hi: optional one-row images [B, 1, W, Cin] holding the row above / below a row stripe
+// (null: rows outside the image are zero).
 int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin, int Cout, int stride,
-                     const GemmEpilogue& epi, int num_sms, cudaStream_t stream);
+                     const GemmEpilogue& epi, int num_sms, cudaStream_t stream, const void* halo_lo = nullptr,
+                     const void* halo_hi = nullptr);
 int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, int W, int Cin, int Cout, int stride,
-                       int split_k, void* status, int num_sms, cudaStream_t stream);
+                       int split_k, void* status, int num_sms, cudaStream_t stream, const void* halo_lo = nullptr,
+                       const void* halo_hi = nullptr);
 
 // elementwise.cu -------------------------------------------------------------------------------
 // LayerNorm over the last dimension (C <= 8192, C % 8 == 0), bf16 in/out, fp32 statistics.

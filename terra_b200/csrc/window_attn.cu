@@ -111,6 +111,12 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
       (reinterpret_cast<uintptr_t>(dbias_s + (BWD ? hpc * geo.nrel : 0)) + 15) & ~uintptr_t(15));  // [NPAD]
   int* rowslot = reinterpret_cast<int*>(rowofs + NPAD);                                      // [NPAD]
   int* rowreg = rowslot + NPAD;                                                              // [NPAD]
+  // cterm[t] = (t / ww) * (2 ww - 1) + (t % ww): the relative-position index of (query r, key c) is
+  // cterm[r] - cterm[c] + rel0, so the inner loops need no division. colinfo packs cterm (low 16 bits) with the
+  // token's mask region (high bits) for the current window.
+  int* cterm = rowreg + NPAD;                                                                // [NPAD]
+  int* colinfo = cterm + NPAD;                                                               // [NPAD]
+  const int rel0 = (a.wh - 1) * (2 * a.ww - 1) + (a.ww - 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
@@ -126,6 +132,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
     bias_s[i] = use_bias ? a.bias_table[r * a.num_heads + head0 + h] : 0.f;
     if (BWD) dbias_s[i] = 0.f;
   }
+  for (int t = tid; t < NPAD; t += WA_THREADS) cterm[t] = (t / a.ww) * (2 * a.ww - 1) + (t % a.ww);
 
   const int items = a.B * my_nw;
   for (int item = blockIdx.x; item < items; item += gridDim.x) {
@@ -139,36 +146,51 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
         rowofs[tid] = h.row;
         rowslot[tid] = h.slot;
         rowreg[tid] = h.region;
+        colinfo[tid] = cterm[tid] | (h.region << 16);
       } else {
         rowofs[tid] = -1;
         rowslot[tid] = 0;
         rowreg[tid] = 0;
+        colinfo[tid] = 0x7fff | (15 << 16);
       }
     }
     __syncthreads();
-    // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group, 16 bytes at a time
+    // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group, 16 bytes at a time, four loads
+    //      in flight per thread
     {
       const int vpr = G / 8;
       const int mats = BWD ? 4 : 3;
-      for (int i = tid; i < NPAD * mats * vpr; i += WA_THREADS) {
-        const int v = i % vpr;
-        const int m = (i / vpr) % mats;
-        const int r = i / (vpr * mats);
-        uint4 val = make_uint4(0, 0, 0, 0);
-        const bool is_q_like = (m == 0 || m == 3);
-        if (r < N && (!is_q_like || BWD || (r >= q0 && r < q1))) {
-          const long long ro = rowofs[r];
-          const int sl = rowslot[r];
-          if (m < 3) {
-            const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(a.qkv[sl]);
-            val = *reinterpret_cast<const uint4*>(base + ro * (3LL * a.C) + m * a.C + cg * G + v * 8);
-          } else {
-            const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(a.dout[sl]);
-            val = *reinterpret_cast<const uint4*>(base + ro * a.C + cg * G + v * 8);
+      const int total = NPAD * mats * vpr;
+      for (int base = tid; base < total; base += 4 * WA_THREADS) {
+        uint4 val[4];
+        __nv_bfloat16* dstp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = base + u * WA_THREADS;
+          val[u] = make_uint4(0, 0, 0, 0);
+          dstp[u] = nullptr;
+          if (i < total) {
+            const int v = i % vpr;
+            const int m = (i / vpr) % mats;
+            const int r = i / (vpr * mats);
+            const bool is_q_like = (m == 0 || m == 3);
+            if (r < N && (!is_q_like || BWD || (r >= q0 && r < q1))) {
+              const long long ro = rowofs[r];
+              const int sl = rowslot[r];
+              if (m < 3) {
+                const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(a.qkv[sl]);
+                val[u] = *reinterpret_cast<const uint4*>(bp + ro * (3LL * a.C) + m * a.C + cg * G + v * 8);
+              } else {
+                const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(a.dout[sl]);
+                val[u] = *reinterpret_cast<const uint4*>(bp + ro * a.C + cg * G + v * 8);
+              }
+            }
+            dstp[u] = (m == 0 ? Qs : (m == 1 ? Ks : (m == 2 ? Vs : dOs))) + r * stride + v * 8;
           }
         }
-        __nv_bfloat16* dst = (m == 0 ? Qs : (m == 1 ? Ks : (m == 2 ? Vs : dOs)));
-        *reinterpret_cast<uint4*>(dst + r * stride + v * 8) = val;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (dstp[u] != nullptr) *reinterpret_cast<uint4*>(dstp[u]) = val[u];
       }
     }
     __syncthreads();
@@ -202,21 +224,21 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
         const int r0 = rb * 16 + gq, r1 = r0 + 8;
         const int reg0 = rowreg[min(r0, NPAD - 1)], reg1 = rowreg[min(r1, NPAD - 1)];
         const int ti0 = r0 / a.ww, tj0 = r0 % a.ww, ti1 = r1 / a.ww, tj1 = r1 % a.ww;
+        const int rt0 = cterm[min(r0, NPAD - 1)] + rel0, rt1 = cterm[min(r1, NPAD - 1)] + rel0;
+        const bool bias0 = use_bias && r0 < N, bias1 = use_bias && r1 < N;
         float mx0 = -1e30f, mx1 = -1e30f;
 #pragma unroll
         for (int nb = 0; nb < NPAD / 8; ++nb) {
+          const int2 ci = *reinterpret_cast<const int2*>(colinfo + nb * 8 + tq * 2);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int col = nb * 8 + tq * 2 + (k & 1);
+            const int info = (k & 1) ? ci.y : ci.x;
             const bool lo = k < 2;
             float v = s[nb][k] * a.scale;
             if (col < N) {
-              const int ki = col / a.ww, kj = col % a.ww;
-              if (use_bias && (lo ? r0 : r1) < N) {
-                const int ti = lo ? ti0 : ti1, tj = lo ? tj0 : tj1;
-                v += bt[(ti - ki + a.wh - 1) * (2 * a.ww - 1) + (tj - kj + a.ww - 1)];
-              }
-              if (a.use_mask && rowreg[col] != (lo ? reg0 : reg1)) v += -100.f;
+              if (lo ? bias0 : bias1) v += bt[(lo ? rt0 : rt1) - (info & 0xffff)];
+              if (a.use_mask && (info >> 16) != (lo ? reg0 : reg1)) v += -100.f;
             } else {
               v = -1e30f;
             }
@@ -320,18 +342,6 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
             *reinterpret_cast<uint32_t*>(Ps + r1 * pstride + col) = pack_bf16x2(s[nb][2], s[nb][3]);
             *reinterpret_cast<uint32_t*>(dSs + r0 * pstride + col) = pack_bf16x2(ds[0], ds[1]);
             *reinterpret_cast<uint32_t*>(dSs + r1 * pstride + col) = pack_bf16x2(ds[2], ds[3]);
-            if (use_bias && a.dbias_table != nullptr) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const int c = col + (k & 1);
-                const int r = (k < 2) ? r0 : r1;
-                if (c < N && r < N && r >= q0 && r < q1) {
-                  const int ti = (k < 2) ? ti0 : ti1, tj = (k < 2) ? tj0 : tj1;
-                  atomicAdd(&dbias_s[hh * geo.nrel + (ti - c / a.ww + a.wh - 1) * (2 * a.ww - 1) + (tj - c % a.ww + a.ww - 1)],
-                            ds[k]);
-                }
-              }
-            }
             dp[nb][0] = ds[0]; dp[nb][1] = ds[1]; dp[nb][2] = ds[2]; dp[nb][3] = ds[3];
           }
           // dQ = scale * dS K
@@ -365,6 +375,22 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
       }
       if (BWD) {
         __syncthreads();
+        // bias gradient: entry e = (di, dj) collects dS[r][c] over the pairs with r - c = (di, dj); every thread
+        // owns whole entries, so no atomics are needed inside the CTA
+        if (use_bias && a.dbias_table != nullptr) {
+          const int span = 2 * a.ww - 1;
+          for (int e = tid; e < geo.nrel; e += WA_THREADS) {
+            const int di = e / span - (a.wh - 1), dj = e % span - (a.ww - 1);
+            float acc = 0.f;
+            for (int ti = max(0, di); ti < min(a.wh, a.wh + di); ++ti) {
+              for (int tj = max(0, dj); tj < min(a.ww, a.ww + dj); ++tj) {
+                const int r = ti * a.ww + tj;
+                if (r >= q0 && r < q1) acc += __bfloat162float(dSs[r * pstride + (ti - di) * a.ww + (tj - dj)]);
+              }
+            }
+            dbias_s[hh * geo.nrel + e] += acc;
+          }
+        }
         // =============================== phase 2: per 16-key block: dV = P^T dO, dK = scale * dS^T Q
         for (int kb = warp; kb < rblocks; kb += WA_WARPS) {
           if (kb * 16 >= N) continue;
@@ -461,7 +487,7 @@ size_t smem_bytes(int hpc, int nrel) {
   if (BWD) b += static_cast<size_t>(NPAD) * pstride * 2 * 2 + static_cast<size_t>(NPAD) * (HD + 8) * 2;
   b += static_cast<size_t>(hpc) * nrel * 4 * (BWD ? 2 : 1);
   b += 16;   // alignment slack before the row tables
-  b += NPAD * (8 + 4 + 4);
+  b += NPAD * (8 + 4 + 4 + 4 + 4);
   return b;
 }
 

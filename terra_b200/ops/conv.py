@@ -52,28 +52,25 @@ class _Conv3x3Fn(torch.autograd.Function):
         w16 = weight.bf16 if getattr(weight, "bf16", None) is not None else weight.detach().to(torch.bfloat16)
         b16 = bias.bf16 if getattr(bias, "bf16", None) is not None else bias.detach().to(torch.bfloat16)
         wp = pack_conv3x3_weight(w16)
-        if dom is None or dom.world == 1:
-            ext.conv3x3_fwd(x, wp, y, stride, F.EPI_BIAS, b16, None, status_word(x.device))
-        else:
-            dom.conv_fwd(x, wp, y, stride, b16)
+        multi = dom is not None and dom.world > 1
+        lo, hi = dom.exchange_rows(x) if multi else (None, None)
+        ext.conv3x3_fwd(x, wp, y, stride, F.EPI_BIAS, b16, None, status_word(x.device), lo, hi)
         ctx.save_for_backward(x)
-        ctx.p = (weight, bias, w16, stride, dom)
+        ctx.p = (weight, bias, w16, stride, dom, lo, hi)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         ext = _ext.load()
         (x,) = ctx.saved_tensors
-        weight, bias, w16, stride, dom = ctx.p
+        weight, bias, w16, stride, dom, lo, hi = ctx.p
+        multi = dom is not None and dom.world > 1
         dy = dy.contiguous()
         B, H, W, Cin = x.shape
         Cout = weight.shape[0]
-        # ---- weight / bias gradients (fp32, accumulated into the arena when there is one)
+        # ---- weight / bias gradients (fp32); the halo rows received in forward serve the boundary taps
         dw9 = torch.zeros(9, Cout, Cin, device=x.device, dtype=torch.float32)
-        if dom is None or dom.world == 1:
-            ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device))
-        else:
-            dom.conv_wgrad(x, dy, dw9, stride)
+        ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device), lo, hi)
         dw = dw9.view(3, 3, Cout, Cin).permute(2, 3, 0, 1)
         db = torch.zeros(Cout, device=x.device, dtype=torch.float32)
         ext.colsum(dy.view(-1, Cout), db)
@@ -83,10 +80,8 @@ class _Conv3x3Fn(torch.autograd.Function):
             if stride == 1:
                 dx = torch.empty_like(x)
                 wf = pack_conv3x3_weight_dgrad(w16)
-                if dom is None or dom.world == 1:
-                    ext.conv3x3_fwd(dy, wf, dx, 1, 0, None, None, status_word(x.device))
-                else:
-                    dom.conv_fwd(dy, wf, dx, 1, None)
+                glo, ghi = dom.exchange_rows(dy) if multi else (None, None)
+                ext.conv3x3_fwd(dy, wf, dx, 1, 0, None, None, status_word(x.device), glo, ghi)
             else:
                 dx = _conv3x3_s2_dgrad(dy, w16, H, W, dom)
         return dx, dw, db, None, None

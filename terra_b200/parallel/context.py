@@ -57,50 +57,13 @@ class DomainComm:
     def all_reduce_small(self, t):
         return C.all_reduce_(t.clone(), self.group)
 
-    def _pad_rows(self, x):
-        """NHWC [B,h,W,C] -> [B,h+2,W,C] with neighbour rows (zeros at the global edges)."""
-        xp = C._HaloRows.forward(_Ctx(), x.permute(0, 3, 1, 2), 1, self.prev, self.next, self.group)
-        return xp.permute(0, 2, 3, 1).contiguous()
-
-    def conv_fwd(self, x, wp, y, stride, bias16):
-        """3x3 convolution of a row stripe: neighbour rows are attached, the single-image kernel runs on the
-        taller tensor and the rows that belong to this rank are kept."""
-        from .. import _ext
-        from ..ops import _flags as F
-        from ..ops.gemm import status_word
-
-        ext = _ext.load()
-        xp = self._pad_rows(x)
-        Bn, h, W, _ = x.shape
-        flags = F.EPI_BIAS if bias16 is not None else 0
-        if stride == 1:
-            yp = torch.empty(Bn, h + 2, W, y.shape[3], device=x.device, dtype=torch.bfloat16)
-            ext.conv3x3_fwd(xp, wp, yp, 1, flags, bias16, None, status_word(x.device))
-            y.copy_(yp[:, 1:h + 1])
-        else:
-            # local output row j reads local rows 2j-1..2j+1 = rows 2j+1..2j+3 of T = [zero row, xp]:
-            # that is output row j+1 of the single-image kernel on T
-            T = torch.cat([xp.new_zeros(Bn, 1, W, xp.shape[3]), xp], dim=1)
-            yp = torch.empty(Bn, (T.shape[1] + 1) // 2, W // 2, y.shape[3], device=x.device, dtype=torch.bfloat16)
-            ext.conv3x3_fwd(T, wp, yp, 2, flags, bias16, None, status_word(x.device))
-            y.copy_(yp[:, 1:1 + y.shape[1]])
-
-    def conv_wgrad(self, x, dy, dw9, stride):
-        from .. import _ext
-        from ..ops.gemm import status_word
-
-        ext = _ext.load()
-        xp = self._pad_rows(x)
-        Bn, h, W, _ = x.shape
-        if stride == 1:
-            dyp = torch.zeros(Bn, h + 2, W, dy.shape[3], device=x.device, dtype=torch.bfloat16)
-            dyp[:, 1:h + 1] = dy
-            ext.conv3x3_wgrad(xp, dyp, dw9, 1, 8, status_word(x.device))
-        else:
-            T = torch.cat([xp.new_zeros(Bn, 1, W, xp.shape[3]), xp], dim=1)
-            dyp = torch.zeros(Bn, (T.shape[1] + 1) // 2, W // 2, dy.shape[3], device=x.device, dtype=torch.bfloat16)
-            dyp[:, 1:1 + dy.shape[1]] = dy
-            ext.conv3x3_wgrad(T, dyp, dw9, 2, 8, status_word(x.device))
+    def exchange_rows(self, x):
+        """Boundary rows of the neighbours' stripes: ``(row above, row below)`` as ``[B, 1, W, C]`` tensors, ``None``
+        at the global edges (the convolution then sees zeros there: non-periodic)."""
+        top = x[:, :1].contiguous()
+        bot = x[:, -1:].contiguous()
+        recv_prev, recv_next = C._exchange(top, bot, self.prev, self.next, self.group)
+        return recv_prev, recv_next
 
     def fold_halo_grad(self, dxp, H, W):
         """dxp: [B, H+2, W+2, C] gradient of the zero/halo padded input -> gradient of the local rows, with the
@@ -154,6 +117,14 @@ class ParallelContext:
         self.dom = DomainComm(m.window_parallel_group if m is not None else None,
                               m.window_parallel_ranks if m is not None else None, self.wp_rank)
         self.fused_comm = None     # peer-memory (NVLink) implementation, attached by terra_b200.parallel.nvlink
+        # stripe <-> window relayout is a local permutation when every rank's windows are exactly the windows of
+        # its own row stripe (no token sharding, no TP chunking)
+        self.local_relayout = self.world == 1
+        if self.world > 1 and self.sp == 1 and self.tp == 1 and self.nWh % self.world == 0:
+            per = (self.nWh // self.world) * self.nWw
+            self.local_relayout = all(
+                len(self.windows_of[g]) == per and self.windows_of[g][0] == g * per and self.windows_of[g][-1] == (g + 1) * per - 1
+                for g in range(self.n_wg))
 
     # ------------------------------------------------------------------ geometry
     def geometry(self, batch: int) -> WindowGeometry:
@@ -248,6 +219,9 @@ class ParallelContext:
     def stripe_to_windows(self, x):
         """NHWC row stripe ``[B, Ht/wp, Wt, C]`` -> this rank's window-major rows."""
         Bn, h, W, Cn = x.shape
+        if self.local_relayout and self.world > 1:
+            win = x.reshape(Bn, h // self.wh, self.wh, self.nWw, self.ww, Cn).permute(0, 1, 3, 2, 4, 5)
+            return win.reshape(-1, Cn).contiguous()
         if self.world == 1:
             full = x
         else:
@@ -269,9 +243,10 @@ class ParallelContext:
     def windows_to_stripe(self, rows, batch):
         """Inverse of ``stripe_to_windows``."""
         Cn = rows.shape[-1]
-        if self.world == 1:
-            win = rows.reshape(batch, self.nWh, self.nWw, self.wh, self.ww, Cn).permute(0, 1, 3, 2, 4, 5)
-            return win.reshape(batch, self.Ht, self.Wt, Cn).contiguous()
+        if self.local_relayout:
+            nh = self.nWh // self.world
+            win = rows.reshape(batch, nh, self.nWw, self.wh, self.ww, Cn).permute(0, 1, 3, 2, 4, 5)
+            return win.reshape(batch, nh * self.wh, self.Wt, Cn).contiguous()
         m = self.manager
         sizes, index = self._relayout_table(batch)
         allrows = C.all_gather_rows(rows.contiguous(), m.window_parallel_group, sizes)

@@ -34,6 +34,14 @@ def _symm():
     return symm_mem
 
 
+class _RawBytes:
+    """CUDA-array-interface view of ``nbytes`` at ``ptr``; keeps ``owner`` alive."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
 class SymmetricArena:
     """Bump allocator over one symmetric allocation shared (by layout) with the ranks of ``group``."""
 
@@ -75,7 +83,11 @@ class SymmetricArena:
             if start != (self.persistent_end + 255) // 256 * 256:
                 raise RuntimeError("persistent symmetric allocations must come before any per-step allocation")
             self.persistent_end = self.cursor
-        return self.buf[start:start + nbytes].view(dtype).view(*shape)
+        # A fresh alias of the bytes (own autograd version counter): tensors carved from one arena must not look
+        # like views of each other, or an in-place update of one (gradient accumulation) would invalidate another
+        # that autograd saved (the bf16 working copy).
+        raw = torch.as_tensor(_RawBytes(self.buf.data_ptr() + start, nbytes, self.buf), device=self.buf.device)
+        return raw.view(dtype).view(*shape)
 
     def reset(self) -> None:
         """Forget the per-step allocations (call between steps, when no kernel of the previous step is pending

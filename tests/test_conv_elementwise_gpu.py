@@ -40,7 +40,7 @@ def test_conv3x3_fwd(B, H, W, Cin, Cout, stride):
     bias = _rand(Cout)
     Ho, Wo = (H, W) if stride == 1 else ((H + 1) // 2, W // 2)
     y = torch.empty(B, Ho, Wo, Cout, device="cuda", dtype=torch.bfloat16)
-    ext.conv3x3_fwd(x, _pack_w(w), y, stride, F.EPI_BIAS, bias, None, status_word("cuda"))
+    ext.conv3x3_fwd(x, _pack_w(w), y, stride, F.EPI_BIAS, bias, None, status_word("cuda"), None, None)
     check_status("cuda")
     ref = TF.conv2d(x.float().permute(0, 3, 1, 2), w.float(), bias.float(), stride=stride, padding=1).permute(0, 2, 3, 1)
     _close(y, ref)
@@ -58,7 +58,7 @@ def test_conv3x3_wgrad(B, H, W, Cin, Cout, stride):
     Ho, Wo = (H, W) if stride == 1 else ((H + 1) // 2, W // 2)
     dy = _rand(B, Ho, Wo, Cout, scale=0.3)
     dw = torch.zeros(9, Cout, Cin, device="cuda", dtype=torch.float32)
-    ext.conv3x3_wgrad(x, dy, dw, stride, 16, status_word("cuda"))
+    ext.conv3x3_wgrad(x, dy, dw, stride, 16, status_word("cuda"), None, None)
     check_status("cuda")
     xr = x.float().permute(0, 3, 1, 2).requires_grad_(False)
     wr = torch.zeros(Cout, Cin, 3, 3, device="cuda", requires_grad=True)
@@ -164,3 +164,39 @@ def test_colsum_loss_adamw():
         ext.adamw_step(p, m, v, gr, pb, 1e-3, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
     assert (p - ref_p.detach()).abs().max().item() < 1e-5
     _close(pb, p, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_conv3x3_row_stripe_with_halo_rows(stride):
+    """A stripe of a taller image convolved with its neighbours' boundary rows passed separately must equal the
+    same rows of the whole-image convolution (forward and weight gradient)."""
+    from terra_b200 import _ext
+    from terra_b200.ops import _flags as F
+    from terra_b200.ops.gemm import status_word, check_status
+
+    torch.manual_seed(5)
+    ext = _ext.load()
+    B, H, W, Cin, Cout = 1, 24, 72, 64, 64
+    x = _rand(B, H, W, Cin, scale=0.5)
+    w = _rand(Cout, Cin, 3, 3, scale=0.05)
+    bias = _rand(Cout)
+    r0, r1 = 8, 16                                   # the middle stripe
+    xs = x[:, r0:r1].contiguous()
+    lo, hi = x[:, r0 - 1:r0].contiguous(), x[:, r1:r1 + 1].contiguous()
+    ho = (r1 - r0) // stride
+    y = torch.empty(B, ho, W // stride, Cout, device="cuda", dtype=torch.bfloat16)
+    ext.conv3x3_fwd(xs, _pack_w(w), y, stride, F.EPI_BIAS, bias, None, status_word("cuda"), lo, hi)
+    check_status("cuda")
+    xr = x.float().permute(0, 3, 1, 2)
+    ref = TF.conv2d(xr, w.float(), bias.float(), stride=stride, padding=1).permute(0, 2, 3, 1)
+    _close(y, ref[:, r0 // stride:r1 // stride])
+
+    dy_full = torch.zeros(B, H // stride, W // stride, Cout, device="cuda")
+    dy = _rand(B, ho, W // stride, Cout, scale=0.3)
+    dy_full[:, r0 // stride:r1 // stride] = dy.float()
+    dw = torch.zeros(9, Cout, Cin, device="cuda")
+    ext.conv3x3_wgrad(xs, dy, dw, stride, 4, status_word("cuda"), lo, hi)
+    check_status("cuda")
+    wr = torch.zeros(Cout, Cin, 3, 3, device="cuda", requires_grad=True)
+    TF.conv2d(xr, wr, None, stride=stride, padding=1).backward(dy_full.permute(0, 3, 1, 2))
+    _close(dw, wr.grad.permute(2, 3, 0, 1).reshape(9, Cout, Cin))
