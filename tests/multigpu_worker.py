@@ -28,12 +28,8 @@ def main():
         # every rank generates its own stripe of the same global field
         losses.append(t.step(t.synthetic_batch(sample=i % 2)))
     check_status(t.device)
-    # report the loss summed over the window-parallel ranks (each holds loss / wp)
-    total = torch.tensor(losses, device=t.device, dtype=torch.float64)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.all_reduce(total)
+    # Trainer.step already returns the loss reduced over the window-parallel group
+    total = torch.tensor(losses, dtype=torch.float64)
     if t.rank == 0:
         print("RESULT " + json.dumps({"losses": total.tolist(), "fused_attn": t.model.pctx.fused_comm is not None,
                                       "fused_opt": getattr(t.optimizer, "fused", None) is not None}), flush=True)
