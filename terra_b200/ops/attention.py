@@ -136,53 +136,56 @@ def window_attention_reference(qkv_all: torch.Tensor, geo: WindowGeometry, num_h
 
 
 class _WindowAttnFn(torch.autograd.Function):
-    """CUDA path. ``qkv`` is this rank's buffer; ``peers`` optionally lists raw device addresses of every peer
-    slot's qkv / out / dout / dqkv buffers (symmetric memory) - absent for a single rank."""
+    """CUDA path. Without ``comm`` this rank owns every window and token. With a fused ``comm`` the q/k/v rows are
+    staged in symmetric memory so that the kernels of the peer ranks can read them (and write outputs / gradients
+    into this rank's rows) directly."""
 
     @staticmethod
     def forward(ctx, qkv, bias_table, geo, num_heads, shifted, use_mask, scale, comm):
         ext = _ext.load()
         C = qkv.shape[-1] // 3
         sh, sw = geo.shift(shifted)
-        bias_f32 = None
-        if bias_table is not None:
-            bias_f32 = bias_table.detach().float().contiguous()
+        bias_f32 = bias_table.detach().float().contiguous() if bias_table is not None else None
         if comm is None:
             out = torch.empty(qkv.shape[0], C, dtype=torch.bfloat16, device=qkv.device)
             qkv_ptrs, out_ptrs = [qkv.data_ptr()], [out.data_ptr()]
         else:
-            out, qkv_ptrs, out_ptrs = comm.attn_forward_buffers(qkv, C)
+            staged = comm.alloc_qkv(qkv.shape[0], 3 * C)
+            staged.copy_(qkv)
+            qkv = staged
+            out, qkv_ptrs, out_ptrs = comm.attn_forward_buffers(qkv, C, shifted)
         ext.window_attn_fwd(qkv_ptrs, out_ptrs, bias_f32, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
                             geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh, geo.ww, sh, sw,
                             bool(use_mask and shifted), float(scale))
         if comm is not None:
-            out = comm.attn_forward_done(out)
+            out, qkv = comm.attn_forward_done(out, qkv, shifted)
         ctx.save_for_backward(qkv, bias_f32 if bias_f32 is not None else torch.empty(0, device=qkv.device))
         ctx.geo, ctx.num_heads, ctx.shifted, ctx.use_mask, ctx.scale, ctx.comm = geo, num_heads, shifted, use_mask, scale, comm
         ctx.has_bias = bias_table is not None
-        ctx.bias_param = bias_table
         return out
 
     @staticmethod
     def backward(ctx, dout):
         ext = _ext.load()
         qkv, bias_f32 = ctx.saved_tensors
-        geo = ctx.geo
+        geo, comm = ctx.geo, ctx.comm
         C = qkv.shape[-1] // 3
         sh, sw = geo.shift(ctx.shifted)
         dout = dout.contiguous()
         dbias = torch.zeros_like(bias_f32) if ctx.has_bias else None
-        if ctx.comm is None:
+        if comm is None:
             dqkv = torch.empty_like(qkv)
             qkv_ptrs, dout_ptrs, dqkv_ptrs = [qkv.data_ptr()], [dout.data_ptr()], [dqkv.data_ptr()]
         else:
-            dqkv, qkv_ptrs, dout_ptrs, dqkv_ptrs = ctx.comm.attn_backward_buffers(qkv, dout)
+            staged = comm.alloc_dout(dout.shape[0], C)
+            staged.copy_(dout)
+            dqkv, qkv_ptrs, dout_ptrs, dqkv_ptrs = comm.attn_backward_buffers(qkv, staged, ctx.shifted)
         ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32 if ctx.has_bias else None, dbias,
                             list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw,
                             C, ctx.num_heads, geo.wh, geo.ww, sh, sw, bool(ctx.use_mask and ctx.shifted),
                             float(ctx.scale))
-        if ctx.comm is not None:
-            dqkv = ctx.comm.attn_backward_done(dqkv)
+        if comm is not None:
+            dqkv = comm.attn_backward_done(dqkv, ctx.shifted)
         return dqkv, dbias, None, None, None, None, None, None
 
 
