@@ -95,17 +95,20 @@ class Trainer:
         self._slot ^= 1
         if self._slots[slot] is None or any(self._slots[slot][k].shape != v.shape for k, v in batch.items()):
             self._slots[slot] = {k: torch.empty(v.shape, dtype=v.dtype, device=self.device) for k, v in batch.items()}
-        dev = self._slots[slot]
+        dev = dict(self._slots[slot])
+        fence = -1
         for k, v in batch.items():
-            self._copy.upload(v, dev[k], False)
+            fence = self._copy.upload(v, dev[k], False)       # copies of one stream complete in order
+        dev["_fence"] = fence
         return dev
 
     def step(self, batch: Dict[str, torch.Tensor], staged=None) -> float:
         """One optimisation step. ``batch`` holds pinned host tensors (``staged`` = handle of an earlier ``stage``
         of the same batch, so that its upload overlapped the previous step). Returns the loss (device->host read)."""
-        dev = staged if staged is not None else self.stage(batch)
-        if self._copy is not None:
-            self._copy.wait_uploads()
+        dev = dict(staged if staged is not None else self.stage(batch))
+        fence = dev.pop("_fence", -1)
+        if self._copy is not None and fence >= 0:
+            self._copy.wait_upload(fence)                     # only this batch's copy, not the next one's
         _, loss, _, _ = one_step_train_production(
             self.task_type, self.model_type, self.model, self.engine, self.optimizer, dev, self.task_data, self.other,
             self.precision, self.cfg.get("half_model", False), None, self.loss_func, self.gscaler, self.manager,

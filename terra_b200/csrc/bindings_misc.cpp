@@ -25,12 +25,14 @@ class PyCopyEngine {
   }
   void wait(int64_t ticket) { TORCH_CHECK(eng_->wait(ticket, cur_stream()) == 0, "copy engine wait failed"); }
   void release(int64_t ticket) { eng_->release(ticket); }
-  void upload(const torch::Tensor& host, torch::Tensor& dst, bool wait) {
+  int64_t upload(const torch::Tensor& host, torch::Tensor& dst, bool wait) {
     TORCH_CHECK(!host.is_cuda() && host.is_pinned() && host.is_contiguous(), "upload: pinned contiguous host tensor");
     TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.nbytes() == host.nbytes(), "upload: matching CUDA tensor");
-    TORCH_CHECK(eng_->upload(host.data_ptr(), dst.data_ptr(), host.nbytes(), cur_stream(), wait) == 0,
-                "copy engine upload failed");
+    const int fence = eng_->upload(host.data_ptr(), dst.data_ptr(), host.nbytes(), cur_stream(), wait);
+    TORCH_CHECK(fence >= 0, "copy engine upload failed");
+    return fence;
   }
+  void wait_upload(int64_t fence) { TORCH_CHECK(eng_->wait_upload(static_cast<int>(fence), cur_stream()) == 0, "bad fence"); }
   void wait_uploads() { eng_->wait_uploads(cur_stream()); }
   int64_t d2h_stream() const { return reinterpret_cast<int64_t>(eng_->d2h_stream()); }
   int64_t h2d_stream() const { return reinterpret_cast<int64_t>(eng_->h2d_stream()); }
@@ -63,6 +65,7 @@ void bind_copy_engine(pybind11::module_& m) {
       .def("wait", &PyCopyEngine::wait)
       .def("release", &PyCopyEngine::release)
       .def("upload", &PyCopyEngine::upload)
+      .def("wait_upload", &PyCopyEngine::wait_upload)
       .def("wait_uploads", &PyCopyEngine::wait_uploads)
       .def("d2h_stream", &PyCopyEngine::d2h_stream)
       .def("h2d_stream", &PyCopyEngine::h2d_stream)

@@ -15,7 +15,7 @@ CopyEngine::CopyEngine(int device) : device_(device) {
   cudaSetDevice(device_);
   cudaStreamCreateWithFlags(&d2h_, cudaStreamNonBlocking);
   cudaStreamCreateWithFlags(&h2d_, cudaStreamNonBlocking);
-  cudaEventCreateWithFlags(&upload_done_, cudaEventDisableTiming);
+  for (auto& e : upload_fence_) cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
   cudaSetDevice(prev);
 }
 
@@ -31,7 +31,8 @@ CopyEngine::~CopyEngine() {
     if (s.last_read) cudaEventDestroy(s.last_read);
     if (s.host) cudaFreeHost(s.host);
   }
-  if (upload_done_) cudaEventDestroy(upload_done_);
+  for (auto& e : upload_fence_)
+    if (e) cudaEventDestroy(e);
   if (d2h_) cudaStreamDestroy(d2h_);
   if (h2d_) cudaStreamDestroy(h2d_);
 }
@@ -161,17 +162,26 @@ int CopyEngine::upload(const void* host_src, void* dev_dst, size_t bytes, cudaSt
     cudaGetLastError();
     return -2;
   }
-  cudaEventRecord(upload_done_, h2d_);
-  has_upload_ = true;
-  if (make_compute_wait) cudaStreamWaitEvent(compute_stream, upload_done_, 0);
+  const int fence = next_fence_;
+  next_fence_ = (next_fence_ + 1) % kUploadFences;
+  cudaEventRecord(upload_fence_[fence], h2d_);
+  last_fence_ = fence;
+  if (make_compute_wait) cudaStreamWaitEvent(compute_stream, upload_fence_[fence], 0);
   stats_.h2d_bytes += bytes;
   stats_.h2d_copies++;
+  return fence;
+}
+
+int CopyEngine::wait_upload(int fence, cudaStream_t compute_stream) {
+  std::lock_guard<std::mutex> lock(mu_);
+  if (fence < 0 || fence >= kUploadFences) return -1;
+  cudaStreamWaitEvent(compute_stream, upload_fence_[fence], 0);
   return 0;
 }
 
 int CopyEngine::wait_uploads(cudaStream_t compute_stream) {
   std::lock_guard<std::mutex> lock(mu_);
-  if (has_upload_) cudaStreamWaitEvent(compute_stream, upload_done_, 0);
+  if (last_fence_ >= 0) cudaStreamWaitEvent(compute_stream, upload_fence_[last_fence_], 0);
   return 0;
 }
 

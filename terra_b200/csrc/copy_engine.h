@@ -35,9 +35,11 @@ class CopyEngine {
   int wait(int64_t ticket, cudaStream_t compute_stream);
   // Drop a ticket; its slab returns to the pool (the next writer waits for the last reader).
   int release(int64_t ticket);
-  // Plain staged upload from caller-owned pinned memory (input pipeline).
+  // Plain staged upload from caller-owned pinned memory (input pipeline). Returns a fence id (>= 0) that
+  // wait_upload() makes a stream wait for, or a negative error code.
   int upload(const void* host_src, void* dev_dst, size_t bytes, cudaStream_t compute_stream, bool make_compute_wait);
-  int wait_uploads(cudaStream_t compute_stream);
+  int wait_upload(int fence, cudaStream_t compute_stream);
+  int wait_uploads(cudaStream_t compute_stream);   // the most recent upload
   // Pinned host buffers for callers (inputs, checkpoint staging).
   void* alloc_pinned(size_t bytes);
   void free_pinned(void* p);
@@ -67,8 +69,10 @@ class CopyEngine {
 
   int device_;
   cudaStream_t d2h_ = nullptr, h2d_ = nullptr;
-  cudaEvent_t upload_done_ = nullptr;
-  bool has_upload_ = false;
+  static constexpr int kUploadFences = 16;
+  cudaEvent_t upload_fence_[kUploadFences] = {nullptr};
+  int next_fence_ = 0;
+  int last_fence_ = -1;
   std::mutex mu_;
   std::vector<Slab> slabs_;
   std::unordered_map<int64_t, Ticket> tickets_;
