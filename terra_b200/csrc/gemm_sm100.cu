@@ -25,6 +25,10 @@
 
 namespace tb {
 
+// warp 0: TMA, warp 1: MMA, warps 2..17: epilogue (four per TMEM lane quadrant, interleaved over the 32-column chunks)
+constexpr int GEMM_EPI_WARPS = 16;
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
+
 template <int BN>
 struct GemmCfg {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
@@ -32,11 +36,9 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 6 : 8);
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+                                    GEMM_EPI_WARPS * 32 * 4 /*per-warp bias slots*/;
 };
-
-// warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per TMEM lane quadrant, each taking half of the columns)
-constexpr int GEMM_THREADS = 320;
 
 struct TileCoord {
   int grp, m_blk, n_blk, split;
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* bias_slots = reinterpret_cast<float*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -79,7 +82,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 8);
+      mbar_init(&tempty[a], GEMM_EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -216,9 +219,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;               // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
+    const int part = (warp - 2) >> 2;     // chunks part, part + 4, ... of the tile's 32-column chunks
     constexpr int CHUNKS = BN / 32;
-    constexpr int CH_LO = (CHUNKS + 1) / 2;
+    float* my_bias = bias_slots + (warp - 2) * 32;
+    const bool has_bias = (p.epi & EPI_BIAS) != 0;
     const int r = q * 32 + lane;          // row inside the 128-row tile
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
@@ -255,29 +259,40 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       const long long gofs = static_cast<long long>(tc.grp) * p.grp_c_stride;
       const int ncols_out = (p.epi & EPI_ROW_SHUFFLE) ? p.shuffle_cout : p.N;
 #pragma unroll 1
-      for (int c = half * CH_LO; c < (half == 0 ? CH_LO : CHUNKS); ++c) {
+      for (int c = part; c < CHUNKS; c += GEMM_EPI_WARPS / 4) {
         if (n0 + c * 32 >= p.N) break;   // warp-uniform
+        const int cb = col0 + c * 32;          // first output column of this chunk
+        const int nb = n0 + c * 32;            // first logical column (bias index)
+        if (has_bias) {
+          // one coalesced load per warp and chunk; the 32 values are then read back as broadcast float4
+          float b = 0.f;
+          if (nb + lane < p.N)
+            b = (p.epi & EPI_BIAS_F32) ? __ldg(static_cast<const float*>(p.bias) + nb + lane)
+                                       : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[nb + lane]);
+          __syncwarp();
+          my_bias[lane] = b;
+          __syncwarp();
+        }
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
         tmem_ld_wait();
         if (row >= 0) {
-          const int cb = col0 + c * 32;          // first output column of this chunk
-          const int nb = n0 + c * 32;            // first logical column (bias index)
           float f[32];
+          if (has_bias) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
-          if (p.epi & EPI_BIAS) {
-            if (p.epi & EPI_BIAS_F32) {
-              const float* b = static_cast<const float*>(p.bias);
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) f[j] += __ldg(b + nb + j);
-            } else {
-              const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias);
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) f[j] += __bfloat162float(b[nb + j]);
+            for (int j = 0; j < 32; j += 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(my_bias + j);
+              f[j] = fmaf(__uint_as_float(v[j]), p.alpha, b4.x);
+              f[j + 1] = fmaf(__uint_as_float(v[j + 1]), p.alpha, b4.y);
+              f[j + 2] = fmaf(__uint_as_float(v[j + 2]), p.alpha, b4.z);
+              f[j + 3] = fmaf(__uint_as_float(v[j + 3]), p.alpha, b4.w);
             }
+          } else if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
           }
           if (p.epi & EPI_SAVE_PRE) {
             __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.C2) + row * p.ldc2 + cb;

@@ -133,6 +133,20 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
     if (BWD) dbias_s[i] = 0.f;
   }
   for (int t = tid; t < NPAD; t += WA_THREADS) cterm[t] = (t / a.ww) * (2 * a.ww - 1) + (t % a.ww);
+  // Row-wise copies between global and shared memory: a warp takes whole rows, lane l moves the 16-byte vectors
+  // l and l + 32 of the row's (matrix, vector) list. The (matrix, vector) split is computed once here, so the
+  // copy loops contain no division.
+  const int vpr = G / 8;                       // 16-byte vectors per row and matrix
+  const int gather_mats = BWD ? 4 : 3;         // q, k, v [, dO]
+  int gm[2], gv[2];
+  bool gok[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int idx = lane + 32 * k;
+    gok[k] = idx < gather_mats * vpr;
+    gm[k] = gok[k] ? idx / vpr : 0;
+    gv[k] = gok[k] ? idx % vpr : 0;
+  }
 
   const int items = a.B * my_nw;
   for (int item = blockIdx.x; item < items; item += gridDim.x) {
@@ -155,42 +169,38 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
       }
     }
     __syncthreads();
-    // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group, 16 bytes at a time, four loads
-    //      in flight per thread
-    {
-      const int vpr = G / 8;
-      const int mats = BWD ? 4 : 3;
-      const int total = NPAD * mats * vpr;
-      for (int base = tid; base < total; base += 4 * WA_THREADS) {
-        uint4 val[4];
-        __nv_bfloat16* dstp[4];
+    // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group: four rows (up to eight 16-byte
+    //      loads) in flight per lane
+    for (int rbase = warp * 4; rbase < NPAD; rbase += WA_WARPS * 4) {
+      uint4 val[4][2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = base + u * WA_THREADS;
-          val[u] = make_uint4(0, 0, 0, 0);
-          dstp[u] = nullptr;
-          if (i < total) {
-            const int v = i % vpr;
-            const int m = (i / vpr) % mats;
-            const int r = i / (vpr * mats);
-            const bool is_q_like = (m == 0 || m == 3);
-            if (r < N && (!is_q_like || BWD || (r >= q0 && r < q1))) {
-              const long long ro = rowofs[r];
-              const int sl = rowslot[r];
-              if (m < 3) {
-                const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(a.qkv[sl]);
-                val[u] = *reinterpret_cast<const uint4*>(bp + ro * (3LL * a.C) + m * a.C + cg * G + v * 8);
-              } else {
-                const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(a.dout[sl]);
-                val[u] = *reinterpret_cast<const uint4*>(bp + ro * a.C + cg * G + v * 8);
-              }
-            }
-            dstp[u] = (m == 0 ? Qs : (m == 1 ? Ks : (m == 2 ? Vs : dOs))) + r * stride + v * 8;
+      for (int u = 0; u < 4; ++u) {
+        const int r = rbase + u;
+        const long long ro = rowofs[r];
+        const int sl = rowslot[r];
+        const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(a.qkv[sl]) + ro * (3LL * a.C) + cg * G;
+        const __nv_bfloat16* db = BWD ? static_cast<const __nv_bfloat16*>(a.dout[sl]) + ro * a.C + cg * G : nullptr;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          val[u][k] = make_uint4(0, 0, 0, 0);
+          const int m = gm[k];
+          const bool q_like = (m == 0 || m == 3);
+          if (gok[k] && r < N && (!q_like || BWD || (r >= q0 && r < q1))) {
+            val[u][k] = (m < 3) ? *reinterpret_cast<const uint4*>(qb + m * a.C + gv[k] * 8)
+                                : *reinterpret_cast<const uint4*>(db + gv[k] * 8);
           }
         }
+      }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (dstp[u] != nullptr) *reinterpret_cast<uint4*>(dstp[u]) = val[u];
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (gok[k]) {
+            const int m = gm[k];
+            __nv_bfloat16* dst = (m == 0 ? Qs : (m == 1 ? Ks : (m == 2 ? Vs : dOs)));
+            *reinterpret_cast<uint4*>(dst + (rbase + u) * stride + gv[k] * 8) = val[u][k];
+          }
+        }
       }
     }
     __syncthreads();
@@ -432,14 +442,15 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
           }
         }
         __syncthreads();
-        // flush dQ of this head to the tokens' home rows
+        // flush dQ of this head to the tokens' home rows (several rows per warp pass: HD/8 lanes per row)
         {
-          const int vpr = HD / 8;
-          for (int i = tid; i < (q1 - q0) * vpr; i += WA_THREADS) {
-            const int r = q0 + i / vpr, v = i % vpr;
+          constexpr int VH = HD / 8;                 // 16-byte vectors per row
+          constexpr int RPW = 32 / VH;               // rows per warp pass
+          const int lr = lane / VH, lv = lane % VH;
+          for (int r = q0 + warp * RPW + lr; r < q1; r += WA_WARPS * RPW) {
             __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.dqkv[rowslot[r]]);
-            *reinterpret_cast<uint4*>(base + rowofs[r] * (3LL * a.C) + cg * G + hh * HD + v * 8) =
-                *reinterpret_cast<const uint4*>(dQs + r * (HD + 8) + v * 8);
+            *reinterpret_cast<uint4*>(base + rowofs[r] * (3LL * a.C) + cg * G + hh * HD + lv * 8) =
+                *reinterpret_cast<const uint4*>(dQs + r * (HD + 8) + lv * 8);
           }
         }
         // the next head's phase 1 writes Ps/dSs/dQs again: wait for every reader
@@ -447,25 +458,21 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
       }
     }
     __syncthreads();
-    // ---- scatter results to the home rows
-    {
-      const int vpr = G / 8;
-      if (!BWD) {
-        for (int i = tid; i < (q1 - q0) * vpr; i += WA_THREADS) {
-          const int r = q0 + i / vpr, v = i % vpr;
-          __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.out[rowslot[r]]);
-          *reinterpret_cast<uint4*>(base + rowofs[r] * a.C + cg * G + v * 8) =
-              *reinterpret_cast<const uint4*>(Qs + r * stride + v * 8);
-        }
-      } else {
-        // With sequence parallelism every rank of the window recomputes the whole window (cheap) and keeps
-        // only the gradients of its own token shard, so no cross-rank reduction of dK/dV is needed.
-        for (int i = tid; i < (q1 - q0) * 2 * vpr; i += WA_THREADS) {
-          const int v = i % vpr;
-          const int m = (i / vpr) % 2;
-          const int r = q0 + i / (2 * vpr);
-          __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.dqkv[rowslot[r]]);
-          *reinterpret_cast<uint4*>(base + rowofs[r] * (3LL * a.C) + (1 + m) * a.C + cg * G + v * 8) =
+    // ---- scatter results to the home rows (a warp per row; lanes over the row's vectors)
+    if (!BWD) {
+      for (int r = q0 + warp; r < q1; r += WA_WARPS) {
+        __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.out[rowslot[r]]) + rowofs[r] * a.C + cg * G;
+        if (lane < vpr) *reinterpret_cast<uint4*>(base + lane * 8) = *reinterpret_cast<const uint4*>(Qs + r * stride + lane * 8);
+      }
+    } else {
+      // With sequence parallelism every rank of the window recomputes the whole window (cheap) and keeps only the
+      // gradients of its own token shard, so no cross-rank reduction of dK/dV is needed.
+      for (int r = q0 + warp; r < q1; r += WA_WARPS) {
+        __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.dqkv[rowslot[r]]) + rowofs[r] * (3LL * a.C) + cg * G;
+        if (lane < 2 * vpr) {
+          const int m = lane >= vpr ? 1 : 0;
+          const int v = lane - m * vpr;
+          *reinterpret_cast<uint4*>(base + (1 + m) * a.C + v * 8) =
               *reinterpret_cast<const uint4*>((m == 0 ? Ks : Vs) + r * stride + v * 8);
         }
       }
