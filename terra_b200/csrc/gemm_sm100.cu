@@ -2,13 +2,13 @@
 //
 //   D[M,N] (+)= A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory.
 //
-// Roles inside a 320-thread CTA (one CTA per SM, tiles assigned round-robin):
+// Roles inside a 576-thread CTA (one CTA per SM, tiles assigned round-robin):
 //   warp 0   one elected lane issues TMA loads (per-CTA, no cluster fan-out) into a ring of
 //            128-byte-swizzled shared-memory stages, signalling `full[s]` by transaction bytes;
 //   warp 1   owns the TMEM allocation; one elected lane issues tcgen05.mma (M=128, N=BN, K=16)
 //            and commits to `empty[s]` (stage reusable) and `tfull[a]` (accumulator a complete);
-//   warps 2-9 epilogue (two per 32-lane TMEM quadrant, half of the columns each): tcgen05.ld, fused bias / GELU / residual /
-//            GELU-gradient / pixel-shuffle / split-K atomics, 16-byte global stores.
+//   warps 2-17 epilogue (four per 32-lane TMEM quadrant, interleaved over the column chunks): tcgen05.ld, fused bias / GELU / residual /
+//            GELU-gradient / pixel-shuffle / split-K atomics; global transfers coalesced through shared memory.
 // Two accumulators (2*BN TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
 //
 // Operand addressing is data driven (see gemm_sm100.cuh) so that the same kernel serves
@@ -36,8 +36,11 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 6 : 8);
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ +
-                                    GEMM_EPI_WARPS * 32 * 4 /*per-warp bias slots*/;
+  // operand ring + barriers + per-warp bias slots + per-warp 2 KB exchange buffers of the epilogue
+  static constexpr int USED_BYTES = STAGES * STAGE_BYTES + 256 + GEMM_EPI_WARPS * 32 * 4 + GEMM_EPI_WARPS * 2048;
+  static constexpr int MAX_SMEM = 232448;   // 227 KB, the per-block limit of sm_100
+  static constexpr int SMEM_BYTES = (USED_BYTES + 1024 <= MAX_SMEM) ? USED_BYTES + 1024 : MAX_SMEM;   // + alignment slack
+  static_assert(USED_BYTES <= MAX_SMEM, "shared memory budget");
 };
 
 struct TileCoord {
@@ -71,6 +74,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* bias_slots = reinterpret_cast<float*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 256);
+  uint8_t* xchg = reinterpret_cast<uint8_t*>(bias_slots + GEMM_EPI_WARPS * 32);
+  // The ring needs a 1024-byte aligned base (128-byte swizzle atoms). The dynamic window normally starts aligned; if
+  // the alignment shift does not fit into the slack the launch is refused as a whole, before any barrier exists.
+  if (smem + Cfg::USED_BYTES > smem_raw + Cfg::SMEM_BYTES) {
+    if (threadIdx.x == 0) report_error(p.status, TB_ERR_BAD_ARG, 0x700u, blockIdx.x, 0u);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -217,14 +227,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // ------------------------------------------------------------------ epilogue (warps 2..17)
+    // tcgen05.ld hands lane l the 32 columns of accumulator row l. Global memory wants the opposite: neighbouring
+    // lanes on neighbouring addresses. Every transfer of a 32 x 32 chunk (output, saved pre-activation, residual,
+    // GELU input) therefore goes through the warp's 2 KB exchange buffer: row-per-lane on one side, four lanes per
+    // row (eight rows, 64 contiguous bytes each, per instruction) on the global side. 16-byte vectors are XOR
+    // swizzled by (row >> 1) so both access patterns are free of bank conflicts.
     const int q = warp & 3;               // TMEM lane quadrant this warp may read
     const int part = (warp - 2) >> 2;     // chunks part, part + 4, ... of the tile's 32-column chunks
     constexpr int CHUNKS = BN / 32;
     float* my_bias = bias_slots + (warp - 2) * 32;
+    uint8_t* my_x = xchg + (warp - 2) * 2048;
     const bool has_bias = (p.epi & EPI_BIAS) != 0;
-    const int r = q * 32 + lane;          // row inside the 128-row tile
+    const int grow = lane >> 2, gvec = lane & 3;      // global side: rows grow + 8 i, vector gvec
     uint32_t tcount = 0;
+    auto xaddr = [&](int rr, int vec) -> uint4* {
+      return reinterpret_cast<uint4*>(my_x + rr * 64 + (((vec ^ (rr >> 1)) & 3) << 4));
+    };
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const TileCoord tc = decode_tile(p, tile);
       const int acc = tcount & 1;
@@ -232,32 +251,66 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       if (!mbar_wait(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
       tc_fence_after();
       const int n0 = tc.n_blk * BN;
-      // ---- row -> output pixel/row index
-      long long row = -1;
+      // ---- tile row -> output row index (-1: outside the output)
       int col0 = n0;
-      if (p.epi & EPI_ROW_CONV) {
-        const int t0 = tc.m_blk % p.tile_n0;
-        const int t1 = (tc.m_blk / p.tile_n0) % p.tile_n1;
-        const int t2 = tc.m_blk / (p.tile_n0 * p.tile_n1);
-        const int w = t0 * GEMM_BM + r;
-        if (w < p.out_w) row = (static_cast<long long>(t2) * p.tile_n1 + t1) * p.out_w + w;
-      } else if (p.epi & EPI_ROW_SHUFFLE) {
-        const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;
-        if (g < p.M) {
+      if (p.epi & EPI_ROW_SHUFFLE) col0 = n0 % p.shuffle_cout;
+      auto out_row = [&](int r) -> long long {
+        if (p.epi & EPI_ROW_CONV) {
+          const int t0 = tc.m_blk % p.tile_n0;
+          const int t1 = (tc.m_blk / p.tile_n0) % p.tile_n1;
+          const int t2 = tc.m_blk / (p.tile_n0 * p.tile_n1);
+          const int w = t0 * GEMM_BM + r;
+          return (w < p.out_w) ? (static_cast<long long>(t2) * p.tile_n1 + t1) * p.out_w + w : -1;
+        } else if (p.epi & EPI_ROW_SHUFFLE) {
+          const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;
+          if (g >= p.M) return -1;
           const int w = static_cast<int>(g % p.out_w);
           const long long t = g / p.out_w;
           const int h = static_cast<int>(t % p.out_h);
           const long long b = t / p.out_h;
           const int qd = n0 / p.shuffle_cout;
-          row = ((b * 2 * p.out_h + 2 * h + (qd >> 1)) * 2 * p.out_w) + 2 * w + (qd & 1);
+          return ((b * 2 * p.out_h + 2 * h + (qd >> 1)) * 2 * p.out_w) + 2 * w + (qd & 1);
+        } else {
+          const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;
+          return (g < p.M) ? g : -1;
         }
-        col0 = n0 % p.shuffle_cout;
-      } else {
-        const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;
-        if (g < p.M) row = g;
-      }
+      };
+      long long grows[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) grows[i] = out_row(q * 32 + grow + 8 * i);
       const long long gofs = static_cast<long long>(tc.grp) * p.grp_c_stride;
       const int ncols_out = (p.epi & EPI_ROW_SHUFFLE) ? p.shuffle_cout : p.N;
+
+      // bf16 chunk from global memory into registers of the row-per-lane layout (zeros outside the output)
+      auto load_chunk = [&](const __nv_bfloat16* base, long long ld, int cb, uint4 (&u)[4]) {
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 t = make_uint4(0, 0, 0, 0);
+          if (grows[i] >= 0 && cb + gvec * 8 < ncols_out)
+            t = *reinterpret_cast<const uint4*>(base + grows[i] * ld + cb + gvec * 8);
+          *xaddr(grow + 8 * i, gvec) = t;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) u[j] = *xaddr(lane, j);
+      };
+      // 32 floats of the row-per-lane layout to bf16 global memory
+      auto store_chunk = [&](__nv_bfloat16* base, long long ld, int cb, const float (&f)[32]) {
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *xaddr(lane, j) = make_uint4(pack_bf16x2(f[8 * j], f[8 * j + 1]), pack_bf16x2(f[8 * j + 2], f[8 * j + 3]),
+                                       pack_bf16x2(f[8 * j + 4], f[8 * j + 5]), pack_bf16x2(f[8 * j + 6], f[8 * j + 7]));
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 t = *xaddr(grow + 8 * i, gvec);
+          if (grows[i] >= 0 && cb + gvec * 8 < ncols_out)
+            *reinterpret_cast<uint4*>(base + grows[i] * ld + cb + gvec * 8) = t;
+        }
+      };
+
 #pragma unroll 1
       for (int c = part; c < CHUNKS; c += GEMM_EPI_WARPS / 4) {
         if (n0 + c * 32 >= p.N) break;   // warp-uniform
@@ -276,93 +329,100 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
         tmem_ld_wait();
-        if (row >= 0) {
-          float f[32];
-          if (has_bias) {
+        float f[32];
+        if (has_bias) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float4 b4 = *reinterpret_cast<const float4*>(my_bias + j);
-              f[j] = fmaf(__uint_as_float(v[j]), p.alpha, b4.x);
-              f[j + 1] = fmaf(__uint_as_float(v[j + 1]), p.alpha, b4.y);
-              f[j + 2] = fmaf(__uint_as_float(v[j + 2]), p.alpha, b4.z);
-              f[j + 3] = fmaf(__uint_as_float(v[j + 3]), p.alpha, b4.w);
+          for (int j = 0; j < 32; j += 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(my_bias + j);
+            f[j] = fmaf(__uint_as_float(v[j]), p.alpha, b4.x);
+            f[j + 1] = fmaf(__uint_as_float(v[j + 1]), p.alpha, b4.y);
+            f[j + 2] = fmaf(__uint_as_float(v[j + 2]), p.alpha, b4.z);
+            f[j + 3] = fmaf(__uint_as_float(v[j + 3]), p.alpha, b4.w);
+          }
+        } else if (p.alpha != 1.0f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        }
+        if (p.epi & EPI_SAVE_PRE) store_chunk(static_cast<__nv_bfloat16*>(p.C2), p.ldc2, cb, f);
+        if (p.epi & EPI_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+        }
+        if (p.epi & EPI_MUL_DGELU) {
+          uint4 u[4];
+          load_chunk(p.aux, p.ldaux, cb, u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t w4[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 x = unpack_bf16x2(w4[k]);
+              f[8 * j + 2 * k] *= gelu_erf_grad(x.x);
+              f[8 * j + 2 * k + 1] *= gelu_erf_grad(x.y);
             }
-          } else if (p.alpha != 1.0f) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
           }
-          if (p.epi & EPI_SAVE_PRE) {
-            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.C2) + row * p.ldc2 + cb;
+        }
+        if (p.epi & EPI_RESIDUAL) {
+          uint4 u[4];
+          load_chunk(p.residual, p.ldr, cb, u);
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (cb + j < ncols_out) {
-                uint4 u = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
-                                     pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
-                *reinterpret_cast<uint4*>(o + j) = u;
-              }
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t w4[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 x = unpack_bf16x2(w4[k]);
+              f[8 * j + 2 * k] += x.x;
+              f[8 * j + 2 * k + 1] += x.y;
             }
           }
-          if (p.epi & EPI_GELU) {
+        }
+        if (p.epi & EPI_OUT_F32) {
+          // fp32 output: two passes of 16 columns through the exchange buffer (4 floats per 16-byte vector)
+          float* obase = static_cast<float*>(p.C) + gofs;
+          const bool vec_ok = ((reinterpret_cast<uintptr_t>(obase) & 15) == 0) && ((p.ldc & 3) == 0);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
-          }
-          if (p.epi & EPI_MUL_DGELU) {
-            const __nv_bfloat16* a = p.aux + row * p.ldaux + cb;
+          for (int hf = 0; hf < 2; ++hf) {
+            __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (cb + j < ncols_out) {
-                const uint4 u = *reinterpret_cast<const uint4*>(a + j);
-                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<float4*>(xaddr(lane, j)) =
+                  make_float4(f[16 * hf + 4 * j], f[16 * hf + 4 * j + 1], f[16 * hf + 4 * j + 2], f[16 * hf + 4 * j + 3]);
+            __syncwarp();
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const float2 x = unpack_bf16x2(w4[k]);
-                  f[j + 2 * k] *= gelu_erf_grad(x.x);
-                  f[j + 2 * k + 1] *= gelu_erf_grad(x.y);
+            for (int i = 0; i < 4; ++i) {
+              const float4 t = *reinterpret_cast<const float4*>(xaddr(grow + 8 * i, gvec));
+              const int col = cb + 16 * hf + gvec * 4;
+              if (grows[i] < 0 || col >= ncols_out) continue;
+              float* o = obase + grows[i] * p.ldc + col;
+              const bool full4 = vec_ok && col + 4 <= ncols_out;
+              if (p.epi & EPI_ATOMIC) {
+                if (full4) {
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(t.x), "f"(t.y), "f"(t.z),
+                               "f"(t.w)
+                               : "memory");
+                } else {
+                  const float tv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    if (col + e < ncols_out) atomicAdd(o + e, tv[e]);
+                }
+              } else {
+                if (full4) {
+                  *reinterpret_cast<float4*>(o) = t;
+                } else {
+                  const float tv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    if (col + e < ncols_out) o[e] = tv[e];
                 }
               }
             }
           }
-          if (p.epi & EPI_RESIDUAL) {
-            const __nv_bfloat16* a = p.residual + row * p.ldr + cb;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (cb + j < ncols_out) {
-                const uint4 u = *reinterpret_cast<const uint4*>(a + j);
-                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const float2 x = unpack_bf16x2(w4[k]);
-                  f[j + 2 * k] += x.x;
-                  f[j + 2 * k + 1] += x.y;
-                }
-              }
-            }
-          }
-          if (p.epi & EPI_OUT_F32) {
-            float* o = static_cast<float*>(p.C) + gofs + row * p.ldc + cb;
-            if (p.epi & EPI_ATOMIC) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (cb + j < ncols_out) atomicAdd(o + j, f[j]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                if (cb + j < ncols_out) *reinterpret_cast<float4*>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-            }
-          } else {
-            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.C) + gofs + row * p.ldc + cb;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (cb + j < ncols_out) {
-                uint4 u = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
-                                     pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
-                *reinterpret_cast<uint4*>(o + j) = u;
-              }
-            }
-          }
+        } else {
+          store_chunk(static_cast<__nv_bfloat16*>(p.C) + gofs, p.ldc, cb, f);
         }
       }
       tc_fence_before();
