@@ -1,4 +1,6 @@
 // Bindings for the memory-bound kernels and window attention.
+#include <stdexcept>
+#include <string>
 #include <torch/extension.h>
 #include <c10/cuda/CUDAStream.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -12,8 +14,13 @@ cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
 const void* opt_ptr(const c10::optional<torch::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 void* opt_mut(const c10::optional<torch::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 
-void need(bool ok, const char* what) { TORCH_CHECK(ok, "terra_b200: ", what); }
-void rc_check(int rc, const char* what) { TORCH_CHECK(rc == 0, "terra_b200: ", what, " failed with code ", rc); }
+// Plain std::runtime_error (pybind11 turns it into RuntimeError): no backtrace collection on the error path.
+void need(bool ok, const char* what) {
+  if (!ok) throw std::runtime_error(std::string("terra_b200: ") + what);
+}
+void rc_check(int rc, const char* what) {
+  if (rc != 0) throw std::runtime_error(std::string("terra_b200: ") + what + " failed with code " + std::to_string(rc));
+}
 
 void layernorm_fwd(const torch::Tensor& x, const torch::Tensor& g, const torch::Tensor& b, torch::Tensor& y,
                    torch::Tensor& mean, torch::Tensor& rstd, double eps) {

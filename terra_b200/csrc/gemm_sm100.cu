@@ -248,8 +248,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       const TileCoord tc = decode_tile(p, tile);
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
-      if (!mbar_wait(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
-      tc_fence_after();
       const int n0 = tc.n_blk * BN;
       // ---- tile row -> output row index (-1: outside the output)
       int col0 = n0;
@@ -275,22 +273,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           return (g < p.M) ? g : -1;
         }
       };
-      long long grows[4];
+      int grows[4];   // row indices fit 32 bits (element offsets may not)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) grows[i] = out_row(q * 32 + grow + 8 * i);
+      for (int i = 0; i < 4; ++i) grows[i] = static_cast<int>(out_row(q * 32 + grow + 8 * i));
       const long long gofs = static_cast<long long>(tc.grp) * p.grp_c_stride;
       const int ncols_out = (p.epi & EPI_ROW_SHUFFLE) ? p.shuffle_cout : p.N;
 
-      // bf16 chunk from global memory into registers of the row-per-lane layout (zeros outside the output)
-      auto load_chunk = [&](const __nv_bfloat16* base, long long ld, int cb, uint4 (&u)[4]) {
-        __syncwarp();
+      // bf16 chunk from global memory, global-side layout (zeros outside the output)
+      auto fetch_chunk = [&](const __nv_bfloat16* base, long long ld, int cb, uint4 (&t)[4]) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          uint4 t = make_uint4(0, 0, 0, 0);
+          t[i] = make_uint4(0, 0, 0, 0);
           if (grows[i] >= 0 && cb + gvec * 8 < ncols_out)
-            t = *reinterpret_cast<const uint4*>(base + grows[i] * ld + cb + gvec * 8);
-          *xaddr(grow + 8 * i, gvec) = t;
+            t[i] = *reinterpret_cast<const uint4*>(base + static_cast<long long>(grows[i]) * ld + cb + gvec * 8);
         }
+      };
+      // global-side registers -> row-per-lane registers
+      auto turn_chunk = [&](const uint4 (&t)[4], uint4 (&u)[4]) {
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) *xaddr(grow + 8 * i, gvec) = t[i];
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 4; ++j) u[j] = *xaddr(lane, j);
@@ -307,15 +309,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         for (int i = 0; i < 4; ++i) {
           const uint4 t = *xaddr(grow + 8 * i, gvec);
           if (grows[i] >= 0 && cb + gvec * 8 < ncols_out)
-            *reinterpret_cast<uint4*>(base + grows[i] * ld + cb + gvec * 8) = t;
+            *reinterpret_cast<uint4*>(base + static_cast<long long>(grows[i]) * ld + cb + gvec * 8) = t;
         }
       };
 
-#pragma unroll 1
-      for (int c = part; c < CHUNKS; c += GEMM_EPI_WARPS / 4) {
-        if (n0 + c * 32 >= p.N) break;   // warp-uniform
+      // The operand the epilogue reads (GELU input of the backward pass, or the residual) does not depend on the
+      // accumulator: pull it into L2 before waiting for the tile, so the DRAM latency hides behind the main loop;
+      // the chunk loop then fetches it (an L2 hit) under the latency of its tcgen05.ld.
+      constexpr int CPW = (CHUNKS + GEMM_EPI_WARPS / 4 - 1) / (GEMM_EPI_WARPS / 4);   // chunks per warp
+      const bool pre_aux = (p.epi & EPI_MUL_DGELU) != 0;
+      const bool pre_res = !pre_aux && (p.epi & EPI_RESIDUAL) != 0;
+      const __nv_bfloat16* pre_ptr = pre_aux ? p.aux : p.residual;
+      const long long pre_ld = pre_aux ? p.ldaux : p.ldr;
+      if (pre_aux || pre_res) {
+#pragma unroll
+        for (int ci = 0; ci < CPW; ++ci) {
+          const int c = part + ci * (GEMM_EPI_WARPS / 4);
+          if (c < CHUNKS && n0 + c * 32 < p.N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (grows[i] >= 0 && col0 + c * 32 + gvec * 8 < ncols_out)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pre_ptr + static_cast<long long>(grows[i]) * pre_ld + col0 + c * 32 + gvec * 8));
+          }
+        }
+      }
+      if (!mbar_wait(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
+      tc_fence_after();
+
+#pragma unroll
+      for (int ci = 0; ci < CPW; ++ci) {
+        const int c = part + ci * (GEMM_EPI_WARPS / 4);
+        if (c >= CHUNKS || n0 + c * 32 >= p.N) break;   // warp-uniform
         const int cb = col0 + c * 32;          // first output column of this chunk
         const int nb = n0 + c * 32;            // first logical column (bias index)
+        uint4 pre[4];
+        if (pre_aux || pre_res) fetch_chunk(pre_ptr, pre_ld, cb, pre);
         if (has_bias) {
           // one coalesced load per warp and chunk; the 32 values are then read back as broadcast float4
           float b = 0.f;
@@ -353,7 +381,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         }
         if (p.epi & EPI_MUL_DGELU) {
           uint4 u[4];
-          load_chunk(p.aux, p.ldaux, cb, u);
+          turn_chunk(pre, u);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint32_t w4[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
@@ -367,7 +395,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         }
         if (p.epi & EPI_RESIDUAL) {
           uint4 u[4];
-          load_chunk(p.residual, p.ldr, cb, u);
+          if (pre_res) {
+            turn_chunk(pre, u);
+          } else {
+            uint4 t[4];
+            fetch_chunk(p.residual, p.ldr, cb, t);
+            turn_chunk(t, u);
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint32_t w4[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
@@ -396,7 +430,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
               const float4 t = *reinterpret_cast<const float4*>(xaddr(grow + 8 * i, gvec));
               const int col = cb + 16 * hf + gvec * 4;
               if (grows[i] < 0 || col >= ncols_out) continue;
-              float* o = obase + grows[i] * p.ldc + col;
+              float* o = obase + static_cast<long long>(grows[i]) * p.ldc + col;
               const bool full4 = vec_ok && col + 4 <= ncols_out;
               if (p.epi & EPI_ATOMIC) {
                 if (full4) {

@@ -74,22 +74,34 @@ __device__ __forceinline__ Home locate(const WindowAttnArgs& a, const Geo& g, in
   return h;
 }
 
-// Shared-memory carve-up (bytes are computed identically on the host).
-template <int HD, int NPAD>
-struct Smem {
-  int G;        // channels per CTA (heads_per_cta * HD)
-  int stride;   // row stride in elements
-  __host__ __device__ Smem(int g) : G(g), stride(g + 8) {}
-  __host__ __device__ size_t tile_bytes() const { return static_cast<size_t>(NPAD) * stride * 2; }
-};
+__device__ __forceinline__ int region_of(const WindowAttnArgs& a, const Geo& g, int hs, int ws) {
+  int rh = 0, rw = 0;
+  if (a.sh > 0) rh = hs < g.Hg - a.wh ? 0 : (hs < g.Hg - a.sh ? 1 : 2);
+  if (a.sw > 0) rw = ws < g.Wg - a.ww ? 0 : (ws < g.Wg - a.sw ? 1 : 2);
+  return rh * 3 + rw;
+}
 
+constexpr float WA_LOG2E = 1.4426950408889634f;
+
+// Kernel layout.
+//   A CTA (4 warps) loops over (batch, window) items for one group of heads (G = heads_per_cta * HD channels).
+//   Per item: locate the window's tokens, gather Q/K/V [dO] rows into shared memory, then per head
+//     phase 1 (a warp per 16 query rows): S = Q K^T, P = softmax(scale S + bias [+ mask]) with the scores kept in the
+//       mma accumulator registers; forward: O = P V; backward: dP = dO V^T, dS = P (dP - rowsum(P dP)), dQ = dS K,
+//       P and dS stashed as bf16 for phase 2, bias gradient by shared-memory reductions;
+//     phase 2 (backward, a warp per 16 keys): dV = P^T dO, dK = dS^T Q;
+//   finally the results are scattered to the tokens' home rows.
+//   Softmax runs in the base-2 domain: the table is stored pre-multiplied by log2(e) and the scale carries the same
+//   factor, so an element costs one fused multiply-add, one table read, one max, one subtract and one ex2.
+//   Windows whose tokens share one mask region (all windows of unshifted layers, the interior windows of shifted
+//   ones) with N == NPAD take a branch-free path; the others a general one with the mask and padding tests.
 template <int HD, int NPAD, bool BWD>
-__global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_constant__ WindowAttnArgs a) {
+__global__ void __launch_bounds__(WA_THREADS, NPAD > 64 ? 1 : (BWD ? 3 : 5)) window_attn_kernel(const __grid_constant__ WindowAttnArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int hpc = a.heads_per_cta;
   const int G = hpc * HD;
   const int stride = G + 8;
-  const int pstride = NPAD + 8;
+  constexpr int pstride = NPAD + 8;
   Geo geo;
   geo.N = a.wh * a.ww;
   geo.nrel = (2 * a.wh - 1) * (2 * a.ww - 1);
@@ -101,21 +113,22 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
   __nv_bfloat16* Ks = Qs + NPAD * stride;
   __nv_bfloat16* Vs = Ks + NPAD * stride;
   __nv_bfloat16* dOs = Vs + NPAD * stride;                              // BWD only
-  __nv_bfloat16* Ps = dOs + (BWD ? NPAD * stride : 0);                  // BWD only [NPAD][pstride]
+  __nv_bfloat16* dQs = dOs + (BWD ? NPAD * stride : 0);                 // BWD only
+  __nv_bfloat16* Ps = dQs + (BWD ? NPAD * stride : 0);                  // BWD only [NPAD][pstride]
   __nv_bfloat16* dSs = Ps + (BWD ? NPAD * pstride : 0);                 // BWD only
-  __nv_bfloat16* dQs = dSs + (BWD ? NPAD * pstride : 0);                // BWD only [NPAD][HD+8]
-  float* bias_s = reinterpret_cast<float*>(dQs + (BWD ? NPAD * (HD + 8) : 0));   // [hpc][nrel]
-  float* dbias_s = bias_s + hpc * geo.nrel;                                         // BWD only [hpc][nrel]
+  float* bias_s = reinterpret_cast<float*>(dSs + (BWD ? NPAD * pstride : 0));   // [hpc][nrel], times log2(e)
+  float* dbias_s = bias_s + hpc * geo.nrel;                                      // BWD only [hpc][nrel]
   // the float tables have an arbitrary length: round up so that the 8-byte row offsets are aligned
   long long* rowofs = reinterpret_cast<long long*>(
       (reinterpret_cast<uintptr_t>(dbias_s + (BWD ? hpc * geo.nrel : 0)) + 15) & ~uintptr_t(15));  // [NPAD]
   int* rowslot = reinterpret_cast<int*>(rowofs + NPAD);                                      // [NPAD]
   int* rowreg = rowslot + NPAD;                                                              // [NPAD]
-  // cterm[t] = (t / ww) * (2 ww - 1) + (t % ww): the relative-position index of (query r, key c) is
-  // cterm[r] - cterm[c] + rel0, so the inner loops need no division. colinfo packs cterm (low 16 bits) with the
-  // token's mask region (high bits) for the current window.
-  int* cterm = rowreg + NPAD;                                                                // [NPAD]
-  int* colinfo = cterm + NPAD;                                                               // [NPAD]
+  // cofs[t] = 4 * ((t / ww) * (2 ww - 1) + (t % ww)): the byte offset into a head's table of the relative position
+  // of (query r, key c) is cofs[r] - cofs[c] + 4 * rel0, so the inner loops need no division.
+  int* cofs = rowreg + NPAD;                                                                 // [NPAD]
+  // bias gradient (BWD): posofs[tj * ww + cj] = tj * pstride + cj (low 16 bits) | tj << 16; one ww*ww fp32 scratch per warp
+  int* posofs = cofs + NPAD;                                                                 // [ww*ww]
+  float* mbuf = reinterpret_cast<float*>(posofs + (BWD ? a.ww * a.ww : 0));                  // [WA_WARPS][ww*ww]
   const int rel0 = (a.wh - 1) * (2 * a.ww - 1) + (a.ww - 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -123,16 +136,20 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
   const int cg = blockIdx.y;            // head group
   const int head0 = cg * hpc;
   const bool use_bias = a.bias_table != nullptr;
+  const bool bias_grad = BWD && use_bias && a.dbias_table != nullptr;
   const int my_nw = a.win_start[a.my_wg + 1] - a.win_start[a.my_wg];
   const int q0 = a.my_sp * a.shardN;
   const int q1 = min(N, q0 + a.shardN);
+  const float scale2 = a.scale * WA_LOG2E;
 
   for (int i = tid; i < hpc * geo.nrel; i += WA_THREADS) {
     const int h = i / geo.nrel, r = i % geo.nrel;
-    bias_s[i] = use_bias ? a.bias_table[r * a.num_heads + head0 + h] : 0.f;
+    bias_s[i] = use_bias ? a.bias_table[r * a.num_heads + head0 + h] * WA_LOG2E : 0.f;
     if (BWD) dbias_s[i] = 0.f;
   }
-  for (int t = tid; t < NPAD; t += WA_THREADS) cterm[t] = (t / a.ww) * (2 * a.ww - 1) + (t % a.ww);
+  for (int t = tid; t < NPAD; t += WA_THREADS) cofs[t] = 4 * ((t / a.ww) * (2 * a.ww - 1) + (t % a.ww));
+  if (BWD)
+    for (int t = tid; t < a.ww * a.ww; t += WA_THREADS) posofs[t] = ((t / a.ww) * pstride + (t % a.ww)) | ((t / a.ww) << 16);
   // Row-wise copies between global and shared memory: a warp takes whole rows, lane l moves the 16-byte vectors
   // l and l + 32 of the row's (matrix, vector) list. The (matrix, vector) split is computed once here, so the
   // copy loops contain no division.
@@ -154,21 +171,22 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
     const int flat = a.win_start[a.my_wg] + lw;
     const int ii = flat / a.nWw, jj = flat % a.nWw;
     __syncthreads();   // previous item fully consumed
+    int differs = 0;
     if (tid < NPAD) {
       if (tid < N) {
         const Home h = locate(a, geo, b, ii, jj, tid);
         rowofs[tid] = h.row;
         rowslot[tid] = h.slot;
         rowreg[tid] = h.region;
-        colinfo[tid] = cterm[tid] | (h.region << 16);
+        differs = h.region != region_of(a, geo, ii * a.wh, jj * a.ww);
       } else {
         rowofs[tid] = -1;
         rowslot[tid] = 0;
-        rowreg[tid] = 0;
-        colinfo[tid] = 0x7fff | (15 << 16);
+        rowreg[tid] = 15;
       }
     }
-    __syncthreads();
+    // (also the barrier that publishes the row tables)
+    const bool general = (__syncthreads_or(differs) != 0 && a.use_mask) || N != NPAD;
     // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group: four rows (up to eight 16-byte
     //      loads) in flight per lane
     for (int rbase = warp * 4; rbase < NPAD; rbase += WA_WARPS * 4) {
@@ -205,9 +223,9 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
     }
     __syncthreads();
 
-    const int rblocks = NPAD / 16;
+    constexpr int rblocks = NPAD / 16;
     for (int hh = 0; hh < hpc; ++hh) {
-      const float* bt = bias_s + hh * geo.nrel;
+      const char* btb = reinterpret_cast<const char*>(bias_s + hh * geo.nrel);
       // =============================== phase 1: per 16-query-row block
       for (int rb = warp; rb < rblocks; rb += WA_WARPS) {
         if (rb * 16 >= N) continue;
@@ -230,30 +248,42 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
             mma_bf16_16816(s[nb + 1], af, b1);
           }
         }
-        // scale, bias, mask, softmax (rows gq and gq+8 of the block)
+        // scale, bias, mask, softmax numerators (rows gq and gq+8 of the block), base-2 domain
         const int r0 = rb * 16 + gq, r1 = r0 + 8;
-        const int reg0 = rowreg[min(r0, NPAD - 1)], reg1 = rowreg[min(r1, NPAD - 1)];
-        const int ti0 = r0 / a.ww, tj0 = r0 % a.ww, ti1 = r1 / a.ww, tj1 = r1 % a.ww;
-        const int rt0 = cterm[min(r0, NPAD - 1)] + rel0, rt1 = cterm[min(r1, NPAD - 1)] + rel0;
-        const bool bias0 = use_bias && r0 < N, bias1 = use_bias && r1 < N;
+        const int ro0 = cofs[r0] + 4 * rel0, ro1 = cofs[r1] + 4 * rel0;   // r1 < NPAD always
         float mx0 = -1e30f, mx1 = -1e30f;
+        if (!general) {
 #pragma unroll
-        for (int nb = 0; nb < NPAD / 8; ++nb) {
-          const int2 ci = *reinterpret_cast<const int2*>(colinfo + nb * 8 + tq * 2);
+          for (int nb = 0; nb < NPAD / 8; ++nb) {
+            const int2 co = *reinterpret_cast<const int2*>(cofs + nb * 8 + tq * 2);
+            s[nb][0] = fmaf(s[nb][0], scale2, *reinterpret_cast<const float*>(btb + (ro0 - co.x)));
+            s[nb][1] = fmaf(s[nb][1], scale2, *reinterpret_cast<const float*>(btb + (ro0 - co.y)));
+            s[nb][2] = fmaf(s[nb][2], scale2, *reinterpret_cast<const float*>(btb + (ro1 - co.x)));
+            s[nb][3] = fmaf(s[nb][3], scale2, *reinterpret_cast<const float*>(btb + (ro1 - co.y)));
+            mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
+          }
+        } else {
+          const int reg0 = rowreg[r0], reg1 = rowreg[r1];
+          const bool row0 = r0 < N, row1 = r1 < N;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int col = nb * 8 + tq * 2 + (k & 1);
-            const int info = (k & 1) ? ci.y : ci.x;
-            const bool lo = k < 2;
-            float v = s[nb][k] * a.scale;
-            if (col < N) {
-              if (lo ? bias0 : bias1) v += bt[(lo ? rt0 : rt1) - (info & 0xffff)];
-              if (a.use_mask && (info >> 16) != (lo ? reg0 : reg1)) v += -100.f;
-            } else {
-              v = -1e30f;
+          for (int nb = 0; nb < NPAD / 8; ++nb) {
+            const int2 co = *reinterpret_cast<const int2*>(cofs + nb * 8 + tq * 2);
+            const int2 cr = *reinterpret_cast<const int2*>(rowreg + nb * 8 + tq * 2);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int col = nb * 8 + tq * 2 + (k & 1);
+              const bool lo = k < 2;
+              float v = s[nb][k] * scale2;
+              if (col < N) {
+                if (lo ? row0 : row1) v += *reinterpret_cast<const float*>(btb + ((lo ? ro0 : ro1) - ((k & 1) ? co.y : co.x)));
+                if (a.use_mask && ((k & 1) ? cr.y : cr.x) != (lo ? reg0 : reg1)) v += -100.f * WA_LOG2E;
+              } else {
+                v = -1e30f;
+              }
+              s[nb][k] = v;
+              if (lo) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
             }
-            s[nb][k] = v;
-            if (lo) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
           }
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -263,27 +293,21 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int nb = 0; nb < NPAD / 8; ++nb) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float e = __expf(s[nb][k] - (k < 2 ? mx0 : mx1));
-            s[nb][k] = e;
-            if (k < 2) sum0 += e; else sum1 += e;
-          }
+          s[nb][0] = exp2f(s[nb][0] - mx0);
+          s[nb][1] = exp2f(s[nb][1] - mx0);
+          s[nb][2] = exp2f(s[nb][2] - mx1);
+          s[nb][3] = exp2f(s[nb][3] - mx1);
+          sum0 += s[nb][0] + s[nb][1];
+          sum1 += s[nb][2] + s[nb][3];
         }
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
         sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
         sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
         const float inv0 = 1.f / sum0, inv1 = 1.f / sum1;
-#pragma unroll
-        for (int nb = 0; nb < NPAD / 8; ++nb) {
-          s[nb][0] *= inv0;
-          s[nb][1] *= inv0;
-          s[nb][2] *= inv1;
-          s[nb][3] *= inv1;
-        }
         if (!BWD) {
-          // O = P V, staged over this warp's own Q rows (no other warp reads them)
+          // O = P V with the numerators as P; the row normalisation is applied to the (much smaller) output.
+          // Staged over this warp's own Q rows (no other warp reads them).
           float o[HD / 8][4];
 #pragma unroll
           for (int nb = 0; nb < HD / 8; ++nb)
@@ -306,10 +330,19 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
           __syncwarp();
 #pragma unroll
           for (int nb = 0; nb < HD / 8; ++nb) {
-            *reinterpret_cast<uint32_t*>(Qs + r0 * stride + hh * HD + nb * 8 + tq * 2) = pack_bf16x2(o[nb][0], o[nb][1]);
-            *reinterpret_cast<uint32_t*>(Qs + r1 * stride + hh * HD + nb * 8 + tq * 2) = pack_bf16x2(o[nb][2], o[nb][3]);
+            *reinterpret_cast<uint32_t*>(Qs + r0 * stride + hh * HD + nb * 8 + tq * 2) =
+                pack_bf16x2(o[nb][0] * inv0, o[nb][1] * inv0);
+            *reinterpret_cast<uint32_t*>(Qs + r1 * stride + hh * HD + nb * 8 + tq * 2) =
+                pack_bf16x2(o[nb][2] * inv1, o[nb][3] * inv1);
           }
         } else {
+#pragma unroll
+          for (int nb = 0; nb < NPAD / 8; ++nb) {
+            s[nb][0] *= inv0;
+            s[nb][1] *= inv0;
+            s[nb][2] *= inv1;
+            s[nb][3] *= inv1;
+          }
           // dP = dO V^T
           float dp[NPAD / 8][4];
 #pragma unroll
@@ -339,7 +372,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
           d0 += __shfl_xor_sync(0xffffffffu, d0, 2);
           d1 += __shfl_xor_sync(0xffffffffu, d1, 1);
           d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
-          // dS = P * (dP - D); stash P and dS (bf16) for phase 2, accumulate the bias gradient
+          // dS = P * (dP - D); stash P and dS (bf16) for phase 2 and the bias gradient
 #pragma unroll
           for (int nb = 0; nb < NPAD / 8; ++nb) {
             float ds[4];
@@ -376,29 +409,45 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
           }
 #pragma unroll
           for (int nb = 0; nb < HD / 8; ++nb) {
-            *reinterpret_cast<uint32_t*>(dQs + r0 * (HD + 8) + nb * 8 + tq * 2) =
+            *reinterpret_cast<uint32_t*>(dQs + r0 * stride + hh * HD + nb * 8 + tq * 2) =
                 pack_bf16x2(dq[nb][0] * a.scale, dq[nb][1] * a.scale);
-            *reinterpret_cast<uint32_t*>(dQs + r1 * (HD + 8) + nb * 8 + tq * 2) =
+            *reinterpret_cast<uint32_t*>(dQs + r1 * stride + hh * HD + nb * 8 + tq * 2) =
                 pack_bf16x2(dq[nb][2] * a.scale, dq[nb][3] * a.scale);
           }
         }
       }
       if (BWD) {
         __syncthreads();
-        // bias gradient: entry e = (di, dj) collects dS[r][c] over the pairs with r - c = (di, dj); every thread
-        // owns whole entries, so no atomics are needed inside the CTA
-        if (use_bias && a.dbias_table != nullptr) {
-          const int span = 2 * a.ww - 1;
-          for (int e = tid; e < geo.nrel; e += WA_THREADS) {
-            const int di = e / span - (a.wh - 1), dj = e % span - (a.ww - 1);
-            float acc = 0.f;
-            for (int ti = max(0, di); ti < min(a.wh, a.wh + di); ++ti) {
-              for (int tj = max(0, dj); tj < min(a.ww, a.ww + dj); ++tj) {
+        // Bias gradient: entry (di, dj) of the table collects dS[r][c] over the pairs with r - c = (di, dj), for
+        // this rank's query rows. A warp takes the row displacements di, di + 4, ...: its lanes first add up, for
+        // each in-row position pair (tj, cj), the ww x ww blocks (ti, ci = ti - di) of dS (conflict-free reads,
+        // balanced over the warps), then lanes sum the diagonals tj - cj = dj of that small matrix. Every entry
+        // has one owner, so no atomics are needed inside the CTA.
+        if (bias_grad) {
+          const int ww2 = a.ww * a.ww, ndi = 2 * a.wh - 1, ndj = 2 * a.ww - 1;
+          const bool partial = q0 > 0 || q1 < N;
+          float* Mw = mbuf + warp * ww2;
+          for (int di_idx = warp; di_idx < ndi; di_idx += WA_WARPS) {
+            const int di = di_idx - (a.wh - 1);
+            const int ti_lo = max(0, di), ti_hi = min(a.wh, a.wh + di);
+            for (int pos = lane; pos < ww2; pos += 32) {
+              const int po = posofs[pos] & 0xffff, tj = posofs[pos] >> 16;
+              float acc = 0.f;
+              for (int ti = ti_lo; ti < ti_hi; ++ti) {
                 const int r = ti * a.ww + tj;
-                if (r >= q0 && r < q1) acc += __bfloat162float(dSs[r * pstride + (ti - di) * a.ww + (tj - dj)]);
+                if (!partial || (r >= q0 && r < q1))
+                  acc += __bfloat162float(dSs[ti * a.ww * pstride + (ti - di) * a.ww + po]);
               }
+              Mw[pos] = acc;
             }
-            dbias_s[hh * geo.nrel + e] += acc;
+            __syncwarp();
+            for (int dj_idx = lane; dj_idx < ndj; dj_idx += 32) {
+              const int dj = dj_idx - (a.ww - 1);
+              float acc = 0.f;
+              for (int tj = max(0, dj); tj < min(a.ww, a.ww + dj); ++tj) acc += Mw[tj * (a.ww + 1) - dj];
+              dbias_s[hh * geo.nrel + di_idx * ndj + dj_idx] += acc;
+            }
+            __syncwarp();
           }
         }
         // =============================== phase 2: per 16-key block: dV = P^T dO, dK = scale * dS^T Q
@@ -441,19 +490,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
             *reinterpret_cast<uint32_t*>(Vs + r1 * stride + c) = pack_bf16x2(dv[nb][2], dv[nb][3]);
           }
         }
-        __syncthreads();
-        // flush dQ of this head to the tokens' home rows (several rows per warp pass: HD/8 lanes per row)
-        {
-          constexpr int VH = HD / 8;                 // 16-byte vectors per row
-          constexpr int RPW = 32 / VH;               // rows per warp pass
-          const int lr = lane / VH, lv = lane % VH;
-          for (int r = q0 + warp * RPW + lr; r < q1; r += WA_WARPS * RPW) {
-            __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.dqkv[rowslot[r]]);
-            *reinterpret_cast<uint4*>(base + rowofs[r] * (3LL * a.C) + cg * G + hh * HD + lv * 8) =
-                *reinterpret_cast<const uint4*>(dQs + r * (HD + 8) + lv * 8);
-          }
-        }
-        // the next head's phase 1 writes Ps/dSs/dQs again: wait for every reader
+        // the next head's phase 1 writes Ps/dSs again: wait for every reader
         __syncthreads();
       }
     }
@@ -469,16 +506,17 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
       // gradients of its own token shard, so no cross-rank reduction of dK/dV is needed.
       for (int r = q0 + warp; r < q1; r += WA_WARPS) {
         __nv_bfloat16* base = static_cast<__nv_bfloat16*>(a.dqkv[rowslot[r]]) + rowofs[r] * (3LL * a.C) + cg * G;
-        if (lane < 2 * vpr) {
-          const int m = lane >= vpr ? 1 : 0;
-          const int v = lane - m * vpr;
-          *reinterpret_cast<uint4*>(base + (1 + m) * a.C + v * 8) =
-              *reinterpret_cast<const uint4*>((m == 0 ? Ks : Vs) + r * stride + v * 8);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int m = gm[k];
+          if (gok[k] && m < 3)
+            *reinterpret_cast<uint4*>(base + m * a.C + gv[k] * 8) =
+                *reinterpret_cast<const uint4*>((m == 0 ? dQs : (m == 1 ? Ks : Vs)) + r * stride + gv[k] * 8);
         }
       }
     }
   }
-  if (BWD && use_bias && a.dbias_table != nullptr) {
+  if (bias_grad) {
     __syncthreads();
     for (int i = tid; i < hpc * geo.nrel; i += WA_THREADS) {
       const int h = i / geo.nrel, r = i % geo.nrel;
@@ -488,38 +526,48 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_kernel(const __grid_co
 }
 
 template <int HD, int NPAD, bool BWD>
-size_t smem_bytes(int hpc, int nrel) {
+size_t smem_bytes(int hpc, int nrel, int ww) {
   const int G = hpc * HD, stride = G + 8, pstride = NPAD + 8;
-  size_t b = static_cast<size_t>(NPAD) * stride * 2 * (BWD ? 4 : 3);
-  if (BWD) b += static_cast<size_t>(NPAD) * pstride * 2 * 2 + static_cast<size_t>(NPAD) * (HD + 8) * 2;
+  size_t b = static_cast<size_t>(NPAD) * stride * 2 * (BWD ? 5 : 3);
+  if (BWD) b += static_cast<size_t>(NPAD) * pstride * 2 * 2;
   b += static_cast<size_t>(hpc) * nrel * 4 * (BWD ? 2 : 1);
   b += 16;   // alignment slack before the row tables
-  b += NPAD * (8 + 4 + 4 + 4 + 4);
+  b += NPAD * (8 + 4 + 4 + 4);
+  if (BWD) b += static_cast<size_t>(ww) * ww * 4 * (1 + WA_WARPS);
   return b;
 }
 
 template <int HD, int NPAD, bool BWD>
 int launch(WindowAttnArgs a, cudaStream_t stream) {
   const int nrel = (2 * a.wh - 1) * (2 * a.ww - 1);
-  // heads per CTA: as many as fit 128 channels and the shared-memory budget, dividing the head count
-  int hpc = 128 / HD;
+  // heads per CTA: 64 channels (128-byte row segments) keep the CTA small enough for several per SM
+  int hpc = 64 / HD;
   if (hpc < 1) hpc = 1;
-  while (hpc > 1 && (a.num_heads % hpc != 0 || smem_bytes<HD, NPAD, BWD>(hpc, nrel) > 200 * 1024)) --hpc;
-  const size_t sb = smem_bytes<HD, NPAD, BWD>(hpc, nrel);
+  while (hpc > 1 && (a.num_heads % hpc != 0 || smem_bytes<HD, NPAD, BWD>(hpc, nrel, a.ww) > 200 * 1024)) --hpc;
+  const size_t sb = smem_bytes<HD, NPAD, BWD>(hpc, nrel, a.ww);
   if (sb > 227 * 1024) return -20;
   a.heads_per_cta = hpc;
   static size_t configured = 0;
+  static int occupancy = 0;
   if (sb > configured) {
     if (cudaFuncSetAttribute(window_attn_kernel<HD, NPAD, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(sb)) != cudaSuccess)
       return -21;
     configured = sb;
+    occupancy = 0;
+  }
+  if (occupancy == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occupancy, window_attn_kernel<HD, NPAD, BWD>, WA_THREADS, sb) !=
+            cudaSuccess || occupancy < 1)
+      occupancy = 1;
   }
   const int my_nw = a.win_start[a.my_wg + 1] - a.win_start[a.my_wg];
   const int items = a.B * my_nw;
   if (items <= 0) return 0;
   const int groups = a.num_heads / hpc;
-  int gx = (148 * 4 + groups - 1) / groups;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int gx = (sms * occupancy + groups - 1) / groups;
   if (gx > items) gx = items;
   dim3 grid(gx, groups);
   window_attn_kernel<HD, NPAD, BWD><<<grid, WA_THREADS, sb, stream>>>(a);
