@@ -116,6 +116,17 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const __nv_bfloat16*
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
     const uint4* dr = reinterpret_cast<const uint4*>(dy + row * C);
     const float mu = mean[row], rs = rstd[row];
+    // all of the row's loads (x, dy and the residual-path gradient) are issued before the first use
+    uint4 xq[VPL], dq[VPL], rq[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        xq[i] = xr[vi];
+        dq[i] = dr[vi];
+        if (dres != nullptr) rq[i] = reinterpret_cast<const uint4*>(dres + row * C)[vi];
+      }
+    }
     float xh[VPL][8], dv[VPL][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -123,8 +134,8 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const __nv_bfloat16*
       const int vi = lane + i * 32;
       if (vi < nvec) {
         float xv[8], dyv[8];
-        unpack8(xr[vi], xv);
-        unpack8(dr[vi], dyv);
+        unpack8(xq[i], xv);
+        unpack8(dq[i], dyv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xv[j] - mu) * rs;
@@ -148,7 +159,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const __nv_bfloat16*
         for (int j = 0; j < 8; ++j) o[j] = rs * (dv[i][j] - s1 - xh[i][j] * s2);
         if (dres != nullptr) {
           float rr[8];
-          unpack8(reinterpret_cast<const uint4*>(dres + row * C)[vi], rr);
+          unpack8(rq[i], rr);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += rr[j];
         }
@@ -188,7 +199,22 @@ __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __rest
   const long long r0 = static_cast<long long>(blockIdx.x) * rows_per_block;
   const long long r1 = min(rows, r0 + rows_per_block);
   if (vi < nvec) {
-    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+    // four independent 16-byte loads in flight per thread
+    const long long step = blockDim.y;
+    long long r = r0 + threadIdx.y;
+    for (; r + 3 * step < r1; r += 4 * step) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(x + (r + u * step) * ld + vi * 8);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(q[u], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    }
+    for (; r < r1; r += step) {
       float f[8];
       unpack8(*reinterpret_cast<const uint4*>(x + r * ld + vi * 8), f);
 #pragma unroll

@@ -71,9 +71,10 @@ static int map_2d(CUtensorMap* out, const void* base, long long inner, long long
 }
 
 static int pick_bn(long long N, int requested) {
-  if (requested == 64 || requested == 128 || requested == 256) return requested;
+  if (requested == 64 || requested == 128 || requested == 192 || requested == 256) return requested;
   if (N <= 64) return 64;
   if (N % 256 == 0 && N >= 1024) return 256;
+  if (N % 192 == 0) return 192;   // 384, 768, 1152: no partial tile, less operand traffic per flop than 128
   return 128;
 }
 

@@ -34,8 +34,9 @@ struct GemmCfg {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 6 : 8);
-  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int STAGES = (BN >= 192) ? 4 : ((BN >= 128) ? 6 : 8);
+  // two accumulators; the allocation must be a power of two
+  static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   // operand ring + barriers + per-warp bias slots + per-warp 2 KB exchange buffers of the epilogue
   static constexpr int USED_BYTES = STAGES * STAGE_BYTES + 256 + GEMM_EPI_WARPS * 32 * 4 + GEMM_EPI_WARPS * 2048;
   static constexpr int MAX_SMEM = 232448;   // 227 KB, the per-block limit of sm_100
@@ -500,6 +501,7 @@ cudaError_t launch_gemm(const GemmParams& p, int bn, int num_sms, cudaStream_t s
   switch (bn) {
     case 64: return launch_bn<64>(p, num_sms, stream);
     case 128: return launch_bn<128>(p, num_sms, stream);
+    case 192: return launch_bn<192>(p, num_sms, stream);
     case 256: return launch_bn<256>(p, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }

@@ -40,6 +40,13 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
                : "r"(smem_u32(p)));
 }
 
+// 16-byte asynchronous copy global -> shared; `valid == false` writes zeros without reading the source.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 struct Geo {
   int N, nrel;
   int Hg, Wg;  // global token grid
@@ -187,40 +194,29 @@ __global__ void __launch_bounds__(WA_THREADS, NPAD > 64 ? 1 : (BWD ? 3 : 5)) win
     }
     // (also the barrier that publishes the row tables)
     const bool general = (__syncthreads_or(differs) != 0 && a.use_mask) || N != NPAD;
-    // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group: four rows (up to eight 16-byte
-    //      loads) in flight per lane
-    for (int rbase = warp * 4; rbase < NPAD; rbase += WA_WARPS * 4) {
-      uint4 val[4][2];
+    // ---- gather Q (query rows), K, V (all rows) [and dO] for this head group with 16-byte asynchronous copies
+    //      (global or peer memory -> shared memory, zero fill for rows outside the window / shard): all of a lane's
+    //      copies are in flight at once, one memory round trip per item
+    for (int r = warp; r < NPAD; r += WA_WARPS) {
+      const long long ro = rowofs[r];
+      const int sl = rowslot[r];
+      const bool in_win = r < N;
+      const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(a.qkv[sl]) + (in_win ? ro * (3LL * a.C) + cg * G : 0);
+      const __nv_bfloat16* db =
+          BWD ? static_cast<const __nv_bfloat16*>(a.dout[sl]) + (in_win ? ro * a.C + cg * G : 0) : nullptr;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = rbase + u;
-        const long long ro = rowofs[r];
-        const int sl = rowslot[r];
-        const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(a.qkv[sl]) + ro * (3LL * a.C) + cg * G;
-        const __nv_bfloat16* db = BWD ? static_cast<const __nv_bfloat16*>(a.dout[sl]) + ro * a.C + cg * G : nullptr;
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          val[u][k] = make_uint4(0, 0, 0, 0);
+      for (int k = 0; k < 2; ++k) {
+        if (gok[k]) {
           const int m = gm[k];
           const bool q_like = (m == 0 || m == 3);
-          if (gok[k] && r < N && (!q_like || BWD || (r >= q0 && r < q1))) {
-            val[u][k] = (m < 3) ? *reinterpret_cast<const uint4*>(qb + m * a.C + gv[k] * 8)
-                                : *reinterpret_cast<const uint4*>(db + gv[k] * 8);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          if (gok[k]) {
-            const int m = gm[k];
-            __nv_bfloat16* dst = (m == 0 ? Qs : (m == 1 ? Ks : (m == 2 ? Vs : dOs)));
-            *reinterpret_cast<uint4*>(dst + (rbase + u) * stride + gv[k] * 8) = val[u][k];
-          }
+          const bool valid = in_win && (!q_like || BWD || (r >= q0 && r < q1));
+          const __nv_bfloat16* src = (m < 3) ? qb + (valid ? m * a.C + gv[k] * 8 : 0) : db + (valid ? gv[k] * 8 : 0);
+          __nv_bfloat16* dst = (m == 0 ? Qs : (m == 1 ? Ks : (m == 2 ? Vs : dOs))) + r * stride + gv[k] * 8;
+          cp_async16(dst, src, valid);
         }
       }
     }
+    cp_async_wait_all();
     __syncthreads();
 
     constexpr int rblocks = NPAD / 16;

@@ -33,9 +33,10 @@ def _split_k_for(m_tiles_n_tiles: int, k_blocks: int, sms: int = 148) -> int:
 def wgrad_accumulate(dy: torch.Tensor, x: torch.Tensor, grad_w: torch.Tensor) -> None:
     """grad_w[N, K] (fp32) += dy[M, N]^T @ x[M, K]."""
     N, K = grad_w.shape
-    tiles = ((N + 127) // 128) * ((K + 127) // 128)
+    bn = 256 if (K % 256 == 0 and K >= 1024) else (192 if K % 192 == 0 else 128)
+    tiles = ((N + 127) // 128) * ((K + bn - 1) // bn)
     split = _split_k_for(tiles, (dy.shape[0] + 63) // 64)
-    gemm(dy, x, a_mn=True, b_mn=True, out=grad_w, accumulate=True, split_k=split, bn=128)
+    gemm(dy, x, a_mn=True, b_mn=True, out=grad_w, accumulate=True, split_k=split, bn=bn)
 
 
 def bias_grad_accumulate(dy: torch.Tensor, grad_b: torch.Tensor) -> None:

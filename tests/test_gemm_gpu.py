@@ -28,7 +28,7 @@ def test_gemm_kmajor(M, N, K):
     _close(c, a.float() @ b.float().t())
 
 
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 128, 192, 256])
 def test_gemm_tile_widths(bn):
     from terra_b200.ops.gemm import gemm, check_status
 
@@ -95,3 +95,22 @@ def test_gemm_large_matches_and_times():
     check_status("cuda")
     ref = a @ b.t()
     _close(c, ref, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("bn", [128, 192, 256])
+def test_gemm_mn_major_operands_tile_widths(bn):
+    """Input-gradient form (B read untransposed) and weight-gradient form (both operands MN-major, split-K fp32
+    accumulation) at every tile width."""
+    from terra_b200.ops.gemm import gemm, check_status
+
+    torch.manual_seed(7)
+    M, N, K = 1000, 384, 768
+    dy, w = _rand(M, K, scale=0.2), _rand(K, N, scale=0.05)      # dx[M, N] = dy[M, K] @ w[K, N]
+    dx = gemm(dy, w, b_mn=True, bn=bn)
+    check_status("cuda")
+    _close(dx, dy.float() @ w.float())
+    x = _rand(M, N, scale=0.2)
+    gw = torch.zeros(K, N, device="cuda")                        # gw[K, N] = dy^T x
+    gemm(dy, x, a_mn=True, b_mn=True, out=gw, accumulate=True, split_k=4, bn=bn)
+    check_status("cuda")
+    _close(gw, dy.float().t() @ x.float())
