@@ -121,6 +121,12 @@ void bind_comm(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_count", []() { return static_cast<int64_t>(tb::g_kernel_launches.load()); });
+  m.def("gemm_stall_counters", [](bool reset) {
+    unsigned long long v[8];
+    TORCH_CHECK(tb::gemm_stall_counters(v, reset ? 1 : 0) == 0, "gemm_stall_counters failed");
+    std::vector<int64_t> out(v, v + 8);
+    return out;
+  });
   m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogues");
   m.def("conv3x3_fwd", &conv3x3_fwd, "implicit-GEMM 3x3 convolution (NHWC bf16)");
   m.def("conv3x3_wgrad", &conv3x3_wgrad, "3x3 convolution weight gradient (fp32 atomics)");

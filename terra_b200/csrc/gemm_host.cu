@@ -10,6 +10,7 @@
 namespace tb {
 
 cudaError_t launch_gemm(const GemmParams& p, int bn, int num_sms, cudaStream_t stream);
+cudaError_t gemm_read_stalls(unsigned long long* out8, bool reset);
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -317,6 +318,10 @@ int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, i
   p.shuffle_cout = 1;
   cudaError_t e = launch_gemm(p, bn, num_sms, stream);
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
+
+int gemm_stall_counters(unsigned long long* out8, int reset) {
+  return gemm_read_stalls(out8, reset != 0) == cudaSuccess ? 0 : -1;
 }
 
 }  // namespace tb

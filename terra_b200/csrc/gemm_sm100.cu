@@ -2,12 +2,12 @@
 //
 //   D[M,N] (+)= A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory.
 //
-// Roles inside a 576-thread CTA (one CTA per SM, tiles assigned round-robin):
+// Roles inside a 448-thread CTA (one CTA per SM, tiles assigned round-robin):
 //   warp 0   one elected lane issues TMA loads (per-CTA, no cluster fan-out) into a ring of
 //            128-byte-swizzled shared-memory stages, signalling `full[s]` by transaction bytes;
 //   warp 1   owns the TMEM allocation; one elected lane issues tcgen05.mma (M=128, N=BN, K=16)
 //            and commits to `empty[s]` (stage reusable) and `tfull[a]` (accumulator a complete);
-//   warps 2-17 epilogue (four per 32-lane TMEM quadrant, interleaved over the column chunks): tcgen05.ld, fused bias / GELU / residual /
+//   warps 2-13 epilogue (three per 32-lane TMEM quadrant, interleaved over the column chunks): tcgen05.ld, fused bias / GELU / residual /
 //            GELU-gradient / pixel-shuffle / split-K atomics; global transfers coalesced through shared memory.
 // Two accumulators (2*BN TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
 //
@@ -25,8 +25,10 @@
 
 namespace tb {
 
-// warp 0: TMA, warp 1: MMA, warps 2..17: epilogue (four per TMEM lane quadrant, interleaved over the 32-column chunks)
-constexpr int GEMM_EPI_WARPS = 16;
+// warp 0: TMA, warp 1: MMA, warps 2..13: epilogue (three per TMEM lane quadrant, interleaved over the 32-column
+// chunks). 14 warps keep every scheduler at four warps or fewer, which allows 128 registers per thread: with 18 warps
+// the cap is 96 and the epilogue spills, and its reloads miss the small L1 left beside 227 KB of shared memory.
+constexpr int GEMM_EPI_WARPS = 12;
 constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 
 template <int BN>
@@ -43,6 +45,11 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = (USED_BYTES + 1024 <= MAX_SMEM) ? USED_BYTES + 1024 : MAX_SMEM;   // + alignment slack
   static_assert(USED_BYTES <= MAX_SMEM, "shared memory budget");
 };
+
+// Cycle counters of the three roles, summed over CTAs and launches since the last reset (read by gemm_read_stalls):
+// [0] MMA thread busy span, [1] of it waiting for a free accumulator, [2] waiting for operand stages,
+// [3] TMA thread span, [4] of it waiting for free stages, [5] first epilogue warp span, [6] of it waiting for tiles.
+__device__ unsigned long long g_gemm_stalls[8];
 
 struct TileCoord {
   int grp, m_blk, n_blk, split;
@@ -115,6 +122,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t it = 0;
+      const long long t_begin = clock64();
+      long long t_wait = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const TileCoord tc = decode_tile(p, tile);
         const int m0 = tc.m_blk * GEMM_BM;
@@ -130,7 +139,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1u;
+          const long long w0 = clock64();
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 0x100u + s)) break;
+          t_wait += clock64() - w0;
           uint8_t* sA = smem + s * Cfg::STAGE_BYTES;
           uint8_t* sB = sA + Cfg::A_BYTES;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
@@ -188,6 +199,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           }
         }
       }
+      atomicAdd(&g_gemm_stalls[3], static_cast<unsigned long long>(clock64() - t_begin));
+      atomicAdd(&g_gemm_stalls[4], static_cast<unsigned long long>(t_wait));
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -200,18 +213,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       const uint32_t a_kstep = a_mn ? (16 * 128) >> 4 : 32 >> 4;   // descriptor units of 16 bytes
       const uint32_t b_kstep = b_mn ? (16 * 128) >> 4 : 32 >> 4;
       uint32_t it = 0, tcount = 0;
+      const long long t_begin = clock64();
+      long long t_acc = 0, t_ops = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
         const TileCoord tc = decode_tile(p, tile);
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1u;
+        const long long w0 = clock64();
         if (!mbar_wait(&tempty[acc], aph ^ 1u, abort_flag, p.status, 0x200u + acc)) break;
+        t_acc += clock64() - w0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
         for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1u;
+          const long long w1 = clock64();
           if (!mbar_wait(&full[s], ph, abort_flag, p.status, 0x300u + s)) { ok = false; break; }
+          t_ops += clock64() - w1;
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + s * Cfg::STAGE_BYTES);
           const uint32_t sB = sA + Cfg::A_BYTES;
@@ -226,9 +245,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         if (!ok) break;
         umma_commit(&tfull[acc]);
       }
+      atomicAdd(&g_gemm_stalls[0], static_cast<unsigned long long>(clock64() - t_begin));
+      atomicAdd(&g_gemm_stalls[1], static_cast<unsigned long long>(t_acc));
+      atomicAdd(&g_gemm_stalls[2], static_cast<unsigned long long>(t_ops));
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..17)
+    // ------------------------------------------------------------------ epilogue (warps 2..13)
     // tcgen05.ld hands lane l the 32 columns of accumulator row l. Global memory wants the opposite: neighbouring
     // lanes on neighbouring addresses. Every transfer of a 32 x 32 chunk (output, saved pre-activation, residual,
     // GELU input) therefore goes through the warp's 2 KB exchange buffer: row-per-lane on one side, four lanes per
@@ -242,6 +264,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     const bool has_bias = (p.epi & EPI_BIAS) != 0;
     const int grow = lane >> 2, gvec = lane & 3;      // global side: rows grow + 8 i, vector gvec
     uint32_t tcount = 0;
+    const long long e_begin = clock64();
+    long long e_wait = 0;
     auto xaddr = [&](int rr, int vec) -> uint4* {
       return reinterpret_cast<uint4*>(my_x + rr * 64 + (((vec ^ (rr >> 1)) & 3) << 4));
     };
@@ -334,7 +358,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           }
         }
       }
+      const long long ew0 = clock64();
       if (!mbar_wait(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
+      e_wait += clock64() - ew0;
       tc_fence_after();
 
 #pragma unroll
@@ -464,6 +490,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
+    if (warp == 2 && lane == 0) {
+      atomicAdd(&g_gemm_stalls[5], static_cast<unsigned long long>(clock64() - e_begin));
+      atomicAdd(&g_gemm_stalls[6], static_cast<unsigned long long>(e_wait));
+    }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -495,6 +525,16 @@ static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stre
   if (grid <= 0) return cudaSuccess;
   gemm_tcgen05_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
   return cudaGetLastError();
+}
+
+cudaError_t gemm_read_stalls(unsigned long long* out8, bool reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out8, g_gemm_stalls, 8 * sizeof(unsigned long long));
+  if (e != cudaSuccess) return e;
+  if (reset) {
+    unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_gemm_stalls, zero, sizeof(zero));
+  }
+  return e;
 }
 
 cudaError_t launch_gemm(const GemmParams& p, int bn, int num_sms, cudaStream_t stream) {

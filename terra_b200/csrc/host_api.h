@@ -30,6 +30,11 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
               const GemmEpilogue& epi, int split_k, int bn_request, int num_sms, cudaStream_t stream);
 // halo_lo / halo_hi: optional one-row images [B, 1, W, Cin] holding the row above / below a row stripe
 // (null: rows outside the image are zero).
+// Cycle counters of the GEMM kernel's roles summed over CTAs and launches since the last reset:
+// [0] MMA span, [1] MMA waiting for an accumulator, [2] MMA waiting for operands, [3] TMA span, [4] TMA waiting for
+// free stages, [5] epilogue span, [6] epilogue waiting for tiles. Synchronises the device.
+int gemm_stall_counters(unsigned long long* out8, int reset);
+
 int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin, int Cout, int stride,
                      const GemmEpilogue& epi, int num_sms, cudaStream_t stream, const void* halo_lo = nullptr,
                      const void* halo_hi = nullptr);

@@ -219,13 +219,26 @@ def main(argv=None):
         check_status("cuda")
         print(json.dumps({"case": a.case, "launches": max(1, a.launches)}))
         return
+    ext = _ext.load()
     ms = time_kernel(fn, a.iters, 3, not a.no_flush)
     check_status("cuda")
+    stalls = None
+    if a.case == "gemm":
+        # share of each role's time spent waiting (cycle counters summed over CTAs), one extra launch
+        torch.cuda.synchronize()
+        ext.gemm_stall_counters(True)
+        fn()
+        torch.cuda.synchronize()
+        c = ext.gemm_stall_counters(True)
+        stalls = {"mma_wait_accumulator": c[1] / max(1, c[0]), "mma_wait_operands": c[2] / max(1, c[0]),
+                  "tma_wait_stage": c[4] / max(1, c[3]), "epilogue_wait_tile": c[6] / max(1, c[5])}
     pk = peaks()
     out = {"case": a.case, "args": {k: v for k, v in vars(a).items() if k not in ("case",)}, "ms": ms,
            "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6,
            "frac_of_" + pk["source"] + "_bf16": flops / ms / 1e9 / pk["bf16_tflops"],
            "frac_of_" + pk["source"] + "_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"]}
+    if stalls is not None:
+        out["wait_fractions"] = stalls
     print(json.dumps(out))
 
 
