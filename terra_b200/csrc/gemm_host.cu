@@ -9,7 +9,7 @@
 
 namespace tb {
 
-cudaError_t launch_gemm(const GemmParams& p, int bn, int num_sms, cudaStream_t stream);
+cudaError_t launch_gemm(const GemmParams& p, int bn, int ctas, int num_sms, cudaStream_t stream);
 cudaError_t gemm_read_stalls(unsigned long long* out8, bool reset);
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -98,11 +98,28 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
               const GemmEpilogue& epi, int split_k, int bn_request, int num_sms, cudaStream_t stream) {
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
+  // CTA pairs (256-row tiles, one MMA over two SMs): explicit request 1000 + BN, or by policy for the shapes where
+  // the main loop dominates (long contraction or wide output) when TERRA_GEMM_2CTA=1.
+  int ctas = 1;
+  if (bn_request >= 1000) {
+    ctas = 2;
+    bn_request -= 1000;
+    if (bn_request != 128 && bn_request != 256) return -11;
+  } else {
+    static const int policy = [] {
+      const char* e = std::getenv("TERRA_GEMM_2CTA");
+      return (e != nullptr) ? std::atoi(e) : 0;
+    }();
+    if (policy == 1 && M >= 512 && N >= 128 && (bn_request == 0 || bn_request == 128 || bn_request == 256)) {
+      ctas = 2;
+      if (bn_request == 0) bn_request = (N % 256 == 0 || N >= 1024) ? 256 : 128;
+    }
+  }
   const int bn = pick_bn(N, bn_request);
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
-  p.num_m_tiles = static_cast<int>((M + GEMM_BM - 1) / GEMM_BM);
+  p.num_m_tiles = static_cast<int>((M + GEMM_BM * ctas - 1) / (GEMM_BM * ctas));
   p.num_n_tiles = static_cast<int>((N + bn - 1) / bn);
   p.k_blocks = static_cast<int>((K + GEMM_BK - 1) / GEMM_BK);
   p.groups = 1;
@@ -121,7 +138,7 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
   else rc = map_2d(&p.map_a, A.ptr, K, M, A.ld, GEMM_BK, GEMM_BM);
   if (rc != 0) return rc;
   if (B.mn_major) rc = map_2d(&p.map_b, B.ptr, N, K, B.ld, 64, GEMM_BK);
-  else rc = map_2d(&p.map_b, B.ptr, K, N, B.ld, GEMM_BK, bn);
+  else rc = map_2d(&p.map_b, B.ptr, K, N, B.ld, GEMM_BK, bn / ctas);   // a CTA of a pair stages half of B's rows
   if (rc != 0) return rc - 1000;
   fill_epilogue(p, epi);
   p.tile_n0 = 1;
@@ -129,7 +146,7 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
   p.out_w = epi.out_w;
   p.out_h = epi.out_h;
   p.shuffle_cout = epi.shuffle_cout > 0 ? epi.shuffle_cout : 1;
-  cudaError_t e = launch_gemm(p, bn, num_sms, stream);
+  cudaError_t e = launch_gemm(p, bn, ctas, num_sms, stream);
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
@@ -232,7 +249,7 @@ int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin,
   p.out_w = Wo;
   p.out_h = Ho;
   p.shuffle_cout = 1;
-  cudaError_t e = launch_gemm(p, bn, num_sms, stream);
+  cudaError_t e = launch_gemm(p, bn, 1, num_sms, stream);
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
@@ -316,7 +333,7 @@ int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, i
   p.tile_n0 = 1;
   p.tile_n1 = 1;
   p.shuffle_cout = 1;
-  cudaError_t e = launch_gemm(p, bn, num_sms, stream);
+  cudaError_t e = launch_gemm(p, bn, 1, num_sms, stream);
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 

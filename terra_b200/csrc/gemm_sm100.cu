@@ -31,19 +31,27 @@ namespace tb {
 constexpr int GEMM_EPI_WARPS = 12;
 constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 
-template <int BN>
+// CTAS = 2: a cluster of two CTAs (two SMs of one TPC) computes a 256 x BN tile with one pair-wide MMA. Each CTA stages
+// its own 128 rows of A and its own half of B, so a k-block costs each SM (16 + BN / 8) KB of shared-memory fill instead
+// of (16 + BN / 4) KB: the operand traffic per flop through shared memory, which bounds the single-CTA main loop, drops
+// by a third at BN = 256.
+template <int BN, int CTAS>
 struct GemmCfg {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
-  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int B_ROWS = BN / CTAS;                 // rows of B staged by one CTA
+  static constexpr int B_BYTES = B_ROWS * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN >= 192) ? 4 : ((BN >= 128) ? 6 : 8);
+  // barriers + per-warp bias slots + per-warp 2 KB exchange buffers of the epilogue
+  static constexpr int FIXED_BYTES = 256 + GEMM_EPI_WARPS * 32 * 4 + GEMM_EPI_WARPS * 2048;
+  static constexpr int MAX_SMEM = 232448;   // 227 KB, the per-block limit of sm_100
+  static constexpr int FIT = (MAX_SMEM - FIXED_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = FIT > 8 ? 8 : FIT;
   // two accumulators; the allocation must be a power of two
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
-  // operand ring + barriers + per-warp bias slots + per-warp 2 KB exchange buffers of the epilogue
-  static constexpr int USED_BYTES = STAGES * STAGE_BYTES + 256 + GEMM_EPI_WARPS * 32 * 4 + GEMM_EPI_WARPS * 2048;
-  static constexpr int MAX_SMEM = 232448;   // 227 KB, the per-block limit of sm_100
+  static constexpr int USED_BYTES = STAGES * STAGE_BYTES + FIXED_BYTES;
   static constexpr int SMEM_BYTES = (USED_BYTES + 1024 <= MAX_SMEM) ? USED_BYTES + 1024 : MAX_SMEM;   // + alignment slack
-  static_assert(USED_BYTES <= MAX_SMEM, "shared memory budget");
+  static_assert(STAGES >= 3 && USED_BYTES <= MAX_SMEM, "shared memory budget");
+  static_assert(CTAS == 1 || (B_ROWS % 64 == 0), "a CTA's half of B must be whole 64-row boxes");
 };
 
 // Cycle counters of the three roles, summed over CTAs and launches since the last reset (read by gemm_read_stalls):
@@ -56,13 +64,14 @@ struct TileCoord {
   int kb_begin, kb_end;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile) {
+// p.num_m_tiles counts tiles of ctas * 128 rows; m_blk is returned in units of 128 rows for CTA `rank` of the pair.
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile, int ctas = 1, int rank = 0) {
   TileCoord t;
   t.split = tile % p.split_k;
   int r = tile / p.split_k;
   t.n_blk = r % p.num_n_tiles;
   r /= p.num_n_tiles;
-  t.m_blk = r % p.num_m_tiles;
+  t.m_blk = (r % p.num_m_tiles) * ctas + rank;
   t.grp = r / p.num_m_tiles;
   const int per = (p.k_blocks + p.split_k - 1) / p.split_k;
   t.kb_begin = t.split * per;
@@ -70,16 +79,18 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile) 
   return t;
 }
 
-template <int BN>
+template <int BN, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, CTAS>;
+  constexpr bool PAIR = CTAS == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
   uint64_t* empty = full + Cfg::STAGES;
   uint64_t* tfull = empty + Cfg::STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* pfull = tempty + 2;   // pair mode, leader CTA: "the peer's half of stage s has landed"
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull + Cfg::STAGES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* bias_slots = reinterpret_cast<float*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 256);
   uint8_t* xchg = reinterpret_cast<uint8_t*>(bias_slots + GEMM_EPI_WARPS * 32);
@@ -92,15 +103,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;     // 0 = leader (issues the MMAs)
+  const int unit = PAIR ? blockIdx.x >> 1 : blockIdx.x;                 // CTA or CTA pair
+  const int units = PAIR ? gridDim.x >> 1 : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      mbar_init(&pfull[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], GEMM_EPI_WARPS);
+      mbar_init(&tempty[a], GEMM_EPI_WARPS * CTAS);   // pair mode: both CTAs' epilogue warps release the leader's
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -108,13 +123,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     tma_prefetch_desc(&p.map_b);
   }
   if (warp == 1) {
-    tmem_alloc<Cfg::TMEM_COLS>(tmem_slot);
-    tmem_relinquish();
+    tmem_alloc<Cfg::TMEM_COLS, CTAS>(tmem_slot);
+    tmem_relinquish<CTAS>();
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();   // barriers and allocations of both CTAs exist from here on
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (PAIR) {
+    // the pair-wide MMA names one tensor-memory address for both CTAs: the two allocations must coincide
+    if (threadIdx.x == 0 && ld_shared_cluster_u32(map_to_cta(tmem_slot, rank ^ 1)) != tmem_base) {
+      *abort_flag = 1;
+      report_error(p.status, TB_ERR_BAD_ARG, 0x701u, tmem_base, 0u);
+    }
+    cluster_sync_all();
+    if (*abort_flag == 0 && ld_shared_cluster_u32(map_to_cta(const_cast<int*>(abort_flag), rank ^ 1)) != 0) *abort_flag = 1;
+    cluster_sync_all();
+  }
 
   const int total_tiles = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
 
@@ -124,10 +149,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       uint32_t it = 0;
       const long long t_begin = clock64();
       long long t_wait = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const TileCoord tc = decode_tile(p, tile);
+      for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units) {
+        const TileCoord tc = decode_tile(p, tile, CTAS, rank);
         const int m0 = tc.m_blk * GEMM_BM;
-        const int n0 = tc.n_blk * BN;
+        const int n0 = tc.n_blk * BN + rank * Cfg::B_ROWS;   // this CTA's rows of B
         int abase[5] = {0, 0, 0, 0, 0};
         if (p.a_mode == OP_TABLE_5D) {
           const int t0 = tc.m_blk % p.tile_n0;
@@ -140,7 +165,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1u;
           const long long w0 = clock64();
-          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 0x100u + s)) break;
+          if (!mbar_wait<PAIR>(&empty[s], ph ^ 1u, abort_flag, p.status, 0x100u + s)) break;
           t_wait += clock64() - w0;
           uint8_t* sA = smem + s * Cfg::STAGE_BYTES;
           uint8_t* sB = sA + Cfg::A_BYTES;
@@ -180,7 +205,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
             tma_load_2d(sB, &p.map_b, &full[s], kb * GEMM_BK, n0);
           } else if (p.b_mode == OP_MNMAJOR_2D) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
+            for (int j = 0; j < Cfg::B_ROWS / 64; ++j)
               tma_load_2d(sB + j * (GEMM_BK * 128), &p.map_b, &full[s], n0 + j * 64, kb * GEMM_BK);
           } else {  // OP_PIXELS_5D with per-group (tap) displacement
             const short* g = p.grp_off[tc.grp];
@@ -203,9 +228,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       atomicAdd(&g_gemm_stalls[4], static_cast<unsigned long long>(t_wait));
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mode == OP_MNMAJOR_2D || p.a_mode == OP_PIXELS_5D,
+    // ------------------------------------------------------------------ MMA issuer (leader CTA in pair mode)
+    if (rank == 0 && elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(GEMM_BM * CTAS, BN, p.a_mode == OP_MNMAJOR_2D || p.a_mode == OP_PIXELS_5D,
                                              p.b_mode == OP_MNMAJOR_2D || p.b_mode == OP_PIXELS_5D);
       const bool a_mn = (p.a_mode == OP_MNMAJOR_2D || p.a_mode == OP_PIXELS_5D);
       const bool b_mn = (p.b_mode == OP_MNMAJOR_2D || p.b_mode == OP_PIXELS_5D);
@@ -215,12 +240,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       uint32_t it = 0, tcount = 0;
       const long long t_begin = clock64();
       long long t_acc = 0, t_ops = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-        const TileCoord tc = decode_tile(p, tile);
+      for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units, ++tcount) {
+        const TileCoord tc = decode_tile(p, tile, CTAS, rank);
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1u;
         const long long w0 = clock64();
-        if (!mbar_wait(&tempty[acc], aph ^ 1u, abort_flag, p.status, 0x200u + acc)) break;
+        if (!mbar_wait<PAIR>(&tempty[acc], aph ^ 1u, abort_flag, p.status, 0x200u + acc)) break;
         t_acc += clock64() - w0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -229,7 +254,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1u;
           const long long w1 = clock64();
-          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 0x300u + s)) { ok = false; break; }
+          if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x300u + s)) { ok = false; break; }
+          if (PAIR && !mbar_wait<PAIR>(&pfull[s], ph, abort_flag, p.status, 0x380u + s)) { ok = false; break; }
           t_ops += clock64() - w1;
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -238,16 +264,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const uint64_t db = make_smem_desc(sB, b_lbo, 1024);
 #pragma unroll
           for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
-            umma_bf16(d_tmem, da + kk * a_kstep, db + kk * b_kstep, idesc, (kb > tc.kb_begin || kk > 0) ? 1u : 0u);
+            umma_bf16<CTAS>(d_tmem, da + kk * a_kstep, db + kk * b_kstep, idesc, (kb > tc.kb_begin || kk > 0) ? 1u : 0u);
           }
-          umma_commit(&empty[s]);
+          umma_commit<CTAS>(&empty[s]);     // frees stage s (in both CTAs of a pair)
         }
         if (!ok) break;
-        umma_commit(&tfull[acc]);
+        umma_commit<CTAS>(&tfull[acc]);     // accumulator complete (in both CTAs of a pair)
       }
       atomicAdd(&g_gemm_stalls[0], static_cast<unsigned long long>(clock64() - t_begin));
       atomicAdd(&g_gemm_stalls[1], static_cast<unsigned long long>(t_acc));
       atomicAdd(&g_gemm_stalls[2], static_cast<unsigned long long>(t_ops));
+    } else if (PAIR && rank == 1 && elect_one()) {
+      // Peer CTA: its MMA warp has nothing to issue. It forwards "my half of stage s has landed" to the leader, whose
+      // MMA thread waits for both halves before it issues.
+      uint32_t it = 0;
+      for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units) {
+        const TileCoord tc = decode_tile(p, tile, CTAS, rank);
+        bool ok = true;
+        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (it / Cfg::STAGES) & 1u;
+          if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x3c0u + s)) { ok = false; break; }
+          mbar_arrive_remote(map_to_cta(&pfull[s], 0));
+        }
+        if (!ok) break;
+      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..13)
@@ -269,8 +310,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     auto xaddr = [&](int rr, int vec) -> uint4* {
       return reinterpret_cast<uint4*>(my_x + rr * 64 + (((vec ^ (rr >> 1)) & 3) << 4));
     };
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
-      const TileCoord tc = decode_tile(p, tile);
+    for (int tile = unit; tile < total_tiles; tile += units, ++tcount) {
+      const TileCoord tc = decode_tile(p, tile, CTAS, rank);
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1u;
       const int n0 = tc.n_blk * BN;
@@ -359,7 +400,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         }
       }
       const long long ew0 = clock64();
-      if (!mbar_wait(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
+      if (!mbar_wait<PAIR>(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
       e_wait += clock64() - ew0;
       tc_fence_after();
 
@@ -488,7 +529,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (lane == 0) {
+        if (PAIR && rank == 1) mbar_arrive_remote(map_to_cta(&tempty[acc], 0));   // the leader's MMA thread waits
+        else mbar_arrive(&tempty[acc]);
+      }
     }
     if (warp == 2 && lane == 0) {
       atomicAdd(&g_gemm_stalls[5], static_cast<unsigned long long>(clock64() - e_begin));
@@ -502,29 +546,46 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   }
   tc_fence_before();
-  __syncthreads();
+  // pair mode: neither CTA may leave while the other can still signal its barriers or read its operands
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc<Cfg::TMEM_COLS>(tmem_base);
+    tmem_dealloc<Cfg::TMEM_COLS, CTAS>(tmem_base);
   }
 }
 
 // ------------------------------------------------------------------------------ host side
-template <int BN>
+template <int BN, int CTAS>
 static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, CTAS>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int total = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
-  const int grid = total < num_sms ? total : num_sms;
-  if (grid <= 0) return cudaSuccess;
-  gemm_tcgen05_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
-  return cudaGetLastError();
+  const int max_units = num_sms / CTAS;
+  const int units = total < max_units ? total : max_units;
+  if (units <= 0) return cudaSuccess;
+  if (CTAS == 1) {
+    gemm_tcgen05_kernel<BN, CTAS><<<units, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units * CTAS);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, CTAS>, p);
 }
 
 cudaError_t gemm_read_stalls(unsigned long long* out8, bool reset) {
@@ -537,12 +598,19 @@ cudaError_t gemm_read_stalls(unsigned long long* out8, bool reset) {
   return e;
 }
 
-cudaError_t launch_gemm(const GemmParams& p, int bn, int num_sms, cudaStream_t stream) {
+cudaError_t launch_gemm(const GemmParams& p, int bn, int ctas, int num_sms, cudaStream_t stream) {
+  if (ctas == 2) {
+    switch (bn) {
+      case 128: return launch_bn<128, 2>(p, num_sms, stream);
+      case 256: return launch_bn<256, 2>(p, num_sms, stream);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   switch (bn) {
-    case 64: return launch_bn<64>(p, num_sms, stream);
-    case 128: return launch_bn<128>(p, num_sms, stream);
-    case 192: return launch_bn<192>(p, num_sms, stream);
-    case 256: return launch_bn<256>(p, num_sms, stream);
+    case 64: return launch_bn<64, 1>(p, num_sms, stream);
+    case 128: return launch_bn<128, 1>(p, num_sms, stream);
+    case 192: return launch_bn<192, 1>(p, num_sms, stream);
+    case 256: return launch_bn<256, 1>(p, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

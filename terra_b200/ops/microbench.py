@@ -72,15 +72,22 @@ def case_gemm(a):
         out = torch.zeros(N, K, device="cuda")
         tiles = ((N + 127) // 128) * ((K + 127) // 128)
         split = max(1, min((M + 63) // 64, 148 // max(1, tiles)))
-        fn = lambda: gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, split_k=split, bn=128)
+        bn = a.bn if a.bn else 128
+        width = bn % 1000
+        rows = 256 if bn >= 1000 else 128
+        tiles = ((N + rows - 1) // rows) * ((K + width - 1) // width)
+        units = 74 if bn >= 1000 else 148
+        split = max(1, min((M + 63) // 64, units // max(1, tiles)))
+        fn = lambda: gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, split_k=split, bn=bn)
         nbytes = (M * N + M * K) * 2 + N * K * 4
     else:
-        x, w = _rand(M, K), _rand(N, K, scale=0.05)
+        x = _rand(M, K)
+        w = _rand(K, N, scale=0.05) if a.b_mn else _rand(N, K, scale=0.05)
         bias = _rand(N)
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         res = _rand(M, N) if a.epilogue in ("residual",) else None
         aux = _rand(M, N) if a.epilogue == "dgelu" else None
-        kw = dict(out=out, bn=a.bn)
+        kw = dict(out=out, bn=a.bn, b_mn=a.b_mn)
         if a.epilogue in ("bias", "gelu", "residual"):
             kw["bias"] = bias
         if a.epilogue == "gelu":
@@ -193,7 +200,8 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=1536)
     ap.add_argument("--k", type=int, default=384)
     ap.add_argument("--c", type=int, default=384)
-    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--bn", type=int, default=0, help="tile width; 1000 + width selects CTA-pair mode")
+    ap.add_argument("--b-mn", action="store_true", help="B given as [K, N] (input-gradient form)")
     ap.add_argument("--epilogue", default="none", choices=["none", "bias", "gelu", "residual", "dgelu", "wgrad"])
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--ws", type=int, default=8)

@@ -114,3 +114,34 @@ def test_gemm_mn_major_operands_tile_widths(bn):
     gemm(dy, x, a_mn=True, b_mn=True, out=gw, accumulate=True, split_k=4, bn=bn)
     check_status("cuda")
     _close(gw, dy.float().t() @ x.float())
+
+
+@pytest.mark.parametrize("bn", [1128, 1256])
+def test_gemm_cta_pair(bn):
+    """Pair mode (a cluster of two CTAs drives one 256-row MMA): forward, input-gradient and weight-gradient forms and
+    the fused epilogues, with M not a multiple of 256 and N not a multiple of the tile width."""
+    from terra_b200.ops.gemm import gemm, check_status
+
+    torch.manual_seed(11)
+    M, N, K = 1000, 640, 448
+    a, w = _rand(M, K, scale=0.3), _rand(N, K, scale=0.05)
+    bias, res = _rand(N), _rand(M, N)
+    c = gemm(a, w, bn=bn)
+    check_status("cuda")
+    _close(c, a.float() @ w.float().t())
+    c = gemm(a, w, bias=bias, residual=res, bn=bn)
+    check_status("cuda")
+    _close(c, a.float() @ w.float().t() + bias.float() + res.float())
+    act, pre = gemm(a, w, bias=bias, gelu=True, save_pre=True, bn=bn)
+    check_status("cuda")
+    ref = a.float() @ w.float().t() + bias.float()
+    _close(pre, ref)
+    _close(act, torch.nn.functional.gelu(ref))
+    dy = _rand(M, N, scale=0.2)
+    dx = gemm(dy, w, b_mn=True, bn=bn)                      # dx[M, K] = dy[M, N] @ w[N, K]
+    check_status("cuda")
+    _close(dx, dy.float() @ w.float())
+    gw = torch.zeros(N, K, device="cuda")
+    gemm(dy, a, a_mn=True, b_mn=True, out=gw, accumulate=True, split_k=3, bn=bn)
+    check_status("cuda")
+    _close(gw, dy.float().t() @ a.float())
