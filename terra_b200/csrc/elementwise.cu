@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const __nv_bfloat16*
 }
 
 template <int VPL>
-__global__ void __launch_bounds__(256) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+__global__ void __launch_bounds__(256, (VPL <= 2) ? 2 : 1) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                             const __nv_bfloat16* __restrict__ x,
                                                             const __nv_bfloat16* __restrict__ gamma,
                                                             const float* __restrict__ mean, const float* __restrict__ rstd,

@@ -47,6 +47,13 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// 32-bit shared-memory load by address (keeps the table lookups of the softmax on LDS with one integer add each).
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));   // the table is read-only inside the item loop
+  return v;
+}
+
 struct Geo {
   int N, nrel;
   int Hg, Wg;  // global token grid
@@ -126,8 +133,10 @@ __global__ void __launch_bounds__(WA_THREADS, NPAD > 64 ? 1 : (BWD ? 3 : 5)) win
   float* bias_s = reinterpret_cast<float*>(dSs + (BWD ? NPAD * pstride : 0));   // [hpc][nrel], times log2(e)
   float* dbias_s = bias_s + hpc * geo.nrel;                                      // BWD only [hpc][nrel]
   // the float tables have an arbitrary length: round up so that the 8-byte row offsets are aligned
-  long long* rowofs = reinterpret_cast<long long*>(
-      (reinterpret_cast<uintptr_t>(dbias_s + (BWD ? hpc * geo.nrel : 0)) + 15) & ~uintptr_t(15));  // [NPAD]
+  // (offset arithmetic on the shared array itself, so the compiler keeps these accesses in the shared state space)
+  const size_t tables_off =
+      (static_cast<size_t>(reinterpret_cast<uint8_t*>(dbias_s + (BWD ? hpc * geo.nrel : 0)) - smem) + 15) & ~size_t(15);
+  long long* rowofs = reinterpret_cast<long long*>(smem + tables_off);                       // [NPAD]
   int* rowslot = reinterpret_cast<int*>(rowofs + NPAD);                                      // [NPAD]
   int* rowreg = rowslot + NPAD;                                                              // [NPAD]
   // cofs[t] = 4 * ((t / ww) * (2 ww - 1) + (t % ww)): the byte offset into a head's table of the relative position
@@ -221,7 +230,7 @@ __global__ void __launch_bounds__(WA_THREADS, NPAD > 64 ? 1 : (BWD ? 3 : 5)) win
 
     constexpr int rblocks = NPAD / 16;
     for (int hh = 0; hh < hpc; ++hh) {
-      const char* btb = reinterpret_cast<const char*>(bias_s + hh * geo.nrel);
+      const uint32_t btb = smem_u32(bias_s + hh * geo.nrel);
       // =============================== phase 1: per 16-query-row block
       for (int rb = warp; rb < rblocks; rb += WA_WARPS) {
         if (rb * 16 >= N) continue;
@@ -252,10 +261,10 @@ __global__ void __launch_bounds__(WA_THREADS, NPAD > 64 ? 1 : (BWD ? 3 : 5)) win
 #pragma unroll
           for (int nb = 0; nb < NPAD / 8; ++nb) {
             const int2 co = *reinterpret_cast<const int2*>(cofs + nb * 8 + tq * 2);
-            s[nb][0] = fmaf(s[nb][0], scale2, *reinterpret_cast<const float*>(btb + (ro0 - co.x)));
-            s[nb][1] = fmaf(s[nb][1], scale2, *reinterpret_cast<const float*>(btb + (ro0 - co.y)));
-            s[nb][2] = fmaf(s[nb][2], scale2, *reinterpret_cast<const float*>(btb + (ro1 - co.x)));
-            s[nb][3] = fmaf(s[nb][3], scale2, *reinterpret_cast<const float*>(btb + (ro1 - co.y)));
+            s[nb][0] = fmaf(s[nb][0], scale2, lds_f32(btb + (ro0 - co.x)));
+            s[nb][1] = fmaf(s[nb][1], scale2, lds_f32(btb + (ro0 - co.y)));
+            s[nb][2] = fmaf(s[nb][2], scale2, lds_f32(btb + (ro1 - co.x)));
+            s[nb][3] = fmaf(s[nb][3], scale2, lds_f32(btb + (ro1 - co.y)));
             mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
             mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
           }
@@ -272,7 +281,7 @@ __global__ void __launch_bounds__(WA_THREADS, NPAD > 64 ? 1 : (BWD ? 3 : 5)) win
               const bool lo = k < 2;
               float v = s[nb][k] * scale2;
               if (col < N) {
-                if (lo ? row0 : row1) v += *reinterpret_cast<const float*>(btb + ((lo ? ro0 : ro1) - ((k & 1) ? co.y : co.x)));
+                if (lo ? row0 : row1) v += lds_f32(btb + ((lo ? ro0 : ro1) - ((k & 1) ? co.y : co.x)));
                 if (a.use_mask && ((k & 1) ? cr.y : cr.x) != (lo ? reg0 : reg1)) v += -100.f * WA_LOG2E;
               } else {
                 v = -1e30f;
