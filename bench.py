@@ -124,12 +124,13 @@ def run_ours(args):
     devb = [{k: v.to(dev, non_blocking=True) for k, v in b.items()} for b in host]
     h2d_bytes = sum(v.numel() * v.element_size() for v in host[0].values())
 
-    # ---- device-timed kernel-only number
+    # ---- device-timed kernel-only number (the clock sampler runs from the warm-up on: nvidia-smi needs a moment to
+    #      start, and a multi-GPU timed region lasts only tens of milliseconds)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
     for i in range(args.warmup):
         trainer.step_on_device(devb[i % 2])
     barrier()
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
     launches0 = ext.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()

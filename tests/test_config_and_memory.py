@@ -133,3 +133,34 @@ def test_lr_schedules():
     assert mid == pytest.approx(1e-6 + (1e-3 - 1e-6) * 0.5, rel=1e-6)
     assert get_finetune_lr_by_global_step(3, 1e-3, 6) == pytest.approx(5e-4)
     assert get_finetune_lr_by_global_step(60, 1e-3, 6) == 1e-3
+
+
+def test_bind_to_gpu_numa_with_fake_nvml(monkeypatch):
+    """CPU affinity follows the mask a (fake) NVML reports for the GPU; GPU settings are never written."""
+    import os
+    import sys
+    import types
+
+    from terra_b200 import distributed as D
+
+    if not hasattr(os, "sched_setaffinity"):
+        return
+    allowed = sorted(os.sched_getaffinity(0))
+    want = set(allowed[: max(1, len(allowed) // 2)])
+    calls = []
+    fake = types.SimpleNamespace(
+        nvmlInit=lambda: calls.append("init"), nvmlShutdown=lambda: calls.append("shutdown"),
+        nvmlDeviceGetHandleByIndex=lambda i: ("h", i),
+        nvmlDeviceGetCpuAffinity=lambda h, n: [sum(1 << (c - 64 * w) for c in want if 64 * w <= c < 64 * (w + 1)) for w in range(n)])
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "3,5")
+    assert D._physical_gpu_index(1) == 5
+    before = os.sched_getaffinity(0)
+    try:
+        assert D.bind_to_gpu_numa(0) is True
+        assert os.sched_getaffinity(0) == want
+        assert calls == ["init", "shutdown"]
+        monkeypatch.setenv("TERRA_NUMA_BIND", "0")
+        assert D.bind_to_gpu_numa(0) is False
+    finally:
+        os.sched_setaffinity(0, before)
