@@ -58,13 +58,13 @@ void peer_sum_small(torch::Tensor& dst, const std::vector<int64_t>& src_ptrs) {
 }
 
 void peer_barrier(const std::vector<int64_t>& pads, int64_t my_rank, int64_t epoch, const c10::optional<torch::Tensor>& status,
-                  int64_t spin_limit) {
+                  int64_t budget_ns) {
   std::vector<uint32_t*> p;
   for (auto v : pads) p.push_back(reinterpret_cast<uint32_t*>(v));
   tb::note_launch();
   TORCH_CHECK(tb::peer_barrier(p.data(), static_cast<int>(my_rank), static_cast<int>(p.size()), static_cast<uint32_t>(epoch),
                                status.has_value() ? status->data_ptr() : nullptr,
-                               static_cast<unsigned long long>(spin_limit), cur_stream()) == 0,
+                               static_cast<unsigned long long>(budget_ns), cur_stream()) == 0,
               "peer_barrier launch failed");
 }
 

@@ -34,6 +34,6 @@ int peer_sum_small(float* dst, const float* const* src_peers, int num_peers, int
 // Group barrier on a symmetric signal pad: every rank adds 1 to its slot on all peers, then waits (bounded) until
 // its own pad shows `epoch` from everyone. `status` receives TB_ERR_PEER_TIMEOUT when the wait runs out.
 int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,
-                 unsigned long long spin_limit, cudaStream_t stream);
+                 unsigned long long budget_ns, cudaStream_t stream);
 
 }  // namespace tb

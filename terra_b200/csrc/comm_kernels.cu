@@ -65,9 +65,16 @@ __global__ void peer_sum_small_kernel(float* dst, const __grid_constant__ PeerPt
 struct PadPtrs {
   uint32_t* p[COMM_MAX_PEERS];
 };
-// One block. Thread t < num_peers signals peer t, then everyone waits on the local pad.
+// One block. Thread t < num_peers signals peer t, then everyone waits on the local pad. The wait is bounded in time
+// (`budget_ns` of the global timer): when a peer never signals, the kernel records {site, peer, expected epoch} in the
+// status word and returns, so the context stays usable and the host can raise.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __global__ void peer_barrier_kernel(const __grid_constant__ PadPtrs pads, int my_rank, int num_peers, uint32_t epoch,
-                                    KernelStatus* status, unsigned long long spin_limit) {
+                                    KernelStatus* status, unsigned long long budget_ns) {
   const int t = threadIdx.x;
   if (t < num_peers) {
     __threadfence_system();
@@ -76,12 +83,13 @@ __global__ void peer_barrier_kernel(const __grid_constant__ PadPtrs pads, int my
   }
   if (t < num_peers) {
     const volatile uint32_t* mine = pads.p[my_rank] + t;
-    unsigned long long spins = 0;
+    const unsigned long long t0 = global_timer_ns();
     uint32_t seen;
+    unsigned int polls = 0;
     while (true) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
       if (static_cast<int32_t>(seen - epoch) >= 0) break;
-      if (++spins > spin_limit) {
+      if ((++polls & 63u) == 0u && global_timer_ns() - t0 > budget_ns) {
         report_error(status, TB_ERR_PEER_TIMEOUT, 0x900u, static_cast<unsigned int>(t), epoch);
         break;
       }
@@ -124,11 +132,11 @@ int peer_sum_small(float* dst, const float* const* src_peers, int num_peers, int
 }
 
 int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,
-                 unsigned long long spin_limit, cudaStream_t stream) {
+                 unsigned long long budget_ns, cudaStream_t stream) {
   if (num_peers < 1 || num_peers > COMM_MAX_PEERS) return -1;
   PadPtrs pp;
   for (int i = 0; i < num_peers; ++i) pp.p[i] = signal_pads[i];
-  peer_barrier_kernel<<<1, 32, 0, stream>>>(pp, my_rank, num_peers, epoch, static_cast<KernelStatus*>(status), spin_limit);
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(pp, my_rank, num_peers, epoch, static_cast<KernelStatus*>(status), budget_ns);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -16,6 +16,8 @@ No TMA load here fans out over a cluster; remote data is read with plain loads o
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, List, Optional
 
 import torch
@@ -25,7 +27,8 @@ from .. import _ext
 from ..ops.gemm import status_word
 
 PAD_BYTES = 4096            # signal pads at the start of every arena
-BARRIER_SPIN_LIMIT = 200_000_000
+# time budget of a device-side wait on a peer (nanoseconds of the GPU's global timer); TERRA_PEER_WAIT_MS overrides
+BARRIER_SPIN_LIMIT = int(float(os.environ.get("TERRA_PEER_WAIT_MS", "5000")) * 1e6)
 
 
 def _symm():
