@@ -1,4 +1,6 @@
 // Python bindings (torch tensors -> raw-pointer host API). Only this file sees torch headers.
+#include <cstring>
+#include <vector>
 #include <torch/extension.h>
 #include <c10/cuda/CUDAStream.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -33,11 +35,17 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
           const c10::optional<torch::Tensor>& bias, const c10::optional<torch::Tensor>& residual,
           const c10::optional<torch::Tensor>& aux, const c10::optional<torch::Tensor>& c2, double alpha,
           int64_t split_k, int64_t bn, const c10::optional<torch::Tensor>& status, int64_t shuffle_cout,
-          int64_t out_w, int64_t out_h, int64_t sms) {
+          int64_t out_w, int64_t out_h, int64_t sms, const std::vector<int64_t>& a_peer_ptrs, int64_t rank,
+          const std::vector<int64_t>& c_peer_ptrs) {
   check_bf16_2d(a, "a");
   check_bf16_2d(b, "b");
   const c10::cuda::CUDAGuard guard(a.device());
-  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  // a_peer_ptrs: `a` is this GPU's shard and the operand is the concatenation of all GPUs' shards (all-gather fused
+  // into the loads). c_peer_ptrs: fp32 accumulation buffers of the row blocks' owners (reduce-scatter fused into the
+  // stores); `c` is then this GPU's own buffer and only gives the leading dimension.
+  const int64_t gather = a_peer_ptrs.size() > 1 ? static_cast<int64_t>(a_peer_ptrs.size()) : 1;
+  TORCH_CHECK(gather == 1 || !a_mn, "gemm: gathered A must be K-major");
+  const int64_t M = (a_mn ? a.size(1) : a.size(0)) * gather;
   const int64_t K = a_mn ? a.size(0) : a.size(1);
   const int64_t N = b_mn ? b.size(1) : b.size(0);
   const int64_t Kb = b_mn ? b.size(0) : b.size(1);
@@ -62,8 +70,23 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
   e.out_w = static_cast<int>(out_w);
   e.out_h = static_cast<int>(out_h);
   tb::note_launch();
-  const int rc = tb::gemm_bf16(A, B, M, N, K, e, static_cast<int>(split_k), static_cast<int>(bn),
-                               sms > 0 ? static_cast<int>(sms) : sm_count(), cur_stream());
+  tb::GemmPeers peers;
+  std::memset(&peers, 0, sizeof(peers));
+  TORCH_CHECK(a_peer_ptrs.size() <= 8 && c_peer_ptrs.size() <= 8, "gemm: at most 8 peers");
+  if (gather > 1) {
+    peers.a_peers = static_cast<int>(gather);
+    peers.a_rows = a.size(0);
+    for (size_t i = 0; i < a_peer_ptrs.size(); ++i) peers.a_ptr[i] = reinterpret_cast<const void*>(a_peer_ptrs[i]);
+  }
+  peers.rank = static_cast<int>(rank);
+  if (c_peer_ptrs.size() > 1) {
+    peers.c_peers = static_cast<int>(c_peer_ptrs.size());
+    TORCH_CHECK(M % peers.c_peers == 0, "gemm: rows not divisible by the number of owners");
+    peers.c_rows = M / peers.c_peers;
+    for (size_t i = 0; i < c_peer_ptrs.size(); ++i) peers.c_ptr[i] = reinterpret_cast<void*>(c_peer_ptrs[i]);
+  }
+  const int rc = tb::gemm_bf16_peers(A, B, M, N, K, e, peers, static_cast<int>(split_k), static_cast<int>(bn),
+                                     sms > 0 ? static_cast<int>(sms) : sm_count(), cur_stream());
   TORCH_CHECK(rc == 0, "terra_b200 gemm launch failed, code ", rc, " (M=", M, " N=", N, " K=", K, ")");
 }
 

@@ -96,8 +96,23 @@ static void fill_epilogue(GemmParams& p, const GemmEpilogue& e) {
 
 int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
               const GemmEpilogue& epi, int split_k, int bn_request, int num_sms, cudaStream_t stream) {
+  GemmPeers none;
+  std::memset(&none, 0, sizeof(none));
+  return gemm_bf16_peers(A, B, M, N, K, epi, none, split_k, bn_request, num_sms, stream);
+}
+
+int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
+                    const GemmEpilogue& epi, const GemmPeers& peers, int split_k, int bn_request, int num_sms,
+                    cudaStream_t stream) {
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
+  const bool gather_a = peers.a_peers > 1;
+  const bool scatter_c = peers.c_peers > 1;
+  if (gather_a && (A.mn_major || peers.a_peers > 8 || peers.a_rows <= 0 || M != peers.a_rows * peers.a_peers)) return -12;
+  if (scatter_c && (peers.c_peers > 8 || peers.c_rows <= 0 || M != peers.c_rows * peers.c_peers ||
+                    !((epi.flags & EPI_ATOMIC) && (epi.flags & EPI_OUT_F32))))
+    return -13;
+  if ((gather_a || scatter_c) && bn_request >= 1000) return -14;   // single-CTA tiles only
   // CTA pairs (256-row tiles, one MMA over two SMs): explicit request 1000 + BN, or by policy for the shapes where
   // the main loop dominates (long contraction or wide output) when TERRA_GEMM_2CTA=1.
   int ctas = 1;
@@ -110,7 +125,8 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
       const char* e = std::getenv("TERRA_GEMM_2CTA");
       return (e != nullptr) ? std::atoi(e) : 0;
     }();
-    if (policy == 1 && M >= 512 && N >= 128 && (bn_request == 0 || bn_request == 128 || bn_request == 256)) {
+    if (policy == 1 && !gather_a && !scatter_c && M >= 512 && N >= 128 &&
+        (bn_request == 0 || bn_request == 128 || bn_request == 256)) {
       ctas = 2;
       if (bn_request == 0) bn_request = (N % 256 == 0 || N >= 1024) ? 256 : 128;
     }
@@ -120,6 +136,23 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   p.num_m_tiles = static_cast<int>((M + GEMM_BM * ctas - 1) / (GEMM_BM * ctas));
+  if (gather_a || scatter_c) ctas = 1;
+  if (gather_a) {
+    p.a_peers = peers.a_peers;
+    p.a_rows = static_cast<int>(peers.a_rows);
+    p.a_tiles = static_cast<int>((peers.a_rows + GEMM_BM - 1) / GEMM_BM);
+    p.a_first = peers.rank % peers.a_peers;
+    p.num_m_tiles = p.a_tiles * p.a_peers;
+    for (int i = 0; i < peers.a_peers; ++i) {
+      const int rc_i = map_2d(&p.map_a_peer[i], peers.a_ptr[i], K, peers.a_rows, A.ld, GEMM_BK, GEMM_BM);
+      if (rc_i != 0) return rc_i - 3000;
+    }
+  }
+  if (scatter_c) {
+    p.c_peers = peers.c_peers;
+    p.c_rows = static_cast<int>(peers.c_rows);
+    for (int i = 0; i < peers.c_peers; ++i) p.c_peer[i] = peers.c_ptr[i];
+  }
   p.num_n_tiles = static_cast<int>((N + bn - 1) / bn);
   p.k_blocks = static_cast<int>((K + GEMM_BK - 1) / GEMM_BK);
   p.groups = 1;
@@ -135,7 +168,7 @@ int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long
   p.b_mode = B.mn_major ? OP_MNMAJOR_2D : OP_KMAJOR_2D;
   int rc;
   if (A.mn_major) rc = map_2d(&p.map_a, A.ptr, M, K, A.ld, 64, GEMM_BK);
-  else rc = map_2d(&p.map_a, A.ptr, K, M, A.ld, GEMM_BK, GEMM_BM);
+  else rc = map_2d(&p.map_a, gather_a ? peers.a_ptr[p.a_first] : A.ptr, K, gather_a ? peers.a_rows : M, A.ld, GEMM_BK, GEMM_BM);
   if (rc != 0) return rc;
   if (B.mn_major) rc = map_2d(&p.map_b, B.ptr, N, K, B.ld, 64, GEMM_BK);
   else rc = map_2d(&p.map_b, B.ptr, K, N, B.ld, GEMM_BK, bn / ctas);   // a CTA of a pair stages half of B's rows

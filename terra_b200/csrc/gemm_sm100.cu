@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     mbar_fence_init();
     tma_prefetch_desc(&p.map_a);
     tma_prefetch_desc(&p.map_b);
+    for (int i = 0; i < p.a_peers && p.a_peers > 1; ++i) tma_prefetch_desc(&p.map_a_peer[i]);
   }
   if (warp == 1) {
     tmem_alloc<Cfg::TMEM_COLS, CTAS>(tmem_slot);
@@ -178,7 +179,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           }
           // ---- operand A
           if (p.a_mode == OP_KMAJOR_2D) {
-            tma_load_2d(sA, &p.map_a, &full[s], kb * GEMM_BK, m0);
+            if (p.a_peers > 1) {
+              const int peer = (tc.m_blk / p.a_tiles + p.a_first) % p.a_peers;
+              tma_load_2d(sA, &p.map_a_peer[peer], &full[s], kb * GEMM_BK, (tc.m_blk % p.a_tiles) * GEMM_BM);
+            } else {
+              tma_load_2d(sA, &p.map_a, &full[s], kb * GEMM_BK, m0);
+            }
           } else if (p.a_mode == OP_MNMAJOR_2D) {
 #pragma unroll
             for (int j = 0; j < GEMM_BM / 64; ++j)
@@ -334,6 +340,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const long long b = t / p.out_h;
           const int qd = n0 / p.shuffle_cout;
           return ((b * 2 * p.out_h + 2 * h + (qd >> 1)) * 2 * p.out_w) + 2 * w + (qd & 1);
+        } else if (p.a_peers > 1) {
+          const int peer = (tc.m_blk / p.a_tiles + p.a_first) % p.a_peers;
+          const int lr = (tc.m_blk % p.a_tiles) * GEMM_BM + r;
+          return (lr < p.a_rows) ? static_cast<long long>(peer) * p.a_rows + lr : -1;
         } else {
           const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;
           return (g < p.M) ? g : -1;
@@ -499,6 +509,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
               const int col = cb + 16 * hf + gvec * 4;
               if (grows[i] < 0 || col >= ncols_out) continue;
               float* o = obase + static_cast<long long>(grows[i]) * p.ldc + col;
+              if (p.c_peers > 1)   // the row's owner accumulates it
+                o = static_cast<float*>(p.c_peer[grows[i] / p.c_rows]) + gofs +
+                    static_cast<long long>(grows[i] % p.c_rows) * p.ldc + col;
               const bool full4 = vec_ok && col + 4 <= ncols_out;
               if (p.epi & EPI_ATOMIC) {
                 if (full4) {

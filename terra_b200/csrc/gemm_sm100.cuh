@@ -69,6 +69,16 @@ struct GemmParams {
   int shuffle_cout;
   float alpha;
   KernelStatus* status;
+  // Tensor-parallel fusions over peer memory (NVLink), single-CTA mode, 2-D K-major A:
+  //  * all-gather -> GEMM: the rows of A live in a_peers buffers of a_rows rows each (one per GPU, one tensor map per
+  //    buffer); tile slot s of the m dimension reads peer (s + a_first) % a_peers, so every GPU starts with its own
+  //    rows while the remote tiles are in flight. Output rows are numbered peer * a_rows + row.
+  //  * GEMM -> reduce-scatter: with c_peers > 1 the fp32 atomic output of row g goes to buffer c_peer[g / c_rows]
+  //    (row g % c_rows), the owner's accumulation buffer, by vector reductions over NVLink.
+  int a_peers, a_rows, a_tiles, a_first;
+  CUtensorMap map_a_peer[8];
+  int c_peers, c_rows;
+  void* c_peer[8];
 };
 
 }  // namespace tb

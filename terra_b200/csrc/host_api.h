@@ -25,7 +25,23 @@ struct GemmEpilogue {
   void* status;       // KernelStatus* (device), may be null
 };
 
+// Tensor-parallel fusions over peer memory. a_ptr[i]: GPU i's [a_rows, K] bf16 shard (K-major, leading dimension of
+// operand A) - A is their concatenation, read tile by tile over NVLink. c_ptr[i]: GPU i's fp32 [c_rows, N] accumulation
+// buffer - output row g is reduced into c_ptr[g / c_rows]. Either part may be unused (count 0 or 1).
+struct GemmPeers {
+  int a_peers;
+  const void* a_ptr[8];
+  long long a_rows;
+  int rank;          // this GPU's index: its own shard's tiles are scheduled first
+  int c_peers;
+  void* c_ptr[8];
+  long long c_rows;
+};
+
 // gemm_host.cu
+int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
+                    const GemmEpilogue& epi, const GemmPeers& peers, int split_k, int bn_request, int num_sms,
+                    cudaStream_t stream);
 int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
               const GemmEpilogue& epi, int split_k, int bn_request, int num_sms, cudaStream_t stream);
 // halo_lo / halo_hi: optional one-row images [B, 1, W, Cin] holding the row above / below a row stripe

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import os
 import sys
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -59,10 +59,23 @@ def gemm(
     alpha: float = 1.0,
     bn: int = 0,
     sms: int = 0,
+    a_peers: Optional[Sequence[int]] = None,
+    rank: int = 0,
+    out_peers: Optional[Sequence[int]] = None,
 ):
-    """Returns ``out`` (and the saved pre-activation when ``save_pre``)."""
+    """Returns ``out`` (and the saved pre-activation when ``save_pre``).
+
+    Tensor-parallel fusions over peer memory: with ``a_peers`` (device pointers of every GPU's ``[rows, K]`` shard in
+    symmetric memory, ``a`` being this GPU's) the operand is the concatenation of the shards, fetched tile by tile over
+    NVLink inside the GEMM (all-gather -> GEMM). With ``out_peers`` (pointers of every GPU's fp32 ``[M / n, N]``
+    accumulation buffer, ``out`` being this GPU's) the result rows are reduced into their owner's buffer from the
+    epilogue (GEMM -> reduce-scatter). The caller brackets both with barriers on the symmetric buffers."""
     ext = _ext.load()
     M = a.shape[1] if a_mn else a.shape[0]
+    if a_peers is not None and len(a_peers) > 1:
+        M *= len(a_peers)
+    if out_peers is not None and len(out_peers) > 1:
+        accumulate = True
     N = b.shape[1] if b_mn else b.shape[0]
     flags = 0
     if bias is not None:
@@ -96,7 +109,7 @@ def gemm(
               f"res={None if residual is None else (tuple(residual.shape), residual.dtype, residual.stride())}",
               file=sys.stderr, flush=True)
     ext.gemm(a, a_mn, b, b_mn, out, flags, bias, residual, dgelu_aux, pre, float(alpha), int(split_k), int(bn),
-             status_word(a.device), 0, 0, 0, int(sms))
+             status_word(a.device), 0, 0, 0, int(sms), list(a_peers or []), int(rank), list(out_peers or []))
     if save_pre:
         return out, pre
     return out

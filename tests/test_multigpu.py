@@ -54,3 +54,19 @@ def test_layout_matches_single_gpu(n, layout):
     got = _launch(n, layout)
     for a, b in zip(got["losses"], ref["losses"]):
         assert abs(a - b) < 3e-2 * abs(b), (got, ref)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_fused_tensor_parallel_linears(n):
+    """All-gather -> GEMM, GEMM -> reduce-scatter and the sequence-sharded MLP built from them (forward and backward)
+    against fp32 PyTorch on the gathered operands."""
+    _need(n)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
+    worker = os.path.join(ROOT, "tests", "tp_fused_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), worker]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-4000:])
+    res = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("RESULT ")][-1][len("RESULT "):])
+    for key in ("ag_gemm", "gemm_rs", "mlp_out", "mlp_dx", "mlp_dw1", "mlp_db1", "mlp_dw2"):
+        assert res[key] < 3e-2, res
