@@ -68,6 +68,15 @@ void peer_barrier(const std::vector<int64_t>& pads, int64_t my_rank, int64_t epo
               "peer_barrier launch failed");
 }
 
+void peer_signal(const std::vector<int64_t>& pad_ptrs, int64_t my_rank, int64_t slot_base) {
+  std::vector<uint32_t*> p;
+  for (auto v : pad_ptrs) p.push_back(reinterpret_cast<uint32_t*>(v));
+  tb::note_launch();
+  TORCH_CHECK(tb::peer_signal(p.data(), static_cast<int>(my_rank), static_cast<int>(p.size()), static_cast<int>(slot_base),
+                              cur_stream()) == 0,
+              "peer_signal launch failed");
+}
+
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
@@ -75,4 +84,5 @@ void bind_comm(pybind11::module_& m) {
   m.def("peer_copy_rows", &peer_copy_rows);
   m.def("peer_sum_small", &peer_sum_small);
   m.def("peer_barrier", &peer_barrier);
+  m.def("peer_signal", &peer_signal);
 }

@@ -33,6 +33,8 @@ int peer_sum_small(float* dst, const float* const* src_peers, int num_peers, int
 
 // Group barrier on a symmetric signal pad: every rank adds 1 to its slot on all peers, then waits (bounded) until
 // its own pad shows `epoch` from everyone. `status` receives TB_ERR_PEER_TIMEOUT when the wait runs out.
+// One-way "my earlier writes are visible" signal into word [slot_base + my_rank] of every peer's pad.
+int peer_signal(uint32_t* const* signal_pads, int my_rank, int num_peers, int slot_base, cudaStream_t stream);
 int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,
                  unsigned long long budget_ns, cudaStream_t stream);
 

@@ -68,11 +68,6 @@ struct PadPtrs {
 // One block. Thread t < num_peers signals peer t, then everyone waits on the local pad. The wait is bounded in time
 // (`budget_ns` of the global timer): when a peer never signals, the kernel records {site, peer, expected epoch} in the
 // status word and returns, so the context stays usable and the host can raise.
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
 __global__ void peer_barrier_kernel(const __grid_constant__ PadPtrs pads, int my_rank, int num_peers, uint32_t epoch,
                                     KernelStatus* status, unsigned long long budget_ns) {
   const int t = threadIdx.x;
@@ -99,7 +94,26 @@ __global__ void peer_barrier_kernel(const __grid_constant__ PadPtrs pads, int my
   __syncthreads();
 }
 
+// One-way signal: adds 1 to word [slot_base + my_rank] of every peer's pad after making this GPU's earlier writes
+// visible system-wide. The consumers (for example the TMA thread of a GEMM that reads this GPU's shard) wait for the
+// count to reach their epoch.
+__global__ void peer_signal_kernel(const __grid_constant__ PadPtrs pads, int my_rank, int num_peers, int slot_base) {
+  const int t = threadIdx.x;
+  if (t < num_peers) {
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(pads.p[t] + slot_base + my_rank) : "memory");
+  }
+}
+
 }  // namespace
+
+int peer_signal(uint32_t* const* signal_pads, int my_rank, int num_peers, int slot_base, cudaStream_t stream) {
+  if (num_peers < 1 || num_peers > COMM_MAX_PEERS || slot_base < 0) return -1;
+  PadPtrs pp;
+  for (int i = 0; i < num_peers; ++i) pp.p[i] = signal_pads[i];
+  peer_signal_kernel<<<1, 32, 0, stream>>>(pp, my_rank, num_peers, slot_base);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 int dist_adamw_step(const DistAdamWArgs& a, cudaStream_t stream) {
   if (a.num_peers < 1 || a.num_peers > COMM_MAX_PEERS || a.n % 4 != 0 || a.lo % 4 != 0) return -1;

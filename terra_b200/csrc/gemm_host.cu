@@ -109,9 +109,9 @@ int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, lon
   const bool gather_a = peers.a_peers > 1;
   const bool scatter_c = peers.c_peers > 1;
   if (gather_a && (A.mn_major || peers.a_peers > 8 || peers.a_rows <= 0 || M != peers.a_rows * peers.a_peers)) return -12;
-  if (scatter_c && (peers.c_peers > 8 || peers.c_rows <= 0 || M != peers.c_rows * peers.c_peers ||
-                    !((epi.flags & EPI_ATOMIC) && (epi.flags & EPI_OUT_F32))))
-    return -13;
+  if (scatter_c && (peers.c_peers > 8 || peers.c_rows <= 0 || M != peers.c_rows * peers.c_peers)) return -13;
+  // scattered output is either the fp32 atomic form or the plain bf16 form (one staging slot per source GPU)
+  if (scatter_c && (epi.flags & EPI_OUT_F32) && !(epi.flags & EPI_ATOMIC)) return -13;
   if ((gather_a || scatter_c) && bn_request >= 1000) return -14;   // single-CTA tiles only
   // CTA pairs (256-row tiles, one MMA over two SMs): explicit request 1000 + BN, or by policy for the shapes where
   // the main loop dominates (long contraction or wide output) when TERRA_GEMM_2CTA=1.
@@ -142,6 +142,9 @@ int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, lon
     p.a_rows = static_cast<int>(peers.a_rows);
     p.a_tiles = static_cast<int>((peers.a_rows + GEMM_BM - 1) / GEMM_BM);
     p.a_first = peers.rank % peers.a_peers;
+    p.a_flags = static_cast<const unsigned int*>(peers.a_flags);
+    p.a_epoch = peers.a_epoch;
+    p.a_budget_ns = peers.a_budget_ns > 0 ? peers.a_budget_ns : 2000000000ull;
     p.num_m_tiles = p.a_tiles * p.a_peers;
     for (int i = 0; i < peers.a_peers; ++i) {
       const int rc_i = map_2d(&p.map_a_peer[i], peers.a_ptr[i], K, peers.a_rows, A.ld, GEMM_BK, GEMM_BM);
@@ -151,6 +154,7 @@ int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, lon
   if (scatter_c) {
     p.c_peers = peers.c_peers;
     p.c_rows = static_cast<int>(peers.c_rows);
+    p.c_slot = peers.rank % peers.c_peers;
     for (int i = 0; i < peers.c_peers; ++i) p.c_peer[i] = peers.c_ptr[i];
   }
   p.num_n_tiles = static_cast<int>((N + bn - 1) / bn);

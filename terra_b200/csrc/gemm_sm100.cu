@@ -150,6 +150,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       uint32_t it = 0;
       const long long t_begin = clock64();
       long long t_wait = 0;
+      unsigned int peers_ready = p.a_peers > 1 ? (1u << p.a_first) : 0u;   // the own shard needs no signal
       for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units) {
         const TileCoord tc = decode_tile(p, tile, CTAS, rank);
         const int m0 = tc.m_blk * GEMM_BM;
@@ -181,6 +182,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           if (p.a_mode == OP_KMAJOR_2D) {
             if (p.a_peers > 1) {
               const int peer = (tc.m_blk / p.a_tiles + p.a_first) % p.a_peers;
+              if (p.a_flags != nullptr && !((peers_ready >> peer) & 1u)) {
+                // first tile from this peer: its shard must have been published (bounded wait on its flag)
+                const unsigned long long w_begin = global_timer_ns();
+                unsigned int seen, polls = 0;
+                while (true) {
+                  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.a_flags + peer) : "memory");
+                  if (static_cast<int>(seen - p.a_epoch) >= 0) break;
+                  if ((++polls & 31u) == 0u && global_timer_ns() - w_begin > p.a_budget_ns) {
+                    *abort_flag = 1;
+                    report_error(p.status, TB_ERR_PEER_TIMEOUT, 0x500u + peer, seen, p.a_epoch);
+                    break;
+                  }
+                  __nanosleep(50);
+                }
+                if (*abort_flag) break;
+                fence_proxy_async_all();   // order the acquire before the asynchronous-proxy reads of the shard
+                peers_ready |= 1u << peer;
+              }
               tma_load_2d(sA, &p.map_a_peer[peer], &full[s], kb * GEMM_BK, (tc.m_blk % p.a_tiles) * GEMM_BM);
             } else {
               tma_load_2d(sA, &p.map_a, &full[s], kb * GEMM_BK, m0);
@@ -384,8 +403,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const uint4 t = *xaddr(grow + 8 * i, gvec);
-          if (grows[i] >= 0 && cb + gvec * 8 < ncols_out)
-            *reinterpret_cast<uint4*>(base + static_cast<long long>(grows[i]) * ld + cb + gvec * 8) = t;
+          if (grows[i] >= 0 && cb + gvec * 8 < ncols_out) {
+            __nv_bfloat16* o = base + static_cast<long long>(grows[i]) * ld + cb + gvec * 8;
+            if (p.c_peers > 1 && base == static_cast<__nv_bfloat16*>(p.C) + gofs)   // the row's owner stages it
+              o = static_cast<__nv_bfloat16*>(p.c_peer[grows[i] / p.c_rows]) + gofs +
+                  (static_cast<long long>(p.c_slot) * p.c_rows + grows[i] % p.c_rows) * ld + cb + gvec * 8;
+            *reinterpret_cast<uint4*>(o) = t;
+          }
         }
       };
 

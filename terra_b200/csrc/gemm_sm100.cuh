@@ -72,12 +72,19 @@ struct GemmParams {
   // Tensor-parallel fusions over peer memory (NVLink), single-CTA mode, 2-D K-major A:
   //  * all-gather -> GEMM: the rows of A live in a_peers buffers of a_rows rows each (one per GPU, one tensor map per
   //    buffer); tile slot s of the m dimension reads peer (s + a_first) % a_peers, so every GPU starts with its own
-  //    rows while the remote tiles are in flight. Output rows are numbered peer * a_rows + row.
-  //  * GEMM -> reduce-scatter: with c_peers > 1 the fp32 atomic output of row g goes to buffer c_peer[g / c_rows]
-  //    (row g % c_rows), the owner's accumulation buffer, by vector reductions over NVLink.
+  //    rows while the remote tiles are in flight. Output rows are numbered peer * a_rows + row. With a_flags the TMA
+  //    thread itself waits (bounded by a_budget_ns of the global timer) until a_flags[peer] has reached a_epoch
+  //    before the first load from that peer: the peers publish "my shard is written" with a one-way signal and no
+  //    barrier sits in front of the GEMM.
+  //  * GEMM -> reduce-scatter: with c_peers > 1 output row g goes to the buffer of its owner, c_peer[g / c_rows].
+  //    fp32 atomic output: vector reductions into row g % c_rows of the owner's accumulation buffer. bf16 output:
+  //    plain stores into slot c_slot (this GPU's) of the owner's [c_peers][c_rows] staging, which the owner sums.
   int a_peers, a_rows, a_tiles, a_first;
   CUtensorMap map_a_peer[8];
-  int c_peers, c_rows;
+  const unsigned int* a_flags;
+  unsigned int a_epoch;
+  unsigned long long a_budget_ns;
+  int c_peers, c_rows, c_slot;
   void* c_peer[8];
 };
 

@@ -32,9 +32,12 @@ struct GemmPeers {
   int a_peers;
   const void* a_ptr[8];
   long long a_rows;
-  int rank;          // this GPU's index: its own shard's tiles are scheduled first
+  int rank;          // this GPU's index: its own shard's tiles are scheduled first; its slot in the owners' staging
+  const void* a_flags;        // optional: uint32 flags, one per peer, in this GPU's memory; a_flags[i] >= a_epoch means
+  unsigned int a_epoch;       // "peer i's shard is written"; the kernel waits for it (at most a_budget_ns) itself
+  unsigned long long a_budget_ns;
   int c_peers;
-  void* c_ptr[8];
+  void* c_ptr[8];    // fp32 [c_rows, N] accumulation buffers (atomic epilogue) or bf16 [c_peers][c_rows, N] staging (plain)
   long long c_rows;
 };
 

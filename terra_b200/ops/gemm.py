@@ -62,6 +62,9 @@ def gemm(
     a_peers: Optional[Sequence[int]] = None,
     rank: int = 0,
     out_peers: Optional[Sequence[int]] = None,
+    a_flags: int = 0,
+    a_epoch: int = 0,
+    a_budget_ns: int = 0,
 ):
     """Returns ``out`` (and the saved pre-activation when ``save_pre``).
 
@@ -69,12 +72,14 @@ def gemm(
     symmetric memory, ``a`` being this GPU's) the operand is the concatenation of the shards, fetched tile by tile over
     NVLink inside the GEMM (all-gather -> GEMM). With ``out_peers`` (pointers of every GPU's fp32 ``[M / n, N]``
     accumulation buffer, ``out`` being this GPU's) the result rows are reduced into their owner's buffer from the
-    epilogue (GEMM -> reduce-scatter). The caller brackets both with barriers on the symmetric buffers."""
+    epilogue (GEMM -> reduce-scatter). With ``a_flags`` / ``a_epoch`` the kernel itself waits for each peer's
+    "shard written" signal instead of a barrier in front of it. ``out_peers`` with a bf16 ``out`` (shape
+    ``[n, M / n, N]``): plain stores into this GPU's slot of the owners' staging, which the owner sums."""
     ext = _ext.load()
     M = a.shape[1] if a_mn else a.shape[0]
     if a_peers is not None and len(a_peers) > 1:
         M *= len(a_peers)
-    if out_peers is not None and len(out_peers) > 1:
+    if out_peers is not None and len(out_peers) > 1 and (out is None or out.dtype == torch.float32):
         accumulate = True
     N = b.shape[1] if b_mn else b.shape[0]
     flags = 0
@@ -109,7 +114,8 @@ def gemm(
               f"res={None if residual is None else (tuple(residual.shape), residual.dtype, residual.stride())}",
               file=sys.stderr, flush=True)
     ext.gemm(a, a_mn, b, b_mn, out, flags, bias, residual, dgelu_aux, pre, float(alpha), int(split_k), int(bn),
-             status_word(a.device), 0, 0, 0, int(sms), list(a_peers or []), int(rank), list(out_peers or []))
+             status_word(a.device), 0, 0, 0, int(sms), list(a_peers or []), int(rank), list(out_peers or []),
+             int(a_flags), int(a_epoch), int(a_budget_ns))
     if save_pre:
         return out, pre
     return out

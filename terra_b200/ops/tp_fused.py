@@ -17,6 +17,7 @@ from typing import Optional
 
 import torch
 
+from ..parallel.nvlink import BARRIER_SPIN_LIMIT as PEER_WAIT_NS
 from .gemm import gemm
 
 
@@ -29,75 +30,95 @@ class TpFusedComm:
 
     # ---- all-gather -> GEMM
     def stage(self, x: torch.Tensor) -> torch.Tensor:
-        """Copy this rank's shard into symmetric memory (unless it already lives there) and publish it."""
+        """This rank's shard in symmetric memory (copied there unless it already is)."""
         try:
             self.arena.offset_of(x)
-            staged = x
+            return x
         except ValueError:
             staged = self.arena.alloc(tuple(x.shape), x.dtype)
             staged.copy_(x)
-        self.arena.barrier()            # every rank's shard is complete before anybody's GEMM reads it
-        return staged
+            return staged
 
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, bias=None, gelu=False,
-                save_pre=False, dgelu_aux=None, release: bool = True):
-        """``concat_ranks(x_shard) @ w^T`` (or ``@ w`` with ``b_mn``) with the usual fused epilogues. ``release`` ends
-        with a barrier after which the staged shards may be overwritten."""
+                save_pre=False, dgelu_aux=None):
+        """``concat_ranks(x_shard) @ w^T`` (or ``@ w`` with ``b_mn``) with the usual fused epilogues. No barrier in
+        front: every rank publishes its shard with a one-way signal and the GEMM's TMA thread waits for a peer's
+        signal right before its first tile from that peer, while the tiles of the own shard are already computing.
+        The staged shards stay untouched until the next barrier of the group (``gemm_rs`` ends with one)."""
         staged = self.stage(x_shard)
-        out = gemm(staged, w, b_mn=b_mn, bias=bias, gelu=gelu, save_pre=save_pre, dgelu_aux=dgelu_aux,
-                   a_peers=self.arena.peer_ptrs(staged), rank=self.rank)
-        if release:
-            self.arena.barrier()
-        return out
+        epoch = self.arena.publish()
+        return gemm(staged, w, b_mn=b_mn, bias=bias, gelu=gelu, save_pre=save_pre, dgelu_aux=dgelu_aux,
+                    a_peers=self.arena.peer_ptrs(staged), rank=self.rank, a_flags=self.arena.signal_flags_ptr,
+                    a_epoch=epoch, a_budget_ns=PEER_WAIT_NS)
 
     # ---- GEMM -> reduce-scatter
-    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False) -> torch.Tensor:
-        """Row block ``rank`` of ``sum_ranks(a @ w^T)`` as fp32 ``[M / world, N]`` (a view into symmetric memory, valid
-        until the arena is reset)."""
+    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, exact: bool = False) -> torch.Tensor:
+        """Row block ``rank`` of ``sum_ranks(a @ w^T)`` as fp32 ``[M / world, N]``.
+
+        Default: every rank stores its bf16 partial of row block j into its own slot of owner j's staging (plain
+        16-byte stores over NVLink, no zeroing, no atomics); after one barrier the owner adds the slots up in fp32.
+        ``exact``: fp32 vector reductions into the owner's accumulation buffer instead (twice the NVLink bytes and a
+        zero + barrier in front, but the partials are not rounded to bf16)."""
         M = a.shape[0]
         N = w.shape[1] if b_mn else w.shape[0]
         if M % self.world:
             raise ValueError(f"{M} rows cannot be scattered over {self.world} ranks")
-        acc = self.arena.alloc((M // self.world, N), torch.float32)
-        acc.zero_()
-        self.arena.barrier()            # all accumulation buffers are zero before the first reduction arrives
-        gemm(a, w, b_mn=b_mn, out=acc, out_peers=self.arena.peer_ptrs(acc), rank=self.rank)
-        self.arena.barrier()            # all partial products have landed
-        return acc
+        rows = M // self.world
+        if exact:
+            acc = self.arena.alloc((rows, N), torch.float32)
+            acc.zero_()
+            self.arena.barrier()        # all accumulation buffers are zero before the first reduction arrives
+            gemm(a, w, b_mn=b_mn, out=acc, out_peers=self.arena.peer_ptrs(acc), rank=self.rank)
+            self.arena.barrier()        # all partial products have landed
+            return acc
+        slots = self.arena.alloc((self.world, rows, N), torch.bfloat16)
+        gemm(a, w, b_mn=b_mn, out=slots, out_peers=self.arena.peer_ptrs(slots), rank=self.rank)
+        self.arena.barrier()            # every rank's partial has landed in this rank's slots
+        return slots.float().sum(0)
 
 
 class _TpMlpFn(torch.autograd.Function):
-    """y_shard = x_shard + fc2(gelu(fc1(LN(x)))) with x sequence-sharded over the TP group, fc1 column-sharded
-    ([F / tp, C]) and fc2 row-sharded ([C, F / tp]); ``xn`` is the already normalised shard."""
+    """y_shard = fc2(gelu(fc1(xn))) with xn (the normalised activations) sequence-sharded over the TP group, fc1
+    column-sharded ([F / tp, C]) and fc2 row-sharded ([C, F / tp]). ``grads`` = (gw1, gb1, gw2): fp32 buffers of the
+    flat parameter arena that the weight gradients are accumulated into (then ``anchor``, any parameter, keeps the
+    node in the graph and no parameter gradient is returned); ``None``: the gradients are returned."""
 
     @staticmethod
-    def forward(ctx, xn, w1, b1, w2, comm: TpFusedComm):
+    def forward(ctx, xn, anchor, w1, b1, w2, grads, comm: TpFusedComm):
         act, pre = comm.ag_gemm(xn, w1, bias=b1, gelu=True, save_pre=True)          # [M, F/tp]
         y = comm.gemm_rs(act, w2)                                                      # fp32 [M/tp, C]
         ctx.save_for_backward(xn, w1, w2, pre, act)
-        ctx.comm = comm
+        ctx.comm, ctx.grads = comm, grads
         return y.to(torch.bfloat16)
 
     @staticmethod
     def backward(ctx, dy):
+        from .blocks import bias_grad_accumulate, wgrad_accumulate
+
         xn, w1, w2, pre, act = ctx.saved_tensors
         comm: TpFusedComm = ctx.comm
         dy = dy.contiguous().to(torch.bfloat16)
-        staged_dy = comm.stage(dy)
+        staged_dy, staged_xn = comm.stage(dy), comm.stage(xn)
         # d(act) = gather(dy) @ w2, times GELU'(pre): all-gather -> GEMM again (the backward of the reduce-scatter)
-        dpre = gemm(staged_dy, w2, b_mn=True, dgelu_aux=pre, a_peers=comm.arena.peer_ptrs(staged_dy), rank=comm.rank)
-        # weight gradients need the gathered operands once; plain peer copies, off the critical path of dgrad
+        dpre = comm.ag_gemm(staged_dy, w2, b_mn=True, dgelu_aux=pre)
+        # weight gradients need the gathered operands once: plain peer copies after a barrier (it also covers xn)
+        comm.arena.barrier()
         dy_full = _gather_rows(comm, staged_dy)
-        comm.arena.barrier()
-        gw2 = gemm(dy_full, act, a_mn=True, b_mn=True, out_f32=True, accumulate=True, split_k=_wgrad_split(dy_full, act))
-        staged_xn = comm.stage(xn)
         xn_full = _gather_rows(comm, staged_xn)
-        comm.arena.barrier()
-        gw1 = gemm(dpre, xn_full, a_mn=True, b_mn=True, out_f32=True, accumulate=True, split_k=_wgrad_split(dpre, xn_full))
-        gb1 = dpre.float().sum(0)
+        if ctx.grads is not None:
+            gw1, gb1, gw2 = ctx.grads
+            wgrad_accumulate(dy_full, act, gw2)
+            wgrad_accumulate(dpre, xn_full, gw1)
+            if gb1 is not None:
+                bias_grad_accumulate(dpre, gb1)
+            ret = (None, None, None)
+        else:
+            gw2 = gemm(dy_full, act, a_mn=True, b_mn=True, out_f32=True, accumulate=True, split_k=_wgrad_split(dy_full, act))
+            gw1 = gemm(dpre, xn_full, a_mn=True, b_mn=True, out_f32=True, accumulate=True, split_k=_wgrad_split(dpre, xn_full))
+            ret = (gw1.to(w1.dtype), dpre.float().sum(0).to(w1.dtype), gw2.to(w2.dtype))
         # d(xn) = reduce-scatter(dpre @ w1): GEMM -> reduce-scatter (the backward of the all-gather)
         dxn = comm.gemm_rs(dpre, w1, b_mn=True)
-        return dxn.to(torch.bfloat16), gw1.to(w1.dtype), gb1.to(w1.dtype), gw2.to(w2.dtype), None
+        return dxn.to(torch.bfloat16), None, ret[0], ret[1], ret[2], None, None
 
 
 def _wgrad_split(a, b) -> int:
@@ -118,6 +139,7 @@ def _gather_rows(comm: TpFusedComm, staged: torch.Tensor) -> torch.Tensor:
     return full
 
 
-def tp_mlp(xn: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor, comm: TpFusedComm):
+def tp_mlp(xn: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor, comm: TpFusedComm,
+           anchor: Optional[torch.Tensor] = None, grads=None):
     """Sequence-sharded MLP body (without the residual and fc2's bias, which the caller adds once)."""
-    return _TpMlpFn.apply(xn, w1, b1, w2, comm)
+    return _TpMlpFn.apply(xn, anchor, w1, b1, w2, grads, comm)

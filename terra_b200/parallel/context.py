@@ -208,6 +208,15 @@ class ParallelContext:
     def _mlp_half_tp(self, x, mod):
         batch = self._batch_of(x)
         xn = self._ln(x, mod.norm2)
+        tpc = getattr(self, "tp_comm", None)
+        if tpc is not None and x.is_cuda and batch == 1 and len(set(self.tp_sizes_windows)) == 1:
+            # fc1 / fc2 with their all-gather / reduce-scatter fused into the GEMMs over NVLink peer memory
+            from ..ops.tp_fused import tp_mlp
+
+            l1, l2 = mod.linear1, mod.linear2
+            y = tp_mlp(xn.contiguous(), l1.weight.bf16, l1.bias.bf16, l2.weight.bf16, tpc, anchor=l1.weight,
+                       grads=(l1.weight.grad, l1.bias.grad, l2.weight.grad))
+            return x + y + mod.bias2.to(y.dtype)
         xa = self._ag_tp(xn, batch)
         h = self._lin(xa, mod.linear1)
         h = TF.gelu(h.float()).to(h.dtype) if h.is_cuda else TF.gelu(h)

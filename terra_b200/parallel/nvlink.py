@@ -108,6 +108,20 @@ class SymmetricArena:
         return [b + off for b in self.base_ptrs]
 
     # ---- synchronisation
+    SIGNAL_SLOT = 64       # words [64, 64 + world) of the pad count the one-way "published" signals per source rank
+
+    def publish(self) -> int:
+        """One-way signal "everything this rank wrote so far (stream order) is visible"; returns the epoch that the
+        consumers wait for. All ranks call it in the same order, so the epochs agree."""
+        self.signal_epoch = getattr(self, "signal_epoch", 0) + 1
+        _ext.load().peer_signal(self.base_ptrs, self.rank, self.SIGNAL_SLOT)
+        return self.signal_epoch
+
+    @property
+    def signal_flags_ptr(self) -> int:
+        """Device address of this rank's ``[world]`` array of published counts (one per source rank)."""
+        return self.base_ptrs[self.rank] + 4 * self.SIGNAL_SLOT
+
     def barrier(self) -> None:
         """Stream-ordered barrier over the group (device side; the host does not wait)."""
         self.epoch += 1
@@ -220,6 +234,17 @@ def attach(model, optimizer, manager) -> None:
         arena = SymmetricArena(manager.xfmr_tp_param_group, nbytes, device)
         pctx.fused_comm = FusedAttnComm(arena, pctx.n_wg, pctx.sp)
         pctx.attn_arena = arena
+    # ---- tensor-parallel MLP: fc1 / fc2 with the all-gather / reduce-scatter fused into the GEMMs
+    if pctx.tp > 1 and os.environ.get("TERRA_TP_FUSED", "1") != "0":
+        from ..ops.tp_fused import TpFusedComm
+
+        rows = max(pctx.tp_sizes_windows) * pctx.shardN * pctx.B
+        C, F = model.embedding_dim, 4 * model.embedding_dim
+        # per MLP forward + backward: staged xn, dy (bf16), reduce-scatter slots (bf16 x tp x 2)
+        per_layer = rows * (2 * C * 2 + 2 * pctx.tp * C * 2)
+        nbytes = int(per_layer * model.num_layers * 1.5) + (64 << 20)
+        pctx.tp_arena = SymmetricArena(manager.xfmr_tp_group, nbytes, device)
+        pctx.tp_comm = TpFusedComm(pctx.tp_arena)
     # ---- sharded optimizer: gradients and working copy must be peer visible. One symmetric allocation is mapped
     # for one group, so the largest parameter class gets the fused kernel; other classes (TP shards, whose replica
     # group differs) keep the collective path on the same buffers.
@@ -237,6 +262,7 @@ def attach(model, optimizer, manager) -> None:
 
 
 def reset_step_arenas(model) -> None:
-    arena = getattr(model.pctx, "attn_arena", None)
-    if arena is not None:
-        arena.reset()
+    for name in ("attn_arena", "tp_arena"):
+        arena = getattr(model.pctx, name, None)
+        if arena is not None:
+            arena.reset()

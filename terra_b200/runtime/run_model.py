@@ -54,9 +54,10 @@ def one_step_train(task_type, model_type, model, engine, optimizer, required_ten
         ev0.record()
 
     pctx = getattr(model.module if hasattr(model, "module") else model, "pctx", None)
-    arena = getattr(pctx, "attn_arena", None)
-    if arena is not None:
-        arena.reset()          # per-step symmetric buffers of the previous step are dead
+    for arena_name in ("attn_arena", "tp_arena"):
+        arena = getattr(pctx, arena_name, None)
+        if arena is not None:
+            arena.reset()      # per-step symmetric buffers of the previous step are dead
     mark_memory_timeline("before_forward")
     post_scale = loss_scale_factor(model_type, other_params.get("embedding_parallel_type") if other_params else None,
                                    manager, task_specific_data_dict, USE_FSDP)

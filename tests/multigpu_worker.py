@@ -32,7 +32,8 @@ def main():
     total = torch.tensor(losses, dtype=torch.float64)
     if t.rank == 0:
         print("RESULT " + json.dumps({"losses": total.tolist(), "fused_attn": t.model.pctx.fused_comm is not None,
-                                      "fused_opt": getattr(t.optimizer, "fused", None) is not None}), flush=True)
+                                      "fused_opt": getattr(t.optimizer, "fused", None) is not None,
+                                      "fused_tp": getattr(t.model.pctx, "tp_comm", None) is not None}), flush=True)
     t.close()
 
 

@@ -22,6 +22,7 @@ def main():
     rank, world, dev = init_distributed()
     arena = SymmetricArena(dist.group.WORLD, 3 << 30 if timing else 256 << 20, dev)
     comm = TpFusedComm(arena)
+    x_sym = None
     torch.manual_seed(5)                      # same weights and global activations on every rank
     rows, C, F = (17408, 384, 1536) if timing else (328, 256, 512)    # rows per rank; 328 is not a tile multiple
     Fs = F // world
@@ -30,6 +31,8 @@ def main():
     b1 = (torch.randn(F, device=dev) * 0.1).to(torch.bfloat16)
     w2 = (torch.randn(C, F, device=dev) * 0.05).to(torch.bfloat16)
     x = x_full[rank * rows:(rank + 1) * rows].contiguous()
+    x_sym = arena.alloc((rows, C), torch.bfloat16, persistent=True)      # an activation produced in symmetric memory
+    x_sym.copy_(x)
     w1s, b1s, w2s = w1[rank * Fs:(rank + 1) * Fs].contiguous(), b1[rank * Fs:(rank + 1) * Fs].contiguous(), \
         w2[:, rank * Fs:(rank + 1) * Fs].contiguous()
     res = {}
@@ -43,9 +46,9 @@ def main():
     # ---- GEMM -> reduce-scatter
     h_full = (torch.randn(rows * world, F, device=dev) * 0.3).to(torch.bfloat16)
     hs = h_full[:, rank * Fs:(rank + 1) * Fs].contiguous()
-    z = comm.gemm_rs(hs, w2s)
     ref = (h_full.float() @ w2.float().t())[rank * rows:(rank + 1) * rows]
-    res["gemm_rs"] = rel(z, ref)
+    res["gemm_rs"] = rel(comm.gemm_rs(hs, w2s), ref)
+    res["gemm_rs_exact"] = rel(comm.gemm_rs(hs, w2s, exact=True), ref)
     arena.reset()
     # ---- MLP forward / backward
     xr = x.clone().requires_grad_(True)
@@ -92,14 +95,18 @@ def main():
 
         def fused_ag():
             arena.reset()
-            return comm.ag_gemm(x, w1s, bias=b1s)
+            return comm.ag_gemm(x_sym, w1s, bias=b1s)
+
+        def fused_rs_exact():
+            arena.reset()
+            return comm.gemm_rs(hs, w2s, exact=True)
 
         def fused_rs():
             arena.reset()
             return comm.gemm_rs(hs, w2s)
 
         res["ms"] = {"nccl_ag_then_gemm": timed(nccl_ag_gemm), "fused_ag_gemm": timed(fused_ag),
-                     "gemm_then_nccl_rs": timed(nccl_gemm_rs), "fused_gemm_rs": timed(fused_rs),
+                     "gemm_then_nccl_rs": timed(nccl_gemm_rs), "fused_gemm_rs": timed(fused_rs), "fused_gemm_rs_fp32_atomics": timed(fused_rs_exact),
                      "local_gemm_same_shape": timed(lambda: gemm(gathered, w1s, bias=b1s)),
                      "shape": {"rows_per_rank": rows, "C": C, "F": F, "ranks": world}}
     if rank == 0:
