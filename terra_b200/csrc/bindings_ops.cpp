@@ -180,6 +180,17 @@ void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int
   rc_check(tb::window_attn_bwd(a, cur_stream()), "window_attn_bwd");
 }
 
+void sum_slots(const torch::Tensor& slots, torch::Tensor& out) {
+  need(slots.is_cuda() && slots.is_contiguous() && slots.scalar_type() == torch::kBFloat16 && slots.dim() >= 2,
+       "sum_slots: [slots, ...] bf16 contiguous");
+  need(out.is_contiguous() && out.scalar_type() == torch::kBFloat16 && out.numel() * slots.size(0) == slots.numel(),
+       "sum_slots: out must hold one slot");
+  const c10::cuda::CUDAGuard guard(slots.device());
+  tb::note_launch();
+  rc_check(tb::sum_slots_bf16(slots.data_ptr(), out.data_ptr(), static_cast<int>(slots.size(0)), out.numel(), cur_stream()),
+           "sum_slots");
+}
+
 }  // namespace
 
 void bind_elementwise(pybind11::module_& m) {
@@ -192,6 +203,7 @@ void bind_elementwise(pybind11::module_& m) {
   m.def("groupnorm_silu_bwd_apply", &groupnorm_silu_bwd_apply);
   m.def("masked_loss", &masked_loss);
   m.def("adamw_step", &adamw_step);
+  m.def("sum_slots", &sum_slots);
 }
 
 void bind_attention(pybind11::module_& m) {

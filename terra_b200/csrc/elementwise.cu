@@ -499,6 +499,22 @@ __global__ void add_bf16_kernel(const uint4* __restrict__ a, const uint4* __rest
   }
 }
 
+// out = sum over `slots` consecutive bf16 buffers of `nvec` 16-byte vectors each (fp32 accumulation)
+__global__ void sum_slots_bf16_kernel(const uint4* __restrict__ src, uint4* __restrict__ o, int slots, long long nvec) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+    unpack8(src[i], acc);
+    for (int s = 1; s < slots; ++s) {
+      float y[8];
+      unpack8(src[i + s * nvec], y);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += y[j];
+    }
+    o[i] = pack8(acc);
+  }
+}
+
 int grid_for(long long work_items, int block, int max_blocks = 148 * 16) {
   long long g = (work_items + block - 1) / block;
   if (g > max_blocks) g = max_blocks;
@@ -640,6 +656,13 @@ int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t 
   if (n % 8 != 0) return -1;
   add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
                                                             static_cast<uint4*>(out), n / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int sum_slots_bf16(const void* src, void* out, int slots, long long n, cudaStream_t stream) {
+  if (n % 8 != 0 || slots < 1) return -1;
+  sum_slots_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(out),
+                                                                  slots, n / 8);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           // ---- operand A
           if (p.a_mode == OP_KMAJOR_2D) {
             if (p.a_peers > 1) {
-              const int peer = (tc.m_blk / p.a_tiles + p.a_first) % p.a_peers;
+              const int peer = (tc.m_blk % p.a_peers + p.a_first) % p.a_peers;
               if (p.a_flags != nullptr && !((peers_ready >> peer) & 1u)) {
                 // first tile from this peer: its shard must have been published (bounded wait on its flag)
                 const unsigned long long w_begin = global_timer_ns();
@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
                 fence_proxy_async_all();   // order the acquire before the asynchronous-proxy reads of the shard
                 peers_ready |= 1u << peer;
               }
-              tma_load_2d(sA, &p.map_a_peer[peer], &full[s], kb * GEMM_BK, (tc.m_blk % p.a_tiles) * GEMM_BM);
+              tma_load_2d(sA, &p.map_a_peer[peer], &full[s], kb * GEMM_BK, (tc.m_blk / p.a_peers) * GEMM_BM);
             } else {
               tma_load_2d(sA, &p.map_a, &full[s], kb * GEMM_BK, m0);
             }
@@ -360,8 +360,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const int qd = n0 / p.shuffle_cout;
           return ((b * 2 * p.out_h + 2 * h + (qd >> 1)) * 2 * p.out_w) + 2 * w + (qd & 1);
         } else if (p.a_peers > 1) {
-          const int peer = (tc.m_blk / p.a_tiles + p.a_first) % p.a_peers;
-          const int lr = (tc.m_blk % p.a_tiles) * GEMM_BM + r;
+          const int peer = (tc.m_blk % p.a_peers + p.a_first) % p.a_peers;
+          const int lr = (tc.m_blk / p.a_peers) * GEMM_BM + r;
           return (lr < p.a_rows) ? static_cast<long long>(peer) * p.a_rows + lr : -1;
         } else {
           const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;

@@ -71,8 +71,9 @@ struct GemmParams {
   KernelStatus* status;
   // Tensor-parallel fusions over peer memory (NVLink), single-CTA mode, 2-D K-major A:
   //  * all-gather -> GEMM: the rows of A live in a_peers buffers of a_rows rows each (one per GPU, one tensor map per
-  //    buffer); tile slot s of the m dimension reads peer (s + a_first) % a_peers, so every GPU starts with its own
-  //    rows while the remote tiles are in flight. Output rows are numbered peer * a_rows + row. With a_flags the TMA
+  //    buffer); m tile i reads tile i / a_peers of peer (i % a_peers + a_first) % a_peers: every GPU starts with a
+  //    tile of its own rows, and local and remote tiles alternate, so NVLink is busy during the whole kernel rather
+  //    than after the local part. Output rows are numbered peer * a_rows + row. With a_flags the TMA
   //    thread itself waits (bounded by a_budget_ns of the global timer) until a_flags[peer] has reached a_epoch
   //    before the first load from that peer: the peers publish "my shard is written" with a one-way signal and no
   //    barrier sits in front of the GEMM.

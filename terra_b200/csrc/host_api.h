@@ -95,6 +95,9 @@ int adamw_step(float* master, float* exp_avg, float* exp_avg_sq, const void* gra
 int cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 // out[b, i, j, c] = a + b elementwise (bf16)
 int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
+// out[n] = sum of `slots` consecutive bf16 buffers of n elements (fp32 accumulation); the owner's side of the
+// slot-staged reduce-scatter
+int sum_slots_bf16(const void* src, void* out, int slots, long long n, cudaStream_t stream);
 
 // window_attn.cu -------------------------------------------------------------------------------
 constexpr int WA_MAX_PEERS = 16;

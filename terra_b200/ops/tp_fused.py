@@ -18,6 +18,7 @@ from typing import Optional
 import torch
 
 from ..parallel.nvlink import BARRIER_SPIN_LIMIT as PEER_WAIT_NS
+from .. import _ext
 from .gemm import gemm
 
 
@@ -53,7 +54,7 @@ class TpFusedComm:
 
     # ---- GEMM -> reduce-scatter
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, exact: bool = False) -> torch.Tensor:
-        """Row block ``rank`` of ``sum_ranks(a @ w^T)`` as fp32 ``[M / world, N]``.
+        """Row block ``rank`` of ``sum_ranks(a @ w^T)``: ``[M / world, N]``, bf16 (fp32 with ``exact``).
 
         Default: every rank stores its bf16 partial of row block j into its own slot of owner j's staging (plain
         16-byte stores over NVLink, no zeroing, no atomics); after one barrier the owner adds the slots up in fp32.
@@ -74,7 +75,9 @@ class TpFusedComm:
         slots = self.arena.alloc((self.world, rows, N), torch.bfloat16)
         gemm(a, w, b_mn=b_mn, out=slots, out_peers=self.arena.peer_ptrs(slots), rank=self.rank)
         self.arena.barrier()            # every rank's partial has landed in this rank's slots
-        return slots.float().sum(0)
+        out = torch.empty(rows, N, dtype=torch.bfloat16, device=a.device)
+        _ext.load().sum_slots(slots, out)
+        return out
 
 
 class _TpMlpFn(torch.autograd.Function):
