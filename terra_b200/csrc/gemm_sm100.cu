@@ -79,7 +79,9 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile, 
   return t;
 }
 
-template <int BN, int CTAS>
+// PEERS: the tensor-parallel variants (A gathered from peer buffers, output scattered to peer buffers). A separate
+// instantiation, so that the plain kernel carries none of their registers and branches.
+template <int BN, int CTAS, bool PEERS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN, CTAS>;
   constexpr bool PAIR = CTAS == 2;
@@ -121,7 +123,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     mbar_fence_init();
     tma_prefetch_desc(&p.map_a);
     tma_prefetch_desc(&p.map_b);
-    for (int i = 0; i < p.a_peers && p.a_peers > 1; ++i) tma_prefetch_desc(&p.map_a_peer[i]);
+    if (PEERS)
+      for (int i = 0; i < p.a_peers && p.a_peers > 1; ++i) tma_prefetch_desc(&p.map_a_peer[i]);
   }
   if (warp == 1) {
     tmem_alloc<Cfg::TMEM_COLS, CTAS>(tmem_slot);
@@ -150,7 +153,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       uint32_t it = 0;
       const long long t_begin = clock64();
       long long t_wait = 0;
-      unsigned int peers_ready = p.a_peers > 1 ? (1u << p.a_first) : 0u;   // the own shard needs no signal
+      unsigned int peers_ready = (PEERS && p.a_peers > 1) ? (1u << p.a_first) : 0u;   // the own shard needs no signal
       for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units) {
         const TileCoord tc = decode_tile(p, tile, CTAS, rank);
         const int m0 = tc.m_blk * GEMM_BM;
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           }
           // ---- operand A
           if (p.a_mode == OP_KMAJOR_2D) {
-            if (p.a_peers > 1) {
+            if (PEERS && p.a_peers > 1) {
               const int peer = (tc.m_blk % p.a_peers + p.a_first) % p.a_peers;
               if (p.a_flags != nullptr && !((peers_ready >> peer) & 1u)) {
                 // first tile from this peer: its shard must have been published (bounded wait on its flag)
@@ -359,7 +362,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const long long b = t / p.out_h;
           const int qd = n0 / p.shuffle_cout;
           return ((b * 2 * p.out_h + 2 * h + (qd >> 1)) * 2 * p.out_w) + 2 * w + (qd & 1);
-        } else if (p.a_peers > 1) {
+        } else if (PEERS && p.a_peers > 1) {
           const int peer = (tc.m_blk % p.a_peers + p.a_first) % p.a_peers;
           const int lr = (tc.m_blk / p.a_peers) * GEMM_BM + r;
           return (lr < p.a_rows) ? static_cast<long long>(peer) * p.a_rows + lr : -1;
@@ -405,7 +408,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const uint4 t = *xaddr(grow + 8 * i, gvec);
           if (grows[i] >= 0 && cb + gvec * 8 < ncols_out) {
             __nv_bfloat16* o = base + static_cast<long long>(grows[i]) * ld + cb + gvec * 8;
-            if (p.c_peers > 1 && base == static_cast<__nv_bfloat16*>(p.C) + gofs)   // the row's owner stages it
+            if (PEERS && p.c_peers > 1 && base == static_cast<__nv_bfloat16*>(p.C) + gofs)   // the row's owner stages it
               o = static_cast<__nv_bfloat16*>(p.c_peer[grows[i] / p.c_rows]) + gofs +
                   (static_cast<long long>(p.c_slot) * p.c_rows + grows[i] % p.c_rows) * ld + cb + gvec * 8;
             *reinterpret_cast<uint4*>(o) = t;
@@ -533,7 +536,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
               const int col = cb + 16 * hf + gvec * 4;
               if (grows[i] < 0 || col >= ncols_out) continue;
               float* o = obase + static_cast<long long>(grows[i]) * p.ldc + col;
-              if (p.c_peers > 1)   // the row's owner accumulates it
+              if (PEERS && p.c_peers > 1)   // the row's owner accumulates it
                 o = static_cast<float*>(p.c_peer[grows[i] / p.c_rows]) + gofs +
                     static_cast<long long>(grows[i] % p.c_rows) * p.ldc + col;
               const bool full4 = vec_ok && col + 4 <= ncols_out;
@@ -592,12 +595,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 }
 
 // ------------------------------------------------------------------------------ host side
-template <int BN, int CTAS>
+template <int BN, int CTAS, bool PEERS = false>
 static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, CTAS>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, CTAS, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     configured = true;
@@ -607,7 +610,7 @@ static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stre
   const int units = total < max_units ? total : max_units;
   if (units <= 0) return cudaSuccess;
   if (CTAS == 1) {
-    gemm_tcgen05_kernel<BN, CTAS><<<units, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+    gemm_tcgen05_kernel<BN, CTAS, PEERS><<<units, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
     return cudaGetLastError();
   }
   cudaLaunchConfig_t cfg = {};
@@ -622,7 +625,7 @@ static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stre
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, CTAS>, p);
+  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, CTAS, PEERS>, p);
 }
 
 cudaError_t gemm_read_stalls(unsigned long long* out8, bool reset) {
@@ -640,6 +643,15 @@ cudaError_t launch_gemm(const GemmParams& p, int bn, int ctas, int num_sms, cuda
     switch (bn) {
       case 128: return launch_bn<128, 2>(p, num_sms, stream);
       case 256: return launch_bn<256, 2>(p, num_sms, stream);
+      default: return cudaErrorInvalidValue;
+    }
+  }
+  if (p.a_peers > 1 || p.c_peers > 1) {
+    switch (bn) {
+      case 64: return launch_bn<64, 1, true>(p, num_sms, stream);
+      case 128: return launch_bn<128, 1, true>(p, num_sms, stream);
+      case 192: return launch_bn<192, 1, true>(p, num_sms, stream);
+      case 256: return launch_bn<256, 1, true>(p, num_sms, stream);
       default: return cudaErrorInvalidValue;
     }
   }
