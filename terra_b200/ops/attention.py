@@ -98,6 +98,9 @@ def shifted_window_sources(geo: WindowGeometry, shifted: bool):
     return part(src_win), part(src_tok), part(reg)
 
 
+MAX_KERNEL_WINDOW_TOKENS = 128      # window_attn.cu keeps a whole window in shared memory
+
+
 def attention_core_reference(q, k, v, scale, bias, mask):
     """q,k,v: [nWin, nH, Nq|N, hd] fp32; bias [nH, Nq, N] or None; mask [nWin, Nq, N] additive or None."""
     attn = (q * scale) @ k.transpose(-2, -1)
@@ -108,8 +111,22 @@ def attention_core_reference(q, k, v, scale, bias, mask):
     return torch.softmax(attn, dim=-1) @ v
 
 
+def attention_core_sdpa(q, k, v, scale, bias, mask):
+    """Same contract as ``attention_core_reference`` on PyTorch's fused attention: no ``[N, N]`` score tensor is kept
+    for autograd, and without bias and mask the flash kernel runs, so windows of thousands of tokens fit. Used for
+    windows above the 128 tokens that ``window_attn.cu`` holds in shared memory."""
+    add = None
+    if bias is not None:
+        add = bias.unsqueeze(0).to(q.dtype)
+    if mask is not None:
+        m = mask.unsqueeze(1).to(q.dtype)
+        add = m if add is None else add + m
+    return torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=add, scale=scale)
+
+
 def window_attention_reference(qkv_all: torch.Tensor, geo: WindowGeometry, num_heads: int, shifted: bool,
-                               bias_table: Optional[torch.Tensor], use_mask: bool, scale: float) -> torch.Tensor:
+                               bias_table: Optional[torch.Tensor], use_mask: bool, scale: float,
+                               core=None) -> torch.Tensor:
     """Reference on the *global* window-major tensor ``[B, nW_total, N, 3C]`` -> ``[B, nW_total, N, C]``
     (single rank view; rows are gathered with explicit index tensors)."""
     B, nW, N = geo.B, geo.nWh * geo.nWw, geo.N
@@ -128,7 +145,7 @@ def window_attention_reference(qkv_all: torch.Tensor, geo: WindowGeometry, num_h
         reg = reg.to(qkv_all.device)
         mask = (reg[:, :, None] != reg[:, None, :]).to(q.dtype) * -100.0
         mask = mask.repeat(B, 1, 1)
-    o = attention_core_reference(q, k, v, scale, bias, mask)                     # [B*nW, nH, N, hd]
+    o = (core or attention_core_reference)(q, k, v, scale, bias, mask)          # [B*nW, nH, N, hd]
     o = o.permute(0, 2, 1, 3).reshape(B, nW * N, C)
     out = torch.empty_like(o)
     out[:, flat_src.reshape(-1)] = o
@@ -194,6 +211,16 @@ def window_attention(qkv: torch.Tensor, geo: WindowGeometry, num_heads: int, shi
     """``qkv``: ``[rows_local, 3C]`` -> ``[rows_local, C]``. ``comm`` supplies peer access for multi-rank layouts
     (``None``: this rank owns every window and token)."""
     fused = comm is None or getattr(comm, "fused", False)
+    if qkv.is_cuda and geo.N > MAX_KERNEL_WINDOW_TOKENS:
+        # large windows (the reference's fine-tuning configs go up to 180 x 180): PyTorch's fused attention on the
+        # gathered windows; single-owner layouts only (every window and token on this rank)
+        if comm is not None and getattr(comm, "world", 1) > 1:
+            raise NotImplementedError(f"windows of {geo.N} tokens are supported on single-owner layouts only "
+                                      f"(the peer-memory kernel holds at most {MAX_KERNEL_WINDOW_TOKENS} tokens)")
+        C = qkv.shape[-1] // 3
+        out = window_attention_reference(qkv.reshape(geo.B, geo.nWh * geo.nWw, geo.N, 3 * C), geo, num_heads, shifted,
+                                         bias_table, use_mask, scale, core=attention_core_sdpa)
+        return out.reshape(-1, C)
     if qkv.is_cuda and fused:
         return _WindowAttnFn.apply(qkv, bias_table, geo, num_heads, shifted, use_mask, scale, comm)
     if comm is not None and comm.world > 1:

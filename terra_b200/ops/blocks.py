@@ -18,7 +18,7 @@ import torch
 import torch.nn.functional as TF
 
 from .. import _ext
-from .attention import WindowGeometry, window_attention
+from .attention import MAX_KERNEL_WINDOW_TOKENS, WindowGeometry, window_attention
 from .gemm import gemm, status_word
 
 LN_EPS = 1e-5
@@ -176,9 +176,38 @@ class _LinearFn(torch.autograd.Function):
         return dx, None, None, None, None, None, (dy if has_res else None), None
 
 
+class LayerNormFn(torch.autograd.Function):
+    """Standalone LayerNorm on the CUDA kernels (where the norm is not fused into a block half: in front of a
+    collective, or for windows too large for the fused attention half). ``weight`` / ``bias`` are arena parameters;
+    their gradients are accumulated in place."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        y, mean, rstd = layernorm_cuda(x, weight.bf16, bias.bf16)
+        ctx.save_for_backward(x, mean, rstd)
+        ctx.p = (weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, mean, rstd = ctx.saved_tensors
+        weight, bias = ctx.p
+        dx = layernorm_bwd_cuda(dy.contiguous(), x, weight.bf16, mean, rstd, weight.grad, bias.grad)
+        return dx, None, None
+
+
 # ------------------------------------------------------------------------------------------------ public entry points
 def attention_half(x, mod, geo: WindowGeometry, shifted: bool, comm=None):
     """x + proj(window_attention(qkv(norm1(x)))) for a ``SwinAttentionHalf`` module ``mod``."""
+    if x.is_cuda and geo.N > MAX_KERNEL_WINDOW_TOKENS:
+        # large windows: the fused half needs the shared-memory kernel; compose the half from its parts instead
+        a = mod.attn
+        xn = LayerNormFn.apply(x.contiguous(), mod.norm1.weight, mod.norm1.bias)
+        qkv = torch.cat([linear(xn, a.q_linear), linear(xn, a.k_linear), linear(xn, a.v_linear)], dim=-1)
+        o = window_attention(qkv, geo, a.num_heads, shifted,
+                             a.relative_position_bias_table if a.use_relative_position_bias else None,
+                             mod.use_attn_mask, a.scale, comm)
+        return linear(o.to(x.dtype).contiguous(), a.proj, residual=x)
     if x.is_cuda:
         fused = getattr(mod.attn, "fused", None)
         if fused is None:

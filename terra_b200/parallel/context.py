@@ -290,22 +290,7 @@ class ParallelContext:
         return cache[key]
 
 
-class _LayerNormFn(torch.autograd.Function):
-    """Standalone LayerNorm on the CUDA kernels (used where the norm is followed by a collective)."""
-
-    @staticmethod
-    def forward(ctx, x, weight, bias):
-        y, mean, rstd = B.layernorm_cuda(x, weight.bf16, bias.bf16)
-        ctx.save_for_backward(x, mean, rstd)
-        ctx.p = (weight, bias)
-        return y
-
-    @staticmethod
-    def backward(ctx, dy):
-        x, mean, rstd = ctx.saved_tensors
-        weight, bias = ctx.p
-        dx = B.layernorm_bwd_cuda(dy.contiguous(), x, weight.bf16, mean, rstd, weight.grad, bias.grad)
-        return dx, None, None
+_LayerNormFn = B.LayerNormFn
 
 
 class _PortableAttnComm:

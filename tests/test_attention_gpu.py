@@ -42,3 +42,25 @@ def test_window_attention_fwd_bwd(B, nWh, nWw, wh, ww, C, heads, shifted, use_bi
     _close(qkv.grad, q32.grad)
     if use_bias:
         _close(table.grad, t32.grad, rtol=3e-2, atol=5e-2)
+
+
+def test_large_window_attention_on_cuda():
+    """144-token windows (above the shared-memory kernel's 128) run on the fused-attention path, forward and backward."""
+    from terra_b200.ops.attention import WindowGeometry, window_attention, window_attention_reference
+
+    torch.manual_seed(3)
+    B, nWh, nWw, w, C, heads = 1, 2, 3, 12, 64, 4
+    geo = WindowGeometry(B, nWh, nWw, w, w)
+    N, nW = w * w, nWh * nWw
+    qkv = (torch.randn(B * nW * N, 3 * C, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    table = (torch.randn((2 * w - 1) ** 2, heads, device="cuda") * 0.2).requires_grad_(True)
+    out = window_attention(qkv, geo, heads, True, table, True, (C // heads) ** -0.5)
+    dout = (torch.randn_like(out.float()) * 0.5).to(torch.bfloat16)
+    out.backward(dout)
+    q32 = qkv.detach().float().requires_grad_(True)
+    t32 = table.detach().clone().requires_grad_(True)
+    ref = window_attention_reference(q32.reshape(B, nW, N, 3 * C), geo, heads, True, t32, True, (C // heads) ** -0.5).reshape(-1, C)
+    ref.backward(dout.float())
+    _close(out, ref)
+    _close(qkv.grad, q32.grad)
+    _close(table.grad, t32.grad, rtol=3e-2, atol=5e-2)

@@ -164,3 +164,20 @@ def test_bind_to_gpu_numa_with_fake_nvml(monkeypatch):
         assert D.bind_to_gpu_numa(0) is False
     finally:
         os.sched_setaffinity(0, before)
+
+
+def test_large_window_attention_core_matches_reference():
+    """Windows above the kernel's 128 tokens run on the fused-attention core; same result as the explicit softmax."""
+    import torch
+
+    from terra_b200.ops.attention import (WindowGeometry, attention_core_sdpa, window_attention_reference)
+
+    torch.manual_seed(0)
+    geo = WindowGeometry(1, 2, 2, 12, 12)                      # 144 tokens per window
+    C, heads = 32, 4
+    qkv = torch.randn(1, 4, geo.N, 3 * C)
+    table = torch.randn((2 * 12 - 1) ** 2, heads) * 0.2
+    for shifted in (False, True):
+        ref = window_attention_reference(qkv, geo, heads, shifted, table, True, 8 ** -0.5)
+        got = window_attention_reference(qkv, geo, heads, shifted, table, True, 8 ** -0.5, core=attention_core_sdpa)
+        assert torch.allclose(ref, got, atol=1e-5, rtol=1e-4)
