@@ -83,6 +83,11 @@ def one_step_train(task_type, model_type, model, engine, optimizer, required_ten
 
     grad_post_process(model_type, optimizer_state_tuple or (False, False, -1, False), model, manager,
                       dp_average=not hasattr(model, "module"))
+    tsd = task_specific_data_dict or {}
+    if tsd.get("show_gradient_flag") and getattr(optimizer, "global_step", 0) == int(tsd.get("test_iter_num", -1)) - 1:
+        from .grad_debug import show_gradient
+
+        show_gradient(model, manager, getattr(manager, "xfmr_tp_group", None) if manager is not None else None)
     if clip_grad and precision == "fp16":
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
     mark_memory_timeline("before_optimizer")

@@ -181,3 +181,39 @@ def test_large_window_attention_core_matches_reference():
         ref = window_attention_reference(qkv, geo, heads, shifted, table, True, 8 ** -0.5)
         got = window_attention_reference(qkv, geo, heads, shifted, table, True, 8 ** -0.5, core=attention_core_sdpa)
         assert torch.allclose(ref, got, atol=1e-5, rtol=1e-4)
+
+
+def test_show_gradient_lists_first_and_last_block():
+    import torch
+
+    from terra_b200.runtime.grad_debug import install_grad_hooks, show_gradient
+
+    class Blk(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm1 = torch.nn.LayerNorm(4)
+            self.norm2 = torch.nn.LayerNorm(4)
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.patch_embed = torch.nn.Linear(4, 4)
+            self.blocks = torch.nn.ModuleList([Blk() for _ in range(3)])
+
+        def forward(self, x):
+            x = self.patch_embed(x)
+            for b in self.blocks:
+                x = b.norm2(b.norm1(x))
+            return x
+
+    m = M()
+    seen = []
+    handles = install_grad_hooks(m, limit=3, printer=seen.append)
+    m(torch.randn(2, 4)).sum().backward()
+    assert len(seen) == 3 and all(s.startswith("[grad hook]") for s in seen)
+    for h in handles:
+        h.remove()
+    lines = show_gradient(m, printer=lambda s: None)
+    names = [ln.split()[3].rstrip(":") for ln in lines]
+    assert "patch_embed.weight" in names and "blocks.0.norm1.weight" in names and "blocks.2.norm2.bias" in names
+    assert not any(n.startswith("blocks.1.") for n in names)

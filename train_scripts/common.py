@@ -73,6 +73,14 @@ class Session:
         self.model, self.engine, self.optimizer, self.gscaler, self.opt_state = get_model_for_train(
             self.archi, self.cfg, self.task_type, self.model_type, o["embedding_parallel_type"], o["attn_parallel_type"],
             o["mlp_parallel_type"], self.manager, self.device, self.cfg.get("kaiming_init", True))
+        from terra_b200 import global_env_config as G
+
+        if G.DEBUG_GRAD_HOOK and self.device.type != "cuda":
+            # (on CUDA the fused kernels accumulate into the flat gradient arena without autograd leaf gradients;
+            # there `show_gradient_flag` prints the arena's sums after the backward pass instead)
+            from terra_b200.runtime.grad_debug import install_grad_hooks
+
+            self.grad_hooks = install_grad_hooks(self.model)
         self.precision = self.cfg["precision"]
         self.my_dtype = dtype_from_precision(self.precision)
         self.criterion = get_criterion(self.cfg["loss_func"])
