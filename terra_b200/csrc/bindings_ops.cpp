@@ -49,8 +49,11 @@ void layernorm_bwd(const torch::Tensor& dy, const torch::Tensor& x, const torch:
 void colsum(const torch::Tensor& x, torch::Tensor& out) {
   need(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == torch::kBFloat16, "colsum: 2-D bf16");
   const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t nparts = (x.size(0) + tb::colsum_rows_per_block() - 1) / tb::colsum_rows_per_block();
+  auto partials = torch::empty({nparts, x.size(1)}, x.options().dtype(torch::kFloat32));
   tb::note_launch();
-  rc_check(tb::colsum_bf16(x.data_ptr(), out.data_ptr<float>(), x.size(0), x.size(1), x.stride(0), cur_stream()),
+  rc_check(tb::colsum_bf16(x.data_ptr(), out.data_ptr<float>(), partials.data_ptr<float>(), x.size(0), x.size(1), x.stride(0),
+                           cur_stream()),
            "colsum");
 }
 

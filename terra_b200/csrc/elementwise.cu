@@ -1,5 +1,6 @@
 // Memory-bound kernels: LayerNorm, GroupNorm(+SiLU), column sums, masked loss, fused AdamW.
 // All are single-pass over HBM where the math allows it, with 16-byte vector accesses.
+#include <cstdlib>
 #include "common.cuh"
 #include "host_api.h"
 
@@ -190,9 +191,10 @@ __global__ void __launch_bounds__(256, (VPL <= 2) ? 2 : 1) layernorm_bwd_kernel(
 }
 
 // ------------------------------------------------------------------------------------------ column sums
-__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
+__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ partials,
                                                      long long rows, int C, long long ld, int rows_per_block) {
-  // thread -> one 8-wide column vector; blockDim.y rows in flight
+  // thread -> one 8-wide column vector; blockDim.y rows in flight. blockDim.x spans the whole row when it has at most
+  // 64 vectors (a row is then one contiguous read), otherwise 32 vectors per block column.
   const int nvec = C >> 3;
   const int vi = blockIdx.y * blockDim.x + threadIdx.x;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -221,19 +223,39 @@ __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __rest
       for (int j = 0; j < 8; ++j) acc[j] += f[j];
     }
   }
-  __shared__ float sh[8][32 * 8 + 1];
-  if (threadIdx.x < 32) {
+  extern __shared__ float csh[];              // [blockDim.y][blockDim.x * 8 + 1]
+  const int pitch = blockDim.x * 8 + 1;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sh[threadIdx.y][threadIdx.x * 8 + j] = acc[j];
-  }
+  for (int j = 0; j < 8; ++j) csh[threadIdx.y * pitch + threadIdx.x * 8 + j] = acc[j];
   __syncthreads();
   if (threadIdx.y == 0 && vi < nvec) {
+    // one partial row per row block: many blocks adding into the same few hundred addresses serialise in L2
+    // (about 80 ns per atomic on one address), so the partials are written out and a second kernel adds them up
+    float* prow = partials + static_cast<long long>(blockIdx.x) * C;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float s = 0.f;
-      for (int y = 0; y < blockDim.y; ++y) s += sh[y][threadIdx.x * 8 + j];
-      atomicAdd(&out[vi * 8 + j], s);
+      for (int y = 0; y < blockDim.y; ++y) s += csh[y * pitch + threadIdx.x * 8 + j];
+      prow[vi * 8 + j] = s;
     }
+  }
+}
+
+// out[c] += sum over r of partials[r][c]. Block = 32 columns x 32 row lanes.
+__global__ void __launch_bounds__(1024) colsum_finish_kernel(const float* __restrict__ partials, float* __restrict__ out,
+                                                             int nparts, int C) {
+  __shared__ float sh[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float s = 0.f;
+  if (c < C)
+    for (int r = threadIdx.y; r < nparts; r += 32) s += partials[static_cast<long long>(r) * C + c];
+  sh[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 32; ++y) t += sh[y][threadIdx.x];
+    out[c] += t;
   }
 }
 
@@ -560,13 +582,21 @@ int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float*
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int colsum_bf16(const void* x, float* out, long long rows, int C, long long ld, cudaStream_t stream) {
-  if (C % 8 != 0) return -1;
+int colsum_rows_per_block() { return 256; }
+
+// out[c] += sum over rows of x[r][c]. `partials`: fp32 scratch of ceil(rows / colsum_rows_per_block()) x C elements.
+int colsum_bf16(const void* x, float* out, float* partials, long long rows, int C, long long ld, cudaStream_t stream) {
+  if (C % 8 != 0 || partials == nullptr) return -1;
   const int nvec = C / 8;
-  dim3 block(32, 8);
-  const int rows_per_block = 512;
-  dim3 grid(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block), (nvec + 31) / 32);
-  colsum_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), out, rows, C, ld, rows_per_block);
+  const int bx = nvec <= 64 ? nvec : 32;
+  const int by = 256 / bx > 0 ? 256 / bx : 1;
+  dim3 block(bx, by);
+  const int rows_per_block = colsum_rows_per_block();
+  const int nparts = static_cast<int>((rows + rows_per_block - 1) / rows_per_block);
+  dim3 grid(static_cast<unsigned>(nparts), (nvec + bx - 1) / bx);
+  const size_t sh = static_cast<size_t>(by) * (bx * 8 + 1) * sizeof(float);
+  colsum_kernel<<<grid, block, sh, stream>>>(static_cast<const __nv_bfloat16*>(x), partials, rows, C, ld, rows_per_block);
+  colsum_finish_kernel<<<(C + 31) / 32, dim3(32, 32), 0, stream>>>(partials, out, nparts, C);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -69,7 +69,9 @@ int layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, f
 int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
                   float* dgamma, float* dbeta, const void* dres, long long rows, int C, cudaStream_t stream);
 // Column sums of a bf16 [rows, C] matrix into fp32 out[C] (atomic accumulate; caller zeroes out).
-int colsum_bf16(const void* x, float* out, long long rows, int C, long long ld, cudaStream_t stream);
+int colsum_rows_per_block();
+// out[c] += column sums of the bf16 matrix x; partials: fp32 scratch of ceil(rows / colsum_rows_per_block()) x C
+int colsum_bf16(const void* x, float* out, float* partials, long long rows, int C, long long ld, cudaStream_t stream);
 // GroupNorm statistics over NHWC bf16 [B, HW, C]: accumulates per (b, group) sum and sum of squares (fp32, zeroed).
 int groupnorm_stats(const void* x, float* sums, int B, long long HW, int C, int groups, cudaStream_t stream);
 // y = silu((x - mean) * rstd * gamma + beta) [+ res]; `stats` holds {mean, rstd} per (b, group).

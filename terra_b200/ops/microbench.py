@@ -7,7 +7,7 @@ fallback figures 6.65 TB/s / 1.59 PFLOP/s). ``--launches N --no-time`` just runs
 used under ``ncu`` (the capture then picks the kernel by name).
 
 Cases: ``gemm`` (``--epilogue none|bias|gelu|residual|dgelu|wgrad``), ``attn`` (``--bwd``), ``conv`` (``--stride``,
-``--wgrad``), ``layernorm`` (``--bwd``), ``groupnorm``, ``adamw``.
+``--wgrad``), ``layernorm`` (``--bwd``), ``groupnorm``, ``adamw``, ``colsum``.
 """
 from __future__ import annotations
 
@@ -180,6 +180,13 @@ def case_groupnorm(a):
     return fn, 0.0, B * HW * C * 2 * 3
 
 
+def case_colsum(a):
+    ext = _ext.load()
+    x = _rand(a.m, a.c)
+    out = torch.zeros(a.c, device="cuda")
+    return (lambda: ext.colsum(x, out)), 0.0, a.m * a.c * 2
+
+
 def case_adamw(a):
     ext = _ext.load()
     n = a.m
@@ -190,7 +197,7 @@ def case_adamw(a):
 
 
 CASES = {"gemm": case_gemm, "attn": case_attn, "conv": case_conv, "layernorm": case_layernorm,
-         "groupnorm": case_groupnorm, "adamw": case_adamw}
+         "groupnorm": case_groupnorm, "adamw": case_adamw, "colsum": case_colsum}
 
 
 def main(argv=None):
