@@ -324,7 +324,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     // lanes on neighbouring addresses. Every transfer of a 32 x 32 chunk (output, saved pre-activation, residual,
     // GELU input) therefore goes through the warp's 2 KB exchange buffer: row-per-lane on one side, four lanes per
     // row (eight rows, 64 contiguous bytes each, per instruction) on the global side. 16-byte vectors are XOR
-    // swizzled by (row >> 1) so both access patterns are free of bank conflicts.
+    // swizzled by (row >> 1); the profiler still counts about two wavefronts per ideal one on the row-gathering
+    // side (a padded 80-byte pitch measured worse), which costs a few percent of the short-K GEMMs.
     const int q = warp & 3;               // TMEM lane quadrant this warp may read
     const int part = (warp - 2) >> 2;     // chunks part, part + 4, ... of the tile's 32-column chunks
     constexpr int CHUNKS = BN / 32;
