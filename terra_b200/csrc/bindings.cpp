@@ -36,7 +36,8 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
           const c10::optional<torch::Tensor>& aux, const c10::optional<torch::Tensor>& c2, double alpha,
           int64_t split_k, int64_t bn, const c10::optional<torch::Tensor>& status, int64_t shuffle_cout,
           int64_t out_w, int64_t out_h, int64_t sms, const std::vector<int64_t>& a_peer_ptrs, int64_t rank,
-          const std::vector<int64_t>& c_peer_ptrs, int64_t a_flags_ptr, int64_t a_epoch, int64_t a_budget_ns) {
+          const std::vector<int64_t>& c_peer_ptrs, int64_t a_flags_ptr, int64_t a_epoch, int64_t a_budget_ns,
+          int64_t a_interleave, int64_t a_chunks) {
   check_bf16_2d(a, "a");
   check_bf16_2d(b, "b");
   const c10::cuda::CUDAGuard guard(a.device());
@@ -82,6 +83,8 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
   peers.a_flags = reinterpret_cast<const void*>(a_flags_ptr);
   peers.a_epoch = static_cast<unsigned int>(a_epoch);
   peers.a_budget_ns = static_cast<unsigned long long>(a_budget_ns);
+  peers.a_interleave = static_cast<int>(a_interleave);
+  peers.a_chunks = static_cast<int>(a_chunks);
   if (c_peer_ptrs.size() > 1) {
     peers.c_peers = static_cast<int>(c_peer_ptrs.size());
     TORCH_CHECK(M % peers.c_peers == 0, "gemm: rows not divisible by the number of owners");

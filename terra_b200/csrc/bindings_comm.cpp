@@ -77,6 +77,20 @@ void peer_signal(const std::vector<int64_t>& pad_ptrs, int64_t my_rank, int64_t 
               "peer_signal launch failed");
 }
 
+// stream: a cudaStream_t as an integer (torch.cuda.Stream.cuda_stream)
+void gather_shards_async(int64_t stream, int64_t dst, const std::vector<int64_t>& src_ptrs, int64_t my_rank, int64_t rows,
+                         int64_t row_bytes, int64_t chunks, int64_t chunk_rows, int64_t signals_ptr, int64_t ready_ptr,
+                         int64_t epoch) {
+  std::vector<const void*> p;
+  for (auto v : src_ptrs) p.push_back(reinterpret_cast<const void*>(v));
+  const int rc = tb::gather_shards_async(reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<void*>(dst), p.data(),
+                                         static_cast<int>(p.size()), static_cast<int>(my_rank), rows,
+                                         static_cast<size_t>(row_bytes), static_cast<int>(chunks), chunk_rows,
+                                         reinterpret_cast<const unsigned int*>(signals_ptr),
+                                         reinterpret_cast<unsigned int*>(ready_ptr), static_cast<unsigned int>(epoch));
+  TORCH_CHECK(rc == 0, "gather_shards_async failed with code ", rc);
+}
+
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
@@ -85,4 +99,5 @@ void bind_comm(pybind11::module_& m) {
   m.def("peer_sum_small", &peer_sum_small);
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_signal", &peer_signal);
+  m.def("gather_shards_async", &gather_shards_async);
 }

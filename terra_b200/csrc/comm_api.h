@@ -1,6 +1,7 @@
 // Peer-memory (NVLink / NVSwitch) communication kernels. Buffers live in symmetric memory: every rank of a group
 // allocated the same layout, so a kernel addresses a peer's copy as peer_base + the same offset.
 #pragma once
+#include <cstddef>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -33,6 +34,12 @@ int peer_sum_small(float* dst, const float* const* src_peers, int num_peers, int
 
 // Group barrier on a symmetric signal pad: every rank adds 1 to its slot on all peers, then waits (bounded) until
 // its own pad shows `epoch` from everyone. `status` receives TB_ERR_PEER_TIMEOUT when the wait runs out.
+// stream_ops.cpp: SM-free pieces of the all-gather that overlaps a persistent GEMM (stream memory operations + copy engine)
+int stream_wait_geq32(cudaStream_t stream, const void* addr, unsigned int value);
+int stream_write32(cudaStream_t stream, void* addr, unsigned int value);
+int gather_shards_async(cudaStream_t stream, void* dst, const void* const* src, int num_peers, int my_rank, long long rows,
+                        size_t row_bytes, int chunks, long long chunk_rows, const unsigned int* signals, unsigned int* ready,
+                        unsigned int epoch);
 // One-way "my earlier writes are visible" signal into word [slot_base + my_rank] of every peer's pad.
 int peer_signal(uint32_t* const* signal_pads, int my_rank, int num_peers, int slot_base, cudaStream_t stream);
 int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,

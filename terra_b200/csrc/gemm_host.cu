@@ -145,6 +145,9 @@ int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, lon
     p.a_flags = static_cast<const unsigned int*>(peers.a_flags);
     p.a_epoch = peers.a_epoch;
     p.a_budget_ns = peers.a_budget_ns > 0 ? peers.a_budget_ns : 2000000000ull;
+    p.a_interleave = peers.a_interleave;
+    p.a_chunks = peers.a_chunks < 1 ? 1 : (peers.a_chunks > 4 ? 4 : peers.a_chunks);
+    p.a_chunk_tiles = (p.a_tiles + p.a_chunks - 1) / p.a_chunks;
     p.num_m_tiles = p.a_tiles * p.a_peers;
     for (int i = 0; i < peers.a_peers; ++i) {
       const int rc_i = map_2d(&p.map_a_peer[i], peers.a_ptr[i], K, peers.a_rows, A.ld, GEMM_BK, GEMM_BM);

@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       uint32_t it = 0;
       const long long t_begin = clock64();
       long long t_wait = 0;
-      unsigned int peers_ready = (PEERS && p.a_peers > 1) ? (1u << p.a_first) : 0u;   // the own shard needs no signal
+      unsigned int peers_ready = 0u;   // bit per (peer, chunk) whose flag has been seen
       for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units) {
         const TileCoord tc = decode_tile(p, tile, CTAS, rank);
         const int m0 = tc.m_blk * GEMM_BM;
@@ -184,13 +184,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           // ---- operand A
           if (p.a_mode == OP_KMAJOR_2D) {
             if (PEERS && p.a_peers > 1) {
-              const int peer = (tc.m_blk % p.a_peers + p.a_first) % p.a_peers;
-              if (p.a_flags != nullptr && !((peers_ready >> peer) & 1u)) {
+              const int slot = p.a_interleave ? tc.m_blk % p.a_peers : tc.m_blk / p.a_tiles;
+              const int lm = p.a_interleave ? tc.m_blk / p.a_peers : tc.m_blk % p.a_tiles;
+              const int peer = (slot + p.a_first) % p.a_peers;
+              const int fidx = peer * p.a_chunks + min(lm / p.a_chunk_tiles, p.a_chunks - 1);
+              if (p.a_flags != nullptr && peer != p.a_first && !((peers_ready >> fidx) & 1u)) {
                 // first tile from this peer: its shard must have been published (bounded wait on its flag)
                 const unsigned long long w_begin = global_timer_ns();
                 unsigned int seen, polls = 0;
                 while (true) {
-                  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.a_flags + peer) : "memory");
+                  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.a_flags + fidx) : "memory");
                   if (static_cast<int>(seen - p.a_epoch) >= 0) break;
                   if ((++polls & 31u) == 0u && global_timer_ns() - w_begin > p.a_budget_ns) {
                     *abort_flag = 1;
@@ -201,9 +204,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
                 }
                 if (*abort_flag) break;
                 fence_proxy_async_all();   // order the acquire before the asynchronous-proxy reads of the shard
-                peers_ready |= 1u << peer;
+                peers_ready |= 1u << fidx;
               }
-              tma_load_2d(sA, &p.map_a_peer[peer], &full[s], kb * GEMM_BK, (tc.m_blk / p.a_peers) * GEMM_BM);
+              tma_load_2d(sA, &p.map_a_peer[peer], &full[s], kb * GEMM_BK, lm * GEMM_BM);
             } else {
               tma_load_2d(sA, &p.map_a, &full[s], kb * GEMM_BK, m0);
             }
@@ -364,8 +367,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const int qd = n0 / p.shuffle_cout;
           return ((b * 2 * p.out_h + 2 * h + (qd >> 1)) * 2 * p.out_w) + 2 * w + (qd & 1);
         } else if (PEERS && p.a_peers > 1) {
-          const int peer = (tc.m_blk % p.a_peers + p.a_first) % p.a_peers;
-          const int lr = (tc.m_blk / p.a_peers) * GEMM_BM + r;
+          const int slot = p.a_interleave ? tc.m_blk % p.a_peers : tc.m_blk / p.a_tiles;
+          const int peer = (slot + p.a_first) % p.a_peers;
+          const int lr = (p.a_interleave ? tc.m_blk / p.a_peers : tc.m_blk % p.a_tiles) * GEMM_BM + r;
           return (lr < p.a_rows) ? static_cast<long long>(peer) * p.a_rows + lr : -1;
         } else {
           const long long g = static_cast<long long>(tc.m_blk) * GEMM_BM + r;

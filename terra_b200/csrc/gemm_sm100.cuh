@@ -81,6 +81,8 @@ struct GemmParams {
   //    fp32 atomic output: vector reductions into row g % c_rows of the owner's accumulation buffer. bf16 output:
   //    plain stores into slot c_slot (this GPU's) of the owner's [c_peers][c_rows] staging, which the owner sums.
   int a_peers, a_rows, a_tiles, a_first;
+  int a_interleave;            // 1: local and remote tiles alternate (direct peer loads); 0: own shard first, then peer by peer
+  int a_chunks, a_chunk_tiles; // flags per peer: flag [peer * a_chunks + tile / a_chunk_tiles] covers a_chunk_tiles m tiles
   CUtensorMap map_a_peer[8];
   const unsigned int* a_flags;
   unsigned int a_epoch;

@@ -36,6 +36,8 @@ struct GemmPeers {
   const void* a_flags;        // optional: uint32 flags, one per peer, in this GPU's memory; a_flags[i] >= a_epoch means
   unsigned int a_epoch;       // "peer i's shard is written"; the kernel waits for it (at most a_budget_ns) itself
   unsigned long long a_budget_ns;
+  int a_interleave;           // 1: alternate local / remote tiles (direct peer loads); 0: own shard first
+  int a_chunks;               // flags per peer (1..4); flag [i * a_chunks + c] covers chunk c of peer i's rows
   int c_peers;
   void* c_ptr[8];    // fp32 [c_rows, N] accumulation buffers (atomic epilogue) or bf16 [c_peers][c_rows, N] staging (plain)
   long long c_rows;

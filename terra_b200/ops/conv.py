@@ -144,7 +144,7 @@ class _ConvT2x2Fn(torch.autograd.Function):
             # every BN-wide column tile lies inside one (dy, dx) phase: the epilogue stores it pixel-shuffled
             flags = F.EPI_BIAS | F.EPI_ROW_SHUFFLE
             ext.gemm(x2, False, wt, False, y.view(-1, Cout), flags, b16.repeat(4), None, None, None, 1.0, 1, bn,
-                     status_word(x.device), Cout, W, H, 0, [], 0, [], 0, 0, 0)
+                     status_word(x.device), Cout, W, H, 0, [], 0, [], 0, 0, 0, 1, 1)
         else:
             flat = gemm(x2, wt, bias=b16.repeat(4))
             y.copy_(flat.view(B, H, W, 2, 2, Cout).permute(0, 1, 3, 2, 4, 5).reshape(B, 2 * H, 2 * W, Cout))

@@ -65,6 +65,8 @@ def gemm(
     a_flags: int = 0,
     a_epoch: int = 0,
     a_budget_ns: int = 0,
+    a_interleave: bool = True,
+    a_chunks: int = 1,
 ):
     """Returns ``out`` (and the saved pre-activation when ``save_pre``).
 
@@ -115,7 +117,7 @@ def gemm(
               file=sys.stderr, flush=True)
     ext.gemm(a, a_mn, b, b_mn, out, flags, bias, residual, dgelu_aux, pre, float(alpha), int(split_k), int(bn),
              status_word(a.device), 0, 0, 0, int(sms), list(a_peers or []), int(rank), list(out_peers or []),
-             int(a_flags), int(a_epoch), int(a_budget_ns))
+             int(a_flags), int(a_epoch), int(a_budget_ns), int(bool(a_interleave)), int(a_chunks))
     if save_pre:
         return out, pre
     return out

@@ -28,6 +28,7 @@ class TpFusedComm:
     def __init__(self, arena):
         self.arena = arena
         self.rank, self.world = arena.rank, arena.world
+        self.side: Optional[torch.cuda.Stream] = None   # stream of the copy-engine gather
 
     # ---- all-gather -> GEMM
     def stage(self, x: torch.Tensor) -> torch.Tensor:
@@ -41,16 +42,49 @@ class TpFusedComm:
             return staged
 
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, bias=None, gelu=False,
-                save_pre=False, dgelu_aux=None):
+                save_pre=False, dgelu_aux=None, via_copy_engine: Optional[bool] = None):
         """``concat_ranks(x_shard) @ w^T`` (or ``@ w`` with ``b_mn``) with the usual fused epilogues. No barrier in
-        front: every rank publishes its shard with a one-way signal and the GEMM's TMA thread waits for a peer's
-        signal right before its first tile from that peer, while the tiles of the own shard are already computing.
+        front: every rank publishes its shard with a one-way signal and the GEMM's TMA thread waits (bounded) for
+        what it needs right before its first tile of a peer's rows, while the tiles of the own shard are computing.
+
+        Two transports. Direct: the GEMM's TMA loads read the peers' shards over NVLink - every output column tile
+        fetches its A tiles again (a peer's memory is not cached in the local L2), so this is for outputs of one
+        column tile (N <= 256). Copy engine (default for wider outputs): a side stream waits for each peer's signal
+        with a stream memory operation, copies the shard into local memory with the copy engines and publishes
+        "ready" with another stream memory operation, all without an SM (a kernel could not be scheduled beside the
+        persistent GEMM); the GEMM reads local memory and waits on the ready words. The shard crosses NVLink once.
         The staged shards stay untouched until the next barrier of the group (``gemm_rs`` ends with one)."""
         staged = self.stage(x_shard)
         epoch = self.arena.publish()
-        return gemm(staged, w, b_mn=b_mn, bias=bias, gelu=gelu, save_pre=save_pre, dgelu_aux=dgelu_aux,
-                    a_peers=self.arena.peer_ptrs(staged), rank=self.rank, a_flags=self.arena.signal_flags_ptr,
-                    a_epoch=epoch, a_budget_ns=PEER_WAIT_NS)
+        N = w.shape[1] if b_mn else w.shape[0]
+        if via_copy_engine is None:
+            via_copy_engine = N > 256
+        kw = dict(b_mn=b_mn, bias=bias, gelu=gelu, save_pre=save_pre, dgelu_aux=dgelu_aux, rank=self.rank, a_epoch=epoch,
+                  a_budget_ns=PEER_WAIT_NS)
+        if not via_copy_engine:
+            return gemm(staged, w, a_peers=self.arena.peer_ptrs(staged), a_flags=self.arena.signal_flags_ptr, **kw)
+        rows, K = staged.shape
+        gathered = torch.empty(self.world * rows, K, dtype=staged.dtype, device=staged.device)
+        main = torch.cuda.current_stream(staged.device)
+        if self.side is None:
+            self.side = torch.cuda.Stream(staged.device)
+        gathered.record_stream(self.side)
+        self.side.wait_stream(main)                     # `gathered` exists, earlier users of the ready words are queued
+        row_bytes = K * staged.element_size()
+        nbytes = rows * row_bytes
+        # up to four pieces per peer, each a whole number of 128-row tiles: the GEMM starts on a peer's rows as soon
+        # as their piece has landed
+        tiles = (rows + 127) // 128
+        chunks = max(1, min(4, tiles))
+        chunk_tiles = (tiles + chunks - 1) // chunks
+        _ext.load().gather_shards_async(self.side.cuda_stream, gathered.data_ptr(), self.arena.peer_ptrs(staged),
+                                        self.rank, rows, row_bytes, chunks, chunk_tiles * 128,
+                                        self.arena.signal_flags_ptr, self.arena.ready_flags_ptr, epoch)
+        local = [gathered.data_ptr() + r * nbytes for r in range(self.world)]
+        local[self.rank] = staged.data_ptr()            # the own shard is read in place
+        out = gemm(staged, w, a_peers=local, a_flags=self.arena.ready_flags_ptr, a_interleave=False, a_chunks=chunks, **kw)
+        main.wait_stream(self.side)                     # the peers' shards have been read before this rank's next barrier
+        return out
 
     # ---- GEMM -> reduce-scatter
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, exact: bool = False) -> torch.Tensor:

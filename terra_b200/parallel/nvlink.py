@@ -117,6 +117,12 @@ class SymmetricArena:
         _ext.load().peer_signal(self.base_ptrs, self.rank, self.SIGNAL_SLOT)
         return self.signal_epoch
 
+    READY_SLOT = 128       # words [128, 128 + world): "peer's shard has been copied into local memory" (copy-engine gather)
+
+    @property
+    def ready_flags_ptr(self) -> int:
+        return self.base_ptrs[self.rank] + 4 * self.READY_SLOT
+
     @property
     def signal_flags_ptr(self) -> int:
         """Device address of this rank's ``[world]`` array of published counts (one per source rank)."""

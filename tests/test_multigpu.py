@@ -70,5 +70,5 @@ def test_fused_tensor_parallel_linears(n):
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-4000:])
     res = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("RESULT ")][-1][len("RESULT "):])
-    for key in ("ag_gemm", "gemm_rs", "gemm_rs_exact", "mlp_out", "mlp_dx", "mlp_dw1", "mlp_db1", "mlp_dw2"):
+    for key in ("ag_gemm", "ag_gemm_copy_engine", "gemm_rs", "gemm_rs_exact", "mlp_out", "mlp_dx", "mlp_dw1", "mlp_db1", "mlp_dw2"):
         assert res[key] < 3e-2, res

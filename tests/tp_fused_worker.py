@@ -20,11 +20,13 @@ def main():
     from terra_b200.parallel.nvlink import SymmetricArena
 
     rank, world, dev = init_distributed()
-    arena = SymmetricArena(dist.group.WORLD, 3 << 30 if timing else 256 << 20, dev)
+    arena = SymmetricArena(dist.group.WORLD, 6 << 30 if timing else 256 << 20, dev)
     comm = TpFusedComm(arena)
     x_sym = None
     torch.manual_seed(5)                      # same weights and global activations on every rank
     rows, C, F = (17408, 384, 1536) if timing else (328, 256, 512)    # rows per rank; 328 is not a tile multiple
+    if timing and len(sys.argv) > 2:
+        rows = int(sys.argv[2])
     Fs = F // world
     x_full = (torch.randn(rows * world, C, device=dev) * 0.5).to(torch.bfloat16)
     w1 = (torch.randn(F, C, device=dev) * 0.05).to(torch.bfloat16)
@@ -41,8 +43,9 @@ def main():
         return float((a.detach().float() - b.detach().float()).abs().max() / (b.detach().float().abs().max() + 1e-6))
 
     # ---- all-gather -> GEMM
-    y = comm.ag_gemm(x, w1s, bias=b1s)
-    res["ag_gemm"] = rel(y, x_full.float() @ w1s.float().t() + b1s.float())
+    ag_ref = x_full.float() @ w1s.float().t() + b1s.float()
+    res["ag_gemm"] = rel(comm.ag_gemm(x, w1s, bias=b1s, via_copy_engine=False), ag_ref)
+    res["ag_gemm_copy_engine"] = rel(comm.ag_gemm(x, w1s, bias=b1s, via_copy_engine=True), ag_ref)
     # ---- GEMM -> reduce-scatter
     h_full = (torch.randn(rows * world, F, device=dev) * 0.3).to(torch.bfloat16)
     hs = h_full[:, rank * Fs:(rank + 1) * Fs].contiguous()
@@ -95,7 +98,11 @@ def main():
 
         def fused_ag():
             arena.reset()
-            return comm.ag_gemm(x_sym, w1s, bias=b1s)
+            return comm.ag_gemm(x_sym, w1s, bias=b1s, via_copy_engine=False)
+
+        def fused_ag_ce():
+            arena.reset()
+            return comm.ag_gemm(x_sym, w1s, bias=b1s, via_copy_engine=True)
 
         def fused_rs_exact():
             arena.reset()
@@ -105,7 +112,7 @@ def main():
             arena.reset()
             return comm.gemm_rs(hs, w2s)
 
-        res["ms"] = {"nccl_ag_then_gemm": timed(nccl_ag_gemm), "fused_ag_gemm": timed(fused_ag),
+        res["ms"] = {"nccl_ag_then_gemm": timed(nccl_ag_gemm), "fused_ag_gemm_direct": timed(fused_ag), "fused_ag_gemm_copy_engine": timed(fused_ag_ce),
                      "gemm_then_nccl_rs": timed(nccl_gemm_rs), "fused_gemm_rs": timed(fused_rs), "fused_gemm_rs_fp32_atomics": timed(fused_rs_exact),
                      "local_gemm_same_shape": timed(lambda: gemm(gathered, w1s, bias=b1s)),
                      "shape": {"rows_per_rank": rows, "C": C, "F": F, "ranks": world}}
