@@ -217,3 +217,15 @@ def test_show_gradient_lists_first_and_last_block():
     names = [ln.split()[3].rstrip(":") for ln in lines]
     assert "patch_embed.weight" in names and "blocks.0.norm1.weight" in names and "blocks.2.norm2.bias" in names
     assert not any(n.startswith("blocks.1.") for n in names)
+
+
+def test_exposed_comm_accounting():
+    from terra_b200.profiler.exposed_comm import account, is_comm_kernel, union_length
+
+    assert union_length([(0, 2), (1, 3), (5, 6)]) == 4
+    assert is_comm_kernel("ncclDevKernel_AllReduce_Sum_f32_RING_LL") and is_comm_kernel("tb::peer_barrier_kernel")
+    assert not is_comm_kernel("void tb::gemm_tcgen05_kernel<192, 1, false>")
+    r = account([("gemm", 0.0, 4.0), ("ncclDevKernel_SendRecv", 3.0, 6.0), ("layernorm", 7.0, 8.0),
+                 ("tb::peer_barrier_kernel", 8.0, 9.0)])
+    assert r["span"] == 9.0 and r["compute_busy"] == 5.0 and r["comm_busy"] == 4.0
+    assert r["comm_hidden"] == 1.0 and r["exposed"] == 4.0
