@@ -183,6 +183,21 @@ void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int
   rc_check(tb::window_attn_bwd(a, cur_stream()), "window_attn_bwd");
 }
 
+void conv_s2_col2im(const torch::Tensor& dcol, torch::Tensor& out, int64_t W, int64_t r0) {
+  need(dcol.is_cuda() && dcol.is_contiguous() && dcol.scalar_type() == torch::kBFloat16 && dcol.dim() == 5 && dcol.size(3) == 9,
+       "conv_s2_col2im: dcol [B, Ho, Wo, 9, C] bf16 contiguous");
+  need(out.is_contiguous() && out.dim() == 4 && out.size(0) == dcol.size(0) && out.size(2) == W && out.size(3) == dcol.size(4) &&
+           (out.scalar_type() == torch::kBFloat16 || out.scalar_type() == torch::kFloat32),
+       "conv_s2_col2im: out [B, rows, W, C] bf16 or fp32 contiguous");
+  const c10::cuda::CUDAGuard guard(dcol.device());
+  tb::note_launch();
+  rc_check(tb::conv_s2_col2im(dcol.data_ptr(), out.data_ptr(), static_cast<int>(dcol.size(0)), static_cast<int>(dcol.size(1)),
+                              static_cast<int>(dcol.size(2)), static_cast<int>(W), static_cast<int>(dcol.size(4)),
+                              static_cast<int>(r0), static_cast<int>(out.size(1)),
+                              out.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()),
+           "conv_s2_col2im");
+}
+
 void sum_slots(const torch::Tensor& slots, torch::Tensor& out) {
   need(slots.is_cuda() && slots.is_contiguous() && slots.scalar_type() == torch::kBFloat16 && slots.dim() >= 2,
        "sum_slots: [slots, ...] bf16 contiguous");
@@ -207,6 +222,7 @@ void bind_elementwise(pybind11::module_& m) {
   m.def("masked_loss", &masked_loss);
   m.def("adamw_step", &adamw_step);
   m.def("sum_slots", &sum_slots);
+  m.def("conv_s2_col2im", &conv_s2_col2im);
 }
 
 void bind_attention(pybind11::module_& m) {

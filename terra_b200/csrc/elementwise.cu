@@ -521,6 +521,53 @@ __global__ void add_bf16_kernel(const uint4* __restrict__ a, const uint4* __rest
   }
 }
 
+// Input gradient of the 3x3 stride-2 convolution from its per-tap columns: dcol[b, ho, wo, tap, c] (tap = ky * 3 + kx)
+// is the contribution of output pixel (ho, wo) to padded input pixel (2 ho + ky, 2 wo + kx). Every padded input pixel
+// gathers its (at most four) contributions; the result is written for padded rows [r0, r0 + rows) and padded columns
+// [1, W + 1) as fp32 (F32: with the halo rows, for the multi-rank fold) or bf16.
+template <bool F32>
+__global__ void conv_s2_col2im_kernel(const uint4* __restrict__ dcol, void* __restrict__ out, int B, int Ho, int Wo, int W,
+                                      int cvec, int r0, int rows) {
+  const long long total = static_cast<long long>(B) * rows * W * cvec;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cv = static_cast<int>(i % cvec);
+    long long t = i / cvec;
+    const int w = static_cast<int>(t % W);
+    t /= W;
+    const int r = static_cast<int>(t % rows);
+    const int b = static_cast<int>(t / rows);
+    const int ph = r0 + r, pw = w + 1;                     // padded coordinates
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // ky in {ph & 1, (ph & 1) + 2 if even}: ph = 2 ho + ky
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int ky = (ph & 1) + 2 * a;
+      if (ky > 2) continue;
+      const int ho = (ph - ky) >> 1;
+      if (ph - ky < 0 || ho >= Ho) continue;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int kx = (pw & 1) + 2 * c;
+        if (kx > 2) continue;
+        const int wo = (pw - kx) >> 1;
+        if (pw - kx < 0 || wo >= Wo) continue;
+        float f[8];
+        unpack8(dcol[((static_cast<long long>(b) * Ho + ho) * Wo + wo) * 9 * cvec + (ky * 3 + kx) * cvec + cv], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    }
+    if (F32) {
+      float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + i * 8);
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      reinterpret_cast<uint4*>(out)[i] = pack8(acc);
+    }
+  }
+}
+
 // out = sum over `slots` consecutive bf16 buffers of `nvec` 16-byte vectors each (fp32 accumulation)
 __global__ void sum_slots_bf16_kernel(const uint4* __restrict__ src, uint4* __restrict__ o, int slots, long long nvec) {
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
@@ -686,6 +733,19 @@ int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t 
   if (n % 8 != 0) return -1;
   add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
                                                             static_cast<uint4*>(out), n / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int conv_s2_col2im(const void* dcol, void* out, int B, int Ho, int Wo, int W, int C, int r0, int rows, int out_f32,
+                   cudaStream_t stream) {
+  if (C % 8 != 0 || rows <= 0) return -1;
+  const long long total = static_cast<long long>(B) * rows * W * (C / 8);
+  if (out_f32)
+    conv_s2_col2im_kernel<true><<<grid_for(total, 256), 256, 0, stream>>>(static_cast<const uint4*>(dcol), out, B, Ho, Wo, W,
+                                                                          C / 8, r0, rows);
+  else
+    conv_s2_col2im_kernel<false><<<grid_for(total, 256), 256, 0, stream>>>(static_cast<const uint4*>(dcol), out, B, Ho, Wo, W,
+                                                                           C / 8, r0, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -99,6 +99,10 @@ int adamw_step(float* master, float* exp_avg, float* exp_avg_sq, const void* gra
 int cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 // out[b, i, j, c] = a + b elementwise (bf16)
 int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
+// Input gradient of the 3x3 stride-2 convolution gathered from per-tap columns dcol[B, Ho, Wo, 9, C] (bf16): padded
+// input rows [r0, r0 + rows) x columns [1, W + 1) -> out[B, rows, W, C] (fp32 when out_f32, else bf16).
+int conv_s2_col2im(const void* dcol, void* out, int B, int Ho, int Wo, int W, int C, int r0, int rows, int out_f32,
+                   cudaStream_t stream);
 // out[n] = sum of `slots` consecutive bf16 buffers of n elements (fp32 accumulation); the owner's side of the
 // slot-staged reduce-scatter
 int sum_slots_bf16(const void* src, void* out, int slots, long long n, cudaStream_t stream);

@@ -96,20 +96,23 @@ def _wgrad_split(B, H, W, stride, Cout, Cin):
 
 def _conv3x3_s2_dgrad(dy, w16, H, W, dom):
     """Input gradient of the stride-2 convolution: dcol = dy @ W (tap-major columns) on the tcgen05 GEMM,
-    then a gather over the (at most four) taps that reach each input pixel."""
+    then one gather kernel over the (at most four) taps that reach each input pixel."""
     B, Ho, Wo, Cout = dy.shape
     Cin = w16.shape[1]
     wk = w16.permute(0, 2, 3, 1).reshape(Cout, 9 * Cin).contiguous()          # [Cout, (tap, ci)]
     dcol = gemm(dy.view(-1, Cout), wk, b_mn=True).view(B, Ho, Wo, 9, Cin)     # dcol[p, tap, ci]
-    dx = torch.zeros(B, H + 2, W + 2, Cin, device=dy.device, dtype=torch.float32)
-    for tap in range(9):
-        ky, kx = divmod(tap, 3)
-        # output pixel (ho, wo) reads padded input (2ho + ky, 2wo + kx)
-        dx[:, ky:ky + 2 * Ho:2, kx:kx + 2 * Wo:2] += dcol[:, :, :, tap]
-    out = dx[:, 1:H + 1, 1:W + 1]
+    ext = _ext.load()
     if dom is not None and dom.world > 1:
-        out = dom.fold_halo_grad(dx, H, W)
-    return out.to(torch.bfloat16).contiguous()
+        # the rows above / below the stripe (padded rows 0 and H + 1) receive gradient too: it goes back to the
+        # neighbours, so the padded rows are produced (fp32, as the halo fold accumulates)
+        dxp = torch.zeros(B, H + 2, W + 2, Cin, device=dy.device, dtype=torch.float32)
+        inner = torch.empty(B, H + 2, W, Cin, device=dy.device, dtype=torch.float32)
+        ext.conv_s2_col2im(dcol.contiguous(), inner, W, 0)
+        dxp[:, :, 1:W + 1] = inner
+        return dom.fold_halo_grad(dxp, H, W).to(torch.bfloat16).contiguous()
+    out = torch.empty(B, H, W, Cin, device=dy.device, dtype=torch.bfloat16)
+    ext.conv_s2_col2im(dcol.contiguous(), out, W, 1)
+    return out
 
 
 def conv3x3(x, conv: torch.nn.Conv2d, stride: int = 1, dom=None):
