@@ -124,5 +124,13 @@ class Trainer:
         return loss
 
     def close(self):
+        pctx = getattr(self.model, "pctx", None)
+        for name in ("tp_arena",):
+            arena = getattr(pctx, name, None)
+            if arena is not None:
+                try:
+                    arena.release_waits()      # no stream may stay blocked on a peer's signal past shutdown
+                except Exception:
+                    pass
         if dist.is_available() and dist.is_initialized():
             dist.destroy_process_group()

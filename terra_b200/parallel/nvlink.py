@@ -26,6 +26,7 @@ import torch.distributed as dist
 from .. import _ext
 from ..ops.gemm import status_word
 
+COMM_MAX_PEERS = 16
 PAD_BYTES = 4096            # signal pads at the start of every arena
 # time budget of a device-side wait on a peer (nanoseconds of the GPU's global timer); TERRA_PEER_WAIT_MS overrides
 BARRIER_SPIN_LIMIT = int(float(os.environ.get("TERRA_PEER_WAIT_MS", "5000")) * 1e6)
@@ -127,6 +128,17 @@ class SymmetricArena:
     def signal_flags_ptr(self) -> int:
         """Device address of this rank's ``[world]`` array of published counts (one per source rank)."""
         return self.base_ptrs[self.rank] + 4 * self.SIGNAL_SLOT
+
+    def release_waits(self) -> None:
+        """Satisfy every stream memory-operation wait that may still be queued on this rank's signal words (the
+        copy-engine gather waits for a peer's signal without a time limit of its own). Called at shutdown and after a
+        peer was reported lost, so that a dead peer cannot keep this process's streams - and its exit - blocked.
+        The arena is unusable for signalling afterwards."""
+        words = self.buf[4 * self.SIGNAL_SLOT:4 * (self.SIGNAL_SLOT + COMM_MAX_PEERS)]
+        side = torch.cuda.Stream(self.buf.device)
+        with torch.cuda.stream(side):
+            words.fill_(0x7F)          # 0x7f7f7f7f: above any epoch a run reaches
+        side.synchronize()
 
     def barrier(self) -> None:
         """Stream-ordered barrier over the group (device side; the host does not wait)."""
