@@ -7,8 +7,9 @@
 //            128-byte-swizzled shared-memory stages, signalling `full[s]` by transaction bytes;
 //   warp 1   owns the TMEM allocation; one elected lane issues tcgen05.mma (M=128, N=BN, K=16)
 //            and commits to `empty[s]` (stage reusable) and `tfull[a]` (accumulator a complete);
-//   warps 2-13 epilogue (three per 32-lane TMEM quadrant, interleaved over the column chunks): tcgen05.ld, fused bias / GELU / residual /
-//            GELU-gradient / pixel-shuffle / split-K atomics; global transfers coalesced through shared memory.
+//   warps 2-13 epilogue (three per 32-lane TMEM quadrant, interleaved over the column chunks): tcgen05.ld, fused
+//            bias / GELU / residual / GELU-gradient / pixel-shuffle / split-K atomics; global transfers coalesced
+//            through shared memory.
 // Two accumulators (2*BN TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
 //
 // Operand addressing is data driven (see gemm_sm100.cuh) so that the same kernel serves
@@ -18,6 +19,9 @@
 //   * 3x3 convolutions (stride 1 and 2) as implicit GEMM: A rows gathered by 5-D TMA boxes with
 //     zero fill outside the image, k-blocks enumerate (tap, channel chunk),
 //   * convolution weight gradients (contraction over pixels, one tile group per tap).
+// Two further instantiations: CTA pairs (a cluster of two drives one cta_group::2 MMA over a 256-row tile, see GemmCfg)
+// and the tensor-parallel forms (A gathered from the peers' buffers, output scattered to the owners' buffers, see
+// gemm_sm100.cuh).
 //
 // Every wait is bounded; on expiry the CTA sets its abort flag, records the site in the
 // KernelStatus word, drains, releases TMEM and returns.
