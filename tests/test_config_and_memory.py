@@ -229,3 +229,28 @@ def test_exposed_comm_accounting():
                  ("tb::peer_barrier_kernel", 8.0, 9.0)])
     assert r["span"] == 9.0 and r["compute_busy"] == 5.0 and r["comm_busy"] == 4.0
     assert r["comm_hidden"] == 1.0 and r["exposed"] == 4.0
+
+
+def test_every_shipped_config_parses():
+    """All YAML files under configs/ resolve to model / layout parameters for the world size their layout names."""
+    import glob
+    import os
+    import re
+
+    import yaml
+
+    from terra_b200.config import get_model_archi_params_and_other_params
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "configs", "**", "*.yaml"), recursive=True))
+    assert len(files) >= 9
+    for f in files:
+        cfg = yaml.safe_load(open(f))
+        world = 1
+        if cfg.get("model_type") == "parallel":
+            a, b = (int(v) for v in re.findall(r"\d+", str(cfg.get("wp_topo", "(1, 1)")))[:2])
+            world = a * b
+        archi, other = get_model_archi_params_and_other_params(cfg.get("task_type", "glorys"), cfg, 1, world)
+        ph, pw = archi["padded_shape"]
+        unit = archi["patch_size"] * 2 * (archi["window_size"] if isinstance(archi["window_size"], int) else archi["window_size"][0])
+        assert ph > 0 and pw > 0 and ph % unit == 0, (f, archi["padded_shape"], unit)
