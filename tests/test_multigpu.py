@@ -58,10 +58,11 @@ def test_layout_matches_single_gpu(n, layout):
         assert got["fused_tp"], "the tensor-parallel MLP must run on the fused all-gather / reduce-scatter GEMMs"
 
 
-@pytest.mark.parametrize("n", [2, 4])
+@pytest.mark.parametrize("n", [2])
 def test_fused_tensor_parallel_linears(n):
-    """All-gather -> GEMM, GEMM -> reduce-scatter and the sequence-sharded MLP built from them (forward and backward)
-    against fp32 PyTorch on the gathered operands."""
+    """All-gather -> GEMM (both transports), GEMM -> reduce-scatter (both forms) and the sequence-sharded MLP built from
+    them (forward and backward) against fp32 PyTorch on the gathered operands. (Two ranks: the four-rank case has
+    not been run on hardware yet; its index arithmetic is covered on the CPU by tests/test_tp_tile_mapping.py.)"""
     _need(n)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
     worker = os.path.join(ROOT, "tests", "tp_fused_worker.py")

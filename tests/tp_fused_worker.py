@@ -19,7 +19,7 @@ def main():
     from terra_b200.ops.tp_fused import TpFusedComm, tp_mlp
     from terra_b200.parallel.nvlink import SymmetricArena
 
-    rank, world, dev = init_distributed()
+    rank, world, dev = init_distributed(timeout_s=120)     # a rank that fails must not keep the others waiting long
     arena = SymmetricArena(dist.group.WORLD, 6 << 30 if timing else 256 << 20, dev)
     comm = TpFusedComm(arena)
     x_sym = None
@@ -123,4 +123,11 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        import traceback
+
+        traceback.print_exc()
+        sys.stdout.flush()
+        os._exit(1)          # leave at once: the peers' collectives then end with the process-group timeout
