@@ -254,3 +254,31 @@ def test_every_shipped_config_parses():
         ph, pw = archi["padded_shape"]
         unit = archi["patch_size"] * 2 * (archi["window_size"] if isinstance(archi["window_size"], int) else archi["window_size"][0])
         assert ph > 0 and pw > 0 and ph % unit == 0, (f, archi["padded_shape"], unit)
+
+
+def test_bench_clock_sampler_parses_nvidia_smi_rows(tmp_path):
+    """The clocks record of the benchmark line: median SM clock, maximum clock, throttle reasons seen."""
+    import sys
+
+    root = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import bench
+
+    class Done:
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            return 0
+
+    f = tmp_path / "clocks.csv"
+    f.write_text("0, 1965, 1965, 612.3, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n"
+                 "0, 1905, 1965, 998.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n"
+                 "0, 1950, 1965, 700.0, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active\n"
+                 "garbage line\n")
+    s = bench.ClockSampler(0)
+    s.proc, s.path = Done(), str(f)
+    out = s.stop()
+    assert out["sm_mhz"] == 1950.0 and out["sm_max_mhz"] == 1965.0 and out["reasons"] == ["sw_power_cap"] and out["samples"] == 3
+    cfg = bench.flagship_config(8)
+    assert cfg["wp_topo"] == "(8, 1)" and cfg["optimizer_config"] == 6 and cfg["height"] == 2048 and cfg["num_channels"] == 186
