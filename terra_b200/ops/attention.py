@@ -17,6 +17,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from .. import _ext
+from ..utils.nvtx import nvtx_range
 
 
 @dataclass
@@ -206,6 +207,7 @@ class _WindowAttnFn(torch.autograd.Function):
         return dqkv, dbias, None, None, None, None, None, None
 
 
+@nvtx_range("terra.window_attention")
 def window_attention(qkv: torch.Tensor, geo: WindowGeometry, num_heads: int, shifted: bool,
                      bias_table: Optional[torch.Tensor], use_mask: bool, scale: float, comm=None) -> torch.Tensor:
     """``qkv``: ``[rows_local, 3C]`` -> ``[rows_local, C]``. ``comm`` supplies peer access for multi-rank layouts

@@ -20,6 +20,7 @@ import torch.nn.functional as TF
 from .. import _ext
 from .attention import MAX_KERNEL_WINDOW_TOKENS, WindowGeometry, window_attention
 from .gemm import gemm, status_word
+from ..utils.nvtx import nvtx_range
 
 LN_EPS = 1e-5
 
@@ -43,6 +44,7 @@ def bias_grad_accumulate(dy: torch.Tensor, grad_b: torch.Tensor) -> None:
     _ext.load().colsum(dy, grad_b)
 
 
+@nvtx_range("terra.layernorm")
 def layernorm_cuda(x, w16, b16):
     ext = _ext.load()
     y = torch.empty_like(x)
@@ -197,6 +199,7 @@ class LayerNormFn(torch.autograd.Function):
 
 
 # ------------------------------------------------------------------------------------------------ public entry points
+@nvtx_range("terra.attention_half")
 def attention_half(x, mod, geo: WindowGeometry, shifted: bool, comm=None):
     """x + proj(window_attention(qkv(norm1(x)))) for a ``SwinAttentionHalf`` module ``mod``."""
     if x.is_cuda and geo.N > MAX_KERNEL_WINDOW_TOKENS:
@@ -231,6 +234,7 @@ def attention_half(x, mod, geo: WindowGeometry, shifted: bool, comm=None):
     return x + a.proj(o)
 
 
+@nvtx_range("terra.mlp_half")
 def mlp_half(x, mod):
     """x + fc2(gelu(fc1(norm2(x))))."""
     if x.is_cuda:

@@ -22,6 +22,7 @@ from .. import _ext
 from . import _flags as F
 from .gemm import gemm, status_word
 from .blocks import wgrad_accumulate, bias_grad_accumulate
+from ..utils.nvtx import nvtx_range
 
 GN_EPS = 1e-5
 
@@ -115,6 +116,7 @@ def _conv3x3_s2_dgrad(dy, w16, H, W, dom):
     return out
 
 
+@nvtx_range("terra.conv3x3")
 def conv3x3(x, conv: torch.nn.Conv2d, stride: int = 1, dom=None):
     """x NHWC -> NHWC. ``conv`` holds a (Cout, Cin, 3, 3) weight and a bias."""
     if x.is_cuda:

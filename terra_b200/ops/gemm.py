@@ -18,6 +18,7 @@ import torch
 
 from .. import _ext
 from . import _flags as F
+from ..utils.nvtx import nvtx_range
 
 _status = {}
 _TRACE = os.environ.get("TERRA_TRACE", "0") == "1"
@@ -41,6 +42,7 @@ def check_status(device) -> None:
         )
 
 
+@nvtx_range("terra.gemm")
 def gemm(
     a: torch.Tensor,
     b: torch.Tensor,

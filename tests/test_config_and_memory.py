@@ -282,3 +282,12 @@ def test_bench_clock_sampler_parses_nvidia_smi_rows(tmp_path):
     assert out["sm_mhz"] == 1950.0 and out["sm_max_mhz"] == 1965.0 and out["reasons"] == ["sw_power_cap"] and out["samples"] == 3
     cfg = bench.flagship_config(8)
     assert cfg["wp_topo"] == "(8, 1)" and cfg["optimizer_config"] == 6 and cfg["height"] == 2048 and cfg["num_channels"] == 186
+
+
+def test_nvtx_decorator_is_a_no_op_by_default():
+    from terra_b200.utils import nvtx
+
+    def f(x):
+        return x + 1
+
+    assert nvtx.ENABLED is False and nvtx.nvtx_range("t")(f) is f
