@@ -11,6 +11,12 @@ What has to differ from the framework's arm, because the reference cannot expres
   * 1 GPU runs the sequential build (the reference's 1-GPU mode), N > 1 the window-parallel build with
     ``wp_topo = (N, 1)`` and ``terra_m1_ragged_auto``; bf16 autocast with fp32 parameters, DDP over the (size-1) data
     parallel group, ``grad_post_process`` all-reduces over the window-parallel group, ``torch.optim.AdamW``.
+
+With an extra layout ``(wg, sp, tp)`` (the 2 x 2 x 2 layout on 8 GPUs) the same model and data are timed a second time
+in the reference's factorised build: ``xfmr_wp_topo = (wg, 1)``, ``xfmr_sp_size = sp``, ``tensor_parallel_size = tp``,
+its own ``DistributedAdamW`` (``optimizer_config: 6``, which the reference requires for TP > 1) under bf16 autocast,
+exactly the objects its ``get_model_for_train`` builds for that configuration. The result is reported under
+``layout_<wg>x<sp>x<tp>`` of the same JSON line.
 """
 from __future__ import annotations
 
@@ -24,7 +30,7 @@ def _emit(obj):
     print(json.dumps(obj), flush=True)
 
 
-def main(args, cfg, ClockSampler, metric):
+def main(args, cfg, ClockSampler, metric, layout=None):
     from baseline import ref_import
 
     if not ref_import.available():
@@ -38,7 +44,7 @@ def main(args, cfg, ClockSampler, metric):
             _emit({"impl": "reference", "unavailable": "no CUDA device (the reference's parallel model needs CUDA + NCCL)"})
             return
         ref_import.enable()
-        _run(args, cfg, ClockSampler, metric)
+        _run(args, cfg, ClockSampler, metric, layout)
     except Exception as exc:  # the reference arm must never take the driver down
         import traceback
 
@@ -46,7 +52,7 @@ def main(args, cfg, ClockSampler, metric):
         _emit({"impl": "reference", "unavailable": f"reference run failed: {type(exc).__name__}: {exc}"[:400]})
 
 
-def _run(args, cfg, ClockSampler, metric):
+def _run(args, cfg, ClockSampler, metric, layout=None):
     import torch
     import torch.distributed as dist
     from torch.nn.parallel import DistributedDataParallel as DDP
@@ -55,6 +61,7 @@ def _run(args, cfg, ClockSampler, metric):
     from core.runtime.run_model import one_step_train                  # reference
     from models.reference_model.parallel_hierarchical_swin import ParallelHierarchicalSwin          # reference
     from models.reference_model.sequential_hierarchical_swin import SequentialHierarchicalSwin      # reference
+    from optimizer.utils import get_optimizer as ref_get_optimizer     # reference
 
     from terra_b200.config import resolve_padding_spec                 # padding arithmetic only
     from terra_b200.data.synthetic import land_mask_for_rank, synthetic_batch   # shared synthetic data
@@ -79,60 +86,77 @@ def _run(args, cfg, ClockSampler, metric):
     layers, heads = sum(cfg["depths"]), 12 if D % 12 == 0 else cfg["num_heads"][0]
     n = args.gpus
     mode = "terra_m1_ragged_auto"
-    spec = resolve_padding_spec({"padding_policy": "auto"}, "credit_hierarchical_swin", H, W, p, ws, (n, 1), (n, 1), mode)
-    manager = ParallelManager(dp_size=1, mp_size=1, wp_topo=(n, 1), xfmr_wp_topo=(n, 1), rank=rank, world_size=world,
-                              device=dev, window_assignment_mode=mode, xfmr_sp_size=1, tensor_parallel_size=1)
-    model_type = "sequential" if n == 1 else "parallel"
-    if n == 1:
-        model = SequentialHierarchicalSwin(padding_scale=1, num_channels=C, patch_size=p, window_size=ws, height=H,
-                                           width=W, embedding_dim=D, num_heads=heads, num_layers=layers,
-                                           recompute_config=None, manager=manager, padding_spec=spec)
-    else:
-        model = ParallelHierarchicalSwin(height=H, width=W, num_channels=C, patch_size=p, embedding_dim=D,
-                                         num_layers=layers, num_heads=heads, window_size=ws, manager=manager, device=dev,
-                                         padding_scale=1, embedding_parallel_type="window_linear", recompute_config=None,
-                                         padding_spec=spec)
-    model = model.to(dev)
-    model = DDP(model, device_ids=[local], process_group=manager.data_parallel_group)
-    optimizer = torch.optim.AdamW(model.parameters(), lr=cfg["learning_rate"], betas=(0.9, 0.95), weight_decay=0.1)
-    optimizer.global_step = 0
     loss_fn = torch.nn.L1Loss(reduction="mean")
-
-    mask, pad_scale = land_mask_for_rank(H, W, C, p, spec["padded_shape"], spec["initial_padding"], model_type, n, rank)
-    task = {"land_sea_mask": mask.to(dev, torch.bfloat16), "padding_loss_scale": pad_scale, "test_iter_num": -1,
-            "show_gradient_flag": False}
-    other = {"embedding_parallel_type": "window_linear" if n > 1 else None}
-    host = [synthetic_batch(H, W, C, p, spec["padded_shape"], spec["initial_padding"], model_type, n, rank, 1, i, 2025,
-                            torch.bfloat16, pin=True, gen_device="cuda") for i in range(2)]
-    devb = [{k: v.to(dev, non_blocking=True) for k, v in b.items()} for b in host]
-    h2d_bytes = sum(v.numel() * v.element_size() for v in host[0].values())
-    state = (True, False, None, False)   # USE_DDP, USE_FSDP, ZERO_STAGE_NUMBER, USE_DIST_OPT
-
-    def step(batch):
-        _, loss, _, _ = one_step_train("glorys", model_type, model, None, optimizer, batch, task, other, "bf16", False,
-                                       torch.bfloat16, loss_fn, None, manager=manager, optimizer_state_tuple=state,
-                                       memory_timeline=None, clip_grad=False, sync_for_timing=False,
-                                       barrier_for_timing=False)
-        return loss
+    model_type = "sequential" if n == 1 else "parallel"
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(devb[i % 2])
-    barrier()
+    def build(lay):
+        """(step function, padding spec) of the reference's own objects for the main layout (``lay is None``) or the
+        factorised one."""
+        wg, sp, tp = lay if lay is not None else (n, 1, 1)
+        spec = resolve_padding_spec({"padding_policy": "auto"}, "credit_hierarchical_swin", H, W, p, ws, (n, 1), (wg, 1), mode)
+        manager = ParallelManager(dp_size=1, mp_size=1, wp_topo=(n, 1), xfmr_wp_topo=(wg, 1), rank=rank, world_size=world,
+                                  device=dev, window_assignment_mode=mode, xfmr_sp_size=sp, tensor_parallel_size=tp)
+        if n == 1:
+            model = SequentialHierarchicalSwin(padding_scale=1, num_channels=C, patch_size=p, window_size=ws, height=H,
+                                               width=W, embedding_dim=D, num_heads=heads, num_layers=layers,
+                                               recompute_config=None, manager=manager, padding_spec=spec)
+        else:
+            model = ParallelHierarchicalSwin(height=H, width=W, num_channels=C, patch_size=p, embedding_dim=D,
+                                             num_layers=layers, num_heads=heads, window_size=ws, manager=manager,
+                                             device=dev, padding_scale=1, embedding_parallel_type="window_linear",
+                                             recompute_config=None, padding_spec=spec)
+        model = model.to(dev)
+        if lay is None:
+            model = DDP(model, device_ids=[local], process_group=manager.data_parallel_group)
+            optimizer = torch.optim.AdamW(model.parameters(), lr=cfg["learning_rate"], betas=(0.9, 0.95), weight_decay=0.1)
+            optimizer.global_step = 0
+            state = (True, False, None, False)   # USE_DDP, USE_FSDP, ZERO_STAGE_NUMBER, USE_DIST_OPT
+        else:
+            model.train()
+            _, optimizer = ref_get_optimizer("bf16", model, cfg["learning_rate"], manager=manager, model_type=model_type,
+                                             zero_stage_number=None, use_distributed_optimizer=True)
+            state = (False, False, None, True)
+        mask, pad_scale = land_mask_for_rank(H, W, C, p, spec["padded_shape"], spec["initial_padding"], model_type, n, rank)
+        task = {"land_sea_mask": mask.to(dev, torch.bfloat16), "padding_loss_scale": pad_scale, "test_iter_num": -1,
+                "show_gradient_flag": False}
+        other = {"embedding_parallel_type": "window_linear" if n > 1 else None}
+
+        def step(batch):
+            _, loss, _, _ = one_step_train("glorys", model_type, model, None, optimizer, batch, task, other, "bf16", False,
+                                           torch.bfloat16, loss_fn, None, manager=manager, optimizer_state_tuple=state,
+                                           memory_timeline=None, clip_grad=False, sync_for_timing=False,
+                                           barrier_for_timing=False)
+            return loss
+
+        return step, spec
+
+    def time_device(step, batches):
+        for i in range(args.warmup):
+            step(batches[i % 2])
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(args.steps):
+            loss = step(batches[i % 2])
+        ev1.record()
+        barrier()
+        ms = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item(), float(loss.item())
+
+    step, spec = build(None)
+    host = [synthetic_batch(H, W, C, p, spec["padded_shape"], spec["initial_padding"], model_type, n, rank, 1, i, 2025,
+                            torch.bfloat16, pin=True, gen_device="cuda") for i in range(2)]
+    devb = [{k: v.to(dev, non_blocking=True) for k, v in b.items()} for b in host]
+    h2d_bytes = sum(v.numel() * v.element_size() for v in host[0].values())
+
     sampler = ClockSampler(local)
     sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        loss = step(devb[i % 2])
-    ev1.record()
-    barrier()
-    ms = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    last_loss = float(loss.item())
+    ms, last_loss = time_device(step, devb)
 
     # end to end the way the reference's own loop does it: pinned host batch -> .to(device, non_blocking) -> step -> .item()
     barrier()
@@ -144,10 +168,28 @@ def _run(args, cfg, ClockSampler, metric):
     e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device=dev)
     dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     clocks = sampler.stop()
+
+    extra = None
+    if layout is not None:
+        import gc
+
+        del step
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            step2, _ = build(layout)
+            ms2, loss2 = time_device(step2, devb)
+            extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms2, "samples_per_s": 1.0 / (ms2 * 1e-3),
+                     "loss": loss2, "optimizer": "reference DistributedAdamW (optimizer_config 6)"}
+        except Exception as exc:   # the main number stands even if the factorised build cannot run
+            import traceback
+
+            traceback.print_exc(file=sys.stderr)
+            extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     if rank == 0:
-        _emit({
-            "metric": metric, "value": 1.0 / (ms.item() * 1e-3), "unit": "samples/s", "n_gpus": n, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms.item(), "higher_is_better": True, "scaling": "strong",
+        line = {
+            "metric": metric, "value": 1.0 / (ms * 1e-3), "unit": "samples/s", "n_gpus": n, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16 autocast, fp32 parameters", "data": "synthetic", "impl": "reference",
             "config": {"model": f"credit_hierarchical_swin {H}x{W}x{C} p{p} D{D} layers {layers} heads {heads} ws{ws}",
                        "global_batch": 1, "parallelism": f"wp{n}" if n > 1 else "sequential",
@@ -157,5 +199,8 @@ def _run(args, cfg, ClockSampler, metric):
             "e2e": {"value": 1.0 / (e2e_ms.item() * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms.item(),
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
             "loss": last_loss, "e2e_loss": e2e_loss,
-        })
+        }
+        if extra is not None:
+            line["layout_" + "x".join(str(v) for v in layout)] = extra
+        _emit(line)
     dist.destroy_process_group()

@@ -32,7 +32,27 @@ if ROOT not in sys.path:
 METRIC = "train_samples_per_s"
 
 
-def flagship_config(n_gpus: int, small: bool = False) -> dict:
+def parse_layout(text, n_gpus):
+    """``"wg,sp,tp"`` -> tuple; the default is the 2 x 2 x 2 layout on 8 GPUs and nothing elsewhere."""
+    if text in (None, "", "none"):
+        return (2, 2, 2) if (text is None and n_gpus == 8) else None
+    wg, sp, tp = (int(v) for v in text.split(","))
+    if wg * sp * tp != n_gpus:
+        raise SystemExit(f"--extra-layout {text}: wg x sp x tp must equal --gpus {n_gpus}")
+    return wg, sp, tp
+
+
+def flagship_config(n_gpus: int, small: bool = False, layout=None) -> dict:
+    """``layout = (window groups, sequence-parallel size, tensor-parallel size)``: the factorised layout of the same
+    model (conv stage still split in ``n_gpus`` row stripes); ``None``: window parallel over all GPUs."""
+    cfg = _flagship_config(n_gpus, small)
+    if layout is not None:
+        wg, sp, tp = layout
+        cfg.update(xfmr_wp_topo=f"({wg}, 1)", xfmr_sp_size=sp, tensor_parallel_size=tp, optimizer_config=6)
+    return cfg
+
+
+def _flagship_config(n_gpus: int, small: bool = False) -> dict:
     cfg = dict(
         task_type="glorys", model_architecture="credit_hierarchical_swin", model_type="parallel",
         height=2048, width=4320, num_channels=186, patch_size=4, embedding_dim=384, depths=[2, 6, 6, 2],
@@ -100,19 +120,45 @@ class ClockSampler:
         return out
 
 
-def run_ours(args):
+def _time_device_steps(trainer, devb, steps, warmup, barrier):
+    """W untimed + K timed steps on device-resident batches: (ms per step as the max over ranks, launches, last loss)."""
     import torch
     import torch.distributed as dist
 
     from terra_b200 import _ext
+
+    ext = _ext.load()
+    for i in range(warmup):
+        trainer.step_on_device(devb[i % 2])
+    barrier()
+    launches0 = ext.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(steps):
+        loss = trainer.step_on_device(devb[i % 2])
+    ev1.record()
+    barrier()
+    launches = ext.launch_count() - launches0
+    ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=trainer.device)
+    if dist.is_initialized():
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item(), int(launches), float(loss.item())
+
+
+def run_ours(args):
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
     from terra_b200.api import Trainer
+    from terra_b200.ops.gemm import check_status
 
     cfg = flagship_config(args.gpus, args.small)
     trainer = Trainer(cfg, data_parallel_group_size=1)
     rank, world, dev = trainer.rank, trainer.world, trainer.device
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    ext = _ext.load()
     live = dist.is_initialized()
 
     def barrier():
@@ -128,22 +174,7 @@ def run_ours(args):
     #      start, and a multi-GPU timed region lasts only tens of milliseconds)
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
-    for i in range(args.warmup):
-        trainer.step_on_device(devb[i % 2])
-    barrier()
-    launches0 = ext.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        loss = trainer.step_on_device(devb[i % 2])
-    ev1.record()
-    barrier()
-    launches = ext.launch_count() - launches0
-    ms = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev)
-    if live:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = ms.item()
-    last_loss = float(loss.item())
+    ms_per_step, launches, last_loss = _time_device_steps(trainer, devb, args.steps, args.warmup, barrier)
 
     # ---- end to end through the public API: staged H2D of every step's batch + D2H of the loss
     e2e_loss, e2e_ms = None, torch.tensor([float("nan")], device=dev)
@@ -164,6 +195,26 @@ def run_ours(args):
         if live:
             dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     clocks = sampler.stop()
+    check_status(dev)
+    seq_len = trainer.archi["padded_shape"][0] // 8 * (trainer.archi["padded_shape"][1] // 8)
+
+    # ---- the factorised layout of the same model and data (window groups x sequence parallel x tensor parallel, sharded
+    #      AdamW): the step in which the fused tensor-parallel GEMMs and the sequence-parallel K/V gather run
+    extra = None
+    layout = parse_layout(args.extra_layout, args.gpus)
+    if layout is not None:
+        trainer.release()
+        del trainer
+        gc.collect()
+        torch.cuda.empty_cache()
+        t2 = Trainer(flagship_config(args.gpus, args.small, layout), data_parallel_group_size=1)
+        ms2, launches2, loss2 = _time_device_steps(t2, devb, args.steps, args.warmup, barrier)
+        check_status(dev)
+        pc = t2.model.pctx
+        extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms2, "samples_per_s": 1.0 / (ms2 * 1e-3),
+                 "gpu_launches": launches2, "loss": loss2, "optimizer": "DistributedAdamW (optimizer_config 6)",
+                 "fused_tp": getattr(pc, "tp_comm", None) is not None, "fused_attn": pc.fused_comm is not None}
+        trainer = t2
 
     gb = 1
     par = f"wp{args.gpus}" if args.gpus > 1 else "single"
@@ -173,7 +224,7 @@ def run_ours(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "terra_b200",
         "config": {"model": "credit_hierarchical_swin 2048x4320x186 p4 D384 depths[2,6,6,2] heads[6,12,24,12] ws8"
                    if not args.small else "credit_hierarchical_swin small (smoke)",
-                   "global_batch": gb, "seq_len": trainer.archi["padded_shape"][0] // 8 * (trainer.archi["padded_shape"][1] // 8),
+                   "global_batch": gb, "seq_len": seq_len,
                    "parallelism": par, "l2_policy": "inputs (3.3 GB each) larger than L2, two batches alternated",
                    "optimizer": "AdamW fp32 master, sharded over ranks when N>1"},
         "clocks": clocks,
@@ -182,6 +233,8 @@ def run_ours(args):
                                            "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches), "loss": last_loss, "e2e_loss": e2e_loss,
     }
+    if extra is not None:
+        line["layout_" + "x".join(str(v) for v in layout)] = extra
     if rank == 0:
         print(json.dumps(line), flush=True)
     trainer.close()
@@ -193,7 +246,8 @@ def run_reference(args):
     except Exception as exc:  # pragma: no cover
         print(json.dumps({"impl": "reference", "unavailable": f"harness import failed: {exc!r}"[:300]}), flush=True)
         return
-    ref_harness.main(args, flagship_config(args.gpus, args.small), ClockSampler, METRIC)
+    ref_harness.main(args, flagship_config(args.gpus, args.small), ClockSampler, METRIC,
+                     parse_layout(args.extra_layout, args.gpus))
 
 
 def main():
@@ -204,6 +258,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test of the harness, not a benchmark)")
     ap.add_argument("--skip-e2e", action="store_true", help="only the device-timed loop (used when profiling)")
+    ap.add_argument("--extra-layout", default=None,
+                    help='also time the factorised layout "wg,sp,tp" of the same model (default: 2,2,2 on 8 GPUs; "none")')
     args = ap.parse_args()
     if args.warmup < 3 and not args.small:
         args.warmup = 3

@@ -53,6 +53,20 @@ class Trainer:
         self._copy = _ext.load().CopyEngine(self.device.index or 0) if self.device.type == "cuda" else None
         self._slots = [None, None]
         self._slot = 0
+        self._steps_done = 0
+        self._guard = self._make_guard()
+
+    def _make_guard(self):
+        """Failure detection between steps: heartbeats in the process group's store, the kernels' status word, and
+        the host watchdogs of the stream waits (see ``terra_b200.runtime.watchdog``)."""
+        from .runtime.watchdog import make_step_guard
+
+        return make_step_guard(self.device, self.rank, self.world, self.model, self.optimizer)
+
+    def _after_step(self):
+        """Host-side checks where the step has synchronised anyway (the loss was just read)."""
+        self._guard.after_step(self._steps_done)
+        self._steps_done += 1
 
     # ------------------------------------------------------------------ shapes
     @property
@@ -113,7 +127,9 @@ class Trainer:
             self.task_type, self.model_type, self.model, self.engine, self.optimizer, dev, self.task_data, self.other,
             self.precision, self.cfg.get("half_model", False), None, self.loss_func, self.gscaler, self.manager,
             self.opt_state)
-        return float(loss.item())
+        value = float(loss.item())
+        self._after_step()
+        return value
 
     def step_on_device(self, dev_batch: Dict[str, torch.Tensor]):
         """Step on tensors that already live on the device; returns the loss tensor (no host synchronisation)."""
@@ -123,7 +139,26 @@ class Trainer:
             self.manager, self.opt_state)
         return loss
 
+    def release(self):
+        """Drop the model, optimizer and their symmetric arenas but keep the process group, so that another
+        ``Trainer`` (another layout of the same job) can be built in this process."""
+        self._guard.close(announce=False)
+        pctx = getattr(self.model, "pctx", None)
+        arena = getattr(pctx, "tp_arena", None)
+        if arena is not None:
+            try:
+                arena.release_waits()
+            except Exception:
+                pass
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+        self.model = self.optimizer = self._guard = self._slots = self.task_data = None
+
     def close(self):
+        if self._guard is not None:
+            self._guard.close()
         pctx = getattr(self.model, "pctx", None)
         for name in ("tp_arena",):
             arena = getattr(pctx, name, None)

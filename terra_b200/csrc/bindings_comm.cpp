@@ -80,20 +80,36 @@ void peer_signal(const std::vector<int64_t>& pad_ptrs, int64_t my_rank, int64_t 
 // stream: a cudaStream_t as an integer (torch.cuda.Stream.cuda_stream)
 void gather_shards_async(int64_t stream, int64_t dst, const std::vector<int64_t>& src_ptrs, int64_t my_rank, int64_t rows,
                          int64_t row_bytes, int64_t chunks, int64_t chunk_rows, int64_t signals_ptr, int64_t ready_ptr,
-                         int64_t epoch) {
+                         int64_t epoch, bool include_self) {
   std::vector<const void*> p;
   for (auto v : src_ptrs) p.push_back(reinterpret_cast<const void*>(v));
   const int rc = tb::gather_shards_async(reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<void*>(dst), p.data(),
                                          static_cast<int>(p.size()), static_cast<int>(my_rank), rows,
                                          static_cast<size_t>(row_bytes), static_cast<int>(chunks), chunk_rows,
                                          reinterpret_cast<const unsigned int*>(signals_ptr),
-                                         reinterpret_cast<unsigned int*>(ready_ptr), static_cast<unsigned int>(epoch));
+                                         reinterpret_cast<unsigned int*>(ready_ptr), static_cast<unsigned int>(epoch),
+                                         include_self ? 1 : 0);
   TORCH_CHECK(rc == 0, "gather_shards_async failed with code ", rc);
+}
+
+// Stream memory operations on a stream given as an integer (torch.cuda.Stream.cuda_stream): the stream waits until the
+// 32-bit word at `addr` is >= value / writes value to it, without occupying an SM.
+void stream_wait_value(int64_t stream, int64_t addr, int64_t value) {
+  TORCH_CHECK(tb::stream_wait_geq32(reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const void*>(addr),
+                                    static_cast<unsigned int>(value)) == 0,
+              "stream_wait_value failed");
+}
+void stream_write_value(int64_t stream, int64_t addr, int64_t value) {
+  TORCH_CHECK(tb::stream_write32(reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<void*>(addr),
+                                 static_cast<unsigned int>(value)) == 0,
+              "stream_write_value failed");
 }
 
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
+  m.def("stream_wait_value", &stream_wait_value);
+  m.def("stream_write_value", &stream_write_value);
   m.def("dist_adamw_step", &dist_adamw_step);
   m.def("peer_copy_rows", &peer_copy_rows);
   m.def("peer_sum_small", &peer_sum_small);

@@ -128,12 +128,21 @@ void adamw_step(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const
            "adamw_step");
 }
 
+void grad_inspect(const torch::Tensor& grad, torch::Tensor& out2) {
+  need(grad.is_cuda() && grad.is_contiguous() && grad.scalar_type() == torch::kFloat32, "grad_inspect: fp32 contiguous");
+  need(out2.scalar_type() == torch::kFloat32 && out2.numel() >= 2, "grad_inspect: out2 fp32 [2]");
+  const c10::cuda::CUDAGuard guard(grad.device());
+  tb::note_launch();
+  rc_check(tb::grad_inspect(grad.data_ptr<float>(), grad.numel(), out2.data_ptr<float>(), cur_stream()), "grad_inspect");
+}
+
 // Peer buffers are passed as raw device addresses (int64) so that symmetric-memory peers can be addressed;
 // for a single rank the lists hold one entry each.
 tb::WindowAttnArgs make_wa(const std::vector<int64_t>& win_start, int64_t my_wg, int64_t sp, int64_t my_sp,
                            int64_t shardN, int64_t B, int64_t nWh, int64_t nWw, int64_t C, int64_t heads, int64_t wh,
-                           int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale) {
+                           int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale, int64_t tp) {
   tb::WindowAttnArgs a{};
+  a.tp = static_cast<int>(tp < 1 ? 1 : tp);
   need(win_start.size() >= 2 && win_start.size() <= 9, "window_attn: win_start must have n_wg+1 <= 9 entries");
   a.n_wg = static_cast<int>(win_start.size()) - 1;
   for (size_t i = 0; i < win_start.size(); ++i) a.win_start[i] = static_cast<int>(win_start[i]);
@@ -149,8 +158,8 @@ tb::WindowAttnArgs make_wa(const std::vector<int64_t>& win_start, int64_t my_wg,
 void window_attn(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t>& out_ptrs,
                  const c10::optional<torch::Tensor>& bias_table, const std::vector<int64_t>& win_start, int64_t my_wg,
                  int64_t sp, int64_t my_sp, int64_t shardN, int64_t B, int64_t nWh, int64_t nWw, int64_t C,
-                 int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale) {
-  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale);
+                 int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale, int64_t tp) {
+  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale, tp);
   need(qkv_ptrs.size() == static_cast<size_t>(a.n_wg * a.sp) && out_ptrs.size() == qkv_ptrs.size(),
        "window_attn: one buffer per peer slot");
   for (size_t i = 0; i < qkv_ptrs.size(); ++i) {
@@ -167,8 +176,8 @@ void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int
                      const c10::optional<torch::Tensor>& dbias_table, const std::vector<int64_t>& win_start,
                      int64_t my_wg, int64_t sp, int64_t my_sp, int64_t shardN, int64_t B, int64_t nWh, int64_t nWw,
                      int64_t C, int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask,
-                     double scale) {
-  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale);
+                     double scale, int64_t tp) {
+  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale, tp);
   need(qkv_ptrs.size() == static_cast<size_t>(a.n_wg * a.sp) && dout_ptrs.size() == qkv_ptrs.size() &&
            dqkv_ptrs.size() == qkv_ptrs.size(),
        "window_attn_bwd: one buffer per peer slot");
@@ -198,14 +207,21 @@ void conv_s2_col2im(const torch::Tensor& dcol, torch::Tensor& out, int64_t W, in
            "conv_s2_col2im");
 }
 
-void sum_slots(const torch::Tensor& slots, torch::Tensor& out) {
+void sum_slots(const torch::Tensor& slots, torch::Tensor& out, const c10::optional<torch::Tensor>& bias,
+               const c10::optional<torch::Tensor>& residual) {
   need(slots.is_cuda() && slots.is_contiguous() && slots.scalar_type() == torch::kBFloat16 && slots.dim() >= 2,
        "sum_slots: [slots, ...] bf16 contiguous");
   need(out.is_contiguous() && out.scalar_type() == torch::kBFloat16 && out.numel() * slots.size(0) == slots.numel(),
        "sum_slots: out must hold one slot");
+  need(!bias.has_value() || (bias->scalar_type() == torch::kBFloat16 && bias->is_contiguous() && bias->numel() == out.size(-1)),
+       "sum_slots: bias must be bf16 [cols]");
+  need(!residual.has_value() || (residual->scalar_type() == torch::kBFloat16 && residual->is_contiguous() &&
+                                 residual->numel() == out.numel()),
+       "sum_slots: residual must be bf16 with the shape of out");
   const c10::cuda::CUDAGuard guard(slots.device());
   tb::note_launch();
-  rc_check(tb::sum_slots_bf16(slots.data_ptr(), out.data_ptr(), static_cast<int>(slots.size(0)), out.numel(), cur_stream()),
+  rc_check(tb::sum_slots_bf16(slots.data_ptr(), out.data_ptr(), static_cast<int>(slots.size(0)), out.numel(), cur_stream(),
+                              opt_ptr(bias), opt_ptr(residual), static_cast<int>(out.size(-1))),
            "sum_slots");
 }
 
@@ -221,7 +237,9 @@ void bind_elementwise(pybind11::module_& m) {
   m.def("groupnorm_silu_bwd_apply", &groupnorm_silu_bwd_apply);
   m.def("masked_loss", &masked_loss);
   m.def("adamw_step", &adamw_step);
-  m.def("sum_slots", &sum_slots);
+  m.def("grad_inspect", &grad_inspect);
+  m.def("sum_slots", &sum_slots, pybind11::arg("slots"), pybind11::arg("out"), pybind11::arg("bias") = pybind11::none(),
+        pybind11::arg("residual") = pybind11::none());
   m.def("conv_s2_col2im", &conv_s2_col2im);
 }
 

@@ -39,7 +39,7 @@ int stream_wait_geq32(cudaStream_t stream, const void* addr, unsigned int value)
 int stream_write32(cudaStream_t stream, void* addr, unsigned int value);
 int gather_shards_async(cudaStream_t stream, void* dst, const void* const* src, int num_peers, int my_rank, long long rows,
                         size_t row_bytes, int chunks, long long chunk_rows, const unsigned int* signals, unsigned int* ready,
-                        unsigned int epoch);
+                        unsigned int epoch, int include_self = 0);
 // One-way "my earlier writes are visible" signal into word [slot_base + my_rank] of every peer's pad.
 int peer_signal(uint32_t* const* signal_pads, int my_rank, int num_peers, int slot_base, cudaStream_t stream);
 int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,

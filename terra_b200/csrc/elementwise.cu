@@ -477,6 +477,39 @@ __global__ void __launch_bounds__(256) masked_loss_kernel(const __nv_bfloat16* _
   }
 }
 
+// ------------------------------------------------------------------------------------------ gradient inspection
+// One pass over a flat fp32 gradient buffer for the loss-scaling path: out[0] += sum of squares (for the clipping
+// norm), out[1] becomes non-zero when any element is inf or nan (the step is then skipped and the scale backed off).
+__global__ void __launch_bounds__(256) grad_inspect_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) {
+  float acc = 0.f;
+  bool bad = false;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float v = g[i];
+    bad |= !(fabsf(v) <= 3.0e38f);     // false for inf and for nan
+    acc = fmaf(v, v, acc);
+  }
+  acc = warp_sum(acc);
+  const unsigned int any_bad = __ballot_sync(0xffffffffu, bad);
+  __shared__ float sh[8];
+  __shared__ unsigned int shb[8];
+  if ((threadIdx.x & 31) == 0) {
+    sh[threadIdx.x >> 5] = acc;
+    shb[threadIdx.x >> 5] = any_bad;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    unsigned int b = 0u;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) {
+      s += sh[w];
+      b |= shb[w];
+    }
+    if (b == 0u) atomicAdd(out, s);           // a poisoned sum would only hide the flag's meaning
+    else out[1] = 1.f;
+  }
+}
+
 // ------------------------------------------------------------------------------------------ AdamW
 template <bool GRAD_BF16>
 __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, float* __restrict__ m,
@@ -568,8 +601,11 @@ __global__ void conv_s2_col2im_kernel(const uint4* __restrict__ dcol, void* __re
   }
 }
 
-// out = sum over `slots` consecutive bf16 buffers of `nvec` 16-byte vectors each (fp32 accumulation)
-__global__ void sum_slots_bf16_kernel(const uint4* __restrict__ src, uint4* __restrict__ o, int slots, long long nvec) {
+// out = sum over `slots` consecutive bf16 buffers of `nvec` 16-byte vectors each (fp32 accumulation), optionally
+// + bias[col] (bf16, `cvec` vectors per row) + residual (bf16, same shape as out): the owner's side of the slot-staged
+// reduce-scatter with the row-parallel layer's bias and the block's shortcut folded in.
+__global__ void sum_slots_bf16_kernel(const uint4* __restrict__ src, uint4* __restrict__ o, int slots, long long nvec,
+                                      const uint4* __restrict__ bias, const uint4* __restrict__ res, int cvec) {
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float acc[8];
@@ -577,6 +613,18 @@ __global__ void sum_slots_bf16_kernel(const uint4* __restrict__ src, uint4* __re
     for (int s = 1; s < slots; ++s) {
       float y[8];
       unpack8(src[i + s * nvec], y);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += y[j];
+    }
+    if (bias != nullptr) {
+      float y[8];
+      unpack8(bias[i % cvec], y);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += y[j];
+    }
+    if (res != nullptr) {
+      float y[8];
+      unpack8(res[i], y);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += y[j];
     }
@@ -749,10 +797,19 @@ int conv_s2_col2im(const void* dcol, void* out, int B, int Ho, int Wo, int W, in
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int sum_slots_bf16(const void* src, void* out, int slots, long long n, cudaStream_t stream) {
+int grad_inspect(const float* grad, long long n, float* out2, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  grad_inspect_kernel<<<grid_for(n, 256 * 8, 148 * 8), 256, 0, stream>>>(grad, n, out2);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int sum_slots_bf16(const void* src, void* out, int slots, long long n, cudaStream_t stream, const void* bias,
+                   const void* residual, int cols) {
   if (n % 8 != 0 || slots < 1) return -1;
+  if (bias != nullptr && (cols <= 0 || cols % 8 != 0 || n % cols != 0)) return -1;
   sum_slots_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(out),
-                                                                  slots, n / 8);
+                                                                  slots, n / 8, static_cast<const uint4*>(bias),
+                                                                  static_cast<const uint4*>(residual), cols > 0 ? cols / 8 : 1);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

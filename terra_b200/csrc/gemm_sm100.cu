@@ -150,6 +150,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   }
 
   const int total_tiles = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
+  // Time budget of the CTA-internal waits. The producer of the tensor-parallel form may wait a_budget_ns for a peer's
+  // shard; the roles that consume its stages must outlast that wait, or ordinary rank skew would abort the tile.
+  const unsigned long long mbar_budget = TB_MBAR_BUDGET_NS + (PEERS ? p.a_budget_ns : 0ull);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -174,7 +177,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1u;
           const long long w0 = clock64();
-          if (!mbar_wait<PAIR>(&empty[s], ph ^ 1u, abort_flag, p.status, 0x100u + s)) break;
+          if (!mbar_wait<PAIR>(&empty[s], ph ^ 1u, abort_flag, p.status, 0x100u + s, mbar_budget)) break;
           t_wait += clock64() - w0;
           uint8_t* sA = smem + s * Cfg::STAGE_BYTES;
           uint8_t* sB = sA + Cfg::A_BYTES;
@@ -280,7 +283,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1u;
         const long long w0 = clock64();
-        if (!mbar_wait<PAIR>(&tempty[acc], aph ^ 1u, abort_flag, p.status, 0x200u + acc)) break;
+        if (!mbar_wait<PAIR>(&tempty[acc], aph ^ 1u, abort_flag, p.status, 0x200u + acc, mbar_budget)) break;
         t_acc += clock64() - w0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -289,8 +292,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1u;
           const long long w1 = clock64();
-          if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x300u + s)) { ok = false; break; }
-          if (PAIR && !mbar_wait<PAIR>(&pfull[s], ph, abort_flag, p.status, 0x380u + s)) { ok = false; break; }
+          if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x300u + s, mbar_budget)) { ok = false; break; }
+          if (PAIR && !mbar_wait<PAIR>(&pfull[s], ph, abort_flag, p.status, 0x380u + s, mbar_budget)) { ok = false; break; }
           t_ops += clock64() - w1;
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t ph = (it / Cfg::STAGES) & 1u;
-          if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x3c0u + s)) { ok = false; break; }
+          if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x3c0u + s, mbar_budget)) { ok = false; break; }
           mbar_arrive_remote(map_to_cta(&pfull[s], 0));
         }
         if (!ok) break;
@@ -446,7 +449,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         }
       }
       const long long ew0 = clock64();
-      if (!mbar_wait<PAIR>(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc)) break;
+      if (!mbar_wait<PAIR>(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc, mbar_budget)) break;
       e_wait += clock64() - ew0;
       tc_fence_after();
 

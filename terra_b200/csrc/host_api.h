@@ -95,6 +95,9 @@ int masked_loss_fwd_bwd(const void* pred, const void* label, const void* mask, l
 int adamw_step(float* master, float* exp_avg, float* exp_avg_sq, const void* grad, int grad_is_bf16, void* param_bf16,
                long long n, float lr, float beta1, float beta2, float eps, float weight_decay, float bias_corr1,
                float bias_corr2_sqrt, float grad_scale, cudaStream_t stream);
+// Loss-scaling support: out2[0] += sum of squares of the fp32 buffer, out2[1] = 1 when any element is inf / nan
+// (caller zeroes out2).
+int grad_inspect(const float* grad, long long n, float* out2, cudaStream_t stream);
 // bf16 <-> fp32 helpers
 int cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 // out[b, i, j, c] = a + b elementwise (bf16)
@@ -104,8 +107,9 @@ int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t 
 int conv_s2_col2im(const void* dcol, void* out, int B, int Ho, int Wo, int W, int C, int r0, int rows, int out_f32,
                    cudaStream_t stream);
 // out[n] = sum of `slots` consecutive bf16 buffers of n elements (fp32 accumulation); the owner's side of the
-// slot-staged reduce-scatter
-int sum_slots_bf16(const void* src, void* out, int slots, long long n, cudaStream_t stream);
+// slot-staged reduce-scatter. Optional: + bias[col] (bf16, `cols` columns per row) and + residual (bf16, n elements).
+int sum_slots_bf16(const void* src, void* out, int slots, long long n, cudaStream_t stream, const void* bias = nullptr,
+                   const void* residual = nullptr, int cols = 0);
 
 // window_attn.cu -------------------------------------------------------------------------------
 constexpr int WA_MAX_PEERS = 16;
@@ -120,6 +124,8 @@ struct WindowAttnArgs {
   int win_start[9];                // flat window range of window-group rank p: [win_start[p], win_start[p+1])
   int n_wg, my_wg;                 // ranks along the window dimension, and mine
   int sp, my_sp, shardN;           // tokens of a window are split into sp shards of shardN tokens
+  int tp;                          // > 1: every buffer is the concatenation of tp chunks [B, ceil(nW_p / tp) windows]
+                                   // (rows all-gathered over a tensor-parallel group); else [B, nW_p windows]
   int B, nWh, nWw;                 // batch and global window grid
   int wh, ww, sh, sw;              // window and cyclic shift (0 for regular blocks)
   int use_mask;                    // shifted-window region mask (-100)

@@ -2,6 +2,8 @@
 // The statistics scratch is a file-scope device array; its device address is resolved once per device.
 #include "terra_noalloc.h"
 
+#include <atomic>
+
 #include "common.cuh"
 #include "host_api.h"
 
@@ -11,7 +13,9 @@ namespace {
 static __device__ __align__(256) float g_gn_scratch[TERRA_NOALLOC_GN_MAX_CELLS * 4];
 
 constexpr int kMaxDevices = 64;
-float* g_scratch_addr[kMaxDevices] = {nullptr};
+// Device address of the array per device ordinal. Host threads may race on a device's first call: each resolves the
+// same address, and the atomic slot makes the publication well defined.
+std::atomic<float*> g_scratch_addr[kMaxDevices];
 
 __global__ void gn_clear_kernel(float* scratch, int cells) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -33,15 +37,17 @@ __global__ void gn_finalize_kernel(const float* sums, float* stats, int cells, f
 int scratch_for_current_device(float** out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TERRA_NOALLOC_ERR_SYMBOL;
-  if (g_scratch_addr[dev] == nullptr) {
+  float* addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_gn_scratch) != cudaSuccess || p == nullptr) {
       cudaGetLastError();
       return TERRA_NOALLOC_ERR_SYMBOL;
     }
-    g_scratch_addr[dev] = static_cast<float*>(p);
+    addr = static_cast<float*>(p);
+    g_scratch_addr[dev].store(addr, std::memory_order_release);
   }
-  *out = g_scratch_addr[dev];
+  *out = addr;
   return 0;
 }
 
@@ -61,9 +67,11 @@ extern "C" int terra_groupnorm_silu_noalloc(const void* x, const void* gamma, co
   float* stats = scratch + 2 * cells;         // [cells][2]
   const int n = static_cast<int>(cells);
   gn_clear_kernel<<<(n * 4 + 255) / 256, 256, 0, stream>>>(scratch, n);
+  if (cudaGetLastError() != cudaSuccess) return TERRA_NOALLOC_ERR_LAUNCH;   // nothing else is queued after a failed clear
   if (tb::groupnorm_stats(x, sums, B, HW, C, groups, stream) != 0) return TERRA_NOALLOC_ERR_LAUNCH;
   const float inv_count = 1.0f / (static_cast<float>(HW) * static_cast<float>(C / groups));
   gn_finalize_kernel<<<(n + 255) / 256, 256, 0, stream>>>(sums, stats, n, inv_count, eps);
+  if (cudaGetLastError() != cudaSuccess) return TERRA_NOALLOC_ERR_LAUNCH;
   if (tb::groupnorm_silu_apply(x, stats, gamma, beta, nullptr, y, B, HW, C, groups, stream) != 0)
     return TERRA_NOALLOC_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? 0 : TERRA_NOALLOC_ERR_LAUNCH;

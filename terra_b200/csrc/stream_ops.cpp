@@ -41,12 +41,17 @@ int stream_write32(cudaStream_t stream, void* addr, unsigned int value) {
 
 // For every peer p != my_rank, nearest first: wait for signals[p] >= epoch, then copy its shard (rows x row_bytes at
 // src[p], peer memory) to dst + p * rows * row_bytes with the copy engine in `chunks` pieces of chunk_rows rows and
-// publish ready[p * chunks + c] = epoch after piece c. Everything on `stream`.
+// publish ready[p * chunks + c] = epoch after piece c. Everything on `stream`. With include_self the own shard is
+// copied into its place too (no wait, no ready word), so that dst ends up holding the whole gathered operand.
 int gather_shards_async(cudaStream_t stream, void* dst, const void* const* src, int num_peers, int my_rank,
                         long long rows, size_t row_bytes, int chunks, long long chunk_rows, const unsigned int* signals,
-                        unsigned int* ready, unsigned int epoch) {
+                        unsigned int* ready, unsigned int epoch, int include_self) {
   if (num_peers < 1 || num_peers > COMM_MAX_PEERS || chunks < 1 || chunks > 4) return -1;
   const size_t shard = static_cast<size_t>(rows) * row_bytes;
+  if (include_self && shard > 0 &&
+      cudaMemcpyAsync(static_cast<char*>(dst) + my_rank * shard, src[my_rank], shard, cudaMemcpyDeviceToDevice, stream) !=
+          cudaSuccess)
+    return -21;
   for (int i = 1; i < num_peers; ++i) {
     const int p = (my_rank + i) % num_peers;
     int rc = stream_wait_geq32(stream, signals + p, epoch);

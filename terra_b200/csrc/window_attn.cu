@@ -77,10 +77,20 @@ __device__ __forceinline__ Home locate(const WindowAttnArgs& a, const Geo& g, in
   int wgr = 0;
   while (wgr + 1 < a.n_wg && flat >= a.win_start[wgr + 1]) ++wgr;
   const int nwp = a.win_start[wgr + 1] - a.win_start[wgr];
+  const int lw = flat - a.win_start[wgr];
   const int s = st / a.shardN;
   Home h;
   h.slot = wgr * a.sp + s;
-  h.row = (static_cast<long long>(b) * nwp + (flat - a.win_start[wgr])) * a.shardN + (st - s * a.shardN);
+  long long wrow;   // index of (batch, window) among the buffer's windows
+  if (a.tp <= 1) {
+    wrow = static_cast<long long>(b) * nwp + lw;
+  } else {
+    // rows gathered over tensor-parallel ranks: chunk t holds [B, wpt windows] of the group, chunks back to back
+    const int wpt = (nwp + a.tp - 1) / a.tp;
+    const int t = lw / wpt;
+    wrow = (static_cast<long long>(t) * a.B + b) * wpt + (lw - t * wpt);
+  }
+  h.row = wrow * a.shardN + (st - s * a.shardN);
   int rh = 0, rw = 0;
   if (a.sh > 0) rh = hs < g.Hg - a.wh ? 0 : (hs < g.Hg - a.sh ? 1 : 2);
   if (a.sw > 0) rw = ws < g.Wg - a.ww ? 0 : (ws < g.Wg - a.sw ? 1 : 2);

@@ -74,9 +74,34 @@ def get_model_for_train(model_archi_params, model_config, task_type="glorys", mo
     state = optimizer_state_tuple(model_config.get("optimizer_config", 4), model_config.get("tensor_parallel_size", 1))
     optimizer = get_optimizer(model, model_config, manager, use_dist_opt=state[3])
     gscaler = None
-    if model_config.get("precision", "bf16") == "fp16" and not (device is not None and torch.device(device).type == "cuda"):
-        gscaler = torch.amp.GradScaler("cpu", enabled=False)
     on_cuda = device is not None and torch.device(device).type == "cuda"
+    precision = model_config.get("precision", "bf16")
+    if precision not in ("fp32", "fp16", "bf16"):
+        raise ValueError(f"precision must be fp32, fp16 or bf16, got {precision!r}")
+    if on_cuda and precision == "fp32":
+        raise ValueError("precision: fp32 is not available on CUDA: the sm_100a kernels compute in bf16 with fp32 "
+                         "accumulation, masters and optimizer state. Use precision: bf16 (or fp16 for loss scaling); "
+                         "the fp32 model runs on the CPU build, which is the numerical oracle.")
+    if precision == "fp16":
+        if on_cuda:
+            import warnings
+
+            from ..optim.grad_scaler import LossScaler
+
+            warnings.warn("precision: fp16 -> bf16 arithmetic (the kernels have no fp16 path) with the dynamic loss "
+                          "scaler, inf/nan skip and fp16-only clipping kept", stacklevel=2)
+            gscaler = LossScaler(init_scale=float(model_config.get("loss_scale_init", 65536.0)),
+                                 growth_interval=int(model_config.get("loss_scale_growth_interval", 2000)))
+        else:
+            gscaler = torch.amp.GradScaler("cpu", enabled=False)
+    oc = int(model_config.get("optimizer_config", 4))
+    if oc in (1, 2, 3, 5, 7, 8, 9) and not getattr(get_model_for_train, "_warned_fallback", False):
+        import warnings
+
+        get_model_for_train._warned_fallback = True
+        warnings.warn(f"optimizer_config {oc}: DeepSpeed / FSDP wrappers are not used; this framework runs its own "
+                      "sharded optimizer (fp32 masters and moments sharded over the replica group, bf16 working copy "
+                      "replicated)", stacklevel=2)
     if on_cuda and manager is not None and manager.wp_size > 1 and model_config.get("comm_backend", "nvlink") == "nvlink":
         from ..parallel import nvlink
 

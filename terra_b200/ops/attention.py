@@ -31,6 +31,7 @@ class WindowGeometry:
     my_wg: int = 0
     sp: int = 1
     my_sp: int = 0
+    tp: int = 1          # > 1: the q/k/v rows are the concatenation of tp chunks [B, ceil(nW/tp) windows] (TP all-gather)
 
     def __post_init__(self):
         if not self.win_start:
@@ -174,7 +175,7 @@ class _WindowAttnFn(torch.autograd.Function):
             out, qkv_ptrs, out_ptrs = comm.attn_forward_buffers(qkv, C, shifted)
         ext.window_attn_fwd(qkv_ptrs, out_ptrs, bias_f32, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
                             geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh, geo.ww, sh, sw,
-                            bool(use_mask and shifted), float(scale))
+                            bool(use_mask and shifted), float(scale), geo.tp)
         if comm is not None:
             out, qkv = comm.attn_forward_done(out, qkv, shifted)
         ctx.save_for_backward(qkv, bias_f32 if bias_f32 is not None else torch.empty(0, device=qkv.device))
@@ -201,7 +202,7 @@ class _WindowAttnFn(torch.autograd.Function):
         ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32 if ctx.has_bias else None, dbias,
                             list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw,
                             C, ctx.num_heads, geo.wh, geo.ww, sh, sw, bool(ctx.use_mask and ctx.shifted),
-                            float(ctx.scale))
+                            float(ctx.scale), geo.tp)
         if comm is not None:
             dqkv = comm.attn_backward_done(dqkv, ctx.shifted)
         return dqkv, dbias, None, None, None, None, None, None

@@ -91,7 +91,7 @@ class _AttnHalfFn(torch.autograd.Function):
         sh, sw = geo.shift(shifted)
         ext.window_attn_fwd(qkv_ptrs, out_ptrs, pk.bias_table, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
                             geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh, geo.ww, sh, sw,
-                            bool(use_mask and shifted), float(scale))
+                            bool(use_mask and shifted), float(scale), geo.tp)
         if comm is not None:
             o, qkv = comm.attn_forward_done(o, qkv, shifted)
         y = gemm(o, pk.proj_w, bias=pk.proj_b, residual=x)
@@ -120,7 +120,7 @@ class _AttnHalfFn(torch.autograd.Function):
         sh, sw = geo.shift(shifted)
         ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, pk.bias_table, pk.bias_table_g, list(geo.win_start),
                             geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh,
-                            geo.ww, sh, sw, bool(use_mask and shifted), float(scale))
+                            geo.ww, sh, sw, bool(use_mask and shifted), float(scale), geo.tp)
         if comm is not None:
             dqkv = comm.attn_backward_done(dqkv, shifted)
         wgrad_accumulate(dqkv, xn, pk.qkv_wg)

@@ -114,7 +114,7 @@ def case_attn(a):
     dtable = torch.zeros_like(table)
     sh = a.ws // 2 if a.shifted else 0
     args = (list(geo.win_start), 0, 1, 0, geo.N, 1, geo.nWh, geo.nWw, C, heads, a.ws, a.ws, sh, sh, bool(a.shifted),
-            (C // heads) ** -0.5)
+            (C // heads) ** -0.5, 1)
     if a.bwd:
         fn = lambda: ext.window_attn_bwd([qkv.data_ptr()], [out.data_ptr()], [dqkv.data_ptr()], table, dtable, *args)
         flops = 2.0 * rows * geo.N * C * 5

@@ -127,9 +127,11 @@ class ParallelContext:
                 for g in range(self.n_wg))
 
     # ------------------------------------------------------------------ geometry
-    def geometry(self, batch: int) -> WindowGeometry:
+    def geometry(self, batch: int, tp_chunked: bool = False) -> WindowGeometry:
+        """``tp_chunked``: the q/k/v rows come out of the fused all-gather GEMM, i.e. as the concatenation of the
+        tensor-parallel ranks' ``[B, windows per rank, tokens]`` chunks instead of ``[B, windows of the group, tokens]``."""
         return WindowGeometry(batch, self.nWh, self.nWw, self.wh, self.ww, list(self.win_start), self.wg_rank, self.sp,
-                              self.sp_rank)
+                              self.sp_rank, self.tp if tp_chunked else 1)
 
     def rows_between_blocks(self, batch: int) -> int:
         return batch * self.tp_sizes_windows[self.tp_rank] * self.shardN
@@ -141,6 +143,13 @@ class ParallelContext:
         comm = self._attn_comm(batch)
         if self.sp == 1 and self.tp == 1 and (comm is None or getattr(comm, "fused", False)):
             return B.attention_half(x, mod, geo, mod.shifted, comm)
+        tpc = getattr(self, "tp_comm", None)
+        if (self.tp > 1 and tpc is not None and x.is_cuda and (comm is None or getattr(comm, "fused", False))
+                and self.N <= B.MAX_KERNEL_WINDOW_TOKENS):
+            # both collectives of the tensor-parallel attention half run inside the GEMMs over NVLink peer memory
+            from ..ops.tp_fused import tp_attention_half
+
+            return tp_attention_half(x, mod, self.geometry(batch, tp_chunked=True), comm, tpc, batch * self.wpt * self.shardN)
         return self._attention_half_factorized(x, mod, geo, batch)
 
     def mlp_half(self, x, mod):
@@ -207,16 +216,13 @@ class ParallelContext:
 
     def _mlp_half_tp(self, x, mod):
         batch = self._batch_of(x)
-        xn = self._ln(x, mod.norm2)
         tpc = getattr(self, "tp_comm", None)
-        if tpc is not None and x.is_cuda and batch == 1 and len(set(self.tp_sizes_windows)) == 1:
+        if tpc is not None and x.is_cuda:
             # fc1 / fc2 with their all-gather / reduce-scatter fused into the GEMMs over NVLink peer memory
-            from ..ops.tp_fused import tp_mlp
+            from ..ops.tp_fused import tp_mlp_half
 
-            l1, l2 = mod.linear1, mod.linear2
-            y = tp_mlp(xn.contiguous(), l1.weight.bf16, l1.bias.bf16, l2.weight.bf16, tpc, anchor=l1.weight,
-                       grads=(l1.weight.grad, l1.bias.grad, l2.weight.grad))
-            return x + y + mod.bias2.to(y.dtype)
+            return tp_mlp_half(x, mod, tpc, batch * self.wpt * self.shardN)
+        xn = self._ln(x, mod.norm2)
         xa = self._ag_tp(xn, batch)
         h = self._lin(xa, mod.linear1)
         h = TF.gelu(h.float()).to(h.dtype) if h.is_cuda else TF.gelu(h)

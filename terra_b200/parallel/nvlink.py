@@ -131,14 +131,18 @@ class SymmetricArena:
 
     def release_waits(self) -> None:
         """Satisfy every stream memory-operation wait that may still be queued on this rank's signal words (the
-        copy-engine gather waits for a peer's signal without a time limit of its own). Called at shutdown and after a
-        peer was reported lost, so that a dead peer cannot keep this process's streams - and its exit - blocked.
-        The arena is unusable for signalling afterwards."""
-        words = self.buf[4 * self.SIGNAL_SLOT:4 * (self.SIGNAL_SLOT + COMM_MAX_PEERS)]
+        copy-engine gather waits for a peer's signal without a time limit of its own). Called at shutdown, by the
+        host watchdog when such a wait outlives its budget and after a peer was reported lost, so that a dead peer
+        cannot keep this process's streams - and its exit - blocked. The words are written with stream memory
+        operations (no SM needed, so a resident persistent kernel cannot delay them). The arena is unusable for
+        signalling afterwards."""
+        ext = _ext.load()
         side = torch.cuda.Stream(self.buf.device)
-        with torch.cuda.stream(side):
-            words.fill_(0x7F)          # 0x7f7f7f7f: above any epoch a run reaches
+        base = self.base_ptrs[self.rank] + 4 * self.SIGNAL_SLOT
+        for i in range(COMM_MAX_PEERS):
+            ext.stream_write_value(side.cuda_stream, base + 4 * i, 0x7F7F7F7F)     # above any epoch a run reaches
         side.synchronize()
+        self.released = True
 
     def barrier(self) -> None:
         """Stream-ordered barrier over the group (device side; the host does not wait)."""
@@ -258,8 +262,9 @@ def attach(model, optimizer, manager) -> None:
 
         rows = max(pctx.tp_sizes_windows) * pctx.shardN * pctx.B
         C, F = model.embedding_dim, 4 * model.embedding_dim
-        # per MLP forward + backward: staged xn, dy (bf16), reduce-scatter slots (bf16 x tp x 2)
-        per_layer = rows * (2 * C * 2 + 2 * pctx.tp * C * 2)
+        # per block half, forward + backward: staged xn, dy (bf16), reduce-scatter slots (bf16 x tp x 2); two halves per
+        # layer; recomputed segments stage their forward buffers a second time within the step
+        per_layer = 2 * rows * (2 * C * 2 + 2 * pctx.tp * C * 2)
         nbytes = int(per_layer * model.num_layers * 1.5) + (64 << 20)
         pctx.tp_arena = SymmetricArena(manager.xfmr_tp_group, nbytes, device)
         pctx.tp_comm = TpFusedComm(pctx.tp_arena)

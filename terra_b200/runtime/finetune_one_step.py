@@ -15,7 +15,7 @@ import torch.distributed as dist
 from ..ops.loss import masked_loss
 from ..profiler.memory_timeline import mark_memory_timeline, set_memory_timeline_context
 from .run_model import make_global_report_loss
-from .run_one_step import criterion_name, grad_post_process, loss_scale_factor
+from .run_one_step import criterion_name, grad_post_process, loss_scale_factor, loss_scale_of, optimizer_step
 
 
 def _lead_scale(lead_time, loss_reduction):
@@ -68,20 +68,20 @@ def run_one_step_for_finetune_train(task_type, model_type, model, optimizer, eng
                              task_specific_data_dict, USE_FSDP)
     optimizer.zero_grad()
     mark_memory_timeline("before_forward")
+    on_cuda = next(model.parameters()).is_cuda
+    scale = loss_scale_of(gscaler, precision, on_cuda)
     outs, loss = finetune_run(task_type, model, required_tensors, task_specific_data_dict, loss_fn, lead_time,
-                              loss_reduction, lead_callback, post)
+                              loss_reduction, lead_callback, post * scale)
     mark_memory_timeline("after_forward")
     set_memory_timeline_context(execution_phase="backward")
     mark_memory_timeline("before_backward")
     loss.backward()
     mark_memory_timeline("after_backward")
     grad_post_process(model_type, optimizer_state_tuple, model, manager, dp_average=not hasattr(model, "module"))
-    if clip_grad and precision == "fp16":
-        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
-    optimizer.step()
+    optimizer_step(model, optimizer, gscaler, precision, clip_grad, on_cuda, scale)
     optimizer.global_step += 1
     mark_memory_timeline("after_optimizer")
-    return outs[0], loss
+    return outs[0], (loss.detach() / scale if scale != 1.0 else loss)
 
 
 @torch.no_grad()

@@ -13,7 +13,7 @@ import torch.distributed as dist
 
 from ..profiler.memory_timeline import mark_memory_timeline
 from .run_one_step import (backbone_run, cal_loss, fused_forward_loss, grad_post_process, loss_post_process,
-                           loss_scale_factor)
+                           loss_scale_factor, loss_scale_of, optimizer_step)
 
 
 def make_global_report_loss(loss, manager, model_type):
@@ -62,9 +62,13 @@ def one_step_train(task_type, model_type, model, engine, optimizer, required_ten
     post_scale = loss_scale_factor(model_type, other_params.get("embedding_parallel_type") if other_params else None,
                                    manager, task_specific_data_dict, USE_FSDP)
     optimizer.zero_grad()
+    scale = loss_scale_of(gscaler, precision, on_cuda)
     if on_cuda:
-        # the sm_100a kernels take bf16 activations and fp32 masters directly: no autocast context is needed
-        output, loss = fused_forward_loss(task_type, model, required_tensors, task_specific_data_dict, loss_fn, post_scale)
+        # The sm_100a kernels take bf16 activations and fp32 masters directly, so no autocast context is needed and
+        # `precision` selects only the loss-scaling behaviour: "bf16" none, "fp16" the dynamic scaler (bf16 arithmetic,
+        # GradScaler semantics), "fp32" is refused when the model is built (terra_b200.models.get_model).
+        output, loss = fused_forward_loss(task_type, model, required_tensors, task_specific_data_dict, loss_fn,
+                                          post_scale * scale)
     else:
         outs = backbone_run(task_type, model, required_tensors, task_specific_data_dict)
         output = outs[0]
@@ -88,11 +92,11 @@ def one_step_train(task_type, model_type, model, engine, optimizer, required_ten
         from .grad_debug import show_gradient
 
         show_gradient(model, manager, getattr(manager, "xfmr_tp_group", None) if manager is not None else None)
-    if clip_grad and precision == "fp16":
-        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
     mark_memory_timeline("before_optimizer")
-    optimizer.step()
+    optimizer_step(model, optimizer, gscaler, precision, clip_grad, on_cuda, scale)
     optimizer.global_step += 1
+    if scale != 1.0:
+        loss = loss.detach() / scale
     mark_memory_timeline("after_optimizer")
 
     if on_cuda:

@@ -111,3 +111,28 @@ def grad_post_process(model_type, optimizer_state_tuple, model, manager, dp_aver
         dist.all_reduce(p.grad, group=group)
         if dp_average and dp > 1:
             p.grad.div_(dp)
+
+
+def loss_scale_of(gscaler, precision, on_cuda) -> float:
+    """Factor folded into the loss gradient on CUDA when ``precision: fp16`` runs with the dynamic loss scaler
+    (``terra_b200.optim.grad_scaler.LossScaler``); 1.0 otherwise."""
+    if on_cuda and precision == "fp16" and gscaler is not None and hasattr(gscaler, "get_scale") and gscaler.is_enabled():
+        return float(gscaler.get_scale())
+    return 1.0
+
+
+def optimizer_step(model, optimizer, gscaler, precision, clip_grad, on_cuda, scale) -> bool:
+    """The optimizer step of both training loops (reference: core/runtime/run_model.py:512-514, 571-593): with loss
+    scaling, inspect the gradients once (inf / nan flag shared by all ranks, squared norm for the fp16-only clipping at
+    max-norm 1.0), fold un-scaling and clipping into the optimizer kernel, skip the step on overflow and update the
+    scale; without it, clip (fp16 only) and step. Returns ``True`` when the parameters were updated."""
+    if scale != 1.0 or (on_cuda and precision == "fp16" and gscaler is not None and hasattr(gscaler, "inspect")):
+        arena = get_arena(_unwrap(model))
+        group = dist.group.WORLD if (dist.is_available() and dist.is_initialized()) else None
+        ran = gscaler.step(optimizer, arena.grad, clip_max_norm=1.0 if clip_grad else None, group=group)
+        gscaler.update()
+        return ran
+    if clip_grad and precision == "fp16":
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+    optimizer.step()
+    return True

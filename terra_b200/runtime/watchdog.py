@@ -1,6 +1,6 @@
 """Host-side failure detection (the reference has none: a dead rank there shows up as a hung collective).
 
-Two pieces, both free of any device-side fault:
+Pieces, all free of any device-side fault:
 
 * ``RankMonitor``: every rank publishes a heartbeat ``(step, wall time)`` in a ``torch.distributed`` store between
   steps; before launching the next step a rank asks for the peers that have stopped beating and raises
@@ -8,12 +8,19 @@ Two pieces, both free of any device-side fault:
 * ``check_device_status``: turns the status word that the kernels' bounded waits write (mbarrier waits of the GEMM,
   waits on a peer's flag in the NVLink kernels) into a Python exception.
 
+* ``StreamWaitWatchdog``: a host thread that bounds the stream memory-operation waits of the copy-engine all-gather
+  (they have no time limit of their own): past the budget it releases the waits and records the failure.
+* ``StepGuard``: what the training loops call between steps - heartbeat, peer check, status word, watchdogs; on a
+  lost peer it releases every arena's stream waits before raising.
+
 Recovery is the checkpoint / ``ckpt_start`` path of the training scripts; elastic resizing is out of scope (as in the
 reference)."""
 from __future__ import annotations
 
+import os
+import threading
 import time
-from typing import Dict, List, Optional
+from typing import Callable, Dict, List, Optional
 
 
 class PeerLost(RuntimeError):
@@ -82,3 +89,150 @@ def check_device_status(device) -> None:
     from ..ops.gemm import check_status
 
     check_status(device)
+
+
+class StreamWaitExpired(RuntimeError):
+    """A stream memory-operation wait on a peer's signal outlived its budget and was released by the host."""
+
+
+class StreamWaitWatchdog:
+    """Bounds the waits that ``gather_shards_async`` queues on a side stream. ``arm()`` (called when a gather is queued)
+    sets a deadline ``budget_s`` ahead; a daemon thread polls the stream and, if it is still busy past the deadline,
+    calls ``arena.release_waits()`` - the queued waits complete, the stream drains, nothing is left blocked - and
+    remembers the event. ``check()`` (training loop, between steps) raises it. The gathered data of a released wait is
+    incomplete, so the step's result must be discarded: the loop stops and resumes from the last checkpoint."""
+
+    def __init__(self, arena, stream_of: Callable[[], object], budget_s: Optional[float] = None, poll_s: float = 0.05):
+        self.arena, self.stream_of = arena, stream_of
+        self.budget_s = float(os.environ.get("TERRA_PEER_WAIT_MS", "5000")) * 1e-3 if budget_s is None else budget_s
+        self.poll_s = poll_s
+        self.tripped: Optional[str] = None
+        self._deadline: Optional[float] = None
+        self._lock = threading.Lock()
+        self._thread: Optional[threading.Thread] = None
+        self._stop = False
+
+    def arm(self) -> None:
+        with self._lock:
+            self._deadline = time.monotonic() + self.budget_s
+        if self._thread is None:
+            self._thread = threading.Thread(target=self._run, name="terra-stream-wait-watchdog", daemon=True)
+            self._thread.start()
+
+    def _run(self) -> None:
+        import torch
+
+        dev = getattr(getattr(self.arena, "buf", None), "device", None)
+        if dev is not None and dev.type == "cuda":
+            torch.cuda.set_device(dev)
+        while not self._stop:
+            time.sleep(self.poll_s)
+            with self._lock:
+                deadline = self._deadline
+            if deadline is None:
+                continue
+            stream = self.stream_of()
+            if stream is None or stream.query():        # drained: every wait was satisfied
+                with self._lock:
+                    if self._deadline == deadline:
+                        self._deadline = None
+                continue
+            if time.monotonic() > deadline:
+                self.tripped = (f"a stream wait on a peer's signal was still pending {self.budget_s:.2f} s after it was "
+                                "queued; released by the host watchdog")
+                try:
+                    self.arena.release_waits()
+                finally:
+                    with self._lock:
+                        self._deadline = None
+
+    def check(self) -> None:
+        if self.tripped is not None:
+            msg, self.tripped = self.tripped, None
+            raise StreamWaitExpired(msg)
+
+    def close(self) -> None:
+        self._stop = True
+
+
+class StepGuard:
+    """Failure detection wired into a training loop. Call ``after_step(step)`` once per step where the host already
+    synchronises (after the loss was read): it raises ``RuntimeError`` when a kernel's bounded wait ran out (status
+    word), ``StreamWaitExpired`` when a watchdog released a stream wait, and ``PeerLost`` when a peer stopped
+    beating - in which case every symmetric arena's stream waits are released first, so that no stream of this
+    process stays blocked on the dead peer."""
+
+    def __init__(self, device, monitor: Optional[RankMonitor] = None, model=None, optimizer=None, arenas=(),
+                 watchdogs=(), check_every: int = 1):
+        self.device, self.monitor = device, monitor
+        self.model, self.optimizer = model, optimizer
+        self.extra_arenas, self.extra_watchdogs = list(arenas), list(watchdogs)
+        self.check_every = max(1, int(check_every))
+
+    def arenas(self):
+        real = self.model.module if hasattr(self.model, "module") else self.model
+        pctx = getattr(real, "pctx", None)
+        found = [getattr(pctx, n, None) for n in ("attn_arena", "tp_arena", "dom_arena")]
+        fused = getattr(self.optimizer, "fused", None)
+        if fused is not None:
+            found += list(getattr(fused, "arenas", {}).values())
+        return [a for a in found if a is not None] + self.extra_arenas
+
+    def watchdogs(self):
+        real = self.model.module if hasattr(self.model, "module") else self.model
+        tpc = getattr(getattr(real, "pctx", None), "tp_comm", None)
+        wd = getattr(tpc, "watchdog", None)
+        return ([wd] if wd is not None else []) + self.extra_watchdogs
+
+    def after_step(self, step: int) -> None:
+        import torch
+
+        for w in self.watchdogs():
+            w.check()
+        if torch.device(self.device).type == "cuda" and step % self.check_every == 0:
+            check_device_status(self.device)
+        if self.monitor is not None:
+            self.monitor.beat(step)
+            try:
+                self.monitor.assert_alive(min_step=step)
+            except PeerLost:
+                self.release()
+                raise
+
+    def release(self) -> None:
+        for a in self.arenas():
+            try:
+                a.release_waits()
+            except Exception:
+                pass
+
+    def close(self, announce: bool = True) -> None:
+        """``announce``: tell the peers that this rank leaves (they then fail fast). Not wanted when only this guard's
+        model is dropped and the process carries on with another one."""
+        if self.monitor is not None and announce:
+            try:
+                self.monitor.leave()
+            except Exception:
+                pass
+        for w in self.watchdogs():
+            w.close()
+
+
+_guards_made = 0
+
+
+def make_step_guard(device, rank: int, world: int, model=None, optimizer=None) -> StepGuard:
+    """The guard the entry points use: heartbeats go through the default process group's store
+    (``TERRA_HEARTBEAT_STALE_S`` seconds without a beat, default 120, count as lost). Every guard of a process gets
+    its own key prefix (all ranks build their guards in the same order), so a second trainer in the same job does not
+    read the first one's last words."""
+    import torch.distributed as dist
+
+    global _guards_made
+    monitor = None
+    if world > 1 and dist.is_available() and dist.is_initialized():
+        store = dist.distributed_c10d._get_default_store()
+        monitor = RankMonitor(store, rank, world, stale_after_s=float(os.environ.get("TERRA_HEARTBEAT_STALE_S", "120")),
+                              prefix=f"terra_hb{_guards_made}")
+    _guards_made += 1
+    return StepGuard(device, monitor, model, optimizer)

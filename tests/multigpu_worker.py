@@ -21,8 +21,11 @@ def main():
                width=512, num_channels=32, patch_size=4, embedding_dim=128, depths=[2, 2], num_heads=[4, 8], num_layers=4,
                window_size=8, padding_policy="auto", window_assignment_mode="terra_m1_ragged_auto", precision="bf16",
                loss_func="L1", learning_rate=1e-3, optimizer_config=6 if world > 1 else 4, wp_topo=f"({world}, 1)")
+    dp = int(layout.pop("dp", 1))
+    if dp > 1:
+        cfg["wp_topo"] = f"({world // dp}, 1)"
     cfg.update(layout)
-    t = Trainer(cfg, data_parallel_group_size=1)
+    t = Trainer(cfg, data_parallel_group_size=dp)
     losses = []
     for i in range(steps):
         # every rank generates its own stripe of the same global field
@@ -33,7 +36,9 @@ def main():
     if t.rank == 0:
         print("RESULT " + json.dumps({"losses": total.tolist(), "fused_attn": t.model.pctx.fused_comm is not None,
                                       "fused_opt": getattr(t.optimizer, "fused", None) is not None,
-                                      "fused_tp": getattr(t.model.pctx, "tp_comm", None) is not None}), flush=True)
+                                      "fused_tp": getattr(getattr(t.model.pctx, "tp_comm", None), "calls", {}).get("mlp", 0) > 0,
+                                      "fused_tp_attn": getattr(getattr(t.model.pctx, "tp_comm", None), "calls", {}).get("attn", 0) > 0}),
+              flush=True)
     t.close()
 
 

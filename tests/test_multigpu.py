@@ -41,21 +41,31 @@ def _need(n):
         pytest.skip(f"needs {n} GPUs")
 
 
+SHAPE_KEYS = ("height", "width", "window_size", "depths", "num_heads", "num_layers", "embedding_dim")
+
+
 @pytest.mark.parametrize("n,layout", [
     (2, {"xfmr_wp_topo": "(2, 1)"}),
     (2, {"xfmr_wp_topo": "(1, 1)", "xfmr_sp_size": 2}),
     (2, {"xfmr_wp_topo": "(1, 1)", "tensor_parallel_size": 2}),
+    # 3 x 7 windows: the two tensor-parallel ranks hold 11 and 10 windows (zero-padded symmetric buffers)
+    (2, {"xfmr_wp_topo": "(1, 1)", "tensor_parallel_size": 2, "height": 192, "width": 448}),
     (4, {"xfmr_wp_topo": "(4, 1)"}),
     (4, {"xfmr_wp_topo": "(2, 1)", "xfmr_sp_size": 2}),
+    (4, {"xfmr_wp_topo": "(1, 1)", "xfmr_sp_size": 2, "tensor_parallel_size": 2}),
+    (4, {"xfmr_wp_topo": "(1, 1)", "tensor_parallel_size": 4}),
+    (4, {"xfmr_wp_topo": "(2, 1)", "dp": 2}),
+    (8, {"xfmr_wp_topo": "(2, 1)", "xfmr_sp_size": 2, "tensor_parallel_size": 2}),
 ])
 def test_layout_matches_single_gpu(n, layout):
     _need(n)
-    ref = _launch(1, {})
+    ref = _launch(1, {k: v for k, v in layout.items() if k in SHAPE_KEYS})
     got = _launch(n, layout)
     for a, b in zip(got["losses"], ref["losses"]):
         assert abs(a - b) < 3e-2 * abs(b), (got, ref)
     if layout.get("tensor_parallel_size", 1) > 1:
         assert got["fused_tp"], "the tensor-parallel MLP must run on the fused all-gather / reduce-scatter GEMMs"
+        assert got["fused_tp_attn"], "the tensor-parallel attention half must run on the fused GEMMs too"
 
 
 @pytest.mark.parametrize("n", [2])

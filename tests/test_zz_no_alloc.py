@@ -4,7 +4,9 @@ Some users of the library run where device allocation is forbidden (inside anoth
 loop that bans cudaMalloc after start-up); ``terra_groupnorm_silu_noalloc`` serves them with a scratch array built
 into the library. This test loads the shared object with ctypes, calls the symbol twice in a row on different
 inputs (the scratch keeps the previous call's contents, so the second call checks that it is cleared) and compares
-with the regular two-kernel path of the extension.
+with the regular two-kernel path of the extension and with PyTorch's fp32 ``group_norm`` + ``silu``. "Allocates
+nothing" is checked twice: PyTorch's caching allocator saw no request, and the driver's free-memory figure
+(``cudaMemGetInfo``, which a raw ``cudaMalloc`` inside the library would move) is unchanged.
 """
 import ctypes
 
@@ -44,14 +46,24 @@ def test_noalloc_groupnorm_silu_matches_regular_path_twice():
         g = torch.randn(C, device="cuda").to(torch.bfloat16)
         b = torch.randn(C, device="cuda").to(torch.bfloat16)
         y = torch.empty_like(x)
+        if call == 0:
+            # the very first call on a device resolves the scratch address; take the driver's figure after it
+            assert fn(x.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), B, HW, C, groups, eps, stream) == 0
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = fn(x.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), B, HW, C, groups, eps, stream)
         assert rc == 0, rc
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         ref = _regular(ext, x, g, b, groups, eps)
         err = (y.float() - ref.float()).abs().max().item()
         assert err <= 2e-2 + 2e-2 * ref.float().abs().max().item(), (call, err)
+        xt = x.float().permute(0, 2, 1)                                   # [B, C, HW]
+        ref32 = torch.nn.functional.silu(torch.nn.functional.group_norm(xt, groups, g.float(), b.float(), eps)).permute(0, 2, 1)
+        err32 = (y.float() - ref32).abs().max().item()
+        assert err32 <= 2e-2 + 2e-2 * ref32.abs().max().item(), (call, err32)
     # sizes beyond the built-in scratch are refused, nothing is launched
     big = torch.empty(200, 8, 32, device="cuda", dtype=torch.bfloat16)
     w = torch.ones(32, device="cuda", dtype=torch.bfloat16)

@@ -88,6 +88,10 @@ class Session:
         self.task_data = get_task_specific_data(self.task_type, self.device, self.opt_state, self.archi, self.other,
                                                 self.manager, self.cfg["micro_batch_size"], self.model_type, self.cfg)
         self.data_dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        from terra_b200.runtime.watchdog import make_step_guard
+
+        # failure detection between steps: peer heartbeats, the kernels' status word, stream-wait watchdogs
+        self.guard = make_step_guard(self.device, self.rank, self.world, self.model, self.optimizer)
 
     def pretrain_loader(self, status=0):
         c = self.cfg
@@ -121,6 +125,8 @@ class Session:
 
     def close(self):
         import torch.distributed as dist
+
+        self.guard.close()
 
         if dist.is_available() and dist.is_initialized():
             dist.destroy_process_group()

@@ -100,6 +100,7 @@ def main(argv=None):
                 loss_reduction=c["finetune_loss_reduction"], clip_grad=c["clip_grad"], sync_for_timing=False,
                 barrier_for_timing=False)
             last = float(loss.item())
+            s.guard.after_step(s.optimizer.global_step)      # raises on a lost peer or a timed-out device wait
             if hasattr(frames, "release"):
                 frames.release()
             if log_file is not None:

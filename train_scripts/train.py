@@ -50,6 +50,7 @@ def main(argv=None):
                 s.task_type, s.model_type, s.model, s.engine, s.optimizer, tensors, s.task_data, s.other, s.precision,
                 c["half_model"], s.my_dtype, s.loss_fn, s.gscaler, s.manager, s.opt_state, clip_grad=c["clip_grad"])
             last_loss = float(loss.item())
+            s.guard.after_step(s.optimizer.global_step)      # raises on a lost peer or a timed-out device wait
             if log_file is not None:
                 log_file.write(f"{c['description']} epoch {epoch} step {step} loss {last_loss:.8f} lr {lr:.3e} "
                                f"global_step {s.optimizer.global_step} step_time_s {step_time:.4f} "
