@@ -14,7 +14,8 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
-BUILD_DIR = os.path.join(_HERE, "_build")
+# TERRA_B200_BUILD_DIR: use (and build into) another directory, e.g. to keep two builds of the kernels side by side
+BUILD_DIR = os.environ.get("TERRA_B200_BUILD_DIR") or os.path.join(_HERE, "_build")
 EXT_NAME = "terra_b200_C"
 
 CUDA_FLAGS = [

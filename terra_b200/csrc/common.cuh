@@ -105,27 +105,25 @@ __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
 }
 // Bounded wait. `abort_flag` lives in shared memory; once any role of the CTA gives up,
 // every later wait of the CTA returns false at once so that all roles drain and the CTA
-// reaches its teardown (TMEM release) instead of spinning for ever. The bound is a time budget on the GPU's global
-// timer (not an iteration count, whose duration depends on clocks and contention): a kernel whose producer may itself
-// wait for another GPU passes a budget larger than the producer's, so that the consumer roles outlast it.
-#ifndef TB_MBAR_BUDGET_NS
-#define TB_MBAR_BUDGET_NS 2000000000ull
+// reaches its teardown (TMEM release) instead of spinning for ever. The bound is a poll count (about a second of
+// polling at TB_MBAR_SPIN_LIMIT: 64 ns of sleep per 256 polls plus the polls themselves) times `scale`. A kernel
+// whose producer may itself wait for another GPU (bounded there by the global timer) passes a scale that makes the
+// consumer roles outlast that wait, so that rank skew cannot abort a tile whose data would have arrived in time.
+#ifndef TB_MBAR_SPIN_LIMIT
+#define TB_MBAR_SPIN_LIMIT (1u << 24)
 #endif
-__device__ __forceinline__ unsigned long long global_timer_ns();
 // CLUSTER marks waits on barriers that the other CTA of a pair (or its tensor core) signals. They use the same
 // CTA-scope wait: a cluster-scope acquire on every poll costs about a microsecond per hand-over (measured).
 template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          KernelStatus* st, unsigned int where,
-                                          unsigned long long budget_ns = TB_MBAR_BUDGET_NS) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > budget_ns) break;
-      __nanosleep(64);
+                                          KernelStatus* st, unsigned int where, uint32_t scale = 1u) {
+  for (uint32_t round = 0; round < scale; ++round) {
+    for (uint32_t i = 0; i < TB_MBAR_SPIN_LIMIT; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((i & 255u) == 255u) {
+        if (*abort_flag) return false;
+        __nanosleep(64);
+      }
     }
   }
   *abort_flag = 1;

@@ -150,9 +150,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   }
 
   const int total_tiles = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
-  // Time budget of the CTA-internal waits. The producer of the tensor-parallel form may wait a_budget_ns for a peer's
-  // shard; the roles that consume its stages must outlast that wait, or ordinary rank skew would abort the tile.
-  const unsigned long long mbar_budget = TB_MBAR_BUDGET_NS + (PEERS ? p.a_budget_ns : 0ull);
+  // Bound of the CTA-internal waits, in units of about a second of polling. The producer of the tensor-parallel form
+  // may wait a_budget_ns (global timer) for a peer's shard; the roles that consume its stages must outlast that wait,
+  // or ordinary rank skew would abort a tile whose data arrives in time. Measured polling rates put one unit between
+  // 0.3 and 2 s, so 4 units per second of peer budget (+ 1) stay above it.
+  const uint32_t mbar_budget = PEERS ? 1u + 4u * static_cast<uint32_t>((p.a_budget_ns + 999999999ull) / 1000000000ull) : 1u;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -449,7 +451,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         }
       }
       const long long ew0 = clock64();
-      if (!mbar_wait<PAIR>(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc, mbar_budget)) break;
+      // Every lane polls for itself and may leave the wait in a different iteration; the vote reconverges the warp
+      // before the warp-collective tcgen05.ld below (and makes a failed wait leave the loop as one warp).
+      const bool tile_ready = mbar_wait<PAIR>(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc, mbar_budget);
+      if (!__all_sync(0xffffffffu, tile_ready)) break;
       e_wait += clock64() - ew0;
       tc_fence_after();
 

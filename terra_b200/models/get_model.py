@@ -68,6 +68,9 @@ def optimizer_state_tuple(optimizer_config: int, tensor_parallel_size: int = 1):
 def get_model_for_train(model_archi_params, model_config, task_type="glorys", model_type="sequential",
                         embedding_parallel_type=None, attn_parallel_type=None, mlp_parallel_type=None, manager=None,
                         device=None, kaiming_init=True):
+    precision = model_config.get("precision", "bf16")
+    if precision not in ("fp32", "fp16", "bf16"):
+        raise ValueError(f"precision must be fp32, fp16 or bf16, got {precision!r}")
     model = get_model(model_archi_params, task_type, model_config.get("model_architecture"), kaiming_init, model_type,
                       embedding_parallel_type, attn_parallel_type, mlp_parallel_type, manager, device)
     ParamArena(model)
@@ -75,9 +78,6 @@ def get_model_for_train(model_archi_params, model_config, task_type="glorys", mo
     optimizer = get_optimizer(model, model_config, manager, use_dist_opt=state[3])
     gscaler = None
     on_cuda = device is not None and torch.device(device).type == "cuda"
-    precision = model_config.get("precision", "bf16")
-    if precision not in ("fp32", "fp16", "bf16"):
-        raise ValueError(f"precision must be fp32, fp16 or bf16, got {precision!r}")
     if on_cuda and precision == "fp32":
         raise ValueError("precision: fp32 is not available on CUDA: the sm_100a kernels compute in bf16 with fp32 "
                          "accumulation, masters and optimizer state. Use precision: bf16 (or fp16 for loss scaling); "

@@ -235,7 +235,8 @@ class _TpAttnHalfFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, anchor, pk, geo, num_heads, shifted, use_mask, scale, attn_comm, comm: TpFusedComm, rows_pad):
+    def forward(ctx, x, anchor, pk, geo, num_heads, shifted, use_mask, scale, attn_comm, comm: TpFusedComm, rows_pad,
+                ragged):
         from .blocks import LN_EPS
 
         ext = _ext.load()
@@ -243,7 +244,7 @@ class _TpAttnHalfFn(torch.autograd.Function):
         Cl = pk.qkv_w.shape[0] // 3
         tp = comm.world
         M = rows_pad * tp
-        ragged = rows_pad > rows
+        short = rows_pad > rows       # this rank holds fewer windows than the buffers have room for
         xn = _padded(comm.arena, rows, rows_pad, C)
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         rstd = torch.empty_like(mean)
@@ -261,19 +262,19 @@ class _TpAttnHalfFn(torch.autograd.Function):
             o = torch.empty(M, Cl, dtype=torch.bfloat16, device=x.device)
             qkv_ptrs, out_ptrs = [qkv.data_ptr()], [o.data_ptr()]
         if ragged:
-            o.zero_()                                   # padding windows are never visited by the attention kernel
+            o.zero_()       # some rank's chunk ends in padding windows, which the attention kernel never visits
         sh, sw = geo.shift(shifted)
         ext.window_attn_fwd(qkv_ptrs, out_ptrs, pk.bias_table, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
                             geo.shardN, geo.B, geo.nWh, geo.nWw, Cl, num_heads, geo.wh, geo.ww, sh, sw,
                             bool(use_mask and shifted), float(scale), geo.tp)
         if attn_comm is not None:
             o, qkv = attn_comm.attn_forward_done(o, qkv, shifted)
-        if ragged:
+        if short:
             y = comm.gemm_rs(o, pk.proj_w, bias=pk.proj_b)[:rows] + x
         else:
             y = comm.gemm_rs(o, pk.proj_w, bias=pk.proj_b, residual=x)
         ctx.save_for_backward(x, mean, rstd, xn_full if save_gathered else xn, qkv, o)
-        ctx.pk, ctx.geo, ctx.args = pk, geo, (num_heads, shifted, use_mask, scale, rows_pad, save_gathered)
+        ctx.pk, ctx.geo, ctx.args = pk, geo, (num_heads, shifted, use_mask, scale, rows_pad, save_gathered, ragged)
         ctx.attn_comm, ctx.comm = attn_comm, comm
         return y
 
@@ -284,11 +285,11 @@ class _TpAttnHalfFn(torch.autograd.Function):
         ext = _ext.load()
         x, mean, rstd, xn_saved, qkv, o = ctx.saved_tensors
         pk, geo, attn_comm, comm = ctx.pk, ctx.geo, ctx.attn_comm, ctx.comm
-        num_heads, shifted, use_mask, scale, rows_pad, save_gathered = ctx.args
+        num_heads, shifted, use_mask, scale, rows_pad, save_gathered, ragged = ctx.args
         rows, C = x.shape
         Cl = pk.qkv_w.shape[0] // 3
         M = rows_pad * comm.world
-        ragged = rows_pad > rows
+        short = rows_pad > rows
         dy = dy.contiguous()
         bias_grad_accumulate(dy, pk.proj_bg)
         dy_s = _padded(comm.arena, rows, rows_pad, C)
@@ -323,8 +324,8 @@ class _TpAttnHalfFn(torch.autograd.Function):
         bias_grad_accumulate(dqkv, pk.qkv_bg)
         # d(norm1 output) = reduce-scatter(dqkv @ qkv_w): GEMM -> reduce-scatter (the adjoint of the all-gather)
         dxn = comm.gemm_rs(dqkv, pk.qkv_w, b_mn=True)
-        dx = layernorm_bwd_cuda(dxn[:rows] if ragged else dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
-        return (dx,) + (None,) * 10
+        dx = layernorm_bwd_cuda(dxn[:rows] if short else dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
+        return (dx,) + (None,) * 11
 
 
 class _TpMlpHalfFn(torch.autograd.Function):
@@ -338,7 +339,7 @@ class _TpMlpHalfFn(torch.autograd.Function):
 
         ext = _ext.load()
         rows, C = x.shape
-        ragged = rows_pad > rows
+        short = rows_pad > rows
         xn = _padded(comm.arena, rows, rows_pad, C)
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         rstd = torch.empty_like(mean)
@@ -346,7 +347,7 @@ class _TpMlpHalfFn(torch.autograd.Function):
         save_gathered = comm.world <= 2
         res = comm.ag_gemm(xn, pk.fc1_w, bias=pk.fc1_b, gelu=True, save_pre=True, keep_gathered=save_gathered)
         (act, pre), xn_full = (res if save_gathered else (res, None))
-        if ragged:
+        if short:
             y = comm.gemm_rs(act, pk.fc2_w, bias=pk.bias2)[:rows] + x
         else:
             y = comm.gemm_rs(act, pk.fc2_w, bias=pk.bias2, residual=x)
@@ -362,7 +363,7 @@ class _TpMlpHalfFn(torch.autograd.Function):
         pk, comm = ctx.pk, ctx.comm
         rows_pad, save_gathered = ctx.args
         rows, C = x.shape
-        ragged = rows_pad > rows
+        short = rows_pad > rows
         dy = dy.contiguous()
         bias_grad_accumulate(dy, pk.bias2_g)
         dy_s = _padded(comm.arena, rows, rows_pad, C)
@@ -378,13 +379,15 @@ class _TpMlpHalfFn(torch.autograd.Function):
         wgrad_accumulate(dpre, xn_full, pk.fc1_wg)
         bias_grad_accumulate(dpre, pk.fc1_bg)
         dxn = comm.gemm_rs(dpre, pk.fc1_w, b_mn=True)
-        dx = layernorm_bwd_cuda(dxn[:rows] if ragged else dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
+        dx = layernorm_bwd_cuda(dxn[:rows] if short else dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
         return dx, None, None, None, None
 
 
-def tp_attention_half(x, mod, geo, attn_comm, comm: TpFusedComm, rows_pad: int):
+def tp_attention_half(x, mod, geo, attn_comm, comm: TpFusedComm, rows_pad: int, ragged: bool = False):
     """The attention half of a Swin block on tensor-parallel shards (``mod``: a ``SwinAttentionHalf`` of the
-    factorised build: q/k/v column-sharded, proj row-sharded, replicated ``proj_bias``)."""
+    factorised build: q/k/v column-sharded, proj row-sharded, replicated ``proj_bias``). ``ragged``: the window
+    count of the group is not a multiple of the tensor-parallel size, so some rank's chunk of the gathered buffers
+    ends in padding windows (a property of the group: every rank passes the same value)."""
     from .blocks import ParamPack
 
     comm.calls["attn"] += 1
@@ -399,7 +402,7 @@ def tp_attention_half(x, mod, geo, attn_comm, comm: TpFusedComm, rows_pad: int):
         bias_table=a.relative_position_bias_table.data if has_bias else None,
         bias_table_g=a.relative_position_bias_table.grad if has_bias else None)
     return _TpAttnHalfFn.apply(x, mod.norm1.weight, pk, geo, a.num_heads, mod.shifted, mod.use_attn_mask, a.scale,
-                               attn_comm, comm, rows_pad)
+                               attn_comm, comm, rows_pad, ragged)
 
 
 def tp_mlp_half(x, mod, comm: TpFusedComm, rows_pad: int):

@@ -149,7 +149,8 @@ class ParallelContext:
             # both collectives of the tensor-parallel attention half run inside the GEMMs over NVLink peer memory
             from ..ops.tp_fused import tp_attention_half
 
-            return tp_attention_half(x, mod, self.geometry(batch, tp_chunked=True), comm, tpc, batch * self.wpt * self.shardN)
+            return tp_attention_half(x, mod, self.geometry(batch, tp_chunked=True), comm, tpc,
+                                     batch * self.wpt * self.shardN, ragged=self.nW_group % self.tp != 0)
         return self._attention_half_factorized(x, mod, geo, batch)
 
     def mlp_half(self, x, mod):

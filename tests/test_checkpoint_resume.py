@@ -1,0 +1,105 @@
+"""Checkpoint save -> resume round trips through the entry points themselves (CPU / gloo ranks):
+
+* ``train.py`` on the serial model (``ckpt_layout: single``), on two window-parallel ranks with a replicated
+  optimizer (``wp_rank``) and with the sharded optimizer (``rank_local``): two epochs in one run must give the same
+  losses as one epoch, a save, and a second run that resumes from it;
+* ``finetune.py``: step checkpoints (``save_interval_steps``) and resuming from ``ckpt_step``.
+
+Reference behaviour: train_scripts/train.py:216-280, finetune.py:219-318.
+"""
+import os
+import re
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+import yaml
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run(script, cfg, tmp_path, name, nproc=1):
+    path = tmp_path / f"{name}.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", PYTHONPATH=ROOT)
+    exe = os.path.join(ROOT, "train_scripts", script)
+    if nproc == 1:
+        cmd = [sys.executable, exe, "--model_cfg", str(path)]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), exe, "--model_cfg", str(path)]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900, cwd=str(tmp_path))
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-4000:])
+
+
+def _losses(log_path):
+    """``[(global_step, loss)]`` of a rank-0 log file."""
+    return [(int(g), float(v)) for v, g in re.findall(r"loss ([0-9.eE+-]+) lr \S+ global_step (\d+)", open(log_path).read())]
+
+
+def _base(name, tmp_path, run):
+    cfg = yaml.safe_load(open(os.path.join(ROOT, "configs", "model", "correctness", name)))
+    cfg.update(train_path=str(tmp_path / run), max_train_steps_per_epoch=2, save_interval_epochs=1, fake_length=4,
+               precision="fp32", warmup_steps=1)
+    return cfg
+
+
+@pytest.mark.parametrize("name,nproc,opt,layout", [
+    ("tiny_seq_cpu.yaml", 1, 4, "single"),
+    ("tiny_para_wp2.yaml", 2, 4, "wp_rank"),
+    ("tiny_para_wp2.yaml", 2, 6, "rank_local"),
+])
+def test_pretrain_resume_matches_uninterrupted_run(tmp_path, name, nproc, opt, layout):
+    whole = dict(_base(name, tmp_path, "whole"), optimizer_config=opt, num_pre_train_epochs=2)
+    _run("train.py", whole, tmp_path, "whole", nproc)
+    first = dict(_base(name, tmp_path, "parts"), optimizer_config=opt, num_pre_train_epochs=1)
+    _run("train.py", first, tmp_path, "first", nproc)
+    # the cosine schedule depends on the planned number of epochs: keep it equal to the uninterrupted run's
+    first_log = os.path.join(first["train_path"], first["description"], "loss", "rank0.txt")
+    assert len(_losses(first_log)) == 2
+    d = os.path.join(first["train_path"], first["description"], "ckpt")
+    sub = {"single": "", "wp_rank": "wp_rank_0", "rank_local": "rank_0"}[layout]
+    blob = torch.load(os.path.join(d, sub, "epoch0.pth"), map_location="cpu", weights_only=False)
+    assert blob["ckpt_layout"] == layout and blob["epoch"] == 0 and blob["global_step"] == 2
+    assert set(blob) >= {"model_state_dict", "optimizer_state_dict", "loss", "epoch", "global_step", "ckpt_layout"}
+    if layout != "single":
+        other = {"wp_rank": "wp_rank_1", "rank_local": "rank_1"}[layout]
+        assert os.path.exists(os.path.join(d, other, "epoch0.pth")), "every owner rank writes its own file"
+    second = dict(first, num_pre_train_epochs=2, ckpt_start=True, ckpt_epoch=0)
+    _run("train.py", second, tmp_path, "second", nproc)
+    resumed = _losses(first_log)                      # the log is appended to
+    straight = _losses(os.path.join(whole["train_path"], whole["description"], "loss", "rank0.txt"))
+    assert [g for g, _ in resumed] == [1, 2, 3, 4] == [g for g, _ in straight]
+    # epoch 1 after the resume continues the optimizer state and the step counter: same losses as without the break
+    # (steps 3, 4; steps 1, 2 differ only through the learning-rate horizon of the shorter first run)
+    for (_, a), (_, b) in zip(resumed[2:], straight[2:]):
+        assert abs(a - b) <= 2e-4 * abs(b), (resumed, straight)
+
+
+def test_finetune_step_checkpoint_and_resume(tmp_path):
+    cfg = yaml.safe_load(open(os.path.join(ROOT, "configs", "finetuning", "tiny_finetune_seq.yaml")))
+    cfg.update(train_path=str(tmp_path / "ft"), max_train_steps_per_epoch=2, save_interval_steps=2, precision="fp32",
+               finetune_lead_time=2, num_finetune_epochs=1, fake_length=4)
+    cfg.pop("activation", None)
+    _run("finetune.py", cfg, tmp_path, "ft1")
+    base = os.path.join(cfg["train_path"], cfg["description"], "lead_2")
+    assert os.path.exists(os.path.join(base, "ckpt", "step2.pth")) and os.path.exists(os.path.join(base, "ckpt", "epoch0.pth"))
+    blob = torch.load(os.path.join(base, "ckpt", "step2.pth"), map_location="cpu", weights_only=False)
+    assert blob["global_step"] == 2 and blob["ckpt_layout"] == "single"
+    log = os.path.join(base, "loss", "rank0.txt")
+    n_before = len(open(log).read().strip().splitlines())
+    resumed = dict(cfg, ckpt_start=True, ckpt_step=2, ckpt_epoch=None, max_train_steps_per_epoch=1)
+    _run("finetune.py", resumed, tmp_path, "ft2")
+    lines = open(log).read().strip().splitlines()
+    assert len(lines) == n_before + 1
+    assert "global_step 3" in lines[-1], lines[-1]           # the optimizer's step counter came from the checkpoint

@@ -110,3 +110,89 @@ def test_bounded_peer_wait_reports_through_the_status_word():
     a = torch.ones(8, device="cuda")
     assert float((a * 2).sum().item()) == 16.0
     check_status("cuda")
+
+
+def test_step_guard_raises_on_a_lost_peer_and_releases_the_arenas():
+    """What the training loops call between steps: a peer that stopped beating turns into ``PeerLost`` on the host,
+    and every arena's stream waits are released first so that nothing of this process stays blocked on the dead peer."""
+    import torch.distributed as dist
+
+    from terra_b200.runtime.watchdog import PeerLost, RankMonitor, StepGuard
+
+    class FakeArena:
+        released = 0
+
+        def release_waits(self):
+            FakeArena.released += 1
+
+    store = dist.HashStore()
+    now = [0.0]
+    mons = [RankMonitor(store, r, 2, stale_after_s=5.0, clock=lambda: now[0]) for r in range(2)]
+    guard = StepGuard("cpu", mons[0], arenas=[FakeArena(), FakeArena()])
+    mons[1].beat(0)
+    guard.after_step(0)                       # both alive
+    now[0] = 10.0                             # rank 1 never beats again
+    with pytest.raises(PeerLost) as e:
+        guard.after_step(1)
+    assert e.value.ranks == [1] and FakeArena.released == 2
+
+
+def test_training_loop_raises_when_a_watchdog_released_a_wait():
+    from terra_b200.runtime.watchdog import StepGuard, StreamWaitExpired
+
+    class Tripped:
+        def check(self):
+            raise StreamWaitExpired("released")
+
+        def close(self):
+            pass
+
+    guard = StepGuard("cpu", None, watchdogs=[Tripped()])
+    with pytest.raises(StreamWaitExpired):
+        guard.after_step(0)
+
+
+@pytest.mark.gpu
+def test_stream_wait_on_a_silent_peer_is_released_by_the_host_watchdog():
+    """The copy-engine all-gather waits for a peer's signal with a stream memory operation, which has no time limit.
+    Here a side stream waits on a word that nobody ever writes (the host-made failure: the "peer" simply does not
+    publish); the watchdog releases the wait after its budget, the stream drains, the event is reported - and no kernel
+    ever spun on the GPU."""
+    import time
+
+    from terra_b200 import _ext
+    from terra_b200.runtime.watchdog import StreamWaitExpired, StreamWaitWatchdog
+
+    ext = _ext.load()
+    words = torch.zeros(16, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+
+    class Arena:
+        buf = words
+
+        def release_waits(self):
+            s = torch.cuda.Stream()
+            for i in range(16):
+                ext.stream_write_value(s.cuda_stream, words.data_ptr() + 4 * i, 0x7F7F7F7F)
+            s.synchronize()
+
+    wd = StreamWaitWatchdog(Arena(), lambda: side, budget_s=0.3, poll_s=0.02)
+    ext.stream_wait_value(side.cuda_stream, words.data_ptr() + 4 * 3, 1)      # waits for word 3 >= 1: never written
+    marker = torch.zeros(1, device="cuda")
+    with torch.cuda.stream(side):
+        marker += 1                                                             # queued behind the wait
+    wd.arm()
+    t0 = time.time()
+    while not side.query() and time.time() - t0 < 10.0:
+        time.sleep(0.02)
+    assert side.query(), "the side stream is still blocked"
+    assert 0.2 < time.time() - t0 < 5.0
+    torch.cuda.synchronize()
+    assert float(marker.item()) == 1.0
+    with pytest.raises(StreamWaitExpired):
+        wd.check()
+    wd.check()                                # reported once
+    wd.close()
+    # main stream and context are fine
+    assert float((torch.ones(4, device="cuda") * 3).sum().item()) == 12.0
