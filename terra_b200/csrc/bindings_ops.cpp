@@ -171,6 +171,27 @@ void window_attn(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t
   rc_check(tb::window_attn_fwd(a, cur_stream()), "window_attn_fwd");
 }
 
+// Forward on the tensor-core (tcgen05) kernel: any window size. `lse_ptrs`: optional per-slot fp32 [rows, heads] buffers
+// that receive the base-2 log-sum-exp of every row (empty list: not stored).
+void window_attn_tc(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t>& out_ptrs,
+                    const c10::optional<torch::Tensor>& bias_table, const std::vector<int64_t>& win_start, int64_t my_wg,
+                    int64_t sp, int64_t my_sp, int64_t shardN, int64_t B, int64_t nWh, int64_t nWw, int64_t C,
+                    int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale, int64_t tp,
+                    const c10::optional<torch::Tensor>& status, const std::vector<int64_t>& lse_ptrs) {
+  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale, tp);
+  need(qkv_ptrs.size() == static_cast<size_t>(a.n_wg * a.sp) && out_ptrs.size() == qkv_ptrs.size(),
+       "window_attn_tc: one buffer per peer slot");
+  need(lse_ptrs.empty() || lse_ptrs.size() == qkv_ptrs.size(), "window_attn_tc: one lse buffer per peer slot (or none)");
+  for (size_t i = 0; i < qkv_ptrs.size(); ++i) {
+    a.qkv[i] = reinterpret_cast<const void*>(qkv_ptrs[i]);
+    a.out[i] = reinterpret_cast<void*>(out_ptrs[i]);
+    a.lse[i] = lse_ptrs.empty() ? nullptr : reinterpret_cast<float*>(lse_ptrs[i]);
+  }
+  a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
+  tb::note_launch();
+  rc_check(tb::window_attn_tc_fwd(a, status.has_value() ? status->data_ptr() : nullptr, cur_stream()), "window_attn_tc_fwd");
+}
+
 void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t>& dout_ptrs,
                      const std::vector<int64_t>& dqkv_ptrs, const c10::optional<torch::Tensor>& bias_table,
                      const c10::optional<torch::Tensor>& dbias_table, const std::vector<int64_t>& win_start,
@@ -246,4 +267,5 @@ void bind_elementwise(pybind11::module_& m) {
 void bind_attention(pybind11::module_& m) {
   m.def("window_attn_fwd", &window_attn);
   m.def("window_attn_bwd", &window_attn_bwd);
+  m.def("window_attn_tc_fwd", &window_attn_tc);
 }

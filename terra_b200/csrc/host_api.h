@@ -121,6 +121,7 @@ struct WindowAttnArgs {
   void* dqkv[WA_MAX_PEERS];        // backward: gradient of qkv
   const float* bias_table;         // fp32 [(2wh-1)*(2ww-1), num_heads] or null
   float* dbias_table;              // backward, fp32 atomics (caller zeroes), or null
+  float* lse[WA_MAX_PEERS];        // optional, tensor-core forward: base-2 log-sum-exp per (row, head), fp32 [rows, num_heads]
   int win_start[9];                // flat window range of window-group rank p: [win_start[p], win_start[p+1])
   int n_wg, my_wg;                 // ranks along the window dimension, and mine
   int sp, my_sp, shardN;           // tokens of a window are split into sp shards of shardN tokens
@@ -135,5 +136,8 @@ struct WindowAttnArgs {
 };
 int window_attn_fwd(const WindowAttnArgs& a, cudaStream_t stream);
 int window_attn_bwd(const WindowAttnArgs& a, cudaStream_t stream);
+// window_attn_tc.cu: forward on tcgen05 / TMEM, any window size (flash-style K/V streaming above 64 tokens).
+// `status`: KernelStatus* (device) for the bounded waits, may be null.
+int window_attn_tc_fwd(const WindowAttnArgs& a, void* status, cudaStream_t stream);
 
 }  // namespace tb

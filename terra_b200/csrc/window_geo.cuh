@@ -1,0 +1,60 @@
+// Geometry of window attention over the window-major activation layout: where a token of a (possibly shifted)
+// window lives (which peer buffer, which row) and which mask region it belongs to. Shared by the attention kernels.
+#pragma once
+#include "common.cuh"
+#include "host_api.h"
+
+namespace tb {
+
+struct Geo {
+  int N, nrel;
+  int Hg, Wg;  // global token grid
+};
+
+// Home of token `tok` of shifted-frame window (ii, jj): which peer slot and which row of its buffer.
+struct Home {
+  int slot;
+  long long row;
+  int region;
+};
+
+__device__ __forceinline__ Home locate(const WindowAttnArgs& a, const Geo& g, int b, int ii, int jj, int tok) {
+  const int ti = tok / a.ww, tj = tok % a.ww;
+  const int hs = ii * a.wh + ti, ws = jj * a.ww + tj;  // position in the rolled frame
+  int gh = hs + a.sh, gw = ws + a.sw;
+  if (gh >= g.Hg) gh -= g.Hg;
+  if (gw >= g.Wg) gw -= g.Wg;
+  const int flat = (gh / a.wh) * a.nWw + (gw / a.ww);
+  const int st = (gh % a.wh) * a.ww + (gw % a.ww);
+  int wgr = 0;
+  while (wgr + 1 < a.n_wg && flat >= a.win_start[wgr + 1]) ++wgr;
+  const int nwp = a.win_start[wgr + 1] - a.win_start[wgr];
+  const int lw = flat - a.win_start[wgr];
+  const int s = st / a.shardN;
+  Home h;
+  h.slot = wgr * a.sp + s;
+  long long wrow;   // index of (batch, window) among the buffer's windows
+  if (a.tp <= 1) {
+    wrow = static_cast<long long>(b) * nwp + lw;
+  } else {
+    // rows gathered over tensor-parallel ranks: chunk t holds [B, wpt windows] of the group, chunks back to back
+    const int wpt = (nwp + a.tp - 1) / a.tp;
+    const int t = lw / wpt;
+    wrow = (static_cast<long long>(t) * a.B + b) * wpt + (lw - t * wpt);
+  }
+  h.row = wrow * a.shardN + (st - s * a.shardN);
+  int rh = 0, rw = 0;
+  if (a.sh > 0) rh = hs < g.Hg - a.wh ? 0 : (hs < g.Hg - a.sh ? 1 : 2);
+  if (a.sw > 0) rw = ws < g.Wg - a.ww ? 0 : (ws < g.Wg - a.sw ? 1 : 2);
+  h.region = rh * 3 + rw;
+  return h;
+}
+
+__device__ __forceinline__ int region_of(const WindowAttnArgs& a, const Geo& g, int hs, int ws) {
+  int rh = 0, rw = 0;
+  if (a.sh > 0) rh = hs < g.Hg - a.wh ? 0 : (hs < g.Hg - a.sh ? 1 : 2);
+  if (a.sw > 0) rw = ws < g.Wg - a.ww ? 0 : (ws < g.Wg - a.sw ? 1 : 2);
+  return rh * 3 + rw;
+}
+
+}  // namespace tb

@@ -100,7 +100,8 @@ def shifted_window_sources(geo: WindowGeometry, shifted: bool):
     return part(src_win), part(src_tok), part(reg)
 
 
-MAX_KERNEL_WINDOW_TOKENS = 128      # window_attn.cu keeps a whole window in shared memory
+MAX_MMA_WINDOW_TOKENS = 128         # window_attn.cu (mma.sync forward / backward) keeps a whole window in shared memory
+MAX_KERNEL_WINDOW_TOKENS = 128      # largest window whose backward runs on a kernel of this package
 
 
 def attention_core_reference(q, k, v, scale, bias, mask):
@@ -154,6 +155,29 @@ def window_attention_reference(qkv_all: torch.Tensor, geo: WindowGeometry, num_h
     return out.reshape(B, nW, N, C)
 
 
+def attn_forward_impl(N: int) -> str:
+    """Which forward kernel runs: ``tc`` (tcgen05 / TMEM, any window size) or ``mma`` (warp-level mma.sync, windows of
+    at most 128 tokens). ``TERRA_ATTN_FWD`` overrides; windows above 128 tokens always take ``tc``."""
+    import os
+
+    if N > MAX_MMA_WINDOW_TOKENS:
+        return "tc"
+    return os.environ.get("TERRA_ATTN_FWD", "tc")
+
+
+def launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, bias_f32, geo: "WindowGeometry", C, num_heads, sh, sw, use_mask, scale,
+                           device, lse_ptrs=()):
+    """One forward launch on the selected kernel (both take the same geometry)."""
+    args = (list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh,
+            geo.ww, sh, sw, bool(use_mask), float(scale), geo.tp)
+    if attn_forward_impl(geo.N) == "tc":
+        from .gemm import status_word
+
+        ext.window_attn_tc_fwd(qkv_ptrs, out_ptrs, bias_f32, *args, status_word(device), list(lse_ptrs))
+    else:
+        ext.window_attn_fwd(qkv_ptrs, out_ptrs, bias_f32, *args)
+
+
 class _WindowAttnFn(torch.autograd.Function):
     """CUDA path. Without ``comm`` this rank owns every window and token. With a fused ``comm`` the q/k/v rows are
     staged in symmetric memory so that the kernels of the peer ranks can read them (and write outputs / gradients
@@ -173,9 +197,8 @@ class _WindowAttnFn(torch.autograd.Function):
             staged.copy_(qkv)
             qkv = staged
             out, qkv_ptrs, out_ptrs = comm.attn_forward_buffers(qkv, C, shifted)
-        ext.window_attn_fwd(qkv_ptrs, out_ptrs, bias_f32, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
-                            geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh, geo.ww, sh, sw,
-                            bool(use_mask and shifted), float(scale), geo.tp)
+        launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, bias_f32, geo, C, num_heads, sh, sw, use_mask and shifted, scale,
+                               qkv.device)
         if comm is not None:
             out, qkv = comm.attn_forward_done(out, qkv, shifted)
         ctx.save_for_backward(qkv, bias_f32 if bias_f32 is not None else torch.empty(0, device=qkv.device))

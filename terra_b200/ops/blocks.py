@@ -18,7 +18,7 @@ import torch
 import torch.nn.functional as TF
 
 from .. import _ext
-from .attention import MAX_KERNEL_WINDOW_TOKENS, WindowGeometry, window_attention
+from .attention import MAX_KERNEL_WINDOW_TOKENS, WindowGeometry, launch_window_attn_fwd, window_attention
 from .gemm import gemm, status_word
 from ..utils.nvtx import nvtx_range
 
@@ -89,9 +89,8 @@ class _AttnHalfFn(torch.autograd.Function):
             o = torch.empty(x.shape[0], C, dtype=torch.bfloat16, device=x.device)
             qkv_ptrs, out_ptrs = [qkv.data_ptr()], [o.data_ptr()]
         sh, sw = geo.shift(shifted)
-        ext.window_attn_fwd(qkv_ptrs, out_ptrs, pk.bias_table, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
-                            geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh, geo.ww, sh, sw,
-                            bool(use_mask and shifted), float(scale), geo.tp)
+        launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, pk.bias_table, geo, C, num_heads, sh, sw, use_mask and shifted,
+                               scale, x.device)
         if comm is not None:
             o, qkv = comm.attn_forward_done(o, qkv, shifted)
         y = gemm(o, pk.proj_w, bias=pk.proj_b, residual=x)

@@ -120,7 +120,10 @@ def case_attn(a):
         flops = 2.0 * rows * geo.N * C * 5
         nbytes = rows * C * 2 * (3 + 1 + 3)
     else:
-        fn = lambda: ext.window_attn_fwd([qkv.data_ptr()], [out.data_ptr()], table, *args)
+        if a.impl == "tc":
+            fn = lambda: ext.window_attn_tc_fwd([qkv.data_ptr()], [out.data_ptr()], table, *args, status_word("cuda"), [])
+        else:
+            fn = lambda: ext.window_attn_fwd([qkv.data_ptr()], [out.data_ptr()], table, *args)
         flops = 2.0 * rows * geo.N * C * 2
         nbytes = rows * C * 2 * (3 + 1)
     return fn, flops, nbytes
@@ -215,6 +218,7 @@ def main(argv=None):
     ap.add_argument("--nwh", type=int, default=32)
     ap.add_argument("--nww", type=int, default=68)
     ap.add_argument("--shifted", action="store_true")
+    ap.add_argument("--impl", default="tc", choices=["tc", "mma"], help="attention forward kernel: tcgen05 or mma.sync")
     ap.add_argument("--bwd", action="store_true")
     ap.add_argument("--h", type=int, default=256)
     ap.add_argument("--w", type=int, default=544)

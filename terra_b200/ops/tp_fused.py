@@ -264,9 +264,10 @@ class _TpAttnHalfFn(torch.autograd.Function):
         if ragged:
             o.zero_()       # some rank's chunk ends in padding windows, which the attention kernel never visits
         sh, sw = geo.shift(shifted)
-        ext.window_attn_fwd(qkv_ptrs, out_ptrs, pk.bias_table, list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp,
-                            geo.shardN, geo.B, geo.nWh, geo.nWw, Cl, num_heads, geo.wh, geo.ww, sh, sw,
-                            bool(use_mask and shifted), float(scale), geo.tp)
+        from .attention import launch_window_attn_fwd
+
+        launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, pk.bias_table, geo, Cl, num_heads, sh, sw, use_mask and shifted,
+                               scale, x.device)
         if attn_comm is not None:
             o, qkv = attn_comm.attn_forward_done(o, qkv, shifted)
         if short:

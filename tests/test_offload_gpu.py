@@ -50,9 +50,9 @@ def test_boundary_offload_matches_recompute_with_lower_peak_memory():
     recompute = _run({"mode": "torch_recompute", "checkpoint_layers": layers})
     offload = _run({"mode": "cpu_boundary_offload_recompute", "checkpoint_layers": layers,
                     "offload": {"min_numel": 4096, "mode": "async_d2h_h2d"}})
-    # same function, same weights, same kernels in the same order: recomputation changes nothing numerically
-    assert abs(recompute[0] - plain[0]) <= 1e-6 * abs(plain[0])
-    assert abs(offload[0] - recompute[0]) <= 1e-6 * abs(recompute[0])
+    # same function, same weights, same kernels in the same order; only the fp32 atomics of the loss reduction reorder
+    assert abs(recompute[0] - plain[0]) <= 1e-5 * abs(plain[0])
+    assert abs(offload[0] - recompute[0]) <= 1e-5 * abs(recompute[0])
     denom = recompute[1].norm().item() + 1e-12
     assert (offload[1] - recompute[1]).norm().item() <= 1e-3 * denom      # split-K atomics reorder fp32 sums slightly
     assert (plain[1] - recompute[1]).norm().item() <= 1e-3 * denom
