@@ -192,6 +192,12 @@ void window_attn_tc(const std::vector<int64_t>& qkv_ptrs, const std::vector<int6
   rc_check(tb::window_attn_tc_fwd(a, status.has_value() ? status->data_ptr() : nullptr, cur_stream()), "window_attn_tc_fwd");
 }
 
+std::vector<int64_t> window_attn_tc_stalls(bool reset) {
+  unsigned long long c[16];
+  rc_check(tb::window_attn_tc_stalls(c, reset ? 1 : 0), "window_attn_tc_stalls");
+  return std::vector<int64_t>(c, c + 16);
+}
+
 void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t>& dout_ptrs,
                      const std::vector<int64_t>& dqkv_ptrs, const c10::optional<torch::Tensor>& bias_table,
                      const c10::optional<torch::Tensor>& dbias_table, const std::vector<int64_t>& win_start,
@@ -211,6 +217,27 @@ void window_attn_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int
   a.dbias_table = dbias_table.has_value() ? dbias_table->data_ptr<float>() : nullptr;
   tb::note_launch();
   rc_check(tb::window_attn_bwd(a, cur_stream()), "window_attn_bwd");
+}
+
+void window_attn_tc_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<int64_t>& dout_ptrs,
+                        const std::vector<int64_t>& dqkv_ptrs, const c10::optional<torch::Tensor>& bias_table,
+                        const c10::optional<torch::Tensor>& dbias_table, const std::vector<int64_t>& win_start,
+                        int64_t my_wg, int64_t sp, int64_t my_sp, int64_t shardN, int64_t B, int64_t nWh, int64_t nWw,
+                        int64_t C, int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask,
+                        double scale, int64_t tp, const c10::optional<torch::Tensor>& status) {
+  tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale, tp);
+  need(qkv_ptrs.size() == static_cast<size_t>(a.n_wg * a.sp) && dout_ptrs.size() == qkv_ptrs.size() &&
+           dqkv_ptrs.size() == qkv_ptrs.size(),
+       "window_attn_tc_bwd: one buffer per peer slot");
+  for (size_t i = 0; i < qkv_ptrs.size(); ++i) {
+    a.qkv[i] = reinterpret_cast<const void*>(qkv_ptrs[i]);
+    a.dout[i] = reinterpret_cast<const void*>(dout_ptrs[i]);
+    a.dqkv[i] = reinterpret_cast<void*>(dqkv_ptrs[i]);
+  }
+  a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
+  a.dbias_table = dbias_table.has_value() ? dbias_table->data_ptr<float>() : nullptr;
+  tb::note_launch();
+  rc_check(tb::window_attn_tc_bwd(a, status.has_value() ? status->data_ptr() : nullptr, cur_stream()), "window_attn_tc_bwd");
 }
 
 void conv_s2_col2im(const torch::Tensor& dcol, torch::Tensor& out, int64_t W, int64_t r0) {
@@ -268,4 +295,6 @@ void bind_attention(pybind11::module_& m) {
   m.def("window_attn_fwd", &window_attn);
   m.def("window_attn_bwd", &window_attn_bwd);
   m.def("window_attn_tc_fwd", &window_attn_tc);
+  m.def("window_attn_tc_stalls", &window_attn_tc_stalls);
+  m.def("window_attn_tc_bwd", &window_attn_tc_bwd);
 }

@@ -139,5 +139,11 @@ int window_attn_bwd(const WindowAttnArgs& a, cudaStream_t stream);
 // window_attn_tc.cu: forward on tcgen05 / TMEM, any window size (flash-style K/V streaming above 64 tokens).
 // `status`: KernelStatus* (device) for the bounded waits, may be null.
 int window_attn_tc_fwd(const WindowAttnArgs& a, void* status, cudaStream_t stream);
+// Cycle counters of the tensor-core attention kernel's roles since the last reset: [0] producer span, [1] of it waiting
+// for a free buffer, [2] MMA thread span, [3] waiting for operands, [4] waiting for probabilities, [5] softmax thread
+// span, [6] waiting for scores, [7] waiting for outputs. Synchronises the device.
+int window_attn_tc_stalls(unsigned long long* out16, int reset);   // [8..13]: softmax thread segments, see window_attn_tc.cu
+// Backward on tcgen05 for windows of at most 64 tokens and head dims 16 / 32 / 64.
+int window_attn_tc_bwd(const WindowAttnArgs& a, void* status, cudaStream_t stream);
 
 }  // namespace tb

@@ -50,6 +50,44 @@ __device__ __forceinline__ Home locate(const WindowAttnArgs& a, const Geo& g, in
   return h;
 }
 
+// The same as `locate` for a token given by its coordinates (ti, tj) inside the window, without the divisions by the
+// window size: a shifted token lies in its own window or the next one (per axis), wrapping at the grid end.
+__device__ __forceinline__ Home locate_ij(const WindowAttnArgs& a, const Geo& g, int b, int ii, int jj, int ti, int tj) {
+  int ri = ti + a.sh, wi = ii;
+  if (ri >= a.wh) {
+    ri -= a.wh;
+    if (++wi == a.nWh) wi = 0;
+  }
+  int rj = tj + a.sw, wj = jj;
+  if (rj >= a.ww) {
+    rj -= a.ww;
+    if (++wj == a.nWw) wj = 0;
+  }
+  const int flat = wi * a.nWw + wj;
+  const int st = ri * a.ww + rj;
+  int wgr = 0;
+  while (wgr + 1 < a.n_wg && flat >= a.win_start[wgr + 1]) ++wgr;
+  const int nwp = a.win_start[wgr + 1] - a.win_start[wgr];
+  const int lw = flat - a.win_start[wgr];
+  const int s = a.sp > 1 ? st / a.shardN : 0;
+  Home h;
+  h.slot = wgr * a.sp + s;
+  long long wrow;
+  if (a.tp <= 1) {
+    wrow = static_cast<long long>(b) * nwp + lw;
+  } else {
+    const int wpt = (nwp + a.tp - 1) / a.tp;
+    const int t = lw / wpt;
+    wrow = (static_cast<long long>(t) * a.B + b) * wpt + (lw - t * wpt);
+  }
+  h.row = wrow * a.shardN + (st - s * a.shardN);
+  int rh = 0, rw = 0;
+  if (a.sh > 0 && ii == a.nWh - 1) rh = ti < a.wh - a.sh ? 1 : 2;
+  if (a.sw > 0 && jj == a.nWw - 1) rw = tj < a.ww - a.sw ? 1 : 2;
+  h.region = rh * 3 + rw;
+  return h;
+}
+
 __device__ __forceinline__ int region_of(const WindowAttnArgs& a, const Geo& g, int hs, int ws) {
   int rh = 0, rw = 0;
   if (a.sh > 0) rh = hs < g.Hg - a.wh ? 0 : (hs < g.Hg - a.sh ? 1 : 2);

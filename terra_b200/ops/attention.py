@@ -157,12 +157,26 @@ def window_attention_reference(qkv_all: torch.Tensor, geo: WindowGeometry, num_h
 
 def attn_forward_impl(N: int) -> str:
     """Which forward kernel runs: ``tc`` (tcgen05 / TMEM, any window size) or ``mma`` (warp-level mma.sync, windows of
-    at most 128 tokens). ``TERRA_ATTN_FWD`` overrides; windows above 128 tokens always take ``tc``."""
+    at most 128 tokens, several CTAs per SM). Windows above 128 tokens always take ``tc``; below, ``mma`` is the default
+    because it measures faster there (0.31 against 0.48 ms on the 2176-window stage with head dim 64): one softmax warp
+    per scheduler leaves the tensor-core kernel latency bound on 64-token windows. ``TERRA_ATTN_FWD=tc`` selects it
+    anyway."""
     import os
 
     if N > MAX_MMA_WINDOW_TOKENS:
         return "tc"
-    return os.environ.get("TERRA_ATTN_FWD", "tc")
+    return os.environ.get("TERRA_ATTN_FWD", "mma")
+
+
+def attn_backward_impl(N: int, head_dim: int) -> str:
+    """``tc``: the tcgen05 backward (two small windows per tile: N <= 64, head dim 16 / 32 / 64), ``mma``: the mma.sync
+    one (N <= 128). Default ``mma`` (faster on small windows, see ``attn_forward_impl``); ``TERRA_ATTN_BWD=tc``."""
+    import os
+
+    want = os.environ.get("TERRA_ATTN_BWD", "mma")
+    if want == "tc" and N <= 64 and head_dim in (16, 32, 64):
+        return "tc"
+    return "mma"
 
 
 def launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, bias_f32, geo: "WindowGeometry", C, num_heads, sh, sw, use_mask, scale,
@@ -176,6 +190,19 @@ def launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, bias_f32, geo: "WindowGeomet
         ext.window_attn_tc_fwd(qkv_ptrs, out_ptrs, bias_f32, *args, status_word(device), list(lse_ptrs))
     else:
         ext.window_attn_fwd(qkv_ptrs, out_ptrs, bias_f32, *args)
+
+
+def launch_window_attn_bwd(ext, qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, geo: "WindowGeometry", C, num_heads, sh, sw,
+                           use_mask, scale, device):
+    """One backward launch on the selected kernel."""
+    args = (list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh,
+            geo.ww, sh, sw, bool(use_mask), float(scale), geo.tp)
+    if attn_backward_impl(geo.N, C // num_heads) == "tc":
+        from .gemm import status_word
+
+        ext.window_attn_tc_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, *args, status_word(device))
+    else:
+        ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, *args)
 
 
 class _WindowAttnFn(torch.autograd.Function):
@@ -222,10 +249,8 @@ class _WindowAttnFn(torch.autograd.Function):
             staged = comm.alloc_dout(dout.shape[0], C)
             staged.copy_(dout)
             dqkv, qkv_ptrs, dout_ptrs, dqkv_ptrs = comm.attn_backward_buffers(qkv, staged, ctx.shifted)
-        ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32 if ctx.has_bias else None, dbias,
-                            list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw,
-                            C, ctx.num_heads, geo.wh, geo.ww, sh, sw, bool(ctx.use_mask and ctx.shifted),
-                            float(ctx.scale), geo.tp)
+        launch_window_attn_bwd(ext, qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32 if ctx.has_bias else None, dbias, geo, C,
+                               ctx.num_heads, sh, sw, ctx.use_mask and ctx.shifted, ctx.scale, qkv.device)
         if comm is not None:
             dqkv = comm.attn_backward_done(dqkv, ctx.shifted)
         return dqkv, dbias, None, None, None, None, None, None

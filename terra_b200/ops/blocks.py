@@ -18,7 +18,8 @@ import torch
 import torch.nn.functional as TF
 
 from .. import _ext
-from .attention import MAX_KERNEL_WINDOW_TOKENS, WindowGeometry, launch_window_attn_fwd, window_attention
+from .attention import (MAX_KERNEL_WINDOW_TOKENS, WindowGeometry, launch_window_attn_bwd, launch_window_attn_fwd,
+                        window_attention)
 from .gemm import gemm, status_word
 from ..utils.nvtx import nvtx_range
 
@@ -117,9 +118,8 @@ class _AttnHalfFn(torch.autograd.Function):
             dqkv = torch.empty_like(qkv)
             qkv_ptrs, dout_ptrs, dqkv_ptrs = [qkv.data_ptr()], [do.data_ptr()], [dqkv.data_ptr()]
         sh, sw = geo.shift(shifted)
-        ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, pk.bias_table, pk.bias_table_g, list(geo.win_start),
-                            geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh,
-                            geo.ww, sh, sw, bool(use_mask and shifted), float(scale), geo.tp)
+        launch_window_attn_bwd(ext, qkv_ptrs, dout_ptrs, dqkv_ptrs, pk.bias_table, pk.bias_table_g, geo, C, num_heads, sh, sw,
+                               use_mask and shifted, scale, x.device)
         if comm is not None:
             dqkv = comm.attn_backward_done(dqkv, shifted)
         wgrad_accumulate(dqkv, xn, pk.qkv_wg)

@@ -116,7 +116,11 @@ def case_attn(a):
     args = (list(geo.win_start), 0, 1, 0, geo.N, 1, geo.nWh, geo.nWw, C, heads, a.ws, a.ws, sh, sh, bool(a.shifted),
             (C // heads) ** -0.5, 1)
     if a.bwd:
-        fn = lambda: ext.window_attn_bwd([qkv.data_ptr()], [out.data_ptr()], [dqkv.data_ptr()], table, dtable, *args)
+        if a.impl == "tc":
+            fn = lambda: ext.window_attn_tc_bwd([qkv.data_ptr()], [out.data_ptr()], [dqkv.data_ptr()], table, dtable, *args,
+                                                status_word("cuda"))
+        else:
+            fn = lambda: ext.window_attn_bwd([qkv.data_ptr()], [out.data_ptr()], [dqkv.data_ptr()], table, dtable, *args)
         flops = 2.0 * rows * geo.N * C * 5
         nbytes = rows * C * 2 * (3 + 1 + 3)
     else:
@@ -256,6 +260,16 @@ def main(argv=None):
            "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6,
            "frac_of_" + pk["source"] + "_bf16": flops / ms / 1e9 / pk["bf16_tflops"],
            "frac_of_" + pk["source"] + "_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"]}
+    if a.case == "attn" and a.impl == "tc" and not a.bwd:
+        torch.cuda.synchronize()
+        ext.window_attn_tc_stalls(True)
+        fn()
+        c = ext.window_attn_tc_stalls(True)
+        stalls = {"producer_wait_buffer": c[1] / max(1, c[0]), "mma_wait_operands": c[3] / max(1, c[2]),
+                  "mma_wait_probabilities": c[4] / max(1, c[2]), "softmax_wait_scores": c[6] / max(1, c[5]),
+                  "softmax_wait_outputs": c[7] / max(1, c[5]),
+                  "softmax_segments": {k: c[8 + i] / max(1, c[5]) for i, k in enumerate(
+                      ("prologue", "score_load", "math", "store_signal", "fold_output", "row_store"))}}
     if stalls is not None:
         out["wait_fractions"] = stalls
     print(json.dumps(out))

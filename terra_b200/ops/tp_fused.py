@@ -310,9 +310,10 @@ class _TpAttnHalfFn(torch.autograd.Function):
         if ragged:
             dqkv.zero_()
         sh, sw = geo.shift(shifted)
-        ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, pk.bias_table, pk.bias_table_g, list(geo.win_start),
-                            geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw, Cl, num_heads, geo.wh,
-                            geo.ww, sh, sw, bool(use_mask and shifted), float(scale), geo.tp)
+        from .attention import launch_window_attn_bwd
+
+        launch_window_attn_bwd(ext, qkv_ptrs, dout_ptrs, dqkv_ptrs, pk.bias_table, pk.bias_table_g, geo, Cl, num_heads, sh,
+                               sw, use_mask and shifted, scale, x.device)
         if attn_comm is not None:
             dqkv = attn_comm.attn_backward_done(dqkv, shifted)
         if save_gathered:
