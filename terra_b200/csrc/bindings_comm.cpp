@@ -92,6 +92,57 @@ void gather_shards_async(int64_t stream, int64_t dst, const std::vector<int64_t>
   TORCH_CHECK(rc == 0, "gather_shards_async failed with code ", rc);
 }
 
+// All addresses are raw device addresses (0: absent).
+void halo_push(int64_t send_prev, int64_t send_next, int64_t dst_prev, int64_t dst_next, int64_t nbytes, int64_t flag_at_prev,
+               int64_t flag_at_next, int64_t my_flag_from_prev, int64_t my_flag_from_next, int64_t epoch, int64_t ticket,
+               const c10::optional<torch::Tensor>& status, int64_t budget_ns) {
+  TORCH_CHECK(nbytes % 16 == 0, "halo_push: rows must be a multiple of 16 bytes");
+  tb::HaloPushArgs a{};
+  a.send_prev = reinterpret_cast<const uint4*>(send_prev);
+  a.send_next = reinterpret_cast<const uint4*>(send_next);
+  a.dst_prev = reinterpret_cast<uint4*>(dst_prev);
+  a.dst_next = reinterpret_cast<uint4*>(dst_next);
+  a.nvec = nbytes / 16;
+  a.flag_at_prev = reinterpret_cast<uint32_t*>(flag_at_prev);
+  a.flag_at_next = reinterpret_cast<uint32_t*>(flag_at_next);
+  a.my_flag_from_prev = reinterpret_cast<const uint32_t*>(my_flag_from_prev);
+  a.my_flag_from_next = reinterpret_cast<const uint32_t*>(my_flag_from_next);
+  a.epoch = static_cast<uint32_t>(epoch);
+  a.ticket = reinterpret_cast<unsigned int*>(ticket);
+  a.status = status.has_value() ? reinterpret_cast<tb::KernelStatus*>(status->data_ptr()) : nullptr;
+  a.budget_ns = static_cast<unsigned long long>(budget_ns);
+  tb::note_launch();
+  TORCH_CHECK(tb::halo_push(a, cur_stream()) == 0, "halo_push launch failed");
+}
+
+void peer_allreduce_small(const std::vector<int64_t>& slot_ptrs, const std::vector<int64_t>& flag_ptrs, const torch::Tensor& in,
+                          torch::Tensor& out, int64_t my_rank, int64_t capacity, int64_t epoch,
+                          const c10::optional<torch::Tensor>& status, int64_t budget_ns) {
+  TORCH_CHECK(slot_ptrs.size() == flag_ptrs.size() && !slot_ptrs.empty() && slot_ptrs.size() <= tb::COMM_MAX_PEERS,
+              "peer_allreduce_small: one staging and one flag array per GPU");
+  TORCH_CHECK(in.is_cuda() && in.is_contiguous() && out.is_contiguous() && in.scalar_type() == torch::kFloat32 &&
+                  out.scalar_type() == torch::kFloat32 && in.numel() == out.numel() && in.numel() <= capacity,
+              "peer_allreduce_small: fp32 contiguous vectors of at most `capacity` elements");
+  const c10::cuda::CUDAGuard guard(in.device());
+  tb::SmallReduceArgs a{};
+  a.num_peers = static_cast<int>(slot_ptrs.size());
+  for (int i = 0; i < a.num_peers; ++i) {
+    a.slots[i] = reinterpret_cast<float*>(slot_ptrs[i]);
+    a.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  a.in = in.data_ptr<float>();
+  a.out = out.data_ptr<float>();
+  a.my_rank = static_cast<int>(my_rank);
+  a.n = static_cast<int>(in.numel());
+  a.capacity = static_cast<int>(capacity);
+  a.parity = static_cast<int>(epoch & 1);
+  a.epoch = static_cast<uint32_t>(epoch);
+  a.status = status.has_value() ? reinterpret_cast<tb::KernelStatus*>(status->data_ptr()) : nullptr;
+  a.budget_ns = static_cast<unsigned long long>(budget_ns);
+  tb::note_launch();
+  TORCH_CHECK(tb::peer_allreduce_small(a, cur_stream()) == 0, "peer_allreduce_small launch failed");
+}
+
 // Stream memory operations on a stream given as an integer (torch.cuda.Stream.cuda_stream): the stream waits until the
 // 32-bit word at `addr` is >= value / writes value to it, without occupying an SM.
 void stream_wait_value(int64_t stream, int64_t addr, int64_t value) {
@@ -108,6 +159,8 @@ void stream_write_value(int64_t stream, int64_t addr, int64_t value) {
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
+  m.def("halo_push", &halo_push);
+  m.def("peer_allreduce_small", &peer_allreduce_small);
   m.def("stream_wait_value", &stream_wait_value);
   m.def("stream_write_value", &stream_write_value);
   m.def("dist_adamw_step", &dist_adamw_step);

@@ -75,15 +75,43 @@ void groupnorm_silu_apply(const torch::Tensor& x, const torch::Tensor& stats, co
            "groupnorm_silu_apply");
 }
 
+// dgamma / dbeta (optional, fp32 [C]): accumulated in place (the gradient views of the affine parameters)
 void groupnorm_silu_bwd_reduce(const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& stats,
-                               const torch::Tensor& g, const torch::Tensor& b, torch::Tensor& red, int64_t groups) {
+                               const torch::Tensor& g, const torch::Tensor& b, torch::Tensor& red, int64_t groups,
+                               const c10::optional<torch::Tensor>& dgamma, const c10::optional<torch::Tensor>& dbeta) {
   need(x.is_contiguous() && dy.is_contiguous() && x.dim() == 3, "groupnorm_silu_bwd_reduce: [B,HW,C]");
+  need(!dgamma.has_value() || (dgamma->scalar_type() == torch::kFloat32 && dgamma->is_contiguous()), "dgamma: fp32 contiguous");
+  need(!dbeta.has_value() || (dbeta->scalar_type() == torch::kFloat32 && dbeta->is_contiguous()), "dbeta: fp32 contiguous");
   const c10::cuda::CUDAGuard guard(x.device());
   tb::note_launch();
   rc_check(tb::groupnorm_silu_bwd_reduce(dy.data_ptr(), x.data_ptr(), stats.data_ptr<float>(), g.data_ptr(), b.data_ptr(),
-                                         red.data_ptr<float>(), nullptr, nullptr, x.size(0), x.size(1), x.size(2), groups,
-                                         cur_stream()),
+                                         red.data_ptr<float>(), dgamma.has_value() ? dgamma->data_ptr<float>() : nullptr,
+                                         dbeta.has_value() ? dbeta->data_ptr<float>() : nullptr, x.size(0), x.size(1),
+                                         x.size(2), groups, cur_stream()),
            "groupnorm_silu_bwd_reduce");
+}
+
+void groupnorm_finalize(torch::Tensor& sums, torch::Tensor& stats, double inv_count, double eps, bool clear) {
+  need(sums.is_cuda() && sums.is_contiguous() && stats.is_contiguous() && sums.scalar_type() == torch::kFloat32 &&
+           stats.scalar_type() == torch::kFloat32 && sums.numel() == stats.numel() && sums.numel() % 2 == 0,
+       "groupnorm_finalize: fp32 [cells, 2] sums and stats");
+  const c10::cuda::CUDAGuard guard(sums.device());
+  tb::note_launch();
+  rc_check(tb::groupnorm_finalize(sums.data_ptr<float>(), stats.data_ptr<float>(), static_cast<int>(sums.numel() / 2),
+                                  static_cast<float>(inv_count), static_cast<float>(eps), clear ? 1 : 0, cur_stream()),
+           "groupnorm_finalize");
+}
+
+void strided_add(torch::Tensor& src, torch::Tensor& dst, int64_t sa, int64_t sb, int64_t sc, bool clear) {
+  need(src.is_cuda() && src.is_contiguous() && src.dim() == 3 && src.scalar_type() == torch::kFloat32 &&
+           dst.scalar_type() == torch::kFloat32 && dst.is_contiguous() && dst.numel() == src.numel(),
+       "strided_add: fp32 src [a, b, c] contiguous, dst contiguous with as many elements");
+  const c10::cuda::CUDAGuard guard(src.device());
+  tb::note_launch();
+  rc_check(tb::strided_add_f32(src.data_ptr<float>(), dst.data_ptr<float>(), static_cast<int>(src.size(0)),
+                               static_cast<int>(src.size(1)), static_cast<int>(src.size(2)), sa, sb, sc, clear ? 1 : 0,
+                               cur_stream()),
+           "strided_add");
 }
 
 void groupnorm_silu_bwd_apply(const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& stats,
@@ -126,6 +154,19 @@ void adamw_step(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const
                           static_cast<float>(wd), static_cast<float>(bc1), static_cast<float>(std::sqrt(bc2)),
                           static_cast<float>(grad_scale), cur_stream()),
            "adamw_step");
+}
+
+void attn_rowdot(const torch::Tensor& o, const torch::Tensor& dout, torch::Tensor& drow, int64_t heads) {
+  need(o.is_cuda() && o.is_contiguous() && dout.is_contiguous() && o.scalar_type() == torch::kBFloat16 &&
+           dout.scalar_type() == torch::kBFloat16 && o.dim() == 2 && o.sizes() == dout.sizes(),
+       "attn_rowdot: o, dout bf16 [rows, C] contiguous");
+  need(drow.scalar_type() == torch::kFloat32 && drow.is_contiguous() && drow.numel() == o.size(0) * heads,
+       "attn_rowdot: drow fp32 [rows, heads]");
+  const c10::cuda::CUDAGuard guard(o.device());
+  tb::note_launch();
+  rc_check(tb::attn_rowdot(o.data_ptr(), dout.data_ptr(), drow.data_ptr<float>(), o.size(0), static_cast<int>(o.size(1)),
+                           static_cast<int>(heads), cur_stream()),
+           "attn_rowdot");
 }
 
 void grad_inspect(const torch::Tensor& grad, torch::Tensor& out2) {
@@ -224,15 +265,20 @@ void window_attn_tc_bwd(const std::vector<int64_t>& qkv_ptrs, const std::vector<
                         const c10::optional<torch::Tensor>& dbias_table, const std::vector<int64_t>& win_start,
                         int64_t my_wg, int64_t sp, int64_t my_sp, int64_t shardN, int64_t B, int64_t nWh, int64_t nWw,
                         int64_t C, int64_t heads, int64_t wh, int64_t ww, int64_t sh, int64_t sw, bool use_mask,
-                        double scale, int64_t tp, const c10::optional<torch::Tensor>& status) {
+                        double scale, int64_t tp, const c10::optional<torch::Tensor>& status,
+                        const std::vector<int64_t>& lse_ptrs, const std::vector<int64_t>& drow_ptrs) {
   tb::WindowAttnArgs a = make_wa(win_start, my_wg, sp, my_sp, shardN, B, nWh, nWw, C, heads, wh, ww, sh, sw, use_mask, scale, tp);
   need(qkv_ptrs.size() == static_cast<size_t>(a.n_wg * a.sp) && dout_ptrs.size() == qkv_ptrs.size() &&
            dqkv_ptrs.size() == qkv_ptrs.size(),
        "window_attn_tc_bwd: one buffer per peer slot");
+  need((lse_ptrs.empty() || lse_ptrs.size() == qkv_ptrs.size()) && drow_ptrs.size() == lse_ptrs.size(),
+       "window_attn_tc_bwd: lse / drow buffers per peer slot (or none)");
   for (size_t i = 0; i < qkv_ptrs.size(); ++i) {
     a.qkv[i] = reinterpret_cast<const void*>(qkv_ptrs[i]);
     a.dout[i] = reinterpret_cast<const void*>(dout_ptrs[i]);
     a.dqkv[i] = reinterpret_cast<void*>(dqkv_ptrs[i]);
+    a.lse[i] = lse_ptrs.empty() ? nullptr : reinterpret_cast<float*>(lse_ptrs[i]);
+    a.drow[i] = drow_ptrs.empty() ? nullptr : reinterpret_cast<const float*>(drow_ptrs[i]);
   }
   a.bias_table = bias_table.has_value() ? bias_table->data_ptr<float>() : nullptr;
   a.dbias_table = dbias_table.has_value() ? dbias_table->data_ptr<float>() : nullptr;
@@ -281,11 +327,16 @@ void bind_elementwise(pybind11::module_& m) {
   m.def("colsum", &colsum);
   m.def("groupnorm_stats", &groupnorm_stats);
   m.def("groupnorm_silu_apply", &groupnorm_silu_apply);
-  m.def("groupnorm_silu_bwd_reduce", &groupnorm_silu_bwd_reduce);
+  m.def("groupnorm_silu_bwd_reduce", &groupnorm_silu_bwd_reduce, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("stats"),
+        pybind11::arg("gamma"), pybind11::arg("beta"), pybind11::arg("red"), pybind11::arg("groups"),
+        pybind11::arg("dgamma") = pybind11::none(), pybind11::arg("dbeta") = pybind11::none());
+  m.def("groupnorm_finalize", &groupnorm_finalize);
+  m.def("strided_add", &strided_add);
   m.def("groupnorm_silu_bwd_apply", &groupnorm_silu_bwd_apply);
   m.def("masked_loss", &masked_loss);
   m.def("adamw_step", &adamw_step);
   m.def("grad_inspect", &grad_inspect);
+  m.def("attn_rowdot", &attn_rowdot);
   m.def("sum_slots", &sum_slots, pybind11::arg("slots"), pybind11::arg("out"), pybind11::arg("bias") = pybind11::none(),
         pybind11::arg("residual") = pybind11::none());
   m.def("conv_s2_col2im", &conv_s2_col2im);

@@ -7,6 +7,8 @@
 
 namespace tb {
 
+struct KernelStatus;
+
 constexpr int COMM_MAX_PEERS = 16;
 
 // Sharded AdamW over replicas: this rank owns `n` elements starting at element `lo` of every replica's flat
@@ -40,6 +42,38 @@ int stream_write32(cudaStream_t stream, void* addr, unsigned int value);
 int gather_shards_async(cudaStream_t stream, void* dst, const void* const* src, int num_peers, int my_rank, long long rows,
                         size_t row_bytes, int chunks, long long chunk_rows, const unsigned int* signals, unsigned int* ready,
                         unsigned int epoch, int include_self = 0);
+// Halo exchange of two boundary rows with the row-stripe neighbours (see comm_kernels.cu). Null pointers: no neighbour
+// on that side. Buffers and flag words live in symmetric memory; `epoch` counts the exchanges of the group.
+struct HaloPushArgs {
+  const uint4* send_prev;          // this GPU's first row (goes to the previous rank's "row below" buffer)
+  const uint4* send_next;          // this GPU's last row (goes to the next rank's "row above" buffer)
+  uint4* dst_prev;                 // peer address of the previous rank's receive buffer, or null
+  uint4* dst_next;
+  long long nvec;                  // 16-byte vectors per row
+  uint32_t* flag_at_prev;          // peer address of the previous rank's "from next" counter, or null
+  uint32_t* flag_at_next;          // peer address of the next rank's "from prev" counter, or null
+  const uint32_t* my_flag_from_prev;   // local counters (null: no neighbour on that side)
+  const uint32_t* my_flag_from_next;
+  uint32_t epoch;
+  unsigned int* ticket;            // local word, zero between exchanges
+  unsigned long long budget_ns;
+  KernelStatus* status;
+};
+int halo_push(const HaloPushArgs& a, cudaStream_t stream);
+
+// Sum of an fp32 vector of at most `capacity` elements over the GPUs of a group, one single-block kernel.
+struct SmallReduceArgs {
+  float* slots[COMM_MAX_PEERS];    // every GPU's [2][num_peers][capacity] staging (symmetric)
+  uint32_t* flags[COMM_MAX_PEERS]; // every GPU's [num_peers] arrival counters (symmetric)
+  const float* in;
+  float* out;
+  int num_peers, my_rank, n, capacity, parity;
+  uint32_t epoch;
+  unsigned long long budget_ns;
+  KernelStatus* status;
+};
+int peer_allreduce_small(const SmallReduceArgs& a, cudaStream_t stream);
+
 // One-way "my earlier writes are visible" signal into word [slot_base + my_rank] of every peer's pad.
 int peer_signal(uint32_t* const* signal_pads, int my_rank, int num_peers, int slot_base, cudaStream_t stream);
 int peer_barrier(uint32_t* const* signal_pads, int my_rank, int num_peers, uint32_t epoch, void* status,

@@ -105,7 +105,101 @@ __global__ void peer_signal_kernel(const __grid_constant__ PadPtrs pads, int my_
   }
 }
 
+// Halo exchange between row-stripe neighbours, push style: every block copies a share of this GPU's two boundary
+// rows straight into the neighbours' receive buffers (16-byte stores over NVLink); the block that finishes last
+// publishes "rows of epoch e written" to each neighbour with a release at system scope and then waits (bounded by the
+// global timer) until the neighbours' rows for the same epoch have landed here. After the kernel the local receive
+// buffers hold the halo rows, so the convolution that follows reads local memory only.
+__global__ void __launch_bounds__(256) halo_push_kernel(const __grid_constant__ HaloPushArgs a) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long t0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (a.dst_prev != nullptr)
+    for (long long i = t0; i < a.nvec; i += stride) a.dst_prev[i] = a.send_prev[i];
+  if (a.dst_next != nullptr)
+    for (long long i = t0; i < a.nvec; i += stride) a.dst_next[i] = a.send_next[i];
+  __threadfence_system();
+  __shared__ unsigned int last;
+  __syncthreads();
+  if (threadIdx.x == 0) last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (last == 0u) return;
+  if (threadIdx.x == 0) *a.ticket = 0u;     // ready for the next exchange (stream order)
+  if (threadIdx.x < 2) {
+    uint32_t* peer_flag = threadIdx.x == 0 ? a.flag_at_prev : a.flag_at_next;
+    const uint32_t* my_flag = threadIdx.x == 0 ? a.my_flag_from_prev : a.my_flag_from_next;
+    if (peer_flag != nullptr) {
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_flag) : "memory");
+    }
+    if (my_flag != nullptr) {
+      const unsigned long long w0 = global_timer_ns();
+      uint32_t seen;
+      unsigned int polls = 0;
+      while (true) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+        if (static_cast<int32_t>(seen - a.epoch) >= 0) break;
+        if ((++polls & 63u) == 0u && global_timer_ns() - w0 > a.budget_ns) {
+          report_error(a.status, TB_ERR_PEER_TIMEOUT, 0xa00u + threadIdx.x, seen, a.epoch);
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+  }
+}
+
+// All-reduce (sum) of a small fp32 vector over the GPUs of a group in one single-block kernel: push this GPU's values
+// into its slot on every peer, publish, wait (bounded) for everybody's slot here, add the slots up. The slots are
+// double buffered by call parity: a peer can be at most one call ahead, because it needs this GPU's signal of call k + 1
+// to get past it, and that signal is sent only after call k has been summed here (stream order).
+__global__ void __launch_bounds__(512) peer_allreduce_small_kernel(const __grid_constant__ SmallReduceArgs a) {
+  const int t = threadIdx.x;
+  for (int p = 0; p < a.num_peers; ++p) {
+    float* dst = a.slots[p] + (static_cast<size_t>(a.parity) * a.num_peers + a.my_rank) * a.capacity;
+    for (int i = t; i < a.n; i += blockDim.x) dst[i] = a.in[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (t < a.num_peers) {
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.flags[t] + a.my_rank) : "memory");
+    const volatile uint32_t* mine = a.flags[a.my_rank] + t;
+    const unsigned long long w0 = global_timer_ns();
+    uint32_t seen;
+    unsigned int polls = 0;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(seen - a.epoch) >= 0) break;
+      if ((++polls & 63u) == 0u && global_timer_ns() - w0 > a.budget_ns) {
+        report_error(a.status, TB_ERR_PEER_TIMEOUT, 0xb00u, static_cast<unsigned int>(t), a.epoch);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  const float* base = a.slots[a.my_rank] + static_cast<size_t>(a.parity) * a.num_peers * a.capacity;
+  for (int i = t; i < a.n; i += blockDim.x) {
+    float acc = 0.f;
+    for (int p = 0; p < a.num_peers; ++p) acc += base[static_cast<size_t>(p) * a.capacity + i];
+    a.out[i] = acc;
+  }
+}
+
 }  // namespace
+
+int halo_push(const HaloPushArgs& a, cudaStream_t stream) {
+  if (a.nvec <= 0 || a.ticket == nullptr) return -1;
+  long long blocks = (a.nvec + 255) / 256;
+  if (blocks > 64) blocks = 64;
+  halo_push_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int peer_allreduce_small(const SmallReduceArgs& a, cudaStream_t stream) {
+  if (a.num_peers < 1 || a.num_peers > COMM_MAX_PEERS || a.n <= 0 || a.n > a.capacity) return -1;
+  peer_allreduce_small_kernel<<<1, 512, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 int peer_signal(uint32_t* const* signal_pads, int my_rank, int num_peers, int slot_base, cudaStream_t stream) {
   if (num_peers < 1 || num_peers > COMM_MAX_PEERS || slot_base < 0) return -1;

@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(256) groupnorm_silu_apply_kernel(const __nv_bf
 __global__ void __launch_bounds__(512) groupnorm_silu_bwd_reduce_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ stats,
     const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta, float* __restrict__ red,
-    long long HW, int C, int groups, int pix_per_block) {
+    long long HW, int C, int groups, int pix_per_block, float* __restrict__ dgamma, float* __restrict__ dbeta) {
   extern __shared__ float sh[];  // [2][C]
   const int nvec = C >> 3;
   const int cpg = C / groups;
@@ -388,6 +388,42 @@ __global__ void __launch_bounds__(512) groupnorm_silu_bwd_reduce_kernel(
   for (int c = threadIdx.y * blockDim.x + threadIdx.x; c < C; c += blockDim.x * blockDim.y) {
     atomicAdd(&red[(static_cast<long long>(b) * C + c) * 2 + 0], sh[c]);
     atomicAdd(&red[(static_cast<long long>(b) * C + c) * 2 + 1], sh[C + c]);
+    // the affine parameters' gradients are the same sums taken over the batch as well
+    if (dbeta != nullptr) atomicAdd(&dbeta[c], sh[c]);
+    if (dgamma != nullptr) atomicAdd(&dgamma[c], sh[C + c]);
+  }
+}
+
+// {sum, sum of squares} per (sample, group) -> {mean, rstd}; the sums are cleared for their next use
+__global__ void groupnorm_finalize_kernel(float* __restrict__ sums, float* __restrict__ stats, int cells, float inv_count,
+                                          float eps, int clear) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < cells) {
+    const float mean = sums[2 * i] * inv_count;
+    const float var = fmaxf(sums[2 * i + 1] * inv_count - mean * mean, 0.f);
+    stats[2 * i] = mean;
+    stats[2 * i + 1] = rsqrtf(var + eps);
+    if (clear) {
+      sums[2 * i] = 0.f;
+      sums[2 * i + 1] = 0.f;
+    }
+  }
+}
+
+// dst[a * sa + b * sb + c * sc] += src[(a * nb + b) * nc + c] (fp32); with `clear` the source is zeroed behind the read,
+// so that a persistent staging buffer is clean for its next accumulation. Used to fold tap-major convolution weight
+// gradients into the (Cout, Cin, kh, kw) layout of the gradient arena.
+__global__ void __launch_bounds__(256) strided_add_kernel(float* __restrict__ src, float* __restrict__ dst, int na, int nb,
+                                                          int nc, long long sa, long long sb, long long sc, int clear) {
+  const long long total = static_cast<long long>(na) * nb * nc;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % nc);
+    const long long t = i / nc;
+    const int b = static_cast<int>(t % nb), a2 = static_cast<int>(t / nb);
+    const float v = src[i];
+    dst[a2 * sa + b * sb + c * sc] += v;
+    if (clear) src[i] = 0.f;
   }
 }
 
@@ -474,6 +510,33 @@ __global__ void __launch_bounds__(256) masked_loss_kernel(const __nv_bfloat16* _
     float s = 0.f;
     for (int w = 0; w < (blockDim.x >> 5); ++w) s += sh[w];
     atomicAdd(loss_sum, s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ attention row dots
+// drow[row, head] = sum over the head's channels of dO * O: the "D" term of the attention backward pass. A warp per row;
+// lanes stride over the row's 16-byte vectors, then the lanes of one head are summed.
+__global__ void __launch_bounds__(256) attn_rowdot_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
+                                                          float* __restrict__ drow, long long rows, int vec_per_row,
+                                                          int vec_per_head, int heads) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = warp; r < rows; r += nwarps) {
+    for (int v0 = 0; v0 < vec_per_row; v0 += 32) {
+      const int v = v0 + lane;
+      float acc = 0.f;
+      if (v < vec_per_row) {
+        float x[8], y[8];
+        unpack8(o[r * vec_per_row + v], x);
+        unpack8(dout[r * vec_per_row + v], y);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(x[j], y[j], acc);
+      }
+      // vec_per_head is 2, 4, 8 or 16 (head dims 16 .. 128): sum groups of that many neighbouring lanes
+      for (int d = 1; d < vec_per_head && d < 32; d <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+      if (v < vec_per_row && (v % vec_per_head) == 0) drow[r * heads + v / vec_per_head] = acc;
+    }
   }
 }
 
@@ -719,7 +782,7 @@ int groupnorm_silu_apply(const void* x, const float* stats, const void* gamma, c
 }
 
 int groupnorm_silu_bwd_reduce(const void* dy, const void* x, const float* stats, const void* gamma, const void* beta,
-                              float* red, float* /*dgamma*/, float* /*dbeta*/, int B, long long HW, int C, int groups,
+                              float* red, float* dgamma, float* dbeta, int B, long long HW, int C, int groups,
                               cudaStream_t stream) {
   if (C % 8 != 0 || C % groups != 0) return -1;
   const int nvec = C / 8;
@@ -730,7 +793,21 @@ int groupnorm_silu_bwd_reduce(const void* dy, const void* x, const float* stats,
   groupnorm_silu_bwd_reduce_kernel<<<grid, block, 2 * C * sizeof(float), stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stats,
       static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta), red, HW, C, groups,
-      pix_per_block);
+      pix_per_block, dgamma, dbeta);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int groupnorm_finalize(float* sums, float* stats, int cells, float inv_count, float eps, int clear, cudaStream_t stream) {
+  if (cells <= 0) return 0;
+  groupnorm_finalize_kernel<<<(cells + 255) / 256, 256, 0, stream>>>(sums, stats, cells, inv_count, eps, clear);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int strided_add_f32(float* src, float* dst, int na, int nb, int nc, long long sa, long long sb, long long sc, int clear,
+                    cudaStream_t stream) {
+  const long long total = static_cast<long long>(na) * nb * nc;
+  if (total <= 0) return 0;
+  strided_add_kernel<<<grid_for(total, 256), 256, 0, stream>>>(src, dst, na, nb, nc, sa, sb, sc, clear);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -794,6 +871,16 @@ int conv_s2_col2im(const void* dcol, void* out, int B, int Ho, int Wo, int W, in
   else
     conv_s2_col2im_kernel<false><<<grid_for(total, 256), 256, 0, stream>>>(static_cast<const uint4*>(dcol), out, B, Ho, Wo, W,
                                                                            C / 8, r0, rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int attn_rowdot(const void* o, const void* dout, float* drow, long long rows, int C, int heads, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (heads <= 0 || C % heads != 0) return -1;
+  const int hd = C / heads;
+  if (hd != 16 && hd != 32 && hd != 64 && hd != 128) return -1;
+  attn_rowdot_kernel<<<grid_for(rows * 32, 256), 256, 0, stream>>>(static_cast<const uint4*>(o), static_cast<const uint4*>(dout),
+                                                                  drow, rows, C / 8, hd / 8, heads);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -87,6 +87,11 @@ int groupnorm_silu_bwd_reduce(const void* dy, const void* x, const float* stats,
 int groupnorm_silu_bwd_apply(const void* dy, const void* x, const float* stats, const float* red, const void* gamma,
                              const void* beta, void* dx, int B, long long HW, int C, int groups, float inv_count,
                              cudaStream_t stream);
+// {sum, sumsq} per (sample, group) cell -> {mean, rstd}; `clear` zeroes the sums afterwards (persistent scratch).
+int groupnorm_finalize(float* sums, float* stats, int cells, float inv_count, float eps, int clear, cudaStream_t stream);
+// dst[a*sa + b*sb + c*sc] += src[a][b][c] (fp32, src contiguous [na][nb][nc]); `clear` zeroes src behind the read.
+int strided_add_f32(float* src, float* dst, int na, int nb, int nc, long long sa, long long sb, long long sc, int clear,
+                    cudaStream_t stream);
 // Masked loss: loss_sum += sum(f(pred * mask - label)), f = |.| (kind 0) or square (kind 1);
 // grad = mask * f'(.) * scale (bf16). `mask` may be null. Partial sums are fp32 atomics on loss_sum[0].
 int masked_loss_fwd_bwd(const void* pred, const void* label, const void* mask, long long n, long long mask_period,
@@ -122,6 +127,7 @@ struct WindowAttnArgs {
   const float* bias_table;         // fp32 [(2wh-1)*(2ww-1), num_heads] or null
   float* dbias_table;              // backward, fp32 atomics (caller zeroes), or null
   float* lse[WA_MAX_PEERS];        // optional, tensor-core forward: base-2 log-sum-exp per (row, head), fp32 [rows, num_heads]
+  const float* drow[WA_MAX_PEERS]; // tensor-core backward of large windows: rowsum(dO o O) per (row, head), fp32 [rows, num_heads]
   int win_start[9];                // flat window range of window-group rank p: [win_start[p], win_start[p+1])
   int n_wg, my_wg;                 // ranks along the window dimension, and mine
   int sp, my_sp, shardN;           // tokens of a window are split into sp shards of shardN tokens
@@ -143,7 +149,10 @@ int window_attn_tc_fwd(const WindowAttnArgs& a, void* status, cudaStream_t strea
 // for a free buffer, [2] MMA thread span, [3] waiting for operands, [4] waiting for probabilities, [5] softmax thread
 // span, [6] waiting for scores, [7] waiting for outputs. Synchronises the device.
 int window_attn_tc_stalls(unsigned long long* out16, int reset);   // [8..13]: softmax thread segments, see window_attn_tc.cu
-// Backward on tcgen05 for windows of at most 64 tokens and head dims 16 / 32 / 64.
+// Backward on tcgen05, head dims 16 / 32 / 64: one pass for windows of at most 64 tokens, two passes (dQ; dK, dV) with
+// `lse` and `drow` for larger ones.
 int window_attn_tc_bwd(const WindowAttnArgs& a, void* status, cudaStream_t stream);
+// drow[row, head] = sum over the head's channels of dO * O (bf16 [rows, C] inputs, fp32 [rows, heads] output).
+int attn_rowdot(const void* o, const void* dout, float* drow, long long rows, int C, int heads, cudaStream_t stream);
 
 }  // namespace tb

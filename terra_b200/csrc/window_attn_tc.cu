@@ -1113,6 +1113,453 @@ int launch_tc_bwd(const WindowAttnArgs& a, void* status, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? 0 : -33;
 }
 
+// ================================================================================================ backward, N > 64
+// Large windows: two passes over 128 x 128 blocks of the score matrix, both without atomics or cross-rank reductions.
+//   PASS 0 (dQ):      an item is a block of 128 of this rank's queries; the window's keys stream by in blocks of 128:
+//                     dQ += dS K, accumulated in tensor memory over the key blocks.
+//   PASS 1 (dK, dV):  an item is a block of 128 of this rank's keys; all of the window's queries (with their dO, LSE and
+//                     D = rowsum(dO o O), read from their home rows, possibly on peers) stream by in blocks of 128:
+//                     dV += P^T dO, dK += dS^T Q.
+// Per step and head: S = Q K^T and dP = dO V^T (M = N = 128); the row's thread turns them into P = exp2(S' - LSE) and
+// dS = P (dP - D) 32 columns at a time - the softmax statistics come from the forward pass, so no row-wide reduction
+// is needed - and writes them as [row][key] tiles, the operands of the output products.
+template <int HD, int PASS>
+__global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_bwd_block_kernel(const __grid_constant__ WindowAttnArgs a,
+                                                                           const __grid_constant__ TcPlan pl,
+                                                                           KernelStatus* status) {
+  constexpr int G = 64, HPG = G / HD;
+  constexpr int MAT = TC_ROWS * 128;
+  constexpr int COL_DP = 128, COL_OUT = 256;      // PASS 0: dQ [G]; PASS 1: dV [G] then dK [G]
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* fixed_set = smem;                         // [2][MAT]: PASS 0: q, dO of the item's queries; PASS 1: k, v of its keys
+  uint8_t* stream_set = fixed_set + 2 * MAT;         // [2 stages][2][MAT]: the other side, block by block
+  uint8_t* p_tiles = stream_set + 4 * MAT;           // [2][MAT] key block 0 / 1
+  uint8_t* ds_tiles = p_tiles + 2 * MAT;
+  uint8_t* tail = ds_tiles + 2 * MAT;
+  struct Bars {
+    uint64_t fixed_full, fixed_empty, st_full[2], st_empty[2], sdp_full, pds_full, out_done, item_done, rows_sync;
+  };
+  Bars* bars = reinterpret_cast<Bars*>(tail);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + sizeof(Bars));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* key_term = reinterpret_cast<int*>(tail + 128);   // [2][128] bias term of the keys of the current key block
+  int* key_reg = key_term + 2 * TC_ROWS;                // [2][128] their mask region (15: beyond the window)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  Geo geo;
+  geo.N = pl.N;
+  geo.nrel = (2 * a.wh - 1) * (2 * a.ww - 1);
+  geo.Hg = a.nWh * a.wh;
+  geo.Wg = a.nWw * a.ww;
+  const int N = pl.N;
+  const int rel0 = (a.wh - 1) * (2 * a.ww - 1) + (a.ww - 1);
+  const int nblk = (N + TC_ROWS - 1) / TC_ROWS;          // blocks of the streamed side (all keys / all queries)
+  const bool use_bias = a.bias_table != nullptr;
+  const bool bias_grad = PASS == 0 && use_bias && a.dbias_table != nullptr;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->fixed_full, 32 * TC_PROD);
+    mbar_init(&bars->fixed_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->st_full[i], 32 * TC_PROD);
+      mbar_init(&bars->st_empty[i], 1);
+    }
+    mbar_init(&bars->sdp_full, 1);
+    mbar_init(&bars->pds_full, 4);
+    mbar_init(&bars->out_done, 1);
+    mbar_init(&bars->item_done, 1);
+    mbar_init(&bars->rows_sync, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == TC_MMA_WARP) {
+    tmem_alloc<512>(tmem_slot);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // item -> (head group, batch, window, block of the fixed side); the fixed side covers this rank's token shard
+  auto decode = [&](int item, int& hg, int& b, int& lw, int& fb) {
+    const int per_hg = pl.items / pl.hgroups;
+    hg = item / per_hg;
+    const int t = item % per_hg;
+    b = t / pl.tiles_per_b;
+    const int tile = t % pl.tiles_per_b;
+    lw = tile / pl.nqb;
+    fb = tile % pl.nqb;
+  };
+
+  if (warp < TC_PROD) {
+    // ================================================================== producers
+    uint64_t* fifo[3] = {nullptr, nullptr, nullptr};
+    int pending = 0;
+    auto retire_oldest = [&]() {
+      fence_proxy_async_smem();
+      mbar_arrive(fifo[0]);
+      fifo[0] = fifo[1];
+      fifo[1] = fifo[2];
+      fifo[2] = nullptr;
+      --pending;
+    };
+    auto submit = [&](uint64_t* bar) {
+      tc_cp_commit();
+      fifo[pending++] = bar;
+      if (pending == 3) {
+        tc_cp_wait<2>();
+        retire_oldest();
+      }
+    };
+    auto wait_empty = [&](uint64_t* bar, uint32_t parity, unsigned where) -> bool {
+      // The consumer may need tiles whose arrival this lane still defers (copies in flight): if the buffer is not
+      // free yet, let everything land and be counted in first - otherwise producer and consumer wait for each other.
+      int ready = 0;
+      if (lane == 0) ready = mbar_try_wait(bar, parity) ? 1 : 0;
+      if (__shfl_sync(0xffffffffu, ready, 0) != 0) return true;
+      tc_cp_wait<0>();
+      while (pending > 0) retire_oldest();
+      int got = 1;
+      if (lane == 0) got = mbar_wait(bar, parity, abort_flag, status, where) ? 1 : 0;
+      return __shfl_sync(0xffffffffu, got, 0) != 0;
+    };
+    // 128 rows = tokens tok0 .. tok0 + 127 of window `flat` (below tok_end): `queries`: q and dO, else k and v
+    auto gather = [&](uint8_t* dst, int b, int flat, int tok0, int tok_end, int hg, bool queries) {
+      const int ii = flat / a.nWw, jj = flat % a.nWw;
+      const uint32_t d0 = smem_u32(dst);
+      for (int g0 = warp * 32; g0 < TC_ROWS; g0 += 32 * TC_PROD) {
+        const int tok = tok0 + g0 + lane;
+        long long o0 = 0, o1 = 0;
+        int slot = -1;
+        if (tok < tok_end) {
+          const int ti = tok / a.ww, tj = tok - ti * a.ww;
+          const Home h = locate_ij(a, geo, b, ii, jj, ti, tj);
+          slot = h.slot;
+          if (queries) {
+            o0 = h.row * (3LL * a.C) + hg * G;                               // q
+            o1 = h.row * static_cast<long long>(a.C) + hg * G;               // dO (its own buffer)
+          } else {
+            o0 = h.row * (3LL * a.C) + a.C + hg * G;                         // k
+            o1 = o0 + a.C;                                                   // v
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int idx = k * 32 + lane;
+          const int rr = idx >> 3, ch = idx & 7;
+          const long long s0 = __shfl_sync(0xffffffffu, o0, rr);
+          const long long s1 = __shfl_sync(0xffffffffu, o1, rr);
+          const int sp = __shfl_sync(0xffffffffu, slot, rr);
+          const int row = g0 + rr;
+          const bool valid = sp >= 0;
+          const __nv_bfloat16* base0 = static_cast<const __nv_bfloat16*>(a.qkv[valid ? sp : 0]);
+          const __nv_bfloat16* base1 = queries ? static_cast<const __nv_bfloat16*>(a.dout[valid ? sp : 0]) : base0;
+          const uint32_t off = row * 128 + ((ch ^ (row & 7)) << 4);
+          tc_cp_async16(d0 + off, base0 + (valid ? s0 + ch * 8 : 0), valid);
+          tc_cp_async16(d0 + MAT + off, base1 + (valid ? s1 + ch * 8 : 0), valid);
+        }
+      }
+    };
+    uint32_t items_done = 0, st_it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < pl.items && ok && !*abort_flag; item += gridDim.x, ++items_done) {
+      int hg, b, lw, fb;
+      decode(item, hg, b, lw, fb);
+      const int flat = a.win_start[a.my_wg] + lw;
+      if (!(ok = wait_empty(&bars->fixed_empty, (items_done & 1u) ^ 1u, 0x6100u))) break;
+      gather(fixed_set, b, flat, pl.q0 + fb * TC_ROWS, pl.q1, hg, PASS == 0);
+      submit(&bars->fixed_full);
+      for (int blk = 0; blk < nblk && ok; ++blk, ++st_it) {
+        const int st = st_it & 1;
+        if (!(ok = wait_empty(&bars->st_empty[st], ((st_it >> 1) & 1u) ^ 1u, 0x6200u + st))) break;
+        gather(stream_set + st * 2 * MAT, b, flat, blk * TC_ROWS, N, hg, PASS == 1);
+        submit(&bars->st_full[st]);
+      }
+    }
+    tc_cp_wait<0>();
+    while (pending > 0) retire_oldest();
+  } else if (warp == TC_MMA_WARP) {
+    // ================================================================== MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(TC_ROWS, 128, 0, 0);
+      constexpr uint32_t idesc_t = make_idesc_bf16(TC_ROWS, HD, 1, 1);
+      constexpr uint32_t idesc_q = make_idesc_bf16(TC_ROWS, HD, 0, 1);
+      const uint32_t p_addr = smem_u32(p_tiles), ds_addr = smem_u32(ds_tiles), fx = smem_u32(fixed_set);
+      uint32_t items_done = 0, st_it = 0, gs = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < pl.items && ok && !*abort_flag; item += gridDim.x, ++items_done) {
+        if (!(ok = mbar_wait(&bars->fixed_full, items_done & 1u, abort_flag, status, 0x6300u))) break;
+        // operands: Q / dO are the fixed set in PASS 0 and the streamed set in PASS 1; K / V the other way round
+        auto issue_sdp = [&](uint32_t sx, int h) {
+          const uint32_t q = PASS == 0 ? fx : sx, dO = q + MAT, k = PASS == 0 ? sx : fx, v = k + MAT;
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (h * HD + kk * 16) * 2;
+            umma_bf16(tmem_base, make_smem_desc(q + off, 16, 1024), make_smem_desc(k + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (h * HD + kk * 16) * 2;
+            umma_bf16(tmem_base + COL_DP, make_smem_desc(dO + off, 16, 1024), make_smem_desc(v + off, 16, 1024), idesc_s,
+                      kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&bars->sdp_full);
+        };
+        for (int blk = 0; blk < nblk && ok; ++blk, ++st_it) {
+          const int st = st_it & 1;
+          if (!(ok = mbar_wait(&bars->st_full[st], (st_it >> 1) & 1u, abort_flag, status, 0x6400u + st))) break;
+          tc_fence_after();
+          const uint32_t sx = smem_u32(stream_set + st * 2 * MAT);
+          if (blk == 0) issue_sdp(sx, 0);
+          for (int h = 0; h < HPG && ok; ++h, ++gs) {
+            if (!(ok = mbar_wait(&bars->pds_full, gs & 1u, abort_flag, status, 0x6500u))) break;
+            tc_fence_after();
+            const uint32_t hb = h * HD * 2;
+            const uint32_t acc = blk > 0 ? 1u : 0u;
+            if (PASS == 0) {
+              // dQ[h] += dS K: contraction over the 128 keys of this block
+#pragma unroll
+              for (int k8 = 0; k8 < 8; ++k8)
+                umma_bf16(tmem_base + COL_OUT + h * HD, make_smem_desc(ds_addr + (k8 >> 2) * MAT + (k8 & 3) * 32, 16, 1024),
+                          make_smem_desc(sx + hb + k8 * 2048, MAT, 1024), idesc_q, (acc | (k8 > 0)) ? 1u : 0u);
+            } else {
+              // dV[h] += P^T dO, dK[h] += dS^T Q: contraction over the 128 queries of this block
+#pragma unroll
+              for (int k8 = 0; k8 < 8; ++k8)
+                umma_bf16(tmem_base + COL_OUT + h * HD, make_smem_desc(p_addr + k8 * 2048, MAT, 1024),
+                          make_smem_desc(sx + MAT + hb + k8 * 2048, MAT, 1024), idesc_t, (acc | (k8 > 0)) ? 1u : 0u);
+#pragma unroll
+              for (int k8 = 0; k8 < 8; ++k8)
+                umma_bf16(tmem_base + COL_OUT + G + h * HD, make_smem_desc(ds_addr + k8 * 2048, MAT, 1024),
+                          make_smem_desc(sx + hb + k8 * 2048, MAT, 1024), idesc_t, (acc | (k8 > 0)) ? 1u : 0u);
+            }
+            umma_commit(&bars->out_done);
+            if (h == HPG - 1) umma_commit(&bars->st_empty[st]);
+            // next step's scores: the next head of this block, or head 0 of the next block (once it has landed)
+            if (h + 1 < HPG) {
+              issue_sdp(sx, h + 1);
+            } else if (blk + 1 < nblk) {
+              const int st2 = (st_it + 1) & 1;
+              if (!(ok = mbar_wait(&bars->st_full[st2], ((st_it + 1) >> 1) & 1u, abort_flag, status, 0x6600u + st2))) break;
+              tc_fence_after();
+              issue_sdp(smem_u32(stream_set + st2 * 2 * MAT), 0);
+            }
+          }
+        }
+        if (!ok) break;
+        umma_commit(&bars->item_done);
+        umma_commit(&bars->fixed_empty);
+      }
+    }
+  } else {
+    // ================================================================== rows
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const float scale2 = a.scale * TC_LOG2E;
+    uint32_t gs = 0, syncs = 0, items_done = 0;
+    bool ok = true;
+    auto rows_barrier = [&]() {
+      mbar_arrive(&bars->rows_sync);
+      if (ok) ok = mbar_wait(&bars->rows_sync, syncs & 1u, abort_flag, status, 0x7500u);
+      ++syncs;
+      ok = __all_sync(0xffffffffu, ok);
+    };
+    for (int item = blockIdx.x; item < pl.items && ok; item += gridDim.x, ++items_done) {
+      int hg, b, lw, fb;
+      decode(item, hg, b, lw, fb);
+      const int flat = a.win_start[a.my_wg] + lw;
+      const int ii = flat / a.nWw, jj = flat % a.nWw;
+      const bool general = a.use_mask && ((a.sh > 0 && ii == a.nWh - 1) || (a.sw > 0 && jj == a.nWw - 1));
+      // the fixed-side token of this thread: a query in PASS 0 (softmax row and output row), a key in PASS 1 (output row)
+      const int ftok = pl.q0 + fb * TC_ROWS + r;
+      const bool factive = ftok < pl.q1;
+      const int ftk = min(ftok, N - 1);
+      const int fti = ftk / a.ww, ftj = ftk - fti * a.ww;
+      const Home fhome = locate_ij(a, geo, b, ii, jj, fti, ftj);
+      float lse_row[HPG], d_row[HPG];
+      int row_term = 0, row_reg = 0;
+      bool row_active = false;
+      auto load_row = [&](int tok) {
+        // softmax statistics of query `tok` from its home row
+        row_active = tok < N;
+        const int tk = min(tok, N - 1);
+        const int ti = tk / a.ww, tj = tk - ti * a.ww;
+        const Home h = (PASS == 0) ? fhome : locate_ij(a, geo, b, ii, jj, ti, tj);
+        row_term = ti * (2 * a.ww - 1) + tj + rel0;
+        row_reg = h.region;
+#pragma unroll
+        for (int hh = 0; hh < HPG; ++hh) {
+          const long long o = h.row * a.num_heads + hg * HPG + hh;
+          lse_row[hh] = row_active ? a.lse[h.slot][o] : 0.f;
+          d_row[hh] = row_active ? a.drow[h.slot][o] : 0.f;
+        }
+      };
+      if (PASS == 0) load_row(ftok);
+      if (PASS == 1) {
+        // the keys of the item are fixed: their bias terms and regions once per item
+        key_term[r] = fti * (2 * a.ww - 1) + ftj;
+        key_reg[r] = factive ? fhome.region : 15;
+        rows_barrier();
+        if (!ok) break;
+      }
+      for (int blk = 0; blk < nblk && ok; ++blk) {
+        const int kt = PASS == 0 ? (blk & 1) : 0;
+        if (PASS == 0) {
+          const int key = blk * TC_ROWS + r;
+          const int kk = min(key, N - 1);
+          const int ki = kk / a.ww, kj = kk - ki * a.ww;
+          key_term[kt * TC_ROWS + r] = ki * (2 * a.ww - 1) + kj;
+          key_reg[kt * TC_ROWS + r] = key < N ? region_of(a, geo, ii * a.wh + ki, jj * a.ww + kj) : 15;
+          rows_barrier();
+          if (!ok) break;
+        } else {
+          load_row(blk * TC_ROWS + r);
+        }
+        const int* kterm = key_term + kt * TC_ROWS;
+        const int* kreg = key_reg + kt * TC_ROWS;
+        for (int h = 0; h < HPG; ++h, ++gs) {
+          if (ok) ok = mbar_wait(&bars->sdp_full, gs & 1u, abort_flag, status, 0x7100u);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          float lse_h = 0.f, d_h = 0.f;
+#pragma unroll
+          for (int hh = 0; hh < HPG; ++hh)
+            if (hh == h) {
+              lse_h = lse_row[hh];
+              d_h = d_row[hh];
+            }
+          // the tiles are still being read by the previous step's products until out_done
+          if (gs > 0) {
+            if (ok) ok = mbar_wait(&bars->out_done, (gs - 1) & 1u, abort_flag, status, 0x7200u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+          }
+          const int head = hg * HPG + h;
+#pragma unroll
+          for (int c0 = 0; c0 < TC_ROWS; c0 += 32) {
+            uint32_t sv[32], dv[32];
+            tmem_ld_32x32(tmem_base + c0 + lane_base, sv);
+            tmem_ld_32x32(tmem_base + COL_DP + c0 + lane_base, dv);
+            tmem_ld_wait();
+            float p[32], ds[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int kc = c0 + c;
+              float sc = __uint_as_float(sv[c]) * scale2;
+              const int kr = kreg[kc];
+              if (use_bias)
+                sc += __ldg(a.bias_table + static_cast<long long>(row_term - kterm[kc]) * a.num_heads + head) * TC_LOG2E;
+              if (general && kr != row_reg) sc += -100.f * TC_LOG2E;
+              const float pv = (kr == 15 || !row_active) ? 0.f : exp2f(sc - lse_h);
+              p[c] = pv;
+              ds[c] = pv * (__uint_as_float(dv[c]) - d_h);
+              if (bias_grad && factive && pv != 0.f)
+                atomicAdd(a.dbias_table + static_cast<long long>(row_term - kterm[kc]) * a.num_heads + head, ds[c]);
+            }
+            // 32 columns = 4 chunks of key block (c0 / 64)
+            uint8_t* prow = p_tiles + (c0 >> 6) * MAT + r * 128;
+            uint8_t* drow = ds_tiles + (c0 >> 6) * MAT + r * 128;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const int c8 = ((c0 & 63) >> 3) + q4;
+              const int o = (c8 ^ (r & 7)) << 4;
+              if (PASS == 1)
+                *reinterpret_cast<uint4*>(prow + o) =
+                    make_uint4(pack_bf16x2(p[8 * q4], p[8 * q4 + 1]), pack_bf16x2(p[8 * q4 + 2], p[8 * q4 + 3]),
+                               pack_bf16x2(p[8 * q4 + 4], p[8 * q4 + 5]), pack_bf16x2(p[8 * q4 + 6], p[8 * q4 + 7]));
+              *reinterpret_cast<uint4*>(drow + o) =
+                  make_uint4(pack_bf16x2(ds[8 * q4], ds[8 * q4 + 1]), pack_bf16x2(ds[8 * q4 + 2], ds[8 * q4 + 3]),
+                             pack_bf16x2(ds[8 * q4 + 4], ds[8 * q4 + 5]), pack_bf16x2(ds[8 * q4 + 6], ds[8 * q4 + 7]));
+            }
+          }
+          tc_fence_before();
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->pds_full);
+        }
+      }
+      if (!ok) break;
+      // ---- all blocks accumulated: store this thread's row of the outputs to the token's home
+      if (ok) ok = mbar_wait(&bars->item_done, items_done & 1u, abort_flag, status, 0x7300u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.dqkv[fhome.slot]) + fhome.row * (3LL * a.C) + hg * G;
+      constexpr int NOUT = PASS == 0 ? 1 : 2;
+#pragma unroll
+      for (int m = 0; m < NOUT; ++m) {
+        // PASS 0: dQ (x scale) -> q columns; PASS 1: m = 0 dV -> v columns, m = 1 dK (x scale) -> k columns
+        const int col_off = PASS == 0 ? 0 : (m == 0 ? 2 * a.C : a.C);
+        const float mul = (PASS == 1 && m == 0) ? 1.f : a.scale;
+#pragma unroll
+        for (int c0 = 0; c0 < G; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + COL_OUT + m * G + c0 + lane_base, v);
+          tmem_ld_wait();
+          if (factive) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8)
+              *reinterpret_cast<uint4*>(dst + col_off + c0 + c) = make_uint4(
+                  pack_bf16x2(__uint_as_float(v[c]) * mul, __uint_as_float(v[c + 1]) * mul),
+                  pack_bf16x2(__uint_as_float(v[c + 2]) * mul, __uint_as_float(v[c + 3]) * mul),
+                  pack_bf16x2(__uint_as_float(v[c + 4]) * mul, __uint_as_float(v[c + 5]) * mul),
+                  pack_bf16x2(__uint_as_float(v[c + 6]) * mul, __uint_as_float(v[c + 7]) * mul));
+          }
+        }
+      }
+      tc_fence_before();
+      rows_barrier();      // everybody has read the outputs (and the key tables) before the next item overwrites them
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == TC_MMA_WARP) {
+    __syncwarp();
+    tmem_dealloc<512>(tmem_base);
+  }
+}
+
+template <int HD>
+int launch_tc_bwd_block(const WindowAttnArgs& a, void* status, cudaStream_t stream) {
+  TcPlan pl;
+  pl.N = a.wh * a.ww;
+  pl.pair = 0;
+  pl.my_nw = a.win_start[a.my_wg + 1] - a.win_start[a.my_wg];
+  pl.q0 = a.my_sp * a.shardN;
+  pl.q1 = pl.q0 + a.shardN < pl.N ? pl.q0 + a.shardN : pl.N;
+  pl.nqb = (pl.q1 - pl.q0 + TC_ROWS - 1) / TC_ROWS;
+  pl.tiles_per_b = pl.my_nw * pl.nqb;
+  pl.hgroups = a.C / 64;
+  pl.items = a.B * pl.tiles_per_b * pl.hgroups;
+  if (pl.items <= 0) return 0;
+  if (a.C % 64 != 0) return -31;
+  const size_t sb = 1024 + 10 * TC_ROWS * 128 + 128 + 4 * TC_ROWS * 4 + 64;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(wattn_tc_bwd_block_kernel<HD, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sb)) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(wattn_tc_bwd_block_kernel<HD, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sb)) !=
+            cudaSuccess)
+      return -32;
+    configured = true;
+  }
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = pl.items < sms ? pl.items : sms;
+  wattn_tc_bwd_block_kernel<HD, 0><<<grid, TC_THREADS, sb, stream>>>(a, pl, static_cast<KernelStatus*>(status));
+  if (cudaGetLastError() != cudaSuccess) return -33;
+  wattn_tc_bwd_block_kernel<HD, 1><<<grid, TC_THREADS, sb, stream>>>(a, pl, static_cast<KernelStatus*>(status));
+  return cudaGetLastError() == cudaSuccess ? 0 : -33;
+}
+
 template <int HD>
 int launch_tc(const WindowAttnArgs& a, void* status, cudaStream_t stream) {
   using Cfg = TcCfg<HD>;
@@ -1171,14 +1618,21 @@ int window_attn_tc_fwd(const WindowAttnArgs& a, void* status, cudaStream_t strea
   }
 }
 
-// Backward on tcgen05 for windows of at most 64 tokens and head dims 16 / 32 / 64 (other shapes: window_attn_bwd).
+// Backward on tcgen05, head dims 16 / 32 / 64. Windows of at most 64 tokens: one pass, two windows per tile, softmax
+// statistics recomputed. Larger windows: two passes (dQ; dK and dV) over 128 x 128 blocks, which need the forward
+// pass's log-sum-exp (`lse`, as written by window_attn_tc_fwd) and `drow` = rowsum(dO o O) per (row, head).
 int window_attn_tc_bwd(const WindowAttnArgs& a, void* status, cudaStream_t stream) {
   if (a.num_heads <= 0 || a.C % a.num_heads != 0) return -10;
   if (a.sp < 1 || a.shardN < 1 || a.n_wg < 1 || a.n_wg > 8 || a.n_wg * a.sp > WA_MAX_PEERS) return -12;
+  const bool large = a.wh * a.ww > TC_KV;
+  if (large) {
+    for (int i = 0; i < a.n_wg * a.sp; ++i)
+      if (a.lse[i] == nullptr || a.drow[i] == nullptr) return -14;
+  }
   switch (a.C / a.num_heads) {
-    case 16: return launch_tc_bwd<16>(a, status, stream);
-    case 32: return launch_tc_bwd<32>(a, status, stream);
-    case 64: return launch_tc_bwd<64>(a, status, stream);
+    case 16: return large ? launch_tc_bwd_block<16>(a, status, stream) : launch_tc_bwd<16>(a, status, stream);
+    case 32: return large ? launch_tc_bwd_block<32>(a, status, stream) : launch_tc_bwd<32>(a, status, stream);
+    case 64: return large ? launch_tc_bwd_block<64>(a, status, stream) : launch_tc_bwd<64>(a, status, stream);
     default: return -13;
   }
 }

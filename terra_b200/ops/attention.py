@@ -101,7 +101,7 @@ def shifted_window_sources(geo: WindowGeometry, shifted: bool):
 
 
 MAX_MMA_WINDOW_TOKENS = 128         # window_attn.cu (mma.sync forward / backward) keeps a whole window in shared memory
-MAX_KERNEL_WINDOW_TOKENS = 128      # largest window whose backward runs on a kernel of this package
+MAX_KERNEL_WINDOW_TOKENS = 128      # windows up to here run inside the fused attention half (LayerNorm .. proj in one node)
 
 
 def attention_core_reference(q, k, v, scale, bias, mask):
@@ -193,16 +193,77 @@ def launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, bias_f32, geo: "WindowGeomet
 
 
 def launch_window_attn_bwd(ext, qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, geo: "WindowGeometry", C, num_heads, sh, sw,
-                           use_mask, scale, device):
-    """One backward launch on the selected kernel."""
+                           use_mask, scale, device, lse_ptrs=(), drow_ptrs=()):
+    """One backward launch on the selected kernel. Windows above 128 tokens run the two-pass tensor-core backward,
+    which needs the forward pass's log-sum-exp (``lse_ptrs``) and ``drow`` = rowsum(dO * O) per (row, head)."""
     args = (list(geo.win_start), geo.my_wg, geo.sp, geo.my_sp, geo.shardN, geo.B, geo.nWh, geo.nWw, C, num_heads, geo.wh,
             geo.ww, sh, sw, bool(use_mask), float(scale), geo.tp)
-    if attn_backward_impl(geo.N, C // num_heads) == "tc":
+    hd = C // num_heads
+    if geo.N > MAX_MMA_WINDOW_TOKENS:
+        if hd not in (16, 32, 64):
+            raise NotImplementedError(f"backward of windows above {MAX_MMA_WINDOW_TOKENS} tokens needs a head dim of 16, 32 "
+                                      f"or 64 (got {hd})")
         from .gemm import status_word
 
-        ext.window_attn_tc_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, *args, status_word(device))
+        ext.window_attn_tc_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, *args, status_word(device), list(lse_ptrs),
+                               list(drow_ptrs))
+    elif attn_backward_impl(geo.N, hd) == "tc":
+        from .gemm import status_word
+
+        ext.window_attn_tc_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, *args, status_word(device), [], [])
     else:
         ext.window_attn_bwd(qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, *args)
+
+
+def attention_forward(ext, qkv, geo: "WindowGeometry", C, num_heads, shifted, use_mask, scale, bias_f32, comm):
+    """Forward on ``qkv`` (already in symmetric memory when ``comm`` is given). Returns ``(out, qkv, lse)``; ``lse``
+    (fp32 ``[rows, heads]``, base 2) exists for windows above 128 tokens, whose backward needs it."""
+    rows = qkv.shape[0]
+    sh, sw = geo.shift(shifted)
+    large = geo.N > MAX_MMA_WINDOW_TOKENS
+    lse, lse_ptrs = None, ()
+    if comm is None:
+        out = torch.empty(rows, C, dtype=torch.bfloat16, device=qkv.device)
+        qkv_ptrs, out_ptrs = [qkv.data_ptr()], [out.data_ptr()]
+        if large:
+            lse = torch.empty(rows, num_heads, dtype=torch.float32, device=qkv.device)
+            lse_ptrs = [lse.data_ptr()]
+    else:
+        if large:
+            lse = comm.alloc_f32(rows, num_heads)
+            lse_ptrs = comm.arena.peer_ptrs(lse)
+        out, qkv_ptrs, out_ptrs = comm.attn_forward_buffers(qkv, C, shifted)
+    launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, bias_f32, geo, C, num_heads, sh, sw, use_mask and shifted, scale,
+                           qkv.device, lse_ptrs)
+    if comm is not None:
+        out, qkv = comm.attn_forward_done(out, qkv, shifted)
+    return out, qkv, lse
+
+
+def attention_backward(ext, qkv, out, dout, lse, geo: "WindowGeometry", C, num_heads, shifted, use_mask, scale, bias_f32,
+                       dbias, comm):
+    """Gradient of ``qkv``. ``dout`` must already be in symmetric memory when ``comm`` is given."""
+    sh, sw = geo.shift(shifted)
+    large = geo.N > MAX_MMA_WINDOW_TOKENS
+    drow, lse_ptrs, drow_ptrs = None, (), ()
+    if large:
+        drow = comm.alloc_f32(qkv.shape[0], num_heads) if comm is not None else \
+            torch.empty(qkv.shape[0], num_heads, dtype=torch.float32, device=qkv.device)
+        ext.attn_rowdot(out, dout, drow, num_heads)          # before the barrier that publishes this rank's rows
+    if comm is None:
+        dqkv = torch.empty_like(qkv)
+        qkv_ptrs, dout_ptrs, dqkv_ptrs = [qkv.data_ptr()], [dout.data_ptr()], [dqkv.data_ptr()]
+        if large:
+            lse_ptrs, drow_ptrs = [lse.data_ptr()], [drow.data_ptr()]
+    else:
+        dqkv, qkv_ptrs, dout_ptrs, dqkv_ptrs = comm.attn_backward_buffers(qkv, dout, shifted)
+        if large:
+            lse_ptrs, drow_ptrs = comm.arena.peer_ptrs(lse), comm.arena.peer_ptrs(drow)
+    launch_window_attn_bwd(ext, qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32, dbias, geo, C, num_heads, sh, sw,
+                           use_mask and shifted, scale, qkv.device, lse_ptrs, drow_ptrs)
+    if comm is not None:
+        dqkv = comm.attn_backward_done(dqkv, shifted)
+    return dqkv
 
 
 class _WindowAttnFn(torch.autograd.Function):
@@ -214,21 +275,14 @@ class _WindowAttnFn(torch.autograd.Function):
     def forward(ctx, qkv, bias_table, geo, num_heads, shifted, use_mask, scale, comm):
         ext = _ext.load()
         C = qkv.shape[-1] // 3
-        sh, sw = geo.shift(shifted)
         bias_f32 = bias_table.detach().float().contiguous() if bias_table is not None else None
-        if comm is None:
-            out = torch.empty(qkv.shape[0], C, dtype=torch.bfloat16, device=qkv.device)
-            qkv_ptrs, out_ptrs = [qkv.data_ptr()], [out.data_ptr()]
-        else:
+        if comm is not None:
             staged = comm.alloc_qkv(qkv.shape[0], 3 * C)
             staged.copy_(qkv)
             qkv = staged
-            out, qkv_ptrs, out_ptrs = comm.attn_forward_buffers(qkv, C, shifted)
-        launch_window_attn_fwd(ext, qkv_ptrs, out_ptrs, bias_f32, geo, C, num_heads, sh, sw, use_mask and shifted, scale,
-                               qkv.device)
-        if comm is not None:
-            out, qkv = comm.attn_forward_done(out, qkv, shifted)
-        ctx.save_for_backward(qkv, bias_f32 if bias_f32 is not None else torch.empty(0, device=qkv.device))
+        out, qkv, lse = attention_forward(ext, qkv, geo, C, num_heads, shifted, use_mask, scale, bias_f32, comm)
+        empty = torch.empty(0, device=qkv.device)
+        ctx.save_for_backward(qkv, bias_f32 if bias_f32 is not None else empty, out, lse if lse is not None else empty)
         ctx.geo, ctx.num_heads, ctx.shifted, ctx.use_mask, ctx.scale, ctx.comm = geo, num_heads, shifted, use_mask, scale, comm
         ctx.has_bias = bias_table is not None
         return out
@@ -236,23 +290,17 @@ class _WindowAttnFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         ext = _ext.load()
-        qkv, bias_f32 = ctx.saved_tensors
+        qkv, bias_f32, out, lse = ctx.saved_tensors
         geo, comm = ctx.geo, ctx.comm
         C = qkv.shape[-1] // 3
-        sh, sw = geo.shift(ctx.shifted)
         dout = dout.contiguous()
         dbias = torch.zeros_like(bias_f32) if ctx.has_bias else None
-        if comm is None:
-            dqkv = torch.empty_like(qkv)
-            qkv_ptrs, dout_ptrs, dqkv_ptrs = [qkv.data_ptr()], [dout.data_ptr()], [dqkv.data_ptr()]
-        else:
+        if comm is not None:
             staged = comm.alloc_dout(dout.shape[0], C)
             staged.copy_(dout)
-            dqkv, qkv_ptrs, dout_ptrs, dqkv_ptrs = comm.attn_backward_buffers(qkv, staged, ctx.shifted)
-        launch_window_attn_bwd(ext, qkv_ptrs, dout_ptrs, dqkv_ptrs, bias_f32 if ctx.has_bias else None, dbias, geo, C,
-                               ctx.num_heads, sh, sw, ctx.use_mask and ctx.shifted, ctx.scale, qkv.device)
-        if comm is not None:
-            dqkv = comm.attn_backward_done(dqkv, ctx.shifted)
+            dout = staged
+        dqkv = attention_backward(ext, qkv, out, dout, lse if lse.numel() else None, geo, C, ctx.num_heads, ctx.shifted,
+                                  ctx.use_mask, ctx.scale, bias_f32 if ctx.has_bias else None, dbias, comm)
         return dqkv, dbias, None, None, None, None, None, None
 
 
@@ -262,16 +310,6 @@ def window_attention(qkv: torch.Tensor, geo: WindowGeometry, num_heads: int, shi
     """``qkv``: ``[rows_local, 3C]`` -> ``[rows_local, C]``. ``comm`` supplies peer access for multi-rank layouts
     (``None``: this rank owns every window and token)."""
     fused = comm is None or getattr(comm, "fused", False)
-    if qkv.is_cuda and geo.N > MAX_KERNEL_WINDOW_TOKENS:
-        # large windows (the reference's fine-tuning configs go up to 180 x 180): PyTorch's fused attention on the
-        # gathered windows; single-owner layouts only (every window and token on this rank)
-        if comm is not None and getattr(comm, "world", 1) > 1:
-            raise NotImplementedError(f"windows of {geo.N} tokens are supported on single-owner layouts only "
-                                      f"(the peer-memory kernel holds at most {MAX_KERNEL_WINDOW_TOKENS} tokens)")
-        C = qkv.shape[-1] // 3
-        out = window_attention_reference(qkv.reshape(geo.B, geo.nWh * geo.nWw, geo.N, 3 * C), geo, num_heads, shifted,
-                                         bias_table, use_mask, scale, core=attention_core_sdpa)
-        return out.reshape(-1, C)
     if qkv.is_cuda and fused:
         return _WindowAttnFn.apply(qkv, bias_table, geo, num_heads, shifted, use_mask, scale, comm)
     if comm is not None and comm.world > 1:

@@ -42,6 +42,54 @@ def pack_conv3x3_weight_dgrad(w: torch.Tensor) -> torch.Tensor:
     return pack_conv3x3_weight(w.flip(2, 3).transpose(0, 1))
 
 
+# Packed operands are functions of the bf16 working copy of a weight, which changes once per optimizer step. They are
+# cached per parameter and rebuilt when the parameter's version counter (bumped by the in-place optimizer update of the
+# master, or by a checkpoint load) or the working copy's address (arena rebinding) has moved.
+_PACK_CACHE = {}
+
+
+def _packed(weight, w16, kind, builder):
+    import weakref
+
+    key = (id(weight), kind)
+    stamp = (weight._version, w16.data_ptr(), PACK_EPOCH[0])
+    hit = _PACK_CACHE.get(key)
+    if hit is not None and hit[0] == stamp and hit[2]() is weight:
+        return hit[1]
+    val = builder(w16)
+    _PACK_CACHE[key] = (stamp, val, weakref.ref(weight))
+    return val
+
+
+PACK_EPOCH = [0]      # bumped by the optimizers after every step (the fused kernels write the working copy directly)
+
+
+def invalidate_packed_weights() -> None:
+    PACK_EPOCH[0] += 1
+
+
+_SCRATCH = {}
+
+
+def _zero_scratch(device, shape, tag):
+    """Persistent fp32 staging that is handed out zeroed and comes back zeroed (its consumer clears it behind the
+    read), so that no fill kernel runs per use."""
+    key = (torch.device(device).index, tuple(shape), tag)
+    buf = _SCRATCH.get(key)
+    if buf is None:
+        buf = torch.zeros(*shape, device=device, dtype=torch.float32)
+        _SCRATCH[key] = buf
+    return buf
+
+
+def _arena_grad(p):
+    """The parameter's fp32 gradient view in the flat arena (accumulated into in place), or None."""
+    g = getattr(p, "grad", None)
+    if g is not None and g.is_cuda and g.dtype == torch.float32 and g.is_contiguous() and getattr(p, "bf16", None) is not None:
+        return g
+    return None
+
+
 class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, stride, dom):
@@ -52,7 +100,7 @@ class _Conv3x3Fn(torch.autograd.Function):
         y = torch.empty(B, Ho, Wo, Cout, device=x.device, dtype=torch.bfloat16)
         w16 = weight.bf16 if getattr(weight, "bf16", None) is not None else weight.detach().to(torch.bfloat16)
         b16 = bias.bf16 if getattr(bias, "bf16", None) is not None else bias.detach().to(torch.bfloat16)
-        wp = pack_conv3x3_weight(w16)
+        wp = _packed(weight, w16, "fwd", pack_conv3x3_weight)
         multi = dom is not None and dom.world > 1
         lo, hi = dom.exchange_rows(x) if multi else (None, None)
         ext.conv3x3_fwd(x, wp, y, stride, F.EPI_BIAS, b16, None, status_word(x.device), lo, hi)
@@ -70,21 +118,33 @@ class _Conv3x3Fn(torch.autograd.Function):
         B, H, W, Cin = x.shape
         Cout = weight.shape[0]
         # ---- weight / bias gradients (fp32); the halo rows received in forward serve the boundary taps
-        dw9 = torch.zeros(9, Cout, Cin, device=x.device, dtype=torch.float32)
-        ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device), lo, hi)
-        dw = dw9.view(3, 3, Cout, Cin).permute(2, 3, 0, 1)
-        db = torch.zeros(Cout, device=x.device, dtype=torch.float32)
-        ext.colsum(dy.view(-1, Cout), db)
+        gw, gb = _arena_grad(weight), _arena_grad(bias)
+        if gw is not None:
+            # tap-major staging [9, Cout, Cin] (persistent, self-cleaning) folded into the arena's (Cout, Cin, 3, 3) view
+            dw9 = _zero_scratch(x.device, (9, Cout, Cin), "conv3x3")
+            ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device), lo, hi)
+            ext.strided_add(dw9, gw, 1, Cin * 9, 9, True)
+            dw = None
+        else:
+            dw9 = torch.zeros(9, Cout, Cin, device=x.device, dtype=torch.float32)
+            ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device), lo, hi)
+            dw = dw9.view(3, 3, Cout, Cin).permute(2, 3, 0, 1)
+        if gb is not None:
+            ext.colsum(dy.view(-1, Cout), gb)
+            db = None
+        else:
+            db = torch.zeros(Cout, device=x.device, dtype=torch.float32)
+            ext.colsum(dy.view(-1, Cout), db)
         # ---- input gradient
         dx = None
         if ctx.needs_input_grad[0]:
             if stride == 1:
                 dx = torch.empty_like(x)
-                wf = pack_conv3x3_weight_dgrad(w16)
+                wf = _packed(weight, w16, "dgrad", pack_conv3x3_weight_dgrad)
                 glo, ghi = dom.exchange_rows(dy) if multi else (None, None)
                 ext.conv3x3_fwd(dy, wf, dx, 1, 0, None, None, status_word(x.device), glo, ghi)
             else:
-                dx = _conv3x3_s2_dgrad(dy, w16, H, W, dom)
+                dx = _conv3x3_s2_dgrad(dy, w16, H, W, dom, weight)
         return dx, dw, db, None, None
 
 
@@ -95,12 +155,13 @@ def _wgrad_split(B, H, W, stride, Cout, Cin):
     return max(1, min(kblocks, (148 + tiles - 1) // tiles))
 
 
-def _conv3x3_s2_dgrad(dy, w16, H, W, dom):
+def _conv3x3_s2_dgrad(dy, w16, H, W, dom, weight=None):
     """Input gradient of the stride-2 convolution: dcol = dy @ W (tap-major columns) on the tcgen05 GEMM,
     then one gather kernel over the (at most four) taps that reach each input pixel."""
     B, Ho, Wo, Cout = dy.shape
     Cin = w16.shape[1]
-    wk = w16.permute(0, 2, 3, 1).reshape(Cout, 9 * Cin).contiguous()          # [Cout, (tap, ci)]
+    build = lambda w: w.permute(0, 2, 3, 1).reshape(Cout, 9 * Cin).contiguous()          # [Cout, (tap, ci)]
+    wk = _packed(weight, w16, "s2dgrad", build) if weight is not None else build(w16)
     dcol = gemm(dy.view(-1, Cout), wk, b_mn=True).view(B, Ho, Wo, 9, Cin)     # dcol[p, tap, ci]
     ext = _ext.load()
     if dom is not None and dom.world > 1:
@@ -141,35 +202,48 @@ class _ConvT2x2Fn(torch.autograd.Function):
         Cout = weight.shape[1]
         w16 = weight.bf16 if getattr(weight, "bf16", None) is not None else weight.detach().to(torch.bfloat16)
         b16 = bias.bf16 if getattr(bias, "bf16", None) is not None else bias.detach().to(torch.bfloat16)
-        wt = w16.permute(2, 3, 1, 0).reshape(4 * Cout, Cin).contiguous()       # [(dy, dx, co), ci]
+        wt = _packed(weight, w16, "convT", lambda w: w.permute(2, 3, 1, 0).reshape(4 * Cout, Cin).contiguous())   # [(dy, dx, co), ci]
+        b4 = _packed(bias, b16, "convT_bias", lambda b: b.repeat(4))
         y = torch.empty(B, 2 * H, 2 * W, Cout, device=x.device, dtype=torch.bfloat16)
         x2 = x.view(-1, Cin)
         bn = 128 if Cout % 128 == 0 else (64 if Cout % 64 == 0 else 0)
         if bn:
             # every BN-wide column tile lies inside one (dy, dx) phase: the epilogue stores it pixel-shuffled
             flags = F.EPI_BIAS | F.EPI_ROW_SHUFFLE
-            ext.gemm(x2, False, wt, False, y.view(-1, Cout), flags, b16.repeat(4), None, None, None, 1.0, 1, bn,
+            ext.gemm(x2, False, wt, False, y.view(-1, Cout), flags, b4, None, None, None, 1.0, 1, bn,
                      status_word(x.device), Cout, W, H, 0, [], 0, [], 0, 0, 0, 1, 1)
         else:
-            flat = gemm(x2, wt, bias=b16.repeat(4))
+            flat = gemm(x2, wt, bias=b4)
             y.copy_(flat.view(B, H, W, 2, 2, Cout).permute(0, 1, 3, 2, 4, 5).reshape(B, 2 * H, 2 * W, Cout))
         ctx.save_for_backward(x)
-        ctx.p = (wt, Cout)
+        ctx.p = (wt, Cout, weight, bias)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         ext = _ext.load()
         (x,) = ctx.saved_tensors
-        wt, Cout = ctx.p
+        wt, Cout, weight, bias = ctx.p
         B, H, W, Cin = x.shape
         # un-shuffle dy to [pixels, (dy, dx, co)] once; both products read it
         dyu = dy.view(B, H, 2, W, 2, Cout).permute(0, 1, 3, 2, 4, 5).reshape(B * H * W, 4 * Cout)
-        dwt = torch.zeros(4 * Cout, Cin, device=x.device, dtype=torch.float32)
-        wgrad_accumulate(dyu, x.view(-1, Cin), dwt)
-        dw = dwt.view(2, 2, Cout, Cin).permute(3, 2, 0, 1)
-        db = torch.zeros(Cout, device=x.device, dtype=torch.float32)
-        ext.colsum(dy.reshape(-1, Cout), db)
+        gw, gb = _arena_grad(weight), _arena_grad(bias)
+        if gw is not None:
+            dwt = _zero_scratch(x.device, (4 * Cout, Cin), "convT")
+            wgrad_accumulate(dyu, x.view(-1, Cin), dwt)
+            # [(tap), co, ci] staging -> (Cin, Cout, 2, 2) arena view
+            ext.strided_add(dwt.view(4, Cout, Cin), gw, 1, 4, Cout * 4, True)
+            dw = None
+        else:
+            dwt = torch.zeros(4 * Cout, Cin, device=x.device, dtype=torch.float32)
+            wgrad_accumulate(dyu, x.view(-1, Cin), dwt)
+            dw = dwt.view(2, 2, Cout, Cin).permute(3, 2, 0, 1)
+        if gb is not None:
+            ext.colsum(dy.reshape(-1, Cout), gb)
+            db = None
+        else:
+            db = torch.zeros(Cout, device=x.device, dtype=torch.float32)
+            ext.colsum(dy.reshape(-1, Cout), db)
         dx = gemm(dyu, wt, b_mn=True).view(B, H, W, Cin) if ctx.needs_input_grad[0] else None
         return dx, dw, db
 
@@ -187,35 +261,44 @@ class _GroupNormSiluFn(torch.autograd.Function):
         ext = _ext.load()
         B, H, W, C = x.shape
         x3 = x.view(B, H * W, C)
-        sums = torch.zeros(B, groups, 2, device=x.device, dtype=torch.float32)
-        ext.groupnorm_stats(x3, sums, groups)
-        count = float(H * W * (C // groups))
-        if dom is not None and dom.world > 1:
+        multi = dom is not None and dom.world > 1
+        count = float(H * W * (C // groups)) * (dom.world if multi else 1)
+        stats = torch.empty(B, groups, 2, device=x.device, dtype=torch.float32)
+        if multi:
+            sums = torch.zeros(B, groups, 2, device=x.device, dtype=torch.float32)
+            ext.groupnorm_stats(x3, sums, groups)
             sums = dom.all_reduce_small(sums)
-            count *= dom.world
-        mean = sums[..., 0] / count
-        var = (sums[..., 1] / count - mean * mean).clamp_min(0.0)
-        stats = torch.stack([mean, torch.rsqrt(var + GN_EPS)], dim=-1).contiguous()
+            ext.groupnorm_finalize(sums, stats, 1.0 / count, GN_EPS, False)
+        else:
+            sums = _zero_scratch(x.device, (B, groups, 2), "gn_sums")          # cleared again by the finalize kernel
+            ext.groupnorm_stats(x3, sums, groups)
+            ext.groupnorm_finalize(sums, stats, 1.0 / count, GN_EPS, True)
         g16 = gamma.bf16 if getattr(gamma, "bf16", None) is not None else gamma.detach().to(torch.bfloat16)
         b16 = beta.bf16 if getattr(beta, "bf16", None) is not None else beta.detach().to(torch.bfloat16)
         y = torch.empty_like(x)
         ext.groupnorm_silu_apply(x3, stats, g16, b16, None if residual is None else residual.view(B, H * W, C),
                                  y.view(B, H * W, C), groups)
         ctx.save_for_backward(x, stats, g16, b16)
-        ctx.p = (groups, dom, count, residual is not None)
+        ctx.p = (groups, dom, count, residual is not None, gamma, beta)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         ext = _ext.load()
         x, stats, g16, b16 = ctx.saved_tensors
-        groups, dom, count, has_res = ctx.p
+        groups, dom, count, has_res, gamma, beta = ctx.p
         B, H, W, C = x.shape
         dy = dy.contiguous()
         x3, dy3 = x.view(B, H * W, C), dy.view(B, H * W, C)
         red = torch.zeros(B, C, 2, device=x.device, dtype=torch.float32)
-        ext.groupnorm_silu_bwd_reduce(dy3, x3, stats, g16, b16, red, groups)
-        dgamma, dbeta = red[..., 1].sum(0), red[..., 0].sum(0)
+        gg, gbt = _arena_grad(gamma), _arena_grad(beta)
+        if gg is not None and gbt is not None:
+            # the affine parameters' gradients are accumulated by the reduce kernel itself
+            ext.groupnorm_silu_bwd_reduce(dy3, x3, stats, g16, b16, red, groups, gg, gbt)
+            dgamma = dbeta = None
+        else:
+            ext.groupnorm_silu_bwd_reduce(dy3, x3, stats, g16, b16, red, groups)
+            dgamma, dbeta = red[..., 1].sum(0), red[..., 0].sum(0)
         if dom is not None and dom.world > 1:
             red = dom.all_reduce_small(red)
         dx = torch.empty_like(x)

@@ -118,7 +118,7 @@ def case_attn(a):
     if a.bwd:
         if a.impl == "tc":
             fn = lambda: ext.window_attn_tc_bwd([qkv.data_ptr()], [out.data_ptr()], [dqkv.data_ptr()], table, dtable, *args,
-                                                status_word("cuda"))
+                                                status_word("cuda"), [], [])
         else:
             fn = lambda: ext.window_attn_bwd([qkv.data_ptr()], [out.data_ptr()], [dqkv.data_ptr()], table, dtable, *args)
         flops = 2.0 * rows * geo.N * C * 5

@@ -14,6 +14,12 @@ from .. import _ext
 from ..utils.flat_params import get_arena
 
 
+def _invalidate_packed():
+    from ..ops.conv import invalidate_packed_weights
+
+    invalidate_packed_weights()
+
+
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, model=None):
         params = list(params)
@@ -44,6 +50,7 @@ class FusedAdamW(torch.optim.Optimizer):
             a = self.arena
             _ext.load().adamw_step(a.master, st["exp_avg"], st["exp_avg_sq"], a.grad, a.bf16, g0["lr"], g0["betas"][0],
                                    g0["betas"][1], g0["eps"], g0["weight_decay"], st["step"], grad_scale)
+            _invalidate_packed()
             return loss
         for group in self.param_groups:
             b1, b2 = group["betas"]

@@ -95,9 +95,13 @@ class DistributedAdamW(torch.optim.Optimizer):
         scale = grad_scale / self._divisor()
         if self.fused is not None:
             self.fused.step(self, g0, scale)
-            return loss
-        for sh in self.shards:
-            self.portable_shard_step(sh, g0, scale)
+        else:
+            for sh in self.shards:
+                self.portable_shard_step(sh, g0, scale)
+        if self.arena.master.is_cuda:
+            from ..ops.conv import invalidate_packed_weights
+
+            invalidate_packed_weights()      # operands packed from the bf16 working copy are stale now
         return loss
 
     def portable_shard_step(self, sh: "_Shard", g0, scale):

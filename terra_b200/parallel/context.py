@@ -53,21 +53,36 @@ class DomainComm:
         xn = (xg - mean[..., None]) * torch.rsqrt(var + eps)[..., None]
         return xn.reshape(Bn, Cn, H, W) * weight[None, :, None, None] + bias[None, :, None, None]
 
-    # ---- CUDA (portable-collective version; the peer-memory halo path replaces these where enabled)
+    # ---- CUDA: over peer memory when ``peer`` is attached (terra_b200.parallel.nvlink.PeerDomain), else collectives
+    peer = None
+
     def all_reduce_small(self, t):
+        if self.peer is not None and t.is_cuda:
+            return self.peer.all_reduce_small(t)
         return C.all_reduce_(t.clone(), self.group)
 
     def exchange_rows(self, x):
         """Boundary rows of the neighbours' stripes: ``(row above, row below)`` as ``[B, 1, W, C]`` tensors, ``None``
         at the global edges (the convolution then sees zeros there: non-periodic)."""
-        top = x[:, :1].contiguous()
-        bot = x[:, -1:].contiguous()
-        recv_prev, recv_next = C._exchange(top, bot, self.prev, self.next, self.group)
+        top = x[:, :1]
+        bot = x[:, -1:]
+        if self.peer is not None and x.is_cuda:
+            return self.peer.exchange_rows(top, bot)
+        recv_prev, recv_next = C._exchange(top.contiguous(), bot.contiguous(), self.prev, self.next, self.group)
         return recv_prev, recv_next
 
     def fold_halo_grad(self, dxp, H, W):
         """dxp: [B, H+2, W+2, C] gradient of the zero/halo padded input -> gradient of the local rows, with the
         halo rows' gradients sent back to their owners."""
+        if self.peer is not None and dxp.is_cuda:
+            # my padded row 0 is the previous rank's last row, my padded row H + 1 the next rank's first row
+            from_prev, from_next = self.peer.exchange_rows(dxp[:, 0:1, 1:W + 1], dxp[:, H + 1:H + 2, 1:W + 1])
+            gx = dxp[:, 1:H + 1, 1:W + 1].contiguous()
+            if from_prev is not None:
+                gx[:, 0:1] += from_prev
+            if from_next is not None:
+                gx[:, H - 1:H] += from_next
+            return gx
         g = dxp[:, :, 1:W + 1].permute(0, 3, 1, 2).contiguous()
         gx = C._HaloRows.backward(_Ctx((1, self.prev, self.next, self.group)), g)[0]
         return gx.permute(0, 2, 3, 1)

@@ -193,6 +193,10 @@ class FusedAttnComm:
     def alloc_dout(self, rows, C):
         return self.arena.alloc((self._rows(rows), C), torch.bfloat16)[:rows]
 
+    def alloc_f32(self, rows, cols):
+        """Per-row fp32 side data that peers read or write (log-sum-exp, row dots of large-window attention)."""
+        return self.arena.alloc((self._rows(rows), cols), torch.float32)[:rows]
+
     def attn_backward_buffers(self, qkv, do, shifted):
         rows = qkv.shape[0]
         dqkv = self.arena.alloc((self._rows(rows), qkv.shape[1]), torch.bfloat16)[:rows]
@@ -204,6 +208,64 @@ class FusedAttnComm:
         if self._needs_peers(shifted):
             self.arena.barrier()
         return dqkv
+
+
+class PeerDomain:
+    """Row-stripe (domain-parallel) communication of the sampling blocks over peer memory: the halo rows of the
+    3 x 3 convolutions are pushed into the neighbours' receive buffers by one kernel (``halo_push``), and the small
+    all-reduces of the distributed GroupNorm (statistics forward, two sums backward) are one single-block kernel
+    (``peer_allreduce_small``). No NCCL call is left in the convolution stage (reference:
+    credit/domain_parallel/halo_exchange.py:18-157, layers.py:18-84)."""
+
+    FROM_PREV, FROM_NEXT, TICKET, SMALL_FLAGS = 256, 257, 258, 272      # words of the arena's signal pad
+    SMALL_CAPACITY = 8192
+
+    def __init__(self, arena: SymmetricArena):
+        self.arena = arena
+        self.rank, self.world = arena.rank, arena.world
+        self.slots = arena.alloc((2, self.world, self.SMALL_CAPACITY), torch.float32, persistent=True)
+        self.halo_epoch = 0
+        self.small_epoch = 0
+
+    def _word(self, rank: int, index: int) -> int:
+        return self.arena.base_ptrs[rank] + 4 * index
+
+    def exchange_rows(self, top: torch.Tensor, bot: torch.Tensor):
+        """Send ``top`` (this stripe's first row) to the previous rank and ``bot`` (its last row) to the next one;
+        returns ``(row above, row below)`` as tensors in this rank's symmetric memory (``None`` at the grid edges).
+        Every rank of the group calls this the same number of times per step."""
+        ext = _ext.load()
+        top, bot = top.contiguous(), bot.contiguous()
+        lo = self.arena.alloc(tuple(top.shape), top.dtype)       # receives the previous rank's last row
+        hi = self.arena.alloc(tuple(bot.shape), bot.dtype)       # receives the next rank's first row
+        self.halo_epoch += 1
+        has_prev, has_next = self.rank > 0, self.rank < self.world - 1
+        nbytes = top.numel() * top.element_size()
+        ext.halo_push(
+            top.data_ptr(), bot.data_ptr(),
+            self.arena.peer_ptrs(hi)[self.rank - 1] if has_prev else 0,      # my first row is the previous rank's row below
+            self.arena.peer_ptrs(lo)[self.rank + 1] if has_next else 0,
+            nbytes,
+            self._word(self.rank - 1, self.FROM_NEXT) if has_prev else 0,
+            self._word(self.rank + 1, self.FROM_PREV) if has_next else 0,
+            self._word(self.rank, self.FROM_PREV) if has_prev else 0,
+            self._word(self.rank, self.FROM_NEXT) if has_next else 0,
+            self.halo_epoch, self._word(self.rank, self.TICKET), status_word(self.arena.buf.device), BARRIER_SPIN_LIMIT)
+        return (lo if has_prev else None), (hi if has_next else None)
+
+    def all_reduce_small(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum of a small fp32 tensor over the group (a new tensor)."""
+        ext = _ext.load()
+        flat = t.contiguous().view(-1)
+        if flat.numel() > self.SMALL_CAPACITY:
+            raise ValueError(f"peer all-reduce holds at most {self.SMALL_CAPACITY} values, got {flat.numel()}")
+        out = torch.empty_like(flat)
+        self.small_epoch += 1
+        ext.peer_allreduce_small(self.arena.peer_ptrs(self.slots),
+                                 [self._word(r, self.SMALL_FLAGS) for r in range(self.world)], flat, out, self.rank,
+                                 self.SMALL_CAPACITY, self.small_epoch, status_word(self.arena.buf.device),
+                                 BARRIER_SPIN_LIMIT)
+        return out.view(t.shape)
 
 
 class FusedDistAdamW:
@@ -249,13 +311,21 @@ def attach(model, optimizer, manager) -> None:
         if gb <= 0:
             rows = max(len(w) for w in pctx.windows_of) * pctx.shardN * pctx.B
             C = model.embedding_dim // pctx.tp
-            per_layer = rows * C * 2 * (3 + 1 + 1 + 3)            # qkv, o, do, dqkv
+            per_layer = rows * C * 2 * (3 + 1 + 1 + 3) + rows * 64 * 4 * 2   # qkv, o, do, dqkv; lse / row dots (large windows)
             nbytes = int(per_layer * model.num_layers * 1.25) + (64 << 20)
         else:
             nbytes = int(gb * (1 << 30))
         arena = SymmetricArena(manager.xfmr_tp_param_group, nbytes, device)
         pctx.fused_comm = FusedAttnComm(arena, pctx.n_wg, pctx.sp)
         pctx.attn_arena = arena
+    # ---- sampling blocks: halo rows and GroupNorm sums over peer memory
+    if manager.wp_size > 1 and getattr(model, "has_sampling", False) and os.environ.get("TERRA_PEER_HALO", "1") != "0":
+        a = model
+        w_tok = a.patches_resolution[1]
+        row = pctx.B * w_tok * model.embedding_dim * 4          # one fp32 boundary row at patch resolution
+        nbytes = 48 * row + 2 * COMM_MAX_PEERS * PeerDomain.SMALL_CAPACITY * 4 + (16 << 20)
+        pctx.dom_arena = SymmetricArena(manager.window_parallel_group, nbytes, device)
+        pctx.dom.peer = PeerDomain(pctx.dom_arena)
     # ---- tensor-parallel MLP: fc1 / fc2 with the all-gather / reduce-scatter fused into the GEMMs
     if pctx.tp > 1 and os.environ.get("TERRA_TP_FUSED", "1") != "0":
         from ..ops.tp_fused import TpFusedComm
@@ -285,7 +355,7 @@ def attach(model, optimizer, manager) -> None:
 
 
 def reset_step_arenas(model) -> None:
-    for name in ("attn_arena", "tp_arena"):
+    for name in ("attn_arena", "tp_arena", "dom_arena"):
         arena = getattr(model.pctx, name, None)
         if arena is not None:
             arena.reset()

@@ -54,7 +54,7 @@ def one_step_train(task_type, model_type, model, engine, optimizer, required_ten
         ev0.record()
 
     pctx = getattr(model.module if hasattr(model, "module") else model, "pctx", None)
-    for arena_name in ("attn_arena", "tp_arena"):
+    for arena_name in ("attn_arena", "tp_arena", "dom_arena"):
         arena = getattr(pctx, arena_name, None)
         if arena is not None:
             arena.reset()      # per-step symmetric buffers of the previous step are dead

@@ -150,6 +150,9 @@ class ParamArena:
         """Refresh the bf16 working copy from the fp32 masters (after init or a checkpoint load)."""
         if self.bf16 is not None:
             self.bf16.copy_(self.master)
+            from ..ops.conv import invalidate_packed_weights
+
+            invalidate_packed_weights()
 
     def zero_grad(self) -> None:
         self.grad.zero_()

@@ -50,6 +50,9 @@ SHAPE_KEYS = ("height", "width", "window_size", "depths", "num_heads", "num_laye
     (2, {"xfmr_wp_topo": "(1, 1)", "tensor_parallel_size": 2}),
     # 3 x 7 windows: the two tensor-parallel ranks hold 11 and 10 windows (zero-padded symmetric buffers)
     (2, {"xfmr_wp_topo": "(1, 1)", "tensor_parallel_size": 2, "height": 192, "width": 448}),
+    # 256-token windows (tensor-core attention with K/V streamed from the peers): window parallel and sequence parallel
+    (2, {"xfmr_wp_topo": "(2, 1)", "window_size": 16}),
+    (2, {"xfmr_wp_topo": "(1, 1)", "xfmr_sp_size": 2, "window_size": 16}),
     (4, {"xfmr_wp_topo": "(4, 1)"}),
     (4, {"xfmr_wp_topo": "(2, 1)", "xfmr_sp_size": 2}),
     (4, {"xfmr_wp_topo": "(1, 1)", "xfmr_sp_size": 2, "tensor_parallel_size": 2}),

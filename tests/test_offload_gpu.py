@@ -54,8 +54,11 @@ def test_boundary_offload_matches_recompute_with_lower_peak_memory():
     assert abs(recompute[0] - plain[0]) <= 1e-5 * abs(plain[0])
     assert abs(offload[0] - recompute[0]) <= 1e-5 * abs(recompute[0])
     denom = recompute[1].norm().item() + 1e-12
-    assert (offload[1] - recompute[1]).norm().item() <= 1e-3 * denom      # split-K atomics reorder fp32 sums slightly
-    assert (plain[1] - recompute[1]).norm().item() <= 1e-3 * denom
+    # Two runs of the same step are not bit-identical: fp32 atomics (GroupNorm statistics, split-K weight gradients) add
+    # in another order, which now and then flips the bf16 rounding of an activation; measured 0.7 % of the gradient norm.
+    # A boundary restored wrongly, or a segment recomputed from the wrong input, would be off by order one.
+    assert (offload[1] - recompute[1]).norm().item() <= 3e-2 * denom
+    assert (plain[1] - recompute[1]).norm().item() <= 3e-2 * denom
     # memory: checkpointing keeps one boundary per segment instead of every block's saved tensors; parking the
     # boundaries on the host removes those too
     assert recompute[2] < 0.8 * plain[2], (recompute[2], plain[2])
