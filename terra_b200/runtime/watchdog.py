@@ -42,11 +42,14 @@ class RankMonitor:
 
     def beat(self, step: int) -> None:
         """Publish "alive at ``step``". Call between steps, with no kernel or collective of the step in flight."""
+        self._last_step = int(step)
         self.store.set(self._key(self.rank), f"{step}:{self.clock():.3f}")
 
     def leave(self) -> None:
-        """Announce an orderly exit so that the peers fail fast instead of waiting for the staleness limit."""
-        self.store.set(self._key(self.rank), "left")
+        """Announce an orderly exit so that the peers fail fast instead of waiting for the staleness limit. The last
+        step this rank completed goes with it: a peer that is still finishing that same step (ranks end a run at
+        slightly different times) must not take the exit for a failure."""
+        self.store.set(self._key(self.rank), f"left:{getattr(self, '_last_step', -1)}")
 
     def read(self, r: int) -> Optional[str]:
         try:
@@ -64,8 +67,10 @@ class RankMonitor:
             if r == self.rank:
                 continue
             v = self.read(r)
-            if v == "left":
-                lost.append(r)
+            if v is not None and v.startswith("left"):
+                left_after = int(v.split(":")[1]) if ":" in v else -1
+                if min_step is None or left_after < min_step:
+                    lost.append(r)
                 continue
             if v is None:
                 first = self._last_seen.setdefault(r, now)

@@ -35,6 +35,23 @@ def test_rank_monitor_detects_stale_and_left_peers():
     assert mons[0].lost_peers() == [1, 2]
 
 
+def test_rank_that_finished_the_same_step_and_left_is_not_a_failure():
+    """Ranks end a run at slightly different times: a peer that left after completing step s is lost only to a rank
+    that expects it at a later step."""
+    import torch.distributed as dist
+
+    from terra_b200.runtime.watchdog import RankMonitor
+
+    store = dist.HashStore()
+    a, b = RankMonitor(store, 0, 2, stale_after_s=60.0), RankMonitor(store, 1, 2, stale_after_s=60.0)
+    a.beat(3)
+    b.beat(3)
+    b.leave()                                   # rank 1 finished its last step (3) and exits
+    assert a.lost_peers(min_step=3) == []       # rank 0 is still wrapping up step 3: fine
+    assert a.lost_peers(min_step=4) == [1]      # it would be missing from step 4
+    assert a.lost_peers() == [1]
+
+
 def test_rank_that_never_joins_is_reported_after_the_limit():
     import torch.distributed as dist
 

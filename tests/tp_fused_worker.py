@@ -1,6 +1,6 @@
 """Worker of the fused tensor-parallel tests (torch.distributed.run, one rank per GPU): all-gather -> GEMM,
 GEMM -> reduce-scatter and the sequence-sharded MLP (forward and backward) against plain PyTorch collectives + fp32
-matmuls, and a timing of the fused kernels against the NCCL + GEMM sequence."""
+matmuls. (Timings of the same kernels: ``python -m terra_b200.ops.microbench_comm ag_gemm|gemm_rs``.)"""
 import json
 import os
 import sys
@@ -13,20 +13,17 @@ import torch.distributed as dist  # noqa: E402
 
 
 def main():
-    timing = len(sys.argv) > 1 and sys.argv[1] == "time"
     from terra_b200.distributed import init_distributed
     from terra_b200.ops.gemm import check_status, gemm
     from terra_b200.ops.tp_fused import TpFusedComm, tp_mlp
     from terra_b200.parallel.nvlink import SymmetricArena
 
     rank, world, dev = init_distributed(timeout_s=120)     # a rank that fails must not keep the others waiting long
-    arena = SymmetricArena(dist.group.WORLD, 6 << 30 if timing else 256 << 20, dev)
+    arena = SymmetricArena(dist.group.WORLD, 256 << 20, dev)
     comm = TpFusedComm(arena)
     x_sym = None
     torch.manual_seed(5)                      # same weights and global activations on every rank
-    rows, C, F = (17408, 384, 1536) if timing else (328, 256, 512)    # rows per rank; 328 is not a tile multiple
-    if timing and len(sys.argv) > 2:
-        rows = int(sys.argv[2])
+    rows, C, F = 328, 256, 512    # rows per rank; 328 is not a tile multiple
     Fs = F // world
     x_full = (torch.randn(rows * world, C, device=dev) * 0.5).to(torch.bfloat16)
     w1 = (torch.randn(F, C, device=dev) * 0.05).to(torch.bfloat16)
@@ -70,52 +67,6 @@ def main():
     res["mlp_dw2"] = rel(p[2].grad, pf[2].grad[:, rank * Fs:(rank + 1) * Fs])
     check_status(dev)
 
-    if timing:
-        def timed(fn, iters=10):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize(); dist.barrier()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            for _ in range(iters):
-                fn()
-            e.record(); torch.cuda.synchronize()
-            t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
-
-        gathered = torch.empty(rows * world, C, dtype=torch.bfloat16, device=dev)
-        scat = torch.empty(rows, C, dtype=torch.bfloat16, device=dev)
-
-        def nccl_ag_gemm():
-            dist.all_gather_into_tensor(gathered, x)
-            return gemm(gathered, w1s, bias=b1s)
-
-        def nccl_gemm_rs():
-            part = gemm(hs, w2s)
-            dist.reduce_scatter_tensor(scat, part)
-            return scat
-
-        def fused_ag():
-            arena.reset()
-            return comm.ag_gemm(x_sym, w1s, bias=b1s, via_copy_engine=False)
-
-        def fused_ag_ce():
-            arena.reset()
-            return comm.ag_gemm(x_sym, w1s, bias=b1s, via_copy_engine=True)
-
-        def fused_rs_exact():
-            arena.reset()
-            return comm.gemm_rs(hs, w2s, exact=True)
-
-        def fused_rs():
-            arena.reset()
-            return comm.gemm_rs(hs, w2s)
-
-        res["ms"] = {"nccl_ag_then_gemm": timed(nccl_ag_gemm), "fused_ag_gemm_direct": timed(fused_ag), "fused_ag_gemm_copy_engine": timed(fused_ag_ce),
-                     "gemm_then_nccl_rs": timed(nccl_gemm_rs), "fused_gemm_rs": timed(fused_rs), "fused_gemm_rs_fp32_atomics": timed(fused_rs_exact),
-                     "local_gemm_same_shape": timed(lambda: gemm(gathered, w1s, bias=b1s)),
-                     "shape": {"rows_per_rank": rows, "C": C, "F": F, "ranks": world}}
     if rank == 0:
         print("RESULT " + json.dumps(res), flush=True)
     dist.barrier()
