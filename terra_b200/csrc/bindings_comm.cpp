@@ -92,6 +92,22 @@ void gather_shards_async(int64_t stream, int64_t dst, const std::vector<int64_t>
   TORCH_CHECK(rc == 0, "gather_shards_async failed with code ", rc);
 }
 
+void peer_gather_indexed(torch::Tensor& dst, const std::vector<int64_t>& src_ptrs, const torch::Tensor& src_slot,
+                         const torch::Tensor& src_row) {
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.dim() == 2, "peer_gather_indexed: dst [rows, cols] contiguous");
+  TORCH_CHECK(src_slot.scalar_type() == torch::kInt32 && src_row.scalar_type() == torch::kInt32 && src_slot.is_cuda() &&
+                  src_row.is_cuda() && src_slot.numel() == dst.size(0) && src_row.numel() == dst.size(0),
+              "peer_gather_indexed: int32 device index arrays, one entry per destination row");
+  const c10::cuda::CUDAGuard guard(dst.device());
+  std::vector<const void*> p;
+  for (auto v : src_ptrs) p.push_back(reinterpret_cast<const void*>(v));
+  tb::note_launch();
+  TORCH_CHECK(tb::peer_gather_indexed(dst.data_ptr(), p.data(), static_cast<int>(p.size()), src_slot.data_ptr<int>(),
+                                      src_row.data_ptr<int>(), dst.size(0), dst.size(1) * dst.element_size(),
+                                      cur_stream()) == 0,
+              "peer_gather_indexed launch failed");
+}
+
 // All addresses are raw device addresses (0: absent).
 void halo_push(int64_t send_prev, int64_t send_next, int64_t dst_prev, int64_t dst_next, int64_t nbytes, int64_t flag_at_prev,
                int64_t flag_at_next, int64_t my_flag_from_prev, int64_t my_flag_from_next, int64_t epoch, int64_t ticket,
@@ -159,6 +175,7 @@ void stream_write_value(int64_t stream, int64_t addr, int64_t value) {
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
+  m.def("peer_gather_indexed", &peer_gather_indexed);
   m.def("halo_push", &halo_push);
   m.def("peer_allreduce_small", &peer_allreduce_small);
   m.def("stream_wait_value", &stream_wait_value);

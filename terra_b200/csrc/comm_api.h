@@ -42,6 +42,10 @@ int stream_write32(cudaStream_t stream, void* addr, unsigned int value);
 int gather_shards_async(cudaStream_t stream, void* dst, const void* const* src, int num_peers, int my_rank, long long rows,
                         size_t row_bytes, int chunks, long long chunk_rows, const unsigned int* signals, unsigned int* ready,
                         unsigned int epoch, int include_self = 0);
+// dst[i] = row src_row[i] of src_peers[src_slot[i]] (rows of row_bytes, a multiple of 16; index arrays on the device).
+int peer_gather_indexed(void* dst, const void* const* src_peers, int num_peers, const int* src_slot, const int* src_row,
+                        long long rows, long long row_bytes, cudaStream_t stream);
+
 // Halo exchange of two boundary rows with the row-stripe neighbours (see comm_kernels.cu). Null pointers: no neighbour
 // on that side. Buffers and flag words live in symmetric memory; `epoch` counts the exchanges of the group.
 struct HaloPushArgs {

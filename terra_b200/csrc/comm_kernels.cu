@@ -53,6 +53,9 @@ __global__ void __launch_bounds__(256) peer_copy_rows_kernel(uint8_t* __restrict
 struct PeerPtrs {
   const float* p[COMM_MAX_PEERS];
 };
+struct GatherPeers {
+  const uint4* p[COMM_MAX_PEERS];
+};
 __global__ void peer_sum_small_kernel(float* dst, const __grid_constant__ PeerPtrs srcs, int num_peers, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
@@ -102,6 +105,23 @@ __global__ void peer_signal_kernel(const __grid_constant__ PadPtrs pads, int my_
   if (t < num_peers) {
     __threadfence_system();
     asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(pads.p[t] + slot_base + my_rank) : "memory");
+  }
+}
+
+// Row gather over peer memory: dst row i = row src_row[i] of the buffer of GPU src_slot[i] (this GPU's own buffer
+// included). One 16-byte vector per thread and step; a row's vectors are handled by neighbouring threads. The general
+// form of the stripe <-> window relayout (an all-to-all-v in which every token has exactly one source).
+__global__ void __launch_bounds__(256) peer_gather_indexed_kernel(uint4* __restrict__ dst, const __grid_constant__ GatherPeers peers,
+                                                                  const int* __restrict__ src_slot,
+                                                                  const int* __restrict__ src_row, long long rows,
+                                                                  int vec_per_row) {
+  const long long total = rows * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int v = static_cast<int>(i - r * vec_per_row);
+    const uint4* src = peers.p[src_slot[r]] + static_cast<long long>(src_row[r]) * vec_per_row + v;
+    dst[i] = *src;
   }
 }
 
@@ -186,6 +206,20 @@ __global__ void __launch_bounds__(512) peer_allreduce_small_kernel(const __grid_
 }
 
 }  // namespace
+
+int peer_gather_indexed(void* dst, const void* const* src_peers, int num_peers, const int* src_slot, const int* src_row,
+                        long long rows, long long row_bytes, cudaStream_t stream) {
+  if (num_peers < 1 || num_peers > COMM_MAX_PEERS || row_bytes % 16 != 0) return -1;
+  if (rows <= 0) return 0;
+  GatherPeers gp;
+  for (int i = 0; i < num_peers; ++i) gp.p[i] = static_cast<const uint4*>(src_peers[i]);
+  const long long total = rows * (row_bytes / 16);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  peer_gather_indexed_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<uint4*>(dst), gp, src_slot, src_row, rows,
+                                                                          static_cast<int>(row_bytes / 16));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 int halo_push(const HaloPushArgs& a, cudaStream_t stream) {
   if (a.nvec <= 0 || a.ticket == nullptr) return -1;

@@ -100,12 +100,32 @@ __device__ __forceinline__ void tc_cp_commit() { asm volatile("cp.async.commit_g
 template <int N>
 __device__ __forceinline__ void tc_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Explicit shared-memory loads by 32-bit address: through a generic pointer the compiler emits generic loads, which wait
+// on the long scoreboard like global memory.
+__device__ __forceinline__ float tc_lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ int4 tc_lds_i4(uint32_t addr) {
+  int4 v;
+  asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+__device__ __forceinline__ void tc_sts_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void tc_red_f32(uint32_t addr, float v) {
+  asm volatile("red.shared.add.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
 // Cycle counters of the roles, summed over CTAs and launches since the last reset (window_attn_tc_stalls):
 // [0] producer span, [1] of it waiting for a free buffer, [2] MMA thread span, [3] of it waiting for operands,
 // [4] of it waiting for probabilities, [5] softmax thread span, [6] of it waiting for scores, [7] for outputs.
 __device__ unsigned long long g_tc_stalls[16];   // [8..13] softmax thread: item prologue, score load, math, store + signal, output fold, row store
 
-template <int HD>
+template <int HD, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __grid_constant__ WindowAttnArgs a,
                                                                      const __grid_constant__ TcPlan pl,
                                                                      KernelStatus* status, int bias_in_smem) {
@@ -413,15 +433,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
         cur_hg = it.hg;
         if (!ok) break;
       }
-      const int sl = pl.pair ? (r >> 6) : 0;
+      const int sl = PAIR ? (r >> 6) : 0;
       const int flat = a.win_start[a.my_wg] + it.w0 + sl;
-      const int tok = pl.pair ? (r & 63) : pl.q0 + it.qb * TC_ROWS + r;
-      const bool active = pl.pair ? (sl < it.nwin && tok < N) : (tok < pl.q1);
-      const int fl = (pl.pair && sl >= it.nwin) ? flat - sl : flat;   // clamp to an existing window
+      const int tok = PAIR ? (r & 63) : pl.q0 + it.qb * TC_ROWS + r;
+      const bool active = PAIR ? (sl < it.nwin && tok < N) : (tok < pl.q1);
+      const int fl = (PAIR && sl >= it.nwin) ? flat - sl : flat;   // clamp to an existing window
       const int ii = fl / a.nWw, jj = fl % a.nWw;
       const int tk = min(tok, N - 1);
       int ti, tj;
-      if (pl.pair) {
+      if (PAIR) {
         ti = tok_ij[tk] >> 16;
         tj = tok_ij[tk] & 0xffff;
       } else {
@@ -431,11 +451,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
       const Home home = locate_ij(a, geo, it.b, ii, jj, ti, tj);
       const int row_term = ti * (2 * a.ww - 1) + tj + rel0;
       const bool general = a.use_mask && ((a.sh > 0 && ii == a.nWh - 1) || (a.sw > 0 && jj == a.nWw - 1));
-      const bool store_row = active && (!pl.pair || (tok >= pl.q0 && tok < pl.q1));
+      const bool store_row = active && (!PAIR || (tok >= pl.q0 && tok < pl.q1));
       // Small windows: the keys of a slot are the window's own tokens. Their bias terms are static; their mask regions
       // matter only in the windows of the last row / column of a shifted frame, where every row publishes its region.
       bool tile_general = false;
-      if (pl.pair && a.use_mask) {
+      if (PAIR && a.use_mask) {
         const int fa = a.win_start[a.my_wg] + it.w0, fb = fa + (it.nwin > 1 ? 1 : 0);
         tile_general = (a.sh > 0 && (fa / a.nWw == a.nWh - 1 || fb / a.nWw == a.nWh - 1)) ||
                        (a.sw > 0 && (fa % a.nWw == a.nWw - 1 || fb % a.nWw == a.nWw - 1));
@@ -445,20 +465,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
         rows_barrier();
         if (!ok) break;
       }
-      float m_run[HPG], l_run[HPG], oacc[G];
+      // Small windows see all their keys in one step, so a head's output is final after its single product and goes
+      // straight to memory; large windows accumulate over the key slots with the online-softmax rescaling.
+      float m_run[HPG], l_run[HPG], oacc[PAIR ? 1 : G];
 #pragma unroll
       for (int h = 0; h < HPG; ++h) {
         m_run[h] = TC_NEG;
         l_run[h] = 0.f;
       }
 #pragma unroll
-      for (int c = 0; c < G; ++c) oacc[c] = 0.f;
+      for (int c = 0; c < (PAIR ? 1 : G); ++c) oacc[c] = 0.f;
+      __nv_bfloat16* const out_row =
+          static_cast<__nv_bfloat16*>(a.out[home.slot]) + home.row * a.C + it.hg * G;
       float alpha_prev = 0.f;
       int h_prev = 0;
       t_seg[0] += clock64() - tq;
 
       auto fold_output = [&](uint32_t step, int h, float alpha) {
-        // O of `step` (head h) is complete in tensor memory: acc = acc * alpha + O
+        // O of `step` (head h) is complete in tensor memory. Large windows: acc = acc * alpha + O (alpha: the rescaling
+        // of that step). Small windows: alpha is 1 / (sum of the row's numerators) and the normalised row is stored.
         const uint32_t buf = step & 1u;
         const long long w0 = clock64();
         if (ok) ok = mbar_wait(&bars->o_full[buf], (step >> 1) & 1u, abort_flag, status, 0x3300u + buf);
@@ -471,12 +496,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
           uint32_t v[32];
           tmem_ld_32x32(tmem_base + Cfg::O_COL + buf * HD + c0 + lane_base, v);
           tmem_ld_wait();
+          if (PAIR) {
+            if (store_row) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if (c0 + c < HD) {
+              for (int c = 0; c < 32 && c0 + c < HD; c += 8)
+                *reinterpret_cast<uint4*>(out_row + h * HD + c0 + c) = make_uint4(
+                    pack_bf16x2(__uint_as_float(v[c]) * alpha, __uint_as_float(v[c + 1]) * alpha),
+                    pack_bf16x2(__uint_as_float(v[c + 2]) * alpha, __uint_as_float(v[c + 3]) * alpha),
+                    pack_bf16x2(__uint_as_float(v[c + 4]) * alpha, __uint_as_float(v[c + 5]) * alpha),
+                    pack_bf16x2(__uint_as_float(v[c + 6]) * alpha, __uint_as_float(v[c + 7]) * alpha));
+            }
+          } else {
 #pragma unroll
-              for (int hh = 0; hh < HPG; ++hh)
-                if (hh == h) oacc[hh * HD + c0 + c] = fmaf(oacc[hh * HD + c0 + c], alpha, __uint_as_float(v[c]));
+            for (int c = 0; c < 32; ++c) {
+              if (c0 + c < HD) {
+#pragma unroll
+                for (int hh = 0; hh < HPG; ++hh)
+                  if (hh == h) oacc[(PAIR ? 0 : hh * HD + c0 + c)] = fmaf(oacc[(PAIR ? 0 : hh * HD + c0 + c)], alpha, __uint_as_float(v[c]));
+              }
             }
           }
         }
@@ -486,8 +523,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
       for (int n = 0; n < it.T; ++n, ++gs) {
         const int j = n / HPG, h = n % HPG;
         const uint32_t buf = gs & 1u;
-        const int kt = pl.pair ? sl : (j & 1);   // which key table
-        if (!pl.pair && h == 0) {
+        const int kt = PAIR ? sl : (j & 1);   // which key table
+        if (!PAIR && h == 0) {
           // keys j*64 .. j*64+63 of this window: bias term, mask region, validity
           if (r < TC_KV) {
             const int key = j * TC_KV + r;
@@ -523,23 +560,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
         t_seg[1] += clock64() - tq;
         tq = clock64();
         // ---- scale, bias, mask (base-2 domain)
-        const int* kterm = key_term + kt * TC_KV;
-        const int* kreg = key_reg + kt * TC_KV;
-        const bool padded = pl.pair ? (N < TC_KV) : ((j + 1) * TC_KV > N);
+        const uint32_t kterm = smem_u32(key_term + kt * TC_KV);
+        const uint32_t kreg = smem_u32(key_reg + kt * TC_KV);
+        const bool padded = PAIR ? (N < TC_KV) : ((j + 1) * TC_KV > N);
         float mx = TC_NEG;
-        if (use_bias) {
-          const float* table = bias_in_smem ? bias_s + h * geo.nrel : nullptr;
+        if (use_bias && bias_in_smem) {
+          const uint32_t table = smem_u32(bias_s + h * geo.nrel) + 4u * row_term;     // entry of (this row, key term 0)
 #pragma unroll
           for (int c4 = 0; c4 < TC_KV; c4 += 4) {
-            const int4 t4 = *reinterpret_cast<const int4*>(kterm + c4);
+            const int4 t4 = tc_lds_i4(kterm + 4 * c4);
+            s[c4] = fmaf(s[c4], scale2, tc_lds_f32(table - 4u * t4.x));
+            s[c4 + 1] = fmaf(s[c4 + 1], scale2, tc_lds_f32(table - 4u * t4.y));
+            s[c4 + 2] = fmaf(s[c4 + 2], scale2, tc_lds_f32(table - 4u * t4.z));
+            s[c4 + 3] = fmaf(s[c4 + 3], scale2, tc_lds_f32(table - 4u * t4.w));
+          }
+        } else if (use_bias) {
+#pragma unroll
+          for (int c4 = 0; c4 < TC_KV; c4 += 4) {
+            const int4 t4 = tc_lds_i4(kterm + 4 * c4);
             const int tt[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int idx = row_term - tt[e];
-              const float bv = bias_in_smem ? table[idx]
-                                            : __ldg(a.bias_table + static_cast<long long>(idx) * a.num_heads + it.hg * HPG + h) * TC_LOG2E;
-              s[c4 + e] = fmaf(s[c4 + e], scale2, bv);
-            }
+            for (int e = 0; e < 4; ++e)
+              s[c4 + e] = fmaf(s[c4 + e], scale2,
+                               __ldg(a.bias_table + static_cast<long long>(row_term - tt[e]) * a.num_heads + it.hg * HPG + h) * TC_LOG2E);
           }
         } else {
 #pragma unroll
@@ -548,7 +591,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
         if (general || padded) {
 #pragma unroll
           for (int c4 = 0; c4 < TC_KV; c4 += 4) {
-            const int4 g4 = *reinterpret_cast<const int4*>(kreg + c4);
+            const int4 g4 = tc_lds_i4(kreg + 4 * c4);
             const int gg[4] = {g4.x, g4.y, g4.z, g4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -585,12 +628,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
         tq = clock64();
         // ---- probabilities (bf16) into the A-operand tile: row r, 16-byte chunk c8 at (c8 ^ (r & 7))
         {
-          uint8_t* prow = p_bufs + buf * Cfg::P_BYTES + sl * Cfg::P_TILE + r * 128;
+          const uint32_t prow = smem_u32(p_bufs + buf * Cfg::P_BYTES + sl * Cfg::P_TILE + r * 128);
 #pragma unroll
           for (int c8 = 0; c8 < 8; ++c8) {
             const uint4 pk = make_uint4(pack_bf16x2(s[8 * c8], s[8 * c8 + 1]), pack_bf16x2(s[8 * c8 + 2], s[8 * c8 + 3]),
                                         pack_bf16x2(s[8 * c8 + 4], s[8 * c8 + 5]), pack_bf16x2(s[8 * c8 + 6], s[8 * c8 + 7]));
-            *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = pk;
+            tc_sts_v4(prow + ((c8 ^ (r & 7)) << 4), pk);
           }
         }
         fence_proxy_async_smem();
@@ -602,7 +645,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
         if (n > 0) fold_output(gs - 1, h_prev, alpha_prev);
         t_seg[4] += clock64() - tq;
         if (!ok) break;
-        alpha_prev = alpha;
+        alpha_prev = PAIR ? 1.f / fmaf(l_old, alpha, sum) : alpha;
         h_prev = h;
       }
       tq = clock64();
@@ -612,16 +655,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_fwd_kernel(const __gri
       tq = clock64();
       // ---- normalise and store the row to its home (this GPU's buffer or a peer's)
       if (store_row) {
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out[home.slot]) + home.row * a.C + it.hg * G;
+        if (!PAIR) {
 #pragma unroll
-        for (int h = 0; h < HPG; ++h) {
-          const float inv = 1.f / l_run[h];
+          for (int h = 0; h < HPG; ++h) {
+            const float inv = 1.f / l_run[h];
 #pragma unroll
-          for (int c = 0; c < HD; c += 8) {
-            const float* o = oacc + h * HD + c;
-            *reinterpret_cast<uint4*>(dst + h * HD + c) =
-                make_uint4(pack_bf16x2(o[0] * inv, o[1] * inv), pack_bf16x2(o[2] * inv, o[3] * inv),
-                           pack_bf16x2(o[4] * inv, o[5] * inv), pack_bf16x2(o[6] * inv, o[7] * inv));
+            for (int c = 0; c < HD; c += 8) {
+              const float* o = oacc + (PAIR ? 0 : h * HD + c);
+              *reinterpret_cast<uint4*>(out_row + h * HD + c) =
+                  make_uint4(pack_bf16x2(o[0] * inv, o[1] * inv), pack_bf16x2(o[2] * inv, o[3] * inv),
+                             pack_bf16x2(o[4] * inv, o[5] * inv), pack_bf16x2(o[6] * inv, o[7] * inv));
+            }
           }
         }
         if (a.lse[home.slot] != nullptr) {
@@ -980,16 +1024,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_bwd_kernel(const __gri
           for (int c = 0; c < 32; ++c) dp[half * 32 + c] = __uint_as_float(v[c]);
         }
         tc_fence_before();
-        const int* kreg = key_reg + sl * TC_KV;
+        const uint32_t kreg = smem_u32(key_reg + sl * TC_KV);
+        const uint32_t kterm = smem_u32(key_term);
         if (use_bias) {
-          const float* table = bias_s + h * geo.nrel;
+          const uint32_t table = smem_u32(bias_s + h * geo.nrel) + 4u * row_term;
 #pragma unroll
           for (int c4 = 0; c4 < TC_KV; c4 += 4) {
-            const int4 t4 = *reinterpret_cast<const int4*>(key_term + c4);
-            s[c4] = fmaf(s[c4], scale2, table[row_term - t4.x]);
-            s[c4 + 1] = fmaf(s[c4 + 1], scale2, table[row_term - t4.y]);
-            s[c4 + 2] = fmaf(s[c4 + 2], scale2, table[row_term - t4.z]);
-            s[c4 + 3] = fmaf(s[c4 + 3], scale2, table[row_term - t4.w]);
+            const int4 t4 = tc_lds_i4(kterm + 4 * c4);
+            s[c4] = fmaf(s[c4], scale2, tc_lds_f32(table - 4u * t4.x));
+            s[c4 + 1] = fmaf(s[c4 + 1], scale2, tc_lds_f32(table - 4u * t4.y));
+            s[c4 + 2] = fmaf(s[c4 + 2], scale2, tc_lds_f32(table - 4u * t4.z));
+            s[c4 + 3] = fmaf(s[c4 + 3], scale2, tc_lds_f32(table - 4u * t4.w));
           }
         } else {
 #pragma unroll
@@ -998,7 +1043,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_bwd_kernel(const __gri
         if (general || N < TC_KV) {
 #pragma unroll
           for (int c4 = 0; c4 < TC_KV; c4 += 4) {
-            const int4 g4 = *reinterpret_cast<const int4*>(kreg + c4);
+            const int4 g4 = tc_lds_i4(kreg + 4 * c4);
             const int gg[4] = {g4.x, g4.y, g4.z, g4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -1026,31 +1071,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) wattn_tc_bwd_kernel(const __gri
 #pragma unroll
         for (int c = 0; c < TC_KV; ++c) dp[c] = s[c] * (dp[c] - dsum);      // dS (before the 1/sqrt(d) factor)
         if (bias_grad && mine) {
-          float* gtab = dbias_s + h * geo.nrel;
+          const uint32_t gtab = smem_u32(dbias_s + h * geo.nrel) + 4u * row_term;
 #pragma unroll
           for (int c4 = 0; c4 < TC_KV; c4 += 4) {
-            const int4 t4 = *reinterpret_cast<const int4*>(key_term + c4);
+            const int4 t4 = tc_lds_i4(kterm + 4 * c4);
             const int tt[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              if (c4 + e < N) atomicAdd(gtab + (row_term - tt[e]), dp[c4 + e]);
+              if (c4 + e < N) tc_red_f32(gtab - 4u * tt[e], dp[c4 + e]);
           }
         }
         // the tiles are read by the previous head's products until out_full: wait for it (and take its results)
         if (h > 0) store_outputs(h - 1);
         if (!ok) break;
         {
-          uint8_t* prow = p_tiles + sl * Cfg::MAT + r * 128;
-          uint8_t* drow = ds_tiles + sl * Cfg::MAT + r * 128;
+          const uint32_t prow = smem_u32(p_tiles + sl * Cfg::MAT + r * 128);
+          const uint32_t drow = smem_u32(ds_tiles + sl * Cfg::MAT + r * 128);
 #pragma unroll
           for (int c8 = 0; c8 < 8; ++c8) {
             const int o = (c8 ^ (r & 7)) << 4;
-            *reinterpret_cast<uint4*>(prow + o) =
-                make_uint4(pack_bf16x2(s[8 * c8], s[8 * c8 + 1]), pack_bf16x2(s[8 * c8 + 2], s[8 * c8 + 3]),
-                           pack_bf16x2(s[8 * c8 + 4], s[8 * c8 + 5]), pack_bf16x2(s[8 * c8 + 6], s[8 * c8 + 7]));
-            *reinterpret_cast<uint4*>(drow + o) =
-                make_uint4(pack_bf16x2(dp[8 * c8], dp[8 * c8 + 1]), pack_bf16x2(dp[8 * c8 + 2], dp[8 * c8 + 3]),
-                           pack_bf16x2(dp[8 * c8 + 4], dp[8 * c8 + 5]), pack_bf16x2(dp[8 * c8 + 6], dp[8 * c8 + 7]));
+            tc_sts_v4(prow + o, make_uint4(pack_bf16x2(s[8 * c8], s[8 * c8 + 1]), pack_bf16x2(s[8 * c8 + 2], s[8 * c8 + 3]),
+                                           pack_bf16x2(s[8 * c8 + 4], s[8 * c8 + 5]), pack_bf16x2(s[8 * c8 + 6], s[8 * c8 + 7])));
+            tc_sts_v4(drow + o, make_uint4(pack_bf16x2(dp[8 * c8], dp[8 * c8 + 1]), pack_bf16x2(dp[8 * c8 + 2], dp[8 * c8 + 3]),
+                                           pack_bf16x2(dp[8 * c8 + 4], dp[8 * c8 + 5]), pack_bf16x2(dp[8 * c8 + 6], dp[8 * c8 + 7])));
           }
         }
         fence_proxy_async_smem();
@@ -1582,15 +1625,20 @@ int launch_tc(const WindowAttnArgs& a, void* status, cudaStream_t stream) {
   const size_t sb = fixed + (bias_in_smem ? table : 0) + 64;
   static size_t configured = 0;
   if (sb > configured) {
-    if (cudaFuncSetAttribute(wattn_tc_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sb)) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(wattn_tc_fwd_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sb)) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(wattn_tc_fwd_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sb)) !=
+            cudaSuccess)
       return -32;
     configured = sb;
   }
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = pl.items < sms ? pl.items : sms;
-  wattn_tc_fwd_kernel<HD><<<grid, TC_THREADS, sb, stream>>>(a, pl, static_cast<KernelStatus*>(status), bias_in_smem);
+  if (pl.pair)
+    wattn_tc_fwd_kernel<HD, true><<<grid, TC_THREADS, sb, stream>>>(a, pl, static_cast<KernelStatus*>(status), bias_in_smem);
+  else
+    wattn_tc_fwd_kernel<HD, false><<<grid, TC_THREADS, sb, stream>>>(a, pl, static_cast<KernelStatus*>(status), bias_in_smem);
   return cudaGetLastError() == cudaSuccess ? 0 : -33;
 }
 

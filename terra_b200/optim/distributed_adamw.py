@@ -186,7 +186,63 @@ class DistributedAdamW(torch.optim.Optimizer):
                             exp_avg_sq=None if s.exp_avg_sq is None else s.exp_avg_sq.cpu()) for s in self.shards],
         }
 
+    def full_state_dict(self):
+        """Collective. The optimizer state in ``torch.optim.AdamW``'s per-parameter layout (``state[i] = {step, exp_avg,
+        exp_avg_sq}`` with whole-parameter fp32 tensors on the CPU, ``i`` in ``model.parameters()`` order) - what the
+        reference's ``DistributedAdamW`` keeps per owned parameter (optimizer/distributed_adamw.py:282-323). The moments
+        of every shard are gathered from their owners, so the result does not depend on how the arena was cut and can be
+        loaded into another layout (``load_state_dict`` accepts it) or into ``torch.optim.AdamW``."""
+        a = self.arena
+        dev = a.master.device
+        m_full = torch.zeros(a.numel, dtype=torch.float32, device=dev)
+        v_full = torch.zeros(a.numel, dtype=torch.float32, device=dev)
+        for sh in self.shards:
+            n_own = sh.hi - sh.lo
+            if sh.exp_avg is not None and n_own > 0:
+                m_full[sh.lo:sh.hi] = sh.exp_avg[:n_own]
+                v_full[sh.lo:sh.hi] = sh.exp_avg_sq[:n_own]
+            if sh.size > 1:
+                # every element has exactly one owner in the group: a sum puts the pieces together
+                dist.all_reduce(m_full[sh.start:sh.end], group=sh.group)
+                dist.all_reduce(v_full[sh.start:sh.end], group=sh.group)
+        state = {}
+        for i, (p, off) in enumerate(zip(a.params, a.offsets)):
+            n = p.numel()
+            state[i] = {"step": torch.tensor(float(self.step_count)), "exp_avg": m_full[off:off + n].view(p.shape).cpu().clone(),
+                        "exp_avg_sq": v_full[off:off + n].view(p.shape).cpu().clone()}
+        groups = [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]
+        groups[0]["params"] = list(range(len(a.params)))
+        return {"state": state, "param_groups": groups, "global_step": self.global_step}
+
+    def _load_per_parameter(self, state):
+        a = self.arena
+        dev = a.master.device
+        m_full = torch.zeros(a.numel, dtype=torch.float32, device=dev)
+        v_full = torch.zeros(a.numel, dtype=torch.float32, device=dev)
+        steps = []
+        for i, (p, off) in enumerate(zip(a.params, a.offsets)):
+            st = state["state"].get(i, state["state"].get(str(i)))
+            if st is None:
+                continue          # owner-only files of the reference hold a subset: missing moments start at zero
+            n = p.numel()
+            m_full[off:off + n] = st["exp_avg"].reshape(-1).to(dev, torch.float32)
+            v_full[off:off + n] = st["exp_avg_sq"].reshape(-1).to(dev, torch.float32)
+            steps.append(int(float(st["step"])))
+        self.step_count = max(steps) if steps else 0
+        self.global_step = int(state.get("global_step", self.global_step))
+        for g, saved in zip(self.param_groups, state.get("param_groups", [])):
+            g.update({k: v for k, v in saved.items() if k != "params"})
+        for sh in self.shards:
+            n_own = max(sh.hi - sh.lo, 1)
+            sh.exp_avg = torch.zeros(n_own, dtype=torch.float32, device=dev)
+            sh.exp_avg_sq = torch.zeros(n_own, dtype=torch.float32, device=dev)
+            if sh.hi > sh.lo:
+                sh.exp_avg[:sh.hi - sh.lo] = m_full[sh.lo:sh.hi]
+                sh.exp_avg_sq[:sh.hi - sh.lo] = v_full[sh.lo:sh.hi]
+
     def load_state_dict(self, state):
+        if "shards" not in state and "state" in state:
+            return self._load_per_parameter(state)      # torch.optim.AdamW / reference per-parameter layout
         self.step_count = int(state["step"])
         self.global_step = int(state.get("global_step", 0))
         for g, saved in zip(self.param_groups, state["param_groups"]):

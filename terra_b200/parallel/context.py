@@ -247,12 +247,64 @@ class ParallelContext:
         return x + y + mod.bias2.to(y.dtype)
 
     # ------------------------------------------------------------------ stripe <-> window relayout
+    def _peer_relayout(self, x):
+        """The peer-memory implementation, when this rank's group has one and the tensor lives on a GPU."""
+        peer = getattr(self.dom, "peer", None)
+        return peer if (peer is not None and x.is_cuda and self.world > 1) else None
+
+    def relayout_routes(self, batch):
+        """Index tables of the general relayout, both directions: for every row of this rank's destination buffer,
+        the window-parallel rank that holds the token and the row inside that rank's source buffer (the closed-form
+        counterpart of the reference's route tables, core/parallel/layout_transform.py:67-87,338-376). Returns
+        ``((rank, row) for stripe -> windows, (rank, row) for windows -> stripe)`` as int32 numpy arrays."""
+        key = ("routes", batch)
+        cache = self.__dict__.setdefault("_cache", {})
+        if key in cache:
+            return cache[key]
+        sizes, img_pos = self._relayout_table(batch)          # image-major token -> position in the ranks' concatenation
+        img_pos = img_pos.numpy()
+        bounds = np.cumsum([0] + list(sizes))
+        h = self.Ht // self.world
+        # windows -> stripe: my stripe rows are image-major tokens (b, gh in my stripe, gw)
+        tok = np.arange(batch * self.Ht * self.Wt, dtype=np.int64).reshape(batch, self.Ht, self.Wt)
+        mine = tok[:, self.wp_rank * h:(self.wp_rank + 1) * h].reshape(-1)
+        pos = img_pos[mine]
+        w2s_rank = (np.searchsorted(bounds, pos, side="right") - 1).astype(np.int32)
+        w2s_row = (pos - bounds[w2s_rank]).astype(np.int32)
+        # stripe -> windows: invert for my window-major rows; a token's stripe rank is its image row // h
+        lo, hi = bounds[self.wp_rank], bounds[self.wp_rank + 1]
+        inv = np.full(hi - lo, -1, dtype=np.int64)
+        sel = np.nonzero((img_pos >= lo) & (img_pos < hi))[0]
+        inv[img_pos[sel] - lo] = sel                          # my row -> image-major token id
+        b = inv // (self.Ht * self.Wt)
+        rem = inv % (self.Ht * self.Wt)
+        gh, gw = rem // self.Wt, rem % self.Wt
+        s2w_rank = (gh // h).astype(np.int32)
+        s2w_row = ((b * h + gh % h) * self.Wt + gw).astype(np.int32)
+        pad = inv < 0                                          # rows of zero-padded windows (ragged TP chunks) have no source
+        s2w_rank[pad] = self.wp_rank
+        s2w_row[pad] = 0
+        cache[key] = ((s2w_rank, s2w_row), (w2s_rank, w2s_row))
+        return cache[key]
+
+    def _routes_on(self, batch, device):
+        key = ("routes_dev", batch, str(device))
+        cache = self.__dict__.setdefault("_cache", {})
+        if key not in cache:
+            (a, b), (c, d) = self.relayout_routes(batch)
+            cache[key] = tuple(torch.from_numpy(t).to(device) for t in (a, b, c, d))
+        return cache[key]
+
     def stripe_to_windows(self, x):
         """NHWC row stripe ``[B, Ht/wp, Wt, C]`` -> this rank's window-major rows."""
         Bn, h, W, Cn = x.shape
         if self.local_relayout and self.world > 1:
             win = x.reshape(Bn, h // self.wh, self.wh, self.nWw, self.ww, Cn).permute(0, 1, 3, 2, 4, 5)
             return win.reshape(-1, Cn).contiguous()
+        peer = self._peer_relayout(x)
+        if peer is not None:
+            s2w_rank, s2w_row, w2s_rank, w2s_row = self._routes_on(Bn, x.device)
+            return _PeerRelayoutFn.apply(x.reshape(-1, Cn), peer, s2w_rank, s2w_row, w2s_rank, w2s_row)
         if self.world == 1:
             full = x
         else:
@@ -279,6 +331,11 @@ class ParallelContext:
             win = rows.reshape(batch, nh, self.nWw, self.wh, self.ww, Cn).permute(0, 1, 3, 2, 4, 5)
             return win.reshape(batch, nh * self.wh, self.Wt, Cn).contiguous()
         m = self.manager
+        peer = self._peer_relayout(rows)
+        if peer is not None:
+            s2w_rank, s2w_row, w2s_rank, w2s_row = self._routes_on(batch, rows.device)
+            out = _PeerRelayoutFn.apply(rows, peer, w2s_rank, w2s_row, s2w_rank, s2w_row)
+            return out.reshape(batch, self.Ht // self.world, self.Wt, Cn)
         sizes, index = self._relayout_table(batch)
         allrows = C.all_gather_rows(rows.contiguous(), m.window_parallel_group, sizes)
         full = allrows[index.to(rows.device)]                                            # [B*Ht*Wt, C] image-major
@@ -313,6 +370,25 @@ class ParallelContext:
 
 
 _LayerNormFn = B.LayerNormFn
+
+
+class _PeerRelayoutFn(torch.autograd.Function):
+    """Relayout as a gather over peer memory: every destination row has exactly one source row on one rank, so the
+    forward pulls the rows by a (rank, row) table and the backward pulls the gradient rows by the opposite table. The
+    source is staged in symmetric memory; one barrier makes every rank's staging complete before the pulls."""
+
+    @staticmethod
+    def forward(ctx, x, peer, f_rank, f_row, b_rank, b_row):
+        ctx.peer, ctx.tables = peer, (b_rank, b_row)
+        ctx.src_rows = x.shape[0]
+        return peer.gather_rows(x, f_rank, f_row)
+
+    @staticmethod
+    def backward(ctx, g):
+        b_rank, b_row = ctx.tables
+        out = ctx.peer.gather_rows(g.contiguous(), b_rank, b_row)
+        assert out.shape[0] == ctx.src_rows
+        return out, None, None, None, None, None
 
 
 class _PortableAttnComm:

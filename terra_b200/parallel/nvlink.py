@@ -253,6 +253,25 @@ class PeerDomain:
             self.halo_epoch, self._word(self.rank, self.TICKET), status_word(self.arena.buf.device), BARRIER_SPIN_LIMIT)
         return (lo if has_prev else None), (hi if has_next else None)
 
+    def gather_rows(self, x: torch.Tensor, src_rank: torch.Tensor, src_row: torch.Tensor) -> torch.Tensor:
+        """``out[i] = row src_row[i] of rank src_rank[i]'s x`` (int32 device tables; every rank passes its own ``x``,
+        all with the same number of columns). The general stripe <-> window relayout: an all-to-all-v in which the
+        receiver pulls exactly the rows it owns, in one kernel, instead of an all-gather of the whole activation."""
+        ext = _ext.load()
+        rows = torch.tensor([x.shape[0]], device=x.device)
+        if not hasattr(self, "_max_rows"):
+            self._max_rows = {}
+        key = (x.shape[0], x.shape[1])
+        if key not in self._max_rows:
+            dist.all_reduce(rows, op=dist.ReduceOp.MAX, group=self.arena.group)      # symmetric allocation: largest shard
+            self._max_rows[key] = int(rows.item())
+        staged = self.arena.alloc((self._max_rows[key], x.shape[1]), x.dtype)[:x.shape[0]]
+        staged.copy_(x)
+        self.arena.barrier()                      # every rank's rows are staged
+        out = torch.empty(src_rank.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+        ext.peer_gather_indexed(out, self.arena.peer_ptrs(staged), src_rank, src_row)
+        return out
+
     def all_reduce_small(self, t: torch.Tensor) -> torch.Tensor:
         """Sum of a small fp32 tensor over the group (a new tensor)."""
         ext = _ext.load()
@@ -324,6 +343,12 @@ def attach(model, optimizer, manager) -> None:
         w_tok = a.patches_resolution[1]
         row = pctx.B * w_tok * model.embedding_dim * 4          # one fp32 boundary row at patch resolution
         nbytes = 48 * row + 2 * COMM_MAX_PEERS * PeerDomain.SMALL_CAPACITY * 4 + (16 << 20)
+        if not pctx.local_relayout:
+            # general relayout: the activation shard is staged twice forward, twice backward (and once more each when
+            # the surrounding segment is recomputed)
+            shard = pctx.B * (pctx.Ht // pctx.world + 1) * pctx.Wt * model.embedding_dim * 2
+            win = pctx.B * (max(len(w) for w in pctx.windows_of) // pctx.tp + 1) * pctx.N * model.embedding_dim * 2
+            nbytes += 4 * (shard + win) + (16 << 20)
         pctx.dom_arena = SymmetricArena(manager.window_parallel_group, nbytes, device)
         pctx.dom.peer = PeerDomain(pctx.dom_arena)
     # ---- tensor-parallel MLP: fc1 / fc2 with the all-gather / reduce-scatter fused into the GEMMs

@@ -51,9 +51,20 @@ WORKER = textwrap.dedent('''
         opt.step(); ropt.step()
         for p, q in zip(mine.parameters(), ref.parameters()):
             worst = max(worst, (p.data - q.data).abs().max().item())
+    # per-parameter view of the sharded state == torch.optim.AdamW's own state, and torch's state loads back in
+    full = opt.full_state_dict()
+    rstate = ropt.state_dict()["state"]
+    state_err = max(max((full["state"][i]["exp_avg"] - rstate[i]["exp_avg"]).abs().max().item(),
+                        (full["state"][i]["exp_avg_sq"] - rstate[i]["exp_avg_sq"]).abs().max().item()) for i in rstate)
+    opt3 = DistributedAdamW(mine.parameters(), lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, model=mine,
+                            process_group=dist.group.WORLD)
+    opt3.load_state_dict(ropt.state_dict())
+    round_trip = max((a.exp_avg[:a.hi - a.lo] - b.exp_avg[:b.hi - b.lo]).abs().max().item()
+                     for a, b in zip(opt3.shards, opt.shards) if a.hi > a.lo)
+    assert opt3.step_count == opt.step_count
     owned = sum(s.hi - s.lo for s in opt.shards)
     with open(os.path.join(os.environ["OUT_DIR"], f"res_{rank}.json"), "w") as f:      # (stdout of ranks interleaves)
-        json.dump(dict(rank=rank, worst=worst, owned=owned, numel=opt.arena.numel), f)
+        json.dump(dict(rank=rank, worst=worst, owned=owned, numel=opt.arena.numel, state_err=state_err, round_trip=round_trip), f)
     dist.destroy_process_group()
 ''')
 
@@ -81,6 +92,7 @@ def test_distributed_adamw_equals_torch_adamw_over_steps(tmp_path, world):
     for r in res:
         assert r["worst"] < 3e-5, r                      # same update rule in fp32; the ranks' gradients are summed in another order
         assert 0 < r["owned"] <= r["numel"]              # every rank owns a slice, none owns everything (world > 1)
+        assert r["state_err"] < 3e-5 and r["round_trip"] < 3e-5, r
     assert sum(r["owned"] for r in res) >= res[0]["numel"] - 1024 * world
 
 
