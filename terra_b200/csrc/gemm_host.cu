@@ -4,6 +4,7 @@
 #include "host_api.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -32,8 +33,18 @@ static EncodeTiledFn get_encode_fn() {
 
 // rank <= 5, bf16 elements, 128-byte swizzle, zero fill outside the tensor.
 // dims/box are innermost first; strides (bytes) are for dims 1..rank-1.
+static int make_tensor_map_bf16_swizzled(CUtensorMap* out, const void* base, int rank, const unsigned long long* dims,
+                                         const unsigned long long* strides_bytes, const unsigned int* box,
+                                         CUtensorMapSwizzle swizzle);
+
 int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const unsigned long long* dims,
                          const unsigned long long* strides_bytes, const unsigned int* box) {
+  return make_tensor_map_bf16_swizzled(out, base, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+static int make_tensor_map_bf16_swizzled(CUtensorMap* out, const void* base, int rank, const unsigned long long* dims,
+                                         const unsigned long long* strides_bytes, const unsigned int* box,
+                                         CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   // cuTensorMapEncodeTiled is a driver call: it needs the primary context bound to THIS thread. A thread that
@@ -58,7 +69,7 @@ int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uns
   for (int i = 0; i + 1 < rank; ++i)
     if (gstr[i] % 16 != 0) return -3;
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
-                  gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -100 - static_cast<int>(r);
 }
@@ -69,6 +80,36 @@ static int map_2d(CUtensorMap* out, const void* base, long long inner, long long
   unsigned long long str[1] = {static_cast<unsigned long long>(ld_elems) * 2ull};
   unsigned int box[2] = {static_cast<unsigned int>(box_inner), static_cast<unsigned int>(box_outer)};
   return make_tensor_map_bf16(out, base, 2, dims, str, box);
+}
+
+// 32 x 32 chunk of a row-major bf16 matrix in the 64-byte-swizzled layout (the epilogue's staging format)
+static int map_chunk(CUtensorMap* out, const void* base, long long cols, long long rows, long long ld_elems) {
+  unsigned long long dims[2] = {static_cast<unsigned long long>(cols), static_cast<unsigned long long>(rows)};
+  unsigned long long str[1] = {static_cast<unsigned long long>(ld_elems) * 2ull};
+  unsigned int box[2] = {32u, 32u};
+  return make_tensor_map_bf16_swizzled(out, base, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
+// Plain row-major bf16 outputs leave through TMA stores (and the residual / GELU-input operand arrives through TMA
+// loads) when every matrix qualifies for a tensor map; otherwise the epilogue keeps its per-lane global accesses.
+static void try_tma_epilogue(GemmParams& p, long long M, long long N) {
+  static const bool enabled = [] {
+    const char* e = std::getenv("TERRA_GEMM_TMA_EPILOGUE");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  p.epi_tma = 0;
+  const int f = p.epi;
+  if (!enabled || (f & (EPI_OUT_F32 | EPI_ATOMIC | EPI_ROW_CONV | EPI_ROW_SHUFFLE))) return;
+  if ((f & EPI_RESIDUAL) && (f & EPI_MUL_DGELU)) return;
+  // The input buffers cost the operand ring one or two stages. A long contraction hides the epilogue behind its main
+  // loop anyway and wants the deeper ring instead (K = 1536 with a residual measured 15 % slower on three stages).
+  if ((f & (EPI_RESIDUAL | EPI_MUL_DGELU)) && p.k_blocks > 12) return;
+  if (p.a_peers > 1 || p.c_peers > 1 || p.groups != 1 || p.C == nullptr) return;
+  if (map_chunk(&p.map_c, p.C, N, M, p.ldc) != 0) return;
+  if ((f & EPI_SAVE_PRE) && map_chunk(&p.map_c2, p.C2, N, M, p.ldc2) != 0) return;
+  if ((f & EPI_RESIDUAL) && map_chunk(&p.map_in, p.residual, N, M, p.ldr) != 0) return;
+  if ((f & EPI_MUL_DGELU) && map_chunk(&p.map_in, p.aux, N, M, p.ldaux) != 0) return;
+  p.epi_tma = 1;
 }
 
 static int pick_bn(long long N, int requested) {
@@ -186,6 +227,7 @@ int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, lon
   p.out_w = epi.out_w;
   p.out_h = epi.out_h;
   p.shuffle_cout = epi.shuffle_cout > 0 ? epi.shuffle_cout : 1;
+  if (ctas == 1) try_tma_epilogue(p, M, N);
   cudaError_t e = launch_gemm(p, bn, ctas, num_sms, stream);
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

@@ -45,16 +45,24 @@ struct GemmCfg {
   static constexpr int B_ROWS = BN / CTAS;                 // rows of B staged by one CTA
   static constexpr int B_BYTES = B_ROWS * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  // barriers + per-warp bias slots + per-warp 2 KB exchange buffers of the epilogue
-  static constexpr int FIXED_BYTES = 256 + GEMM_EPI_WARPS * 32 * 4 + GEMM_EPI_WARPS * 2048;
+  // After the operand ring: 512 bytes of barriers, the per-warp bias slots (together 2 KB), then `bufs` buffers of
+  // 2 KB per epilogue warp (1: the exchange / output staging buffer; 3: two more for the operand the epilogue reads,
+  // loaded ahead by TMA). The ring takes what is left: the launcher passes the stage count to the kernel.
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int FIXED_BASE = 2048;
+  static constexpr int EPI_BUF = 2048;
   static constexpr int MAX_SMEM = 232448;   // 227 KB, the per-block limit of sm_100
-  static constexpr int FIT = (MAX_SMEM - FIXED_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = FIT > 8 ? 8 : FIT;
+  static constexpr int MAX_STAGES = 8;
+  static constexpr int fixed_bytes(int bufs) { return FIXED_BASE + GEMM_EPI_WARPS * bufs * EPI_BUF; }
+  static constexpr int stages_for(int bufs) {
+    return (MAX_SMEM - 1024 - fixed_bytes(bufs)) / STAGE_BYTES > MAX_STAGES ? MAX_STAGES
+                                                                            : (MAX_SMEM - 1024 - fixed_bytes(bufs)) / STAGE_BYTES;
+  }
+  static constexpr int smem_bytes(int bufs) { return stages_for(bufs) * STAGE_BYTES + fixed_bytes(bufs) + 1024; }   // + alignment slack
   // two accumulators; the allocation must be a power of two
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
-  static constexpr int USED_BYTES = STAGES * STAGE_BYTES + FIXED_BYTES;
-  static constexpr int SMEM_BYTES = (USED_BYTES + 1024 <= MAX_SMEM) ? USED_BYTES + 1024 : MAX_SMEM;   // + alignment slack
-  static_assert(STAGES >= 3 && USED_BYTES <= MAX_SMEM, "shared memory budget");
+  static_assert(stages_for(3) >= 3 && smem_bytes(1) <= MAX_SMEM && smem_bytes(3) <= MAX_SMEM, "shared memory budget");
+  static_assert(GEMM_EPI_WARPS * 32 * 4 + BAR_BYTES <= FIXED_BASE, "bias slots");
   static_assert(CTAS == 1 || (B_ROWS % 64 == 0), "a CTA's half of B must be whole 64-row boxes");
 };
 
@@ -91,18 +99,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   constexpr bool PAIR = CTAS == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-  uint64_t* empty = full + Cfg::STAGES;
-  uint64_t* tfull = empty + Cfg::STAGES;
+  const int stages = p.stages;
+  uint8_t* fixed = smem + stages * Cfg::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(fixed);
+  uint64_t* empty = full + Cfg::MAX_STAGES;
+  uint64_t* tfull = empty + Cfg::MAX_STAGES;
   uint64_t* tempty = tfull + 2;
   uint64_t* pfull = tempty + 2;   // pair mode, leader CTA: "the peer's half of stage s has landed"
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull + Cfg::STAGES);
+  uint64_t* in_bar = pfull + Cfg::MAX_STAGES;   // two per epilogue warp: "the epilogue operand chunk has landed"
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + 2 * GEMM_EPI_WARPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* bias_slots = reinterpret_cast<float*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 256);
-  uint8_t* xchg = reinterpret_cast<uint8_t*>(bias_slots + GEMM_EPI_WARPS * 32);
+  static_assert((3 * Cfg::MAX_STAGES + 4 + 2 * GEMM_EPI_WARPS) * 8 + 8 <= Cfg::BAR_BYTES, "barrier block");
+  float* bias_slots = reinterpret_cast<float*>(fixed + Cfg::BAR_BYTES);
+  uint8_t* xchg = fixed + Cfg::FIXED_BASE;
   // The ring needs a 1024-byte aligned base (128-byte swizzle atoms). The dynamic window normally starts aligned; if
   // the alignment shift does not fit into the slack the launch is refused as a whole, before any barrier exists.
-  if (smem + Cfg::USED_BYTES > smem_raw + Cfg::SMEM_BYTES) {
+  if (stages < 1 || stages > Cfg::MAX_STAGES ||
+      xchg + GEMM_EPI_WARPS * p.epi_bufs * Cfg::EPI_BUF > smem_raw + p.smem_bytes) {
     if (threadIdx.x == 0) report_error(p.status, TB_ERR_BAD_ARG, 0x700u, blockIdx.x, 0u);
     return;
   }
@@ -114,11 +127,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   const int units = PAIR ? gridDim.x >> 1 : gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) {
+    for (int s = 0; s < Cfg::MAX_STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
       mbar_init(&pfull[s], 1);
     }
+    for (int i = 0; i < 2 * GEMM_EPI_WARPS; ++i) mbar_init(&in_bar[i], 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], GEMM_EPI_WARPS * CTAS);   // pair mode: both CTAs' epilogue warps release the leader's
@@ -127,6 +141,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     mbar_fence_init();
     tma_prefetch_desc(&p.map_a);
     tma_prefetch_desc(&p.map_b);
+    if (p.epi_tma) {
+      tma_prefetch_desc(&p.map_c);
+      if (p.epi & EPI_SAVE_PRE) tma_prefetch_desc(&p.map_c2);
+      if (p.epi & (EPI_RESIDUAL | EPI_MUL_DGELU)) tma_prefetch_desc(&p.map_in);
+    }
     if (PEERS)
       for (int i = 0; i < p.a_peers && p.a_peers > 1; ++i) tma_prefetch_desc(&p.map_a_peer[i]);
   }
@@ -159,7 +178,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       const long long t_begin = clock64();
       long long t_wait = 0;
       unsigned int peers_ready = 0u;   // bit per (peer, chunk) whose flag has been seen
@@ -175,9 +195,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 #pragma unroll
           for (int d = 0; d < 5; ++d) abase[d] = t0 * p.a_mul0[d] + t1 * p.a_mul1[d] + t2 * p.a_mul2[d];
         }
-        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
-          const int s = it % Cfg::STAGES;
-          const uint32_t ph = (it / Cfg::STAGES) & 1u;
+        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
           const long long w0 = clock64();
           if (!mbar_wait<PAIR>(&empty[s], ph ^ 1u, abort_flag, p.status, 0x100u + s, mbar_budget)) break;
           t_wait += clock64() - w0;
@@ -277,7 +295,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       const uint32_t a_lbo = a_mn ? GEMM_BK * 128 : 16, b_lbo = b_mn ? GEMM_BK * 128 : 16;
       const uint32_t a_kstep = a_mn ? (16 * 128) >> 4 : 32 >> 4;   // descriptor units of 16 bytes
       const uint32_t b_kstep = b_mn ? (16 * 128) >> 4 : 32 >> 4;
-      uint32_t it = 0, tcount = 0;
+      int s = 0;
+      uint32_t ph = 0, tcount = 0;
       const long long t_begin = clock64();
       long long t_acc = 0, t_ops = 0;
       for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units, ++tcount) {
@@ -290,9 +309,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
-        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
-          const int s = it % Cfg::STAGES;
-          const uint32_t ph = (it / Cfg::STAGES) & 1u;
+        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
           const long long w1 = clock64();
           if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x300u + s, mbar_budget)) { ok = false; break; }
           if (PAIR && !mbar_wait<PAIR>(&pfull[s], ph, abort_flag, p.status, 0x380u + s, mbar_budget)) { ok = false; break; }
@@ -317,13 +334,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     } else if (PAIR && rank == 1 && elect_one()) {
       // Peer CTA: its MMA warp has nothing to issue. It forwards "my half of stage s has landed" to the leader, whose
       // MMA thread waits for both halves before it issues.
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       for (int tile = unit; tile < total_tiles && !*abort_flag; tile += units) {
         const TileCoord tc = decode_tile(p, tile, CTAS, rank);
         bool ok = true;
-        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
-          const int s = it % Cfg::STAGES;
-          const uint32_t ph = (it / Cfg::STAGES) & 1u;
+        for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
           if (!mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 0x3c0u + s, mbar_budget)) { ok = false; break; }
           mbar_arrive_remote(map_to_cta(&pfull[s], 0));
         }
@@ -351,6 +367,172 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     auto xaddr = [&](int rr, int vec) -> uint4* {
       return reinterpret_cast<uint4*>(my_x + rr * 64 + (((vec ^ (rr >> 1)) & 3) << 4));
     };
+    constexpr int CPW = (CHUNKS + GEMM_EPI_WARPS / 4 - 1) / (GEMM_EPI_WARPS / 4);   // chunks per warp
+    if (!PAIR && !PEERS && p.epi_tma) {
+      // ---- plain row-major bf16 outputs: chunks leave (and the operand the epilogue reads arrives) through TMA.
+      // A chunk is 32 rows of 64 bytes in the 64-byte-swizzled layout, which is also conflict-free for the
+      // row-per-lane 16-byte accesses of the warp. Buffer 0 of the warp stages outputs: one lane issues the store and,
+      // before the next chunk is written, waits until the store has read the buffer. Buffers 1 and 2 receive the
+      // input operand two chunks ahead (across tiles), so its latency hides behind the chunks in between.
+      uint8_t* my_bufs = xchg + (warp - 2) * p.epi_bufs * Cfg::EPI_BUF;
+      uint64_t* my_in = in_bar + (warp - 2) * 2;
+      const bool has_in = (p.epi & (EPI_RESIDUAL | EPI_MUL_DGELU)) != 0;
+      const uint32_t row_off = static_cast<uint32_t>(lane) * 64u;
+      const uint32_t swz = (static_cast<uint32_t>(lane) >> 1) & 3u;
+      const uint32_t out_addr = smem_u32(my_bufs);
+      uint32_t issued = 0, consumed = 0;
+      int pf_tile = unit, pf_ci = 0;
+      auto prefetch_next = [&]() {   // issue the load of this warp's next input chunk, if there is one
+        while (pf_tile < total_tiles) {
+          const TileCoord t = decode_tile(p, pf_tile, 1, 0);
+          const int c = part + pf_ci * (GEMM_EPI_WARPS / 4);
+          const int col = t.n_blk * BN + c * 32;
+          const int row = t.m_blk * GEMM_BM + q * 32;
+          const bool ok = c < CHUNKS && col < p.N;
+          if (++pf_ci >= CPW) {
+            pf_ci = 0;
+            pf_tile += units;
+          }
+          if (ok) {
+            if (lane == 0) {
+              uint64_t* b = my_in + (issued & 1u);
+              mbar_expect_tx(b, Cfg::EPI_BUF);
+              tma_load_2d(my_bufs + Cfg::EPI_BUF * (1 + (issued & 1u)), &p.map_in, b, col, row);
+            }
+            ++issued;
+            return;
+          }
+        }
+      };
+      auto stage_store = [&](const CUtensorMap* map, const float (&f)[32], int col, int row) {
+        if (lane == 0) bulk_wait_group_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t a = out_addr + row_off + (((static_cast<uint32_t>(j) ^ swz) & 3u) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack_bf16x2(f[8 * j], f[8 * j + 1])),
+                       "r"(pack_bf16x2(f[8 * j + 2], f[8 * j + 3])), "r"(pack_bf16x2(f[8 * j + 4], f[8 * j + 5])),
+                       "r"(pack_bf16x2(f[8 * j + 6], f[8 * j + 7]))
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row < p.M) {
+          tma_store_2d(map, out_addr, col, row);
+          bulk_commit_group();
+        }
+      };
+      if (has_in) {
+        prefetch_next();
+        prefetch_next();
+      }
+      bool failed = false;
+      for (int tile = unit; tile < total_tiles && !failed; tile += units, ++tcount) {
+        const TileCoord tc = decode_tile(p, tile, 1, 0);
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1u;
+        const int n0 = tc.n_blk * BN;
+        const int row0 = tc.m_blk * GEMM_BM + q * 32;
+        const long long ew0 = clock64();
+        const bool tile_ready = mbar_wait<PAIR>(&tfull[acc], aph, abort_flag, p.status, 0x400u + acc, mbar_budget);
+        if (!__all_sync(0xffffffffu, tile_ready)) break;
+        e_wait += clock64() - ew0;
+        tc_fence_after();
+        bool released = false;
+#pragma unroll
+        for (int ci = 0; ci < CPW; ++ci) {
+          const int c = part + ci * (GEMM_EPI_WARPS / 4);
+          if (c >= CHUNKS || n0 + c * 32 >= p.N) break;   // warp-uniform
+          const int nb = n0 + c * 32;
+          const bool last = (ci + 1 >= CPW) || (c + GEMM_EPI_WARPS / 4 >= CHUNKS) || (nb + 32 * (GEMM_EPI_WARPS / 4) >= p.N);
+          if (has_bias) {
+            float b = 0.f;
+            if (nb + lane < p.N)
+              b = (p.epi & EPI_BIAS_F32) ? __ldg(static_cast<const float*>(p.bias) + nb + lane)
+                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[nb + lane]);
+            __syncwarp();
+            my_bias[lane] = b;
+            __syncwarp();
+          }
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+          uint4 u[4];
+          if (has_in) {
+            const uint32_t b = consumed & 1u;
+            const bool in_ready =
+                mbar_wait<false>(&my_in[b], (consumed >> 1) & 1u, abort_flag, p.status, 0x600u + b, mbar_budget);
+            if (!__all_sync(0xffffffffu, in_ready)) {
+              tmem_ld_wait();
+              failed = true;
+              break;
+            }
+            const uint32_t src = smem_u32(my_bufs + Cfg::EPI_BUF * (1 + b)) + row_off;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t a = src + (((static_cast<uint32_t>(j) ^ swz) & 3u) << 4);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(u[j].x), "=r"(u[j].y), "=r"(u[j].z), "=r"(u[j].w)
+                           : "r"(a)
+                           : "memory");
+            }
+            ++consumed;
+          }
+          tmem_ld_wait();
+          if (last) {   // the accumulator has been read: the MMA thread may start the tile after next
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+            released = true;
+          }
+          float f[32];
+          if (has_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(my_bias + j);
+              f[j] = fmaf(__uint_as_float(v[j]), p.alpha, b4.x);
+              f[j + 1] = fmaf(__uint_as_float(v[j + 1]), p.alpha, b4.y);
+              f[j + 2] = fmaf(__uint_as_float(v[j + 2]), p.alpha, b4.z);
+              f[j + 3] = fmaf(__uint_as_float(v[j + 3]), p.alpha, b4.w);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+          }
+          if (p.epi & EPI_SAVE_PRE) stage_store(&p.map_c2, f, nb, row0);
+          if (p.epi & EPI_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+          }
+          if (has_in) {
+            const bool dgelu = (p.epi & EPI_MUL_DGELU) != 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w4[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float2 x = unpack_bf16x2(w4[k]);
+                if (dgelu) {
+                  f[8 * j + 2 * k] *= gelu_erf_grad(x.x);
+                  f[8 * j + 2 * k + 1] *= gelu_erf_grad(x.y);
+                } else {
+                  f[8 * j + 2 * k] += x.x;
+                  f[8 * j + 2 * k + 1] += x.y;
+                }
+              }
+            }
+            __syncwarp();        // every lane holds its part of the input chunk: its buffer may be refilled
+            prefetch_next();
+          }
+          stage_store(&p.map_c, f, nb, row0);
+        }
+        if (!released && !failed) {   // a warp without a chunk in this tile (narrow last column tile)
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+      }
+      if (lane == 0) bulk_wait_group_read<0>();
+    } else
     for (int tile = unit; tile < total_tiles; tile += units, ++tcount) {
       const TileCoord tc = decode_tile(p, tile, CTAS, rank);
       const int acc = tcount & 1;
@@ -433,7 +615,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       // The operand the epilogue reads (GELU input of the backward pass, or the residual) does not depend on the
       // accumulator: pull it into L2 before waiting for the tile, so the DRAM latency hides behind the main loop;
       // the chunk loop then fetches it (an L2 hit) under the latency of its tcgen05.ld.
-      constexpr int CPW = (CHUNKS + GEMM_EPI_WARPS / 4 - 1) / (GEMM_EPI_WARPS / 4);   // chunks per warp
       const bool pre_aux = (p.epi & EPI_MUL_DGELU) != 0;
       const bool pre_res = !pre_aux && (p.epi & EPI_RESIDUAL) != 0;
       const __nv_bfloat16* pre_ptr = pre_aux ? p.aux : p.residual;
@@ -613,27 +794,32 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 
 // ------------------------------------------------------------------------------ host side
 template <int BN, int CTAS, bool PEERS = false>
-static cudaError_t launch_bn(const GemmParams& p, int num_sms, cudaStream_t stream) {
+static cudaError_t launch_bn(const GemmParams& p_in, int num_sms, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, CTAS>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, CTAS, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM_BYTES);
+                                         Cfg::MAX_SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
   }
+  GemmParams p = p_in;
+  if (CTAS != 1 || PEERS) p.epi_tma = 0;
+  p.epi_bufs = (p.epi_tma && (p.epi & (EPI_RESIDUAL | EPI_MUL_DGELU))) ? 3 : 1;
+  p.stages = p.epi_bufs == 3 ? Cfg::stages_for(3) : Cfg::stages_for(1);
+  p.smem_bytes = p.epi_bufs == 3 ? Cfg::smem_bytes(3) : Cfg::smem_bytes(1);
   const int total = p.groups * p.num_m_tiles * p.num_n_tiles * p.split_k;
   const int max_units = num_sms / CTAS;
   const int units = total < max_units ? total : max_units;
   if (units <= 0) return cudaSuccess;
   if (CTAS == 1) {
-    gemm_tcgen05_kernel<BN, CTAS, PEERS><<<units, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+    gemm_tcgen05_kernel<BN, CTAS, PEERS><<<units, GEMM_THREADS, p.smem_bytes, stream>>>(p);
     return cudaGetLastError();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(units * CTAS);
   cfg.blockDim = dim3(GEMM_THREADS);
-  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.dynamicSmemBytes = p.smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;

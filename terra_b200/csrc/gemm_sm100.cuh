@@ -69,6 +69,16 @@ struct GemmParams {
   int shuffle_cout;
   float alpha;
   KernelStatus* status;
+  // Epilogue through TMA (plain row-major bf16 outputs, single-CTA tiles): every epilogue warp stages its 32 x 32
+  // chunk in shared memory in the 64-byte-swizzled layout and one lane stores it through map_c / map_c2; the operand
+  // the epilogue reads (residual, or the GELU input of the backward pass) arrives through map_in, loaded two chunks
+  // ahead into per-warp buffers. epi_bufs = buffers of 2 KB per epilogue warp (1: output staging; 3: + two inputs).
+  // stages / smem_bytes: the launcher sizes the operand ring with what the epilogue buffers leave.
+  CUtensorMap map_c, map_c2, map_in;
+  int epi_tma;
+  int epi_bufs;
+  int stages;
+  int smem_bytes;
   // Tensor-parallel fusions over peer memory (NVLink), single-CTA mode, 2-D K-major A:
   //  * all-gather -> GEMM: the rows of A live in a_peers buffers of a_rows rows each (one per GPU, one tensor map per
   //    buffer); m tile i reads tile i / a_peers of peer (i % a_peers + a_first) % a_peers: every GPU starts with a

@@ -70,15 +70,17 @@ def case_gemm(a):
     if a.epilogue == "wgrad":
         dy, x = _rand(M, N, scale=0.1), _rand(M, K, scale=0.1)
         out = torch.zeros(N, K, device="cuda")
-        tiles = ((N + 127) // 128) * ((K + 127) // 128)
-        split = max(1, min((M + 63) // 64, 148 // max(1, tiles)))
         bn = a.bn if a.bn else 128
         width = bn % 1000
         rows = 256 if bn >= 1000 else 128
         tiles = ((N + rows - 1) // rows) * ((K + width - 1) // width)
         units = 74 if bn >= 1000 else 148
         split = max(1, min((M + 63) // 64, units // max(1, tiles)))
-        fn = lambda: gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, split_k=split, bn=bn)
+        if a.bn:
+            fn = lambda: gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, split_k=split, bn=bn)
+        else:       # tile width and split as the model's linears choose them
+            from .blocks import wgrad_accumulate
+            fn = lambda: wgrad_accumulate(dy, x, out)
         nbytes = (M * N + M * K) * 2 + N * K * 4
     else:
         x = _rand(M, K)

@@ -107,8 +107,8 @@ def case_tp_gemm(a, rank, world, dev, which):
     from .tp_fused import TpFusedComm
 
     pk = peaks()
-    for nk in a.nk:
-        for M in a.m:
+    for nk in a.width:
+        for M in a.tokens:
             rows = M // world
             Ns = nk // world
             arena = SymmetricArena(dist.group.WORLD, rows * nk * 2 * 2 + world * rows * nk * 2 * 2 + (64 << 20), dev)
@@ -222,8 +222,8 @@ def main(argv=None):
     ap.add_argument("--widths", type=int, nargs="+", default=[1440, 4320])
     ap.add_argument("--channels", type=int, nargs="+", default=[192, 384, 768])
     ap.add_argument("--rows", type=int, default=8)
-    ap.add_argument("--m", type=int, nargs="+", default=[4096, 16384, 65536, 262144])
-    ap.add_argument("--nk", type=int, nargs="+", default=[1536, 3072])
+    ap.add_argument("--tokens", type=int, nargs="+", default=[4096, 16384, 65536, 262144])
+    ap.add_argument("--width", type=int, nargs="+", default=[1536, 3072])
     ap.add_argument("--mb", type=int, nargs="+", default=[16, 64, 256, 1024, 4096])
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)

@@ -62,6 +62,33 @@ def test_gemm_epilogues():
     check_status("cuda")
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(40000, 800, 128, 128), (33001, 384, 384, 192), (20010, 1536, 384, 256),
+                                      (3000, 64, 64, 0), (29000, 416, 256, 192)])
+def test_gemm_epilogues_over_many_tiles(M, N, K, bn):
+    """Every CTA runs several tiles (the epilogue's operand prefetch crosses tile boundaries), the last row tile is
+    ragged and, where N is not a multiple of the tile width, the last column tile is narrow."""
+    from terra_b200.ops.gemm import gemm, check_status
+
+    torch.manual_seed(5)
+    a, b = _rand(M, K), _rand(N, K, scale=0.05)
+    bias, res, aux = _rand(N), _rand(M, N), _rand(M, N)
+    acc = a.float() @ b.float().t()
+    ref = acc + bias.float()
+    out, pre = gemm(a, b, bias=bias, gelu=True, save_pre=True, bn=bn)
+    _close(pre, ref)
+    _close(out, torch.nn.functional.gelu(ref))
+    _close(gemm(a, b, bias=bias, residual=res, bn=bn), ref + res.float())
+    _close(gemm(a, b, bias=bias, bn=bn), ref)
+    x = aux.float().requires_grad_(True)
+    torch.nn.functional.gelu(x).sum().backward()
+    _close(gemm(a, b, dgelu_aux=aux, bn=bn), acc * x.grad)
+    view = torch.zeros(M, N + 64, device="cuda", dtype=torch.bfloat16)      # output rows with a pitch wider than N
+    gemm(a, b, bias=bias, out=view[:, 32:32 + N], bn=bn)
+    _close(view[:, 32:32 + N], ref)
+    assert float(view[:, :32].abs().max()) == 0.0 and float(view[:, 32 + N:].abs().max()) == 0.0
+    check_status("cuda")
+
+
 def test_gemm_dgrad_b_mnmajor():
     from terra_b200.ops.gemm import gemm, check_status
 
