@@ -347,7 +347,7 @@ int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, i
   std::memset(&p, 0, sizeof(p));
   const int Ho = (stride == 1) ? H : (H + 1) / 2;
   const int Wo = (stride == 1) ? W : W / 2;
-  const int bn = pick_bn(Cin, 128);
+  const int bn = pick_bn(Cin, Cin % 192 == 0 ? 192 : 128);   // 384 input channels: two tiles of 192, a fifth less operand traffic per flop
   p.M = Cout;
   p.N = Cin;
   p.pix_n0 = (Wo + GEMM_BK - 1) / GEMM_BK;

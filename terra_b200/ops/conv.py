@@ -148,11 +148,24 @@ class _Conv3x3Fn(torch.autograd.Function):
         return dx, dw, db, None, None
 
 
+def balanced_split(tiles: int, kblocks: int, sms: int = 148, limit: int = 64) -> int:
+    """Split-K factor for a persistent kernel of ``sms`` CTAs: the one whose ``tiles * split`` work items fill whole
+    rounds of CTAs best (time ~ ceil(tiles * split / sms) / split), the smaller factor on near ties (every split adds
+    one pass of fp32 atomics over the output)."""
+    best, best_cost = 1, float("inf")
+    for s in range(1, max(1, min(kblocks, limit)) + 1):
+        cost = -(-tiles * s // sms) / s + 0.002 * s
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
 def _wgrad_split(B, H, W, stride, Cout, Cin):
     Ho, Wo = (H, W) if stride == 1 else ((H + 1) // 2, W // 2)
     kblocks = B * Ho * ((Wo + 63) // 64)
-    tiles = 9 * ((Cout + 127) // 128) * ((Cin + 127) // 128)
-    return max(1, min(kblocks, (148 + tiles - 1) // tiles))
+    bn = 192 if Cin % 192 == 0 else 128            # the tile width conv3x3_wgrad picks
+    tiles = 9 * ((Cout + 127) // 128) * ((Cin + bn - 1) // bn)
+    return balanced_split(tiles, kblocks)
 
 
 def _conv3x3_s2_dgrad(dy, w16, H, W, dom, weight=None):

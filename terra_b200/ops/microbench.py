@@ -147,8 +147,8 @@ def case_conv(a):
     if a.wgrad:
         dy = _rand(B, Ho, Wo, C, scale=0.1)
         dw = torch.zeros(9, C, C, device="cuda")
-        tiles = 9 * ((C + 127) // 128) ** 2
-        split = max(1, (148 + tiles - 1) // tiles)
+        from .conv import _wgrad_split
+        split = a.split if a.split else _wgrad_split(B, H, W, a.stride, C, C)      # the model's choice
         fn = lambda: ext.conv3x3_wgrad(x, dy, dw, a.stride, split, status_word("cuda"), None, None)
         nbytes = (x.numel() + dy.numel()) * 2
     else:
@@ -230,6 +230,7 @@ def main(argv=None):
     ap.add_argument("--w", type=int, default=544)
     ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--wgrad", action="store_true")
+    ap.add_argument("--split", type=int, default=0, help="split-K factor of the convolution weight gradient (0: the model's choice)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--launches", type=int, default=0)
     ap.add_argument("--no-time", action="store_true")

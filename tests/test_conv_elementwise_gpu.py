@@ -47,7 +47,7 @@ def test_conv3x3_fwd(B, H, W, Cin, Cout, stride):
 
 
 @pytest.mark.parametrize("B,H,W,Cin,Cout,stride", [(1, 16, 64, 64, 128, 1), (2, 13, 200, 96, 96, 1), (1, 16, 64, 128, 64, 2),
-                                                    (1, 33, 272, 96, 96, 2)])
+                                                    (1, 33, 272, 96, 96, 2), (1, 20, 136, 384, 384, 1), (1, 21, 144, 192, 128, 2)])
 def test_conv3x3_wgrad(B, H, W, Cin, Cout, stride):
     from terra_b200 import _ext
     from terra_b200.ops.gemm import status_word, check_status
