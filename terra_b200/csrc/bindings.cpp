@@ -37,7 +37,7 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
           int64_t split_k, int64_t bn, const c10::optional<torch::Tensor>& status, int64_t shuffle_cout,
           int64_t out_w, int64_t out_h, int64_t sms, const std::vector<int64_t>& a_peer_ptrs, int64_t rank,
           const std::vector<int64_t>& c_peer_ptrs, int64_t a_flags_ptr, int64_t a_epoch, int64_t a_budget_ns,
-          int64_t a_interleave, int64_t a_chunks) {
+          int64_t a_interleave, int64_t a_chunks, const c10::optional<torch::Tensor>& colsum) {
   check_bf16_2d(a, "a");
   check_bf16_2d(b, "b");
   const c10::cuda::CUDAGuard guard(a.device());
@@ -70,6 +70,11 @@ void gemm(const torch::Tensor& a, bool a_mn, const torch::Tensor& b, bool b_mn, 
   e.shuffle_cout = static_cast<int>(shuffle_cout);
   e.out_w = static_cast<int>(out_w);
   e.out_h = static_cast<int>(out_h);
+  if (colsum.has_value()) {
+    TORCH_CHECK(colsum->scalar_type() == torch::kFloat32 && colsum->is_contiguous() && colsum->numel() == M,
+                "gemm: colsum must be contiguous fp32 with one entry per output row");
+    e.colsum = colsum->data_ptr<float>();
+  }
   tb::note_launch();
   tb::GemmPeers peers;
   std::memset(&peers, 0, sizeof(peers));
@@ -128,16 +133,20 @@ void conv3x3_fwd(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& 
 // dw: [9, Cout, Cin] fp32 (zeroed by the caller)
 void conv3x3_wgrad(const torch::Tensor& x, const torch::Tensor& dy, torch::Tensor& dw, int64_t stride, int64_t split_k,
                    const c10::optional<torch::Tensor>& status, const c10::optional<torch::Tensor>& halo_lo,
-                   const c10::optional<torch::Tensor>& halo_hi) {
+                   const c10::optional<torch::Tensor>& halo_hi, const c10::optional<torch::Tensor>& bias_grad) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 4, "x: NHWC bf16");
   TORCH_CHECK(dy.scalar_type() == torch::kBFloat16 && dy.is_contiguous() && dy.dim() == 4, "dy: NHWC bf16");
+  TORCH_CHECK(!bias_grad.has_value() || (bias_grad->scalar_type() == torch::kFloat32 && bias_grad->is_contiguous() &&
+                                         bias_grad->numel() == dy.size(3)),
+              "bias_grad: contiguous fp32 [Cout]");
   TORCH_CHECK(dw.scalar_type() == torch::kFloat32 && dw.is_contiguous(), "dw: fp32 [9,Cout,Cin]");
   const c10::cuda::CUDAGuard guard(x.device());
   tb::note_launch();
   const int rc = tb::conv3x3_wgrad_bf16(x.data_ptr(), dy.data_ptr(), dw.data_ptr<float>(), x.size(0), x.size(1),
                                         x.size(2), x.size(3), dy.size(3), static_cast<int>(stride),
                                         static_cast<int>(split_k), status.has_value() ? status->data_ptr() : nullptr,
-                                        sm_count(), cur_stream(), opt_ptr(halo_lo), opt_ptr(halo_hi));
+                                        sm_count(), cur_stream(), opt_ptr(halo_lo), opt_ptr(halo_hi),
+                                        bias_grad.has_value() ? bias_grad->data_ptr<float>() : nullptr);
   TORCH_CHECK(rc == 0, "terra_b200 conv3x3_wgrad launch failed, code ", rc);
 }
 
@@ -156,9 +165,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     std::vector<int64_t> out(v, v + 8);
     return out;
   });
-  m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogues");
+  namespace py = pybind11;
+  m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogues", py::arg("a"), py::arg("a_mn"), py::arg("b"),
+        py::arg("b_mn"), py::arg("c"), py::arg("flags"), py::arg("bias"), py::arg("residual"), py::arg("aux"),
+        py::arg("c2"), py::arg("alpha"), py::arg("split_k"), py::arg("bn"), py::arg("status"), py::arg("shuffle_cout"),
+        py::arg("out_w"), py::arg("out_h"), py::arg("sms"), py::arg("a_peer_ptrs"), py::arg("rank"),
+        py::arg("c_peer_ptrs"), py::arg("a_flags_ptr"), py::arg("a_epoch"), py::arg("a_budget_ns"),
+        py::arg("a_interleave"), py::arg("a_chunks"), py::arg("colsum") = py::none());
   m.def("conv3x3_fwd", &conv3x3_fwd, "implicit-GEMM 3x3 convolution (NHWC bf16)");
-  m.def("conv3x3_wgrad", &conv3x3_wgrad, "3x3 convolution weight gradient (fp32 atomics)");
+  m.def("conv3x3_wgrad", &conv3x3_wgrad, "3x3 convolution weight gradient (fp32 atomics)", py::arg("x"), py::arg("dy"),
+        py::arg("dw"), py::arg("stride"), py::arg("split_k"), py::arg("status"), py::arg("halo_lo"), py::arg("halo_hi"),
+        py::arg("bias_grad") = py::none());
   bind_elementwise(m);
   bind_attention(m);
   bind_copy_engine(m);

@@ -133,6 +133,7 @@ static void fill_epilogue(GemmParams& p, const GemmEpilogue& e) {
   p.ldaux = e.ldaux;
   p.alpha = e.alpha;
   p.status = static_cast<KernelStatus*>(e.status);
+  p.colsum = e.colsum;
 }
 
 int gemm_bf16(const GemmOperand& A, const GemmOperand& B, long long M, long long N, long long K,
@@ -171,6 +172,11 @@ int gemm_bf16_peers(const GemmOperand& A, const GemmOperand& B, long long M, lon
       ctas = 2;
       if (bn_request == 0) bn_request = (N % 256 == 0 || N >= 1024) ? 256 : 128;
     }
+  }
+  if (epi.colsum != nullptr) {
+    // column sums ride on the weight-gradient form only, and need room for their accumulators behind the tile's
+    if (!A.mn_major || (epi.flags & EPI_BIAS) || !(epi.flags & EPI_ATOMIC) || ctas != 1 || gather_a || scatter_c) return -15;
+    if (bn_request == 256 || (bn_request == 0 && pick_bn(N, 0) == 256)) bn_request = (N % 192 == 0) ? 192 : 128;
   }
   const int bn = pick_bn(N, bn_request);
   p.M = static_cast<int>(M);
@@ -339,7 +345,7 @@ int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin,
 //   = sum over output pixels of dy[pix][Cout]^T * x[pix shifted by tap][Cin].
 int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, int W, int Cin, int Cout, int stride,
                        int split_k, void* status, int num_sms, cudaStream_t stream, const void* halo_lo,
-                       const void* halo_hi) {
+                       const void* halo_hi, float* bias_grad) {
   if (stride != 1 && stride != 2) return -11;
   if (stride == 2 && (W % 2 != 0)) return -12;
   if (Cin % 8 != 0 || Cout % 8 != 0) return -13;
@@ -408,6 +414,7 @@ int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, i
   }
   p.grp_c_stride = static_cast<long long>(Cout) * Cin;
   p.epi = EPI_OUT_F32 | EPI_ATOMIC;
+  p.colsum = bias_grad;
   p.C = dw;
   p.ldc = Cin;
   p.alpha = 1.0f;

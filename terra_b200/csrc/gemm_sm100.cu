@@ -60,7 +60,10 @@ struct GemmCfg {
   }
   static constexpr int smem_bytes(int bufs) { return stages_for(bufs) * STAGE_BYTES + fixed_bytes(bufs) + 1024; }   // + alignment slack
   // two accumulators; the allocation must be a power of two
-  static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  // behind them two 32-column accumulators of the column sums (weight-gradient form with a bias gradient, BN <= 192)
+  static constexpr int SUM_COL0 = 2 * BN;
+  static constexpr int TMEM_COLS = (2 * BN + 64 <= 256) ? 256 : 512;
+  static constexpr bool CAN_COLSUM = CTAS == 1 && 2 * BN + 64 <= 512;
   static_assert(stages_for(3) >= 3 && smem_bytes(1) <= MAX_SMEM && smem_bytes(3) <= MAX_SMEM, "shared memory budget");
   static_assert(GEMM_EPI_WARPS * 32 * 4 + BAR_BYTES <= FIXED_BASE, "bias slots");
   static_assert(CTAS == 1 || (B_ROWS % 64 == 0), "a CTA's half of B must be whole 64-row boxes");
@@ -152,6 +155,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
   if (warp == 1) {
     tmem_alloc<Cfg::TMEM_COLS, CTAS>(tmem_slot);
     tmem_relinquish<CTAS>();
+  }
+  if (Cfg::CAN_COLSUM && p.colsum != nullptr && threadIdx.x >= 64 && threadIdx.x < 64 + 128) {
+    // 16 x 16 tile of ones (four 128-byte core matrices) in the bias slots, which this form does not use
+    reinterpret_cast<uint32_t*>(bias_slots)[threadIdx.x - 64] = 0x3F803F80u;
+    fence_proxy_async_smem();
   }
   tc_fence_before();
   if (PAIR) cluster_sync_all(); else __syncthreads();   // barriers and allocations of both CTAs exist from here on
@@ -295,6 +303,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       const uint32_t a_lbo = a_mn ? GEMM_BK * 128 : 16, b_lbo = b_mn ? GEMM_BK * 128 : 16;
       const uint32_t a_kstep = a_mn ? (16 * 128) >> 4 : 32 >> 4;   // descriptor units of 16 bytes
       const uint32_t b_kstep = b_mn ? (16 * 128) >> 4 : 32 >> 4;
+      const uint32_t idesc_sums = make_idesc_bf16(GEMM_BM, 16, a_mn, 0);
+      const uint64_t d_ones = make_smem_desc_plain(smem_u32(bias_slots), 128, 256);
       int s = 0;
       uint32_t ph = 0, tcount = 0;
       const long long t_begin = clock64();
@@ -308,6 +318,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         t_acc += clock64() - w0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const bool sums = Cfg::CAN_COLSUM && p.colsum != nullptr && tc.n_blk == 0 && tc.grp == 0;
+        const uint32_t d_sums = tmem_base + Cfg::SUM_COL0 + acc * 32;
         bool ok = true;
         for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
           const long long w1 = clock64();
@@ -322,6 +334,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 #pragma unroll
           for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
             umma_bf16<CTAS>(d_tmem, da + kk * a_kstep, db + kk * b_kstep, idesc, (kb > tc.kb_begin || kk > 0) ? 1u : 0u);
+          }
+          if (sums) {   // column sums of A: the same A tiles against 16 columns of ones
+#pragma unroll
+            for (int kk = 0; kk < GEMM_BK / 16; ++kk)
+              umma_bf16<CTAS>(d_sums, da + kk * a_kstep, d_ones, idesc_sums, (kb > tc.kb_begin || kk > 0) ? 1u : 0u);
           }
           umma_commit<CTAS>(&empty[s]);     // frees stage s (in both CTAs of a pair)
         }
@@ -764,6 +781,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         } else {
           store_chunk(static_cast<__nv_bfloat16*>(p.C) + gofs, p.ldc, cb, f);
         }
+      }
+      if (Cfg::CAN_COLSUM && p.colsum != nullptr && tc.n_blk == 0 && tc.grp == 0 && part == 0) {
+        uint32_t v[32];   // column 0 of the sums accumulator: lane l holds the sum of A's column (row of D) q * 32 + l
+        tmem_ld_32x32(tmem_base + Cfg::SUM_COL0 + acc * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+        tmem_ld_wait();
+        const int g = tc.m_blk * GEMM_BM + q * 32 + lane;
+        if (g < p.M) atomicAdd(p.colsum + g, __uint_as_float(v[0]) * p.alpha);
       }
       tc_fence_before();
       __syncwarp();

@@ -74,6 +74,7 @@ struct GemmParams {
   // the epilogue reads (residual, or the GELU input of the backward pass) arrives through map_in, loaded two chunks
   // ahead into per-warp buffers. epi_bufs = buffers of 2 KB per epilogue warp (1: output staging; 3: + two inputs).
   // stages / smem_bytes: the launcher sizes the operand ring with what the epilogue buffers leave.
+  float* colsum;               // weight-gradient form: += column sums of operand A over the contraction (see GemmEpilogue)
   CUtensorMap map_c, map_c2, map_in;
   int epi_tma;
   int epi_bufs;

@@ -23,6 +23,10 @@ struct GemmEpilogue {
   float alpha;
   int out_w, out_h, shuffle_cout;
   void* status;       // KernelStatus* (device), may be null
+  // Weight-gradient form (A read MN-major, fp32 atomic output): also accumulate the sums of A's columns over the
+  // contraction (sum over tokens of dy[token][n], the bias gradient) into colsum[n] (fp32), from an extra
+  // 16-column MMA against a tile of ones. Null: off. Tile widths up to 192.
+  float* colsum;
 };
 
 // Tensor-parallel fusions over peer memory. a_ptr[i]: GPU i's [a_rows, K] bf16 shard (K-major, leading dimension of
@@ -61,7 +65,7 @@ int conv3x3_fwd_bf16(const void* x, const void* w, int B, int H, int W, int Cin,
                      const void* halo_hi = nullptr);
 int conv3x3_wgrad_bf16(const void* x, const void* dy, float* dw, int B, int H, int W, int Cin, int Cout, int stride,
                        int split_k, void* status, int num_sms, cudaStream_t stream, const void* halo_lo = nullptr,
-                       const void* halo_hi = nullptr);
+                       const void* halo_hi = nullptr, float* bias_grad = nullptr);   // bias_grad[Cout] += sums of dy
 
 // elementwise.cu -------------------------------------------------------------------------------
 // LayerNorm over the last dimension (C <= 8192, C % 8 == 0), bf16 in/out, fp32 statistics.

@@ -12,6 +12,8 @@ backward. On CPU the same math is plain PyTorch (autograd does the rest); that p
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import torch
@@ -26,19 +28,32 @@ from ..utils.nvtx import nvtx_range
 LN_EPS = 1e-5
 
 
+# Bias gradients come out of the weight-gradient GEMM itself (3 ms of an 88 ms step against the separate column-sum
+# kernel, measured back to back on one GPU); TERRA_FUSED_BIAS_GRAD=0 restores the separate kernel.
+FUSE_BIAS_GRAD = os.environ.get("TERRA_FUSED_BIAS_GRAD", "1") == "1"
+
+
 def _split_k_for(m_tiles_n_tiles: int, k_blocks: int, sms: int = 148) -> int:
     """Enough K splits to fill the GPU once, never more than the number of 64-wide k-blocks."""
     want = max(1, sms // max(1, m_tiles_n_tiles))
     return max(1, min(want, k_blocks))
 
 
-def wgrad_accumulate(dy: torch.Tensor, x: torch.Tensor, grad_w: torch.Tensor) -> None:
-    """grad_w[N, K] (fp32) += dy[M, N]^T @ x[M, K]."""
+def wgrad_accumulate(dy: torch.Tensor, x: torch.Tensor, grad_w: torch.Tensor, grad_b: torch.Tensor = None) -> None:
+    """grad_w[N, K] (fp32) += dy[M, N]^T @ x[M, K]; with ``grad_b``: grad_b[N] (fp32) += column sums of dy, from the
+    same kernel (a 16-column MMA of the dy tiles against ones), which saves the separate pass over dy."""
     N, K = grad_w.shape
-    bn = 256 if (K % 256 == 0 and K >= 1024) else (192 if K % 192 == 0 else 128)
+    if grad_b is not None and not FUSE_BIAS_GRAD:
+        bias_grad_accumulate(dy, grad_b)
+        grad_b = None
+    wide = K % 256 == 0 and K >= 1024 and (grad_b is None or K % 192 != 0)     # the sums need tile widths <= 192
+    bn = 256 if wide else (192 if K % 192 == 0 else 128)
     tiles = ((N + 127) // 128) * ((K + bn - 1) // bn)
     split = _split_k_for(tiles, (dy.shape[0] + 63) // 64)
-    gemm(dy, x, a_mn=True, b_mn=True, out=grad_w, accumulate=True, split_k=split, bn=bn)
+    if grad_b is not None and bn == 256:
+        bias_grad_accumulate(dy, grad_b)
+        grad_b = None
+    gemm(dy, x, a_mn=True, b_mn=True, out=grad_w, accumulate=True, split_k=split, bn=bn, colsum=grad_b)
 
 
 def bias_grad_accumulate(dy: torch.Tensor, grad_b: torch.Tensor) -> None:
@@ -107,8 +122,7 @@ class _AttnHalfFn(torch.autograd.Function):
         num_heads, shifted, use_mask, scale = ctx.args
         C = x.shape[1]
         dy = dy.contiguous()
-        wgrad_accumulate(dy, o, pk.proj_wg)
-        bias_grad_accumulate(dy, pk.proj_bg)
+        wgrad_accumulate(dy, o, pk.proj_wg, pk.proj_bg)
         if comm is not None:
             do = comm.alloc_dout(x.shape[0], C)
             gemm(dy, pk.proj_w, b_mn=True, out=do)
@@ -122,8 +136,7 @@ class _AttnHalfFn(torch.autograd.Function):
                                use_mask and shifted, scale, x.device)
         if comm is not None:
             dqkv = comm.attn_backward_done(dqkv, shifted)
-        wgrad_accumulate(dqkv, xn, pk.qkv_wg)
-        bias_grad_accumulate(dqkv, pk.qkv_bg)
+        wgrad_accumulate(dqkv, xn, pk.qkv_wg, pk.qkv_bg)
         dxn = gemm(dqkv, pk.qkv_w, b_mn=True)
         dx = layernorm_bwd_cuda(dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
         return dx, None, None, None, None, None, None, None, None
@@ -144,11 +157,9 @@ class _MlpHalfFn(torch.autograd.Function):
         x, mean, rstd, xn, pre, act = ctx.saved_tensors
         pk = ctx.pk
         dy = dy.contiguous()
-        wgrad_accumulate(dy, act, pk.fc2_wg)
-        bias_grad_accumulate(dy, pk.fc2_bg)
+        wgrad_accumulate(dy, act, pk.fc2_wg, pk.fc2_bg)
         dpre = gemm(dy, pk.fc2_w, b_mn=True, dgelu_aux=pre, bn=256 if pk.fc2_w.shape[1] % 256 == 0 else 0)
-        wgrad_accumulate(dpre, xn, pk.fc1_wg)
-        bias_grad_accumulate(dpre, pk.fc1_bg)
+        wgrad_accumulate(dpre, xn, pk.fc1_wg, pk.fc1_bg)
         dxn = gemm(dpre, pk.fc1_w, b_mn=True)
         dx = layernorm_bwd_cuda(dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
         return dx, None, None
@@ -170,9 +181,7 @@ class _LinearFn(torch.autograd.Function):
         (x,) = ctx.saved_tensors
         w16, wg, bg, has_res, need_dx = ctx.p
         dy = dy.contiguous()
-        wgrad_accumulate(dy, x, wg)
-        if bg is not None:
-            bias_grad_accumulate(dy, bg)
+        wgrad_accumulate(dy, x, wg, bg)
         dx = gemm(dy, w16, b_mn=True) if need_dx else None
         return dx, None, None, None, None, None, (dy if has_res else None), None
 

@@ -21,7 +21,7 @@ import torch.nn.functional as TF
 from .. import _ext
 from . import _flags as F
 from .gemm import gemm, status_word
-from .blocks import wgrad_accumulate, bias_grad_accumulate
+from .blocks import FUSE_BIAS_GRAD, wgrad_accumulate, bias_grad_accumulate
 from ..utils.nvtx import nvtx_range
 
 GN_EPS = 1e-5
@@ -122,7 +122,9 @@ class _Conv3x3Fn(torch.autograd.Function):
         if gw is not None:
             # tap-major staging [9, Cout, Cin] (persistent, self-cleaning) folded into the arena's (Cout, Cin, 3, 3) view
             dw9 = _zero_scratch(x.device, (9, Cout, Cin), "conv3x3")
-            ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device), lo, hi)
+            # the bias gradient (column sums of dy) comes out of the same kernel
+            ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device), lo, hi,
+                              bias_grad=gb if FUSE_BIAS_GRAD else None)
             ext.strided_add(dw9, gw, 1, Cin * 9, 9, True)
             dw = None
         else:
@@ -130,7 +132,8 @@ class _Conv3x3Fn(torch.autograd.Function):
             ext.conv3x3_wgrad(x, dy, dw9, stride, _wgrad_split(B, H, W, stride, Cout, Cin), status_word(x.device), lo, hi)
             dw = dw9.view(3, 3, Cout, Cin).permute(2, 3, 0, 1)
         if gb is not None:
-            ext.colsum(dy.view(-1, Cout), gb)
+            if gw is None or not FUSE_BIAS_GRAD:
+                ext.colsum(dy.view(-1, Cout), gb)
             db = None
         else:
             db = torch.zeros(Cout, device=x.device, dtype=torch.float32)

@@ -69,6 +69,7 @@ def gemm(
     a_budget_ns: int = 0,
     a_interleave: bool = True,
     a_chunks: int = 1,
+    colsum: Optional[torch.Tensor] = None,
 ):
     """Returns ``out`` (and the saved pre-activation when ``save_pre``).
 
@@ -77,7 +78,9 @@ def gemm(
     NVLink inside the GEMM (all-gather -> GEMM). With ``out_peers`` (pointers of every GPU's fp32 ``[M / n, N]``
     accumulation buffer, ``out`` being this GPU's) the result rows are reduced into their owner's buffer from the
     epilogue (GEMM -> reduce-scatter). With ``a_flags`` / ``a_epoch`` the kernel itself waits for each peer's
-    "shard written" signal instead of a barrier in front of it. ``out_peers`` with a bf16 ``out`` (shape
+    "shard written" signal instead of a barrier in front of it. ``colsum`` (fp32, one entry per output row; the
+    weight-gradient form ``a_mn and b_mn`` with ``accumulate``): the sums of ``a``'s columns over the contraction, i.e.
+    the bias gradient, are accumulated into it by the same kernel. ``out_peers`` with a bf16 ``out`` (shape
     ``[n, M / n, N]``): plain stores into this GPU's slot of the owners' staging, which the owner sums."""
     ext = _ext.load()
     M = a.shape[1] if a_mn else a.shape[0]
@@ -119,7 +122,7 @@ def gemm(
               file=sys.stderr, flush=True)
     ext.gemm(a, a_mn, b, b_mn, out, flags, bias, residual, dgelu_aux, pre, float(alpha), int(split_k), int(bn),
              status_word(a.device), 0, 0, 0, int(sms), list(a_peers or []), int(rank), list(out_peers or []),
-             int(a_flags), int(a_epoch), int(a_budget_ns), int(bool(a_interleave)), int(a_chunks))
+             int(a_flags), int(a_epoch), int(a_budget_ns), int(bool(a_interleave)), int(a_chunks), colsum)
     if save_pre:
         return out, pre
     return out

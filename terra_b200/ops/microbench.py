@@ -80,7 +80,8 @@ def case_gemm(a):
             fn = lambda: gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, split_k=split, bn=bn)
         else:       # tile width and split as the model's linears choose them
             from .blocks import wgrad_accumulate
-            fn = lambda: wgrad_accumulate(dy, x, out)
+            gb = torch.zeros(N, device="cuda") if a.colsum else None      # bias gradient from the same kernel
+            fn = lambda: wgrad_accumulate(dy, x, out, gb)
         nbytes = (M * N + M * K) * 2 + N * K * 4
     else:
         x = _rand(M, K)
@@ -230,6 +231,7 @@ def main(argv=None):
     ap.add_argument("--w", type=int, default=544)
     ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--wgrad", action="store_true")
+    ap.add_argument("--colsum", action="store_true", help="weight-gradient GEMM: also produce the bias gradient")
     ap.add_argument("--split", type=int, default=0, help="split-K factor of the convolution weight gradient (0: the model's choice)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--launches", type=int, default=0)

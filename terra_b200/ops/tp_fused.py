@@ -322,8 +322,7 @@ class _TpAttnHalfFn(torch.autograd.Function):
             xn_s = comm.stage(xn_saved)
             comm.arena.barrier()
             xn_full = _gather_rows(comm, xn_s)
-        wgrad_accumulate(dqkv, xn_full, pk.qkv_wg)
-        bias_grad_accumulate(dqkv, pk.qkv_bg)
+        wgrad_accumulate(dqkv, xn_full, pk.qkv_wg, pk.qkv_bg)
         # d(norm1 output) = reduce-scatter(dqkv @ qkv_w): GEMM -> reduce-scatter (the adjoint of the all-gather)
         dxn = comm.gemm_rs(dqkv, pk.qkv_w, b_mn=True)
         dx = layernorm_bwd_cuda(dxn[:rows] if short else dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
@@ -378,8 +377,7 @@ class _TpMlpHalfFn(torch.autograd.Function):
             xn_s = comm.stage(xn_saved)
             comm.arena.barrier()
             xn_full = _gather_rows(comm, xn_s)
-        wgrad_accumulate(dpre, xn_full, pk.fc1_wg)
-        bias_grad_accumulate(dpre, pk.fc1_bg)
+        wgrad_accumulate(dpre, xn_full, pk.fc1_wg, pk.fc1_bg)
         dxn = comm.gemm_rs(dpre, pk.fc1_w, b_mn=True)
         dx = layernorm_bwd_cuda(dxn[:rows] if short else dxn, x, pk.ln_w, mean, rstd, pk.ln_wg, pk.ln_bg, dres=dy)
         return dx, None, None, None, None

@@ -58,8 +58,10 @@ def test_conv3x3_wgrad(B, H, W, Cin, Cout, stride):
     Ho, Wo = (H, W) if stride == 1 else ((H + 1) // 2, W // 2)
     dy = _rand(B, Ho, Wo, Cout, scale=0.3)
     dw = torch.zeros(9, Cout, Cin, device="cuda", dtype=torch.float32)
-    ext.conv3x3_wgrad(x, dy, dw, stride, 16, status_word("cuda"), None, None)
+    db = torch.zeros(Cout, device="cuda")
+    ext.conv3x3_wgrad(x, dy, dw, stride, 16, status_word("cuda"), None, None, bias_grad=db)
     check_status("cuda")
+    _close(db, dy.float().sum((0, 1, 2)))
     xr = x.float().permute(0, 3, 1, 2).requires_grad_(False)
     wr = torch.zeros(Cout, Cin, 3, 3, device="cuda", requires_grad=True)
     TF.conv2d(xr, wr, None, stride=stride, padding=1).backward(dy.float().permute(0, 3, 1, 2))

@@ -112,6 +112,22 @@ def test_gemm_wgrad_both_mnmajor(split_k):
     _close(dw, dy.float().t() @ x.float())
 
 
+@pytest.mark.parametrize("M,N,K,bn,split_k", [(5000, 384, 1536, 192, 7), (3000, 1152, 384, 192, 1), (4100, 200, 96, 128, 5),
+                                              (2000, 48, 64, 64, 3)])
+def test_gemm_wgrad_with_fused_column_sums(M, N, K, bn, split_k):
+    """dW = dy^T x and, from the same kernel, db = column sums of dy (a 16-column MMA of the dy tiles against ones)."""
+    from terra_b200.ops.gemm import gemm, check_status
+
+    torch.manual_seed(6)
+    dy, x = _rand(M, N, scale=0.1), _rand(M, K, scale=0.1)
+    dw = torch.zeros(N, K, device="cuda")
+    db = torch.full((N,), 0.5, device="cuda")          # accumulated into, not overwritten
+    gemm(dy, x, a_mn=True, b_mn=True, out=dw, accumulate=True, split_k=split_k, bn=bn, colsum=db)
+    check_status("cuda")
+    _close(dw, dy.float().t() @ x.float())
+    _close(db, 0.5 + dy.float().sum(0))
+
+
 def test_gemm_large_matches_and_times():
     from terra_b200.ops.gemm import gemm, check_status
 
