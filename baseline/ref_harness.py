@@ -169,38 +169,63 @@ def _run(args, cfg, ClockSampler, metric, layout=None):
     dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     clocks = sampler.stop()
 
-    extra = None
+    line = {
+        "metric": metric, "value": 1.0 / (ms * 1e-3), "unit": "samples/s", "n_gpus": n, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 autocast, fp32 parameters", "data": "synthetic", "impl": "reference",
+        "config": {"model": f"credit_hierarchical_swin {H}x{W}x{C} p{p} D{D} layers {layers} heads {heads} ws{ws}",
+                   "global_batch": 1, "parallelism": f"wp{n}" if n > 1 else "sequential",
+                   "deviations": "single num_heads (reference is single-stage); grid passed to constructors; timm shim",
+                   "l2_policy": "inputs (3.3 GB each) larger than L2, two batches alternated"},
+        "clocks": clocks,
+        "e2e": {"value": 1.0 / (e2e_ms.item() * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms.item(),
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
+        "loss": last_loss, "e2e_loss": e2e_loss,
+    }
     if layout is not None:
+        # The main number is measured; the factorised build must not be able to lose it. An exception is reported in
+        # the line; a rank that stops answering is turned into an orderly exit of every rank by the deadline.
         import gc
+        import threading
 
+        key = "layout_" + "x".join(str(v) for v in layout)
+        name = "wg{}xsp{}xtp{}".format(*layout)
+        deadline = float(getattr(args, "extra_deadline", 420.0))
+        printed = threading.Lock()
+
+        def give_up():
+            if printed.acquire(blocking=False):
+                line[key] = {"layout": name, "unavailable": f"no result within {deadline} s"}
+                if rank == 0:
+                    _emit(line)
+                os._exit(0)
+
+        timer = threading.Timer(deadline, give_up)
+        timer.daemon = True
+        timer.start()
         del step
         gc.collect()
         torch.cuda.empty_cache()
+        failed = False
         try:
             step2, _ = build(layout)
             ms2, loss2 = time_device(step2, devb)
-            extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms2, "samples_per_s": 1.0 / (ms2 * 1e-3),
+            extra = {"layout": name, "ms_per_step": ms2, "samples_per_s": 1.0 / (ms2 * 1e-3),
                      "loss": loss2, "optimizer": "reference DistributedAdamW (optimizer_config 6)"}
         except Exception as exc:   # the main number stands even if the factorised build cannot run
             import traceback
 
             traceback.print_exc(file=sys.stderr)
-            extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+            extra = {"layout": name, "unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+            failed = True
+        if not printed.acquire(blocking=False):
+            return
+        timer.cancel()
+        line[key] = extra
+        if failed:                 # other ranks may sit in a collective: leave without another one
+            if rank == 0:
+                _emit(line)
+            os._exit(0)
     if rank == 0:
-        line = {
-            "metric": metric, "value": 1.0 / (ms * 1e-3), "unit": "samples/s", "n_gpus": n, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16 autocast, fp32 parameters", "data": "synthetic", "impl": "reference",
-            "config": {"model": f"credit_hierarchical_swin {H}x{W}x{C} p{p} D{D} layers {layers} heads {heads} ws{ws}",
-                       "global_batch": 1, "parallelism": f"wp{n}" if n > 1 else "sequential",
-                       "deviations": "single num_heads (reference is single-stage); grid passed to constructors; timm shim",
-                       "l2_policy": "inputs (3.3 GB each) larger than L2, two batches alternated"},
-            "clocks": clocks,
-            "e2e": {"value": 1.0 / (e2e_ms.item() * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms.item(),
-                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
-            "loss": last_loss, "e2e_loss": e2e_loss,
-        }
-        if extra is not None:
-            line["layout_" + "x".join(str(v) for v in layout)] = extra
         _emit(line)
     dist.destroy_process_group()

@@ -23,6 +23,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -48,6 +49,8 @@ def flagship_config(n_gpus: int, small: bool = False, layout=None) -> dict:
     cfg = _flagship_config(n_gpus, small)
     if layout is not None:
         wg, sp, tp = layout
+        if small:                         # head counts every sp x tp of the smoke layouts divides
+            cfg.update(embedding_dim=128, num_heads=[4, 8])
         cfg.update(xfmr_wp_topo=f"({wg}, 1)", xfmr_sp_size=sp, tensor_parallel_size=tp, optimizer_config=6)
     return cfg
 
@@ -198,24 +201,6 @@ def run_ours(args):
     check_status(dev)
     seq_len = trainer.archi["padded_shape"][0] // 8 * (trainer.archi["padded_shape"][1] // 8)
 
-    # ---- the factorised layout of the same model and data (window groups x sequence parallel x tensor parallel, sharded
-    #      AdamW): the step in which the fused tensor-parallel GEMMs and the sequence-parallel K/V gather run
-    extra = None
-    layout = parse_layout(args.extra_layout, args.gpus)
-    if layout is not None:
-        trainer.release()
-        del trainer
-        gc.collect()
-        torch.cuda.empty_cache()
-        t2 = Trainer(flagship_config(args.gpus, args.small, layout), data_parallel_group_size=1)
-        ms2, launches2, loss2 = _time_device_steps(t2, devb, args.steps, args.warmup, barrier)
-        check_status(dev)
-        pc = t2.model.pctx
-        extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms2, "samples_per_s": 1.0 / (ms2 * 1e-3),
-                 "gpu_launches": launches2, "loss": loss2, "optimizer": "DistributedAdamW (optimizer_config 6)",
-                 "fused_tp": getattr(pc, "tp_comm", None) is not None, "fused_attn": pc.fused_comm is not None}
-        trainer = t2
-
     gb = 1
     par = f"wp{args.gpus}" if args.gpus > 1 else "single"
     line = {
@@ -233,11 +218,51 @@ def run_ours(args):
                                            "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches), "loss": last_loss, "e2e_loss": e2e_loss,
     }
-    if extra is not None:
-        line["layout_" + "x".join(str(v) for v in layout)] = extra
+
+    # ---- the factorised layout of the same model and data (window groups x sequence parallel x tensor parallel, sharded
+    #      AdamW): the step in which the fused tensor-parallel GEMMs and the sequence-parallel K/V gather run. The
+    #      headline above is already measured: whatever happens here (an exception, or a rank that stops answering,
+    #      which the deadline turns into an orderly exit of every rank), rank 0 still prints it.
+    layout = parse_layout(args.extra_layout, args.gpus)
+    if layout is not None:
+        key = "layout_" + "x".join(str(v) for v in layout)
+        printed = threading.Lock()
+
+        def give_up():
+            if printed.acquire(blocking=False):
+                line[key] = {"error": f"no result within {args.extra_deadline} s"}
+                if rank == 0:
+                    print(json.dumps(line), flush=True)
+                os._exit(0)
+
+        timer = threading.Timer(args.extra_deadline, give_up)
+        timer.daemon = True
+        timer.start()
+        try:
+            trainer.release()
+            del trainer
+            gc.collect()
+            torch.cuda.empty_cache()
+            trainer = Trainer(flagship_config(args.gpus, args.small, layout), data_parallel_group_size=1)
+            ms2, launches2, loss2 = _time_device_steps(trainer, devb, args.steps, args.warmup, barrier)
+            check_status(dev)
+            pc = trainer.model.pctx
+            extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms2, "samples_per_s": 1.0 / (ms2 * 1e-3),
+                     "gpu_launches": launches2, "loss": loss2, "optimizer": "DistributedAdamW (optimizer_config 6)",
+                     "fused_tp": getattr(pc, "tp_comm", None) is not None, "fused_attn": pc.fused_comm is not None}
+        except Exception as exc:      # reported in the line; the ranks leave without further collectives
+            extra = {"error": repr(exc)[:300]}
+            trainer = None
+        if not printed.acquire(blocking=False):
+            return                    # the deadline fired meanwhile and is printing
+        timer.cancel()
+        line[key] = extra
     if rank == 0:
         print(json.dumps(line), flush=True)
-    trainer.close()
+    if trainer is not None:
+        trainer.close()
+    else:
+        os._exit(0)
 
 
 def run_reference(args):
@@ -258,6 +283,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test of the harness, not a benchmark)")
     ap.add_argument("--skip-e2e", action="store_true", help="only the device-timed loop (used when profiling)")
+    ap.add_argument("--extra-deadline", type=float, default=420.0,
+                    help="seconds after which the extra layout is given up and the headline printed without it")
     ap.add_argument("--extra-layout", default=None,
                     help='also time the factorised layout "wg,sp,tp" of the same model (default: 2,2,2 on 8 GPUs; "none")')
     args = ap.parse_args()
