@@ -23,7 +23,6 @@ import statistics
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -220,49 +219,80 @@ def run_ours(args):
     }
 
     # ---- the factorised layout of the same model and data (window groups x sequence parallel x tensor parallel, sharded
-    #      AdamW): the step in which the fused tensor-parallel GEMMs and the sequence-parallel K/V gather run. The
-    #      headline above is already measured: whatever happens here (an exception, or a rank that stops answering,
-    #      which the deadline turns into an orderly exit of every rank), rank 0 still prints it.
+    #      AdamW): the step in which the fused tensor-parallel GEMMs and the sequence-parallel K/V gather run. Every rank
+    #      runs it in a child process of its own (a fresh CUDA context, process group and rendezvous port, as a separate
+    #      launch would have) and waits for it no longer than the deadline; the headline above is already measured and is
+    #      printed whatever the child does.
     layout = parse_layout(args.extra_layout, args.gpus)
+    trainer.close()                       # frees the model; destroys the process group
+    del trainer, devb
+    gc.collect()
+    torch.cuda.empty_cache()
     if layout is not None:
-        key = "layout_" + "x".join(str(v) for v in layout)
-        printed = threading.Lock()
-
-        def give_up():
-            if printed.acquire(blocking=False):
-                line[key] = {"error": f"no result within {args.extra_deadline} s"}
-                if rank == 0:
-                    print(json.dumps(line), flush=True)
-                os._exit(0)
-
-        timer = threading.Timer(args.extra_deadline, give_up)
-        timer.daemon = True
-        timer.start()
-        try:
-            trainer.release()
-            del trainer
-            gc.collect()
-            torch.cuda.empty_cache()
-            trainer = Trainer(flagship_config(args.gpus, args.small, layout), data_parallel_group_size=1)
-            ms2, launches2, loss2 = _time_device_steps(trainer, devb, args.steps, args.warmup, barrier)
-            check_status(dev)
-            pc = trainer.model.pctx
-            extra = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms2, "samples_per_s": 1.0 / (ms2 * 1e-3),
-                     "gpu_launches": launches2, "loss": loss2, "optimizer": "DistributedAdamW (optimizer_config 6)",
-                     "fused_tp": getattr(pc, "tp_comm", None) is not None, "fused_attn": pc.fused_comm is not None}
-        except Exception as exc:      # reported in the line; the ranks leave without further collectives
-            extra = {"error": repr(exc)[:300]}
-            trainer = None
-        if not printed.acquire(blocking=False):
-            return                    # the deadline fired meanwhile and is printing
-        timer.cancel()
-        line[key] = extra
+        line["layout_" + "x".join(str(v) for v in layout)] = _extra_layout_in_child(args, layout, rank)
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if trainer is not None:
-        trainer.close()
-    else:
-        os._exit(0)
+
+
+def _extra_layout_in_child(args, layout, rank):
+    """Runs ``bench.py --only-layout`` as a child of this rank; returns rank 0's result (or the reason there is none)."""
+    text = ",".join(str(v) for v in layout)
+    out = os.path.join(tempfile.gettempdir(), f"terra_bench_layout_{os.environ.get('MASTER_PORT', '0')}_{text.replace(',', 'x')}.json")
+    if rank == 0 and os.path.exists(out):
+        os.unlink(out)
+    env = dict(os.environ)
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 17)      # a rendezvous of its own
+    env.pop("TORCHELASTIC_RUN_ID", None)
+    cmd = [sys.executable, os.path.abspath(__file__), "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup",
+           str(args.warmup), "--only-layout", text, "--result-file", out] + (["--small"] if args.small else [])
+    try:
+        child = subprocess.Popen(cmd, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE, text=True)
+    except Exception as exc:
+        return {"error": f"could not start: {exc!r}"[:300]}
+    try:
+        _, err = child.communicate(timeout=args.extra_deadline)
+    except subprocess.TimeoutExpired:
+        child.kill()                      # the exact child started above
+        child.communicate()
+        return {"error": f"no result within {args.extra_deadline} s"}
+    if rank != 0:
+        return None
+    try:
+        with open(out) as f:
+            return json.load(f)
+    except Exception:
+        return {"error": f"child exit code {child.returncode}: {(err or '').strip()[-300:]}"}
+
+
+def run_layout_only(args):
+    """Child of ``run_ours``: the device-timed loop of one factorised layout; rank 0 writes the result file."""
+    import torch
+    import torch.distributed as dist
+
+    from terra_b200.api import Trainer
+    from terra_b200.ops.gemm import check_status
+
+    layout = parse_layout(args.only_layout, args.gpus)
+    trainer = Trainer(flagship_config(args.gpus, args.small, layout), data_parallel_group_size=1)
+    dev = trainer.device
+
+    def barrier():
+        if dist.is_initialized():
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    devb = [{k: v.to(dev, non_blocking=True) for k, v in trainer.synthetic_batch(sample=i).items()} for i in range(2)]
+    ms, launches, loss = _time_device_steps(trainer, devb, args.steps, args.warmup, barrier)
+    check_status(dev)
+    pc = trainer.model.pctx
+    if trainer.rank == 0:
+        result = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms, "samples_per_s": 1.0 / (ms * 1e-3),
+                  "gpu_launches": launches, "loss": loss, "optimizer": "DistributedAdamW (optimizer_config 6)",
+                  "fused_tp": getattr(pc, "tp_comm", None) is not None, "fused_attn": pc.fused_comm is not None}
+        with open(args.result_file + ".tmp", "w") as f:
+            json.dump(result, f)
+        os.replace(args.result_file + ".tmp", args.result_file)
+    trainer.close()
 
 
 def run_reference(args):
@@ -283,14 +313,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", action="store_true", help="tiny model (smoke test of the harness, not a benchmark)")
     ap.add_argument("--skip-e2e", action="store_true", help="only the device-timed loop (used when profiling)")
-    ap.add_argument("--extra-deadline", type=float, default=420.0,
+    ap.add_argument("--only-layout", default=None, help=argparse.SUPPRESS)     # child mode, see run_ours
+    ap.add_argument("--result-file", default=None, help=argparse.SUPPRESS)
+    ap.add_argument("--extra-deadline", type=float, default=300.0,
                     help="seconds after which the extra layout is given up and the headline printed without it")
     ap.add_argument("--extra-layout", default=None,
                     help='also time the factorised layout "wg,sp,tp" of the same model (default: 2,2,2 on 8 GPUs; "none")')
     args = ap.parse_args()
     if args.warmup < 3 and not args.small:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.only_layout:
+        run_layout_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
