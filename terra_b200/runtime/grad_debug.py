@@ -6,7 +6,11 @@
   serial and parallel runs can be compared line by line.
 * ``install_grad_hooks`` (env ``DEBUG_GRAD_HOOK=1``): per-parameter hooks that print the gradient sum at the moment
   autograd produces it, at most ``DEBUG_GRAD_HOOK_PRINT_LIMIT`` lines. With the flat parameter arena the hook reads
-  the arena's gradient view, which the fused kernels accumulate into directly."""
+  the arena's gradient view, which the fused kernels accumulate into directly.
+* ``report_arena_gradients``: the CUDA form of the same switch. The fused kernels write parameter gradients into the
+  flat gradient arena without autograd ever producing a leaf gradient, so no hook fires there; instead the step
+  prints, right after the backward pass, the gradient sum of every parameter from the arena's views (one
+  device-side reduction over the arena segments, one host transfer), under the same line limit."""
 from __future__ import annotations
 
 from typing import Iterable, List, Optional
@@ -85,3 +89,27 @@ def install_grad_hooks(model, limit: Optional[int] = None, printer=print):
 
         handles.append(p.register_hook(hook))
     return handles
+
+
+_arena_lines = {"n": 0}
+
+
+def report_arena_gradients(model, limit: Optional[int] = None, printer=print) -> List[str]:
+    """Per-parameter gradient sums from the flat gradient arena (``DEBUG_GRAD_HOOK=1`` on CUDA, where gradients are
+    accumulated in place by the kernels and autograd hooks do not fire). At most ``limit`` lines over the run."""
+    limit = G.DEBUG_GRAD_HOOK_PRINT_LIMIT if limit is None else limit
+    if _arena_lines["n"] >= limit:
+        return []
+    named = [(n, p) for n, p in model.named_parameters() if p.requires_grad and _grad_of(p) is not None]
+    if not named:
+        return []
+    sums = torch.stack([_grad_of(p).detach().double().sum() for _, p in named]).cpu()      # one transfer
+    lines = []
+    for (name, _), v in zip(named, sums.tolist()):
+        if _arena_lines["n"] >= limit:
+            break
+        _arena_lines["n"] += 1
+        lines.append(f"[grad hook] {name}: {v:+.8e}")
+    for ln in lines:
+        printer(ln)
+    return lines

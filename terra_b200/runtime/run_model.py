@@ -11,6 +11,7 @@ import time
 import torch
 import torch.distributed as dist
 
+from .. import global_env_config as G
 from ..profiler.memory_timeline import mark_memory_timeline
 from .run_one_step import (backbone_run, cal_loss, fused_forward_loss, grad_post_process, loss_post_process,
                            loss_scale_factor, loss_scale_of, optimizer_step)
@@ -92,6 +93,10 @@ def one_step_train(task_type, model_type, model, engine, optimizer, required_ten
         from .grad_debug import show_gradient
 
         show_gradient(model, manager, getattr(manager, "xfmr_tp_group", None) if manager is not None else None)
+    if on_cuda and G.DEBUG_GRAD_HOOK:
+        from .grad_debug import report_arena_gradients
+
+        report_arena_gradients(model)
     mark_memory_timeline("before_optimizer")
     optimizer_step(model, optimizer, gscaler, precision, clip_grad, on_cuda, scale)
     optimizer.global_step += 1

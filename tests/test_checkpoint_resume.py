@@ -1,7 +1,8 @@
 """Checkpoint save -> resume round trips through the entry points themselves (CPU / gloo ranks):
 
 * ``train.py`` on the serial model (``ckpt_layout: single``), on two window-parallel ranks with a replicated
-  optimizer (``wp_rank``) and with the sharded optimizer (``rank_local``): two epochs in one run must give the same
+  optimizer (``wp_rank``), with the sharded optimizer (``rank_local``) and with the reference's FSDP configurations
+  (``fsdp_full``, ``fsdp_sharded``): two epochs in one run must give the same
   losses as one epoch, a save, and a second run that resumes from it;
 * ``finetune.py``: step checkpoints (``save_interval_steps``) and resuming from ``ckpt_step``.
 
@@ -58,21 +59,36 @@ def _base(name, tmp_path, run):
     ("tiny_seq_cpu.yaml", 1, 4, "single"),
     ("tiny_para_wp2.yaml", 2, 4, "wp_rank"),
     ("tiny_para_wp2.yaml", 2, 6, "rank_local"),
+    ("tiny_para_wp2.yaml", 2, 7, "fsdp_full"),           # the reference's FSDP configurations: one gathered file ...
+    ("tiny_para_wp2.yaml", 2, 7, "fsdp_sharded"),        # ... or every rank's own ranges of masters and moments
 ])
 def test_pretrain_resume_matches_uninterrupted_run(tmp_path, name, nproc, opt, layout):
-    whole = dict(_base(name, tmp_path, "whole"), optimizer_config=opt, num_pre_train_epochs=2)
+    extra = {"fsdp_checkpoint_type": layout[len("fsdp_"):]} if layout.startswith("fsdp_") else {}
+    whole = dict(_base(name, tmp_path, "whole"), optimizer_config=opt, num_pre_train_epochs=2, **extra)
     _run("train.py", whole, tmp_path, "whole", nproc)
-    first = dict(_base(name, tmp_path, "parts"), optimizer_config=opt, num_pre_train_epochs=1)
+    first = dict(_base(name, tmp_path, "parts"), optimizer_config=opt, num_pre_train_epochs=1, **extra)
     _run("train.py", first, tmp_path, "first", nproc)
     # the cosine schedule depends on the planned number of epochs: keep it equal to the uninterrupted run's
     first_log = os.path.join(first["train_path"], first["description"], "loss", "rank0.txt")
     assert len(_losses(first_log)) == 2
     d = os.path.join(first["train_path"], first["description"], "ckpt")
-    sub = {"single": "", "wp_rank": "wp_rank_0", "rank_local": "rank_0"}[layout]
+    sub = {"single": "", "wp_rank": "wp_rank_0", "rank_local": "rank_0", "fsdp_full": "",
+           "fsdp_sharded": os.path.join("fsdp_sharded", "rank_0")}[layout]
     blob = torch.load(os.path.join(d, sub, "epoch0.pth"), map_location="cpu", weights_only=False)
     assert blob["ckpt_layout"] == layout and blob["epoch"] == 0 and blob["global_step"] == 2
     assert set(blob) >= {"model_state_dict", "optimizer_state_dict", "loss", "epoch", "global_step", "ckpt_layout"}
-    if layout != "single":
+    if layout == "fsdp_full":
+        # one file, optimizer state in torch.optim.AdamW's per-parameter layout with whole-parameter tensors
+        st = blob["optimizer_state_dict"]["state"]
+        shapes = [tuple(v.shape) for v in blob["model_state_dict"].values()]
+        assert all(tuple(e["exp_avg"].shape) in shapes for e in st.values()) and len(st) > 10
+        assert not os.path.exists(os.path.join(d, "rank_1")) and not os.path.exists(os.path.join(d, "fsdp_sharded"))
+    elif layout == "fsdp_sharded":
+        ranges = blob["model_state_dict"]["__flat_ranges__"]
+        owned = sum(r["hi"] - r["lo"] for r in ranges)
+        assert 0 < owned < blob["model_state_dict"]["__numel__"], "a rank's file holds only the ranges it owns"
+        assert os.path.exists(os.path.join(d, "fsdp_sharded", "rank_1", "epoch0.pth"))
+    elif layout != "single":
         other = {"wp_rank": "wp_rank_1", "rank_local": "rank_1"}[layout]
         assert os.path.exists(os.path.join(d, other, "epoch0.pth")), "every owner rank writes its own file"
     second = dict(first, num_pre_train_epochs=2, ckpt_start=True, ckpt_epoch=0)

@@ -77,7 +77,7 @@ class Session:
 
         if G.DEBUG_GRAD_HOOK and self.device.type != "cuda":
             # (on CUDA the fused kernels accumulate into the flat gradient arena without autograd leaf gradients;
-            # there `show_gradient_flag` prints the arena's sums after the backward pass instead)
+            # there the step itself prints the arena's per-parameter sums after the backward pass)
             from terra_b200.runtime.grad_debug import install_grad_hooks
 
             self.grad_hooks = install_grad_hooks(self.model)

@@ -75,7 +75,7 @@ def main(argv=None):
     if c.get("ckpt_start", False):
         epoch, gstep, _ = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type, s.opt_state,
                                           s.manager, epoch=c.get("ckpt_epoch"), step=c.get("ckpt_step"), scaler=s.gscaler,
-                                          lead=lead)
+                                          lead=lead, model_config=c)
         start_epoch = epoch + (0 if c.get("ckpt_step") is not None else 1)
     loader = s.finetune_loader(lead, status=0)
     log_file = None
@@ -109,10 +109,11 @@ def main(argv=None):
             every = int(c.get("save_interval_steps") or 0)
             if every > 0 and s.optimizer.global_step % every == 0:
                 save_checkpoint(s.model, s.optimizer, last, epoch, c["train_path"], c["description"], s.model_type,
-                                s.opt_state, s.manager, s.gscaler, lead=lead, step=s.optimizer.global_step)
+                                s.opt_state, s.manager, s.gscaler, lead=lead, step=s.optimizer.global_step,
+                                model_config=c)
         if (epoch + 1) % int(c["save_interval_epochs"]) == 0:
             save_checkpoint(s.model, s.optimizer, last, epoch, c["train_path"], c["description"], s.model_type, s.opt_state,
-                            s.manager, s.gscaler, lead=lead)
+                            s.manager, s.gscaler, lead=lead, model_config=c)
     if log_file is not None:
         log_file.close()
     s.close()

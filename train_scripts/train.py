@@ -27,7 +27,7 @@ def main(argv=None):
     start_epoch = int(c.get("start_epoch", 0))
     if c.get("ckpt_start", False):
         epoch, gstep, _ = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type, s.opt_state,
-                                          s.manager, epoch=c["ckpt_epoch"], scaler=s.gscaler)
+                                          s.manager, epoch=c["ckpt_epoch"], scaler=s.gscaler, model_config=c)
         start_epoch = epoch + 1
     log_file = None
     if s.is_log_rank():
@@ -57,7 +57,7 @@ def main(argv=None):
                                f"forward_time_s {fwd_time:.4f}\n")
         if (epoch + 1) % int(c["save_interval_epochs"]) == 0:
             save_checkpoint(s.model, s.optimizer, last_loss, epoch, c["train_path"], c["description"], s.model_type,
-                            s.opt_state, s.manager, s.gscaler)
+                            s.opt_state, s.manager, s.gscaler, model_config=c)
     if log_file is not None:
         log_file.close()
     s.close()
