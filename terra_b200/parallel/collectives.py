@@ -2,12 +2,14 @@
 
 These are the portable building blocks of the multi-rank layouts and the baseline that the fused peer-memory
 kernels are measured against. Only primitives that gloo implements are used in the CPU branches
-(all_gather on lists, all_reduce, send/recv), so every multi-rank code path can be exercised without a GPU.
+(all_gather on lists, all_reduce, all_to_all_single, send/recv), so every multi-rank code path can be exercised without a GPU.
 
 Gradient conventions (the loss of the job is the SUM of the per-rank losses):
   all-gather        <->  reduce-scatter (sum)
   reduce-scatter    <->  all-gather
   all-reduce (sum)  <->  all-reduce (sum)
+  all-to-all        <->  all-to-all with the chunk extents swapped
+  ring transfer     <->  ring transfer in the opposite direction
   halo exchange     <->  halo gradients travel back and are added to the rows they were copied from
 """
 from __future__ import annotations
@@ -120,6 +122,69 @@ def all_reduce_sum(x, group):
     if group_size(group) == 1:
         return x
     return _AllReduceSum.apply(x, group)
+
+
+class _AllToAllRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, send_sizes, recv_sizes):
+        ctx.group, ctx.send_sizes, ctx.recv_sizes = group, send_sizes, recv_sizes
+        x = x.contiguous()
+        out = x.new_empty((sum(recv_sizes),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x, output_split_sizes=list(recv_sizes), input_split_sizes=list(send_sizes), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        # the adjoint sends every received chunk's gradient back where the chunk came from
+        return _AllToAllRows.apply(g.contiguous(), ctx.group, ctx.recv_sizes, ctx.send_sizes), None, None, None
+
+
+def all_to_all_rows(x, group, send_sizes: Optional[Sequence[int]] = None, recv_sizes: Optional[Sequence[int]] = None):
+    """The rows of ``x``, cut into one consecutive chunk per group rank (extents ``send_sizes``), travel to their rank;
+    returns the chunks received from every rank, concatenated in group-rank order (extents ``recv_sizes``). Defaults:
+    equal chunks. The Ulysses exchange of the sequence-parallel baseline and the all-to-all-v of a general relayout
+    (reference: core/tensor_parallel.py:291-356, core/parallel/layout_transform.py:107-173)."""
+    world = group_size(group)
+    if world == 1:
+        return x
+    if send_sizes is None:
+        if x.shape[0] % world:
+            raise ValueError(f"all_to_all_rows: {x.shape[0]} rows do not split evenly over {world} ranks")
+        send_sizes = [x.shape[0] // world] * world
+    if recv_sizes is None:
+        recv_sizes = list(send_sizes)
+    if sum(send_sizes) != x.shape[0] or len(send_sizes) != world or len(recv_sizes) != world:
+        raise ValueError("all_to_all_rows: chunk extents do not match the tensor / the group")
+    return _AllToAllRows.apply(x, group, list(send_sizes), list(recv_sizes))
+
+
+class _RingTransfer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, shift):
+        ctx.group, ctx.shift = group, shift
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        dst = dist.get_global_rank(group, (rank + shift) % world)
+        src = dist.get_global_rank(group, (rank - shift) % world)
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        reqs = dist.batch_isend_irecv([dist.P2POp(dist.isend, x, dst, group), dist.P2POp(dist.irecv, out, src, group)])
+        for r in reqs:
+            r.wait()
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return _RingTransfer.apply(g.contiguous(), ctx.group, -ctx.shift), None, None
+
+
+def ring_transfer(x, group, shift: int = 1):
+    """Every rank sends ``x`` to the rank ``shift`` places further along the group's ring and returns what it receives
+    from the rank ``shift`` places behind (same shape on every rank). Gradients travel the ring the other way
+    (reference: core/p2p_comm.py:4-71, the +-1 ring of the regular window-parallel shift)."""
+    world = group_size(group)
+    if world == 1 or shift % world == 0:
+        return x
+    return _RingTransfer.apply(x, group, int(shift))
 
 
 def all_reduce_(x: torch.Tensor, group) -> torch.Tensor:

@@ -14,6 +14,8 @@ With one rank every method degenerates to local index permutations.
 """
 from __future__ import annotations
 
+import os
+
 from typing import List, Optional
 
 import numpy as np
@@ -182,6 +184,8 @@ class ParallelContext:
             return None
         if self.fused_comm is not None and self.contiguous:
             return self.fused_comm
+        if self.n_wg == 1 and self.sp > 1 and os.environ.get("TERRA_SP_BASELINE", "ulysses") == "ulysses":
+            return _UlyssesAttnComm(self, batch)
         return _PortableAttnComm(self, batch)
 
     # ---- factorised SP / TP halves on portable collectives (CPU oracle path and the NCCL baseline)
@@ -430,3 +434,38 @@ class _PortableAttnComm:
         ids = torch.as_tensor(p.windows_of[p.wg_rank], device=qkv.device)
         mine = out[:, ids][:, :, p.sp_rank * sN:(p.sp_rank + 1) * sN]
         return mine.reshape(-1, C3 // 3)
+
+
+class _UlyssesAttnComm(_PortableAttnComm):
+    """Sequence-parallel window attention by head <-> token all-to-all (DeepSpeed-Ulysses, the reference's
+    ``WPUlyssesWindowAttention``: models/attention.py:795-819, 912-918; core/tensor_parallel.py:291-356): the token
+    shards of all windows are exchanged for head groups, every rank runs ordinary single-rank window attention on all
+    tokens of ``heads / sp`` heads, and a second all-to-all brings the outputs back to token shards. The collective
+    baseline of the peer-memory K/V gather (``comm_backend: nccl`` and gloo ranks), used when one window group spans
+    the set (``n_wg == 1``) and the local head count divides by ``sp``; otherwise the gather path of the base class
+    runs. ``TERRA_SP_BASELINE=gather`` forces the latter."""
+
+    def window_attention_portable(self, qkv, geo, num_heads, shifted, bias_table, use_mask, scale):
+        p, m = self.p, self.p.manager
+        sp, sN, N, Bn = p.sp, p.shardN, p.N, self.batch
+        if num_heads % sp != 0 or p.n_wg != 1:
+            return super().window_attention_portable(qkv, geo, num_heads, shifted, bias_table, use_mask, scale)
+        group = m.xfmr_tp_param_group                  # the sp ranks that share this TP rank (n_wg == 1)
+        nW = p.nWh * p.nWw
+        rows = Bn * nW * sN
+        Cl = qkv.shape[-1] // 3
+        Cd, hd = Cl // sp, Cl // num_heads
+        # head groups to their ranks: chunk d of the send buffer = (q | k | v) columns of head group d
+        q, k, v = qkv.reshape(rows, 3, sp, Cd).unbind(1)
+        send = torch.stack([q, k, v], dim=2).permute(1, 0, 2, 3).reshape(sp * rows, 3 * Cd)      # [d][row][q|k|v]
+        recv = C.all_to_all_rows(send.contiguous(), group)                                      # [source shard][row][q|k|v]
+        full = recv.reshape(sp, Bn, nW, sN, 3 * Cd).permute(1, 2, 0, 3, 4).reshape(Bn * nW * N, 3 * Cd)
+        mine = p.sp_rank * (num_heads // sp)
+        table = None if bias_table is None else bias_table[:, mine:mine + num_heads // sp]
+        gfull = WindowGeometry(Bn, p.nWh, p.nWw, p.wh, p.ww)
+        o = window_attention(full.contiguous(), gfull, num_heads // sp, shifted, table, use_mask, scale, None)
+        # token shards back to their ranks; the received head groups are concatenated along the channels
+        back = o.reshape(Bn, nW, sp, sN, Cd).permute(2, 0, 1, 3, 4).reshape(sp * rows, Cd)
+        got = C.all_to_all_rows(back.contiguous(), group)                                       # [head group][row][Cd]
+        assert hd * (num_heads // sp) == Cd
+        return got.reshape(sp, rows, Cd).permute(1, 0, 2).reshape(rows, Cl)

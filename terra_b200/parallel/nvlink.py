@@ -30,6 +30,8 @@ COMM_MAX_PEERS = 16
 PAD_BYTES = 4096            # signal pads at the start of every arena
 # time budget of a device-side wait on a peer (nanoseconds of the GPU's global timer); TERRA_PEER_WAIT_MS overrides
 BARRIER_SPIN_LIMIT = int(float(os.environ.get("TERRA_PEER_WAIT_MS", "5000")) * 1e6)
+# debugging aid: wipe the per-step region of every symmetric arena with NaN patterns at each reset (see reset())
+ARENA_POISON = os.environ.get("TERRA_ARENA_POISON", "0") == "1"
 
 
 def _symm():
@@ -95,7 +97,15 @@ class SymmetricArena:
 
     def reset(self) -> None:
         """Forget the per-step allocations (call between steps, when no kernel of the previous step is pending
-        on a peer: the last cross-rank access of a step is followed by a barrier)."""
+        on a peer: the last cross-rank access of a step is followed by a barrier).
+
+        ``TERRA_ARENA_POISON=1`` (race hunting): the region the step used is filled with 0xFF bytes first - NaN as
+        bf16 and as fp32 - so that a kernel which reads a peer buffer before its producer wrote it, or a buffer of
+        the previous step, turns the loss into NaN instead of silently using stale numbers. A barrier follows the
+        fill: a faster peer must not push the new step's rows into this region before it has been wiped."""
+        if ARENA_POISON and self.cursor > self.persistent_end:
+            self.buf[self.persistent_end:self.cursor].fill_(0xFF)
+            self.barrier()
         self.cursor = self.persistent_end
 
     def offset_of(self, t: torch.Tensor) -> int:

@@ -86,13 +86,13 @@ def _free_port():
     return port
 
 
-def _run(world, extra):
-    code = WORKER % dict(root=ROOT, cfg=BASE + extra)
+def _run(world, extra, code=None, **env_extra):
+    code = code if code is not None else WORKER % dict(root=ROOT, cfg=BASE + extra)
     port = _free_port()
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port), OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+                   MASTER_PORT=str(port), OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="", **env_extra)
         procs.append(subprocess.Popen([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
                                       text=True))
     results = []
@@ -121,3 +121,56 @@ def test_parallel_layout_matches_serial(world, extra):
         assert abs(res["loss"] - res["ref_loss"]) < 1e-4 * max(1.0, abs(res["ref_loss"])), res
         assert res["out_err"] < 2e-3, res
         assert res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res
+
+
+def test_sequence_parallel_gather_baseline_matches_serial():
+    """The sequence-parallel layouts above run the Ulysses all-to-all baseline (heads divisible by sp); the gather
+    baseline (every rank collects all q/k/v rows) must give the same numbers."""
+    extra = "wp_topo='(2, 1)', xfmr_wp_topo='(1, 1)', xfmr_sp_size=2, window_assignment_mode='terra_m1_ragged_auto'"
+    for res in _run(2, extra, TERRA_SP_BASELINE="gather"):
+        assert abs(res["loss"] - res["ref_loss"]) < 1e-4 * max(1.0, abs(res["ref_loss"])), res
+        assert res["out_err"] < 2e-3 and res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res
+
+
+COLLECTIVES = textwrap.dedent('''
+    import json, sys
+    sys.path.insert(0, %(root)r)
+    import torch, torch.distributed as dist
+    from terra_b200.distributed import init_distributed
+    from terra_b200.parallel import collectives as C
+
+    rank, world, _ = init_distributed("gloo")
+    g = dist.group.WORLD
+    torch.manual_seed(rank)
+    # ragged all-to-all: rank r sends r + d + 1 rows to rank d
+    send = [rank + d + 1 for d in range(world)]
+    recv = [s + rank + 1 for s in range(world)]
+    x = (torch.arange(sum(send) * 3, dtype=torch.float64).reshape(-1, 3) + 1000 * rank).requires_grad_(True)
+    y = C.all_to_all_rows(x, g, send, recv)
+    # what must arrive from source s: its chunk for me
+    ok = True
+    off = 0
+    for s in range(world):
+        s_send = [s + d + 1 for d in range(world)]
+        start = sum(s_send[:rank])
+        want = torch.arange(sum(s_send) * 3, dtype=torch.float64).reshape(-1, 3)[start:start + s_send[rank]] + 1000 * s
+        ok = ok and torch.equal(y[off:off + recv[s]].detach(), want)
+        off += recv[s]
+    # adjoint: d/dx sum_r <w_r, y_r> with w_r = (r + 1): the gradient of a row is the weight of the rank it went to
+    (y * (rank + 1)).sum().backward()
+    want_g = torch.cat([torch.full((send[d], 3), float(d + 1), dtype=torch.float64) for d in range(world)])
+    ok = ok and torch.equal(x.grad, want_g)
+    # ring: forward one place, gradient comes back one place
+    z = torch.full((2,), float(rank), dtype=torch.float64, requires_grad=True)
+    got = C.ring_transfer(z, g, 1)
+    ok = ok and torch.equal(got.detach(), torch.full((2,), float((rank - 1) %% world), dtype=torch.float64))
+    (got * (rank + 10)).sum().backward()
+    ok = ok and torch.equal(z.grad, torch.full((2,), float((rank + 1) %% world + 10), dtype=torch.float64))
+    print("RESULT " + json.dumps(dict(ok=bool(ok))), flush=True)
+    dist.destroy_process_group()
+''')
+
+
+def test_all_to_all_and_ring_transfer_with_their_adjoints():
+    for res in _run(3, "", code=COLLECTIVES % dict(root=ROOT)):
+        assert res["ok"], res
