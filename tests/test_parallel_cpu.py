@@ -174,3 +174,53 @@ COLLECTIVES = textwrap.dedent('''
 def test_all_to_all_and_ring_transfer_with_their_adjoints():
     for res in _run(3, "", code=COLLECTIVES % dict(root=ROOT)):
         assert res["ok"], res
+
+
+DIST_MATMUL = textwrap.dedent('''
+    import json, sys
+    sys.path.insert(0, %(root)r)
+    import torch, torch.distributed as dist
+    from terra_b200.distributed import init_distributed
+    from terra_b200.parallel import dist_matmul as D
+
+    rank, world, _ = init_distributed("gloo")
+    g = dist.group.WORLD
+    torch.manual_seed(0)                                    # the same full operands on every rank
+    T, IN, OUT = 12, 8, 6 * world
+    xf = torch.randn(T, IN, dtype=torch.float64)
+    wf = torch.randn(OUT, IN, dtype=torch.float64)
+    bf = torch.randn(OUT, dtype=torch.float64)
+    cot = torch.randn(T, OUT, dtype=torch.float64)          # cotangent of the full output
+    xr, wr, br = xf.clone().requires_grad_(True), wf.clone().requires_grad_(True), bf.clone().requires_grad_(True)
+    (D.full_reference(xr, wr, br) * cot).sum().backward()
+    worst = 0.0
+    for isplit in D.LAYOUTS:
+        for osplit in D.LAYOUTS:
+            x = D.shard(xf, isplit, rank, world).clone().requires_grad_(True)
+            wsplit = "(1,n)" if isplit == "(1,n)" else "(m,1)"
+            w = D.shard(wf, wsplit, rank, world).clone().requires_grad_(True)
+            # the bias is added once per output element: by everybody for column-sharded outputs (own columns), and
+            # for row-sharded outputs of a distributed contraction after the reduction (whole bias)
+            b = (D.shard(bf[None], "(1,n)", rank, world)[0] if osplit == "(1,n)" else bf).clone().requires_grad_(True)
+            y = D.xwt_apply(x, w, b, g, isplit, osplit)
+            want = D.shard(D.full_reference(xf, wf, bf), osplit, rank, world)
+            worst = max(worst, (y.detach() - want).abs().max().item())
+            (y * D.shard(cot, osplit, rank, world)).sum().backward()
+            worst = max(worst, (x.grad - D.shard(xr.grad, isplit, rank, world)).abs().max().item())
+            worst = max(worst, (w.grad - D.shard(wr.grad, wsplit, rank, world)).abs().max().item())
+            gb = b.grad.clone()
+            if osplit == "(m,1)":
+                dist.all_reduce(gb)                          # every rank saw only its rows
+                worst = max(worst, (gb - br.grad).abs().max().item())
+            else:
+                worst = max(worst, (gb - D.shard(br.grad[None], "(1,n)", rank, world)[0]).abs().max().item())
+    print("RESULT " + json.dumps(dict(worst=worst)), flush=True)
+    dist.destroy_process_group()
+''')
+
+
+def test_distributed_matmul_layouts_and_gradients():
+    """All four (input split, output split) layouts of the distributed X W^T against the undistributed product: the
+    output shard, and the shards of the input / weight / bias gradients (reference: core/dist_matmul.py:8-459)."""
+    for res in _run(2, "", code=DIST_MATMUL % dict(root=ROOT)):
+        assert res["worst"] < 1e-10, res
