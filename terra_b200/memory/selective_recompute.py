@@ -36,30 +36,42 @@ class SelectiveRecomputeScheduler:
         self.block_indices = {i for s, e in self.checkpoint_segments for i in range(s, e)}
 
     def set_checkpoint_layers(self, checkpoint_layers) -> None:
-        self.config["checkpoint_layers"] = checkpoint_layers
-        self.config.pop("checkpoint_segments", None)
-        self._rebuild()
+        self._replan(checkpoint_layers)
 
     def set_checkpoint_plan(self, checkpoint_layers, activation_mode=None, offload_config=None,
                             segment_activation_modes=None) -> None:
-        cfg = dict(self.config)
+        """Replace the plan between rollout leads: new layer entries and, optionally, a new default mode, offload
+        options and one mode per entry."""
+        changes = {}
         if activation_mode is not None:
-            cfg["mode"] = str(activation_mode)
+            changes["mode"] = str(activation_mode)
         if offload_config is not None:
-            cfg["offload"] = dict(offload_config)
-        cfg["checkpoint_layers"] = list(checkpoint_layers)
-        cfg.pop("checkpoint_segments", None)
+            changes["offload"] = dict(offload_config)
         if segment_activation_modes is not None:
-            modes = list(segment_activation_modes)
-            segs = self._from_entries(cfg["checkpoint_layers"])
-            if len(modes) != len(segs):
-                raise ValueError(f"segment_activation_modes must match checkpoint_layers: {len(modes)} != {len(segs)}")
-            cfg["layer_modes"] = {int(s): normalize_activation_mode(m) for (s, _), m in zip(segs, modes)}
-        new_cfg = normalize_activation_config(config=cfg)
-        self.config = new_cfg
-        self.enabled = bool(new_cfg.get("enabled", False))
-        self.mode = self.impl = new_cfg.get("mode", "none")
-        self.set_checkpoint_layers(checkpoint_layers)
+            changes["layer_modes"] = self._modes_by_first_block(checkpoint_layers, segment_activation_modes)
+        self._replan(checkpoint_layers, changes)
+
+    def _modes_by_first_block(self, entries, modes) -> Dict[int, str]:
+        """``{first block of segment i: mode i}`` - the form in which per-layer modes are stored."""
+        firsts = [start for start, _ in self._from_entries(list(entries))]
+        modes = list(modes)
+        if len(modes) != len(firsts):
+            raise ValueError(f"segment_activation_modes must match checkpoint_layers: {len(modes)} != {len(firsts)}")
+        return {int(b): normalize_activation_mode(m) for b, m in zip(firsts, modes)}
+
+    def _replan(self, checkpoint_layers, changes: Optional[dict] = None) -> None:
+        raw = {k: v for k, v in self.config.items() if k != "checkpoint_segments"}
+        raw["checkpoint_layers"] = list(checkpoint_layers) if changes is not None else checkpoint_layers
+        if changes:
+            raw.update(changes)
+            raw = normalize_activation_config(config=raw)
+            # the normaliser derives segments from the layer entries; the plan below is built from the entries themselves
+            raw["checkpoint_layers"] = checkpoint_layers
+            raw.pop("checkpoint_segments", None)
+            self.enabled = bool(raw.get("enabled", False))
+            self.mode = self.impl = raw.get("mode", "none")
+        self.config = raw
+        self._rebuild()
 
     # ------------------------------------------------------------------ planning
     def _sanitise(self, segments: Iterable[Tuple[int, int]]) -> List[Tuple[int, int]]:
@@ -123,13 +135,12 @@ class SelectiveRecomputeScheduler:
                 i += 1
 
     def summary(self) -> dict:
-        return {
-            "enabled": self.enabled, "mode": self.mode, "policy": self.policy, "depth": self.depth,
-            "input_resolution": self.input_resolution, "hidden_dim": self.hidden_dim,
-            "block_indices": sorted(self.block_indices),
-            "checkpoint_segments": [list(s) for s in self.checkpoint_segments],
-            "layer_modes": dict(sorted(self.config.get("layer_modes", {}).items())),
-            "segment_activation_modes": [self.config_for_block(s)["mode"] for s, _ in self.checkpoint_segments],
-            "sampling_checkpoint": dict(self.config.get("sampling_checkpoint", {"down": "none", "up": "none"})),
-            "sampling_modes": dict(self.config.get("sampling_modes", {})),
-        }
+        cfg = self.config
+        plan = {"block_indices": sorted(self.block_indices),
+                "checkpoint_segments": [list(seg) for seg in self.checkpoint_segments],
+                "segment_activation_modes": [self.config_for_block(first)["mode"] for first, _ in self.checkpoint_segments],
+                "layer_modes": dict(sorted(cfg.get("layer_modes", {}).items()))}
+        sampling = {"sampling_checkpoint": dict(cfg.get("sampling_checkpoint", {"down": "none", "up": "none"})),
+                    "sampling_modes": dict(cfg.get("sampling_modes", {}))}
+        shape = {name: getattr(self, name) for name in ("enabled", "mode", "policy", "depth", "input_resolution", "hidden_dim")}
+        return {**shape, **plan, **sampling}
