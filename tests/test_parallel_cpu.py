@@ -224,3 +224,41 @@ def test_distributed_matmul_layouts_and_gradients():
     output shard, and the shards of the input / weight / bias gradients (reference: core/dist_matmul.py:8-459)."""
     for res in _run(2, "", code=DIST_MATMUL % dict(root=ROOT)):
         assert res["worst"] < 1e-10, res
+
+
+LEGACY_EMB = textwrap.dedent('''
+    import json, sys
+    sys.path.insert(0, %(root)r)
+    import torch, torch.distributed as dist
+    from terra_b200.distributed import init_distributed
+    from terra_b200.models.legacy_embeddings import DomainParaPatchEmbedding, DomainParaPatchRecovery
+    from terra_b200.parallel.dist_matmul import shard
+
+    rank, world, _ = init_distributed("gloo")
+    g = dist.group.WORLD
+    worst = 0.0
+    for isplit, osplit in (("(1,n)", "(m,1)"), ("(m,1)", "(m,1)"), ("(m,1)", "(1,n)"), ("(1,n)", "(1,n)")):
+        torch.manual_seed(3)                                   # every rank draws the same full weights
+        full = torch.nn.Linear(4 * 4 * 3, 16)
+        torch.manual_seed(3)
+        emb = DomainParaPatchEmbedding(g, patch_size=4, num_channel=3, embedding_dim=16, input_split=isplit, output_split=osplit)
+        torch.manual_seed(9)
+        x = torch.randn(2, 8, 48)
+        xs = shard(x.reshape(-1, 48), isplit, rank, world)
+        y = emb(xs)
+        want = shard(full(x.reshape(-1, 48)), osplit, rank, world)
+        worst = max(worst, (y - want).abs().max().item())
+    torch.manual_seed(5)
+    full = torch.nn.Linear(16, 48)
+    torch.manual_seed(5)
+    rec = DomainParaPatchRecovery(g, patch_size=4, num_channel=3, embedding_dim=16, input_split="(m,1)", output_split="(1,n)")
+    h = torch.randn(16, 16)
+    worst = max(worst, (rec(shard(h, "(m,1)", rank, world)) - shard(full(h), "(1,n)", rank, world)).abs().max().item())
+    print("RESULT " + json.dumps(dict(worst=worst)), flush=True)
+    dist.destroy_process_group()
+''')
+
+
+def test_legacy_domain_parallel_embeddings_match_the_full_linear():
+    for res in _run(2, "", code=LEGACY_EMB % dict(root=ROOT)):
+        assert res["worst"] < 1e-5, res
