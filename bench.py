@@ -130,18 +130,24 @@ def _time_device_steps(trainer, devb, steps, warmup, barrier):
     from terra_b200 import _ext
 
     ext = _ext.load()
+    on_gpu = trainer.device.type == "cuda"
     for i in range(warmup):
         trainer.step_on_device(devb[i % 2])
     barrier()
     launches0 = ext.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
+    if on_gpu:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+    t0 = time.perf_counter()
     for i in range(steps):
         loss = trainer.step_on_device(devb[i % 2])
-    ev1.record()
+    if on_gpu:
+        ev1.record()
     barrier()
     launches = ext.launch_count() - launches0
-    ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=trainer.device)
+    # the host clock only where there is no device (the harness's own test on CPU ranks)
+    elapsed = ev0.elapsed_time(ev1) if on_gpu else (time.perf_counter() - t0) * 1e3
+    ms = torch.tensor([elapsed / steps], device=trainer.device)
     if dist.is_initialized():
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     return ms.item(), int(launches), float(loss.item())
@@ -166,7 +172,8 @@ def run_ours(args):
     def barrier():
         if live:
             dist.barrier()
-        torch.cuda.synchronize()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
 
     host = [trainer.synthetic_batch(sample=i) for i in range(2)]
     devb = [{k: v.to(dev, non_blocking=True) for k, v in b.items()} for b in host]
@@ -197,7 +204,8 @@ def run_ours(args):
         if live:
             dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     clocks = sampler.stop()
-    check_status(dev)
+    if dev.type == "cuda":
+        check_status(dev)
     seq_len = trainer.archi["padded_shape"][0] // 8 * (trainer.archi["padded_shape"][1] // 8)
 
     gb = 1
@@ -227,7 +235,8 @@ def run_ours(args):
     trainer.close()                       # frees the model; destroys the process group
     del trainer, devb
     gc.collect()
-    torch.cuda.empty_cache()
+    if dev.type == "cuda":
+        torch.cuda.empty_cache()
     if layout is not None:
         line["layout_" + "x".join(str(v) for v in layout)] = _extra_layout_in_child(args, layout, rank)
     if rank == 0:
@@ -242,7 +251,10 @@ def _extra_layout_in_child(args, layout, rank):
         os.unlink(out)
     env = dict(os.environ)
     env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 17)      # a rendezvous of its own
-    env.pop("TORCHELASTIC_RUN_ID", None)
+    for name in [k for k in env if k.startswith("TORCHELASTIC_")]:
+        # without TORCHELASTIC_USE_AGENT_STORE the child of rank 0 hosts the store on the new port itself (the launcher's
+        # agent store listens on the old one only)
+        env.pop(name)
     cmd = [sys.executable, os.path.abspath(__file__), "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup",
            str(args.warmup), "--only-layout", text, "--result-file", out] + (["--small"] if args.small else [])
     try:
@@ -279,11 +291,13 @@ def run_layout_only(args):
     def barrier():
         if dist.is_initialized():
             dist.barrier()
-        torch.cuda.synchronize()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
 
     devb = [{k: v.to(dev, non_blocking=True) for k, v in trainer.synthetic_batch(sample=i).items()} for i in range(2)]
     ms, launches, loss = _time_device_steps(trainer, devb, args.steps, args.warmup, barrier)
-    check_status(dev)
+    if dev.type == "cuda":
+        check_status(dev)
     pc = trainer.model.pctx
     if trainer.rank == 0:
         result = {"layout": "wg{}xsp{}xtp{}".format(*layout), "ms_per_step": ms, "samples_per_s": 1.0 / (ms * 1e-3),
