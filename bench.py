@@ -129,12 +129,12 @@ def _time_device_steps(trainer, devb, steps, warmup, barrier):
 
     from terra_b200 import _ext
 
-    ext = _ext.load()
     on_gpu = trainer.device.type == "cuda"
+    ext = _ext.load() if on_gpu else None          # the kernels (and their launch counter) exist on a GPU only
     for i in range(warmup):
         trainer.step_on_device(devb[i % 2])
     barrier()
-    launches0 = ext.launch_count()
+    launches0 = ext.launch_count() if on_gpu else 0
     if on_gpu:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
@@ -144,7 +144,7 @@ def _time_device_steps(trainer, devb, steps, warmup, barrier):
     if on_gpu:
         ev1.record()
     barrier()
-    launches = ext.launch_count() - launches0
+    launches = ext.launch_count() - launches0 if on_gpu else 0
     # the host clock only where there is no device (the harness's own test on CPU ranks)
     elapsed = ev0.elapsed_time(ev1) if on_gpu else (time.perf_counter() - t0) * 1e3
     ms = torch.tensor([elapsed / steps], device=trainer.device)
