@@ -18,3 +18,50 @@ def test_arena_gradient_report_lists_every_parameter_up_to_the_limit():
     assert abs(float(lines[0].split(": ")[1]) - want) <= 1e-7 * max(1.0, abs(want))      # the line prints 9 digits
     assert grad_debug.report_arena_gradients(net, limit=3, printer=seen.append) == []      # the limit holds over the run
     grad_debug._arena_lines["n"] = 0
+
+
+def test_memory_timeline_intervals_outputs_and_filters(tmp_path, monkeypatch):
+    """The timeline on a machine without a GPU records the event stream with zero sizes; with a stand-in for the
+    allocator readings it must attribute interval peaks to the closing event, keep the peaks its resets fold away,
+    merge the semantic context into events, and write CSV / summary / event table with hidden classes filtered."""
+    from terra_b200.profiler import memory_timeline as M
+
+    tl = M.CudaMemoryTimeline(None, enabled=True, output_dir=str(tmp_path), tag="t")
+    assert tl.force_cpu or tl.enabled
+    levels = iter([(10, 20, 10), (12, 20, 12), (30, 40, 55), (14, 40, 60), (14, 40, 14), (9, 40, 14), (9, 40, 14)])
+
+    def fake_snapshot():
+        a, r, p = next(levels)
+        return float(a), float(r), float(p), float(r) + 5.0, 5.0
+
+    monkeypatch.setattr(tl, "_snapshot", fake_snapshot)
+    M.set_memory_timeline_context(lead_idx=3, execution_phase="forward")
+    with tl.iteration(M.MEMORY_TIMELINE_OUTPUT_START_ITER):
+        occ = M.new_memory_timeline_occurrence("block0")
+        M.mark_memory_timeline("primitive_forward_pre", "block0", occurrence_id=occ, primitive_kind="transformer")
+        M.mark_memory_timeline("module_fwd_pre", "attn")                      # hidden class by default
+        M.mark_memory_timeline("primitive_forward_post", "block0", occurrence_id=occ, primitive_kind="transformer")
+        M.mark_memory_timeline("after_forward")
+        M.set_memory_timeline_context(execution_phase=None)
+        M.mark_memory_timeline("before_backward")
+    M.set_memory_timeline_context(lead_idx=None)
+    phases = [e["phase"] for e in tl.events]
+    assert phases == ["iter_start", "primitive_forward_pre", "module_fwd_pre", "primitive_forward_post", "after_forward",
+                      "before_backward", "iter_end"]
+    closer = tl.events[3]["meta"]
+    assert closer["interval_kind"] == "primitive_forward" and closer["interval_start_allocated_mib"] == 12.0
+    assert closer["interval_peak_allocated_mib"] == 60.0 and closer["interval_peak_rise_mib"] == 48.0
+    assert closer["lead_idx"] == 3 and closer["execution_phase"] == "forward"
+    assert "execution_phase" not in tl.events[5]["meta"]                      # removed from the context
+    assert tl.overall_peak_allocated_mib == 60.0 == tl.iteration_peak_allocated_mib
+    rows = tl.primitive_intervals()
+    assert len(rows) == 1 and rows[0]["interval_peak_mib"] == 60.0 and rows[0]["direction"] == "forward"
+    assert [e["phase"] for e in tl.visible_events()] == [p for p in phases if p != "module_fwd_pre"]
+    made = tl.write_outputs()
+    assert {"csv", "summary", "primitive_summary", "event_table"} <= set(made)
+    table = open(made["event_table"]).read()
+    assert "primitive_forward_post" in table and "module_fwd_pre" not in table and "rise +48.0" in table
+    assert "module_fwd_pre" in open(made["csv"]).read()                       # the CSV keeps every event
+    assert "overall_peak_allocated_mib: 60.0" in open(made["summary"]).read()
+    assert M.event_class("sampling_down_enter") == "sampling_boundary" and M.event_class("sampling_conv1") == "sampling_internal"
+    assert not M.memory_timeline_iteration_enabled(M.MEMORY_TIMELINE_OUTPUT_START_ITER + M.MEMORY_TIMELINE_OUTPUT_MAX_ITERS)

@@ -119,6 +119,7 @@ def main(argv=None):
         if dist.is_available() and dist.is_initialized() and s.model_type != "sequential":
             dist.all_reduce(out_sum, group=s.manager.window_parallel_group)
         peak = torch.cuda.max_memory_allocated(s.device) / 2 ** 20 if s.device.type == "cuda" else 0.0
+        peak = max(peak, timeline.iteration_peak_allocated_mib)      # peaks the timeline's interval resets folded away
         off = get_boundary_offload_stats()
         rows.append(dict(iter=i, lead_time=lead, loss=float(loss.item()), output_sum=float(out_sum.item()),
                          dtype=str(out.dtype), peak_memory_mb=peak, step_time_s=step_time, forward_time_s=fwd_time,
@@ -145,9 +146,7 @@ def main(argv=None):
                                offload=get_boundary_offload_stats(), final_loss=rows[-1]["loss"],
                                recompute=s.model.recompute_scheduler.summary()), f, indent=1, default=str)
         if mem_prof > 0 and timeline.events:
-            d = os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline")
-            timeline.write_csv(os.path.join(d, "finetune_timeline_rank0.csv"))
-            timeline.write_summary_csv(os.path.join(d, "finetune_primitive_summary_rank0.csv"))
+            timeline.write_outputs(os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline"), "finetune_rank0")
     s.close()
     return rows
 

@@ -74,6 +74,7 @@ def main(argv=None):
             if dist.is_available() and dist.is_initialized() and s.model_type != "sequential":
                 dist.all_reduce(out_sum, group=s.manager.window_parallel_group)
             peak = torch.cuda.max_memory_allocated(s.device) / 2 ** 20 if s.device.type == "cuda" else 0.0
+            peak = max(peak, timeline.iteration_peak_allocated_mib)      # peaks the timeline's interval resets folded away
             rows.append(dict(iter=i, loss=float(loss.item()), output_sum=float(out_sum.item()), dtype=str(out.dtype),
                              peak_memory_mb=peak, step_time_s=step_time, forward_time_s=fwd_time,
                              padded_h=s.archi["padded_shape"][0], padded_w=s.archi["padded_shape"][1],
@@ -103,10 +104,8 @@ def main(argv=None):
             with open(args.metrics_json, "w") as f:
                 json.dump(meta, f, indent=1)
         if mem_prof > 0 and timeline.events:
-            d = os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline")
-            timeline.write_csv(os.path.join(d, "timeline_rank0.csv"))
-            if mem_prof > 1:
-                timeline.write_summary_csv(os.path.join(d, "primitive_summary_rank0.csv"))
+            # CSV, summary, event table and plot as the MEMORY_TIMELINE_WRITE_* switches ask
+            timeline.write_outputs(os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline"), "rank0")
     s.close()
     return rows
 
