@@ -65,3 +65,22 @@ def test_memory_timeline_intervals_outputs_and_filters(tmp_path, monkeypatch):
     assert "overall_peak_allocated_mib: 60.0" in open(made["summary"]).read()
     assert M.event_class("sampling_down_enter") == "sampling_boundary" and M.event_class("sampling_conv1") == "sampling_internal"
     assert not M.memory_timeline_iteration_enabled(M.MEMORY_TIMELINE_OUTPUT_START_ITER + M.MEMORY_TIMELINE_OUTPUT_MAX_ITERS)
+
+
+def test_balanced_split_fills_whole_rounds_of_the_persistent_grid():
+    """Split-K policy of the convolution weight gradient: ``tiles * split`` work items over 148 persistent CTAs."""
+    from terra_b200.ops.conv import balanced_split
+
+    def rounds_per_unit_work(tiles, s):
+        return -(-tiles * s // 148) / s
+
+    # 54 tiles (9 taps x 3 x 2 at 384 channels): a split of 2 would run two rounds, the second nearly empty
+    s = balanced_split(54, 8704)
+    assert s == 8 and rounds_per_unit_work(54, s) < 0.38 < rounds_per_unit_work(54, 2)
+    assert balanced_split(81, 8704) == 9
+    assert balanced_split(148, 8704) == 1              # one full round already
+    assert balanced_split(54, 3) <= 3                   # never more splits than k-blocks
+    for tiles in (6, 18, 24, 48, 72, 81, 148, 149, 300):
+        s = balanced_split(tiles, 100000)
+        ideal = tiles / 148
+        assert rounds_per_unit_work(tiles, s) <= 1.15 * max(ideal, 1 / 64) + 1e-9, (tiles, s)
