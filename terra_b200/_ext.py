@@ -14,8 +14,12 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
+# TERRA_DEBUG_BOUNDS=1: the bounds-checked build of the kernels (indices that come from tables or from cross-rank
+# arithmetic are checked before the access and a violation is reported through the status word, see csrc/common.cuh).
+# It is a separate shared object in its own directory, so the two builds never mix.
+DEBUG_BOUNDS = os.environ.get("TERRA_DEBUG_BOUNDS", "0") == "1"
 # TERRA_B200_BUILD_DIR: use (and build into) another directory, e.g. to keep two builds of the kernels side by side
-BUILD_DIR = os.environ.get("TERRA_B200_BUILD_DIR") or os.path.join(_HERE, "_build")
+BUILD_DIR = os.environ.get("TERRA_B200_BUILD_DIR") or os.path.join(_HERE, "_build_debug" if DEBUG_BOUNDS else "_build")
 EXT_NAME = "terra_b200_C"
 
 CUDA_FLAGS = [
@@ -24,6 +28,9 @@ CUDA_FLAGS = [
     "-U__CUDA_NO_HALF_OPERATORS__", "-U__CUDA_NO_HALF_CONVERSIONS__",
     "-U__CUDA_NO_BFLOAT16_CONVERSIONS__", "-U__CUDA_NO_HALF2_OPERATORS__",
 ]
+
+if DEBUG_BOUNDS:
+    CUDA_FLAGS.append("-DTERRA_DEBUG_BOUNDS")
 
 _lock = threading.Lock()
 _module = None
@@ -54,7 +61,7 @@ def build(verbose: bool = False):
         mod = cpp_extension.load(
             name=EXT_NAME,
             sources=sources(),
-            extra_cflags=["-O3", "-std=c++17"],
+            extra_cflags=["-O3", "-std=c++17"] + (["-DTERRA_DEBUG_BOUNDS"] if DEBUG_BOUNDS else []),
             extra_cuda_cflags=CUDA_FLAGS,
             extra_include_paths=[CSRC],
             build_directory=BUILD_DIR,

@@ -93,7 +93,7 @@ void gather_shards_async(int64_t stream, int64_t dst, const std::vector<int64_t>
 }
 
 void peer_gather_indexed(torch::Tensor& dst, const std::vector<int64_t>& src_ptrs, const torch::Tensor& src_slot,
-                         const torch::Tensor& src_row) {
+                         const torch::Tensor& src_row, int64_t src_rows, const c10::optional<torch::Tensor>& status) {
   TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.dim() == 2, "peer_gather_indexed: dst [rows, cols] contiguous");
   TORCH_CHECK(src_slot.scalar_type() == torch::kInt32 && src_row.scalar_type() == torch::kInt32 && src_slot.is_cuda() &&
                   src_row.is_cuda() && src_slot.numel() == dst.size(0) && src_row.numel() == dst.size(0),
@@ -104,7 +104,7 @@ void peer_gather_indexed(torch::Tensor& dst, const std::vector<int64_t>& src_ptr
   tb::note_launch();
   TORCH_CHECK(tb::peer_gather_indexed(dst.data_ptr(), p.data(), static_cast<int>(p.size()), src_slot.data_ptr<int>(),
                                       src_row.data_ptr<int>(), dst.size(0), dst.size(1) * dst.element_size(),
-                                      cur_stream()) == 0,
+                                      cur_stream(), src_rows, status.has_value() ? status->data_ptr() : nullptr) == 0,
               "peer_gather_indexed launch failed");
 }
 
@@ -175,7 +175,8 @@ void stream_write_value(int64_t stream, int64_t addr, int64_t value) {
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
-  m.def("peer_gather_indexed", &peer_gather_indexed);
+  m.def("peer_gather_indexed", &peer_gather_indexed, pybind11::arg("dst"), pybind11::arg("src_ptrs"), pybind11::arg("src_slot"),
+        pybind11::arg("src_row"), pybind11::arg("src_rows") = -1, pybind11::arg("status") = pybind11::none());
   m.def("halo_push", &halo_push);
   m.def("peer_allreduce_small", &peer_allreduce_small);
   m.def("stream_wait_value", &stream_wait_value);

@@ -179,6 +179,19 @@ void grad_inspect(const torch::Tensor& grad, torch::Tensor& out2) {
 
 // Peer buffers are passed as raw device addresses (int64) so that symmetric-memory peers can be addressed;
 // for a single rank the lists hold one entry each.
+// Status word that the bounds-checked debug build of the attention kernels reports to (set once from Python).
+void* g_debug_status = nullptr;
+void set_debug_status(const c10::optional<torch::Tensor>& status) {
+  g_debug_status = status.has_value() ? status->data_ptr() : nullptr;
+}
+bool debug_bounds_build() {
+#ifdef TERRA_DEBUG_BOUNDS
+  return true;
+#else
+  return false;
+#endif
+}
+
 tb::WindowAttnArgs make_wa(const std::vector<int64_t>& win_start, int64_t my_wg, int64_t sp, int64_t my_sp,
                            int64_t shardN, int64_t B, int64_t nWh, int64_t nWw, int64_t C, int64_t heads, int64_t wh,
                            int64_t ww, int64_t sh, int64_t sw, bool use_mask, double scale, int64_t tp) {
@@ -192,6 +205,7 @@ tb::WindowAttnArgs make_wa(const std::vector<int64_t>& win_start, int64_t my_wg,
   a.wh = wh; a.ww = ww; a.sh = sh; a.sw = sw;
   a.use_mask = use_mask ? 1 : 0;
   a.scale = static_cast<float>(scale);
+  a.debug_status = g_debug_status;
   need(a.n_wg * a.sp <= tb::WA_MAX_PEERS, "window_attn: too many peer slots");
   return a;
 }
@@ -348,4 +362,6 @@ void bind_attention(pybind11::module_& m) {
   m.def("window_attn_tc_fwd", &window_attn_tc);
   m.def("window_attn_tc_stalls", &window_attn_tc_stalls);
   m.def("window_attn_tc_bwd", &window_attn_tc_bwd);
+  m.def("set_debug_status", &set_debug_status, "status word for the bounds-checked debug build of the attention kernels");
+  m.def("debug_bounds_build", &debug_bounds_build, "whether this extension was compiled with -DTERRA_DEBUG_BOUNDS");
 }

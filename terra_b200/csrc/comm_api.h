@@ -43,8 +43,10 @@ int gather_shards_async(cudaStream_t stream, void* dst, const void* const* src, 
                         size_t row_bytes, int chunks, long long chunk_rows, const unsigned int* signals, unsigned int* ready,
                         unsigned int epoch, int include_self = 0);
 // dst[i] = row src_row[i] of src_peers[src_slot[i]] (rows of row_bytes, a multiple of 16; index arrays on the device).
+// src_rows / status: extent of every source buffer and the KernelStatus word, used by the bounds-checked debug build.
 int peer_gather_indexed(void* dst, const void* const* src_peers, int num_peers, const int* src_slot, const int* src_row,
-                        long long rows, long long row_bytes, cudaStream_t stream);
+                        long long rows, long long row_bytes, cudaStream_t stream, long long src_rows = -1,
+                        void* status = nullptr);
 
 // Halo exchange of two boundary rows with the row-stripe neighbours (see comm_kernels.cu). Null pointers: no neighbour
 // on that side. Buffers and flag words live in symmetric memory; `epoch` counts the exchanges of the group.

@@ -114,13 +114,21 @@ __global__ void peer_signal_kernel(const __grid_constant__ PadPtrs pads, int my_
 __global__ void __launch_bounds__(256) peer_gather_indexed_kernel(uint4* __restrict__ dst, const __grid_constant__ GatherPeers peers,
                                                                   const int* __restrict__ src_slot,
                                                                   const int* __restrict__ src_row, long long rows,
-                                                                  int vec_per_row) {
+                                                                  int vec_per_row, int num_peers, long long src_rows,
+                                                                  KernelStatus* status) {
   const long long total = rows * vec_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = i / vec_per_row;
     const int v = static_cast<int>(i - r * vec_per_row);
-    const uint4* src = peers.p[src_slot[r]] + static_cast<long long>(src_row[r]) * vec_per_row + v;
+    const int slot = src_slot[r], row = src_row[r];
+    // debug build: a route must name a GPU of the group and a row of its staged buffer (src_rows < 0: unknown extent)
+    if (!tb_index_ok(slot >= 0 && slot < num_peers && row >= 0 && (src_rows < 0 || row < src_rows), status, 0xA00u,
+                     static_cast<unsigned int>(slot), static_cast<unsigned int>(row))) {
+      dst[i] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const uint4* src = peers.p[slot] + static_cast<long long>(row) * vec_per_row + v;
     dst[i] = *src;
   }
 }
@@ -208,7 +216,7 @@ __global__ void __launch_bounds__(512) peer_allreduce_small_kernel(const __grid_
 }  // namespace
 
 int peer_gather_indexed(void* dst, const void* const* src_peers, int num_peers, const int* src_slot, const int* src_row,
-                        long long rows, long long row_bytes, cudaStream_t stream) {
+                        long long rows, long long row_bytes, cudaStream_t stream, long long src_rows, void* status) {
   if (num_peers < 1 || num_peers > COMM_MAX_PEERS || row_bytes % 16 != 0) return -1;
   if (rows <= 0) return 0;
   GatherPeers gp;
@@ -217,7 +225,8 @@ int peer_gather_indexed(void* dst, const void* const* src_peers, int num_peers, 
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   peer_gather_indexed_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<uint4*>(dst), gp, src_slot, src_row, rows,
-                                                                          static_cast<int>(row_bytes / 16));
+                                                                          static_cast<int>(row_bytes / 16), num_peers, src_rows,
+                                                                          static_cast<KernelStatus*>(status));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

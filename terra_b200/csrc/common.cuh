@@ -15,6 +15,7 @@ enum : unsigned int {
   TB_ERR_MBAR_TIMEOUT = 1,   // an mbarrier wait inside a CTA ran out
   TB_ERR_PEER_TIMEOUT = 2,   // a wait on a flag written by another GPU ran out
   TB_ERR_BAD_ARG = 3,
+  TB_ERR_BOUNDS = 4,         // TERRA_DEBUG_BOUNDS build: an index computed from a table or across ranks left its buffer
 };
 
 // One status record per launch family, in global memory. Kernels only ever write
@@ -33,6 +34,22 @@ __device__ __forceinline__ void report_error(KernelStatus* st, unsigned int code
     st->info0 = i0;
     st->info1 = i1;
   }
+}
+
+// Bounds-checked debug build (-DTERRA_DEBUG_BOUNDS, `TERRA_DEBUG_BOUNDS=1` for terra_b200/_ext.py): accesses whose
+// index comes from a table or from cross-rank arithmetic (a token's home buffer and row, a relayout route) go through
+// tb_index_ok first. A violation is recorded once in the status word {TB_ERR_BOUNDS, site, two words of the index}
+// and the caller skips or redirects the access: nothing traps, the host raises from the status word after the step.
+// In the normal build the check is a compile-time constant and disappears.
+#ifdef TERRA_DEBUG_BOUNDS
+constexpr bool TB_DEBUG_BOUNDS = true;
+#else
+constexpr bool TB_DEBUG_BOUNDS = false;
+#endif
+__device__ __forceinline__ bool tb_index_ok(bool ok, KernelStatus* st, unsigned int site, unsigned int i0, unsigned int i1) {
+  if (!TB_DEBUG_BOUNDS || ok) return true;
+  report_error(st, TB_ERR_BOUNDS, site, i0, i1);
+  return false;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

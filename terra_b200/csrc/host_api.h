@@ -143,6 +143,7 @@ struct WindowAttnArgs {
   int C, num_heads;                // channels / heads held by this rank (C/tp, nH/tp)
   int heads_per_cta;               // filled by the launcher
   float scale;
+  void* debug_status;              // KernelStatus* for the bounds-checked debug build (token locations), may be null
 };
 int window_attn_fwd(const WindowAttnArgs& a, cudaStream_t stream);
 int window_attn_bwd(const WindowAttnArgs& a, cudaStream_t stream);

@@ -18,6 +18,20 @@ struct Home {
   int region;
 };
 
+// Debug build: a located token must lie inside the buffer of its slot; otherwise the violation is recorded and the
+// location is replaced by row 0 of this rank's own buffer (a valid address), so that the kernel finishes.
+__device__ __forceinline__ void check_home(const WindowAttnArgs& a, Home& h, int nwp) {
+  if (!TB_DEBUG_BOUNDS) return;
+  const int windows = a.tp <= 1 ? nwp : ((nwp + a.tp - 1) / a.tp) * a.tp;
+  const long long rows = static_cast<long long>(a.B) * windows * a.shardN;
+  const bool ok = h.slot >= 0 && h.slot < a.n_wg * a.sp && h.row >= 0 && h.row < rows;
+  if (!tb_index_ok(ok, static_cast<KernelStatus*>(a.debug_status), 0x900u + static_cast<unsigned int>(h.slot & 0xff),
+                   static_cast<unsigned int>(h.row), static_cast<unsigned int>(h.row >> 32))) {
+    h.slot = a.my_wg * a.sp + a.my_sp;
+    h.row = 0;
+  }
+}
+
 __device__ __forceinline__ Home locate(const WindowAttnArgs& a, const Geo& g, int b, int ii, int jj, int tok) {
   const int ti = tok / a.ww, tj = tok % a.ww;
   const int hs = ii * a.wh + ti, ws = jj * a.ww + tj;  // position in the rolled frame
@@ -47,6 +61,7 @@ __device__ __forceinline__ Home locate(const WindowAttnArgs& a, const Geo& g, in
   if (a.sh > 0) rh = hs < g.Hg - a.wh ? 0 : (hs < g.Hg - a.sh ? 1 : 2);
   if (a.sw > 0) rw = ws < g.Wg - a.ww ? 0 : (ws < g.Wg - a.sw ? 1 : 2);
   h.region = rh * 3 + rw;
+  check_home(a, h, nwp);
   return h;
 }
 
@@ -85,6 +100,7 @@ __device__ __forceinline__ Home locate_ij(const WindowAttnArgs& a, const Geo& g,
   if (a.sh > 0 && ii == a.nWh - 1) rh = ti < a.wh - a.sh ? 1 : 2;
   if (a.sw > 0 && jj == a.nWw - 1) rw = tj < a.ww - a.sw ? 1 : 2;
   h.region = rh * 3 + rw;
+  check_home(a, h, nwp);
   return h;
 }
 

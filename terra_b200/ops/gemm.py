@@ -29,6 +29,8 @@ def status_word(device) -> torch.Tensor:
     key = torch.device(device).index or 0
     if key not in _status:
         _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        if _ext.DEBUG_BOUNDS and torch.device(device).type == "cuda":
+            _ext.load().set_debug_status(_status[key])      # the attention kernels' location checks report here
     return _status[key]
 
 

@@ -279,7 +279,8 @@ class PeerDomain:
         staged.copy_(x)
         self.arena.barrier()                      # every rank's rows are staged
         out = torch.empty(src_rank.numel(), x.shape[1], dtype=x.dtype, device=x.device)
-        ext.peer_gather_indexed(out, self.arena.peer_ptrs(staged), src_rank, src_row)
+        ext.peer_gather_indexed(out, self.arena.peer_ptrs(staged), src_rank, src_row, self._max_rows[key],
+                                status_word(x.device))
         return out
 
     def all_reduce_small(self, t: torch.Tensor) -> torch.Tensor:
