@@ -18,8 +18,12 @@ CSRC = os.path.join(_HERE, "csrc")
 # arithmetic are checked before the access and a violation is reported through the status word, see csrc/common.cuh).
 # It is a separate shared object in its own directory, so the two builds never mix.
 DEBUG_BOUNDS = os.environ.get("TERRA_DEBUG_BOUNDS", "0") == "1"
+# TERRA_GELU_EXACT=1: GELU and its derivative through erff / expf instead of the tanh-based fit (csrc/common.cuh); also a
+# build of its own.
+GELU_EXACT = os.environ.get("TERRA_GELU_EXACT", "0") == "1"
 # TERRA_B200_BUILD_DIR: use (and build into) another directory, e.g. to keep two builds of the kernels side by side
-BUILD_DIR = os.environ.get("TERRA_B200_BUILD_DIR") or os.path.join(_HERE, "_build_debug" if DEBUG_BOUNDS else "_build")
+BUILD_DIR = os.environ.get("TERRA_B200_BUILD_DIR") or os.path.join(
+    _HERE, "_build" + ("_debug" if DEBUG_BOUNDS else "") + ("_erf" if GELU_EXACT else ""))
 EXT_NAME = "terra_b200_C"
 
 CUDA_FLAGS = [
@@ -31,6 +35,8 @@ CUDA_FLAGS = [
 
 if DEBUG_BOUNDS:
     CUDA_FLAGS.append("-DTERRA_DEBUG_BOUNDS")
+if GELU_EXACT:
+    CUDA_FLAGS.append("-DTERRA_GELU_EXACT_ERF")
 
 _lock = threading.Lock()
 _module = None

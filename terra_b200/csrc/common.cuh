@@ -331,6 +331,19 @@ __device__ __forceinline__ float tanh_fast(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+#ifdef TERRA_GELU_EXACT_ERF
+// Build switch (TERRA_GELU_EXACT=1 for terra_b200/_ext.py): the erf form itself, 0.5 x (1 + erf(x / sqrt 2)), and its
+// derivative Phi(x) + x phi(x), for runs that must not depend on the fit below (a few more instructions per element
+// in the fc1 / d(fc2) epilogues).
+__device__ __forceinline__ float gelu_erf(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+__device__ __forceinline__ float gelu_erf_grad(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+  const float pdf = 0.39894228040143268f * __expf(-0.5f * x * x);
+  return fmaf(x, pdf, cdf);
+}
+#else
 __device__ __forceinline__ float gelu_erf(float x) {
   const float xc = fminf(fmaxf(x, -8.0f), 8.0f);
   const float x2 = xc * xc;
@@ -346,6 +359,7 @@ __device__ __forceinline__ float gelu_erf_grad(float x) {
   const float sech2 = fmaf(-t, t, 1.0f);
   return fmaf(0.5f * xc * sech2, du, fmaf(0.5f, t, 0.5f));
 }
+#endif
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
