@@ -232,25 +232,37 @@ def run_ours(args):
     #      launch would have) and waits for it no longer than the deadline; the headline above is already measured and is
     #      printed whatever the child does.
     layout = parse_layout(args.extra_layout, args.gpus)
+    child_port = [None]
+    if layout is not None:
+        if rank == 0:                     # a port that is free now, agreed on while the ranks can still talk
+            import socket
+
+            with socket.socket() as sock:
+                sock.bind(("127.0.0.1", 0))
+                child_port[0] = sock.getsockname()[1]
+        if live:
+            dist.broadcast_object_list(child_port, src=0)
     trainer.close()                       # frees the model; destroys the process group
     del trainer, devb
     gc.collect()
     if dev.type == "cuda":
         torch.cuda.empty_cache()
     if layout is not None:
-        line["layout_" + "x".join(str(v) for v in layout)] = _extra_layout_in_child(args, layout, rank)
+        line["layout_" + "x".join(str(v) for v in layout)] = _extra_layout_in_child(args, layout, rank, child_port[0])
     if rank == 0:
         print(json.dumps(line), flush=True)
 
 
-def _extra_layout_in_child(args, layout, rank):
-    """Runs ``bench.py --only-layout`` as a child of this rank; returns rank 0's result (or the reason there is none)."""
+def _extra_layout_in_child(args, layout, rank, port):
+    """Runs ``bench.py --only-layout`` as a child of this rank; returns rank 0's result (or the reason there is none).
+    ``port``: the rendezvous port of the children (the same on every rank)."""
     text = ",".join(str(v) for v in layout)
-    out = os.path.join(tempfile.gettempdir(), f"terra_bench_layout_{os.environ.get('MASTER_PORT', '0')}_{text.replace(',', 'x')}.json")
+    out = os.path.join(tempfile.gettempdir(), f"terra_bench_layout_{port}_{text.replace(',', 'x')}.json")
     if rank == 0 and os.path.exists(out):
         os.unlink(out)
     env = dict(os.environ)
-    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 17)      # a rendezvous of its own
+    env["MASTER_ADDR"] = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    env["MASTER_PORT"] = str(port)                                                  # a rendezvous of its own
     for name in [k for k in env if k.startswith("TORCHELASTIC_")]:
         # without TORCHELASTIC_USE_AGENT_STORE the child of rank 0 hosts the store on the new port itself (the launcher's
         # agent store listens on the old one only)
