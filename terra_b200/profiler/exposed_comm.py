@@ -1,7 +1,7 @@
 """Exposed-communication accounting for one training step.
 
 A step's device timeline is split into compute kernels and communication kernels (NCCL kernels, the peer barrier /
-signal kernels; kernels that compute and communicate at once, such as the window-attention kernel reading peer rows or
+signal / halo / small all-reduce / relayout kernels; kernels that compute and communicate at once, such as the window-attention kernel reading peer rows or
 the peer-scattering GEMM, count as compute). ``exposed`` is the part of the step during which no compute kernel runs:
 time the GPU spends waiting for peers or moving data with nothing to overlap it, plus launch gaps; ``comm_busy`` is the
 union of the communication kernels' intervals, of which ``comm_hidden`` overlaps compute.
@@ -14,7 +14,10 @@ from __future__ import annotations
 import json
 from typing import Iterable, List, Sequence, Tuple
 
-COMM_KERNEL_MARKERS = ("nccl", "peer_barrier", "peer_signal", "Memcpy PtoP", "Memcpy DtoD (Peer")
+# pure communication kernels: NCCL, the flag barrier / signal kernels, the halo push, the small all-reduce, the indexed
+# relayout gather, peer row copies, and peer-to-peer copies of the copy engines
+COMM_KERNEL_MARKERS = ("nccl", "peer_barrier", "peer_signal", "halo_push", "peer_allreduce_small", "peer_gather_indexed",
+                       "peer_copy_rows", "peer_sum_small", "Memcpy PtoP", "Memcpy DtoD (Peer")
 
 
 def is_comm_kernel(name: str) -> bool:

@@ -224,7 +224,9 @@ def test_exposed_comm_accounting():
 
     assert union_length([(0, 2), (1, 3), (5, 6)]) == 4
     assert is_comm_kernel("ncclDevKernel_AllReduce_Sum_f32_RING_LL") and is_comm_kernel("tb::peer_barrier_kernel")
-    assert not is_comm_kernel("void tb::gemm_tcgen05_kernel<192, 1, false>")
+    assert is_comm_kernel("tb::(anonymous namespace)::halo_push_kernel(tb::HaloPushArgs)")
+    assert is_comm_kernel("tb::(anonymous namespace)::peer_allreduce_small_kernel") and is_comm_kernel("peer_gather_indexed_kernel")
+    assert not is_comm_kernel("void tb::gemm_tcgen05_kernel<192, 1, false>") and not is_comm_kernel("dist_adamw_kernel")
     r = account([("gemm", 0.0, 4.0), ("ncclDevKernel_SendRecv", 3.0, 6.0), ("layernorm", 7.0, 8.0),
                  ("tb::peer_barrier_kernel", 8.0, 9.0)])
     assert r["span"] == 9.0 and r["compute_busy"] == 5.0 and r["comm_busy"] == 4.0
