@@ -123,6 +123,18 @@ def test_parallel_layout_matches_serial(world, extra):
         assert res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res
 
 
+def test_ragged_ownership_with_rectangular_windows_matches_serial():
+    """The structure of the medium-resolution benchmark layout in small: 8 x 12 windows, a window grid (3 x 2) whose rows
+    do not divide over the ranks, row-major ragged ownership (3 windows each: the ranks share a window row), hence the
+    general stripe <-> window relayout and a halo that is part of a window row."""
+    base = BASE.replace("height=128, width=256", "height=192, width=192").replace("window_size=8", "window_size=[8, 12]")
+    assert base != BASE
+    extra = "wp_topo='(2, 1)', xfmr_wp_topo='(2, 1)', window_assignment_mode='terra_m1_ragged_auto'"
+    for res in _run(2, "", code=WORKER % dict(root=ROOT, cfg=base + extra)):
+        assert abs(res["loss"] - res["ref_loss"]) < 1e-4 * max(1.0, abs(res["ref_loss"])), res
+        assert res["out_err"] < 2e-3 and res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res
+
+
 def test_sequence_parallel_gather_baseline_matches_serial():
     """The sequence-parallel layouts above run the Ulysses all-to-all baseline (heads divisible by sp); the gather
     baseline (every rank collects all q/k/v rows) must give the same numbers."""
