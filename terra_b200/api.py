@@ -5,6 +5,7 @@ loss as a Python float.
     trainer = Trainer("configs/model/pretrain/x.yaml", data_parallel_group_size=1)
     batch = trainer.synthetic_batch(sample=0)           # pinned host tensors of this rank's stripe
     loss = trainer.step(batch)
+    trainer.save_checkpoint(epoch=0, loss=loss)         # and trainer.load_checkpoint(epoch=0) to resume
 
 The same object backs ``train_scripts/train.py`` and ``bench.py``.
 """
@@ -138,6 +139,31 @@ class Trainer:
             self.other, self.precision, self.cfg.get("half_model", False), None, self.loss_func, self.gscaler,
             self.manager, self.opt_state)
         return loss
+
+    # ------------------------------------------------------------------ checkpoints, schedule
+    def save_checkpoint(self, epoch: int, loss: Optional[float] = None, step: Optional[int] = None) -> Optional[str]:
+        """Write ``{train_path}/{description}/ckpt/...`` in the layout the configuration implies (``single``,
+        ``wp_rank``, ``rank_local``, ``fsdp_full`` or ``fsdp_sharded``: see ``terra_b200.checkpoint_io``). Collective:
+        every rank calls it; returns the path this rank wrote, if any."""
+        from .checkpoint_io import save_checkpoint
+
+        return save_checkpoint(self.model, self.optimizer, loss, epoch, self.cfg.get("train_path", "./runs"),
+                               self.cfg.get("description", "run"), self.model_type, self.opt_state, self.manager,
+                               self.gscaler, step=step, model_config=self.cfg)
+
+    def load_checkpoint(self, epoch: Optional[int] = None, step: Optional[int] = None):
+        """Resume from a file written by ``save_checkpoint`` (or by ``train_scripts/train.py``); returns
+        ``(epoch, global_step, loss)``."""
+        from .checkpoint_io import load_checkpoint
+
+        return load_checkpoint(self.model, self.optimizer, self.cfg.get("train_path", "./runs"),
+                               self.cfg.get("description", "run"), self.model_type, self.opt_state, self.manager,
+                               epoch=epoch, step=step, scaler=self.gscaler, model_config=self.cfg)
+
+    def set_lr(self, lr: float) -> None:
+        from .optim.utils import set_lr
+
+        set_lr(self.optimizer, lr)
 
     def release(self):
         """Drop the model, optimizer and their symmetric arenas but keep the process group, so that another
