@@ -233,10 +233,26 @@ class GlorysLeadDoubleBuffer:
         self.seq = None
 
 
-def resolve_glorys_finetune_double_buffer(sequence_batch, device, dtype, lead_time, enabled=True):
-    """``[B, L+1, ...]`` pinned batch -> per-lead accessor (double buffered on CUDA when ``enabled``)."""
+class _WholeSequenceOnDevice(list):
+    """Every frame uploaded at once (no double buffering); keeps the upload time for the metrics."""
+
+    transfer_s = 0.0
+
+    def transfer_time_s(self):
+        return self.transfer_s
+
+
+def resolve_glorys_finetune_double_buffer(sequence_batch, device, dtype, lead_time, enabled=True, non_blocking=True):
+    """``[B, L+1, ...]`` pinned batch -> per-lead accessor (double buffered on CUDA when ``enabled``). ``non_blocking``
+    (YAML ``input_transfer_non_blocking``) applies to the single upload of the path without double buffering; the
+    double buffer is asynchronous by construction (reference: train_scripts/test_finetune.py:116-131,940-960)."""
     seq = sequence_batch.transpose(0, 1).contiguous()        # [L+1, B, ...]
     if enabled:
         return GlorysLeadDoubleBuffer(seq, device, dtype, lead_time)
-    dev = seq.to(device=device, dtype=dtype)
-    return [dev[i] for i in range(dev.shape[0])]
+    t0 = time.time()
+    dev = seq.to(device=device, dtype=dtype, non_blocking=bool(non_blocking))
+    if not non_blocking and torch.device(device).type == "cuda":
+        torch.cuda.synchronize(device)
+    frames = _WholeSequenceOnDevice(dev[i] for i in range(dev.shape[0]))
+    frames.transfer_s = time.time() - t0
+    return frames

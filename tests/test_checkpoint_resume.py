@@ -119,3 +119,37 @@ def test_finetune_step_checkpoint_and_resume(tmp_path):
     lines = open(log).read().strip().splitlines()
     assert len(lines) == n_before + 1
     assert "global_step 3" in lines[-1], lines[-1]           # the optimizer's step counter came from the checkpoint
+
+
+def test_finetune_harness_data_path_switches(tmp_path):
+    """``test_finetune.py`` with the reference's data-path keys: a blocking single upload instead of the double buffer,
+    the upload counted into the step time, the CPU batch released after the transfer; per-lead plans applied; and the
+    combination the reference refuses (double buffering with blocking copies) refused here too."""
+    import csv
+
+    cfg = yaml.safe_load(open(os.path.join(ROOT, "configs", "finetuning", "tiny_finetune_seq.yaml")))
+    cfg.update(train_path=str(tmp_path / "ft"), precision="fp32", finetune_lead_time=2, fake_length=3,
+               input_double_buffer=False, input_transfer_non_blocking=False, include_input_transfer_in_step_time=True,
+               release_cpu_batch_after_transfer=True)
+    path = tmp_path / "ok.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", PYTHONPATH=ROOT)
+    exe = os.path.join(ROOT, "train_scripts", "test_finetune.py")
+    out = subprocess.run([sys.executable, exe, "--model_cfg", str(path), "--steps", "2", "--metrics_csv",
+                          str(tmp_path / "m.csv"), "--memory_timeline_csv", str(tmp_path / "leads.csv"), "--metrics_no_json",
+                          "--disable_torch_prof", "--disable_rank_log_redirect"], env=env, capture_output=True, text=True,
+                         timeout=900, cwd=str(tmp_path))
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-4000:])
+    rows = list(csv.DictReader(open(tmp_path / "m.csv")))
+    assert len(rows) == 2 and all(float(r["input_transfer_time_s"]) > 0 for r in rows)
+    assert all(float(r["step_time_s"]) > float(r["input_transfer_time_s"]) for r in rows)
+    leads = list(csv.DictReader(open(tmp_path / "leads.csv")))
+    assert [int(r["lead"]) for r in leads] == [0, 1, 0, 1]            # two leads per step, the per-lead plan recorded
+
+    bad = dict(cfg, input_double_buffer=True)
+    path2 = tmp_path / "bad.yaml"
+    path2.write_text(yaml.safe_dump(bad))
+    out = subprocess.run([sys.executable, exe, "--model_cfg", str(path2), "--steps", "1", "--metrics_no_json",
+                          "--disable_torch_prof", "--disable_rank_log_redirect"], env=env, capture_output=True, text=True,
+                         timeout=900, cwd=str(tmp_path))
+    assert out.returncode != 0 and "input_double_buffer requires input_transfer_non_blocking=true" in out.stderr

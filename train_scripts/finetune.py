@@ -50,7 +50,8 @@ def sequence_to_leads(s: Session, seq_batch, lead_time):
 
         seq_batch = to_nhwc(seq_batch, s.archi["num_channels"])
     frames = resolve_glorys_finetune_double_buffer(seq_batch, s.device, s.data_dtype, lead_time,
-                                                   enabled=s.cfg.get("input_double_buffer", True))
+                                                   enabled=s.cfg.get("input_double_buffer", True),
+                                                   non_blocking=s.cfg.get("input_transfer_non_blocking", True))
 
     class _Leads:
         def __getitem__(self, lead):

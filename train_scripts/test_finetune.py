@@ -86,6 +86,21 @@ def main(argv=None):
     s = Session(args.model_cfg, args.data_parallel_group_size, dict(FINETUNE_DEFAULTS, use_fake_input=True))
     c = s.cfg
     lead = int(c["finetune_lead_time"])
+    # data-path switches of the reference harness (train_scripts/test_finetune.py:107-160)
+    non_blocking = bool(c.get("input_transfer_non_blocking", True))
+    count_transfer = bool(c.get("include_input_transfer_in_step_time", False))
+    release_cpu = bool(c.get("release_cpu_batch_after_transfer", False))
+    if c.get("input_double_buffer", True) and not non_blocking:
+        raise ValueError("input_double_buffer requires input_transfer_non_blocking=true")
+    if non_blocking and not c.get("dataloader_pin_memory", True) and s.is_log_rank():
+        print("warning: input_transfer_non_blocking=true without dataloader_pin_memory: the copies are synchronous", flush=True)
+    if c.get("fake_input_dmp_local", False):
+        # the fake datasets here always generate only the rows a rank owns (block-addressable generator), which is
+        # what this switch asks for; it keeps the reference's preconditions
+        if not c.get("use_fake_input", False):
+            raise ValueError("fake_input_dmp_local requires use_fake_input=true")
+        if s.model_type not in ("parallel", "hybrid"):
+            raise ValueError("fake_input_dmp_local only supports parallel/hybrid GLORYS finetune")
     set_dp_rank_print_redirect(s.manager, s.model_type, s.opt_state, s.other.get("embedding_parallel_type"),
                                quiet=args.quiet_metrics, disable=args.disable_rank_log_redirect or s.world == 1)
     reset_boundary_offload_stats()
@@ -115,6 +130,12 @@ def main(argv=None):
                 loss_reduction=c["finetune_loss_reduction"], lead_callback=cb, memory_timeline=timeline,
                 clip_grad=c["clip_grad"])
         transfer = frames.transfer_time_s() if hasattr(frames, "transfer_time_s") else 0.0
+        if count_transfer:
+            step_time += transfer
+        if release_cpu:
+            if hasattr(frames, "release"):
+                frames.release()               # pinned source and device slots of the double buffer
+            del seq
         out_sum = out.detach().float().sum()
         if dist.is_available() and dist.is_initialized() and s.model_type != "sequential":
             dist.all_reduce(out_sum, group=s.manager.window_parallel_group)
