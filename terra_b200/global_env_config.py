@@ -15,6 +15,8 @@ DEBUG_GRAD_HOOK = _flag("DEBUG_GRAD_HOOK")
 DEBUG_GRAD_HOOK_PRINT_LIMIT = int(os.environ.get("DEBUG_GRAD_HOOK_PRINT_LIMIT", "20"))
 FSDP_WRAPPER_CFG = int(os.environ.get("FSDP_WRAPPER_CFG", "1"))
 TERRA_USE_FAKE_INPUT = _flag("TERRA_USE_FAKE_INPUT")
+USE_FAKE_INPUT = TERRA_USE_FAKE_INPUT            # the reference's name for the same switch
+USE_FLASH_ATTENTION = "no use now"               # kept for code that imports it; attention has one implementation per device
 TERRA_ALLOW_UNALIGNED_CROSS_NODE_WP = _flag("TERRA_ALLOW_UNALIGNED_CROSS_NODE_WP")
 
 MEM_PROF = 0
