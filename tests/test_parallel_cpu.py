@@ -274,3 +274,86 @@ LEGACY_EMB = textwrap.dedent('''
 def test_legacy_domain_parallel_embeddings_match_the_full_linear():
     for res in _run(2, "", code=LEGACY_EMB % dict(root=ROOT)):
         assert res["worst"] < 1e-5, res
+
+
+DOMAIN_PARALLEL = textwrap.dedent('''
+    import copy, json, sys
+    sys.path.insert(0, %(root)r)
+    import torch, torch.nn as nn, torch.distributed as dist
+    from terra_b200.distributed import init_distributed
+    from terra_b200.parallel import domain_parallel as DP
+
+    rank, world, _ = init_distributed("gloo")
+    dom = DP.DomainGroup(dist.group.WORLD)
+    torch.manual_seed(0)
+    torch.set_default_dtype(torch.float64)
+
+    class Periodic(nn.Module):                       # circular in W, reflect in H, then an unpadded convolution
+        def __init__(self):
+            super().__init__()
+            self.padding = 1
+            self.conv = nn.Conv2d(8, 8, 3, padding=0)
+        def forward(self, x):
+            x = nn.functional.pad(x, (1, 1, 0, 0), mode="circular")
+            return self.conv(nn.functional.pad(x, (0, 0, 1, 1), mode="reflect"))
+
+    full = nn.Sequential(
+        nn.Conv2d(3, 8, 3, padding=1), nn.GroupNorm(2, 8), nn.SiLU(),
+        nn.Conv2d(8, 8, 3, stride=2, padding=1), nn.Conv2d(8, 8, 1),
+        nn.ConvTranspose2d(8, 8, 4, stride=2, padding=1), nn.GroupNorm(4, 8),
+        nn.Conv2d(8, 8, 5, padding=2, dilation=1), nn.ConvTranspose2d(8, 4, 2, stride=2))
+    par = DP.convert_to_domain_parallel(copy.deepcopy(full), dom)
+    counts = par.domain_parallel_counts
+    x = torch.randn(2, 3, 16 * world, 12)
+    cot = torch.randn(2, 4, 32 * world, 24)
+    xr = x.clone().requires_grad_(True)
+    yf = full(xr)
+    (yf * cot).sum().backward()
+    xs = DP.shard_tensor(x, -2, dom).requires_grad_(True)
+    yp = par(xs)
+    (yp * DP.shard_tensor(cot, -2, dom)).sum().backward()
+    worst = (yp.detach() - DP.shard_tensor(yf.detach(), -2, dom)).abs().max().item()
+    worst = max(worst, (xs.grad - DP.shard_tensor(xr.grad, -2, dom)).abs().max().item())
+    for pf, pp in zip(full.parameters(), par.parameters()):
+        g = pp.grad.clone(); dist.all_reduce(g)                  # every rank saw its rows only
+        worst = max(worst, (g - pf.grad).abs().max().item())
+    gathered = DP.gather_tensor(yp.detach(), -2, dom)
+    worst = max(worst, (gathered - yf.detach()).abs().max().item())
+
+    # 3-D layers: [B, C, T, H, W] cut along H
+    full3 = nn.Sequential(nn.Conv3d(2, 4, 3, padding=1), nn.ConvTranspose3d(4, 2, (1, 4, 4), stride=(1, 2, 2), padding=(0, 1, 1)))
+    par3 = DP.convert_to_domain_parallel(copy.deepcopy(full3), dom)
+    v = torch.randn(1, 2, 3, 8 * world, 6)
+    worst = max(worst, (par3(DP.shard_tensor(v, 3, dom)) - DP.shard_tensor(full3(v), 3, dom)).abs().max().item())
+    counts3 = par3.domain_parallel_counts
+
+    # a custom wrapper replaced as a whole; inner rows agree (the first and the last row differ by design: zero halo
+    # at the poles instead of the reflection)
+    per = Periodic()
+    pper = DP.convert_to_domain_parallel(nn.Sequential(copy.deepcopy(per)), dom,
+                                         custom_converters={Periodic: lambda m: DP.DomainParallelPeriodicConv2d(m, dom=dom)})
+    u = torch.randn(1, 8, 8 * world, 10)
+    a, b = pper(DP.shard_tensor(u, -2, dom)), DP.shard_tensor(per(u), -2, dom)
+    lo, hi = (1 if rank == 0 else 0), (a.shape[2] - 1 if rank == world - 1 else a.shape[2])
+    worst = max(worst, (a[:, :, lo:hi] - b[:, :, lo:hi]).abs().max().item())
+
+    batch = DP.shard_batch({"x": x, "t": torch.zeros(2), "v": v, "name": "n"}, dom=dom)
+    ok = batch["x"].shape[2] == 16 and batch["v"].shape[3] == 8 and batch["t"].shape == (2,) and batch["name"] == "n"
+    notes = DP.validate_sharding_constraints(par, 12, window_sizes=[8, (4, 4)])
+    print("RESULT " + json.dumps(dict(worst=worst, counts=counts, counts3=counts3, ok=bool(ok), notes=len(notes),
+                                      custom=pper.domain_parallel_counts["custom"])), flush=True)
+    dist.destroy_process_group()
+''')
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_generic_domain_parallel_layers_match_the_unsharded_model(world):
+    """``convert_to_domain_parallel`` on a stack of plain / strided / wide convolutions, overlapping and non-overlapping
+    transposed convolutions and GroupNorms: outputs, input gradients and (summed) parameter gradients of the sharded
+    model equal the unsharded one (reference: credit/domain_parallel/*)."""
+    for res in _run(world, "", code=DOMAIN_PARALLEL % dict(root=ROOT)):
+        assert res["worst"] < 1e-9, res
+        assert res["counts"] == {"conv2d": 3, "conv3d": 0, "conv_transpose2d": 1, "conv_transpose3d": 0, "group_norm": 2,
+                                 "custom": 0}, res
+        assert res["counts3"]["conv3d"] == 1 and res["counts3"]["conv_transpose3d"] == 1 and res["custom"] == 1
+        assert res["ok"] and res["notes"] == 2          # 12 % 8 and 6 % 4
