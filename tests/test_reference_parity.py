@@ -69,3 +69,30 @@ def test_unshifted_only_model_and_no_bias_variant_match():
     x = torch.randn(1, KW["height"], KW["width"], KW["num_channels"])
     with torch.no_grad():
         assert (ref(x) - mine(x)).abs().max().item() <= 2e-4 * max(1.0, float(ref(x).abs().max()))
+
+
+def test_window_utilities_match_the_reference_and_the_kernel_index_math():
+    """``ops/window_utils.py`` against the reference's helpers (models/utils.py), and against the closed-form region
+    numbering that the attention kernels use instead of a mask tensor."""
+    import models.utils as ref_utils
+
+    from terra_b200.ops import window_utils as U
+    from terra_b200.ops.attention import region_ids
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 16, 24, 5)
+    assert torch.equal(U.window_partition(x, 8), ref_utils.window_partition(x, 8))
+    assert torch.equal(U.window_reverse(U.window_partition(x, 8), 8, 16, 24), x)
+    assert torch.equal(U.window_reverse(ref_utils.window_partition(x, 8), 8, 16, 24),
+                       ref_utils.window_reverse(ref_utils.window_partition(x, 8), 8, 16, 24))
+    h = torch.randn(16, 24, 2, 5)
+    assert torch.equal(U.window_partition_HWBC(h, 8), ref_utils.window_partition_HWBC(h, 8))
+    for res, win in (((13, 721, 1440), (2, 6, 12)), ((4, 48, 96), (2, 6, 12)), ((7, 50, 99), (3, 8, 8))):
+        assert tuple(U.get_pad3d(res, win)) == tuple(ref_utils.get_pad3d(res, win))
+        assert tuple(U.get_pad2d(res[1:], win[1:])) == tuple(ref_utils.get_pad2d(res[1:], win[1:]))
+    mask = U.get_swin_attention_mask("sequential", (16, 24), 8, 4)
+    assert torch.equal(mask, ref_utils.get_swin_attention_mask("sequential", (16, 24), 8, 4))
+    # the kernels' closed form: region numbers of the rolled frame, rectangular windows included
+    for (H, W, wh, ww) in ((16, 24, 8, 8), (16, 36, 8, 12)):
+        want = U.shift_region_map(H, W, (wh, ww), (wh // 2, ww // 2))
+        assert torch.equal(region_ids(H, W, wh, ww, wh // 2, ww // 2).reshape(H, W).long(), want)
