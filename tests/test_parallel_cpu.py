@@ -357,3 +357,94 @@ def test_generic_domain_parallel_layers_match_the_unsharded_model(world):
                                  "custom": 0}, res
         assert res["counts3"]["conv3d"] == 1 and res["counts3"]["conv_transpose3d"] == 1 and res["custom"] == 1
         assert res["ok"] and res["notes"] == 2          # 12 % 8 and 6 % 4
+
+
+TENSOR_PARALLEL = textwrap.dedent('''
+    import json, sys
+    sys.path.insert(0, %(root)r)
+    import torch, torch.nn as nn, torch.nn.functional as F, torch.distributed as dist
+    from terra_b200.distributed import init_distributed
+    from terra_b200.parallel import tensor_parallel as TP
+
+    rank, world, _ = init_distributed("gloo")
+    g = dist.group.WORLD
+    torch.set_default_dtype(torch.float64)
+    worst = 0.0
+    C, Fh, B, S = 8, 8 * world, 2, 4 * world
+
+    def serial(seed):
+        torch.manual_seed(seed)
+        norm, fc1, fc2 = nn.LayerNorm(C), nn.Linear(C, Fh), nn.Linear(Fh, C)
+        return norm, fc1, fc2
+
+    torch.manual_seed(1)
+    x = torch.randn(B, S, C)
+    cot = torch.randn(B, S, C)
+    # ---- Megatron tensor parallel: replicated activations
+    torch.manual_seed(5)
+    tp = TP.TensorParallelMLP(g, C, Fh)            # draws norm, fc1, fc2 in this order from seed 5
+    norm, fc1, fc2 = serial(5)
+    xr = x.clone().requires_grad_(True)
+    yr = xr + fc2(F.gelu(fc1(norm(xr))))
+    (yr * cot).sum().backward()
+    xp = x.clone().requires_grad_(True)
+    yp = tp(xp)
+    (yp * cot).sum().backward()
+    per = Fh // world
+    worst = max(worst, (yp - yr).abs().max().item(), (xp.grad - xr.grad).abs().max().item())
+    worst = max(worst, (tp.weight1.grad - fc1.weight.grad[rank * per:(rank + 1) * per]).abs().max().item())
+    worst = max(worst, (tp.weight2.grad - fc2.weight.grad[:, rank * per:(rank + 1) * per]).abs().max().item())
+    worst = max(worst, (tp.bias2.grad - fc2.bias.grad).abs().max().item())
+    # ---- Megatron sequence parallel: token shards outside the layer
+    torch.manual_seed(5)
+    sp = TP.MegatronSequenceParallelMLP(g, C, Fh, seq_dim=1)
+    sh = S // world
+    xs = x[:, rank * sh:(rank + 1) * sh].clone().requires_grad_(True)
+    ys = sp(xs)
+    (ys * cot[:, rank * sh:(rank + 1) * sh]).sum().backward()
+    worst = max(worst, (ys - yr[:, rank * sh:(rank + 1) * sh]).abs().max().item())
+    worst = max(worst, (xs.grad - xr.grad[:, rank * sh:(rank + 1) * sh]).abs().max().item())
+    worst = max(worst, (sp.weight1.grad - fc1.weight.grad[rank * per:(rank + 1) * per]).abs().max().item())
+    gb = sp.bias2.grad.clone(); dist.all_reduce(gb)               # bias2 sees this rank's tokens only
+    worst = max(worst, (gb - fc2.bias.grad).abs().max().item())
+    # ---- Ulysses: replicated weights, token shards, gradients summed afterwards
+    torch.manual_seed(5)
+    ul = TP.UlyssesSequenceParallelMLP(C, Fh)
+    yu = ul(x[:, rank * sh:(rank + 1) * sh])
+    (yu * cot[:, rank * sh:(rank + 1) * sh]).sum().backward()
+    gw = ul.fc1.weight.grad.clone(); dist.all_reduce(gw)
+    worst = max(worst, (yu - yr[:, rank * sh:(rank + 1) * sh]).abs().max().item(), (gw - fc1.weight.grad).abs().max().item())
+    # ---- head <-> token exchange and its inverse, with gradients
+    H = 2 * world
+    t = torch.randn(B, sh, H, 3, requires_grad=True)              # [B, S / n, heads, d]
+    full = TP.all_to_all_dims(t, g, split_dim=2, concat_dim=1)    # [B, S, heads / n, d]
+    ok = tuple(full.shape) == (B, S, H // world, 3)
+    gathered = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(gathered, t.detach())
+    want = torch.cat(gathered, dim=1)[:, :, rank * 2:(rank + 1) * 2]
+    worst = max(worst, (full.detach() - want).abs().max().item())
+    back = TP.all_to_all_dims(full, g, split_dim=1, concat_dim=2)
+    worst = max(worst, (back.detach() - t.detach()).abs().max().item())
+    (back * 3.0).sum().backward()
+    worst = max(worst, (t.grad - 3.0).abs().max().item())
+    # ---- last-dimension regions
+    z = torch.randn(3, 4 * world, requires_grad=True)
+    piece = TP.scatter_to_region(z, g)
+    again = TP.gather_from_region(piece, g)
+    worst = max(worst, (again.detach() - z.detach()).abs().max().item())
+    (again * (rank + 1.0)).sum().backward()
+    # gather's adjoint keeps this rank's slice of the cotangent, scatter's adjoint gathers the slices of all ranks:
+    # slice j of the input gradient is rank j's weight
+    wantg = torch.cat([torch.full((3, 4), r + 1.0) for r in range(world)], dim=-1)
+    worst = max(worst, (z.grad - wantg).abs().max().item())
+    print("RESULT " + json.dumps(dict(worst=worst, ok=bool(ok))), flush=True)
+    dist.destroy_process_group()
+''')
+
+
+def test_classic_tensor_and_sequence_parallel_layers_match_the_serial_mlp():
+    """Megatron tensor-parallel, Megatron sequence-parallel and Ulysses MLPs over a 2-rank group against the serial MLP
+    with the same seeded weights (outputs, input gradients, weight-shard gradients), plus the head <-> token all-to-all
+    and the last-dimension scatter / gather regions (reference: core/tensor_parallel.py, models/mlp.py:177-373)."""
+    for res in _run(2, "", code=TENSOR_PARALLEL % dict(root=ROOT)):
+        assert res["ok"] and res["worst"] < 1e-10, res
