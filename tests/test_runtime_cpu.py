@@ -107,3 +107,21 @@ def test_trainer_checkpoint_round_trip_through_the_public_api(tmp_path):
     assert (epoch, gstep, loss) == (0, 2, 1.0)
     got = t2.step(batches[2])
     assert abs(got - want) <= 1e-6 * max(1.0, abs(want)), (got, want)
+
+
+def test_small_utilities():
+    from terra_b200.utils.misc import check_parallel_config, get_task_partition, sort_key
+
+    spans = [get_task_partition(r, 8, 331) for r in range(8)]
+    assert spans[0] == (0, 41) and spans[-1] == (289, 331)
+    assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))                  # contiguous, nothing lost
+    assert [e - s for s, e in spans] == [41] * 5 + [42] * 3
+    assert get_task_partition(3, 4, 331, div_10=True) == (25, 34)
+    assert sorted(["/d/10.nc", "/d/9.nc", "/d/100.nc"], key=sort_key) == ["/d/9.nc", "/d/10.nc", "/d/100.nc"]
+    check_parallel_config(2, 1, (4, 1), (1, 1), 8, 2048, 4320, 4, 8, padding_scale=2)
+    import pytest
+
+    with pytest.raises(ValueError, match="world_size"):
+        check_parallel_config(2, 1, (4, 1), (1, 1), 16, 2048, 4320, 4, 8)
+    with pytest.raises(ValueError, match="window grid"):
+        check_parallel_config(1, 1, (7, 1), (1, 1), 7, 2048, 4320, 4, 8, padding_scale=2)
