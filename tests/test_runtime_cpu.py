@@ -125,3 +125,17 @@ def test_small_utilities():
         check_parallel_config(2, 1, (4, 1), (1, 1), 16, 2048, 4320, 4, 8)
     with pytest.raises(ValueError, match="window grid"):
         check_parallel_config(1, 1, (7, 1), (1, 1), 7, 2048, 4320, 4, 8, padding_scale=2)
+
+
+def test_buffer_helpers():
+    from terra_b200.utils import buffers as Bf
+
+    a = Bf.get_preallocated_buffer((2, 3), torch.float32, "cpu", key="x")
+    assert Bf.get_preallocated_buffer((2, 3), torch.float32, "cpu", key="x") is a
+    assert Bf.get_preallocated_buffer((2, 3), torch.float32, "cpu", key="y") is not a
+    assert Bf.get_preallocated_buffer((2, 4), torch.float32, "cpu", key="x").shape == (2, 4)
+    t = torch.zeros(4, 6).t()                                   # non-contiguous: strides are kept
+    h = Bf.new_cpu_buffer_like(t)
+    assert h.shape == t.shape and h.stride() == t.stride() and h.device.type == "cpu"
+    assert Bf.get_cuda_stream("cpu") is None or torch.cuda.is_available()
+    Bf.release_preallocated_buffers()
