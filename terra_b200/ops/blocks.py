@@ -9,6 +9,9 @@ Backward runs the transposed products on the same tcgen05 kernel (weights read M
 both operands MN-major with split-K fp32 atomics for weight gradients, accumulated straight into the flat
 gradient arena), fuses GELU' into the fc2 input-gradient epilogue and the shortcut gradient into the LayerNorm
 backward. On CPU the same math is plain PyTorch (autograd does the rest); that path is the oracle of the tests.
+
+What these nodes compute is the reference's block halves: models/transformer.py:71-160 (``SequentialSwinTransformer``),
+:963-1036 (window-parallel forward), models/attention.py:874-910 (window attention), models/mlp.py:138-175, 375-412 (MLP).
 """
 from __future__ import annotations
 

@@ -10,6 +10,9 @@ the block's shortcut), its backward a reduce pass plus an apply pass.
 With row-stripe domain parallelism (``dom`` given) halo rows come from the neighbours and GroupNorm statistics
 are summed over the stripe group, so that the result equals the single-rank one.
 CPU: plain PyTorch on the same NHWC tensors (oracle for the tests, gloo ranks for the multi-rank logic).
+
+Reference: models/utils.py:101-180 (``CreditDownBlock`` / ``CreditUpBlock``), credit/domain_parallel/layers.py:18-84,
+87-208, 429-483 and halo_exchange.py:18-157 for the row-stripe forms.
 """
 from __future__ import annotations
 

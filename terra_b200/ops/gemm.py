@@ -7,6 +7,9 @@ without materialising a transpose:
     forward      y  = x  @ W^T          a=x  [M,K]         b=W  [N,K]
     input grad   dx = dy @ W            a=dy [M,N]         b=W  [N,K] read MN-major (b_mn=True)
     weight grad  dW = dy^T @ x          a=dy [M,N] (a_mn)  b=x  [M,K] (b_mn), split-K fp32 atomics
+
+The reference reaches cuBLAS for these products through ``nn.Linear`` / ``torch.matmul`` (models/attention.py:766-793,
+models/mlp.py:478-530, core/dist_matmul.py:8-459); here they are one hand-written kernel family (csrc/gemm_sm100.cu).
 """
 from __future__ import annotations
 

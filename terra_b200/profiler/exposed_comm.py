@@ -8,7 +8,9 @@ union of the communication kernels' intervals, of which ``comm_hidden`` overlaps
 
     python -m torch.distributed.run --nproc-per-node N -m terra_b200.profiler.exposed_comm [--small]
 
-prints one JSON line from rank 0 (max over ranks of every figure)."""
+prints one JSON line from rank 0 (max over ranks of every figure). The reference has no such accounting (its profiler
+reports FLOPs and memory: profiler/flops_profiler.py:27-152, profiler/memory_timeline.py:172-727); the figure answers
+the "exposed communication per step" target of the benchmark plan."""
 from __future__ import annotations
 
 import json

@@ -11,6 +11,11 @@ back so that their concatenation along dim 0 is a free view (``module.fused["nam
 projection weights of an attention block form one ``[3C, C]`` GEMM operand while ``state_dict()`` still shows
 three tensors. Arena segments are grouped by the communication label of the parameter
 (``terra_grad_reduce_group``), so that gradient reduction and the sharded optimizer work on whole ranges.
+
+The reference keeps ordinary per-parameter tensors: gradients are reduced parameter by parameter
+(core/runtime/run_model.py:240-330), its ``DistributedAdamW`` assigns whole parameters to owners and broadcasts them
+(optimizer/distributed_adamw.py:122-146, 202-264); the arenas are what lets one collective and one kernel do that work
+here while the parameter names, shapes and ``state_dict`` stay the reference's.
 """
 from __future__ import annotations
 

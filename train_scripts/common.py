@@ -1,4 +1,6 @@
-"""Shared set-up of the four entry points: distributed bootstrap, config defaults, topology, model, optimizer, data."""
+"""Shared set-up of the four entry points: distributed bootstrap, config defaults, topology, model, optimizer, data
+(what the reference repeats at the top of each script: train_scripts/train.py:40-53, 372-470; finetune.py:334-470;
+test_pretrain.py:100-390; test_finetune.py:100-360)."""
 from __future__ import annotations
 
 import argparse
