@@ -37,4 +37,4 @@ if command -v nvcc >/dev/null 2>&1; then
   echo "sm_100a cross-compile: ok"
 fi
 
-"$py" -m pytest -q tests -m "not gpu"
+"$py" -m pytest -q tests -m "not gpu" "$@"
