@@ -283,7 +283,9 @@ def _extra_layout_in_child(args, layout, rank, port):
         return None
     try:
         with open(out) as f:
-            return json.load(f)
+            result = json.load(f)
+        os.unlink(out)
+        return result
     except Exception:
         return {"error": f"child exit code {child.returncode}: {(err or '').strip()[-300:]}"}
 
