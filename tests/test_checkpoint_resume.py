@@ -144,7 +144,9 @@ def test_finetune_harness_data_path_switches(tmp_path):
     assert len(rows) == 2 and all(float(r["input_transfer_time_s"]) > 0 for r in rows)
     assert all(float(r["step_time_s"]) > float(r["input_transfer_time_s"]) for r in rows)
     leads = list(csv.DictReader(open(tmp_path / "leads.csv")))
-    assert [int(r["lead"]) for r in leads] == [0, 1, 0, 1]            # two leads per step, the per-lead plan recorded
+    assert [int(r["lead"]) for r in leads] == [1, 2, 1, 2]            # two leads per step, numbered from 1
+    assert [r["checkpoint_layers"] for r in leads[:2]] == ["[]", '["0-1"]'] and leads[1]["checkpoint_label"] == "lead2-2"
+    assert {r["transformer_activation_mode"] for r in leads} == {"none", "torch_recompute"}
 
     bad = dict(cfg, input_double_buffer=True)
     path2 = tmp_path / "bad.yaml"

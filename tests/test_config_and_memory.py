@@ -293,3 +293,50 @@ def test_nvtx_decorator_is_a_no_op_by_default():
         return x + 1
 
     assert nvtx.ENABLED is False and nvtx.nvtx_range("t")(f) is f
+
+
+def test_lead_schedules_parse_the_reference_formats_and_drive_the_model():
+    """Per-lead activation plans: dict and list forms, ranges, aliases, string layer lists, validation; applied to a
+    model only when the plan changes; sampling modes return to the base configuration outside their range."""
+    import pytest
+    from terra_b200.memory.lead_schedule import LeadScheduler, parse_lead_checkpoint_schedule, parse_lead_sampling_schedule
+    from terra_b200.models import SequentialHierarchicalSwin
+
+    act = {"mode": "torch_recompute", "offload": {"min_numel": 7},
+           "lead_checkpoint_schedule": [
+               {"lead": 3, "end": 4, "layers": "0-1, 3", "mode": "cpu_boundary_offload_recompute", "label": "late"},
+               {"start": 2, "checkpoint_layers": [0], "segment_activation_modes": "torch_recompute"}],
+           "lead_sampling_checkpoint_schedule": {"3-4": {"down": "d1", "up": "U0"}}}
+    plans = parse_lead_checkpoint_schedule(act)
+    assert [(p.lead_start, p.lead_end, p.label) for p in plans] == [(2, 2, "lead2-2"), (3, 4, "late")]
+    assert plans[1].checkpoint_layers == ["0-1", "3"] and plans[1].offload == {"min_numel": 7}
+    assert plans[1].segment_activation_modes == ["cpu_boundary_offload_recompute"] * 2
+    assert parse_lead_checkpoint_schedule({"lead_checkpoint_layers": {"1-2": [0, 1]}})[0].lead_end == 2      # older key
+    smp = parse_lead_sampling_schedule(act)
+    assert (smp[0].down, smp[0].up, smp[0].lead_start, smp[0].lead_end) == ("D1", "U0", 3, 4)
+    with pytest.raises(ValueError, match="must match checkpoint_layers"):
+        parse_lead_checkpoint_schedule({"lead_checkpoint_schedule": [{"lead": 1, "layers": [0, 1], "segment_activation_modes": ["none"]}]})
+    with pytest.raises(ValueError, match="missing checkpoint_layers"):
+        parse_lead_checkpoint_schedule({"lead_checkpoint_schedule": [{"lead": 1}]})
+    with pytest.raises(ValueError, match="must contain down or up"):
+        parse_lead_sampling_schedule({"lead_sampling_checkpoint_schedule": {"1": {"offload": {}}}})
+    with pytest.raises(ValueError, match="unsupported axes"):
+        parse_lead_sampling_schedule({"lead_sampling_checkpoint_schedule": [{"lead": 1, "down": "D0", "sampling_modes": {"side": "x"}}]})
+
+    model = SequentialHierarchicalSwin(padding_scale=1, num_channels=8, patch_size=4, window_size=8, height=64, width=128,
+                                       embedding_dim=32, num_heads=2, num_layers=4,
+                                       recompute_config={"mode": "torch_recompute", "checkpoint_layers": []})
+    sched = LeadScheduler(model, act)
+    rs = model.recompute_scheduler
+    sched.before_lead(0)                                   # lead 1: nothing scheduled, the installed plan stays
+    assert rs.checkpoint_segments == [] and model.checkpoint_down_mode == "none"
+    sched.before_lead(1)                                   # lead 2
+    assert rs.checkpoint_segments == [(0, 1)] and sched.describe(1)["checkpoint_label"] == "lead2-2"
+    sched.before_lead(2)                                   # lead 3: offload plan + sampling checkpoints
+    assert rs.checkpoint_segments == [(0, 2), (3, 4)] and rs.mode == "cpu_boundary_offload_recompute"
+    assert (model.checkpoint_down_mode, model.checkpoint_up_mode) == ("D1", "U0")
+    row = sched.describe(2)
+    assert row["lead"] == 3 and row["sampling_down"] == "D1" and row["checkpoint_layers"] == '["0-1", "3"]'
+    sched.before_lead(4)                                   # lead 5: sampling back to the base, transformer plan kept
+    assert (model.checkpoint_down_mode, model.checkpoint_up_mode) == ("none", "none")
+    assert rs.checkpoint_segments == [(0, 2), (3, 4)] and sched.describe(4)["checkpoint_label"] == "late"

@@ -1,15 +1,17 @@
 """Benchmark / correctness harness for rollout finetuning (reference: train_scripts/test_finetune.py:60-1270).
 
 Per step: loss, output sum, peak memory, step time, input-transfer time, offload statistics; ``--memory_timeline_csv``
-writes one row per (iteration, lead). Activation plans can change per lead:
+writes one row per (iteration, lead). Activation plans can change per lead (``activation.lead_checkpoint_schedule`` and
+``activation.lead_sampling_checkpoint_schedule``, leads numbered from 1; formats in
+``terra_b200/memory/lead_schedule.py``):
 
     activation:
-      lead_checkpoint_schedule:            # lead index -> plan applied just before that lead's forward
-        0: {checkpoint_layers: [], mode: none}
-        1: {checkpoint_layers: ['0-3'], mode: torch_recompute}
-        2: {checkpoint_layers: ['0-7'], mode: cpu_boundary_offload_recompute, offload: {min_numel: 1048576}}
-      lead_sampling_checkpoint_schedule:   # lead index -> {down: D0|D1|none, up: U0|U1|none}
-        2: {down: D1, up: U1}
+      lead_checkpoint_schedule:
+        "1": []
+        "2": ['0-3']
+        "3-4": {checkpoint_layers: ['0-7'], mode: cpu_boundary_offload_recompute, offload: {min_numel: 1048576}}
+      lead_sampling_checkpoint_schedule:
+        "3-4": {down: D1, up: U1}
 """
 from __future__ import annotations
 
@@ -28,44 +30,38 @@ from train_scripts.common import FINETUNE_DEFAULTS, Session, base_parser  # noqa
 from train_scripts.finetune import sequence_to_leads  # noqa: E402
 from terra_b200 import global_env_config as G  # noqa: E402
 from terra_b200.logging_utils import set_dp_rank_print_redirect  # noqa: E402
-from terra_b200.memory.activation import normalize_sampling_mode  # noqa: E402
+from terra_b200.memory.lead_schedule import LeadScheduler  # noqa: E402
 from terra_b200.memory.boundary_offload import get_boundary_offload_stats, reset_boundary_offload_stats  # noqa: E402
-from terra_b200.profiler.memory_timeline import CudaMemoryTimeline, set_memory_timeline_context  # noqa: E402
+from terra_b200.profiler.memory_timeline import (CudaMemoryTimeline, get_memory_timeline_peak_mib,  # noqa: E402
+                                                 mark_memory_timeline, set_memory_timeline_context)
 from terra_b200.runtime.finetune_one_step import one_step_finetune  # noqa: E402
 
 
-def _int_keys(d):
-    return {int(k): v for k, v in (d or {}).items()}
-
-
-def make_lead_callback(model, cfg, records):
-    """Applies ``lead_checkpoint_schedule`` / ``lead_sampling_checkpoint_schedule`` before each lead's forward."""
-    act = cfg.get("activation") or {}
-    plans = _int_keys(act.get("lead_checkpoint_schedule"))
-    sampling = _int_keys(act.get("lead_sampling_checkpoint_schedule"))
-    real = model.module if hasattr(model, "module") else model
-    sched = real.recompute_scheduler
-    base_down, base_up = real.checkpoint_down_mode, real.checkpoint_up_mode
+def make_lead_callback(model, cfg, records, timeline_rows_wanted=False, device=None):
+    """Applies the per-lead activation plans before each lead's forward and records one row per lead (the fields of
+    the reference's ``--memory_timeline_csv``: train_scripts/test_finetune.py:671-800)."""
+    sched = LeadScheduler(model, cfg.get("activation") or {})
+    if not (sched.active or timeline_rows_wanted):
+        return None, sched
 
     def callback(event, lead, loss):
         if event == "before_forward":
-            plan = plans.get(lead)
-            if plan is not None:
-                sched.set_checkpoint_plan(plan.get("checkpoint_layers", []), plan.get("mode"), plan.get("offload"),
-                                          plan.get("segment_activation_modes"))
-            smp = sampling.get(lead)
-            if smp is not None:
-                real.checkpoint_down_mode = normalize_sampling_mode(smp.get("down"), "down")
-                real.checkpoint_up_mode = normalize_sampling_mode(smp.get("up"), "up")
-            else:
-                real.checkpoint_down_mode, real.checkpoint_up_mode = base_down, base_up
-            records.append(dict(lead=lead, segments=list(sched.checkpoint_segments), mode=sched.mode,
-                                down=real.checkpoint_down_mode, up=real.checkpoint_up_mode,
-                                allocated_mib=torch.cuda.memory_allocated() / 2 ** 20 if torch.cuda.is_available() else 0.0))
-        elif event == "after_loss" and records:
-            records[-1]["loss"] = float(loss.detach().item()) if loss is not None else None
+            set_memory_timeline_context(lead_idx=int(lead) + 1)
+            sched.before_lead(lead)
+            mark_memory_timeline("rollout_lead_pre", f"lead_{int(lead) + 1}", lead_idx=int(lead) + 1)
+        elif event == "after_loss":
+            mark_memory_timeline("rollout_lead_post", f"lead_{int(lead) + 1}", lead_idx=int(lead) + 1)
+            row = sched.describe(lead)
+            on_gpu = device is not None and device.type == "cuda"
+            if on_gpu:
+                torch.cuda.synchronize(device)
+            row.update(allocated_memory_mb=torch.cuda.memory_allocated(device) / 2 ** 20 if on_gpu else 0.0,
+                       reserved_memory_mb=torch.cuda.memory_reserved(device) / 2 ** 20 if on_gpu else 0.0,
+                       peak_memory_mb=get_memory_timeline_peak_mib(),
+                       loss=float(loss.detach().float().item()) if loss is not None else "")
+            records.append(row)
 
-    return callback if (plans or sampling) else (lambda event, lead, loss: records.append(dict(lead=lead)) if event == "before_forward" else None)
+    return callback, sched
 
 
 def main(argv=None):
@@ -119,7 +115,7 @@ def main(argv=None):
         load_time = time.time() - t_load
         leads, frames = sequence_to_leads(s, seq, lead)
         records = []
-        cb = make_lead_callback(s.model, c, records)
+        cb, _ = make_lead_callback(s.model, c, records, args.memory_timeline_csv is not None, s.device)
         if s.device.type == "cuda":
             torch.cuda.reset_peak_memory_stats(s.device)
         set_memory_timeline_context(iter=i)
