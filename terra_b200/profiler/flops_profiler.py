@@ -8,10 +8,37 @@ FLOPs the profiler cannot see, ``analytic_step_flops`` supplies the model's FLOP
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
+
+
+@dataclass
+class FlopsSummary:
+    """What the profiler counted (reference: profiler/flops_profiler.py:7-24). ``enabled`` False: nothing was profiled
+    and every figure is zero."""
+    enabled: bool
+    local_flops_per_step: float = 0.0
+    world_flops_per_step: float = 0.0
+    world_avg_flops_per_step: float = 0.0
+    active_steps: int = 0
+    event_count: int = 0
+
+    def local_tflops(self, step_time_s: float) -> float:
+        return self.local_flops_per_step / step_time_s / 1e12 if step_time_s > 0 else 0.0
+
+    def world_tflops(self, step_time_s: float) -> float:
+        return self.world_flops_per_step / step_time_s / 1e12 if step_time_s > 0 else 0.0
+
+    def as_metadata(self) -> Dict[str, float]:
+        """The ``flops_profiler_*`` keys of the harnesses' JSON records."""
+        return {"flops_profiler_enabled": self.enabled, "flops_profiler_active_steps": self.active_steps,
+                "flops_profiler_event_count": self.event_count,
+                "flops_profiler_local_flops_per_step": self.local_flops_per_step,
+                "flops_profiler_world_flops_per_step": self.world_flops_per_step,
+                "flops_profiler_world_avg_flops_per_step": self.world_avg_flops_per_step}
 
 
 class TorchFlopsProfiler:
@@ -21,6 +48,7 @@ class TorchFlopsProfiler:
         self.rank = rank
         self.trace_dir = trace_dir
         self.prof = None
+        self._summary = None
 
     def __enter__(self):
         if not self.enabled:
@@ -50,20 +78,27 @@ class TorchFlopsProfiler:
     def total_steps(self) -> int:
         return (self.wait + self.warmup + self.active) * max(1, self.repeat)
 
-    def summarize(self) -> Dict[str, float]:
+    def summarize(self) -> "FlopsSummary":
+        """FLOPs per active step on this rank, summed and averaged over the ranks. Collective when a process group is
+        up, so every rank calls it; the result is kept, later calls return it without communicating."""
+        if self._summary is not None:
+            return self._summary
         if self.prof is None:
-            return {}
-        flops = sum(getattr(e, "flops", 0) or 0 for e in self.prof.key_averages())
-        per_step = flops / max(1, self.active * max(1, self.repeat))
-        out = {"flops_per_step_local": float(per_step)}
+            self._summary = FlopsSummary(enabled=False)
+            return self._summary
+        counted = [getattr(e, "flops", 0) or 0 for e in self.prof.key_averages()]
+        steps = max(1, self.active * max(1, self.repeat))
+        local = float(sum(counted)) / steps
+        world_sum = world_avg = local
         if dist.is_available() and dist.is_initialized():
-            t = torch.tensor([per_step], dtype=torch.float64, device="cuda" if torch.cuda.is_available() else "cpu")
+            t = torch.tensor([local], dtype=torch.float64, device="cuda" if torch.cuda.is_available() else "cpu")
             dist.all_reduce(t)
-            out["flops_per_step_world_sum"] = float(t.item())
-            out["flops_per_step_world_avg"] = float(t.item() / dist.get_world_size())
-        else:
-            out["flops_per_step_world_sum"] = out["flops_per_step_world_avg"] = float(per_step)
-        return out
+            world_sum = float(t.item())
+            world_avg = world_sum / dist.get_world_size()
+        self._summary = FlopsSummary(enabled=True, local_flops_per_step=local, world_flops_per_step=world_sum,
+                                     world_avg_flops_per_step=world_avg, active_steps=steps,
+                                     event_count=sum(1 for f in counted if f > 0))
+        return self._summary
 
     def top_ops(self, n=20) -> List[Dict[str, float]]:
         if self.prof is None:

@@ -1,5 +1,10 @@
 """Step-runtime helpers that need no GPU."""
+import os
+import sys
+
 import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_arena_gradient_report_lists_every_parameter_up_to_the_limit():
@@ -139,3 +144,67 @@ def test_buffer_helpers():
     assert h.shape == t.shape and h.stride() == t.stride() and h.device.type == "cpu"
     assert Bf.get_cuda_stream("cpu") is None or torch.cuda.is_available()
     Bf.release_preallocated_buffers()
+
+
+def test_harness_metric_files_use_the_reference_columns(tmp_path):
+    """The harnesses' CSV columns and JSON keys, in the reference's names and order (train_scripts/test_pretrain.py:555-660,
+    train_scripts/test_finetune.py:1105-1206 there), with this framework's additional columns after them."""
+    import argparse
+    import csv
+    import json
+    import types
+
+    import torch
+
+    sys.path.insert(0, ROOT)
+    from train_scripts import metrics as M
+    from terra_b200.profiler.flops_profiler import FlopsSummary
+
+    archi = dict(height=100, width=200, padded_shape=[128, 256], initial_padding=[14, 14, 28, 28], padding_policy="auto",
+                 padding_spec=dict(need_padding=True, patch_token_resolution=(32, 64), transformer_token_resolution=(16, 32),
+                                   num_windows=(2, 4), transformer_downsample_scale=2))
+    pad = M.padding_facts(archi)
+    assert pad["padded_shape"] == (128, 256) and pad["input_shape"] == (100, 200) and pad["need_padding"] is True
+    assert abs(pad["padding_overhead_pct"] - (128 * 256 / 20000 - 1) * 100) < 1e-9
+
+    r = M.finetune_row(0, 4, "mean", 0.5, 3.0, torch.bfloat16, 10.0, 2.0, 1.5, 0.1, local_flops_per_step=4e12, h2d_bytes=7)
+    assert list(r)[:len(M.FINETUNE_COLUMNS)] == list(M.FINETUNE_COLUMNS) and r["h2d_bytes"] == 7
+    assert r["loss_per_lead"] == 0.5 and r["loss_sum_estimated"] == 2.0 and r["rest_time_s"] == 0.5 and r["flops_tflops"] == 2.0
+    r = M.finetune_row(0, 4, "sum", 2.0, 3.0, torch.float32, 10.0, 2.0, None, None)
+    assert r["loss_per_lead"] == 0.5 and r["loss_sum_estimated"] == 2.0 and r["rest_time_s"] is None and r["flops_tflops"] == 0.0
+
+    ns = argparse.Namespace(metrics_csv=str(tmp_path / "a" / "m.csv"), metrics_json=None, metrics_no_json=False,
+                            model_cfg="x.yaml", memory_timeline_csv=None)
+    assert M.json_path_for(ns) == str(tmp_path / "a" / "m.json")
+    assert M.json_path_for(argparse.Namespace(metrics_csv="m.csv", metrics_json="j.json", metrics_no_json=True)) is None
+
+    model = torch.nn.Linear(3, 2)
+    session = types.SimpleNamespace(
+        model=model, archi=archi, world=1, dp=1, task_type="glorys", model_type="sequential",
+        other=dict(wp_topo=[1, 1], xfmr_wp_topo=[1, 1], tensor_parallel_size=1),
+        cfg=dict(optimizer_config=7, precision="bf16", micro_batch_size=1, padding_scale=1, num_layers=4))
+    rows = [dict(iter=i, loss=1.0 - 0.1 * i, output_sum=2.0, output_dtype="torch.float32", peak_memory_mb=5.0,
+                 step_time_s=0.25, forward_time_s=0.1) for i in range(2)]
+    facts = M.gather_run_facts(session, rows, dict(offloaded_tensors=0))
+    assert facts["parameter_count"]["global_parameter_count"] == 8 and facts["parameter_count"]["fsdp_group_size"] == 1
+    assert facts["step_time_last_by_rank"] == [0.25] and facts["boundary_offload_stats_by_rank"] == [dict(offloaded_tensors=0)]
+    M.write_pretrain_metrics(session, ns, rows, facts, FlopsSummary(enabled=False), extra=dict(final_loss=0.9))
+    got = list(csv.DictReader(open(ns.metrics_csv)))
+    assert list(got[0])[:len(M.PRETRAIN_COLUMNS)] == list(M.PRETRAIN_COLUMNS) and list(got[0])[-1] == "forward_time_s"
+    assert got[1]["padded_shape"] == "(128, 256)" and got[1]["num_windows"] == "(2, 4)" and got[1]["iter"] == "1"
+    meta = json.load(open(tmp_path / "a" / "m.json"))
+    for k in ("model_cfg", "steps", "ranks_per_dp", "wp_topo", "padding_overhead_pct", "parameter_count",
+              "parameter_count_method", "pre_wrap_parameter_counts_by_rank", "flops_profiler_enabled",
+              "flops_profiler_world_avg_flops_per_step", "final_loss"):
+        assert k in meta, k
+    assert meta["steps"] == 2 and meta["padded_shape"] == [128, 256] and meta["flops_profiler_enabled"] is False
+
+    ns.memory_timeline_csv = str(tmp_path / "a" / "leads.csv")
+    lead_rows = [dict(iter=0, lead=1, checkpoint_label="lead1-1", loss=0.3, peak_memory_mb=1.0)]
+    M.write_finetune_metrics(session, ns, [M.finetune_row(0, 2, "mean", 0.5, 3.0, "torch.float32", 10.0, 2.0, 1.0, 0.1)],
+                             lead_rows, facts, FlopsSummary(enabled=False), 2, "mean", dict(input_double_buffer=True))
+    assert list(csv.DictReader(open(ns.memory_timeline_csv)))[0]["checkpoint_label"] == "lead1-1"
+    assert tuple(csv.DictReader(open(ns.memory_timeline_csv)).fieldnames) == M.LEAD_COLUMNS
+    meta = json.load(open(tmp_path / "a" / "m.json"))
+    assert meta["script"] == "test_finetune.py" and meta["lead_time"] == 2 and meta["input_double_buffer"] is True
+    assert meta["parameter_count_by_rank"] == [8] and meta["test_iter_num"] == 1

@@ -15,8 +15,6 @@ writes one row per (iteration, lead). Activation plans can change per lead (``ac
 """
 from __future__ import annotations
 
-import csv
-import json
 import os
 import sys
 import time
@@ -28,8 +26,10 @@ import torch.distributed as dist  # noqa: E402
 
 from train_scripts.common import FINETUNE_DEFAULTS, Session, base_parser  # noqa: E402
 from train_scripts.finetune import sequence_to_leads  # noqa: E402
+from train_scripts.metrics import finetune_row, gather_run_facts, write_finetune_metrics  # noqa: E402
 from terra_b200 import global_env_config as G  # noqa: E402
 from terra_b200.logging_utils import set_dp_rank_print_redirect  # noqa: E402
+from terra_b200.profiler.flops_profiler import TorchFlopsProfiler, analytic_step_flops  # noqa: E402
 from terra_b200.memory.lead_schedule import LeadScheduler  # noqa: E402
 from terra_b200.memory.boundary_offload import get_boundary_offload_stats, reset_boundary_offload_stats  # noqa: E402
 from terra_b200.profiler.memory_timeline import (CudaMemoryTimeline, get_memory_timeline_peak_mib,  # noqa: E402
@@ -102,6 +102,11 @@ def main(argv=None):
     reset_boundary_offload_stats()
     mem_prof = args.mem_prof if args.mem_prof is not None else int(os.environ.get("MEM_PROF", G.MEM_PROF))
     timeline = CudaMemoryTimeline(s.device if s.device.type == "cuda" else None, enabled=mem_prof > 0)
+    use_prof = G.ENABLE_TORCH_PROF and not args.disable_torch_prof and not G.DISABLE_TORCH_PROF
+    prof = TorchFlopsProfiler(G.TORCH_PROF_STEP_LIST, enabled=use_prof, rank=s.rank,
+                              trace_dir="./log/torch_prof" if G.TORCH_PROF_WRITE_TRACE else None)
+    prof.__enter__()
+    analytic_flops = analytic_step_flops(s.archi, c["micro_batch_size"])      # one lead's forward and backward
     loader = s.finetune_loader(lead, status=0)
     rows, lead_rows = [], []
     it = iter(loader)
@@ -138,30 +143,31 @@ def main(argv=None):
         peak = torch.cuda.max_memory_allocated(s.device) / 2 ** 20 if s.device.type == "cuda" else 0.0
         peak = max(peak, timeline.iteration_peak_allocated_mib)      # peaks the timeline's interval resets folded away
         off = get_boundary_offload_stats()
-        rows.append(dict(iter=i, lead_time=lead, loss=float(loss.item()), output_sum=float(out_sum.item()),
-                         dtype=str(out.dtype), peak_memory_mb=peak, step_time_s=step_time, forward_time_s=fwd_time,
-                         load_data_time_s=load_time, input_transfer_time_s=transfer,
-                         offloaded_tensors=off["offloaded_tensors"], d2h_bytes=off["d2h_bytes"], h2d_bytes=off["h2d_bytes"]))
+        rows.append(finetune_row(i, lead, c["finetune_loss_reduction"], float(loss.item()), float(out_sum.item()), out.dtype,
+                                 peak, step_time, fwd_time, load_time, local_flops_per_step=analytic_flops * lead,
+                                 input_transfer_time_s=transfer, offloaded_tensors=off["offloaded_tensors"],
+                                 d2h_bytes=off["d2h_bytes"], h2d_bytes=off["h2d_bytes"]))
+        prof.step()
         for r in records:
             lead_rows.append(dict(iter=i, **{k: (str(v) if isinstance(v, list) else v) for k, v in r.items()}))
         if s.is_log_rank() and not args.quiet_metrics:
             print(f"iter {i} loss {rows[-1]['loss']:.8f} peak_memory_mb {peak:.1f} step_time_s {step_time:.4f} "
                   f"offloaded {off['offloaded_tensors']}", flush=True)
+    prof.__exit__(None, None, None)
+    flops_summary = prof.summarize()                      # collective: every rank
+    facts = gather_run_facts(s, rows, get_boundary_offload_stats())
     if s.is_log_rank():
-        for path, data in ((args.metrics_csv, rows), (args.memory_timeline_csv, lead_rows)):
-            if path and data:
-                os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
-                keys = sorted({k for r in data for k in r})
-                with open(path, "w", newline="") as f:
-                    w = csv.DictWriter(f, fieldnames=keys)
-                    w.writeheader()
-                    w.writerows(data)
-        if args.metrics_json and not args.metrics_no_json:
-            os.makedirs(os.path.dirname(os.path.abspath(args.metrics_json)), exist_ok=True)
-            with open(args.metrics_json, "w") as f:
-                json.dump(dict(description=c.get("description"), lead_time=lead, world_size=s.world,
-                               offload=get_boundary_offload_stats(), final_loss=rows[-1]["loss"],
-                               recompute=s.model.recompute_scheduler.summary()), f, indent=1, default=str)
+        data_path = dict(fake_input_dmp_local=bool(c.get("fake_input_dmp_local", False)),
+                         release_cpu_batch_after_transfer=release_cpu,
+                         dataloader_pin_memory=bool(c.get("dataloader_pin_memory", True)),
+                         input_transfer_non_blocking=non_blocking,
+                         include_input_transfer_in_step_time=count_transfer,
+                         input_double_buffer=bool(c.get("input_double_buffer", True)))
+        write_finetune_metrics(s, args, rows, lead_rows, facts, flops_summary, lead, c["finetune_loss_reduction"],
+                               data_path, extra=dict(
+                                   description=c.get("description"), offload=get_boundary_offload_stats(),
+                                   final_loss=rows[-1]["loss"], analytic_flops_per_step=analytic_flops * lead,
+                                   recompute=s.model.recompute_scheduler.summary()))
         if mem_prof > 0 and timeline.events:
             timeline.write_outputs(os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline"), "finetune_rank0")
     s.close()

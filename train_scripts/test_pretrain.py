@@ -6,8 +6,6 @@ the memory timeline on (2 adds the per-primitive summary).
 """
 from __future__ import annotations
 
-import csv
-import json
 import os
 import sys
 
@@ -17,6 +15,7 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 from train_scripts.common import PRETRAIN_DEFAULTS, Session, base_parser  # noqa: E402
+from train_scripts.metrics import gather_run_facts, write_pretrain_metrics  # noqa: E402
 from terra_b200 import global_env_config as G  # noqa: E402
 from terra_b200.logging_utils import set_dp_rank_print_redirect  # noqa: E402
 from terra_b200.memory.boundary_offload import get_boundary_offload_stats, reset_boundary_offload_stats  # noqa: E402
@@ -75,34 +74,22 @@ def main(argv=None):
                 dist.all_reduce(out_sum, group=s.manager.window_parallel_group)
             peak = torch.cuda.max_memory_allocated(s.device) / 2 ** 20 if s.device.type == "cuda" else 0.0
             peak = max(peak, timeline.iteration_peak_allocated_mib)      # peaks the timeline's interval resets folded away
-            rows.append(dict(iter=i, loss=float(loss.item()), output_sum=float(out_sum.item()), dtype=str(out.dtype),
-                             peak_memory_mb=peak, step_time_s=step_time, forward_time_s=fwd_time,
-                             padded_h=s.archi["padded_shape"][0], padded_w=s.archi["padded_shape"][1],
-                             padding_policy=s.archi.get("padding_policy", "")))
+            rows.append(dict(iter=i, loss=float(loss.item()), output_sum=float(out_sum.item()), output_dtype=str(out.dtype),
+                             peak_memory_mb=peak, step_time_s=step_time, forward_time_s=fwd_time))
             if s.is_log_rank() and not args.quiet_metrics:
                 print(f"iter {i} loss {rows[-1]['loss']:.8f} output_sum {rows[-1]['output_sum']:.6f} "
                       f"peak_memory_mb {peak:.1f} step_time_s {step_time:.4f}", flush=True)
+    flops_summary = prof.summarize()                      # collective: every rank
+    facts = gather_run_facts(s, rows)
     if s.is_log_rank():
-        if args.metrics_csv:
-            os.makedirs(os.path.dirname(os.path.abspath(args.metrics_csv)), exist_ok=True)
-            with open(args.metrics_csv, "w", newline="") as f:
-                w = csv.DictWriter(f, fieldnames=list(rows[0].keys()))
-                w.writeheader()
-                w.writerows(rows)
-        if args.metrics_json and not args.metrics_no_json:
-            total, trainable = count_parameters(s.model)
-            flops = analytic_step_flops(s.archi, c["micro_batch_size"])
-            times = [r["step_time_s"] for r in rows[1:]] or [rows[0]["step_time_s"]]
-            meta = dict(description=c.get("description"), model_type=s.model_type, world_size=s.world, dp=s.dp,
-                        wp_topo=list(s.other["wp_topo"]), xfmr_wp_topo=list(s.other["xfmr_wp_topo"]),
-                        xfmr_sp_size=s.other["xfmr_sp_size"], tensor_parallel_size=s.other["tensor_parallel_size"],
-                        optimizer_config=c["optimizer_config"], precision=s.precision, parameters=total,
-                        trainable_parameters=trainable, analytic_flops_per_step=flops,
-                        avg_step_time_s=sum(times) / len(times), tflops=flops / (sum(times) / len(times)) / 1e12,
-                        profiler=prof.summarize(), offload=get_boundary_offload_stats(), final_loss=rows[-1]["loss"])
-            os.makedirs(os.path.dirname(os.path.abspath(args.metrics_json)), exist_ok=True)
-            with open(args.metrics_json, "w") as f:
-                json.dump(meta, f, indent=1)
+        flops = analytic_step_flops(s.archi, c["micro_batch_size"])
+        times = [r["step_time_s"] for r in rows[1:]] or [rows[0]["step_time_s"]]
+        avg = sum(times) / len(times)
+        total, trainable = count_parameters(s.model)
+        write_pretrain_metrics(s, args, rows, facts, flops_summary, extra=dict(
+            description=c.get("description"), parameters=total, trainable_parameters=trainable,
+            analytic_flops_per_step=flops, avg_step_time_s=avg, tflops=flops / avg / 1e12,
+            offload=get_boundary_offload_stats(), final_loss=rows[-1]["loss"]))
         if mem_prof > 0 and timeline.events:
             # CSV, summary, event table and plot as the MEMORY_TIMELINE_WRITE_* switches ask
             timeline.write_outputs(os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline"), "rank0")
