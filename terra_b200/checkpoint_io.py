@@ -68,9 +68,20 @@ def strip_module_prefix(state_dict):
     return {(k[len("module."):] if k.startswith("module.") else k): v for k, v in state_dict.items()}
 
 
+def _non_parameters(real):
+    names = {n for n, _ in real.named_parameters()}
+    return {k: v.detach().cpu() for k, v in real.state_dict().items() if k not in names}
+
+
 def _owned_ranges(real, optimizer):
     """This rank's contiguous ranges of the flat fp32 masters (one per optimizer shard), and everything in the state
     dict that is not a parameter (buffers such as the relative-position index)."""
+    sharder = getattr(real, "_param_sharder", None)
+    if sharder is not None:
+        # sharded parameters: the owned slices are all a rank holds; ranges are positions within their unit's arena
+        ranges = [dict(unit=u.name, label=r.label, rank=r.rank, size=r.size, start=r.start, end=r.end, lo=r.lo, hi=r.hi,
+                       master=r.own_master.detach().cpu().clone()) for u in sharder.all_units() for r in u.ranges]
+        return {"__flat_ranges__": ranges, "__numel__": int(sharder.total_numel()), "__non_parameters__": _non_parameters(real)}
     arena = real._param_arena
     names = {id(p): n for n, p in real.named_parameters()}
     param_keys = {names[id(p)] for p in arena.params if id(p) in names}
@@ -83,6 +94,24 @@ def _owned_ranges(real, optimizer):
 def _restore_owned_ranges(real, optimizer, saved):
     """Inverse of ``_owned_ranges``: own ranges from the file, the rest from their owners (every element of a shard's
     segment has exactly one owner in the shard's group, so a sum over the group puts the pieces together)."""
+    sharder = getattr(real, "_param_sharder", None)
+    if sharder is not None:
+        if int(saved["__numel__"]) != int(sharder.total_numel()):
+            raise ValueError("sharded checkpoint was written for a model with a different parameter count")
+        mine = [(u, r) for u in sharder.all_units() for r in u.ranges]
+        if len(mine) != len(saved["__flat_ranges__"]):
+            raise ValueError("sharded checkpoint was written for a different unit layout")
+        for (u, r), rg in zip(mine, saved["__flat_ranges__"]):
+            if (rg.get("unit"), rg["label"], rg["rank"], rg["size"], rg["lo"], rg["hi"]) != (u.name, r.label, r.rank, r.size, r.lo, r.hi):
+                raise ValueError("sharded checkpoint was written for a different layout (use fsdp_checkpoint_type: full "
+                                 "to move between layouts)")
+            with torch.no_grad():
+                r.own_master.copy_(rg["master"])
+                if r.own_work is not None:
+                    r.own_work.copy_(r.own_master)
+        if saved["__non_parameters__"]:
+            real.load_state_dict(saved["__non_parameters__"], strict=False)
+        return
     arena = real._param_arena
     if int(saved["__numel__"]) != int(arena.numel):
         raise ValueError("sharded checkpoint was written for a model with a different parameter count")
@@ -108,8 +137,11 @@ def save_checkpoint(model, optimizer, loss, epoch, train_path, description, mode
     if hasattr(optimizer, "sync_masters"):
         optimizer.sync_masters()
     real = model.module if hasattr(model, "module") else model
+    sharder = getattr(real, "_param_sharder", None)
     # the gathered optimizer state is a collective: every rank takes part, rank 0 writes
     opt_state = optimizer.full_state_dict() if kind == "fsdp_full" else None
+    # so is the gathered model of sharded parameters (every kind but the per-rank one stores whole tensors)
+    full_model = sharder.full_state_dict() if (sharder is not None and kind != "fsdp_sharded") else None
     if should_write(kind, manager):
         d = checkpoint_dir(train_path, description, kind, manager, lead)
         os.makedirs(d, exist_ok=True)
@@ -117,6 +149,8 @@ def save_checkpoint(model, optimizer, loss, epoch, train_path, description, mode
         path = os.path.join(d, name)
         if kind == "fsdp_sharded":
             model_state = _owned_ranges(real, optimizer)
+        elif full_model is not None:
+            model_state = full_model
         else:
             model_state = {k: v.detach().cpu() for k, v in real.state_dict().items()}
         blob = {"model_state_dict": model_state,
@@ -144,6 +178,8 @@ def load_checkpoint(model, optimizer, train_path, description, model_type, optim
     real = model.module if hasattr(model, "module") else model
     if kind == "fsdp_sharded":
         _restore_owned_ranges(real, optimizer, blob["model_state_dict"])
+    elif getattr(real, "_param_sharder", None) is not None:
+        real._param_sharder.load_full_state_dict(strip_module_prefix(blob["model_state_dict"]), strict=strict)
     else:
         real.load_state_dict(strip_module_prefix(blob["model_state_dict"]), strict=strict)
     arena = getattr(real, "_param_arena", None)
@@ -173,7 +209,10 @@ def load_pretrained_weights(model, path, skip_suffixes=("attn_mask",), log=print
         else:
             dropped.append(k)
     missing = [k for k in own if k not in keep]
-    real.load_state_dict(keep, strict=False)
+    if getattr(real, "_param_sharder", None) is not None:
+        real._param_sharder.load_full_state_dict(keep, strict=False)      # collective: every rank loads the same file
+    else:
+        real.load_state_dict(keep, strict=False)
     arena = getattr(real, "_param_arena", None)
     if arena is not None:
         arena.sync_bf16()

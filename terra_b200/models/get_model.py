@@ -7,12 +7,19 @@ framework implements natively:
   4          replicated AdamW; gradients averaged over DP (and summed over WP / TP replicas) in one collective
              per parameter class - the role DDP + ``grad_post_process`` play in the reference
   6          ``DistributedAdamW``: reduce-scatter + sharded fp32 update + all-gather
-  1, 2, 3    ZeRO stages, 5 / 7 / 8 / 9 FSDP variants: run on the same sharded-optimizer path as 6 (optimizer state
-             and master weights sharded; parameters stay replicated in bf16 - 2 bytes per parameter - instead of
-             being re-gathered per unit)
+  5, 7, 8, 9 the reference's FSDP configurations, and 3 (ZeRO stage 3): parameters, gradients and optimizer state
+             sharded; a unit's parameters are all-gathered while it runs (``terra_b200.parallel.param_sharding``).
+             5 shards the model as one unit; 7 (TP = 1) and 8 / 9 (TP > 1) shard per ``FSDP_WRAPPER_CFG`` transformer
+             blocks, TP-sharded parameters over the ranks at the same TP rank, the others over the full replica group
+  1, 2       ZeRO stages 1 and 2: the sharded-optimizer path of 6 (state and updates sharded, gradients
+             reduce-scattered, parameters replicated)
   0          replicated AdamW
+
+``TERRA_PARAM_SHARDING=0`` runs 3 / 5 / 7 / 8 / 9 on the sharded-optimizer path instead (parameters replicated).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -65,17 +72,69 @@ def optimizer_state_tuple(optimizer_config: int, tensor_parallel_size: int = 1):
     return use_ddp, False, zero_stage, use_dist
 
 
+PARAM_SHARDING_CONFIGS = (3, 5, 7, 8, 9)
+
+
+def _sharded_parameters(model, archi, model_config, manager, oc):
+    """Cut the model into parameter-sharding units and return their optimizer (reference:
+    models/model_utils/get_model.py:1196-1283)."""
+    import torch.distributed as dist
+
+    from .. import global_env_config as G
+    from ..optim.sharded_param_adamw import ShardedParamAdamW
+    from ..parallel.param_sharding import ParamSharder
+
+    live = dist.is_available() and dist.is_initialized()
+
+    def resolve(label):
+        if manager is None or not live:
+            return None, 0, 1
+        if label == "xfmr_tp_param_group":
+            g = manager.xfmr_tp_param_replica_group
+        elif label == "full":
+            g = manager.full_param_replica_group
+        else:
+            raise ValueError(f"Unknown terra_grad_reduce_group: {label}")
+        if g is None and dist.get_world_size() == 1:
+            return None, 0, 1
+        if g is None:
+            raise ValueError(f"optimizer_config={oc} requires manager.{'xfmr_tp_param_replica_group' if label != 'full' else 'full_param_replica_group'}.")
+        return g, dist.get_rank(g), dist.get_world_size(g)
+
+    sharder = ParamSharder(model, resolve, blocks_per_unit=G.FSDP_WRAPPER_CFG, whole_model=(oc == 5),
+                           prefetch=archi.get("FSDP_CONFIG7_PREFETCH_POLICY", "none"))
+    if manager is None or manager.get_rank() == 0:
+        print(f"[FSDP] optimizer_config={oc} {sharder.describe()}, wrapper_cfg={G.FSDP_WRAPPER_CFG}", flush=True)
+    opt = ShardedParamAdamW(sharder, lr=float(model_config.get("learning_rate", 1e-4)), betas=(0.9, 0.95), weight_decay=0.1,
+                            manager=manager)
+    opt.global_step = 0
+    return opt
+
+
 def get_model_for_train(model_archi_params, model_config, task_type="glorys", model_type="sequential",
                         embedding_parallel_type=None, attn_parallel_type=None, mlp_parallel_type=None, manager=None,
                         device=None, kaiming_init=True):
     precision = model_config.get("precision", "bf16")
     if precision not in ("fp32", "fp16", "bf16"):
         raise ValueError(f"precision must be fp32, fp16 or bf16, got {precision!r}")
+    oc = int(model_config.get("optimizer_config", 4))
+    tp = int(model_config.get("tensor_parallel_size", 1) or 1)
+    if oc in (5, 7) and tp > 1:
+        raise ValueError(f"optimizer_config={oc} (FSDP) is currently only allowed when tensor_parallel_size == 1. Got "
+                         f"tensor_parallel_size={tp}. Use optimizer_config=8/9 for TP-aware FSDP or optimizer_config=6 "
+                         "for the custom distributed optimizer.")
+    if oc in (8, 9) and tp <= 1:
+        raise ValueError(f"optimizer_config={oc} (TP-aware FSDP) requires tensor_parallel_size > 1. Got "
+                         f"tensor_parallel_size={tp}. Use optimizer_config=7 for block-level FSDP.")
     model = get_model(model_archi_params, task_type, model_config.get("model_architecture"), kaiming_init, model_type,
                       embedding_parallel_type, attn_parallel_type, mlp_parallel_type, manager, device)
-    ParamArena(model)
-    state = optimizer_state_tuple(model_config.get("optimizer_config", 4), model_config.get("tensor_parallel_size", 1))
-    optimizer = get_optimizer(model, model_config, manager, use_dist_opt=state[3])
+    state = optimizer_state_tuple(oc, tp)
+    shard_params = oc in PARAM_SHARDING_CONFIGS and os.environ.get("TERRA_PARAM_SHARDING", "1") != "0"
+    if shard_params:
+        optimizer = _sharded_parameters(model, model_archi_params, model_config, manager, oc)
+    else:
+        ParamArena(model)
+        optimizer = get_optimizer(model, model_config, manager, use_dist_opt=state[3])
     gscaler = None
     on_cuda = device is not None and torch.device(device).type == "cuda"
     if on_cuda and precision == "fp32":
@@ -94,14 +153,14 @@ def get_model_for_train(model_archi_params, model_config, task_type="glorys", mo
                                  growth_interval=int(model_config.get("loss_scale_growth_interval", 2000)))
         else:
             gscaler = torch.amp.GradScaler("cpu", enabled=False)
-    oc = int(model_config.get("optimizer_config", 4))
-    if oc in (1, 2, 3, 5, 7, 8, 9) and not getattr(get_model_for_train, "_warned_fallback", False):
-        import warnings
+    if oc in (1, 2) or (oc in PARAM_SHARDING_CONFIGS and not shard_params):
+        if not getattr(get_model_for_train, "_warned_fallback", False):
+            import warnings
 
-        get_model_for_train._warned_fallback = True
-        warnings.warn(f"optimizer_config {oc}: DeepSpeed / FSDP wrappers are not used; this framework runs its own "
-                      "sharded optimizer (fp32 masters and moments sharded over the replica group, bf16 working copy "
-                      "replicated)", stacklevel=2)
+            get_model_for_train._warned_fallback = True
+            warnings.warn(f"optimizer_config {oc}: runs on the sharded optimizer (fp32 masters' updates and moments "
+                          "sharded over the replica group, gradients reduce-scattered, parameters replicated)",
+                          stacklevel=2)
     if on_cuda and manager is not None and manager.wp_size > 1 and model_config.get("comm_backend", "nvlink") == "nvlink":
         from ..parallel import nvlink
 

@@ -17,6 +17,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from .. import _ext
+from .packed import fp32_values
 from ..utils.nvtx import nvtx_range
 
 
@@ -275,7 +276,7 @@ class _WindowAttnFn(torch.autograd.Function):
     def forward(ctx, qkv, bias_table, geo, num_heads, shifted, use_mask, scale, comm):
         ext = _ext.load()
         C = qkv.shape[-1] // 3
-        bias_f32 = bias_table.detach().float().contiguous() if bias_table is not None else None
+        bias_f32 = fp32_values(bias_table).detach().float().contiguous() if bias_table is not None else None
         if comm is not None:
             staged = comm.alloc_qkv(qkv.shape[0], 3 * C)
             staged.copy_(qkv)

@@ -26,6 +26,7 @@ from .. import _ext
 from .attention import (MAX_KERNEL_WINDOW_TOKENS, WindowGeometry, launch_window_attn_bwd, launch_window_attn_fwd,
                         window_attention)
 from .gemm import gemm, status_word
+from .packed import fp32_values
 from ..utils.nvtx import nvtx_range
 
 LN_EPS = 1e-5
@@ -233,7 +234,7 @@ def attention_half(x, mod, geo: WindowGeometry, shifted: bool, comm=None):
             qkv_bg=fused["qkv_bias"].grad,
             proj_w=mod.attn.proj.weight.bf16, proj_b=mod.attn.proj.bias.bf16, proj_wg=mod.attn.proj.weight.grad,
             proj_bg=mod.attn.proj.bias.grad,
-            bias_table=mod.attn.relative_position_bias_table.data if has_bias else None,
+            bias_table=fp32_values(mod.attn.relative_position_bias_table) if has_bias else None,
             bias_table_g=mod.attn.relative_position_bias_table.grad if has_bias else None)
         return _AttnHalfFn.apply(x, mod.norm1.weight, pk, geo, mod.attn.num_heads, shifted, mod.use_attn_mask,
                                  mod.attn.scale, comm)

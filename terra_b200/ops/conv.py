@@ -24,6 +24,7 @@ import torch.nn.functional as TF
 from .. import _ext
 from . import _flags as F
 from .gemm import gemm, status_word
+from .packed import PACK_EPOCH, _packed, fp32_values, invalidate_packed_weights  # noqa: F401  (re-exported)
 from .blocks import FUSE_BIAS_GRAD, wgrad_accumulate, bias_grad_accumulate
 from ..utils.nvtx import nvtx_range
 
@@ -45,30 +46,6 @@ def pack_conv3x3_weight_dgrad(w: torch.Tensor) -> torch.Tensor:
     return pack_conv3x3_weight(w.flip(2, 3).transpose(0, 1))
 
 
-# Packed operands are functions of the bf16 working copy of a weight, which changes once per optimizer step. They are
-# cached per parameter and rebuilt when the parameter's version counter (bumped by the in-place optimizer update of the
-# master, or by a checkpoint load) or the working copy's address (arena rebinding) has moved.
-_PACK_CACHE = {}
-
-
-def _packed(weight, w16, kind, builder):
-    import weakref
-
-    key = (id(weight), kind)
-    stamp = (weight._version, w16.data_ptr(), PACK_EPOCH[0])
-    hit = _PACK_CACHE.get(key)
-    if hit is not None and hit[0] == stamp and hit[2]() is weight:
-        return hit[1]
-    val = builder(w16)
-    _PACK_CACHE[key] = (stamp, val, weakref.ref(weight))
-    return val
-
-
-PACK_EPOCH = [0]      # bumped by the optimizers after every step (the fused kernels write the working copy directly)
-
-
-def invalidate_packed_weights() -> None:
-    PACK_EPOCH[0] += 1
 
 
 _SCRATCH = {}

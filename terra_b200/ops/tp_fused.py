@@ -20,6 +20,7 @@ import torch
 from ..parallel.nvlink import BARRIER_SPIN_LIMIT as PEER_WAIT_NS
 from .. import _ext
 from .gemm import gemm
+from .packed import fp32_values
 
 
 class TpFusedComm:
@@ -399,7 +400,7 @@ def tp_attention_half(x, mod, geo, attn_comm, comm: TpFusedComm, rows_pad: int, 
         qkv_w=fused["qkv_weight"].bf16, qkv_b=fused["qkv_bias"].bf16, qkv_wg=fused["qkv_weight"].grad,
         qkv_bg=fused["qkv_bias"].grad, proj_w=a.proj.weight.bf16, proj_wg=a.proj.weight.grad,
         proj_b=a.proj_bias.bf16, proj_bg=a.proj_bias.grad,
-        bias_table=a.relative_position_bias_table.data if has_bias else None,
+        bias_table=fp32_values(a.relative_position_bias_table) if has_bias else None,
         bias_table_g=a.relative_position_bias_table.grad if has_bias else None)
     return _TpAttnHalfFn.apply(x, mod.norm1.weight, pk, geo, a.num_heads, mod.shifted, mod.use_attn_mask, a.scale,
                                attn_comm, comm, rows_pad, ragged)

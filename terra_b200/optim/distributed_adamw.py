@@ -61,6 +61,11 @@ class DistributedAdamW(torch.optim.Optimizer):
             group, rank, size = self._resolve_group(seg.label, process_group)
             self.shards.append(_Shard(seg.label, group, rank, size, seg.start, seg.end))
         self.fused = None     # peer-memory implementation (attached by terra_b200.parallel.nvlink)
+        if self.arena.bf16 is not None and any(sh.size > 1 for sh in self.shards):
+            # the step refreshes every replica's bf16 working copy but only the owner's fp32 master: kernels that read a
+            # parameter in fp32 take the widened working copy instead (ops/packed.py)
+            for p in self.arena.params:
+                p.terra_master_sharded = True
 
     def _resolve_group(self, label, process_group):
         live = dist.is_available() and dist.is_initialized()

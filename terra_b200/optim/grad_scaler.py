@@ -63,6 +63,12 @@ class LossScaler:
         """Inspect, then either run ``optimizer.step(grad_scale=...)`` with the un-scaling and the clip coefficient
         folded in, or skip. Returns ``True`` when the step ran. Call ``update()`` afterwards."""
         found_inf, norm = self.inspect(grad, group)
+        return self.step_with_stats(optimizer, found_inf, norm * self.get_scale(), clip_max_norm)
+
+    def step_with_stats(self, optimizer, found_inf: bool, scaled_norm: float, clip_max_norm: Optional[float] = None) -> bool:
+        """The decision of ``step`` from statistics gathered elsewhere: ``scaled_norm`` is the norm of the gradients as
+        they are (still multiplied by the loss scale)."""
+        norm = scaled_norm / self.get_scale()
         self._found_inf = found_inf
         if found_inf:
             self.skipped_steps += 1

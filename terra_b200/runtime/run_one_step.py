@@ -127,12 +127,19 @@ def optimizer_step(model, optimizer, gscaler, precision, clip_grad, on_cuda, sca
     max-norm 1.0), fold un-scaling and clipping into the optimizer kernel, skip the step on overflow and update the
     scale; without it, clip (fp16 only) and step. Returns ``True`` when the parameters were updated."""
     if scale != 1.0 or (on_cuda and precision == "fp16" and gscaler is not None and hasattr(gscaler, "inspect")):
-        arena = get_arena(_unwrap(model))
         group = dist.group.WORLD if (dist.is_available() and dist.is_initialized()) else None
-        ran = gscaler.step(optimizer, arena.grad, clip_max_norm=1.0 if clip_grad else None, group=group)
+        if hasattr(optimizer, "gradient_stats"):
+            # sharded parameters: the gradients live in the owned slices; the optimizer reports their statistics
+            ran = gscaler.step_with_stats(optimizer, *optimizer.gradient_stats(), clip_max_norm=1.0 if clip_grad else None)
+        else:
+            arena = get_arena(_unwrap(model))
+            ran = gscaler.step(optimizer, arena.grad, clip_max_norm=1.0 if clip_grad else None, group=group)
         gscaler.update()
         return ran
     if clip_grad and precision == "fp16":
-        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        if hasattr(optimizer, "clip_grad_norm_"):
+            optimizer.clip_grad_norm_(1.0)
+        else:
+            torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
     optimizer.step()
     return True

@@ -47,10 +47,19 @@ def _label_of(p) -> str:
 
 
 class ParamArena:
-    def __init__(self, model: torch.nn.Module, bf16_shadow: Optional[bool] = None):
-        params = [(n, p) for n, p in model.named_parameters()]
+    def __init__(self, model: torch.nn.Module, bf16_shadow: Optional[bool] = None, params=None, modules=None,
+                 segment_align: int = SEGMENT_ALIGN):
+        """``params`` (a list of ``(name, parameter)``) and ``modules`` (where fused groups are looked up) restrict the
+        arena to a part of ``model``, which then is not registered as the model's arena: the parameter-sharding units
+        (``terra_b200.parallel.param_sharding``) each own one. ``segment_align``: every segment's length is a multiple
+        of it (a multiple of ``ALIGN``; the default splits evenly over 1, 2, 4, 8 or 16 ranks)."""
+        partial = params is not None
+        params = [(n, p) for n, p in (model.named_parameters() if params is None else params)]
         if not params:
             raise ValueError("model has no parameters")
+        if segment_align % ALIGN:
+            raise ValueError(f"segment_align must be a multiple of {ALIGN}")
+        wanted = {id(p) for _, p in params}
         device = params[0][1].device
         self.device = device
         self.bf16_shadow = (device.type == "cuda") if bf16_shadow is None else bf16_shadow
@@ -59,14 +68,14 @@ class ParamArena:
         name_of = {id(p): n for n, p in params}
         placed = set()
         ordered: Dict[str, List[Tuple[List[torch.nn.Parameter], Optional[Tuple[torch.nn.Module, str]]]]] = {}
-        for mod in model.modules():
+        for mod in (model.modules() if modules is None else modules):
             groups = getattr(mod, "_fused_param_groups", None)
             if not groups:
                 continue
             local = dict(mod.named_parameters())
             for gname, names in groups.items():
                 members = [local[n] for n in names if n in local]
-                if len(members) != len(names) or any(id(m) in placed for m in members):
+                if len(members) != len(names) or any(id(m) in placed or id(m) not in wanted for m in members):
                     continue
                 labels = {_label_of(m) for m in members}
                 if len(labels) != 1:
@@ -90,7 +99,7 @@ class ParamArena:
                 for m in members:
                     offsets[id(m)] = cursor
                     cursor += m.numel()
-            cursor = (cursor + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
+            cursor = (cursor + segment_align - 1) // segment_align * segment_align
             self.segments.append(Segment(label, seg_start, cursor))
         self.numel = cursor
 
@@ -130,7 +139,8 @@ class ParamArena:
                     self.master[off:off + total].view(shape), self.grad[off:off + total].view(shape),
                     self.bf16[off:off + total].view(shape) if self.bf16 is not None else None)
         self.sync_bf16()
-        model._param_arena = self
+        if not partial:
+            model._param_arena = self
 
     def rebind(self, grad: torch.Tensor, bf16: Optional[torch.Tensor]) -> None:
         """Move the gradient arena (and the bf16 working copy) into caller-provided flat buffers of the same
