@@ -132,3 +132,24 @@ def test_precision_is_never_switched_silently():
 
     with pytest.raises(ValueError, match="precision"):
         get_model_for_train({}, {"precision": "fp8", "model_architecture": "nope"})
+
+
+def test_fp32_reads_take_the_working_copy_when_masters_are_sharded():
+    """A kernel that reads a parameter in fp32 (the relative-position bias table) must not read the fp32 master on a
+    rank that does not own it: under a sharded optimizer only the bf16 working copy is refreshed everywhere. The
+    widened copy is built once per optimizer step."""
+    import torch
+
+    from terra_b200.ops.packed import fp32_values, invalidate_packed_weights
+
+    p = torch.nn.Parameter(torch.full((4,), 1.0))
+    assert fp32_values(p).data_ptr() == p.data.data_ptr()                    # plain parameter: the master itself
+    p.bf16 = torch.full((4,), 2.0, dtype=torch.bfloat16)
+    assert fp32_values(p).data_ptr() == p.data.data_ptr()                    # replicated masters are exact everywhere
+    p.terra_master_sharded = True
+    a = fp32_values(p)
+    assert a.dtype == torch.float32 and a.tolist() == [2.0] * 4              # the gathered working copy, widened
+    assert fp32_values(p) is a                                               # cached within the step
+    p.bf16.fill_(3.0)
+    invalidate_packed_weights()                                              # what every optimizer step does
+    assert fp32_values(p).tolist() == [3.0] * 4
