@@ -148,6 +148,24 @@ def test_finetune_harness_data_path_switches(tmp_path):
     assert [r["checkpoint_layers"] for r in leads[:2]] == ["[]", '["0-1"]'] and leads[1]["checkpoint_label"] == "lead2-2"
     assert {r["transformer_activation_mode"] for r in leads} == {"none", "torch_recompute"}
 
+    # pretrained weights named by the config are imported before the run (here: every tensor zeroed, so the first loss
+    # is that of a model that outputs its bias-free zero field and differs from the seeded initialisation's)
+    maker = ("import sys, torch; sys.path.insert(0, %r); from train_scripts.common import FINETUNE_DEFAULTS, Session; "
+             "s = Session(%r, 1, dict(FINETUNE_DEFAULTS, use_fake_input=True)); "
+             "torch.save({'model_state_dict': {k: torch.zeros_like(v) for k, v in s.model.state_dict().items()}}, %r); s.close()"
+             % (ROOT, str(path), str(tmp_path / "zero.pth")))
+    made = subprocess.run([sys.executable, "-c", maker], env=env, capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert made.returncode == 0, made.stderr[-3000:]
+    path3 = tmp_path / "pre.yaml"
+    path3.write_text(yaml.safe_dump(dict(cfg, trained_model_checkpoint_path=str(tmp_path / "zero.pth"))))
+    out = subprocess.run([sys.executable, exe, "--model_cfg", str(path3), "--steps", "1", "--metrics_csv",
+                          str(tmp_path / "pre.csv"), "--metrics_no_json", "--disable_torch_prof", "--disable_rank_log_redirect"],
+                         env=env, capture_output=True, text=True, timeout=900, cwd=str(tmp_path))
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-4000:])
+    assert "[pretrained] loaded" in out.stdout and "No trained_model_config_path" not in out.stdout
+    first = list(csv.DictReader(open(tmp_path / "pre.csv")))[0]
+    assert abs(float(first["loss"]) - float(rows[0]["loss"])) > 1e-3 * float(rows[0]["loss"])
+
     bad = dict(cfg, input_double_buffer=True)
     path2 = tmp_path / "bad.yaml"
     path2.write_text(yaml.safe_dump(bad))

@@ -25,8 +25,12 @@ def pretrained_path(s: Session):
     c = s.cfg
     if c.get("trained_model_checkpoint_path"):
         return c["trained_model_checkpoint_path"]
-    if c.get("trained_model_config_path") and c.get("trained_model_epoch") is not None:
+    if c.get("trained_model_config_path"):
         src = load_yaml(c["trained_model_config_path"])
+        # the epoch to import: this run's key, else the epoch the pretraining config resumes from, else the
+        # reference's default of 200 (train_scripts/test_finetune.py:309 there)
+        epoch = c.get("trained_model_epoch")
+        epoch = src.get("ckpt_epoch", 200) if epoch is None else epoch
         kind = checkpoint_kind(src.get("model_type", s.model_type), s.opt_state)
 
         class _Rank0:
@@ -39,7 +43,7 @@ def pretrained_path(s: Session):
                 return 0 if c.get("load_pretrained_from_wp_rank0", True) else s.manager.get_wp_rank()
 
         d = checkpoint_dir(src.get("train_path", "./outputs"), src.get("description", "terra_run"), kind, _Rank0())
-        return os.path.join(d, f"epoch{c['trained_model_epoch']}.pth")
+        return os.path.join(d, f"epoch{epoch}.pth")
     return None
 
 

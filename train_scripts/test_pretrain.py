@@ -17,7 +17,7 @@ import torch.distributed as dist  # noqa: E402
 from train_scripts.common import PRETRAIN_DEFAULTS, Session, base_parser  # noqa: E402
 from train_scripts.metrics import gather_run_facts, write_pretrain_metrics  # noqa: E402
 from terra_b200 import global_env_config as G  # noqa: E402
-from terra_b200.logging_utils import set_dp_rank_print_redirect  # noqa: E402
+from terra_b200.logging_utils import debug_log_wp_ranks, set_dp_rank_print_redirect  # noqa: E402
 from terra_b200.memory.boundary_offload import get_boundary_offload_stats, reset_boundary_offload_stats  # noqa: E402
 from terra_b200.profiler.flops_profiler import TorchFlopsProfiler, analytic_step_flops  # noqa: E402
 from terra_b200.profiler.memory_timeline import CudaMemoryTimeline  # noqa: E402
@@ -42,8 +42,18 @@ def main(argv=None):
 
     s = Session(args.model_cfg, args.data_parallel_group_size, dict(PRETRAIN_DEFAULTS, use_fake_input=True))
     c = s.cfg
+    log_ranks = debug_log_wp_ranks(s.manager, s.model_type, s.other)
     set_dp_rank_print_redirect(s.manager, s.model_type, s.opt_state, s.other.get("embedding_parallel_type"),
-                               quiet=args.quiet_metrics, disable=args.disable_rank_log_redirect or s.world == 1)
+                               quiet=args.quiet_metrics, disable=args.disable_rank_log_redirect or s.world == 1,
+                               only_wp_ranks=log_ranks)
+    if s.manager.get_wp_rank() in log_ranks and not args.quiet_metrics:
+        o = s.other
+        print("[TERRA parallel config]", "task_type=", s.task_type, "model_architecture=", c.get("model_architecture"),
+              "model_type=", s.model_type, "dp_size=", s.dp, "ranks_per_dp=", s.world // max(1, s.dp), "wp_topo=", o["wp_topo"],
+              "xfmr_wp_topo=", o["xfmr_wp_topo"], "xfmr_sp_size=", o.get("xfmr_sp_size", 1), "tensor_parallel_size=",
+              o.get("tensor_parallel_size", 1), "sp_tp_placement=", o.get("sp_tp_placement", "tp_first"),
+              "embedding_parallel_type=", o.get("embedding_parallel_type"), "optimizer_config=", c["optimizer_config"],
+              "optimizer_state_tuple=", s.opt_state, flush=True)
     reset_boundary_offload_stats()
     mem_prof = args.mem_prof if args.mem_prof is not None else int(os.environ.get("MEM_PROF", G.MEM_PROF))
     timeline = CudaMemoryTimeline(s.device if s.device.type == "cuda" else None, enabled=mem_prof > 0)
