@@ -102,13 +102,11 @@ def _sharded_parameters(model, archi, model_config, manager, oc):
         return g, dist.get_rank(g), dist.get_world_size(g)
 
     sharder = ParamSharder(model, resolve, blocks_per_unit=G.FSDP_WRAPPER_CFG, whole_model=(oc == 5),
-                           prefetch=archi.get("FSDP_CONFIG7_PREFETCH_POLICY", "none"))
+                           prefetch=archi.get("FSDP_CONFIG7_PREFETCH_POLICY", "none"),
+                           sampling_units=int(archi.get("FSDP_SAMPLING_WRAPPER_CFG", 0) or 0) > 0)
     if manager is None or manager.get_rank() == 0:
-        print(f"[FSDP] optimizer_config={oc} {sharder.describe()}, wrapper_cfg={G.FSDP_WRAPPER_CFG}", flush=True)
-        if int(archi.get("FSDP_SAMPLING_WRAPPER_CFG", 0) or 0) > 0:
-            # the sampling blocks run as functions over their layers, not as module calls that a unit's hooks could
-            # bracket: their (few) parameters stay in the root unit, which is resident for the whole step
-            print("[FSDP] FSDP_SAMPLING_WRAPPER_CFG > 0: patch and sampling parameters stay in the root unit", flush=True)
+        print(f"[FSDP] optimizer_config={oc} {sharder.describe()}, wrapper_cfg={G.FSDP_WRAPPER_CFG}, "
+              f"sampling_wrapper_cfg={int(archi.get('FSDP_SAMPLING_WRAPPER_CFG', 0) or 0)}", flush=True)
     opt = ShardedParamAdamW(sharder, lr=float(model_config.get("learning_rate", 1e-4)), betas=(0.9, 0.95), weight_decay=0.1,
                             manager=manager)
     opt.global_step = 0

@@ -104,33 +104,54 @@ class _SwinBase(nn.Module):
     def _dom(self):
         return self.pctx.dom if self.parallel else None
 
+    def _in_unit(self, mod, fn, *args):
+        """Run a piece of the sampling path with the parameters of ``mod`` present: a plain call, unless the parameters
+        are sharded with the sampling modules as units of their own (``terra_b200.parallel.param_sharding``)."""
+        sharder = getattr(self, "_param_sharder", None)
+        if sharder is None:
+            return fn(*args)
+        return sharder.run_in_unit(mod, fn, *args)
+
     def _patch_embed(self, patches):
-        Bn, h, w, F = patches.shape
-        y = B.linear(patches.reshape(-1, F), self._embed_linear(), need_dx=patches.requires_grad)
-        return y.reshape(Bn, h, w, -1)
+        def run(patches):
+            Bn, h, w, F = patches.shape
+            y = B.linear(patches.reshape(-1, F), self._embed_linear(), need_dx=patches.requires_grad)
+            return y.reshape(Bn, h, w, -1)
+        return self._in_unit(self.patch_embed, run, patches)
 
     def _down_conv(self, x):
-        return conv3x3(x, unwrap(self.down_blk.conv), 2, self._dom())
+        return self._in_unit(self.down_blk, lambda t: conv3x3(t, unwrap(self.down_blk.conv), 2, self._dom()), x)
+
+    def _up_conv(self, x):
+        return self._in_unit(self.up_blk, lambda t: conv_transpose2x2(t, unwrap(self.up_blk.conv)), x)
 
     def _residual_first(self, blk, x):
-        return groupnorm_silu(conv3x3(x, unwrap(blk.b[0]), 1, self._dom()), blk.b[1], None, self._dom())
+        return self._in_unit(blk, lambda t: groupnorm_silu(conv3x3(t, unwrap(blk.b[0]), 1, self._dom()), blk.b[1], None,
+                                                           self._dom()), x)
 
     def _residual_second(self, blk, x, shortcut):
-        return groupnorm_silu(conv3x3(x, unwrap(blk.b[3]), 1, self._dom()), blk.b[4], shortcut, self._dom())
+        return self._in_unit(blk, lambda t, s: groupnorm_silu(conv3x3(t, unwrap(blk.b[3]), 1, self._dom()), blk.b[4], s,
+                                                              self._dom()), x, shortcut)
 
     def _down_block(self, x):
-        x = self._down_conv(x)
-        return self._residual_second(self.down_blk, self._residual_first(self.down_blk, x), x)
+        def run(x):
+            x = self._down_conv(x)
+            return self._residual_second(self.down_blk, self._residual_first(self.down_blk, x), x)
+        return self._in_unit(self.down_blk, run, x)
 
     def _up_block(self, x):
-        x = conv_transpose2x2(x, unwrap(self.up_blk.conv))
-        return self._residual_second(self.up_blk, self._residual_first(self.up_blk, x), x)
+        def run(x):
+            x = self._up_conv(x)
+            return self._residual_second(self.up_blk, self._residual_first(self.up_blk, x), x)
+        return self._in_unit(self.up_blk, run, x)
 
     def _patch_recovery(self, x, residual=None):
-        Bn, h, w, D = x.shape
-        res = None if residual is None else residual.reshape(Bn * h * w, -1)
-        y = B.linear(x.reshape(-1, D), self._recovery_linear(), residual=res)
-        return y.reshape(Bn, h, w, -1)
+        def run(x, residual):
+            Bn, h, w, D = x.shape
+            res = None if residual is None else residual.reshape(Bn * h * w, -1)
+            y = B.linear(x.reshape(-1, D), self._recovery_linear(), residual=res)
+            return y.reshape(Bn, h, w, -1)
+        return self._in_unit(self.patch_recovery, run, x, residual)
 
     def _ckpt(self, fn, *args, cfg):
         label = getattr(fn, "__name__", "piece")
@@ -170,7 +191,7 @@ class _SwinBase(nn.Module):
         elif mode == "U0":
             out = self._ckpt(lambda t, r: self._patch_recovery(self._up_block(t), r), x, residual, cfg=cfg)
         elif mode == "U1":
-            u = self._ckpt(lambda t: conv_transpose2x2(t, unwrap(self.up_blk.conv)), x, cfg=cfg)
+            u = self._ckpt(lambda t: self._up_conv(t), x, cfg=cfg)
             h = self._ckpt(lambda t: self._residual_first(self.up_blk, t), u, cfg=cfg)
             h = self._ckpt(lambda t, s: self._residual_second(self.up_blk, t, s), h, u, cfg=cfg)
             out = self._ckpt(lambda t, r: self._patch_recovery(t, r), h, residual, cfg=cfg)

@@ -6,7 +6,9 @@ The design here follows the flat arenas instead of wrapping modules:
 
 * A *unit* is a group of consecutive transformer blocks (``blocks_per_unit``, the reference's ``FSDP_WRAPPER_CFG``); every
   other parameter (patch embedding / recovery, sampling blocks) belongs to the *root* unit, as in the reference's default
-  ``FSDP_SAMPLING_WRAPPER_CFG: 0``. ``whole_model`` (config 5) makes the root the only unit.
+  ``FSDP_SAMPLING_WRAPPER_CFG: 0``. With ``sampling_units`` (that key at 1 or 2) the patch embedding, the down block, the
+  up block and the patch recovery are units of their own; the model runs those pieces as functions, so it brackets them
+  with ``run_in_unit`` instead of module hooks. ``whole_model`` (config 5) makes the root the only unit.
 * Each unit owns a flat arena (``ParamArena`` over its parameters): fp32 values, fp32 gradients and, on the GPU, the bf16
   working copy that the kernels read. The arena is cut per communication label exactly as the sharded optimizer cuts the
   model-wide arena, so TP-sharded parameters are split over the ranks that replicate them (fixed TP rank) and everything
@@ -249,7 +251,8 @@ class ParamSharder:
     """Owns the units of one model and the hooks that gather and release them."""
 
     def __init__(self, model: torch.nn.Module, resolve_group: Optional[Callable] = None, blocks_per_unit: int = 1,
-                 whole_model: bool = False, prefetch: str = "none", reshard_after_forward: bool = True):
+                 whole_model: bool = False, prefetch: str = "none", reshard_after_forward: bool = True,
+                 sampling_units: bool = False):
         prefetch = (prefetch or "none").lower()
         if prefetch not in PREFETCH_POLICIES:
             raise ValueError(f"Unsupported FSDP prefetch policy: {prefetch}")
@@ -263,6 +266,16 @@ class ParamSharder:
         self.units: List[ShardedUnit] = []
         self._hooks = []
         groups = [] if whole_model else transformer_block_groups(model, blocks_per_unit)
+        self.named_units: Dict[int, ShardedUnit] = {}          # id(module) -> unit, for run_in_unit
+        self._depth: Dict[int, int] = {}
+        head, tail = [], []
+        if sampling_units and not whole_model:
+            for attr, where in (("patch_embed", head), ("down_blk", head), ("up_blk", tail), ("patch_recovery", tail)):
+                mod = getattr(model, attr, None)
+                if isinstance(mod, torch.nn.Module) and any(p.requires_grad for p in mod.parameters()):
+                    where.append((attr, mod))
+        for attr, mod in head:
+            self._add_function_unit(attr, mod, names, taken, resolve)
         for uname, mods in groups:
             ps = []
             for m in mods:
@@ -279,6 +292,8 @@ class ParamSharder:
             for m in mods:
                 last = m is mods[-1]
                 self._hooks.append(m.register_forward_hook(lambda mod, args, out, u=unit, last=last: self._post_forward(u, out, last)))
+        for attr, mod in tail:
+            self._add_function_unit(attr, mod, names, taken, resolve)
         rest = [(n, p) for n, p in model.named_parameters() if id(p) not in taken and p.requires_grad]
         frozen = [n for n, p in model.named_parameters() if not p.requires_grad]
         if frozen:
@@ -286,11 +301,38 @@ class ParamSharder:
         self.root: Optional[ShardedUnit] = None
         if rest:
             covered = {id(x) for u_, mods in groups for m in mods for x in m.modules()}
+            covered |= {id(x) for _, mod in head + tail for x in mod.modules()}
             sub = [m for m in model.modules() if id(m) not in covered]
             self.root = ShardedUnit("root", model, rest, sub, resolve, -1)
             self._hooks.append(model.register_forward_pre_hook(lambda mod, args: self._root_pre_forward()))
         model._param_sharder = self
         model.pre_wrap_parameter_count = sum(p.numel() for p in self.param_order)
+
+    def _add_function_unit(self, name, mod, names, taken, resolve):
+        ps = [(names[id(p)], p) for p in mod.parameters() if id(p) not in taken and p.requires_grad]
+        for _, p in ps:
+            taken.add(id(p))
+        unit = ShardedUnit(name, self.model, ps, list(mod.modules()), resolve, len(self.units))
+        self.units.append(unit)
+        self.named_units[id(mod)] = unit
+        self._depth[id(mod)] = 0
+
+    def run_in_unit(self, mod: torch.nn.Module, fn: Callable, *args):
+        """``fn(*args)`` with the unit of ``mod`` resident; calls may nest (a block function calling its layers'
+        functions): the outermost one gathers and releases."""
+        unit = self.named_units.get(id(mod))
+        if unit is None:
+            return fn(*args)
+        key = id(mod)
+        if self._depth[key] == 0:
+            self._pre_forward(unit)
+        self._depth[key] += 1
+        try:
+            out = fn(*args)
+        finally:
+            self._depth[key] -= 1
+        self._post_forward(unit, out, last=self._depth[key] == 0)
+        return out
 
     # ------------------------------------------------------------------ schedule
     def all_units(self) -> List[ShardedUnit]:

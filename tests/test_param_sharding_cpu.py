@@ -77,6 +77,14 @@ def test_fsdp_configurations_match_the_sharded_optimizer(tmp_path):
     assert "[FSDP] optimizer_config=9" in log and "group sizes=[1, 2]" in log and "prefetch_policy=overlap" in log
     assert want[-1] < want[0] and all(abs(a - b) <= 1e-6 * abs(b) for a, b in zip(got, want)), (got, want)
 
+    # the sampling path as units of its own (bracketed function calls), with its checkpoint modes and prefetching
+    act = dict(mode="torch_recompute", checkpoint_layers=["0-1", "D1", "U0"])
+    want, _ = _pretrain_losses(tmp_path, "s6", dict(base, optimizer_config=6, activation=act), 2, steps=3)
+    got, log = _pretrain_losses(tmp_path, "s7", dict(base, optimizer_config=7, activation=act, FSDP_SAMPLING_WRAPPER_CFG=1,
+                                                     FSDP_CONFIG7_PREFETCH_POLICY="overlap"), 2, steps=3)
+    assert "units=8 (+root=False)" in log and "sampling_wrapper_cfg=1" in log
+    assert all(abs(a - b) <= 1e-6 * abs(b) for a, b in zip(got, want)), (got, want)
+
     want, _ = _pretrain_losses(tmp_path, "wp6", dict(base, optimizer_config=6), 2)
     for oc in (5, 7):
         got, log = _pretrain_losses(tmp_path, f"wp{oc}", dict(base, optimizer_config=oc), 2)
