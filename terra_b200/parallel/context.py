@@ -23,7 +23,7 @@ import torch
 import torch.nn.functional as TF
 
 from ..ops import blocks as B
-from ..ops.attention import WindowGeometry, window_attention, window_attention_reference
+from ..ops.attention import WindowGeometry, shifted_window_sources, window_attention, window_attention_reference
 from . import collectives as C
 from .window_assignment import window_owner_map
 
@@ -186,7 +186,16 @@ class ParallelContext:
             return self.fused_comm
         if self.n_wg == 1 and self.sp > 1 and os.environ.get("TERRA_SP_BASELINE", "ulysses") == "ulysses":
             return _UlyssesAttnComm(self, batch)
+        if self.sp == 1 and self.n_wg > 1 and os.environ.get("TERRA_WP_BASELINE", "exchange") == "exchange":
+            return self._cached_comm(_ShiftExchangeAttnComm, batch)
         return _PortableAttnComm(self, batch)
+
+    def _cached_comm(self, cls, batch):
+        """One communicator per batch size: its route tables are built once."""
+        cache = self.__dict__.setdefault("_comm_cache", {})
+        if (cls, batch) not in cache:
+            cache[(cls, batch)] = cls(self, batch)
+        return cache[(cls, batch)]
 
     # ---- factorised SP / TP halves on portable collectives (CPU oracle path and the NCCL baseline)
     def _tp_sizes_rows(self, batch):
@@ -434,6 +443,133 @@ class _PortableAttnComm:
         ids = torch.as_tensor(p.windows_of[p.wg_rank], device=qkv.device)
         mine = out[:, ids][:, :, p.sp_rank * sN:(p.sp_rank + 1) * sN]
         return mine.reshape(-1, C3 // 3)
+
+
+class _ShiftExchangeAttnComm(_PortableAttnComm):
+    """Window attention across window groups for ANY ownership map (contiguous or not), without gathering everything:
+    the shifted window ``g`` is computed by the owner of window ``g``, which pulls the pieces of it that live in other
+    windows - the role of the reference's quadrant exchange (core/window_parallel.py:26-266, point-to-point sends of the
+    window corners along routes derived from the owner map). Here the routes are index tables over token rows: one
+    all-to-all-v brings the foreign rows of every owned shifted window, the windows are then local (unshifted attention
+    for the interior ones, which takes the fast kernel on a GPU; the windows on the frame's last row / column, whose
+    tokens wrap around, with the region mask), and one all-to-all-v along the reversed routes returns the outputs to
+    their home rows. Unshifted blocks need no communication. Token shards (SP > 1) stay on the gather / all-to-all
+    baselines."""
+
+    def __init__(self, pctx: "ParallelContext", batch: int):
+        super().__init__(pctx, batch)
+        self._tables = {}
+
+    def _routes(self, device):
+        key = str(device)
+        if key in self._tables:
+            return self._tables[key]
+        p, Bn, N = self.p, self.batch, self.p.N
+        gfull = WindowGeometry(Bn, p.nWh, p.nWw, p.wh, p.ww)
+        src_win, src_tok, reg = (t.numpy() for t in shifted_window_sources(gfull, True))       # [nW, N]
+        owner = np.asarray(p.owner)
+        local_idx = np.zeros(owner.shape[0], dtype=np.int64)
+        counts = []
+        for g in range(p.n_wg):
+            local_idx[p.windows_of[g]] = np.arange(len(p.windows_of[g]))
+            counts.append(len(p.windows_of[g]))
+        me = p.wg_rank
+
+        def rows_of(rank_windows_count, b, wl, t):          # row of (batch b, local window wl, token t) on a rank
+            return (b * rank_windows_count + wl) * N + t
+
+        b_idx = np.arange(Bn)[:, None, None]
+        # what I need: for my shifted windows, the source rank / row of every token, in (b, window, token) order
+        mine = np.asarray(p.windows_of[me])
+        s_rank = owner[src_win[mine]]                                                     # [nWl, N]
+        s_row = rows_of(np.asarray(counts)[s_rank][None], b_idx, local_idx[src_win[mine]][None], src_tok[mine][None])
+        s_rank_b = np.broadcast_to(s_rank[None], s_row.shape).reshape(-1)                 # [Bn * nWl * N]
+        s_row = s_row.reshape(-1)
+        n_mine = s_row.shape[0]
+        recv_sizes = [int(((s_rank_b == r) & (r != me)).sum()) for r in range(p.n_wg)]
+        recv_start = np.concatenate([[0], np.cumsum(recv_sizes)])
+        assemble = np.empty(n_mine, dtype=np.int64)
+        local = s_rank_b == me
+        assemble[local] = s_row[local]
+        for r in range(p.n_wg):
+            if r == me:
+                continue
+            sel = s_rank_b == r
+            assemble[sel] = n_mine_rows(self, me) + recv_start[r] + np.arange(int(sel.sum()))
+        # what the others need from me, each in the destination's (b, window, token) order
+        send_index, send_sizes = [], []
+        for d in range(p.n_wg):
+            if d == me or counts[d] == 0:
+                send_sizes.append(0)
+                continue
+            theirs = np.asarray(p.windows_of[d])
+            from_me = owner[src_win[theirs]] == me                                        # [nWd, N]
+            rows = rows_of(counts[me], b_idx, local_idx[src_win[theirs]][None], src_tok[theirs][None])
+            pick = np.broadcast_to(from_me[None], rows.shape).reshape(-1)
+            send_index.append(rows.reshape(-1)[pick])
+            send_sizes.append(int(pick.sum()))
+        send_index = np.concatenate(send_index) if send_index else np.zeros(0, dtype=np.int64)
+        # the way back: the rows I received return to their sources in the order they came; my home rows are then
+        # either rows I computed myself or rows of the returned chunk, which arrives in my send order
+        return_index = np.concatenate([np.nonzero(s_rank_b == r)[0] for r in range(p.n_wg) if r != me] or
+                                      [np.zeros(0, dtype=np.int64)])
+        home = np.full(n_mine_rows(self, me), -1, dtype=np.int64)
+        home[s_row[local]] = np.nonzero(local)[0]
+        home[send_index] = n_mine + np.arange(send_index.shape[0])
+        if (home < 0).any():
+            raise RuntimeError("shift exchange: a home row has no producer (owner map and routes disagree)")
+        edge = np.array([i for i, g in enumerate(mine) if (reg[g] != reg[g][0]).any()], dtype=np.int64)
+        inner = np.array([i for i, g in enumerate(mine) if not (reg[g] != reg[g][0]).any()], dtype=np.int64)
+        to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+        t = dict(send_index=to(send_index), send_sizes=send_sizes, recv_sizes=recv_sizes, assemble=to(assemble),
+                 return_index=to(return_index), home=to(home), edge=to(edge), inner=to(inner),
+                 edge_reg=to(reg[mine[edge]]) if edge.size else None, windows=len(mine))
+        self._tables[key] = t
+        return t
+
+    def window_attention_portable(self, qkv, geo, num_heads, shifted, bias_table, use_mask, scale):
+        from ..ops.attention import attention_core_reference, relative_position_index
+
+        p, Bn, N = self.p, self.batch, self.p.N
+        C3 = qkv.shape[-1]
+        nWl = len(p.windows_of[p.wg_rank])
+        plain = WindowGeometry(Bn, nWl, 1, p.wh, p.ww)
+        if not shifted:
+            return window_attention(qkv.contiguous(), plain, num_heads, False, bias_table, use_mask, scale, None)
+        t = self._routes(qkv.device)
+        group = p.manager.xfmr_tp_param_group
+        got = C.all_to_all_rows(qkv.index_select(0, t["send_index"]), group, t["send_sizes"], t["recv_sizes"])
+        sq = torch.cat([qkv, got], 0).index_select(0, t["assemble"])                     # my shifted windows, complete
+        if not use_mask or t["edge"].numel() == 0:
+            o = window_attention(sq, plain, num_heads, False, bias_table, use_mask, scale, None)
+        else:
+            sq4 = sq.reshape(Bn, nWl, N, C3)
+            o4 = sq.new_zeros(Bn, nWl, N, C3 // 3)
+            if t["inner"].numel():
+                xi = sq4.index_select(1, t["inner"]).reshape(-1, C3)
+                oi = window_attention(xi, WindowGeometry(Bn, int(t["inner"].numel()), 1, p.wh, p.ww), num_heads, False,
+                                      bias_table, use_mask, scale, None)
+                o4 = o4.index_copy(1, t["inner"], oi.reshape(Bn, -1, N, C3 // 3).to(o4.dtype))
+            ne = int(t["edge"].numel())
+            hd = C3 // 3 // num_heads
+            xe = sq4.index_select(1, t["edge"]).reshape(Bn * ne, N, 3, num_heads, hd)
+            q, k, v = (xe[:, :, i].permute(0, 2, 1, 3) for i in range(3))                 # [Bn*ne, heads, N, hd]
+            bias = None
+            if bias_table is not None:
+                idx = relative_position_index(p.wh, p.ww).to(bias_table.device)
+                bias = bias_table[idx.reshape(-1)].reshape(N, N, num_heads).permute(2, 0, 1).to(q.dtype)
+            reg = t["edge_reg"]
+            mask = ((reg[:, :, None] != reg[:, None, :]).to(q.dtype) * -100.0).repeat(Bn, 1, 1)
+            oe = attention_core_reference(q, k, v, scale, bias, mask).permute(0, 2, 1, 3).reshape(Bn, ne, N, C3 // 3)
+            o4 = o4.index_copy(1, t["edge"], oe.to(o4.dtype))
+            o = o4.reshape(-1, C3 // 3)
+        back = C.all_to_all_rows(o.index_select(0, t["return_index"]), group, t["recv_sizes"], t["send_sizes"])
+        return torch.cat([o, back], 0).index_select(0, t["home"])
+
+
+def n_mine_rows(comm, rank) -> int:
+    """Rows of q/k/v a rank holds: batch x its windows x the window's tokens."""
+    return comm.batch * len(comm.p.windows_of[rank]) * comm.p.N
 
 
 class _UlyssesAttnComm(_PortableAttnComm):

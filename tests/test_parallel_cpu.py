@@ -69,7 +69,9 @@ WORKER = textwrap.dedent('''
         worst = max(worst, ((q.grad - g_ref).abs().max() / (g_ref.abs().max() + 1e-12)).item())
         checked += 1
     print("RESULT " + json.dumps(dict(rank=dist.get_rank(), loss=rep.item(), ref_loss=ref_loss.item(), out_err=out_err,
-                                      worst_grad_rel=worst, checked=checked)), flush=True)
+                                      worst_grad_rel=worst, checked=checked,
+                                      comms=sorted(c.__name__ for c, _ in getattr(t.model.pctx, "_comm_cache", {})))),
+          flush=True)
     dist.destroy_process_group()
 ''')
 
@@ -121,6 +123,25 @@ def test_parallel_layout_matches_serial(world, extra):
         assert abs(res["loss"] - res["ref_loss"]) < 1e-4 * max(1.0, abs(res["ref_loss"])), res
         assert res["out_err"] < 2e-3, res
         assert res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res
+        # window groups without token shards exchange only the pieces of their shifted windows
+        assert res["comms"] == (["_ShiftExchangeAttnComm"] if ("xfmr_wp_topo='(1, 1)'" not in extra and "sp_size" not in extra) else []), res
+
+
+@pytest.mark.parametrize("world,extra,baseline", [
+    (2, "wp_topo='(2, 1)', xfmr_wp_topo='(1, 2)', window_assignment_mode='regular'", "exchange"),          # column split
+    (2, "wp_topo='(2, 1)', xfmr_wp_topo='(2, 1)', window_assignment_mode='ragged_round_robin'", "exchange"),
+    (4, "wp_topo='(4, 1)', xfmr_wp_topo='(2, 2)', window_assignment_mode='regular'", "exchange"),          # 2-D blocks
+    (3, "wp_topo='(3, 1)', xfmr_wp_topo='(3, 1)', window_assignment_mode='ragged_round_robin'", "exchange"),
+    (2, "wp_topo='(2, 1)', xfmr_wp_topo='(1, 2)', window_assignment_mode='regular'", "gather"),            # the old baseline
+])
+def test_non_contiguous_window_ownership_matches_serial(world, extra, baseline):
+    """Ownership maps in which a rank's windows are not one range of the row-major order (column blocks, 2-D blocks,
+    round robin): the shifted windows are put together from routed pieces (reference: core/window_parallel.py:26-266);
+    ``TERRA_WP_BASELINE=gather`` keeps the gather-everything form."""
+    for res in _run(world, extra, TERRA_WP_BASELINE=baseline):
+        assert abs(res["loss"] - res["ref_loss"]) < 1e-4 * max(1.0, abs(res["ref_loss"])), res
+        assert res["out_err"] < 2e-3 and res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res
+        assert res["comms"] == (["_ShiftExchangeAttnComm"] if baseline == "exchange" else []), res
 
 
 def test_ragged_ownership_with_rectangular_windows_matches_serial():
