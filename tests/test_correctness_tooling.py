@@ -23,7 +23,7 @@ def test_generate_run_analyze(tmp_path):
                MODEL_PARALLEL_SIZE="2", DATA_PARALLEL_SIZE="1", CONFIG_DIR=str(tmp_path / "configs"),
                HEIGHT="64", WIDTH="128", PADDED_SHAPE_H="64", PADDED_SHAPE_W="128", NUM_CHANNELS="8", PATCH_SIZE="2",
                WINDOW_SIZE="4", SMALL_NUM_LAYERS="2", SMALL_EMBEDDING_DIM="32", SMALL_NUM_HEADS="2", PRECISION="fp32",
-               USE_FAKE_INPUT="1", WARMUP_STEPS="1", LOSS_FUNC="MSE", SEQ_OPTIMIZER_CONFIG="4", NUM_WORKERS="0",
+               USE_FAKE_INPUT="1", WARMUP_STEPS="1", LOSS_FUNC="MSE", NUM_WORKERS="0",
                SAMPLING_CHECKPOINT_DOWN="none", SAMPLING_CHECKPOINT_UP="none", ACTIVATION_MODE="none",
                MASTER_ADDR="127.0.0.1")
     _run([sys.executable, str(TOOLS / "generate_configs.py")], env)
@@ -41,7 +41,8 @@ def test_generate_run_analyze(tmp_path):
         out.mkdir(parents=True)
         cfg = tmp_path / "configs" / f"correctness_{case}.yaml"
         c = yaml.safe_load(cfg.read_text())
-        c.update(fake_length=4, use_splited_data=(case != "seq_fsdp"), optimizer_config=4 if case == "seq_fsdp" else 6)
+        c.update(fake_length=4, use_splited_data=(case != "seq_fsdp"))        # optimizer_config stays the generated 7 (sharded parameters)
+        assert c["optimizer_config"] == 7
         cfg.write_text(yaml.safe_dump(c, sort_keys=False))
         _run([sys.executable, "-m", "torch.distributed.run", "--master_addr", "127.0.0.1", "--master_port", str(port),
               "--nnodes", "1", "--nproc_per_node", str(nproc), "train_scripts/test_pretrain.py",
