@@ -107,6 +107,8 @@ class ShardedParamAdamW(torch.optim.Optimizer):
             bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
             denom = r.exp_avg_sq.sqrt().div_(math.sqrt(bc2)).add_(g0["eps"])
             r.own_master.addcdiv_(r.exp_avg, denom, value=-g0["lr"] / bc1)
+            if r.own_work is not None:
+                r.own_work.copy_(r.own_master)           # the kernel writes the bf16 slice itself
         return loss
 
     # ------------------------------------------------------------------ checkpoint surface

@@ -82,7 +82,8 @@ class OwnedRange:
 
 
 class ShardedUnit:
-    def __init__(self, name: str, model, named_params, modules, resolve_group: Callable, index: int):
+    def __init__(self, name: str, model, named_params, modules, resolve_group: Callable, index: int,
+                 bf16_shadow: Optional[bool] = None):
         self.name, self.index = name, index
         groups = {}
         for _, p in named_params:
@@ -92,7 +93,8 @@ class ShardedUnit:
         lcm = 16
         for _, _, size in groups.values():
             lcm = lcm * size // math.gcd(lcm, size)
-        self.arena = ParamArena(model, params=named_params, modules=modules, segment_align=ALIGN * lcm)
+        self.arena = ParamArena(model, bf16_shadow=bf16_shadow, params=named_params, modules=modules,
+                                segment_align=ALIGN * lcm)
         self.params = list(self.arena.params)
         if self.arena.bf16 is not None:
             for p in self.params:
@@ -252,11 +254,14 @@ class ParamSharder:
 
     def __init__(self, model: torch.nn.Module, resolve_group: Optional[Callable] = None, blocks_per_unit: int = 1,
                  whole_model: bool = False, prefetch: str = "none", reshard_after_forward: bool = True,
-                 sampling_units: bool = False):
+                 sampling_units: bool = False, bf16_shadow: Optional[bool] = None):
+        """``bf16_shadow``: keep a bf16 working copy next to the fp32 values (default: on CUDA only); it is then the copy
+        that is gathered, and the fp32 values exist only under ``summon_full_params``."""
         prefetch = (prefetch or "none").lower()
         if prefetch not in PREFETCH_POLICIES:
             raise ValueError(f"Unsupported FSDP prefetch policy: {prefetch}")
         self.model = model
+        self.bf16_shadow = bf16_shadow
         self.prefetch = prefetch
         self.reshard_after_forward = bool(reshard_after_forward)
         resolve = resolve_group or (lambda label: (None, 0, 1))
@@ -286,7 +291,7 @@ class ParamSharder:
             if not ps:
                 continue
             sub = [x for m in mods for x in m.modules()]
-            unit = ShardedUnit(uname, model, ps, sub, resolve, len(self.units))
+            unit = ShardedUnit(uname, model, ps, sub, resolve, len(self.units), bf16_shadow)
             self.units.append(unit)
             self._hooks.append(mods[0].register_forward_pre_hook(lambda mod, args, u=unit: self._pre_forward(u)))
             for m in mods:
@@ -303,7 +308,7 @@ class ParamSharder:
             covered = {id(x) for u_, mods in groups for m in mods for x in m.modules()}
             covered |= {id(x) for _, mod in head + tail for x in mod.modules()}
             sub = [m for m in model.modules() if id(m) not in covered]
-            self.root = ShardedUnit("root", model, rest, sub, resolve, -1)
+            self.root = ShardedUnit("root", model, rest, sub, resolve, -1, bf16_shadow)
             self._hooks.append(model.register_forward_pre_hook(lambda mod, args: self._root_pre_forward()))
         model._param_sharder = self
         model.pre_wrap_parameter_count = sum(p.numel() for p in self.param_order)
@@ -312,7 +317,7 @@ class ParamSharder:
         ps = [(names[id(p)], p) for p in mod.parameters() if id(p) not in taken and p.requires_grad]
         for _, p in ps:
             taken.add(id(p))
-        unit = ShardedUnit(name, self.model, ps, list(mod.modules()), resolve, len(self.units))
+        unit = ShardedUnit(name, self.model, ps, list(mod.modules()), resolve, len(self.units), self.bf16_shadow)
         self.units.append(unit)
         self.named_units[id(mod)] = unit
         self._depth[id(mod)] = 0

@@ -74,10 +74,60 @@ def loss_of(net, xs, y):
     return total
 
 
+def working_copy_mode(rank, world):
+    """The bookkeeping of the GPU form on CPU tensors: a bf16 working copy is what gets gathered, the fp32 values exist
+    only under ``summon_full_params``. No model compute (the CPU operators read the fp32 values): gradients are
+    written by hand, the way the GPU kernels write them into the gradient views."""
+    torch.manual_seed(7)
+    net, ref = Net(), Net()
+    ref.load_state_dict(net.state_dict())
+    group = dist.group.WORLD
+    sharder = ParamSharder(net, lambda label: (group, rank, world), bf16_shadow=True)
+    opt = ShardedParamAdamW(sharder, lr=1e-2, weight_decay=0.1)
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    assert sharder.resident_bytes() == 0
+    names = dict(net.named_parameters())
+    for step in range(3):
+        opt.zero_grad()
+        for u in sharder.all_units():
+            u.gather()
+            assert u.arena.master.untyped_storage().size() == 0, "the fp32 values stay released"
+            for p in u.params:
+                n = [k for k, v in names.items() if v is p][0]
+                want = dict(ref.named_parameters())[n].detach()
+                # bf16 of this optimizer's fp32 values; the oracle's differ in the last fp32 bits, which may move a
+                # bf16 rounding: one bf16 step of slack
+                assert p.bf16.dtype == torch.bfloat16 and p.bf16.shape == want.shape
+                assert ((p.bf16.float() - want).abs() <= want.abs() * 2 ** -7 + 1e-30).all(), (step, n)
+                assert getattr(p, "terra_master_sharded", False)
+            u.materialise_grad()
+            for i, p in enumerate(u.params):
+                p.grad.fill_(0.01 * (rank + 1) * (i + 1) * (step + 1))
+            u.reduce_grad()
+            u.release()
+        opt.step()
+        for i_all, (n, q) in enumerate(ref.named_parameters()):
+            unit = [u for u in sharder.all_units() if any(x is names[n] for x in u.params)][0]
+            i = [k for k, x in enumerate(unit.params) if x is names[n]][0]
+            q.grad = torch.full_like(q, sum(0.01 * (r + 1) * (i + 1) * (step + 1) for r in range(world)))
+        ref_opt.step()
+    got = sharder.full_state_dict()
+    err = max((got[k] - v).abs().max().item() for k, v in ref.state_dict().items())
+    assert err < 1e-6, err
+    assert sharder.resident_bytes() == 0
+    if rank == 0:
+        print("RESULT " + json.dumps(dict(worst=err)), flush=True)
+
+
 def main():
     mode = json.loads(sys.argv[1])
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
+    if mode.get("working_copy"):
+        working_copy_mode(rank, world)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     torch.manual_seed(7)
     net = Net(recompute=mode.get("recompute", False))
     ref = Net(recompute=False)

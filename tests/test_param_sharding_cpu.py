@@ -54,6 +54,15 @@ def test_sharded_parameters_train_like_adamw_on_the_summed_loss(nproc, mode):
         assert res["peak_bytes"] < 2 * res["total_bytes"] * (0.5 if mode.get("prefetch") else 0.4), res
 
 
+def test_working_copy_bookkeeping_of_the_gpu_form():
+    """With a bf16 working copy (the GPU form, forced on CPU tensors here) that copy is what the units gather, the fp32
+    values stay released outside ``summon_full_params``, the optimizer keeps the owned bf16 slices current, and the
+    gathered model equals ``torch.optim.AdamW``'s."""
+    out = _torchrun(2, os.path.join(ROOT, "tests", "param_sharding_worker.py"), json.dumps({"working_copy": True}), timeout=600)
+    res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert res["worst"] < 1e-6
+
+
 def _pretrain_losses(tmp_path, tag, cfg, nproc, steps=4):
     path = tmp_path / f"{tag}.yaml"
     path.write_text(yaml.safe_dump(cfg, sort_keys=False))
