@@ -45,7 +45,7 @@ def _run(script, cfg, tmp_path, name, nproc=1):
 
 def _losses(log_path):
     """``[(global_step, loss)]`` of a rank-0 log file."""
-    return [(int(g), float(v)) for v, g in re.findall(r"loss ([0-9.eE+-]+) lr \S+ global_step (\d+)", open(log_path).read())]
+    return [(int(g), float(v)) for v, g in re.findall(r"loss ([0-9.eE+-]+) lr: \S+ train_gs (\d+)", open(log_path).read())]
 
 
 def _base(name, tmp_path, run):
@@ -118,7 +118,7 @@ def test_finetune_step_checkpoint_and_resume(tmp_path):
     _run("finetune.py", resumed, tmp_path, "ft2")
     lines = open(log).read().strip().splitlines()
     assert len(lines) == n_before + 1
-    assert "global_step 3" in lines[-1], lines[-1]           # the optimizer's step counter came from the checkpoint
+    assert "train_gs 2 " in lines[-1], lines[-1]            # third step: the optimizer's step counter came from the checkpoint
 
 
 def test_finetune_harness_data_path_switches(tmp_path):

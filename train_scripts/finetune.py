@@ -109,8 +109,15 @@ def main(argv=None):
             if hasattr(frames, "release"):
                 frames.release()
             if log_file is not None:
-                log_file.write(f"{c['description']} lead {lead} epoch {epoch} step {step} loss {last:.8f} lr {lr:.3e} "
-                               f"global_step {s.optimizer.global_step} step_time_s {step_time:.4f}\n")
+                # the reference's line (train_scripts/finetune.py:588-601: train_gs counts the steps before this one),
+                # then this framework's additions
+                parts = [c["description"], "epoch", epoch, "finetune step:", step, "loss", last, "lr:", f"{lr:.8f}",
+                         "train_gs", s.optimizer.global_step - 1]
+                if s.gscaler is not None and hasattr(s.gscaler, "get_scale"):
+                    parts += ["scale", s.gscaler.get_scale()]
+                parts += ["lead", lead, "step_time_s", f"{step_time:.4f}"]
+                print(*parts, flush=True)
+                print(*parts, file=log_file)
             every = int(c.get("save_interval_steps") or 0)
             if every > 0 and s.optimizer.global_step % every == 0:
                 save_checkpoint(s.model, s.optimizer, last, epoch, c["train_path"], c["description"], s.model_type,

@@ -23,12 +23,24 @@ def main(argv=None):
     args = base_parser("terra_b200 pretraining").parse_args(argv)
     s = Session(args.model_cfg, args.data_parallel_group_size, PRETRAIN_DEFAULTS)
     c = s.cfg
+    if s.is_log_rank():
+        use_ddp, use_fsdp, zero_stage, use_dist_opt = s.opt_state
+        print("training description:", c["description"])
+        print("task/model:", s.task_type, c.get("model_architecture"), s.model_type)
+        print("optimizer_config:", c["optimizer_config"], "DDP/FSDP/Zero/DistOpt:", use_ddp, use_fsdp, zero_stage, use_dist_opt)
+        print("parallel:", "wp_topo=", s.other.get("wp_topo"), "xfmr_wp_topo=", s.other.get("xfmr_wp_topo"), "sp=",
+              s.other.get("xfmr_sp_size"), "tp=", s.other.get("tensor_parallel_size"), flush=True)
     loader = s.pretrain_loader(status=0)
     start_epoch = int(c.get("start_epoch", 0))
     if c.get("ckpt_start", False):
-        epoch, gstep, _ = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type, s.opt_state,
-                                          s.manager, epoch=c["ckpt_epoch"], scaler=s.gscaler, model_config=c)
+        epoch, gstep, ckpt_loss = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type,
+                                                  s.opt_state, s.manager, epoch=c["ckpt_epoch"], scaler=s.gscaler,
+                                                  model_config=c)
         start_epoch = epoch + 1
+        if s.is_log_rank():
+            print("resumed epoch:", start_epoch)
+            print("resumed global_step:", gstep)
+            print("resumed loss:", ckpt_loss, flush=True)
     log_file = None
     if s.is_log_rank():
         d = os.path.join(c["train_path"], c["description"], "loss")
@@ -52,12 +64,19 @@ def main(argv=None):
             last_loss = float(loss.item())
             s.guard.after_step(s.optimizer.global_step)      # raises on a lost peer or a timed-out device wait
             if log_file is not None:
-                log_file.write(f"{c['description']} epoch {epoch} step {step} loss {last_loss:.8f} lr {lr:.3e} "
-                               f"global_step {s.optimizer.global_step} step_time_s {step_time:.4f} "
-                               f"forward_time_s {fwd_time:.4f}\n")
+                # the reference's line (train_scripts/train.py:552-571), on stdout and appended to loss/rank0.txt
+                parts = [c["description"], "epoch", epoch, "train step:", step, "loss", last_loss, "lr:", f"{lr:.8f}",
+                         "train_gs", s.optimizer.global_step, "step_time_s", f"{step_time:.4f}", "forward_time_s",
+                         f"{fwd_time:.4f}"]
+                if s.gscaler is not None and hasattr(s.gscaler, "get_scale"):
+                    parts += ["scale", s.gscaler.get_scale()]
+                print(*parts, flush=True)
+                print(*parts, file=log_file)
         if (epoch + 1) % int(c["save_interval_epochs"]) == 0:
-            save_checkpoint(s.model, s.optimizer, last_loss, epoch, c["train_path"], c["description"], s.model_type,
-                            s.opt_state, s.manager, s.gscaler, model_config=c)
+            path = save_checkpoint(s.model, s.optimizer, last_loss, epoch, c["train_path"], c["description"], s.model_type,
+                                   s.opt_state, s.manager, s.gscaler, model_config=c)
+            if path is not None and s.is_log_rank():
+                print(f"saved checkpoint: {path}", flush=True)
     if log_file is not None:
         log_file.close()
     s.close()
