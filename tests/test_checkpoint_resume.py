@@ -114,11 +114,12 @@ def test_finetune_step_checkpoint_and_resume(tmp_path):
     assert blob["global_step"] == 2 and blob["ckpt_layout"] == "single"
     log = os.path.join(base, "loss", "rank0.txt")
     n_before = len(open(log).read().strip().splitlines())
-    resumed = dict(cfg, ckpt_start=True, ckpt_step=2, ckpt_epoch=None, max_train_steps_per_epoch=1)
+    # a step checkpoint resumes inside its epoch: with 3 steps per epoch, step 2 is the one still to do
+    resumed = dict(cfg, ckpt_start=True, ckpt_step=2, ckpt_epoch=None, max_train_steps_per_epoch=3)
     _run("finetune.py", resumed, tmp_path, "ft2")
     lines = open(log).read().strip().splitlines()
     assert len(lines) == n_before + 1
-    assert "train_gs 2 " in lines[-1], lines[-1]            # third step: the optimizer's step counter came from the checkpoint
+    assert "train_gs 2 " in lines[-1] and "finetune step: 2 " in lines[-1], lines[-1]     # counters from the checkpoint
 
 
 def test_finetune_harness_data_path_switches(tmp_path):

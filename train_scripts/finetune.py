@@ -76,13 +76,28 @@ def main(argv=None):
     if path is not None and os.path.exists(path):
         load_pretrained_weights(s.model, path, tuple(c.get("skip_pretrained_state_suffixes", ["attn_mask"])),
                                 log=print if s.is_log_rank() else None)
-    start_epoch = int(c.get("start_epoch", 0))
-    if c.get("ckpt_start", False):
-        epoch, gstep, _ = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type, s.opt_state,
-                                          s.manager, epoch=c.get("ckpt_epoch"), step=c.get("ckpt_step"), scaler=s.gscaler,
-                                          lead=lead, model_config=c)
-        start_epoch = epoch + (0 if c.get("ckpt_step") is not None else 1)
     loader = s.finetune_loader(lead, status=0)
+    start_epoch, skip_steps = int(c.get("start_epoch", 0)), 0
+    if c.get("ckpt_start", False):
+        epoch, gstep, ckpt_loss = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type,
+                                                  s.opt_state, s.manager, epoch=c.get("ckpt_epoch"), step=c.get("ckpt_step"),
+                                                  scaler=s.gscaler, lead=lead, model_config=c)
+        if c.get("ckpt_step") is not None:
+            # a step checkpoint resumes inside its epoch: the steps already taken are skipped, so the sampler's order
+            # for that epoch continues where it stopped (reference: train_scripts/finetune.py:259-265, 541-543)
+            per_epoch = len(loader)
+            if c.get("max_train_steps_per_epoch") is not None:
+                per_epoch = min(per_epoch, int(c["max_train_steps_per_epoch"]))
+            if per_epoch <= 0:
+                raise RuntimeError(f"invalid steps_per_epoch for finetune step resume: {per_epoch}")
+            start_epoch, skip_steps = gstep // per_epoch, gstep % per_epoch
+        else:
+            start_epoch = epoch + 1
+        if s.is_log_rank():
+            print("resume start_epoch:", start_epoch)
+            print("resume skip_steps_in_epoch:", skip_steps)
+            print("resume global_step:", gstep)
+            print("ckpt loss:", ckpt_loss, flush=True)
     log_file = None
     if s.is_log_rank():
         d = os.path.join(c["train_path"], c["description"], f"lead_{lead}", "loss")
@@ -93,6 +108,8 @@ def main(argv=None):
         if hasattr(loader.sampler, "set_epoch"):
             loader.sampler.set_epoch(epoch)
         for step, seq in enumerate(loader):
+            if epoch == start_epoch and step < skip_steps:
+                continue
             limit = c.get("max_train_steps_per_epoch")
             if limit is not None and step >= int(limit):
                 break
