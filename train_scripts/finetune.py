@@ -77,6 +77,12 @@ def main(argv=None):
         load_pretrained_weights(s.model, path, tuple(c.get("skip_pretrained_state_suffixes", ["attn_mask"])),
                                 log=print if s.is_log_rank() else None)
     loader = s.finetune_loader(lead, status=0)
+    if s.is_log_rank():
+        print("[TERRA finetune config]", "description=", c["description"], "task_type=", s.task_type, "model_type=",
+              s.model_type, "optimizer_config=", c["optimizer_config"], "precision=", s.precision, "norm_type=",
+              c.get("norm_type"), "data_precision=", c.get("data_precision"), "use_splited_data=", c["use_splited_data"],
+              "lead_time=", lead, "wp_topo=", c.get("wp_topo"), "xfmr_wp_topo=", c.get("xfmr_wp_topo"), "xfmr_sp_size=",
+              c.get("xfmr_sp_size", 1), "tensor_parallel_size=", c.get("tensor_parallel_size", 1), flush=True)
     start_epoch, skip_steps = int(c.get("start_epoch", 0)), 0
     if c.get("ckpt_start", False):
         epoch, gstep, ckpt_loss = load_checkpoint(s.model, s.optimizer, c["train_path"], c["description"], s.model_type,
