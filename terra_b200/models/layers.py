@@ -26,6 +26,7 @@ from ..memory.activation import activation_checkpoint
 from ..memory.selective_recompute import SelectiveRecomputeScheduler
 from ..ops import blocks as B
 from ..ops.attention import relative_position_index
+from ..ops.packed import fp32_param
 from ..profiler.memory_timeline import mark_memory_timeline
 from .init_utils import (linear_from_tensors, make_linear_with_seed, run_with_seed, sharded_linear_tensors)
 
@@ -96,7 +97,8 @@ class WindowAttention(nn.Module):
             self.proj = make_linear_with_seed(embedding_dim, embedding_dim, True, seed(4))
 
     def bias_table(self) -> Optional[torch.Tensor]:
-        return self.relative_position_bias_table if self.use_relative_position_bias else None
+        """The table for differentiable code that reads it in fp32 (see ``ops/packed.py::fp32_param``)."""
+        return fp32_param(self.relative_position_bias_table) if self.use_relative_position_bias else None
 
 
 class SwinAttentionHalf(nn.Module):

@@ -219,9 +219,7 @@ def attention_half(x, mod, geo: WindowGeometry, shifted: bool, comm=None):
         a = mod.attn
         xn = LayerNormFn.apply(x.contiguous(), mod.norm1.weight, mod.norm1.bias)
         qkv = torch.cat([linear(xn, a.q_linear), linear(xn, a.k_linear), linear(xn, a.v_linear)], dim=-1)
-        o = window_attention(qkv, geo, a.num_heads, shifted,
-                             a.relative_position_bias_table if a.use_relative_position_bias else None,
-                             mod.use_attn_mask, a.scale, comm)
+        o = window_attention(qkv, geo, a.num_heads, shifted, a.bias_table(), mod.use_attn_mask, a.scale, comm)
         return linear(o.to(x.dtype).contiguous(), a.proj, residual=x)
     if x.is_cuda:
         fused = getattr(mod.attn, "fused", None)
@@ -241,8 +239,7 @@ def attention_half(x, mod, geo: WindowGeometry, shifted: bool, comm=None):
     a = mod.attn
     xn = TF.layer_norm(x, (x.shape[-1],), mod.norm1.weight, mod.norm1.bias, LN_EPS)
     qkv = torch.cat([a.q_linear(xn), a.k_linear(xn), a.v_linear(xn)], dim=-1)
-    o = window_attention(qkv, geo, a.num_heads, shifted, a.relative_position_bias_table if a.use_relative_position_bias else None,
-                         mod.use_attn_mask, a.scale, comm)
+    o = window_attention(qkv, geo, a.num_heads, shifted, a.bias_table(), mod.use_attn_mask, a.scale, comm)
     return x + a.proj(o)
 
 

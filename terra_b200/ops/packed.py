@@ -6,6 +6,8 @@ optimizer step instead of once per call.
 """
 from __future__ import annotations
 
+import torch
+
 # Packed operands are functions of the bf16 working copy of a weight, which changes once per optimizer step. They are
 # cached per parameter and rebuilt when the parameter's version counter (bumped by the in-place optimizer update of the
 # master, or by a checkpoint load) or the working copy's address (arena rebinding) has moved.
@@ -33,6 +35,27 @@ def fp32_values(p):
     if getattr(p, "bf16", None) is None or not getattr(p, "terra_master_sharded", False):
         return p.data
     return _packed(p, p.bf16, "f32", lambda t: t.float())
+
+
+class _WidenedValues(torch.autograd.Function):
+    """fp32 values of a parameter taken from its bf16 working copy; the gradient goes to the parameter unchanged."""
+
+    @staticmethod
+    def forward(ctx, p):
+        return fp32_values(p).clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
+def fp32_param(p):
+    """``p`` for differentiable PyTorch code that reads it in fp32 (the composed attention paths index the bias table):
+    the parameter itself, unless its fp32 master is owner-only (or released, with sharded parameters) - then the widened
+    working copy, with the gradient passed on to the parameter."""
+    if getattr(p, "bf16", None) is None or not getattr(p, "terra_master_sharded", False):
+        return p
+    return _WidenedValues.apply(p)
 
 
 PACK_EPOCH = [0]      # bumped by the optimizers after every step (the fused kernels write the working copy directly)

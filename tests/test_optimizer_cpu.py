@@ -153,3 +153,27 @@ def test_fp32_reads_take_the_working_copy_when_masters_are_sharded():
     p.bf16.fill_(3.0)
     invalidate_packed_weights()                                              # what every optimizer step does
     assert fp32_values(p).tolist() == [3.0] * 4
+
+
+def test_differentiable_fp32_reads_pass_the_gradient_to_the_parameter():
+    """``fp32_param``: PyTorch code that indexes the bias table gets the widened working copy when the fp32 master is
+    owner-only, and the table's gradient still arrives at the parameter."""
+    import torch
+
+    from terra_b200.ops.packed import fp32_param, invalidate_packed_weights
+
+    p = torch.nn.Parameter(torch.full((5,), 1.0))
+    assert fp32_param(p) is p
+    p.bf16 = torch.arange(5, dtype=torch.float32).bfloat16()
+    p.terra_master_sharded = True
+    invalidate_packed_weights()
+    t = fp32_param(p)
+    assert t is not p and t.dtype == torch.float32 and t.tolist() == [0.0, 1.0, 2.0, 3.0, 4.0] and t.requires_grad
+    (t[torch.tensor([1, 1, 3])] * torch.tensor([1.0, 2.0, 5.0])).sum().backward()
+    assert p.grad.tolist() == [0.0, 3.0, 0.0, 5.0, 0.0]
+    # two uses in one graph are two nodes over fresh tensors
+    a, b = fp32_param(p), fp32_param(p)
+    assert a is not b
+    p.grad = None
+    (a.sum() + 2 * b.sum()).backward()
+    assert p.grad.tolist() == [3.0] * 5
