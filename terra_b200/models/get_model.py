@@ -11,11 +11,12 @@ framework implements natively:
              sharded; a unit's parameters are all-gathered while it runs (``terra_b200.parallel.param_sharding``).
              5 shards the model as one unit; 7 (TP = 1) and 8 / 9 (TP > 1) shard per ``FSDP_WRAPPER_CFG`` transformer
              blocks, TP-sharded parameters over the ranks at the same TP rank, the others over the full replica group
-  1, 2       ZeRO stages 1 and 2: the sharded-optimizer path of 6 (state and updates sharded, gradients
-             reduce-scattered, parameters replicated)
+  2          ZeRO stage 2: the same units with the parameters kept between a unit's forward and backward pass
+             (gathered once per step, gradients and optimizer state sharded)
+  1          ZeRO stage 1: the sharded-optimizer path of 6 (state and updates sharded, parameters replicated)
   0          replicated AdamW
 
-``TERRA_PARAM_SHARDING=0`` runs 3 / 5 / 7 / 8 / 9 on the sharded-optimizer path instead (parameters replicated).
+``TERRA_PARAM_SHARDING=0`` runs 2 / 3 / 5 / 7 / 8 / 9 on the sharded-optimizer path instead (parameters replicated).
 """
 from __future__ import annotations
 
@@ -72,7 +73,7 @@ def optimizer_state_tuple(optimizer_config: int, tensor_parallel_size: int = 1):
     return use_ddp, False, zero_stage, use_dist
 
 
-PARAM_SHARDING_CONFIGS = (3, 5, 7, 8, 9)
+PARAM_SHARDING_CONFIGS = (2, 3, 5, 7, 8, 9)
 
 
 def _sharded_parameters(model, archi, model_config, manager, oc):
@@ -102,7 +103,7 @@ def _sharded_parameters(model, archi, model_config, manager, oc):
         return g, dist.get_rank(g), dist.get_world_size(g)
 
     sharder = ParamSharder(model, resolve, blocks_per_unit=G.FSDP_WRAPPER_CFG, whole_model=(oc == 5),
-                           prefetch=archi.get("FSDP_CONFIG7_PREFETCH_POLICY", "none"),
+                           prefetch=archi.get("FSDP_CONFIG7_PREFETCH_POLICY", "none"), reshard_after_forward=(oc != 2),
                            sampling_units=int(archi.get("FSDP_SAMPLING_WRAPPER_CFG", 0) or 0) > 0)
     if manager is None or manager.get_rank() == 0:
         print(f"[FSDP] optimizer_config={oc} {sharder.describe()}, wrapper_cfg={G.FSDP_WRAPPER_CFG}, "
@@ -155,7 +156,7 @@ def get_model_for_train(model_archi_params, model_config, task_type="glorys", mo
                                  growth_interval=int(model_config.get("loss_scale_growth_interval", 2000)))
         else:
             gscaler = torch.amp.GradScaler("cpu", enabled=False)
-    if oc in (1, 2) or (oc in PARAM_SHARDING_CONFIGS and not shard_params):
+    if oc == 1 or (oc in PARAM_SHARDING_CONFIGS and not shard_params):
         if not getattr(get_model_for_train, "_warned_fallback", False):
             import warnings
 

@@ -136,7 +136,8 @@ def main():
 
     group = dist.group.WORLD
     sharder = ParamSharder(net, lambda label: (group, rank, world), blocks_per_unit=mode.get("blocks_per_unit", 1),
-                           whole_model=mode.get("whole_model", False), prefetch=mode.get("prefetch", "none"))
+                           whole_model=mode.get("whole_model", False), prefetch=mode.get("prefetch", "none"),
+                           reshard_after_forward=mode.get("reshard_after_forward", True))
     opt = ShardedParamAdamW(sharder, lr=1e-2, weight_decay=0.1)
     ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
     assert sharder.resident_bytes() == 0, "nothing but the owned slices exists between steps"

@@ -38,6 +38,7 @@ def _torchrun(nproc, script, *args, timeout=900):
     (2, {"whole_model": True}),
     (3, {"recompute": True, "blocks_per_unit": 2}),
     (3, {"prefetch": "overlap", "rollout": 2}),
+    (2, {"reshard_after_forward": False, "recompute": True}),
 ])
 def test_sharded_parameters_train_like_adamw_on_the_summed_loss(nproc, mode):
     out = _torchrun(nproc, os.path.join(ROOT, "tests", "param_sharding_worker.py"), json.dumps(mode), timeout=600)
@@ -47,7 +48,11 @@ def test_sharded_parameters_train_like_adamw_on_the_summed_loss(nproc, mode):
     # recomputed segment stays resident for its backward pass; a prefetched unit is not gathered again); the root
     # unit is gathered once per step. 5 training steps and one evaluation ran.
     blocks, root = res["gathers"][:-1], res["gathers"][-1]
-    assert root == 6 and all(g == 5 * 2 * passes + passes for g in blocks), res
+    if mode.get("reshard_after_forward", True):
+        assert root == 6 and all(g == 5 * 2 * passes + passes for g in blocks), res
+    else:
+        # kept between forward and backward: one gather per training step (the evaluation pass gathers once more)
+        assert root == 6 and all(g == 6 for g in blocks), res
     assert all(r == 5 * passes for r in res["reductions"][:-1]) and res["reductions"][-1] == 5
     if not mode.get("whole_model") and not mode.get("recompute"):
         # values and gradients of at most two units (the running one and a prefetched neighbour) next to the root's
