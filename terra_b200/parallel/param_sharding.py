@@ -31,7 +31,7 @@ from __future__ import annotations
 
 import contextlib
 import math
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -39,10 +39,6 @@ import torch.distributed as dist
 from ..utils.flat_params import ALIGN, ParamArena
 
 PREFETCH_POLICIES = ("none", "overlap", "conservative")
-
-
-def _live() -> bool:
-    return dist.is_available() and dist.is_initialized()
 
 
 def _free(t: Optional[torch.Tensor]) -> None:

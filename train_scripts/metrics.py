@@ -15,7 +15,6 @@ import json
 import os
 from typing import Dict, List, Optional, Sequence
 
-import torch
 import torch.distributed as dist
 
 from terra_b200.checkpoint_io import FSDP_OPTIMIZER_CONFIGS
@@ -78,15 +77,18 @@ def _gather(value, kind=float) -> List:
 
 def gather_run_facts(session, rows: Sequence[dict], offload_stats: Optional[dict] = None) -> Dict[str, object]:
     """Per-rank parameter counts, last-step peak memory and step time, and the offload counters. Collective."""
-    local = sum(p.numel() for p in session.model.parameters())
-    pre_wrap = int(getattr(session.model, "pre_wrap_parameter_count", local))
+    whole = sum(p.numel() for p in session.model.parameters())
+    sharder = getattr(session.model, "_param_sharder", None)
+    # with sharded parameters a rank holds its owned slices (alignment padding included); otherwise the whole model
+    local = int(sharder.owned_numel()) if sharder is not None else whole
+    pre_wrap = int(getattr(session.model, "pre_wrap_parameter_count", whole))
     by_rank = _gather(local, int)
     pre_by_rank = _gather(pre_wrap, int)
     tp = int(session.other.get("tensor_parallel_size", 1))
-    sharded_state = session.cfg.get("optimizer_config") in FSDP_OPTIMIZER_CONFIGS
-    # Parameters are never sharded here (the sharded optimisers split their state and the update, not the weights), so
-    # outside tensor parallelism every rank's count is the model's.
-    if tp > 1:
+    sharded_state = sharder is not None or session.cfg.get("optimizer_config") in FSDP_OPTIMIZER_CONFIGS
+    if sharder is not None:
+        total, method = max(pre_by_rank), "pre_wrap_full_count_before_fsdp_wrap"
+    elif tp > 1:
         total, method = None, "tp_sharded_local_count_only"
     else:
         total, method = max(pre_by_rank), "pre_wrap_replicated_full_count"
