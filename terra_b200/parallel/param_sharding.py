@@ -23,7 +23,9 @@ The design here follows the flat arenas instead of wrapping modules:
   pass that runs inside the backward pass (activation recompute) leaves its units resident for the gradient computation
   that follows. The root unit stays resident from the start of the forward pass to ``finish_backward``.
 * ``prefetch: overlap`` starts the all-gather of the neighbouring unit (next in forward, previous in backward)
-  asynchronously before the current unit computes; the collective runs on the backend's own stream / thread.
+  asynchronously before the current unit computes, and starts a unit's reduce-scatter when the backward pass leaves
+  it without waiting for it (it is folded in when the next unit is left, or in ``finish_backward``); the collectives
+  run on the backend's own stream / thread.
 
 Not run on a GPU so far: the CPU (gloo) ranks exercise the schedule, the collectives and the optimizer math.
 """
@@ -107,6 +109,7 @@ class ShardedUnit:
         self.grad_live = True         # the full gradient buffer has storage and the parameters' .grad point into it
         self.in_backward = False
         self._pending: list = []
+        self._reducing: list = []     # (handle, range, received slice) of reduce-scatters in flight
         self.gathers = 0              # counters for tests and reports
         self.reductions = 0
         self.release()
@@ -158,6 +161,7 @@ class ShardedUnit:
 
     # ------------------------------------------------------------------ gradients
     def materialise_grad(self) -> None:
+        self.finish_reduce()              # an earlier pass's reduction still reads the buffer
         if self.grad_live:
             return
         g = self.arena.grad
@@ -179,8 +183,14 @@ class ShardedUnit:
     def has_stray_gradients(self) -> bool:
         return (not self.grad_live) and any(p.grad is not None for p in self.arena.params)
 
-    def reduce_grad(self) -> None:
-        """Sum the unit's gradients over each label's replica group, keep the owned slice, drop the rest."""
+    def reduce_grad(self, async_op: bool = False) -> None:
+        """Sum the unit's gradients over each label's replica group, keep the owned slice, drop the rest. With
+        ``async_op`` the reduce-scatters are only started (they run on the backend's stream / thread while the backward
+        pass goes on); ``finish_reduce`` folds the results in and frees the gradient buffer."""
+        if self._reducing:
+            if not async_op:
+                self.finish_reduce()
+            return
         if not self.grad_live:
             return
         g = self.arena.grad
@@ -188,11 +198,22 @@ class ShardedUnit:
             for r in self.ranges:
                 if r.size > 1:
                     part = torch.empty_like(r.own_grad)
-                    dist.reduce_scatter_tensor(part, g[r.start:r.end], group=r.group)
-                    r.own_grad.add_(part)
+                    h = dist.reduce_scatter_tensor(part, g[r.start:r.end], group=r.group, async_op=True)
+                    self._reducing.append((h, r, part))
                 else:
                     r.own_grad.add_(g[r.lo:r.hi])
         self.reductions += 1
+        if not async_op or not self._reducing:
+            self.finish_reduce(force=True)
+
+    def finish_reduce(self, force: bool = False) -> None:
+        if not self._reducing and not force:
+            return
+        with torch.no_grad():
+            for h, r, part in self._reducing:
+                h.wait()
+                r.own_grad.add_(part)
+        self._reducing = []
         self.release_grad()
 
     # ------------------------------------------------------------------ fp32 values (state_dict, load)
@@ -265,6 +286,7 @@ class ParamSharder:
         self.param_order = [p for p in model.parameters()]
         taken = set()
         self.units: List[ShardedUnit] = []
+        self._reducing_unit: Optional[ShardedUnit] = None
         self._hooks = []
         groups = [] if whole_model else transformer_block_groups(model, blocks_per_unit)
         self.named_units: Dict[int, ShardedUnit] = {}          # id(module) -> unit, for run_in_unit
@@ -378,7 +400,11 @@ class ParamSharder:
         return None
 
     def _leave_backward(self, unit: ShardedUnit):
-        unit.reduce_grad()
+        overlap = self.prefetch == "overlap"
+        if self._reducing_unit is not None and self._reducing_unit is not unit:
+            self._reducing_unit.finish_reduce()       # at most one unit's reduction in flight besides the new one
+        unit.reduce_grad(async_op=overlap)
+        self._reducing_unit = unit if overlap else None
         unit.release()
         unit.in_backward = False
 
@@ -393,6 +419,9 @@ class ParamSharder:
                 u.reduce_grad()
             if u.resident:
                 u.release()
+        for u in self.units:
+            u.finish_reduce()
+        self._reducing_unit = None
         if self.root is not None:
             if self.root.has_stray_gradients():
                 self.root.materialise_grad()
