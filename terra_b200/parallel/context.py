@@ -186,8 +186,8 @@ class ParallelContext:
             return self.fused_comm
         if self.n_wg == 1 and self.sp > 1 and os.environ.get("TERRA_SP_BASELINE", "ulysses") == "ulysses":
             return _UlyssesAttnComm(self, batch)
-        if self.sp == 1 and self.n_wg > 1 and os.environ.get("TERRA_WP_BASELINE", "exchange") == "exchange":
-            return self._cached_comm(_ShiftExchangeAttnComm, batch)
+        if self.n_wg > 1 and os.environ.get("TERRA_WP_BASELINE", "exchange") == "exchange":
+            return self._cached_comm(_ShiftExchangeAttnComm if self.sp == 1 else _ShardedShiftExchangeAttnComm, batch)
         return _PortableAttnComm(self, batch)
 
     def _cached_comm(self, cls, batch):
@@ -570,6 +570,123 @@ class _ShiftExchangeAttnComm(_PortableAttnComm):
 def n_mine_rows(comm, rank) -> int:
     """Rows of q/k/v a rank holds: batch x its windows x the window's tokens."""
     return comm.batch * len(comm.p.windows_of[rank]) * comm.p.N
+
+
+class _ShardedShiftExchangeAttnComm(_PortableAttnComm):
+    """The routed exchange with token shards (SP > 1, any number of window groups, any owner map): rank ``(g, s)`` computes
+    the query slots ``[s * shardN, (s + 1) * shardN)`` of the (shifted) windows its group owns. One all-to-all-v brings
+    the q rows of those slots, another the k / v rows of all slots of those windows, each from the rank that holds the
+    token - ``(owner of its window, its shard)`` -, and a third returns the outputs along the reversed q routes. For
+    unshifted blocks the q rows are local and the k / v exchange stays inside the group."""
+
+    def __init__(self, pctx: "ParallelContext", batch: int):
+        super().__init__(pctx, batch)
+        self._tables = {}
+
+    def _rows_held(self, rank_index):
+        p = self.p
+        return self.batch * len(p.windows_of[rank_index // p.sp]) * p.shardN
+
+    def _needs(self, rank_index, shifted, queries_only):
+        """(source rank, source row) of every (batch, owned window, slot) the rank needs, in that order; slots are its
+        query slots or all of them."""
+        p, Bn, N, sN = self.p, self.batch, self.p.N, self.p.shardN
+        g, s = divmod(rank_index, p.sp)
+        src_win, src_tok, _ = self._sources[shifted]
+        wins = np.asarray(p.windows_of[g])
+        slots = np.arange(s * sN, (s + 1) * sN) if queries_only else np.arange(N)
+        sw, st = src_win[wins][:, slots], src_tok[wins][:, slots]                          # [nW_g, slots]
+        rank = self._owner[sw] * p.sp + st // sN
+        held = self._counts[self._owner[sw]]                                               # windows held by the source rank
+        row = (np.arange(Bn)[:, None, None] * held[None] + self._local_idx[sw][None]) * sN + (st % sN)[None]
+        return np.broadcast_to(rank[None], row.shape).reshape(-1), row.reshape(-1)
+
+    def _route(self, shifted, queries_only, device):
+        p = self.p
+        world = p.n_wg * p.sp
+        me = p.wg_rank * p.sp + p.sp_rank
+        rank, row = self._needs(me, shifted, queries_only)
+        held = self._rows_held(me)
+        recv_sizes = [int(((rank == r) & (r != me)).sum()) for r in range(world)]
+        start = np.concatenate([[0], np.cumsum(recv_sizes)])
+        assemble = np.empty(rank.shape[0], dtype=np.int64)
+        assemble[rank == me] = row[rank == me]
+        for r in range(world):
+            if r != me and recv_sizes[r]:
+                assemble[rank == r] = held + start[r] + np.arange(recv_sizes[r])
+        send_index, send_sizes = [], []
+        for d in range(world):
+            if d == me:
+                send_sizes.append(0)
+                continue
+            d_rank, d_row = self._needs(d, shifted, queries_only)
+            pick = d_rank == me
+            send_index.append(d_row[pick])
+            send_sizes.append(int(pick.sum()))
+        send_index = np.concatenate(send_index) if send_index else np.zeros(0, dtype=np.int64)
+        out = dict(send_sizes=send_sizes, recv_sizes=recv_sizes)
+        to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+        out.update(send_index=to(send_index), assemble=to(assemble))
+        if queries_only:
+            # the way back: what I received returns in the order it came; my home rows are rows I computed or rows of
+            # the returned chunk, which arrives in my send order
+            back = np.concatenate([np.nonzero(rank == r)[0] for r in range(world) if r != me] or [np.zeros(0, dtype=np.int64)])
+            home = np.full(held, -1, dtype=np.int64)
+            home[row[rank == me]] = np.nonzero(rank == me)[0]
+            home[send_index] = rank.shape[0] + np.arange(send_index.shape[0])
+            if (home < 0).any():
+                raise RuntimeError("shift exchange: a home row has no producer (owner map and routes disagree)")
+            out.update(return_index=to(back), home=to(home))
+        return out
+
+    def _tables_for(self, shifted, device):
+        key = (bool(shifted), str(device))
+        if key not in self._tables:
+            p = self.p
+            if not hasattr(self, "_sources"):
+                gfull = WindowGeometry(self.batch, p.nWh, p.nWw, p.wh, p.ww)
+                self._sources = {flag: tuple(t.numpy() for t in shifted_window_sources(gfull, flag)) for flag in (False, True)}
+                self._owner = np.asarray(p.owner)
+                self._counts = np.asarray([len(w) for w in p.windows_of])
+                self._local_idx = np.zeros(self._owner.shape[0], dtype=np.int64)
+                for g in range(p.n_wg):
+                    self._local_idx[p.windows_of[g]] = np.arange(len(p.windows_of[g]))
+            reg = self._sources[shifted][2][np.asarray(p.windows_of[p.wg_rank])]               # [nWl, N]
+            self._tables[key] = dict(q=self._route(shifted, True, device), kv=self._route(shifted, False, device),
+                                     reg=torch.from_numpy(np.ascontiguousarray(reg)).to(device),
+                                     masked=bool((reg != reg[:, :1]).any()))
+        return self._tables[key]
+
+    def window_attention_portable(self, qkv, geo, num_heads, shifted, bias_table, use_mask, scale):
+        from ..ops.attention import attention_core_reference, relative_position_index
+
+        p, Bn, N, sN = self.p, self.batch, self.p.N, self.p.shardN
+        Cd = qkv.shape[-1] // 3
+        hd = Cd // num_heads
+        nWl = len(p.windows_of[p.wg_rank])
+        t = self._tables_for(shifted, qkv.device)
+        group = p.manager.xfmr_tp_param_group
+
+        def pull(cols, route):
+            got = C.all_to_all_rows(cols.index_select(0, route["send_index"]), group, route["send_sizes"], route["recv_sizes"])
+            return torch.cat([cols, got], 0).index_select(0, route["assemble"])
+
+        q = pull(qkv[:, :Cd].contiguous(), t["q"]).reshape(Bn * nWl, sN, num_heads, hd).permute(0, 2, 1, 3)
+        kv = pull(qkv[:, Cd:].contiguous(), t["kv"]).reshape(Bn * nWl, N, 2, num_heads, hd)
+        k, v = kv[:, :, 0].permute(0, 2, 1, 3), kv[:, :, 1].permute(0, 2, 1, 3)
+        mine = slice(p.sp_rank * sN, (p.sp_rank + 1) * sN)
+        bias = None
+        if bias_table is not None:
+            idx = relative_position_index(p.wh, p.ww).to(bias_table.device)
+            bias = bias_table[idx.reshape(-1)].reshape(N, N, num_heads).permute(2, 0, 1)[:, mine].to(q.dtype)
+        mask = None
+        if use_mask and shifted and t["masked"]:
+            reg = t["reg"]
+            mask = ((reg[:, mine, None] != reg[:, None, :]).to(q.dtype) * -100.0).repeat(Bn, 1, 1)
+        o = attention_core_reference(q, k, v, scale, bias, mask).permute(0, 2, 1, 3).reshape(Bn * nWl * sN, Cd)
+        route = t["q"]
+        back = C.all_to_all_rows(o.index_select(0, route["return_index"]), group, route["recv_sizes"], route["send_sizes"])
+        return torch.cat([o, back], 0).index_select(0, route["home"])
 
 
 class _UlyssesAttnComm(_PortableAttnComm):

@@ -133,15 +133,19 @@ def test_parallel_layout_matches_serial(world, extra):
     (4, "wp_topo='(4, 1)', xfmr_wp_topo='(2, 2)', window_assignment_mode='regular'", "exchange"),          # 2-D blocks
     (3, "wp_topo='(3, 1)', xfmr_wp_topo='(3, 1)', window_assignment_mode='ragged_round_robin'", "exchange"),
     (2, "wp_topo='(2, 1)', xfmr_wp_topo='(1, 2)', window_assignment_mode='regular'", "gather"),            # the old baseline
+    # with token shards: q rows of the own query slots and k / v rows of whole windows travel along their own routes
+    (4, "wp_topo='(4, 1)', xfmr_wp_topo='(2, 1)', xfmr_sp_size=2, window_assignment_mode='terra_m1_ragged_auto'", "exchange-sp"),
+    (4, "wp_topo='(4, 1)', xfmr_wp_topo='(1, 2)', xfmr_sp_size=2, window_assignment_mode='regular'", "exchange-sp"),
 ])
 def test_non_contiguous_window_ownership_matches_serial(world, extra, baseline):
     """Ownership maps in which a rank's windows are not one range of the row-major order (column blocks, 2-D blocks,
     round robin): the shifted windows are put together from routed pieces (reference: core/window_parallel.py:26-266);
     ``TERRA_WP_BASELINE=gather`` keeps the gather-everything form."""
-    for res in _run(world, extra, TERRA_WP_BASELINE=baseline):
+    want = {"exchange": ["_ShiftExchangeAttnComm"], "exchange-sp": ["_ShardedShiftExchangeAttnComm"], "gather": []}[baseline]
+    for res in _run(world, extra, TERRA_WP_BASELINE=baseline.split("-")[0]):
         assert abs(res["loss"] - res["ref_loss"]) < 1e-4 * max(1.0, abs(res["ref_loss"])), res
         assert res["out_err"] < 2e-3 and res["checked"] > 10 and res["worst_grad_rel"] < 2e-3, res
-        assert res["comms"] == (["_ShiftExchangeAttnComm"] if baseline == "exchange" else []), res
+        assert res["comms"] == want, res
 
 
 def test_ragged_ownership_with_rectangular_windows_matches_serial():
