@@ -80,7 +80,9 @@ def main(argv=None):
     if args.steps is not None and args.steps <= 0:
         raise ValueError(f"--steps must be positive, got {args.steps}")
     steps = args.steps or 2
-    s = Session(args.model_cfg, args.data_parallel_group_size, dict(FINETUNE_DEFAULTS, use_fake_input=True))
+    # synthetic fields unless the config says otherwise; TERRA_USE_FAKE_INPUT (the reference's switch) sets the default
+    fake_default = G.USE_FAKE_INPUT if os.environ.get("TERRA_USE_FAKE_INPUT") else True
+    s = Session(args.model_cfg, args.data_parallel_group_size, dict(FINETUNE_DEFAULTS, use_fake_input=fake_default))
     c = s.cfg
     lead = int(c["finetune_lead_time"])
     # data-path switches of the reference harness (train_scripts/test_finetune.py:107-160)

@@ -40,7 +40,9 @@ def main(argv=None):
         raise ValueError(f"--steps must be positive, got {args.steps}")
     steps = args.steps or 4
 
-    s = Session(args.model_cfg, args.data_parallel_group_size, dict(PRETRAIN_DEFAULTS, use_fake_input=True))
+    # synthetic fields unless the config says otherwise; TERRA_USE_FAKE_INPUT (the reference's switch) sets the default
+    fake_default = G.USE_FAKE_INPUT if os.environ.get("TERRA_USE_FAKE_INPUT") else True
+    s = Session(args.model_cfg, args.data_parallel_group_size, dict(PRETRAIN_DEFAULTS, use_fake_input=fake_default))
     c = s.cfg
     log_ranks = debug_log_wp_ranks(s.manager, s.model_type, s.other)
     set_dp_rank_print_redirect(s.manager, s.model_type, s.opt_state, s.other.get("embedding_parallel_type"),
