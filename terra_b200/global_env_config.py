@@ -10,7 +10,7 @@ ON_H200 = _flag("TERRA_ON_H200")                 # sequential model takes NCHW i
 ENABLE_TORCH_PROF = _flag("ENABLE_TORCH_PROF")
 DISABLE_TORCH_PROF = _flag("DISABLE_TORCH_PROF")
 TORCH_PROF_WRITE_TRACE = _flag("TORCH_PROF_WRITE_TRACE")
-TORCH_PROF_STEP_LIST = [int(v) for v in os.environ.get("TORCH_PROF_STEP_LIST", "1,1,2,1").split(",")]
+TORCH_PROF_STEP_LIST = [int(v) for v in os.environ.get("TORCH_PROF_STEP_LIST", "1,1,3,1").split(",")]
 DEBUG_GRAD_HOOK = _flag("DEBUG_GRAD_HOOK")
 DEBUG_GRAD_HOOK_PRINT_LIMIT = int(os.environ.get("DEBUG_GRAD_HOOK_PRINT_LIMIT", "20"))
 FSDP_WRAPPER_CFG = int(os.environ.get("FSDP_WRAPPER_CFG", "1"))

@@ -42,7 +42,7 @@ class FlopsSummary:
 
 
 class TorchFlopsProfiler:
-    def __init__(self, step_list=(1, 1, 2, 1), enabled=True, trace_dir=None, rank=0):
+    def __init__(self, step_list=(1, 1, 3, 1), enabled=True, trace_dir=None, rank=0):
         self.wait, self.warmup, self.active, self.repeat = (int(v) for v in step_list)
         self.enabled = enabled
         self.rank = rank
