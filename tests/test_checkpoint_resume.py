@@ -102,24 +102,30 @@ def test_pretrain_resume_matches_uninterrupted_run(tmp_path, name, nproc, opt, l
         assert abs(a - b) <= 2e-4 * abs(b), (resumed, straight)
 
 
-def test_finetune_step_checkpoint_and_resume(tmp_path):
+@pytest.mark.parametrize("opt,kind,sub", [(4, "single", ""), (7, "fsdp_sharded", os.path.join("fsdp_sharded", "rank_0"))])
+def test_finetune_step_checkpoint_and_resume(tmp_path, opt, kind, sub):
+    """The rollout loop saves every ``save_interval_steps`` steps; resuming from such a file continues inside the epoch:
+    the steps already taken are skipped and the next one reproduces the uninterrupted run's loss (replicated parameters,
+    and sharded parameters with per-rank files)."""
     cfg = yaml.safe_load(open(os.path.join(ROOT, "configs", "finetuning", "tiny_finetune_seq.yaml")))
-    cfg.update(train_path=str(tmp_path / "ft"), max_train_steps_per_epoch=2, save_interval_steps=2, precision="fp32",
-               finetune_lead_time=2, num_finetune_epochs=1, fake_length=4)
+    cfg.update(train_path=str(tmp_path / "ft"), max_train_steps_per_epoch=3, save_interval_steps=2, precision="fp32",
+               finetune_lead_time=2, num_finetune_epochs=1, fake_length=4, optimizer_config=opt,
+               fsdp_checkpoint_type="sharded")
     cfg.pop("activation", None)
     _run("finetune.py", cfg, tmp_path, "ft1")
     base = os.path.join(cfg["train_path"], cfg["description"], "lead_2")
-    assert os.path.exists(os.path.join(base, "ckpt", "step2.pth")) and os.path.exists(os.path.join(base, "ckpt", "epoch0.pth"))
-    blob = torch.load(os.path.join(base, "ckpt", "step2.pth"), map_location="cpu", weights_only=False)
-    assert blob["global_step"] == 2 and blob["ckpt_layout"] == "single"
+    assert os.path.exists(os.path.join(base, "ckpt", sub, "step2.pth")) and os.path.exists(os.path.join(base, "ckpt", sub, "epoch0.pth"))
+    blob = torch.load(os.path.join(base, "ckpt", sub, "step2.pth"), map_location="cpu", weights_only=False)
+    assert blob["global_step"] == 2 and blob["ckpt_layout"] == kind
     log = os.path.join(base, "loss", "rank0.txt")
-    n_before = len(open(log).read().strip().splitlines())
-    # a step checkpoint resumes inside its epoch: with 3 steps per epoch, step 2 is the one still to do
-    resumed = dict(cfg, ckpt_start=True, ckpt_step=2, ckpt_epoch=None, max_train_steps_per_epoch=3)
-    _run("finetune.py", resumed, tmp_path, "ft2")
+    before = open(log).read().strip().splitlines()
+    assert len(before) == 3 and "finetune step: 2 " in before[-1]
+    _run("finetune.py", dict(cfg, ckpt_start=True, ckpt_step=2, ckpt_epoch=None), tmp_path, "ft2")
     lines = open(log).read().strip().splitlines()
-    assert len(lines) == n_before + 1
+    assert len(lines) == len(before) + 1, "steps 0 and 1 of the epoch are skipped, step 2 runs"
     assert "train_gs 2 " in lines[-1] and "finetune step: 2 " in lines[-1], lines[-1]     # counters from the checkpoint
+    loss = lambda line: float(re.search(r"loss ([0-9.eE+-]+) lr:", line).group(1))
+    assert abs(loss(lines[-1]) - loss(before[-1])) <= 1e-6 * abs(loss(before[-1])), (lines[-1], before[-1])
 
 
 def test_finetune_harness_data_path_switches(tmp_path):
