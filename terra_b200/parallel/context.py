@@ -10,6 +10,11 @@ Layouts (reference semantics: core/parallel/layout_transform.py, core/rank_manag
   ``[s*shardN, (s+1)*shardN)`` of each window, TP rank ``t`` the chunk ``[t*wpt, (t+1)*wpt)`` of the group's
   windows between blocks (activations) and the heads / hidden channels ``t`` inside blocks (parameters).
 
+Attention across ranks: the peer-memory kernels when the owner map is contiguous (``fused_comm``); otherwise, and on
+the collective back ends, a routed exchange of the pieces of the owned (shifted) windows (``_ShiftExchangeAttnComm``,
+with token shards ``_ShardedShiftExchangeAttnComm``), the Ulysses all-to-all for token shards of one window group, or
+the gather-everything oracle (``_PortableAttnComm``).
+
 With one rank every method degenerates to local index permutations.
 """
 from __future__ import annotations
