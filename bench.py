@@ -343,7 +343,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="only the device-timed loop (used when profiling)")
     ap.add_argument("--only-layout", default=None, help=argparse.SUPPRESS)     # child mode, see run_ours
     ap.add_argument("--result-file", default=None, help=argparse.SUPPRESS)
-    ap.add_argument("--extra-deadline", type=float, default=300.0,
+    ap.add_argument("--extra-deadline", type=float, default=200.0,
                     help="seconds after which the extra layout is given up and the headline printed without it")
     ap.add_argument("--extra-layout", default=None,
                     help='also time the factorised layout "wg,sp,tp" of the same model (default: 2,2,2 on 8 GPUs; "none")')
