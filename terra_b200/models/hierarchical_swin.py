@@ -60,6 +60,7 @@ class _SwinBase(nn.Module):
             downsample=2 if self.has_sampling else 1)
         hp, wp = self.padded_shape[0] // patch_size, self.padded_shape[1] // patch_size
         self.patches_resolution = [hp, wp]
+        self._param_sharder = None          # set by terra_b200.parallel.param_sharding when parameters are sharded
         ds = 2 if self.has_sampling else 1
         self.div_val = patch_size * ds
         self.token_hw = (hp // ds, wp // ds)
