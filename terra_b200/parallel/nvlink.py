@@ -48,6 +48,26 @@ class _RawBytes:
         self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
 
 
+_GROUP_OF_NAME = {}      # group name -> the process-group object that was registered for symmetric memory under it
+
+
+def _register_group(symm_mem, group) -> None:
+    """Register ``group`` with torch's symmetric-memory layer. That layer keeps a process-wide table keyed by the group's
+    NAME and never re-registers a name it knows; names are handed out from a counter that ``destroy_process_group``
+    resets. So after a process has torn its groups down and built another topology, a new group inherits the name - and
+    with it the rank, size and store - of a group of the old topology, and the rendezvous waits on a dead store for the
+    wrong number of peers. A name that is known for a different group object is therefore dropped before registering."""
+    name = group.group_name
+    table = getattr(symm_mem, "_group_name_to_store", None)
+    if _GROUP_OF_NAME.get(name) is not group and isinstance(table, dict):
+        table.pop(name, None)
+    _GROUP_OF_NAME[name] = group
+    try:
+        symm_mem.enable_symm_mem_for_group(name)
+    except Exception:
+        pass
+
+
 class SymmetricArena:
     """Bump allocator over one symmetric allocation shared (by layout) with the ranks of ``group``."""
 
@@ -57,10 +77,7 @@ class SymmetricArena:
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.nbytes = int(nbytes + PAD_BYTES + 255) // 256 * 256
-        try:
-            symm_mem.enable_symm_mem_for_group(group.group_name)
-        except Exception:
-            pass
+        _register_group(symm_mem, group)
         self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, group=group)

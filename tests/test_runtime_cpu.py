@@ -208,3 +208,32 @@ def test_harness_metric_files_use_the_reference_columns(tmp_path):
     meta = json.load(open(tmp_path / "a" / "m.json"))
     assert meta["script"] == "test_finetune.py" and meta["lead_time"] == 2 and meta["input_double_buffer"] is True
     assert meta["parameter_count_by_rank"] == [8] and meta["test_iter_num"] == 1
+
+
+def test_symmetric_memory_group_names_are_not_inherited_across_topologies():
+    """torch's symmetric-memory layer registers a group under its NAME once and for all, and ``destroy_process_group``
+    restarts the name counter: a group of a second topology in the same process would inherit the store, rank and size of
+    a dead group of the first (its rendezvous then waits for ever). ``_register_group`` drops a name that is known for
+    another group object before registering; the same object is registered once."""
+    import types
+
+    from terra_b200.parallel import nvlink
+
+    calls = []
+    fake = types.SimpleNamespace(_group_name_to_store={}, enable_symm_mem_for_group=None)
+
+    def enable(name):
+        calls.append(name)
+        fake._group_name_to_store.setdefault(name, object())
+
+    fake.enable_symm_mem_for_group = enable
+    nvlink._GROUP_OF_NAME.clear()
+    first = types.SimpleNamespace(group_name="1")
+    nvlink._register_group(fake, first)
+    store_a = fake._group_name_to_store["1"]
+    nvlink._register_group(fake, first)                       # a second arena on the same group: nothing is dropped
+    assert fake._group_name_to_store["1"] is store_a
+    second = types.SimpleNamespace(group_name="1")            # another topology, the counter started again
+    nvlink._register_group(fake, second)
+    assert fake._group_name_to_store["1"] is not store_a and calls == ["1", "1", "1"]
+    nvlink._GROUP_OF_NAME.clear()
