@@ -108,6 +108,11 @@ def _sharded_parameters(model, archi, model_config, manager, oc):
     if manager is None or manager.get_rank() == 0:
         print(f"[FSDP] optimizer_config={oc} {sharder.describe()}, wrapper_cfg={G.FSDP_WRAPPER_CFG}, "
               f"sampling_wrapper_cfg={int(archi.get('FSDP_SAMPLING_WRAPPER_CFG', 0) or 0)}", flush=True)
+    if G.DEBUG_GRAD_HOOK and next(model.parameters()).is_cuda:
+        # on CUDA the kernels write gradients in place and no autograd hook fires: report when a unit is left
+        from ..runtime.grad_debug import report_unit_gradients
+
+        sharder.observe_gradients(report_unit_gradients)
     opt = ShardedParamAdamW(sharder, lr=float(model_config.get("learning_rate", 1e-4)), betas=(0.9, 0.95), weight_decay=0.1,
                             manager=manager)
     opt.global_step = 0

@@ -110,6 +110,7 @@ class ShardedUnit:
         self.in_backward = False
         self._pending: list = []
         self._reducing: list = []     # (handle, range, received slice) of reduce-scatters in flight
+        self.gradient_observer = None  # callable(unit) run before the unit's gradients are reduced (debug reports)
         self.gathers = 0              # counters for tests and reports
         self.reductions = 0
         self.release()
@@ -193,6 +194,8 @@ class ShardedUnit:
             return
         if not self.grad_live:
             return
+        if self.gradient_observer is not None:
+            self.gradient_observer(self)          # whole-parameter gradients exist until the reduction below
         g = self.arena.grad
         with torch.no_grad():
             for r in self.ranges:
@@ -474,6 +477,11 @@ class ParamSharder:
         return (f"[param sharding] units={len(self.units)} (+root={self.root is not None}), "
                 f"elements total={self.total_numel()} owned={self.owned_numel()}, group sizes={sizes}, "
                 f"prefetch_policy={self.prefetch}")
+
+    def observe_gradients(self, callback) -> None:
+        """``callback(unit)`` runs for every unit just before its gradients are reduce-scattered."""
+        for u in self.all_units():
+            u.gradient_observer = callback
 
     def remove_hooks(self) -> None:
         for h in self._hooks:

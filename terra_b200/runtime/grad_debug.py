@@ -94,13 +94,13 @@ def install_grad_hooks(model, limit: Optional[int] = None, printer=print):
 _arena_lines = {"n": 0}
 
 
-def report_arena_gradients(model, limit: Optional[int] = None, printer=print) -> List[str]:
-    """Per-parameter gradient sums from the flat gradient arena (``DEBUG_GRAD_HOOK=1`` on CUDA, where gradients are
-    accumulated in place by the kernels and autograd hooks do not fire). At most ``limit`` lines over the run."""
+def report_named_gradients(named, limit: Optional[int] = None, printer=print) -> List[str]:
+    """One ``[grad hook] name: sum`` line per ``(name, parameter)`` that has a gradient, at most ``limit`` lines over the
+    run (shared with the other reports), with one device-to-host transfer."""
     limit = G.DEBUG_GRAD_HOOK_PRINT_LIMIT if limit is None else limit
     if _arena_lines["n"] >= limit:
         return []
-    named = [(n, p) for n, p in model.named_parameters() if p.requires_grad and _grad_of(p) is not None]
+    named = [(n, p) for n, p in named if p.requires_grad and _grad_of(p) is not None]
     if not named:
         return []
     sums = torch.stack([_grad_of(p).detach().double().sum() for _, p in named]).cpu()      # one transfer
@@ -113,3 +113,16 @@ def report_arena_gradients(model, limit: Optional[int] = None, printer=print) ->
     for ln in lines:
         printer(ln)
     return lines
+
+
+def report_arena_gradients(model, limit: Optional[int] = None, printer=print) -> List[str]:
+    """Per-parameter gradient sums from the flat gradient arena (``DEBUG_GRAD_HOOK=1`` on CUDA, where gradients are
+    accumulated in place by the kernels and autograd hooks do not fire). At most ``limit`` lines over the run."""
+    return report_named_gradients(model.named_parameters(), limit, printer)
+
+
+def report_unit_gradients(unit, limit: Optional[int] = None, printer=print) -> List[str]:
+    """The same for one unit of sharded parameters, called when the backward pass leaves the unit: its whole-parameter
+    gradients exist only until the reduce-scatter that follows (the reference prints per-parameter sums out of FSDP's
+    flat shards at the same point: core/runtime/run_model.py:107-195)."""
+    return report_named_gradients(zip(unit.arena.names, unit.arena.params), limit, printer)

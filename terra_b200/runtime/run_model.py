@@ -90,10 +90,10 @@ def one_step_train(task_type, model_type, model, engine, optimizer, required_ten
                       dp_average=not hasattr(model, "module"))
     tsd = task_specific_data_dict or {}
     sharded = getattr(model.module if hasattr(model, "module") else model, "_param_sharder", None) is not None
-    if sharded and (tsd.get("show_gradient_flag") or (on_cuda and G.DEBUG_GRAD_HOOK)) and not getattr(one_step_train, "_told", False):
+    if sharded and tsd.get("show_gradient_flag") and not getattr(one_step_train, "_told", False):
         one_step_train._told = True
         print("[grad debug] parameters are sharded: whole-parameter gradients exist only inside the backward pass; "
-              "the after-backward gradient reports are skipped", flush=True)
+              "show_gradient_flag is skipped (DEBUG_GRAD_HOOK reports them unit by unit)", flush=True)
     if not sharded and tsd.get("show_gradient_flag") and getattr(optimizer, "global_step", 0) == int(tsd.get("test_iter_num", -1)) - 1:
         from .grad_debug import show_gradient
 

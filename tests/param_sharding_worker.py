@@ -143,6 +143,9 @@ def main():
     assert sharder.resident_bytes() == 0, "nothing but the owned slices exists between steps"
     assert sharder.owned_numel() * world == sharder.total_numel() >= total
 
+    from terra_b200.runtime.grad_debug import report_unit_gradients
+    observed, lines = [], []
+    sharder.observe_gradients(lambda u: (observed.append(u.name), report_unit_gradients(u, limit=10 ** 9, printer=lines.append)))
     peak = [0]
 
     def watch(mod, args):
@@ -212,7 +215,8 @@ def main():
     if rank == 0:
         print("RESULT " + json.dumps(dict(
             worst=worst, total_bytes=4 * sharder.total_numel(), peak_bytes=peak[0], units=len(sharder.units),
-            gathers=[u.gathers for u in units], reductions=[u.reductions for u in units])), flush=True)
+            gathers=[u.gathers for u in units], reductions=[u.reductions for u in units], observed=len(observed),
+            lines=len(lines), first_line=lines[0])), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -54,6 +54,10 @@ def test_sharded_parameters_train_like_adamw_on_the_summed_loss(nproc, mode):
         # kept between forward and backward: one gather per training step (the evaluation pass gathers once more)
         assert root == 6 and all(g == 6 for g in blocks), res
     assert all(r == 5 * passes for r in res["reductions"][:-1]) and res["reductions"][-1] == 5
+    # the gradient observer (the DEBUG_GRAD_HOOK report of sharded parameters) ran once per reduction, with one line per
+    # parameter that had a gradient
+    assert res["observed"] == sum(res["reductions"]) and res["lines"] >= res["observed"], res
+    assert res["first_line"].startswith("[grad hook] "), res
     if not mode.get("whole_model") and not mode.get("recompute"):
         # values and gradients of at most two units (the running one and a prefetched neighbour) next to the root's
         assert res["peak_bytes"] < 2 * res["total_bytes"] * (0.5 if mode.get("prefetch") else 0.4), res
