@@ -105,6 +105,26 @@ def main(argv=None):
         if mem_prof > 0 and timeline.events:
             # CSV, summary, event table and plot as the MEMORY_TIMELINE_WRITE_* switches ask
             timeline.write_outputs(os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline"), "rank0")
+        if not args.quiet_metrics:
+            # the closing report of the reference's harness (train_scripts/test_pretrain.py:671-696)
+            counts = facts["parameter_count"]
+            print("all_parameters", counts["post_wrap_local_parameter_counts_by_rank"])
+            print("all_pre_wrap_parameters", counts["pre_wrap_parameter_counts_by_rank"])
+            print("parameter_count_summary", counts)
+            print("all_mem_peak_last", facts["peak_memory_last_by_rank"])
+            print("all_time_peak", facts["step_time_last_by_rank"])
+            # the profiler's count where it ran; the kernels' FLOPs are invisible to it, so the closed form otherwise
+            per_step = flops_summary.local_flops_per_step if flops_summary.enabled else flops / max(1, s.world // max(1, s.dp))
+            print("-----------------------------Accuracy------------------------------")
+            for r in rows:
+                print("iter", r["iter"], r["output_dtype"], "sum:", r["output_sum"], "loss", r["loss"])
+            print("-----------------------------Per-step memory------------------------------")
+            for r in rows:
+                print("iter", r["iter"], "peak_memory", r["peak_memory_mb"])
+            print("-----------------------------Per-step time and FLOPS------------------------------")
+            for r in rows:
+                print("iter", r["iter"], f"Total Time  : {r['step_time_s'] * 1000:.3f} ms",
+                      f"FLOPS : {per_step / r['step_time_s'] / 1e12:.3f} TFLOPS", flush=True)
     s.close()
     return rows
 
