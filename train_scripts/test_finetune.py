@@ -190,6 +190,34 @@ def main(argv=None):
                                    recompute=s.model.recompute_scheduler.summary()))
         if mem_prof > 0 and timeline.events:
             timeline.write_outputs(os.environ.get("MEMORY_TIMELINE_OUTPUT_DIR", "./log/memory_timeline"), "finetune_rank0")
+        if not args.quiet_metrics:
+            # the closing report of the reference's harness (train_scripts/test_finetune.py:1240-1267)
+            print("all_parameters", facts["parameter_count"]["post_wrap_local_parameter_counts_by_rank"])
+            print("all_mem_peak_last", facts["peak_memory_last_by_rank"])
+            print("all_time_peak", facts["step_time_last_by_rank"])
+            if flops_summary.enabled:
+                prof.print_top_ops(20)
+                print("local_FLOPs_per_step", flops_summary.local_flops_per_step)
+                print("world_FLOPs_per_step", flops_summary.world_flops_per_step)
+                print("world_avg_FLOPs_per_step", flops_summary.world_avg_flops_per_step)
+            per_step = flops_summary.local_flops_per_step if flops_summary.enabled else analytic_flops * lead / max(1, s.world // max(1, s.dp))
+            print("-----------------------------Accuracy------------------------------")
+            for r in rows:
+                print("iter", r["iter"], r["output_dtype"], "sum:", r["output_sum"], "loss", r["loss"])
+            print("-----------------------------Per-step memory------------------------------")
+            for r in rows:
+                print("iter", r["iter"], "peak_memory", r["peak_memory_mb"])
+            print("-----------------------------Per-step time and FLOPS------------------------------")
+            for r in rows:
+                print("iter", r["iter"], f"Total Time  : {r['step_time_s'] * 1000:.3f} ms",
+                      f"FLOPS : {per_step / r['step_time_s'] / 1e12:.3f} TFLOPS",
+                      f"forward Time  : {(r['forward_time_s'] or 0.0) * 1000:.3f} ms",
+                      f"load data time {(r['load_data_time_s'] or 0.0) * 1000:.3f} ms")
+            print("-----------------------------Per-step time break down------------------------------")
+            for r in rows:
+                fwd = r["forward_time_s"] or 0.0
+                print("iter", r["iter"], f"Total Time  : {r['step_time_s'] * 1000:.3f} ms", f"forward Time  : {fwd * 1000:.3f} ms",
+                      f"Rest Time  : {(r['step_time_s'] - fwd) * 1000:.3f} ms", flush=True)
     s.close()
     return rows
 
