@@ -61,7 +61,7 @@ def main(argv=None):
     timeline = CudaMemoryTimeline(s.device if s.device.type == "cuda" else None, enabled=mem_prof > 0)
     use_prof = G.ENABLE_TORCH_PROF and not args.disable_torch_prof and not G.DISABLE_TORCH_PROF
     prof = TorchFlopsProfiler(G.TORCH_PROF_STEP_LIST, enabled=use_prof, rank=s.rank,
-                              trace_dir="./log/torch_prof" if G.TORCH_PROF_WRITE_TRACE else None)
+                              trace_dir="./log/profiler/rank0" if G.TORCH_PROF_WRITE_TRACE else None)
     loader = s.pretrain_loader(status=0)
     rows = []
     it = iter(loader)
