@@ -29,7 +29,7 @@ PRETRAIN_DEFAULTS = {
     "num_pre_train_epochs": 1, "save_interval_epochs": 1, "max_train_steps_per_epoch": None, "precision": "bf16",
     "half_model": False, "clip_grad": False, "learning_rate": 1e-4, "warmup_steps": 100, "loss_func": "L1",
     "micro_batch_size": 1, "kaiming_init": True, "optimizer_config": 4, "use_splited_data": True,
-    "use_fake_input": False, "fake_input_random": True, "fake_input_seed": 2025, "num_workers": 1,
+    "use_fake_input": False, "fake_input_random": True, "fake_input_seed": 1234, "num_workers": 1,
 }
 FINETUNE_DEFAULTS = dict(PRETRAIN_DEFAULTS, num_finetune_epochs=1, finetune_lead_time=2, finetune_loss_reduction="mean",
                          save_interval_steps=0, ckpt_step=None, trained_model_config_path=None,
@@ -101,7 +101,7 @@ class Session:
                                        c.get("num_workers", c.get("dataloader_num_workers", 1)), manager=self.manager,
                                        model_type=self.model_type, model_archi_params=self.archi, other_params=self.other,
                                        use_fake_input=c["use_fake_input"], fake_input_random=c.get("fake_input_random", True),
-                                       fake_input_seed=c.get("fake_input_seed", 2025), fake_length=int(c.get("fake_length", 64)))
+                                       fake_input_seed=c.get("fake_input_seed", 1234), fake_length=int(c.get("fake_length", 64)))
 
     def finetune_loader(self, lead_time, status=0):
         c = self.cfg
@@ -111,7 +111,7 @@ class Session:
                                                 model_archi_params=self.archi, other_params=self.other,
                                                 use_fake_input=c["use_fake_input"],
                                                 fake_input_random=c.get("fake_input_random", True),
-                                                fake_input_seed=c.get("fake_input_seed", 2025),
+                                                fake_input_seed=c.get("fake_input_seed", 1234),
                                                 fake_length=int(c.get("fake_length", 64)),
                                                 pin_memory=c.get("dataloader_pin_memory", True))
 

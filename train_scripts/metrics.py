@@ -237,7 +237,7 @@ def write_finetune_metrics(session, args, rows: Sequence[dict], lead_rows: Seque
         record[k] = meta[k]
     record.update({"lead_time": lead, "finetune_loss_reduction": reduction, "micro_batch_size": c.get("micro_batch_size"),
                    "use_fake_input": c.get("use_fake_input"), "fake_input_random": c.get("fake_input_random", True),
-                   "fake_input_seed": c.get("fake_input_seed", 2025)})
+                   "fake_input_seed": c.get("fake_input_seed", 1234)})
     record.update(data_path)
     record["num_workers"] = int(c.get("num_workers", c.get("dataloader_num_workers", 1)))
     record["test_iter_num"] = len(rows)
